@@ -1,0 +1,243 @@
+// C ABI, level 1: the FrozenMatmul trait (reference src/frozen.rs:14-25) over host buffers.
+#include "ctx.h"
+#include "../../include/rt_b200.h"
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+void* rt_ctx::get_scratch(int slot, size_t bytes) {
+  if (bytes <= scratch_bytes[slot]) return scratch[slot];
+  if (scratch[slot]) cudaFree(scratch[slot]);
+  scratch[slot] = nullptr;
+  scratch_bytes[slot] = 0;
+  size_t want = bytes + bytes / 4 + 256;
+  if (cudaMalloc(&scratch[slot], want) != cudaSuccess) return nullptr;
+  scratch_bytes[slot] = want;
+  return scratch[slot];
+}
+
+rt_status rt_ctx::check_device_status(const char* where) {
+  cudaError_t e = cudaMemcpyAsync(status_host, status_dev, sizeof(int), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return cuda_fail(e, where);
+  int s = *status_host;
+  if (s == 0) return RT_OK;
+  cudaMemsetAsync(status_dev, 0, sizeof(int), stream);
+  char buf[160];
+  if (s == RT_ERR_BAD_INDEX) {
+    snprintf(buf, sizeof buf, "%s: index out of range on device", where);
+    err = buf;
+    return RT_ERR_BAD_INDEX;
+  }
+  snprintf(buf, sizeof buf, "%s: device wait timed out at site %d", where, s);
+  err = buf;
+  return RT_ERR_DEVICE_WAIT_TIMEOUT;
+}
+
+extern "C" {
+
+rt_status rt_ctx_create(int device, rt_ctx** out) {
+  if (!out) return RT_ERR_BAD_ARG;
+  *out = nullptr;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) return RT_ERR_CUDA;
+  rt_ctx* c = new rt_ctx();
+  c->device = device;
+  cudaError_t e = cudaSetDevice(device);
+  cudaDeviceProp prop;
+  if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, device);
+  if (e == cudaSuccess && prop.major != 10) {
+    fprintf(stderr, "rt_b200: device %d is sm_%d%d; this library is built for sm_100a only\n", device, prop.major,
+            prop.minor);
+    delete c;
+    return RT_ERR_CUDA;
+  }
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking);
+  c->stream = c->own_stream;
+  if (e == cudaSuccess) e = cudaMalloc(&c->status_dev, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(c->status_dev, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaMallocHost(&c->status_host, sizeof(int));
+  if (e != cudaSuccess || rt::qgemm_init() != RT_OK) {
+    fprintf(stderr, "rt_b200: context creation failed: %s\n", cudaGetErrorString(e));
+    delete c;
+    return RT_ERR_CUDA;
+  }
+  c->num_sms = prop.multiProcessorCount;
+  *out = c;
+  return RT_OK;
+}
+
+void rt_ctx_destroy(rt_ctx* c) {
+  if (!c) return;
+  cudaSetDevice(c->device);
+  if (c->stream) cudaStreamSynchronize(c->stream);
+  for (int i = 0; i < 4; ++i)
+    if (c->scratch[i]) cudaFree(c->scratch[i]);
+  if (c->status_dev) cudaFree(c->status_dev);
+  if (c->status_host) cudaFreeHost(c->status_host);
+  if (c->own_stream) cudaStreamDestroy(c->own_stream);
+  delete c;
+}
+
+const char* rt_last_error(const rt_ctx* c) { return c ? c->err.c_str() : "null context"; }
+
+rt_status rt_ctx_synchronize(rt_ctx* c) {
+  if (!c) return RT_ERR_BAD_ARG;
+  return c->check_device_status("rt_ctx_synchronize");
+}
+
+rt_status rt_ctx_set_stream(rt_ctx* c, void* s) {
+  if (!c) return RT_ERR_BAD_ARG;
+  c->user_stream = (cudaStream_t)s;
+  c->stream = s ? (cudaStream_t)s : c->own_stream;
+  return RT_OK;
+}
+
+void* rt_ctx_stream(rt_ctx* c) { return c ? (void*)c->stream : nullptr; }
+
+size_t rt_ggml_nbytes(int t, size_t rows, size_t cols) {
+  int be = rt::fmt_block_elems(t), bb = rt::fmt_block_bytes(t);
+  if (bb == 0 || cols % be != 0) return 0;
+  return rows * (cols / be) * bb;
+}
+
+rt_status rt_frozen_create(rt_ctx* c, int ggml_type, size_t rows, size_t cols, const void* packed_host,
+                           size_t nbytes, rt_frozen** out) {
+  if (!c || !out || !packed_host) return RT_ERR_BAD_ARG;
+  *out = nullptr;
+  if (rt::fmt_block_bytes(ggml_type) == 0) return c->fail(RT_ERR_UNSUPPORTED_TYPE, "unsupported ggml tensor type");
+  if (rows == 0 || cols == 0 || rows > (1u << 30) || cols > (1u << 30)) return c->fail(RT_ERR_BAD_SHAPE, "empty or oversized weight");
+  const int be = rt::fmt_block_elems(ggml_type);
+  if (cols % be != 0) return c->fail(RT_ERR_BAD_SHAPE, "row length is not a multiple of the block size");
+  if (rt::fmt_is_16bit(ggml_type) && cols % 8 != 0) return c->fail(RT_ERR_BAD_SHAPE, "16-bit rows must be a multiple of 8 long");
+  if (nbytes != rt_ggml_nbytes(ggml_type, rows, cols)) return c->fail(RT_ERR_BAD_SHAPE, "nbytes does not match type and shape");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  rt_frozen* f = new rt_frozen();
+  f->ctx = c;
+  rt::QWeight& w = f->w;
+  w.fmt = ggml_type;
+  w.rows = (int)rows;
+  w.cols = (int)cols;
+  w.ggml_nbytes = nbytes;
+  cudaError_t e;
+  if (rt::fmt_is_16bit(ggml_type)) {
+    e = cudaMalloc(&w.dense16, nbytes);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w.dense16, packed_host, nbytes, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    w.dev_nbytes = nbytes;
+  } else {
+    w.nbr = (int)((rows + 127) / 128) * 2;
+    w.nbk = (int)((cols + 127) / 128) * 2;
+    w.dev_nbytes = (size_t)w.nbr * w.nbk * rt::fmt_brick_bytes(ggml_type);
+    void* raw = nullptr;
+    e = cudaMalloc(&w.bricks, w.dev_nbytes);
+    if (e == cudaSuccess) e = cudaMalloc(&raw, nbytes);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(raw, packed_host, nbytes, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) {
+      rt::launch_repack((const uint8_t*)raw, w, c->stream);
+      e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (raw) cudaFree(raw);
+  }
+  if (e != cudaSuccess) {
+    rt_frozen_destroy(f);
+    return c->cuda_fail(e, "rt_frozen_create");
+  }
+  *out = f;
+  return RT_OK;
+}
+
+void rt_frozen_destroy(rt_frozen* f) {
+  if (!f) return;
+  cudaSetDevice(f->ctx->device);
+  if (f->w.bricks) cudaFree(f->w.bricks);
+  if (f->w.dense16) cudaFree(f->w.dense16);
+  delete f;
+}
+
+size_t rt_frozen_out_dim(const rt_frozen* f) { return f ? (size_t)f->w.rows : 0; }
+size_t rt_frozen_in_dim(const rt_frozen* f) { return f ? (size_t)f->w.cols : 0; }
+size_t rt_frozen_nbytes(const rt_frozen* f) { return f ? f->w.ggml_nbytes : 0; }
+
+static rt_status frozen_matmul_host(rt_frozen* f, int dir, const float* in_host, size_t t, float* out_host,
+                                    bool accumulate) {
+  if (!f || !in_host || !out_host) return RT_ERR_BAD_ARG;
+  rt_ctx* c = f->ctx;
+  if (t == 0) return RT_OK;
+  if (t > (1u << 24)) return c->fail(RT_ERR_BAD_SHAPE, "too many rows");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  const size_t in_dim = dir == rt::QG_FWD ? f->w.cols : f->w.rows;
+  const size_t out_dim = dir == rt::QG_FWD ? f->w.rows : f->w.cols;
+  float* in_f32 = (float*)c->get_scratch(0, t * in_dim * sizeof(float));
+  __nv_bfloat16* in_bf = (__nv_bfloat16*)c->get_scratch(1, t * in_dim * sizeof(__nv_bfloat16));
+  float* out_f32 = (float*)c->get_scratch(2, t * out_dim * sizeof(float));
+  if (!in_f32 || !in_bf || !out_f32) return c->fail(RT_ERR_CUDA, "out of device memory");
+  RT_CUDA(c, cudaMemcpyAsync(in_f32, in_host, t * in_dim * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  if (accumulate)
+    RT_CUDA(c, cudaMemcpyAsync(out_f32, out_host, t * out_dim * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  rt::launch_f32_to_bf16(in_f32, in_bf, t * in_dim, c->stream);
+  rt::QGemmArgs a;
+  a.dir = dir;
+  a.act = in_bf;
+  a.M = (int)t;
+  a.out = out_f32;
+  a.out_dtype = rt::OUT_F32;
+  a.accumulate = accumulate ? 1 : 0;
+  int rc = rt::qgemm_launch(f->w, a, c->status_dev, c->num_sms, c->stream);
+  if (rc) return c->fail(rc, "qgemm launch failed");
+  RT_CUDA(c, cudaMemcpyAsync(out_host, out_f32, t * out_dim * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+  return c->check_device_status("rt_frozen matmul");
+}
+
+rt_status rt_frozen_forward(rt_frozen* f, const float* x_host, size_t t, float* y_host) {
+  return frozen_matmul_host(f, rt::QG_FWD, x_host, t, y_host, false);
+}
+
+rt_status rt_frozen_backward_input(rt_frozen* f, const float* dy_host, size_t t, float* dx_host) {
+  return frozen_matmul_host(f, rt::QG_BWD, dy_host, t, dx_host, true);
+}
+
+static rt_status frozen_matmul_dev(rt_frozen* f, int dir, const void* in_dev, size_t t, void* out_dev, int out_bf16,
+                                   int accumulate) {
+  if (!f || !in_dev || !out_dev) return RT_ERR_BAD_ARG;
+  rt_ctx* c = f->ctx;
+  if (t == 0) return RT_OK;
+  if (t > (1u << 24)) return c->fail(RT_ERR_BAD_SHAPE, "too many rows");
+  if (accumulate && out_bf16) return c->fail(RT_ERR_BAD_ARG, "accumulate needs an f32 output");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  rt::QGemmArgs a;
+  a.dir = dir;
+  a.act = (const __nv_bfloat16*)in_dev;
+  a.M = (int)t;
+  a.out = out_dev;
+  a.out_dtype = out_bf16 ? rt::OUT_BF16 : rt::OUT_F32;
+  a.accumulate = accumulate ? 1 : 0;
+  int rc = rt::qgemm_launch(f->w, a, c->status_dev, c->num_sms, c->stream);
+  if (rc) return c->fail(rc, "qgemm launch failed");
+  return RT_OK;
+}
+
+rt_status rt_frozen_forward_dev(rt_frozen* f, const void* x, size_t t, void* y, int y_bf16, int acc) {
+  return frozen_matmul_dev(f, rt::QG_FWD, x, t, y, y_bf16, acc);
+}
+rt_status rt_frozen_backward_input_dev(rt_frozen* f, const void* dy, size_t t, void* dx, int dx_bf16, int acc) {
+  return frozen_matmul_dev(f, rt::QG_BWD, dy, t, dx, dx_bf16, acc);
+}
+
+rt_status rt_frozen_row(rt_frozen* f, size_t r, float* out_host) {
+  if (!f || !out_host) return RT_ERR_BAD_ARG;
+  rt_ctx* c = f->ctx;
+  if (r >= (size_t)f->w.rows) return c->fail(RT_ERR_BAD_INDEX, "row index out of range");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  float* out = (float*)c->get_scratch(2, (size_t)f->w.cols * sizeof(float));
+  int* id = (int*)c->get_scratch(3, sizeof(int));
+  if (!out || !id) return c->fail(RT_ERR_CUDA, "out of device memory");
+  int ri = (int)r;
+  RT_CUDA(c, cudaMemcpyAsync(id, &ri, sizeof(int), cudaMemcpyHostToDevice, c->stream));
+  rt::launch_gather_rows(f->w, id, 1, out, c->status_dev, c->stream);
+  RT_CUDA(c, cudaMemcpyAsync(out_host, out, (size_t)f->w.cols * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+  return c->check_device_status("rt_frozen_row");
+}
+
+}  // extern "C"

@@ -1,0 +1,48 @@
+// Per-GPU context and the opaque handle types behind the C ABI.
+#pragma once
+#include "qformat.cuh"
+#include "rt_internal.h"
+#include <string>
+#include <vector>
+
+struct rt_ctx {
+  int device = 0;
+  int num_sms = 0;
+  cudaStream_t stream = nullptr;       // the stream in use (own_stream unless the host set one)
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t user_stream = nullptr;
+  int* status_dev = nullptr;   // device word the kernels report bounded-wait failures into
+  int* status_host = nullptr;  // pinned mirror
+  std::string err;
+  // grow-only scratch buffers for the host-pointer entry points
+  void* scratch[4] = {nullptr, nullptr, nullptr, nullptr};
+  size_t scratch_bytes[4] = {0, 0, 0, 0};
+
+  rt_status fail(rt_status code, const std::string& msg) {
+    err = msg;
+    return code;
+  }
+  rt_status cuda_fail(cudaError_t e, const char* where) {
+    err = std::string(where) + ": " + cudaGetErrorString(e);
+    return RT_ERR_CUDA;
+  }
+  void* get_scratch(int slot, size_t bytes);
+  // Reads the device status word (after synchronising); maps non-zero to an error.
+  rt_status check_device_status(const char* where);
+};
+
+#define RT_CUDA(ctx, call)                                        \
+  do {                                                            \
+    cudaError_t e__ = (call);                                     \
+    if (e__ != cudaSuccess) return (ctx)->cuda_fail(e__, #call);  \
+  } while (0)
+
+struct rt_frozen {
+  rt_ctx* ctx = nullptr;
+  rt::QWeight w;
+};
+
+namespace rt {
+// small elementwise helpers (ops.cu)
+void launch_f32_to_bf16(const float* in, __nv_bfloat16* out, size_t n, cudaStream_t st);
+}

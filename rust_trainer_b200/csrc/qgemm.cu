@@ -1,0 +1,481 @@
+// Frozen quantised matmul on tcgen05 tensor cores (sm_100a).
+//
+//   forward  (reference src/rie.rs:74-82,  RieFrozen::forward)        Y[M x N]  = X[M x K] . W^T
+//   backward (reference src/rie.rs:84-120, RieFrozen::backward_input) dX[M x K] = dY[M x N] . W
+//
+// both read the SAME packed weight bytes (64x64 bricks of ggml codes, see qformat.cuh); no
+// dequantised copy of W exists in global memory.  The weight is the UMMA "A" operand (128
+// weight rows or columns per tile), the activations are the "B" operand (up to 256 tokens per
+// tile), so the TMEM accumulator is the transposed output tile [128 x tokens].
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      producer : TMA tiles of activations (128B swizzle) + bulk copies of packed bricks
+//   warp 1      MMA      : one thread issues tcgen05.mma (kind::f16, fp32 accumulate in TMEM)
+//   warps 2-5   unpack   : packed bricks -> f16 tile in the UMMA shared-memory layout
+//                          (forward reads it K-major, backward reads the same bytes MN-major)
+//   warps 6-9   epilogue : tcgen05.ld the accumulator (double buffered: 2 x 256 TMEM columns),
+//                          add bias / accumulate, store f32 and/or bf16
+// The LoRA low-rank term is one more contraction chunk fed through the same accumulator.
+#include "ptx.cuh"
+#include "qformat.cuh"
+#include "rt_internal.h"
+#include <stdio.h>
+
+namespace rt {
+
+constexpr int NS = 4;                 // activation / unpacked-weight stages
+constexpr int NR = 3;                 // packed brick-pair stages
+constexpr int ACT_STAGE = 32768;      // 256 tokens x 64 x bf16
+constexpr int W_STAGE = 16384;        // 128 x 64 x 16-bit
+constexpr int RAW_STAGE = 2 * 4352;   // largest brick pair (Q8_0)
+constexpr int QG_THREADS = 320;
+constexpr int OFF_W = NS * ACT_STAGE;
+constexpr int OFF_RAW = OFF_W + NS * W_STAGE;
+constexpr int OFF_BAR = OFF_RAW + NR * RAW_STAGE;
+constexpr int N_BARS = 3 * NS + 2 * NR + 4;
+constexpr int SMEM_BYTES = OFF_BAR + N_BARS * 8 + 16 + 1024;
+
+struct KParams {
+  const uint8_t* bricks;
+  int brick_bytes, nbk, fmt, wbf16;
+  int dir, out_rows, M, TN;
+  int n_main, lora_mmas;
+  int n_row_tiles, n_tok_tiles;
+  void* out;
+  __nv_bfloat16* out2;
+  int out_dtype, accumulate, ld_out;
+  const float* bias;
+  uint32_t idesc_main, idesc_lora;
+  int* status;
+};
+
+// ------------------------------------------------------------------ unpackers
+__device__ __forceinline__ void store_chunk(uint8_t* dst, int r, int c, uint32_t a, uint32_t b, uint32_t c2,
+                                            uint32_t d) {
+  *(uint4*)(dst + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(a, b, c2, d);
+}
+template <bool WBF16>
+__device__ __forceinline__ uint32_t fin(__half2 h) {
+  if (WBF16) {
+    __nv_bfloat162 b = __float22bfloat162_rn(__half22float2(h));
+    return *(uint32_t*)&b;
+  }
+  return *(uint32_t*)&h;
+}
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t x) { return *(__half2*)&x; }
+
+template <bool WBF16>
+__device__ __forceinline__ void unpack_q4_0(const uint8_t* brick, int t, uint8_t* dst) {
+  const uint4 q = *(const uint4*)(brick + t * 16);
+  const __half2 d2 = __half2half2(((const __half*)(brick + 2048))[t]);
+  const __half2 off = __floats2half2_rn(1032.f, 1032.f);  // 1024 (magic) + 8 (code bias)
+  const int r = t >> 1, cb = (t & 1) * 4;
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t o[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      uint32_t x = ((w[j] >> (4 * p)) & 0x000F000Fu) | 0x64006400u;
+      o[p] = fin<WBF16>(__hmul2(__hsub2(u32_as_h2(x), off), d2));
+    }
+    store_chunk(dst, r, cb + j, o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <bool WBF16>
+__device__ __forceinline__ void unpack_q8_0(const uint8_t* brick, int t, uint8_t* dst) {
+  const uint4 qa = *(const uint4*)(brick + t * 32);
+  const uint4 qb = *(const uint4*)(brick + t * 32 + 16);
+  const __half2 d2 = __half2half2(((const __half*)(brick + 4096))[t]);
+  const __half2 off = __floats2half2_rn(1152.f, 1152.f);  // 1024 (magic) + 128 (stored offset)
+  const int r = t >> 1, cb = (t & 1) * 4;
+  const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t o[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      uint32_t x = __byte_perm(w[2 * j + (p >> 1)], 0x64646464u, (p & 1) ? 0x4342 : 0x4140);
+      o[p] = fin<WBF16>(__hmul2(__hsub2(u32_as_h2(x), off), d2));
+    }
+    store_chunk(dst, r, cb + j, o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <bool WBF16>
+__device__ __forceinline__ void unpack_q4_k(const uint8_t* brick, int t, uint8_t* dst) {
+  const uint4 q = *(const uint4*)(brick + t * 16);
+  const __half2 dd = ((const __half2*)(brick + 2048))[t >> 1];
+  const uchar2 sm = ((const uchar2*)(brick + 2304))[t];
+  const float2 ddf = __half22float2(dd);
+  const __half2 dsc = __half2half2(__float2half_rn(ddf.x * (float)sm.x));
+  const __half2 ndm = __half2half2(__float2half_rn(-ddf.y * (float)sm.y));
+  const __half2 off = __floats2half2_rn(1024.f, 1024.f);
+  const int r = t >> 1, cb = (t & 1) * 4;
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t o[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      uint32_t x = ((w[j] >> (4 * p)) & 0x000F000Fu) | 0x64006400u;
+      o[p] = fin<WBF16>(__hfma2(__hsub2(u32_as_h2(x), off), dsc, ndm));
+    }
+    store_chunk(dst, r, cb + j, o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <bool WBF16>
+__device__ __forceinline__ void unpack_q6_k(const uint8_t* brick, int t, uint8_t* dst) {
+  const uint4 lo = *(const uint4*)(brick + t * 16);
+  const uint2 hi = *(const uint2*)(brick + 2048 + t * 8);
+  const char2 sc = ((const char2*)(brick + 3072))[t];
+  const float d = __half2float(((const __half*)(brick + 3328))[t >> 1]);
+  const __half2 ds0 = __half2half2(__float2half_rn(d * (float)sc.x));
+  const __half2 ds1 = __half2half2(__float2half_rn(d * (float)sc.y));
+  const __half2 off = __floats2half2_rn(1056.f, 1056.f);  // 1024 (magic) + 32 (code bias)
+  const int r = t >> 1, cb = (t & 1) * 4;
+  const uint32_t w[4] = {lo.x, lo.y, lo.z, lo.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t hw = (j < 2) ? hi.x : hi.y;
+    if (j & 1) hw = __funnelshift_r(hw, hw, 8);
+    const __half2 ds = (j < 2) ? ds0 : ds1;
+    uint32_t o[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      uint32_t x = ((w[j] >> (4 * p)) & 0x000F000Fu) | ((hw >> (2 * p)) & 0x00300030u) | 0x64006400u;
+      o[p] = fin<WBF16>(__hmul2(__hsub2(u32_as_h2(x), off), ds));
+    }
+    store_chunk(dst, r, cb + j, o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <bool WBF16>
+__device__ __forceinline__ void unpack_pair(int fmt, const uint8_t* raw, int bb, int t, uint8_t* dst) {
+  switch (fmt) {
+    case GGML_Q4_0: unpack_q4_0<WBF16>(raw, t, dst); unpack_q4_0<WBF16>(raw + bb, t, dst + 8192); break;
+    case GGML_Q8_0: unpack_q8_0<WBF16>(raw, t, dst); unpack_q8_0<WBF16>(raw + bb, t, dst + 8192); break;
+    case GGML_Q4_K: unpack_q4_k<WBF16>(raw, t, dst); unpack_q4_k<WBF16>(raw + bb, t, dst + 8192); break;
+    case GGML_Q6_K: unpack_q6_k<WBF16>(raw, t, dst); unpack_q6_k<WBF16>(raw + bb, t, dst + 8192); break;
+  }
+}
+
+// ------------------------------------------------------------------ kernel
+__global__ void __launch_bounds__(QG_THREADS, 1)
+qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_w16,
+             const __grid_constant__ CUtensorMap tm_lact, const __grid_constant__ CUtensorMap tm_lw,
+             const KParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sAct = smem;
+  uint8_t* sW = smem + OFF_W;
+  uint8_t* sRaw = smem + OFF_RAW;
+  uint64_t* bars = (uint64_t*)(smem + OFF_BAR);
+  uint64_t* full = bars;                   // [NS] activations (+ TMA'd weight tile) landed
+  uint64_t* w_ready = bars + NS;           // [NS] unpack warps done with the weight tile
+  uint64_t* stage_empty = bars + 2 * NS;   // [NS] MMAs reading the stage have completed
+  uint64_t* raw_full = bars + 3 * NS;      // [NR]
+  uint64_t* raw_empty = raw_full + NR;     // [NR]
+  uint64_t* acc_full = raw_empty + NR;     // [2]
+  uint64_t* acc_empty = acc_full + 2;      // [2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + N_BARS);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool is16 = fmt_is_16bit(p.fmt);
+  const int n_steps = p.n_main + (p.lora_mmas > 0 ? 1 : 0);
+  const int n_tiles = p.n_row_tiles * p.n_tok_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NS; ++i) { mbar_init(&full[i], 1); mbar_init(&w_ready[i], 128); mbar_init(&stage_empty[i], 1); }
+    for (int i = 0; i < NR; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 128); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128); }
+    mbar_fence_init();
+    prefetch_tmap(&tm_act);
+    prefetch_tmap(&tm_w16);
+    prefetch_tmap(&tm_lact);
+    prefetch_tmap(&tm_lw);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0, rit = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int r0 = (tile % p.n_row_tiles) * 128, m0 = (tile / p.n_row_tiles) * p.TN;
+        for (int s = 0; s < n_steps && ok; ++s, ++it) {
+          const int st = it % NS;
+          const uint32_t ph = (it / NS) & 1;
+          if (!mbar_wait(&stage_empty[st], ph ^ 1, p.status, 101)) { ok = false; break; }
+          const bool lora = s >= p.n_main;
+          uint8_t* a_dst = sAct + st * ACT_STAGE;
+          uint8_t* w_dst = sW + st * W_STAGE;
+          mbar_expect_tx(&full[st], (uint32_t)p.TN * 128u + ((is16 || lora) ? (uint32_t)W_STAGE : 0u));
+          if (!lora) {
+            tma_load_2d(a_dst, &tm_act, s * 64, m0, &full[st]);
+            if (is16) {
+              if (p.dir == QG_FWD) {
+                tma_load_2d(w_dst, &tm_w16, s * 64, r0, &full[st]);
+                tma_load_2d(w_dst + 8192, &tm_w16, s * 64, r0 + 64, &full[st]);
+              } else {
+                tma_load_2d(w_dst, &tm_w16, r0, s * 64, &full[st]);
+                tma_load_2d(w_dst + 8192, &tm_w16, r0 + 64, s * 64, &full[st]);
+              }
+            } else {
+              const int rs = rit % NR;
+              const uint32_t rph = (rit / NR) & 1;
+              if (!mbar_wait(&raw_empty[rs], rph ^ 1, p.status, 102)) { ok = false; break; }
+              const uint32_t bb = (uint32_t)p.brick_bytes;
+              mbar_expect_tx(&raw_full[rs], 2 * bb);
+              const int tr2 = (r0 >> 6);
+              const uint8_t *b0, *b1;
+              if (p.dir == QG_FWD) {
+                b0 = p.bricks + ((size_t)tr2 * p.nbk + s) * bb;
+                b1 = p.bricks + ((size_t)(tr2 + 1) * p.nbk + s) * bb;
+              } else {
+                b0 = p.bricks + ((size_t)s * p.nbk + tr2) * bb;
+                b1 = b0 + bb;
+              }
+              bulk_load_1d(sRaw + rs * RAW_STAGE, b0, bb, &raw_full[rs]);
+              bulk_load_1d(sRaw + rs * RAW_STAGE + bb, b1, bb, &raw_full[rs]);
+              ++rit;
+            }
+          } else {
+            tma_load_2d(a_dst, &tm_lact, 0, m0, &full[st]);
+            if (p.dir == QG_FWD) {
+              tma_load_2d(w_dst, &tm_lw, 0, r0, &full[st]);
+              tma_load_2d(w_dst + 8192, &tm_lw, 0, r0 + 64, &full[st]);
+            } else {
+              tma_load_2d(w_dst, &tm_lw, r0, 0, &full[st]);
+              tma_load_2d(w_dst + 8192, &tm_lw, r0 + 64, 0, &full[st]);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
+        const int acc = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], aph ^ 1, p.status, 301)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * 256;
+        for (int s = 0; s < n_steps; ++s, ++it) {
+          const int st = it % NS;
+          const uint32_t ph = (it / NS) & 1;
+          if (!mbar_wait(&full[st], ph, p.status, 302)) { ok = false; break; }
+          if (!mbar_wait(&w_ready[st], ph, p.status, 303)) { ok = false; break; }
+          tc_fence_after();
+          const bool lora = s >= p.n_main;
+          const int nm = lora ? p.lora_mmas : 4;
+          const uint32_t idesc = lora ? p.idesc_lora : p.idesc_main;
+          const uint32_t a_base = smem_u32(sW + st * W_STAGE);
+          const uint32_t b_base = smem_u32(sAct + st * ACT_STAGE);
+          for (int kk = 0; kk < nm; ++kk) {
+            const uint64_t adesc = (p.dir == QG_FWD) ? umma_desc_sw128(a_base + kk * 32, 16, 1024)
+                                                     : umma_desc_sw128(a_base + kk * 2048, 8192, 1024);
+            const uint64_t bdesc = umma_desc_sw128(b_base + kk * 32, 16, 1024);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (uint32_t)((s | kk) != 0));
+          }
+          umma_commit(&stage_empty[st]);
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------ unpack
+    const int t = threadIdx.x - 64;
+    uint32_t it = 0, rit = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      for (int s = 0; s < n_steps; ++s, ++it) {
+        const int st = it % NS;
+        const uint32_t ph = (it / NS) & 1;
+        if (!mbar_wait(&stage_empty[st], ph ^ 1, p.status, 201)) { ok = false; break; }
+        if (!is16 && s < p.n_main) {
+          const int rs = rit % NR;
+          const uint32_t rph = (rit / NR) & 1;
+          if (!mbar_wait(&raw_full[rs], rph, p.status, 202)) { ok = false; break; }
+          const uint8_t* raw = sRaw + rs * RAW_STAGE;
+          uint8_t* dst = sW + st * W_STAGE;
+          if (p.wbf16) unpack_pair<true>(p.fmt, raw, p.brick_bytes, t, dst);
+          else unpack_pair<false>(p.fmt, raw, p.brick_bytes, t, dst);
+          fence_proxy_async_smem();
+          mbar_arrive(&raw_empty[rs]);
+          ++rit;
+        }
+        mbar_arrive(&w_ready[st]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int wq = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
+      const int r0 = (tile % p.n_row_tiles) * 128, m0 = (tile / p.n_row_tiles) * p.TN;
+      const int acc = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], aph, p.status, 401)) { ok = false; break; }
+      tc_fence_after();
+      const int row = r0 + wq * 32 + lane;
+      const bool row_ok = row < p.out_rows;
+      const float bias_v = (p.bias != nullptr && row_ok) ? p.bias[row] : 0.f;
+      for (int c = 0; c < p.TN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(wq * 32) << 16) + c * 32, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int tok = m0 + c * 32 + j;
+            if (tok < p.M) {
+              const size_t idx = (size_t)tok * p.ld_out + row;
+              float val = __uint_as_float(v[j]) + bias_v;
+              if (p.out_dtype == OUT_F32) {
+                float* o = (float*)p.out;
+                if (p.accumulate) val += o[idx];
+                o[idx] = val;
+              } else {
+                ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(val);
+              }
+              if (p.out2) p.out2[idx] = __float2bfloat16_rn(val);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (*(volatile int*)p.status != 0) {
+    // A wait gave up somewhere: give copies already in flight time to land before smem goes away.
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static PFN_encodeTiled g_encode = nullptr;
+
+size_t qgemm_smem_bytes() { return SMEM_BYTES; }
+
+int qgemm_init() {
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn)
+      return RT_ERR_CUDA;
+    g_encode = (PFN_encodeTiled)fn;
+  }
+  if (cudaFuncSetAttribute(qgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    return RT_ERR_CUDA;
+  return RT_OK;
+}
+
+// 2-D row-major 16-bit matrix [rows x cols]; box = box_cols x box_rows, 128-byte swizzle.
+static int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                    uint32_t box_rows, bool is_bf16) {
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(m, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RT_OK : RT_ERR_CUDA;
+}
+
+static int g_force_wbf16 = -1;
+
+int qgemm_launch(const QWeight& w, const QGemmArgs& a, int* status_dev, int num_sms, cudaStream_t st) {
+  if (!g_encode) {
+    int rc = qgemm_init();
+    if (rc) return rc;
+  }
+  if (g_force_wbf16 < 0) {
+    const char* e = getenv("RT_B200_WBF16");
+    g_force_wbf16 = (e && e[0] == '1') ? 1 : 0;
+  }
+  if (a.M <= 0) return RT_OK;
+  const bool is16 = fmt_is_16bit(w.fmt);
+  const int contract = a.dir == QG_FWD ? w.cols : w.rows;
+  const int out_rows = a.dir == QG_FWD ? w.rows : w.cols;
+  if (contract % 8 != 0 || (is16 && w.cols % 8 != 0)) return RT_ERR_BAD_SHAPE;
+  if (a.accumulate && a.out_dtype != OUT_F32) return RT_ERR_BAD_ARG;
+  if (a.lora.rank > 64 || (a.lora.rank > 0 && (!a.lora.act || !a.lora.w))) return RT_ERR_BAD_ARG;
+
+  KParams p;
+  p.bricks = w.bricks;
+  p.brick_bytes = fmt_brick_bytes(w.fmt);
+  p.nbk = w.nbk;
+  p.fmt = w.fmt;
+  p.wbf16 = (!is16 && g_force_wbf16) ? 1 : 0;
+  p.dir = a.dir;
+  p.out_rows = out_rows;
+  p.M = a.M;
+  p.TN = a.M > 128 ? 256 : a.M > 64 ? 128 : a.M > 32 ? 64 : 32;
+  p.n_main = (contract + 63) / 64;
+  p.lora_mmas = a.lora.rank > 0 ? (a.lora.rank + 15) / 16 : 0;
+  p.n_row_tiles = (out_rows + 127) / 128;
+  p.n_tok_tiles = (a.M + p.TN - 1) / p.TN;
+  p.out = a.out;
+  p.out2 = (__nv_bfloat16*)a.out2;
+  p.out_dtype = a.out_dtype;
+  p.accumulate = a.accumulate;
+  p.ld_out = out_rows;
+  p.bias = a.dir == QG_FWD ? a.bias : nullptr;
+  const int a_fmt = (w.fmt == GGML_BF16 || p.wbf16) ? 1 : 0;
+  p.idesc_main = umma_idesc(a_fmt, 1, a.dir == QG_BWD ? 1 : 0, 0, 128, p.TN);
+  p.idesc_lora = umma_idesc(1, 1, a.dir == QG_BWD ? 1 : 0, 0, 128, p.TN);
+  p.status = status_dev;
+
+  CUtensorMap tm_act, tm_w16, tm_lact, tm_lw;
+  int rc = make_map(&tm_act, a.act, (uint64_t)a.M, (uint64_t)contract, 64, (uint32_t)p.TN, true);
+  if (rc) return rc;
+  tm_w16 = tm_act;
+  tm_lact = tm_act;
+  tm_lw = tm_act;
+  if (is16) {
+    rc = make_map(&tm_w16, w.dense16, (uint64_t)w.rows, (uint64_t)w.cols, 64, 64, w.fmt == GGML_BF16);
+    if (rc) return rc;
+  }
+  if (a.lora.rank > 0) {
+    rc = make_map(&tm_lact, a.lora.act, (uint64_t)a.M, 64, 64, (uint32_t)p.TN, true);
+    if (rc) return rc;
+    if (a.dir == QG_FWD) rc = make_map(&tm_lw, a.lora.w, (uint64_t)w.rows, 64, 64, 64, true);
+    else rc = make_map(&tm_lw, a.lora.w, (uint64_t)a.lora.rank, (uint64_t)w.cols, 64, 64, true);
+    if (rc) return rc;
+  }
+  const int n_tiles = p.n_row_tiles * p.n_tok_tiles;
+  const int grid = n_tiles < num_sms ? n_tiles : num_sms;
+  qgemm_kernel<<<grid, QG_THREADS, SMEM_BYTES, st>>>(tm_act, tm_w16, tm_lact, tm_lw, p);
+  return cudaGetLastError() == cudaSuccess ? RT_OK : RT_ERR_CUDA;
+}
+
+}  // namespace rt

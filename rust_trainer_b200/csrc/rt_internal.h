@@ -1,0 +1,49 @@
+// Internal declarations shared by the .cu/.cpp files of the library (not part of the C ABI).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/rt_b200.h"  // status codes and public types
+
+namespace rt {
+
+struct QWeight;
+
+// ---- repack.cu
+void launch_repack(const uint8_t* raw_dev, const QWeight& w, cudaStream_t st);
+void launch_gather_rows(const QWeight& w, const int* ids_dev, int n, float* out, int* status, cudaStream_t st);
+
+// ---- qgemm.cu
+enum { QG_FWD = 0, QG_BWD = 1 };
+enum { OUT_F32 = 0, OUT_BF16 = 1 };
+
+// Extra contraction chunk of rank r <= 64 appended after the frozen weight's own chunks:
+//   forward : Y += Hs[M x 64] . Bp[N x 64]^T      (Hs = s.X.A^T, zero beyond column r)
+//   backward: dX += Gs[M x 64] . A[r x K]          (Gs = s.dY.B,  zero beyond column r)
+struct LoraSide {
+  const __nv_bfloat16* act = nullptr;  // Hs / Gs, [M x 64] bf16
+  const __nv_bfloat16* w = nullptr;    // forward: Bp [N x 64]; backward: A [r x K]
+  int rank = 0;
+};
+
+struct QGemmArgs {
+  int dir = QG_FWD;
+  const __nv_bfloat16* act = nullptr;  // forward: X [M x K]; backward: dY [M x N]
+  int M = 0;
+  void* out = nullptr;                 // forward: Y [M x N]; backward: dX [M x K]
+  int out_dtype = OUT_F32;
+  int accumulate = 0;                  // out += result (f32 only)
+  const float* bias = nullptr;         // forward only, per output feature
+  void* out2 = nullptr;                // optional second copy of the result in bf16
+  LoraSide lora;
+};
+
+int qgemm_launch(const QWeight& w, const QGemmArgs& a, int* status_dev, int num_sms, cudaStream_t st);
+size_t qgemm_smem_bytes();
+int qgemm_init();  // resolves the driver entry point for tensor-map encoding; sets smem attributes
+
+}  // namespace rt
