@@ -49,6 +49,9 @@ enum {
   RT_GGML_BF16 = 30
 };
 
+/* Element types of device-resident activations. */
+enum { RT_DT_F32 = 0, RT_DT_BF16 = 1, RT_DT_F16 = 2 };
+
 typedef struct rt_ctx rt_ctx;
 typedef struct rt_frozen rt_frozen;
 typedef struct rt_linear rt_linear;
@@ -89,15 +92,119 @@ rt_status rt_frozen_backward_input(rt_frozen* w, const float* dy_host, size_t t,
 rt_status rt_frozen_row(rt_frozen* w, size_t r, float* out_host);
 
 
-/* Device-resident forms of forward / backward_input: activations stay in HBM as bf16
- * [t x dim]; the result is written as f32 or bf16; `accumulate` (f32 only) adds into the
+/* Device-resident forms of forward / backward_input.  Activations stay in HBM as 16-bit
+ * [t x dim] (`in_dtype` RT_DT_F16 or RT_DT_BF16; the tensor-core instruction needs both operands
+ * in ONE 16-bit type, so the packed weight is unpacked to that type on the fly: f16 keeps 11
+ * significant bits and suits the forward, bf16 keeps f32's range and suits gradients).  The
+ * result is written as `out_dtype` (f32, bf16 or f16); `accumulate` (f32 only) adds into the
  * output, which is what backward_input's `+=` and the residual adds of
  * src/model.rs:178,181 need.  Asynchronous on the ctx stream; a kernel-side failure is
  * reported by the next rt_ctx_synchronize. */
-rt_status rt_frozen_forward_dev(rt_frozen* w, const void* x_bf16_dev, size_t t, void* y_dev, int y_is_bf16,
+rt_status rt_frozen_forward_dev(rt_frozen* w, const void* x_dev, int in_dtype, size_t t, void* y_dev,
+                                int out_dtype, int accumulate);
+rt_status rt_frozen_backward_input_dev(rt_frozen* w, const void* dy_dev, int in_dtype, size_t t, void* dx_dev,
+                                       int out_dtype, int accumulate);
+
+/* ------------------------------------------------------------------ level 2: struct Linear / struct Lora
+ * src/linear.rs:9-122.  y = W.x + b + (alpha/r).B.A.x forward; dx = W^T.dy + (LoRA term) and
+ * the adapter gradients dA, dB backward.  Device-resident: this is the performance boundary,
+ * a Rust `Linear` holding device buffers calls these instead of crossing PCIe per layer. */
+
+/* Linear::new (src/linear.rs:48-53).  `bias_host` has out_dim floats or is NULL.  The linear
+ * borrows `w` (several linears may share one frozen weight, as embed/lm_head do when tied,
+ * src/rie.rs:189); destroy the linear before the weight. */
+rt_status rt_linear_create(rt_ctx* ctx, rt_frozen* w, const float* bias_host, const char* name, rt_linear** out);
+void rt_linear_destroy(rt_linear* lin);
+/* Linear::attach_lora (src/linear.rs:60-62) with explicit initial values: a_host is
+ * [rank x in], b_host is [out x rank] (row-major f32).  rank <= 64.  Gradients start at zero. */
+rt_status rt_linear_attach_lora(rt_linear* lin, int rank, float alpha, const float* a_host, const float* b_host);
+/* Linear::lora_enabled (src/linear.rs:44-45,64-70): 0 bypasses the adapter. */
+rt_status rt_linear_set_lora_enabled(rt_linear* lin, int enabled);
+/* Linear::forward (src/linear.rs:73-93), device form: x_f16_dev is [t x in] f16; y_dev is
+ * [t x out] of y_dtype (RT_DT_*); accumulate (f32 only) adds into y. */
+rt_status rt_linear_forward_dev(rt_linear* lin, const void* x_f16_dev, size_t t, void* y_dev, int y_dtype,
                                 int accumulate);
-rt_status rt_frozen_backward_input_dev(rt_frozen* w, const void* dy_bf16_dev, size_t t, void* dx_dev,
-                                       int dx_is_bf16, int accumulate);
+/* Linear::backward (src/linear.rs:97-121), device form.  dy is passed as f16 rows divided by a
+ * per-row positive scale (dy[m,:] = dy_f16[m,:] * dy_row_scale[m]; NULL scale = 1), which keeps
+ * 11 significant bits for gradients of any magnitude.  Writes (or, with accumulate, adds to)
+ * dx_f32_dev [t x in] and adds dA, dB into the adapter's gradient buffers. */
+rt_status rt_linear_backward_dev(rt_linear* lin, const void* x_f16_dev, const void* dy_f16_dev,
+                                 const float* dy_row_scale_dev, size_t t, float* dx_f32_dev, int accumulate);
+/* Host-buffer forms with the reference's exact signatures: Linear::forward(x, t) -> y and
+ * Linear::backward(x, dy, t) -> dx (fresh; accumulates ga/gb). */
+rt_status rt_linear_forward(rt_linear* lin, const float* x_host, size_t t, float* y_host);
+rt_status rt_linear_backward(rt_linear* lin, const float* x_host, const float* dy_host, size_t t, float* dx_host);
+/* Read / write the adapter (struct Lora fields a, b, ga, gb; any pointer may be NULL). */
+rt_status rt_lora_read(rt_linear* lin, float* a_host, float* b_host, float* ga_host, float* gb_host);
+rt_status rt_lora_write(rt_linear* lin, const float* a_host, const float* b_host);
+/* Lora::zero_grad (src/linear.rs:29-32). */
+rt_status rt_lora_zero_grad(rt_linear* lin);
+
+/* ------------------------------------------------------------------ level 3: struct Model
+ * src/model.rs:292-687 as built by load_gguf_from (src/rie.rs:164-260): dense llama / qwen2 /
+ * qwen3 decoders, pre-norm blocks, GQA attention with optional QK-norm and q/k/v bias, SwiGLU,
+ * f16-rounded K/V (kv_f16 = true, src/rie.rs:200), activation recomputation per block
+ * (checkpointing = true, src/rie.rs:254). */
+typedef struct rt_model_config {
+  int32_t vocab, hidden, ff, n_layers;
+  int32_t n_heads, n_kv_heads, head_dim, rot_dim;
+  float rope_theta, rope_freq_scale, rms_eps;
+  int32_t rope_neox;       /* 1: pairs (i, i+rot/2); 0: pairs (2i, 2i+1)            src/ops.rs:177 */
+  int32_t qk_norm;         /* 1: per-head RMSNorm on q and k                        src/attention.rs:170-177 */
+  int32_t tie_embeddings;  /* 1: lm_head shares token_embd                          src/rie.rs:186-189 */
+  int32_t head_rows;       /* rows of logits held at once (the reference's logits_chunk is 64,
+                              src/rie.rs:255; 0 picks 1024); results do not depend on it */
+} rt_model_config;
+
+rt_status rt_model_create(rt_ctx* ctx, const rt_model_config* cfg, rt_model** out);
+void rt_model_destroy(rt_model* m);
+/* One call per GGUF tensor, by its GGUF name: token_embd.weight, output.weight (untied only),
+ * output_norm.weight, rope_freqs.weight (optional), blk.N.{attn_norm,ffn_norm,attn_q_norm,
+ * attn_k_norm}.weight, blk.N.{attn_q,attn_k,attn_v,attn_output,ffn_gate,ffn_up,ffn_down}.weight
+ * and blk.N.attn_{q,k,v}.bias.  ggml_type 0 means f32 (norms, biases, rope_freqs). */
+rt_status rt_model_set_tensor(rt_model* m, const char* name, int ggml_type, size_t rows, size_t cols,
+                              const void* data_host, size_t nbytes);
+/* Checks that every tensor the configuration needs has arrived (load_gguf_from's refusals). */
+rt_status rt_model_finalize(rt_model* m);
+/* Model::attach_lora (src/model.rs:406-419): adapters on the listed modules (comma-separated
+ * GGUF or HF short names, NULL = all seven projections), A ~ U(-1/sqrt(in), 1/sqrt(in)) from the
+ * trainer's SplitMix64 stream seeded with `seed`, B = 0.  Returns the number of trainable
+ * parameters through n_params_out. */
+rt_status rt_model_attach_lora(rt_model* m, int rank, float alpha, const char* targets_csv, uint64_t seed,
+                               size_t* n_params_out);
+/* Model::lora_linears (src/model.rs:431-433), in parameter order (optim.rs:32-34). */
+size_t rt_model_num_lora(const rt_model* m);
+rt_linear* rt_model_lora_linear(rt_model* m, size_t index);
+const char* rt_linear_name(const rt_linear* lin);
+size_t rt_linear_in_dim(const rt_linear* lin);
+size_t rt_linear_out_dim(const rt_linear* lin);
+int rt_linear_lora_rank(const rt_linear* lin);
+/* Model::set_lora_enabled (src/model.rs:421-427), Model::zero_grad (src/model.rs:435-439). */
+rt_status rt_model_set_lora_enabled(rt_model* m, int enabled);
+rt_status rt_model_zero_grad(rt_model* m);
+/* Model::forward_backward (src/model.rs:613-687) over a batch of independent sequences laid
+ * end to end: tokens[seq_offsets[s] .. seq_offsets[s+1]) is sequence s.  Target i is scored
+ * from the hidden state at global position target_pos[i] against token target_tok[i] with
+ * weight weights[i] (the trainer passes 1/batch_tokens, src/train.rs:263,275).  Adds into every
+ * adapter's gradients; writes log-probabilities per target and the count of argmax hits. */
+rt_status rt_model_forward_backward(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
+                                    const int32_t* target_pos, const int32_t* target_tok, const float* weights,
+                                    int32_t n_targets, float* logp_out, int32_t* hits_out);
+/* Model::score / logprobs / logits_at (src/model.rs:505-557): forward only.  logits_out is
+ * NULL or [n_targets x vocab]. */
+rt_status rt_model_score(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
+                         const int32_t* target_pos, const int32_t* target_tok, int32_t n_targets, float* logp_out,
+                         int32_t* hits_out, float* logits_out);
+/* The flat f32 gradient buffer on the device, [A_0 | B_0 | A_1 | B_1 ...] in parameter order:
+ * what a data-parallel host all-reduces (sum) across ranks before rt_optim_step. */
+rt_status rt_model_grad_buffer(rt_model* m, void** grads_dev_out, size_t* n_floats_out);
+/* clip_grad_norm (src/optim.rs:73-90) followed by AdamW::step (src/optim.rs:48-69) on the
+ * device; returns the pre-clip gradient norm. */
+rt_status rt_optim_step(rt_model* m, float lr, float max_norm, float beta1, float beta2, float eps,
+                        float weight_decay, float* grad_norm_out);
+/* Optimiser state for checkpoints (src/train.rs:389-406): step count and flat m, v. */
+rt_status rt_optim_state_read(rt_model* m, uint64_t* t_out, float* m_host, float* v_host);
+rt_status rt_optim_state_write(rt_model* m, uint64_t t, const float* m_host, const float* v_host);
 
 #ifdef __cplusplus
 }

@@ -88,8 +88,7 @@ rt_status rt_ctx_synchronize(rt_ctx* c) {
 
 rt_status rt_ctx_set_stream(rt_ctx* c, void* s) {
   if (!c) return RT_ERR_BAD_ARG;
-  c->user_stream = (cudaStream_t)s;
-  c->stream = s ? (cudaStream_t)s : c->own_stream;
+  c->stream = (cudaStream_t)s;  // NULL is the legacy default stream, a valid choice
   return RT_OK;
 }
 
@@ -176,10 +175,13 @@ static rt_status frozen_matmul_host(rt_frozen* f, int dir, const float* in_host,
   RT_CUDA(c, cudaMemcpyAsync(in_f32, in_host, t * in_dim * sizeof(float), cudaMemcpyHostToDevice, c->stream));
   if (accumulate)
     RT_CUDA(c, cudaMemcpyAsync(out_f32, out_host, t * out_dim * sizeof(float), cudaMemcpyHostToDevice, c->stream));
-  rt::launch_f32_to_bf16(in_f32, in_bf, t * in_dim, c->stream);
+  // forward activations go in as f16 (11 significant bits); gradients as bf16 (f32's range)
+  const bool f16 = dir == rt::QG_FWD;
+  rt::launch_f32_to_16(in_f32, in_bf, t * in_dim, f16, c->stream);
   rt::QGemmArgs a;
   a.dir = dir;
   a.act = in_bf;
+  a.act_f16 = f16;
   a.M = (int)t;
   a.out = out_f32;
   a.out_dtype = rt::OUT_F32;
@@ -198,31 +200,35 @@ rt_status rt_frozen_backward_input(rt_frozen* f, const float* dy_host, size_t t,
   return frozen_matmul_host(f, rt::QG_BWD, dy_host, t, dx_host, true);
 }
 
-static rt_status frozen_matmul_dev(rt_frozen* f, int dir, const void* in_dev, size_t t, void* out_dev, int out_bf16,
-                                   int accumulate) {
+static rt_status frozen_matmul_dev(rt_frozen* f, int dir, const void* in_dev, int in_dtype, size_t t, void* out_dev,
+                                   int out_dtype, int accumulate) {
   if (!f || !in_dev || !out_dev) return RT_ERR_BAD_ARG;
   rt_ctx* c = f->ctx;
   if (t == 0) return RT_OK;
   if (t > (1u << 24)) return c->fail(RT_ERR_BAD_SHAPE, "too many rows");
-  if (accumulate && out_bf16) return c->fail(RT_ERR_BAD_ARG, "accumulate needs an f32 output");
+  if (in_dtype != RT_DT_F16 && in_dtype != RT_DT_BF16) return c->fail(RT_ERR_BAD_ARG, "activations must be f16 or bf16");
+  if (out_dtype < 0 || out_dtype > 2) return c->fail(RT_ERR_BAD_ARG, "bad output dtype");
+  if (accumulate && out_dtype != RT_DT_F32) return c->fail(RT_ERR_BAD_ARG, "accumulate needs an f32 output");
   RT_CUDA(c, cudaSetDevice(c->device));
   rt::QGemmArgs a;
   a.dir = dir;
-  a.act = (const __nv_bfloat16*)in_dev;
+  a.act = in_dev;
+  a.act_f16 = in_dtype == RT_DT_F16;
   a.M = (int)t;
   a.out = out_dev;
-  a.out_dtype = out_bf16 ? rt::OUT_BF16 : rt::OUT_F32;
+  a.out_dtype = out_dtype;
   a.accumulate = accumulate ? 1 : 0;
   int rc = rt::qgemm_launch(f->w, a, c->status_dev, c->num_sms, c->stream);
   if (rc) return c->fail(rc, "qgemm launch failed");
   return RT_OK;
 }
 
-rt_status rt_frozen_forward_dev(rt_frozen* f, const void* x, size_t t, void* y, int y_bf16, int acc) {
-  return frozen_matmul_dev(f, rt::QG_FWD, x, t, y, y_bf16, acc);
+rt_status rt_frozen_forward_dev(rt_frozen* f, const void* x, int in_dt, size_t t, void* y, int out_dt, int acc) {
+  return frozen_matmul_dev(f, rt::QG_FWD, x, in_dt, t, y, out_dt, acc);
 }
-rt_status rt_frozen_backward_input_dev(rt_frozen* f, const void* dy, size_t t, void* dx, int dx_bf16, int acc) {
-  return frozen_matmul_dev(f, rt::QG_BWD, dy, t, dx, dx_bf16, acc);
+rt_status rt_frozen_backward_input_dev(rt_frozen* f, const void* dy, int in_dt, size_t t, void* dx, int out_dt,
+                                       int acc) {
+  return frozen_matmul_dev(f, rt::QG_BWD, dy, in_dt, t, dx, out_dt, acc);
 }
 
 rt_status rt_frozen_row(rt_frozen* f, size_t r, float* out_host) {

@@ -10,7 +10,6 @@ struct rt_ctx {
   int num_sms = 0;
   cudaStream_t stream = nullptr;       // the stream in use (own_stream unless the host set one)
   cudaStream_t own_stream = nullptr;
-  cudaStream_t user_stream = nullptr;
   int* status_dev = nullptr;   // device word the kernels report bounded-wait failures into
   int* status_host = nullptr;  // pinned mirror
   std::string err;
@@ -42,7 +41,4 @@ struct rt_frozen {
   rt::QWeight w;
 };
 
-namespace rt {
-// small elementwise helpers (ops.cu)
-void launch_f32_to_bf16(const float* in, __nv_bfloat16* out, size_t n, cudaStream_t st);
-}
+#include "ops.h"

@@ -1,0 +1,912 @@
+// C ABI levels 2 and 3: Linear + LoRA and the whole decoder step on the device.
+// The arithmetic lives in qgemm.cu (frozen matmuls), attention.cu and ops.cu; this file is the
+// sequencing the reference does in src/linear.rs, src/attention.rs, src/model.rs and
+// src/optim.rs, plus buffer management.
+#include "model.h"
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+bool DevBuf::reserve(size_t want, bool zero) {
+  if (want <= bytes) return true;
+  if (p) cudaFree(p);
+  p = nullptr;
+  bytes = 0;
+  if (cudaMalloc(&p, want) != cudaSuccess) return false;
+  bytes = want;
+  if (zero) cudaMemset(p, 0, want);
+  return true;
+}
+void DevBuf::release() {
+  if (p) cudaFree(p);
+  p = nullptr;
+  bytes = 0;
+}
+
+namespace rt {
+
+rt_status lora_refresh(rt_linear* l) {
+  if (!l->has_lora || !l->lora.stale) return RT_OK;
+  LoraDev& lo = l->lora;
+  launch_lora_refresh(lo.a, lo.b, lo.rank, l->in_dim(), l->out_dim(), lo.scale(), lo.a_s, lo.a_h, lo.bp, lo.bt_s,
+                      l->ctx->stream);
+  lo.stale = false;
+  return RT_OK;
+}
+
+// Hs / Gs are [M x 64] f16 with zeros beyond column `rank`: only the first `rank` columns are
+// ever written, so the buffer is cleared when it grows or when the rank changes.
+static __half* lowrank_buf(rt_ctx* c, DevBuf& b, int& cur_rank, int M, int rank) {
+  const size_t want = (size_t)M * 64 * sizeof(__half);
+  if (want > b.bytes) {
+    if (!b.reserve(want + want / 2)) return nullptr;
+    cur_rank = -1;
+  }
+  if (cur_rank != rank) {
+    cudaMemsetAsync(b.p, 0, b.bytes, c->stream);
+    cur_rank = rank;
+  }
+  return b.as<__half>();
+}
+
+static QWeight dense_view(const __half* p, int rows, int cols) {
+  QWeight w;
+  w.fmt = GGML_F16;
+  w.rows = rows;
+  w.cols = cols;
+  w.dense16 = (void*)p;
+  return w;
+}
+
+rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16, int M, void* y, int y_dtype,
+                             int accumulate) {
+  rt_ctx* c = l->ctx;
+  if (M <= 0) return RT_OK;
+  QGemmArgs a;
+  a.dir = QG_FWD;
+  a.act = x16;
+  a.act_f16 = 1;
+  a.M = M;
+  a.out = y;
+  a.out_dtype = y_dtype;
+  a.accumulate = accumulate;
+  a.bias = l->bias;
+  if (l->lora_active()) {
+    lora_refresh(l);
+    const int r = l->lora.rank;
+    __half* hs = lowrank_buf(c, sc.hs, sc.hs_rank, M, r);
+    if (!hs) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+    QGemmArgs ha;  // Hs = X . (sA)^T
+    ha.dir = QG_FWD;
+    ha.act = x16;
+    ha.act_f16 = 1;
+    ha.M = M;
+    ha.out = hs;
+    ha.out_dtype = OUT_F16;
+    ha.ld_out = 64;
+    int rc = qgemm_launch(dense_view(l->lora.a_s, r, l->in_dim()), ha, c->status_dev, c->num_sms, c->stream);
+    if (rc) return c->fail(rc, "lora H matmul launch failed");
+    a.lora.act = hs;
+    a.lora.w = l->lora.bp;
+    a.lora.rank = r;
+  }
+  int rc = qgemm_launch(l->w->w, a, c->status_dev, c->num_sms, c->stream);
+  if (rc) return c->fail(rc, "frozen forward matmul launch failed");
+  return RT_OK;
+}
+
+rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16, const __half* dy16,
+                              const float* dscale, int M, float* dx, int accumulate) {
+  rt_ctx* c = l->ctx;
+  if (M <= 0) return RT_OK;
+  const int K = l->in_dim(), N = l->out_dim();
+  QGemmArgs a;
+  a.dir = QG_BWD;
+  a.act = dy16;
+  a.act_f16 = 1;
+  a.M = M;
+  a.out = dx;
+  a.out_dtype = OUT_F32;
+  a.accumulate = accumulate;
+  a.row_scale = dscale;
+  if (l->lora_active()) {
+    lora_refresh(l);
+    const int r = l->lora.rank;
+    __half* hs = lowrank_buf(c, sc.hs, sc.hs_rank, M, r);
+    __half* gs = lowrank_buf(c, sc.gs, sc.gs_rank, M, r);
+    size_t wsf = lora_grad_workspace_floats(M, K > N ? K : N, r);
+    if (!hs || !gs || !sc.grad_ws.reserve(wsf * sizeof(float)))
+      return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+    QGemmArgs ha;  // Hs = X . (sA)^T   (recomputed, as src/linear.rs:105 does)
+    ha.dir = QG_FWD;
+    ha.act = x16;
+    ha.act_f16 = 1;
+    ha.M = M;
+    ha.out = hs;
+    ha.out_dtype = OUT_F16;
+    ha.ld_out = 64;
+    int rc = qgemm_launch(dense_view(l->lora.a_s, r, K), ha, c->status_dev, c->num_sms, c->stream);
+    if (rc) return c->fail(rc, "lora H matmul launch failed");
+    QGemmArgs ga;  // Gs = dY~ . (sB)   (unit rows: the row scale is applied where Gs is consumed)
+    ga.dir = QG_FWD;
+    ga.act = dy16;
+    ga.act_f16 = 1;
+    ga.M = M;
+    ga.out = gs;
+    ga.out_dtype = OUT_F16;
+    ga.ld_out = 64;
+    rc = qgemm_launch(dense_view(l->lora.bt_s, r, N), ga, c->status_dev, c->num_sms, c->stream);
+    if (rc) return c->fail(rc, "lora G matmul launch failed");
+    // gb[N x r] += dY^T . Hs ; ga[r x K] += Gs^T . X
+    launch_lora_grad(hs, dy16, nullptr, dscale, M, N, r, 1, (size_t)r, l->lora.gb, sc.grad_ws.as<float>(), c->stream);
+    launch_lora_grad(gs, x16, dscale, nullptr, M, K, r, (size_t)K, 1, l->lora.ga, sc.grad_ws.as<float>(), c->stream);
+    a.lora.act = gs;
+    a.lora.w = l->lora.a_h;
+    a.lora.rank = r;
+  }
+  int rc = qgemm_launch(l->w->w, a, c->status_dev, c->num_sms, c->stream);
+  if (rc) return c->fail(rc, "frozen backward matmul launch failed");
+  return RT_OK;
+}
+
+// tensor.rs:155-199 Rng, host side, for Lora::new's A ~ U(-1/sqrt(in), 1/sqrt(in))
+struct SplitMix {
+  uint64_t state;
+  explicit SplitMix(uint64_t seed) : state(seed ^ 0x9E3779B97F4A7C15ull) {}
+  uint64_t next() {
+    state += 0x9E3779B97F4A7C15ull;
+    uint64_t z = state;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+  }
+  float uniform() { return (float)(next() >> 40) / (float)(1ull << 24); }
+  float uniform_sym(float bound) { return (uniform() * 2.0f - 1.0f) * bound; }
+};
+
+}  // namespace rt
+
+using namespace rt;
+
+static rt_status attach_views(rt_linear* l, int rank, float alpha, float* a, float* b, float* ga, float* gb) {
+  rt_ctx* c = l->ctx;
+  const int K = l->in_dim(), N = l->out_dim();
+  LoraDev& lo = l->lora;
+  lo.rank = rank;
+  lo.alpha = alpha;
+  lo.a = a;
+  lo.b = b;
+  lo.ga = ga;
+  lo.gb = gb;
+  const size_t n_as = (size_t)rank * K, n_bp = (size_t)N * 64, n_bt = (size_t)rank * N;
+  // each operand copy starts on a 256-byte boundary (TMA needs 16)
+  auto up = [](size_t n) { return (n * 2 + 255) / 256 * 256; };
+  const size_t total = 2 * up(n_as) + up(n_bp) + up(n_bt);
+  if (!lo.shadows.reserve(total)) return c->fail(RT_ERR_CUDA, "out of device memory (adapter copies)");
+  uint8_t* base = (uint8_t*)lo.shadows.p;
+  lo.a_s = (__half*)base;
+  lo.a_h = (__half*)(base + up(n_as));
+  lo.bp = (__half*)(base + 2 * up(n_as));
+  lo.bt_s = (__half*)(base + 2 * up(n_as) + up(n_bp));
+  lo.stale = true;
+  l->has_lora = true;
+  return RT_OK;
+}
+
+extern "C" {
+
+// ------------------------------------------------------------------ level 2
+rt_status rt_linear_create(rt_ctx* c, rt_frozen* w, const float* bias_host, const char* name, rt_linear** out) {
+  if (!c || !w || !out) return RT_ERR_BAD_ARG;
+  *out = nullptr;
+  RT_CUDA(c, cudaSetDevice(c->device));
+  rt_linear* l = new rt_linear();
+  l->ctx = c;
+  l->w = w;
+  l->name = name ? name : "";
+  if (bias_host) {
+    cudaError_t e = cudaMalloc(&l->bias, (size_t)w->w.rows * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemcpy(l->bias, bias_host, (size_t)w->w.rows * sizeof(float), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+      delete l;
+      return c->cuda_fail(e, "rt_linear_create");
+    }
+  }
+  *out = l;
+  return RT_OK;
+}
+
+void rt_linear_destroy(rt_linear* l) {
+  if (!l) return;
+  cudaSetDevice(l->ctx->device);
+  if (l->bias) cudaFree(l->bias);
+  l->lora.shadows.release();
+  l->own_params.release();
+  if (l->owns_w) rt_frozen_destroy(l->w);
+  delete l;
+}
+
+rt_status rt_linear_attach_lora(rt_linear* l, int rank, float alpha, const float* a_host, const float* b_host) {
+  if (!l || !a_host || !b_host) return RT_ERR_BAD_ARG;
+  rt_ctx* c = l->ctx;
+  if (rank <= 0 || rank > 64) return c->fail(RT_ERR_BAD_ARG, "LoRA rank must be in 1..64");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  const size_t na = (size_t)rank * l->in_dim(), nb = (size_t)l->out_dim() * rank;
+  if (!l->own_params.reserve(2 * (na + nb) * sizeof(float))) return c->fail(RT_ERR_CUDA, "out of device memory");
+  float* base = l->own_params.as<float>();
+  RT_CUDA(c, cudaMemcpyAsync(base, a_host, na * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  RT_CUDA(c, cudaMemcpyAsync(base + na, b_host, nb * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  RT_CUDA(c, cudaMemsetAsync(base + na + nb, 0, (na + nb) * sizeof(float), c->stream));
+  RT_CUDA(c, cudaStreamSynchronize(c->stream));
+  return attach_views(l, rank, alpha, base, base + na, base + na + nb, base + 2 * na + nb);
+}
+
+rt_status rt_linear_set_lora_enabled(rt_linear* l, int on) {
+  if (!l) return RT_ERR_BAD_ARG;
+  l->lora_enabled = on != 0;
+  return RT_OK;
+}
+
+static LinearScratch& ctx_scratch(rt_ctx* c) {
+  static std::map<rt_ctx*, LinearScratch> m;  // scratch for linears used outside a model
+  return m[c];
+}
+
+rt_status rt_linear_forward_dev(rt_linear* l, const void* x, size_t t, void* y, int y_dtype, int accumulate) {
+  if (!l || !x || !y) return RT_ERR_BAD_ARG;
+  rt_ctx* c = l->ctx;
+  if (t > (1u << 24)) return c->fail(RT_ERR_BAD_SHAPE, "too many rows");
+  if (y_dtype < 0 || y_dtype > 2) return c->fail(RT_ERR_BAD_ARG, "bad output dtype");
+  if (accumulate && y_dtype != RT_DT_F32) return c->fail(RT_ERR_BAD_ARG, "accumulate needs an f32 output");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  return linear_forward_dev(l, ctx_scratch(c), (const __half*)x, (int)t, y, y_dtype, accumulate);
+}
+
+rt_status rt_linear_backward_dev(rt_linear* l, const void* x, const void* dy, const float* dscale, size_t t, float* dx,
+                                 int accumulate) {
+  if (!l || !x || !dy || !dx) return RT_ERR_BAD_ARG;
+  rt_ctx* c = l->ctx;
+  if (t > (1u << 24)) return c->fail(RT_ERR_BAD_SHAPE, "too many rows");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  return linear_backward_dev(l, ctx_scratch(c), (const __half*)x, (const __half*)dy, dscale, (int)t, dx, accumulate);
+}
+
+rt_status rt_linear_forward(rt_linear* l, const float* x_host, size_t t, float* y_host) {
+  if (!l || !x_host || !y_host) return RT_ERR_BAD_ARG;
+  rt_ctx* c = l->ctx;
+  if (t == 0) return RT_OK;
+  if (t > (1u << 24)) return c->fail(RT_ERR_BAD_SHAPE, "too many rows");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  const size_t K = l->in_dim(), N = l->out_dim();
+  float* xf = (float*)c->get_scratch(0, t * K * sizeof(float));
+  __half* xh = (__half*)c->get_scratch(1, t * K * sizeof(__half));
+  float* yf = (float*)c->get_scratch(2, t * N * sizeof(float));
+  if (!xf || !xh || !yf) return c->fail(RT_ERR_CUDA, "out of device memory");
+  RT_CUDA(c, cudaMemcpyAsync(xf, x_host, t * K * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  launch_f32_to_16(xf, xh, t * K, true, c->stream);
+  rt_status st = linear_forward_dev(l, ctx_scratch(c), xh, (int)t, yf, RT_DT_F32, 0);
+  if (st) return st;
+  RT_CUDA(c, cudaMemcpyAsync(y_host, yf, t * N * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+  return c->check_device_status("rt_linear_forward");
+}
+
+rt_status rt_linear_backward(rt_linear* l, const float* x_host, const float* dy_host, size_t t, float* dx_host) {
+  if (!l || !x_host || !dy_host || !dx_host) return RT_ERR_BAD_ARG;
+  rt_ctx* c = l->ctx;
+  if (t == 0) return RT_OK;
+  if (t > (1u << 24)) return c->fail(RT_ERR_BAD_SHAPE, "too many rows");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  const size_t K = l->in_dim(), N = l->out_dim();
+  float* xf = (float*)c->get_scratch(0, (t * (K > N ? K : N)) * sizeof(float));
+  uint8_t* s1 = (uint8_t*)c->get_scratch(1, t * (K + N) * sizeof(__half) + t * sizeof(float) + 512);
+  float* dxf = (float*)c->get_scratch(2, t * K * sizeof(float));
+  if (!xf || !s1 || !dxf) return c->fail(RT_ERR_CUDA, "out of device memory");
+  __half* xh = (__half*)s1;
+  __half* dyh = (__half*)(s1 + (t * K * sizeof(__half) + 255) / 256 * 256);
+  float* dsc = (float*)((uint8_t*)dyh + (t * N * sizeof(__half) + 255) / 256 * 256);
+  RT_CUDA(c, cudaMemcpyAsync(xf, x_host, t * K * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  launch_f32_to_16(xf, xh, t * K, true, c->stream);
+  RT_CUDA(c, cudaMemcpyAsync(xf, dy_host, t * N * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  launch_normalize_rows(xf, (int)t, (int)N, dyh, dsc, c->stream);
+  rt_status st = linear_backward_dev(l, ctx_scratch(c), xh, dyh, dsc, (int)t, dxf, 0);
+  if (st) return st;
+  RT_CUDA(c, cudaMemcpyAsync(dx_host, dxf, t * K * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+  return c->check_device_status("rt_linear_backward");
+}
+
+rt_status rt_lora_read(rt_linear* l, float* a, float* b, float* ga, float* gb) {
+  if (!l) return RT_ERR_BAD_ARG;
+  rt_ctx* c = l->ctx;
+  if (!l->has_lora) return c->fail(RT_ERR_BAD_ARG, "linear has no adapter");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  const size_t na = (size_t)l->lora.rank * l->in_dim() * sizeof(float), nb = (size_t)l->out_dim() * l->lora.rank * sizeof(float);
+  if (a) RT_CUDA(c, cudaMemcpyAsync(a, l->lora.a, na, cudaMemcpyDeviceToHost, c->stream));
+  if (b) RT_CUDA(c, cudaMemcpyAsync(b, l->lora.b, nb, cudaMemcpyDeviceToHost, c->stream));
+  if (ga) RT_CUDA(c, cudaMemcpyAsync(ga, l->lora.ga, na, cudaMemcpyDeviceToHost, c->stream));
+  if (gb) RT_CUDA(c, cudaMemcpyAsync(gb, l->lora.gb, nb, cudaMemcpyDeviceToHost, c->stream));
+  return c->check_device_status("rt_lora_read");
+}
+
+rt_status rt_lora_write(rt_linear* l, const float* a, const float* b) {
+  if (!l) return RT_ERR_BAD_ARG;
+  rt_ctx* c = l->ctx;
+  if (!l->has_lora) return c->fail(RT_ERR_BAD_ARG, "linear has no adapter");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  const size_t na = (size_t)l->lora.rank * l->in_dim() * sizeof(float), nb = (size_t)l->out_dim() * l->lora.rank * sizeof(float);
+  if (a) RT_CUDA(c, cudaMemcpyAsync(l->lora.a, a, na, cudaMemcpyHostToDevice, c->stream));
+  if (b) RT_CUDA(c, cudaMemcpyAsync(l->lora.b, b, nb, cudaMemcpyHostToDevice, c->stream));
+  RT_CUDA(c, cudaStreamSynchronize(c->stream));
+  l->lora.stale = true;
+  return RT_OK;
+}
+
+rt_status rt_lora_zero_grad(rt_linear* l) {
+  if (!l) return RT_ERR_BAD_ARG;
+  rt_ctx* c = l->ctx;
+  if (!l->has_lora) return RT_OK;
+  RT_CUDA(c, cudaSetDevice(c->device));
+  const size_t na = (size_t)l->lora.rank * l->in_dim() * sizeof(float), nb = (size_t)l->out_dim() * l->lora.rank * sizeof(float);
+  RT_CUDA(c, cudaMemsetAsync(l->lora.ga, 0, na, c->stream));
+  RT_CUDA(c, cudaMemsetAsync(l->lora.gb, 0, nb, c->stream));
+  return RT_OK;
+}
+
+const char* rt_linear_name(const rt_linear* l) { return l ? l->name.c_str() : ""; }
+size_t rt_linear_in_dim(const rt_linear* l) { return l ? (size_t)l->in_dim() : 0; }
+size_t rt_linear_out_dim(const rt_linear* l) { return l ? (size_t)l->out_dim() : 0; }
+int rt_linear_lora_rank(const rt_linear* l) { return (l && l->has_lora) ? l->lora.rank : 0; }
+
+// ------------------------------------------------------------------ level 3
+static const char* LIN_NAMES[7] = {"attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down"};
+static const char* HF_NAMES[7] = {"q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"};
+
+rt_status rt_model_create(rt_ctx* c, const rt_model_config* cfg, rt_model** out) {
+  if (!c || !cfg || !out) return RT_ERR_BAD_ARG;
+  *out = nullptr;
+  if (cfg->vocab <= 0 || cfg->hidden <= 0 || cfg->ff <= 0 || cfg->n_layers <= 0 || cfg->n_heads <= 0 ||
+      cfg->n_kv_heads <= 0 || cfg->n_heads % cfg->n_kv_heads != 0)
+    return c->fail(RT_ERR_BAD_SHAPE, "bad model dimensions");
+  if (cfg->head_dim != 64 && cfg->head_dim != 128) return c->fail(RT_ERR_BAD_SHAPE, "head_dim must be 64 or 128");
+  if (cfg->rot_dim <= 0 || cfg->rot_dim > cfg->head_dim || cfg->rot_dim % 2) return c->fail(RT_ERR_BAD_SHAPE, "bad rot_dim");
+  rt_model* m = new rt_model();
+  m->ctx = c;
+  m->cfg = *cfg;
+  if (m->cfg.head_rows <= 0) m->cfg.head_rows = 1024;
+  m->blocks.resize(cfg->n_layers);
+  *out = m;
+  return RT_OK;
+}
+
+void rt_model_destroy(rt_model* m) {
+  if (!m) return;
+  cudaSetDevice(m->ctx->device);
+  cudaStreamSynchronize(m->ctx->stream);
+  for (auto& b : m->blocks)
+    for (int i = 0; i < 7; ++i)
+      if (b.lin[i]) rt_linear_destroy(b.lin[i]);
+  if (m->lm_head && m->lm_head != m->embed) rt_frozen_destroy(m->lm_head);
+  if (m->embed) rt_frozen_destroy(m->embed);
+  for (void* p : m->owned) cudaFree(p);
+  DevBuf* bufs[] = {&m->P, &m->G, &m->Mo, &m->Vo, &m->opt_scalars, &m->inv_freq, &m->rope_cos, &m->rope_sin,
+                    &m->lsc.hs, &m->lsc.gs, &m->lsc.grad_ws, &m->tokens, &m->pos, &m->seq_start, &m->x, &m->ckpt, &m->h,
+                    &m->n1, &m->n2, &m->q_raw, &m->k_raw, &m->v_raw, &m->q16, &m->k16, &m->v16, &m->o16, &m->lse,
+                    &m->delta, &m->g16, &m->u16, &m->hm16, &m->dx, &m->dy16, &m->sc_y, &m->dhm, &m->dg16, &m->du16,
+                    &m->sc_g, &m->sc_u, &m->dn, &m->d_o, &m->dO16, &m->amax, &m->dq, &m->dk, &m->dv, &m->dq16, &m->dk16,
+                    &m->dv16, &m->sc_q, &m->sc_k, &m->sc_v, &m->tpos, &m->ttok, &m->tw, &m->logp, &m->hits, &m->xs,
+                    &m->ns16, &m->logits, &m->dl16, &m->sc_l, &m->dns, &m->dxs};
+  for (DevBuf* b : bufs) b->release();
+  delete m;
+}
+
+static rt_status upload_f32(rt_model* m, const void* data, size_t n, float** out) {
+  rt_ctx* c = m->ctx;
+  float* p = nullptr;
+  RT_CUDA(c, cudaMalloc(&p, n * sizeof(float)));
+  m->owned.push_back(p);
+  RT_CUDA(c, cudaMemcpy(p, data, n * sizeof(float), cudaMemcpyHostToDevice));
+  *out = p;
+  return RT_OK;
+}
+
+rt_status rt_model_set_tensor(rt_model* m, const char* name, int ggml_type, size_t rows, size_t cols,
+                              const void* data, size_t nbytes) {
+  if (!m || !name || !data) return RT_ERR_BAD_ARG;
+  rt_ctx* c = m->ctx;
+  RT_CUDA(c, cudaSetDevice(c->device));
+  const rt_model_config& g = m->cfg;
+  const std::string n(name);
+  const size_t d = g.hidden, qd = (size_t)g.n_heads * g.head_dim, kvd = (size_t)g.n_kv_heads * g.head_dim;
+  auto want_f32 = [&](size_t len) -> rt_status {
+    if (ggml_type != 0) return c->fail(RT_ERR_UNSUPPORTED_TYPE, n + ": expected an f32 tensor");
+    if (rows * cols != len || nbytes != len * 4) return c->fail(RT_ERR_BAD_SHAPE, n + ": wrong length");
+    return RT_OK;
+  };
+  rt_status st;
+  if (n == "token_embd.weight" || n == "output.weight") {
+    if (rows != (size_t)g.vocab || cols != d) return c->fail(RT_ERR_BAD_SHAPE, n + ": expected [vocab x hidden]");
+    rt_frozen* f = nullptr;
+    st = rt_frozen_create(c, ggml_type, rows, cols, data, nbytes, &f);
+    if (st) return st;
+    if (n == "token_embd.weight") {
+      if (m->embed) rt_frozen_destroy(m->embed);
+      m->embed = f;
+    } else {
+      if (g.tie_embeddings) {
+        rt_frozen_destroy(f);
+        return c->fail(RT_ERR_BAD_ARG, "output.weight given for a model with tied embeddings");
+      }
+      if (m->lm_head) rt_frozen_destroy(m->lm_head);
+      m->lm_head = f;
+    }
+    return RT_OK;
+  }
+  if (n == "output_norm.weight") {
+    if ((st = want_f32(d))) return st;
+    return upload_f32(m, data, d, &m->final_norm);
+  }
+  if (n == "rope_freqs.weight") {
+    if ((st = want_f32((size_t)g.rot_dim / 2))) return st;
+    m->rope_factors.assign((const float*)data, (const float*)data + g.rot_dim / 2);
+    m->rope_max_pos = 0;
+    return RT_OK;
+  }
+  int li = -1, off = 0;
+  if (sscanf(name, "blk.%d.%n", &li, &off) < 1 || off == 0 || li < 0 || li >= g.n_layers)
+    return c->fail(RT_ERR_BAD_ARG, n + ": unknown tensor name");
+  const std::string rest(name + off);
+  BlockDev& b = m->blocks[li];
+  if (rest == "attn_norm.weight") { if ((st = want_f32(d))) return st; return upload_f32(m, data, d, &b.input_norm); }
+  if (rest == "ffn_norm.weight") { if ((st = want_f32(d))) return st; return upload_f32(m, data, d, &b.post_norm); }
+  if (rest == "attn_q_norm.weight") { if ((st = want_f32(g.head_dim))) return st; return upload_f32(m, data, g.head_dim, &b.q_norm); }
+  if (rest == "attn_k_norm.weight") { if ((st = want_f32(g.head_dim))) return st; return upload_f32(m, data, g.head_dim, &b.k_norm); }
+  const size_t shapes[7][2] = {{qd, d}, {kvd, d}, {kvd, d}, {d, qd}, {(size_t)g.ff, d}, {(size_t)g.ff, d}, {d, (size_t)g.ff}};
+  for (int i = 0; i < 7; ++i) {
+    if (rest == std::string(LIN_NAMES[i]) + ".weight") {
+      if (rows != shapes[i][0] || cols != shapes[i][1]) return c->fail(RT_ERR_BAD_SHAPE, n + ": wrong shape for this configuration");
+      rt_frozen* f = nullptr;
+      st = rt_frozen_create(c, ggml_type, rows, cols, data, nbytes, &f);
+      if (st) return st;
+      if (b.lin[i]) rt_linear_destroy(b.lin[i]);
+      rt_linear* l = nullptr;
+      char nm[64];
+      snprintf(nm, sizeof nm, "blk.%d.%s", li, LIN_NAMES[i]);
+      st = rt_linear_create(c, f, nullptr, nm, &l);
+      if (st) { rt_frozen_destroy(f); return st; }
+      l->owns_w = true;
+      b.lin[i] = l;
+      return RT_OK;
+    }
+    if (i < 3 && rest == std::string(LIN_NAMES[i]) + ".bias") {
+      if (!b.lin[i]) return c->fail(RT_ERR_BAD_ARG, n + ": set the weight before its bias");
+      if ((st = want_f32(shapes[i][0]))) return st;
+      rt_linear* l = b.lin[i];  // the linear owns its bias
+      if (!l->bias) RT_CUDA(c, cudaMalloc(&l->bias, shapes[i][0] * sizeof(float)));
+      RT_CUDA(c, cudaMemcpy(l->bias, data, shapes[i][0] * sizeof(float), cudaMemcpyHostToDevice));
+      return RT_OK;
+    }
+  }
+  return c->fail(RT_ERR_BAD_ARG, n + ": unknown tensor name");
+}
+
+rt_status rt_model_finalize(rt_model* m) {
+  if (!m) return RT_ERR_BAD_ARG;
+  rt_ctx* c = m->ctx;
+  if (!m->embed) return c->fail(RT_ERR_BAD_ARG, "token_embd.weight missing");
+  if (m->cfg.tie_embeddings) m->lm_head = m->embed;
+  if (!m->lm_head) return c->fail(RT_ERR_BAD_ARG, "output.weight missing (untied model)");
+  if (!m->final_norm) return c->fail(RT_ERR_BAD_ARG, "output_norm.weight missing");
+  for (int li = 0; li < m->cfg.n_layers; ++li) {
+    BlockDev& b = m->blocks[li];
+    char buf[96];
+    if (!b.input_norm || !b.post_norm) { snprintf(buf, sizeof buf, "blk.%d: norm weights missing", li); return c->fail(RT_ERR_BAD_ARG, buf); }
+    if (m->cfg.qk_norm && (!b.q_norm || !b.k_norm)) { snprintf(buf, sizeof buf, "blk.%d: q/k norm weights missing", li); return c->fail(RT_ERR_BAD_ARG, buf); }
+    for (int i = 0; i < 7; ++i)
+      if (!b.lin[i]) { snprintf(buf, sizeof buf, "blk.%d.%s.weight missing", li, LIN_NAMES[i]); return c->fail(RT_ERR_BAD_ARG, buf); }
+  }
+  // opt_scalars: [0,1024) f64 partials, [1024] f64 sum, then one f32 norm
+  if (!m->opt_scalars.reserve(1025 * sizeof(double) + 16) || !m->amax.reserve(16)) return c->fail(RT_ERR_CUDA, "out of device memory");
+  m->finalized = true;
+  return RT_OK;
+}
+
+rt_status rt_model_attach_lora(rt_model* m, int rank, float alpha, const char* targets, uint64_t seed, size_t* n_out) {
+  if (!m) return RT_ERR_BAD_ARG;
+  rt_ctx* c = m->ctx;
+  if (!m->finalized) return c->fail(RT_ERR_BAD_ARG, "finalize the model first");
+  if (rank <= 0 || rank > 64) return c->fail(RT_ERR_BAD_ARG, "LoRA rank must be in 1..64");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  bool sel[7];
+  for (int i = 0; i < 7; ++i) sel[i] = targets == nullptr;
+  if (targets) {
+    std::string t(targets);
+    size_t p = 0;
+    while (p <= t.size()) {
+      size_t e = t.find(',', p);
+      if (e == std::string::npos) e = t.size();
+      std::string tok = t.substr(p, e - p);
+      for (int i = 0; i < 7; ++i)
+        if (tok == LIN_NAMES[i] || tok == HF_NAMES[i]) sel[i] = true;
+      p = e + 1;
+    }
+  }
+  m->lora_order.clear();
+  size_t total = 0;
+  for (auto& b : m->blocks)
+    for (int i = 0; i < 7; ++i) {
+      b.lin[i]->has_lora = false;
+      if (sel[i]) {
+        m->lora_order.push_back(b.lin[i]);
+        total += (size_t)rank * (b.lin[i]->in_dim() + b.lin[i]->out_dim());
+      }
+    }
+  m->n_params = total;
+  if (total == 0) { if (n_out) *n_out = 0; return RT_OK; }
+  const size_t bytes = total * sizeof(float);
+  if (!m->P.reserve(bytes) || !m->G.reserve(bytes) || !m->Mo.reserve(bytes) || !m->Vo.reserve(bytes))
+    return c->fail(RT_ERR_CUDA, "out of device memory (adapter state)");
+  std::vector<float> host(total, 0.f);
+  SplitMix rng(seed);
+  size_t off = 0;
+  for (rt_linear* l : m->lora_order) {
+    const size_t na = (size_t)rank * l->in_dim(), nb = (size_t)l->out_dim() * rank;
+    const float bound = 1.0f / sqrtf((float)l->in_dim());
+    for (size_t i = 0; i < na; ++i) host[off + i] = rng.uniform_sym(bound);
+    float* base = m->P.as<float>();
+    float* gbase = m->G.as<float>();
+    rt_status st = attach_views(l, rank, alpha, base + off, base + off + na, gbase + off, gbase + off + na);
+    if (st) return st;
+    off += na + nb;
+  }
+  RT_CUDA(c, cudaMemcpy(m->P.p, host.data(), bytes, cudaMemcpyHostToDevice));
+  RT_CUDA(c, cudaMemset(m->G.p, 0, bytes));
+  RT_CUDA(c, cudaMemset(m->Mo.p, 0, bytes));
+  RT_CUDA(c, cudaMemset(m->Vo.p, 0, bytes));
+  m->opt_t = 0;
+  if (n_out) *n_out = total;
+  return RT_OK;
+}
+
+size_t rt_model_num_lora(const rt_model* m) { return m ? m->lora_order.size() : 0; }
+rt_linear* rt_model_lora_linear(rt_model* m, size_t i) { return (m && i < m->lora_order.size()) ? m->lora_order[i] : nullptr; }
+
+rt_status rt_model_set_lora_enabled(rt_model* m, int on) {
+  if (!m) return RT_ERR_BAD_ARG;
+  for (auto& b : m->blocks)
+    for (int i = 0; i < 7; ++i)
+      if (b.lin[i]) b.lin[i]->lora_enabled = on != 0;
+  return RT_OK;
+}
+
+rt_status rt_model_zero_grad(rt_model* m) {
+  if (!m) return RT_ERR_BAD_ARG;
+  rt_ctx* c = m->ctx;
+  if (m->n_params == 0) return RT_OK;
+  RT_CUDA(c, cudaSetDevice(c->device));
+  RT_CUDA(c, cudaMemsetAsync(m->G.p, 0, m->n_params * sizeof(float), c->stream));
+  return RT_OK;
+}
+
+rt_status rt_model_grad_buffer(rt_model* m, void** p, size_t* n) {
+  if (!m || !p || !n) return RT_ERR_BAD_ARG;
+  *p = m->G.p;
+  *n = m->n_params;
+  return RT_OK;
+}
+
+// ---- workspace
+static bool ensure_tokens(rt_model* m, int M) {
+  if (M <= m->cap_tokens) return true;
+  const rt_model_config& g = m->cfg;
+  const size_t d = g.hidden, ff = g.ff, qd = (size_t)g.n_heads * g.head_dim, kvd = (size_t)g.n_kv_heads * g.head_dim;
+  const size_t T = (size_t)M;
+  bool ok = true;
+  ok &= m->tokens.reserve(T * 4) && m->pos.reserve(T * 4) && m->seq_start.reserve(T * 4);
+  ok &= m->x.reserve(T * d * 4) && m->ckpt.reserve(T * d * 4 * g.n_layers) && m->h.reserve(T * d * 4);
+  ok &= m->n1.reserve(T * d * 2) && m->n2.reserve(T * d * 2);
+  ok &= m->q_raw.reserve(T * qd * 4) && m->k_raw.reserve(T * kvd * 4) && m->v_raw.reserve(T * kvd * 4);
+  ok &= m->q16.reserve(T * qd * 2) && m->k16.reserve(T * kvd * 2) && m->v16.reserve(T * kvd * 2) && m->o16.reserve(T * qd * 2);
+  ok &= m->lse.reserve(T * g.n_heads * 4) && m->delta.reserve(T * g.n_heads * 4);
+  ok &= m->g16.reserve(T * ff * 2) && m->u16.reserve(T * ff * 2) && m->hm16.reserve(T * ff * 2);
+  ok &= m->dx.reserve(T * d * 4) && m->dy16.reserve(T * d * 2) && m->sc_y.reserve(T * 4);
+  ok &= m->dhm.reserve(T * ff * 4) && m->dg16.reserve(T * ff * 2) && m->du16.reserve(T * ff * 2);
+  ok &= m->sc_g.reserve(T * 4) && m->sc_u.reserve(T * 4) && m->dn.reserve(T * d * 4);
+  ok &= m->d_o.reserve(T * qd * 4) && m->dO16.reserve(T * qd * 2);
+  ok &= m->dq.reserve(T * qd * 4) && m->dk.reserve(T * kvd * 4) && m->dv.reserve(T * kvd * 4);
+  ok &= m->dq16.reserve(T * qd * 2) && m->dk16.reserve(T * kvd * 2) && m->dv16.reserve(T * kvd * 2);
+  ok &= m->sc_q.reserve(T * 4) && m->sc_k.reserve(T * 4) && m->sc_v.reserve(T * 4);
+  if (ok) m->cap_tokens = M;
+  return ok;
+}
+
+static bool ensure_targets(rt_model* m, int n, bool backward) {
+  const rt_model_config& g = m->cfg;
+  bool ok = true;
+  if (n > m->cap_targets) {
+    ok &= m->tpos.reserve((size_t)n * 4) && m->ttok.reserve((size_t)n * 4) && m->tw.reserve((size_t)n * 4) &&
+          m->logp.reserve((size_t)n * 4) && m->hits.reserve(16);
+    if (ok) m->cap_targets = n;
+  }
+  const int R = n < g.head_rows ? n : g.head_rows;
+  if (R > m->cap_head_rows || (backward && m->dl16.bytes == 0)) {
+    const size_t d = g.hidden, V = g.vocab;
+    ok &= m->xs.reserve((size_t)R * d * 4) && m->ns16.reserve((size_t)R * d * 2) && m->logits.reserve((size_t)R * V * 4);
+    ok &= m->sc_l.reserve((size_t)R * 4) && m->dns.reserve((size_t)R * d * 4) && m->dxs.reserve((size_t)R * d * 4);
+    if (backward) ok &= m->dl16.reserve((size_t)R * V * 2);
+    if (ok && R > m->cap_head_rows) m->cap_head_rows = R;
+  }
+  return ok;
+}
+
+// ops.rs:118-131 inverse frequencies (host, f32 like the reference), tables on the device
+static rt_status ensure_rope(rt_model* m, int max_pos) {
+  rt_ctx* c = m->ctx;
+  if (max_pos <= m->rope_max_pos) return RT_OK;
+  const rt_model_config& g = m->cfg;
+  const int half = g.rot_dim / 2;
+  int cap = 256;
+  while (cap < max_pos) cap *= 2;
+  std::vector<float> inv(half);
+  for (int i = 0; i < half; ++i) {
+    float f = powf(g.rope_theta, -2.0f * (float)i / (float)g.rot_dim) * g.rope_freq_scale;
+    if (i < (int)m->rope_factors.size() && m->rope_factors[i] != 0.0f) f /= m->rope_factors[i];
+    inv[i] = f;
+  }
+  if (!m->inv_freq.reserve(half * 4) || !m->rope_cos.reserve((size_t)cap * half * 4) || !m->rope_sin.reserve((size_t)cap * half * 4))
+    return c->fail(RT_ERR_CUDA, "out of device memory (rope tables)");
+  RT_CUDA(c, cudaMemcpyAsync(m->inv_freq.p, inv.data(), half * 4, cudaMemcpyHostToDevice, c->stream));
+  RT_CUDA(c, cudaStreamSynchronize(c->stream));
+  launch_rope_table(m->inv_freq.as<float>(), half, cap, m->rope_cos.as<float>(), m->rope_sin.as<float>(), c->stream);
+  m->rope_max_pos = cap;
+  return RT_OK;
+}
+
+#define RT_TRY(expr)          \
+  do {                        \
+    rt_status s__ = (expr);   \
+    if (s__) return s__;      \
+  } while (0)
+
+// Block::forward (src/model.rs:165-183).  x_in is read only; h receives x_in + attention;
+// when x_out is non-null it receives the block output (h + mlp), and may alias h.
+static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, float* h, float* x_out) {
+  rt_ctx* c = m->ctx;
+  const rt_model_config& g = m->cfg;
+  BlockDev& b = m->blocks[li];
+  cudaStream_t st = c->stream;
+  const int d = g.hidden;
+  launch_rmsnorm_fwd(x_in, b.input_norm, M, d, g.rms_eps, m->n1.as<__half>(), st);
+  RT_TRY(linear_forward_dev(b.lin[0], m->lsc, m->n1.as<__half>(), M, m->q_raw.p, RT_DT_F32, 0));
+  RT_TRY(linear_forward_dev(b.lin[1], m->lsc, m->n1.as<__half>(), M, m->k_raw.p, RT_DT_F32, 0));
+  RT_TRY(linear_forward_dev(b.lin[2], m->lsc, m->n1.as<__half>(), M, m->v_raw.p, RT_DT_F32, 0));
+  launch_qk_rope_fwd(m->q_raw.as<float>(), m->k_raw.as<float>(), m->v_raw.as<float>(), g.qk_norm ? b.q_norm : nullptr,
+                     g.qk_norm ? b.k_norm : nullptr, m->pos.as<int>(), m->rope_cos.as<float>(), m->rope_sin.as<float>(), M,
+                     g.n_heads, g.n_kv_heads, g.head_dim, g.rot_dim, g.rope_neox, g.rms_eps, m->q16.as<__half>(),
+                     m->k16.as<__half>(), m->v16.as<__half>(), st);
+  if (launch_attn_fwd(m->q16.as<__half>(), m->k16.as<__half>(), m->v16.as<__half>(), m->seq_start.as<int>(), M, g.n_heads,
+                      g.n_kv_heads, g.head_dim, m->o16.as<__half>(), m->lse.as<float>(), st))
+    return c->fail(RT_ERR_CUDA, "attention forward launch failed");
+  if (h != x_in) RT_CUDA(c, cudaMemcpyAsync(h, x_in, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
+  RT_TRY(linear_forward_dev(b.lin[3], m->lsc, m->o16.as<__half>(), M, h, RT_DT_F32, 1));
+  launch_rmsnorm_fwd(h, b.post_norm, M, d, g.rms_eps, m->n2.as<__half>(), st);
+  RT_TRY(linear_forward_dev(b.lin[4], m->lsc, m->n2.as<__half>(), M, m->g16.p, RT_DT_F16, 0));
+  RT_TRY(linear_forward_dev(b.lin[5], m->lsc, m->n2.as<__half>(), M, m->u16.p, RT_DT_F16, 0));
+  launch_swiglu_fwd(m->g16.as<__half>(), m->u16.as<__half>(), m->hm16.as<__half>(), (size_t)M * g.ff, st);
+  if (x_out) {
+    if (x_out != h) RT_CUDA(c, cudaMemcpyAsync(x_out, h, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
+    RT_TRY(linear_forward_dev(b.lin[6], m->lsc, m->hm16.as<__half>(), M, x_out, RT_DT_F32, 1));
+  }
+  return RT_OK;
+}
+
+// Block::backward (src/model.rs:185-197).  On entry dx holds the gradient of the block output
+// and (dy16, sc_y) its row-normalised f16 copy; on exit both describe the block input's.
+static rt_status block_backward(rt_model* m, int li, int M, const float* x_in) {
+  rt_ctx* c = m->ctx;
+  const rt_model_config& g = m->cfg;
+  BlockDev& b = m->blocks[li];
+  cudaStream_t st = c->stream;
+  const int d = g.hidden;
+  float* dx = m->dx.as<float>();
+  __half* dy16 = m->dy16.as<__half>();
+  float* sc_y = m->sc_y.as<float>();
+  // Mlp::backward (src/model.rs:120-134)
+  RT_TRY(linear_backward_dev(b.lin[6], m->lsc, m->hm16.as<__half>(), dy16, sc_y, M, m->dhm.as<float>(), 0));
+  launch_swiglu_bwd(m->dhm.as<float>(), m->g16.as<__half>(), m->u16.as<__half>(), M, g.ff, m->dg16.as<__half>(),
+                    m->du16.as<__half>(), m->sc_g.as<float>(), m->sc_u.as<float>(), st);
+  RT_TRY(linear_backward_dev(b.lin[4], m->lsc, m->n2.as<__half>(), m->dg16.as<__half>(), m->sc_g.as<float>(), M, m->dn.as<float>(), 0));
+  RT_TRY(linear_backward_dev(b.lin[5], m->lsc, m->n2.as<__half>(), m->du16.as<__half>(), m->sc_u.as<float>(), M, m->dn.as<float>(), 1));
+  // dh = dy + rmsnorm_backward(h, post_norm, dn2)
+  launch_rmsnorm_bwd(m->h.as<float>(), b.post_norm, m->dn.as<float>(), dx, M, d, g.rms_eps, dx, dy16, sc_y, st);
+  // Attention::backward (src/attention.rs:246-367)
+  RT_TRY(linear_backward_dev(b.lin[3], m->lsc, m->o16.as<__half>(), dy16, sc_y, M, m->d_o.as<float>(), 0));
+  const size_t nqd = (size_t)M * g.n_heads * g.head_dim;
+  launch_global_normalize(m->d_o.as<float>(), nqd, m->amax.as<float>(), m->dO16.as<__half>(), st);
+  if (launch_attn_bwd(m->q16.as<__half>(), m->k16.as<__half>(), m->v16.as<__half>(), m->o16.as<__half>(), m->dO16.as<__half>(),
+                      m->amax.as<float>(), m->lse.as<float>(), m->seq_start.as<int>(), M, g.n_heads, g.n_kv_heads, g.head_dim,
+                      m->delta.as<float>(), m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>(), st))
+    return c->fail(RT_ERR_CUDA, "attention backward launch failed");
+  launch_qk_rope_bwd(m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>(), m->q_raw.as<float>(), m->k_raw.as<float>(),
+                     g.qk_norm ? b.q_norm : nullptr, g.qk_norm ? b.k_norm : nullptr, m->pos.as<int>(), m->rope_cos.as<float>(),
+                     m->rope_sin.as<float>(), M, g.n_heads, g.n_kv_heads, g.head_dim, g.rot_dim, g.rope_neox, g.rms_eps,
+                     m->dq16.as<__half>(), m->dk16.as<__half>(), m->dv16.as<__half>(), m->sc_q.as<float>(), m->sc_k.as<float>(),
+                     m->sc_v.as<float>(), st);
+  RT_TRY(linear_backward_dev(b.lin[0], m->lsc, m->n1.as<__half>(), m->dq16.as<__half>(), m->sc_q.as<float>(), M, m->dn.as<float>(), 0));
+  RT_TRY(linear_backward_dev(b.lin[1], m->lsc, m->n1.as<__half>(), m->dk16.as<__half>(), m->sc_k.as<float>(), M, m->dn.as<float>(), 1));
+  RT_TRY(linear_backward_dev(b.lin[2], m->lsc, m->n1.as<__half>(), m->dv16.as<__half>(), m->sc_v.as<float>(), M, m->dn.as<float>(), 1));
+  // dx = dh + rmsnorm_backward(x, input_norm, dn1)
+  launch_rmsnorm_bwd(x_in, b.input_norm, m->dn.as<float>(), dx, M, d, g.rms_eps, dx, dy16, sc_y, st);
+  return RT_OK;
+}
+
+// Model::head (src/model.rs:561-609) in chunks of head_rows targets.
+static rt_status model_head(rt_model* m, int M, int n_targets, bool backward, float* logits_out_host) {
+  rt_ctx* c = m->ctx;
+  const rt_model_config& g = m->cfg;
+  cudaStream_t st = c->stream;
+  const int d = g.hidden, V = g.vocab;
+  (void)M;
+  RT_CUDA(c, cudaMemsetAsync(m->hits.p, 0, 4, st));
+  rt_linear head;  // a bias-free, adapter-free Linear over the lm_head weight
+  head.ctx = c;
+  head.w = m->lm_head;
+  for (int c0 = 0; c0 < n_targets; c0 += g.head_rows) {
+    const int R = n_targets - c0 < g.head_rows ? n_targets - c0 : g.head_rows;
+    const int* tpos = m->tpos.as<int>() + c0;
+    launch_gather_f32_rows(m->x.as<float>(), tpos, R, d, m->xs.as<float>(), st);
+    launch_rmsnorm_fwd(m->xs.as<float>(), m->final_norm, R, d, g.rms_eps, m->ns16.as<__half>(), st);
+    RT_TRY(linear_forward_dev(&head, m->lsc, m->ns16.as<__half>(), R, m->logits.p, RT_DT_F32, 0));
+    if (logits_out_host)
+      RT_CUDA(c, cudaMemcpyAsync(logits_out_host + (size_t)c0 * V, m->logits.p, (size_t)R * V * 4, cudaMemcpyDeviceToHost, st));
+    launch_ce_rows(m->logits.as<float>(), R, V, m->ttok.as<int>() + c0, m->tw.as<float>() + c0, m->logp.as<float>() + c0,
+                   m->hits.as<int>(), backward ? m->dl16.as<__half>() : nullptr, backward ? m->sc_l.as<float>() : nullptr,
+                   c->status_dev, st);
+    if (backward) {
+      RT_TRY(linear_backward_dev(&head, m->lsc, m->ns16.as<__half>(), m->dl16.as<__half>(), m->sc_l.as<float>(), R, m->dns.as<float>(), 0));
+      launch_rmsnorm_bwd(m->xs.as<float>(), m->final_norm, m->dns.as<float>(), nullptr, R, d, g.rms_eps, m->dxs.as<float>(), nullptr, nullptr, st);
+      launch_scatter_add_rows(m->dxs.as<float>(), tpos, R, d, m->dx.as<float>(), st);
+    }
+  }
+  return RT_OK;
+}
+
+static rt_status upload_batch(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int n_seq,
+                              const int32_t* tpos, const int32_t* ttok, const float* tw, int n_targets, bool backward,
+                              int* M_out) {
+  rt_ctx* c = m->ctx;
+  if (!m->finalized) return c->fail(RT_ERR_BAD_ARG, "finalize the model first");
+  if (!tokens || !seq_offsets || n_seq <= 0) return c->fail(RT_ERR_BAD_ARG, "empty batch");
+  if (n_targets < 0 || (n_targets > 0 && (!tpos || !ttok))) return c->fail(RT_ERR_BAD_ARG, "bad targets");
+  if (seq_offsets[0] != 0) return c->fail(RT_ERR_BAD_ARG, "seq_offsets must start at 0");
+  const long long M = seq_offsets[n_seq];
+  if (M <= 0 || M > (1 << 24)) return c->fail(RT_ERR_BAD_SHAPE, "token count out of range");
+  m->h_pos.resize(M);
+  m->h_seq_start.resize(M);
+  int max_len = 0;
+  for (int s = 0; s < n_seq; ++s) {
+    const int a = seq_offsets[s], e = seq_offsets[s + 1];
+    if (e <= a) return c->fail(RT_ERR_BAD_SHAPE, "empty or unordered sequence");
+    for (int i = a; i < e; ++i) { m->h_pos[i] = i - a; m->h_seq_start[i] = a; }
+    if (e - a > max_len) max_len = e - a;
+  }
+  for (long long i = 0; i < M; ++i)
+    if (tokens[i] < 0 || tokens[i] >= m->cfg.vocab) return c->fail(RT_ERR_BAD_INDEX, "token id out of vocabulary");  // model.rs:450 asserts
+  for (int i = 0; i < n_targets; ++i) {
+    if (tpos[i] < 0 || tpos[i] >= M) return c->fail(RT_ERR_BAD_INDEX, "target position out of range");  // model.rs:573 asserts
+    if (ttok[i] < 0 || ttok[i] >= m->cfg.vocab) return c->fail(RT_ERR_BAD_INDEX, "target token out of vocabulary");
+  }
+  RT_CUDA(c, cudaSetDevice(c->device));
+  if (!ensure_tokens(m, (int)M) || !ensure_targets(m, n_targets > 0 ? n_targets : 1, backward))
+    return c->fail(RT_ERR_CUDA, "out of device memory (activations)");
+  RT_TRY(ensure_rope(m, max_len));
+  cudaStream_t st = c->stream;
+  RT_CUDA(c, cudaMemcpyAsync(m->tokens.p, tokens, M * 4, cudaMemcpyHostToDevice, st));
+  RT_CUDA(c, cudaMemcpyAsync(m->pos.p, m->h_pos.data(), M * 4, cudaMemcpyHostToDevice, st));
+  RT_CUDA(c, cudaMemcpyAsync(m->seq_start.p, m->h_seq_start.data(), M * 4, cudaMemcpyHostToDevice, st));
+  if (n_targets > 0) {
+    RT_CUDA(c, cudaMemcpyAsync(m->tpos.p, tpos, (size_t)n_targets * 4, cudaMemcpyHostToDevice, st));
+    RT_CUDA(c, cudaMemcpyAsync(m->ttok.p, ttok, (size_t)n_targets * 4, cudaMemcpyHostToDevice, st));
+    if (tw) RT_CUDA(c, cudaMemcpyAsync(m->tw.p, tw, (size_t)n_targets * 4, cudaMemcpyHostToDevice, st));
+  }
+  *M_out = (int)M;
+  return RT_OK;
+}
+
+rt_status rt_model_forward_backward(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
+                                    const int32_t* tpos, const int32_t* ttok, const float* weights, int32_t n_targets,
+                                    float* logp_out, int32_t* hits_out) {
+  if (!m) return RT_ERR_BAD_ARG;
+  rt_ctx* c = m->ctx;
+  if (n_targets > 0 && !weights) return c->fail(RT_ERR_BAD_ARG, "weights missing");  // model.rs:652 asserts equal lengths
+  int M = 0;
+  RT_TRY(upload_batch(m, tokens, seq_offsets, n_seq, tpos, ttok, weights, n_targets, true, &M));
+  cudaStream_t st = c->stream;
+  const rt_model_config& g = m->cfg;
+  const size_t xd = (size_t)M * g.hidden;
+  float* x = m->x.as<float>();
+  launch_gather_rows(m->embed->w, m->tokens.as<int>(), M, x, c->status_dev, st);
+  for (int li = 0; li < g.n_layers; ++li) {
+    RT_CUDA(c, cudaMemcpyAsync(m->ckpt.as<float>() + (size_t)li * xd, x, xd * 4, cudaMemcpyDeviceToDevice, st));
+    RT_TRY(block_forward(m, li, M, x, x, x));
+  }
+  RT_CUDA(c, cudaMemsetAsync(m->dx.p, 0, xd * 4, st));
+  if (n_targets > 0) RT_TRY(model_head(m, M, n_targets, true, nullptr));
+  launch_normalize_rows(m->dx.as<float>(), M, g.hidden, m->dy16.as<__half>(), m->sc_y.as<float>(), st);
+  for (int li = g.n_layers - 1; li >= 0; --li) {
+    const float* x_in = m->ckpt.as<float>() + (size_t)li * xd;
+    RT_TRY(block_forward(m, li, M, x_in, m->h.as<float>(), nullptr));  // recompute the block's caches
+    RT_TRY(block_backward(m, li, M, x_in));
+  }
+  if (n_targets > 0 && logp_out) RT_CUDA(c, cudaMemcpyAsync(logp_out, m->logp.p, (size_t)n_targets * 4, cudaMemcpyDeviceToHost, st));
+  int hits = 0;
+  RT_CUDA(c, cudaMemcpyAsync(&hits, m->hits.p, 4, cudaMemcpyDeviceToHost, st));
+  rt_status s = c->check_device_status("rt_model_forward_backward");
+  if (hits_out) *hits_out = hits;
+  return s;
+}
+
+rt_status rt_model_score(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
+                         const int32_t* tpos, const int32_t* ttok, int32_t n_targets, float* logp_out,
+                         int32_t* hits_out, float* logits_out) {
+  if (!m) return RT_ERR_BAD_ARG;
+  rt_ctx* c = m->ctx;
+  int M = 0;
+  RT_TRY(upload_batch(m, tokens, seq_offsets, n_seq, tpos, ttok, nullptr, n_targets, false, &M));
+  cudaStream_t st = c->stream;
+  const rt_model_config& g = m->cfg;
+  float* x = m->x.as<float>();
+  launch_gather_rows(m->embed->w, m->tokens.as<int>(), M, x, c->status_dev, st);
+  for (int li = 0; li < g.n_layers; ++li) RT_TRY(block_forward(m, li, M, x, x, x));
+  if (n_targets > 0) RT_TRY(model_head(m, M, n_targets, false, logits_out));
+  if (n_targets > 0 && logp_out) RT_CUDA(c, cudaMemcpyAsync(logp_out, m->logp.p, (size_t)n_targets * 4, cudaMemcpyDeviceToHost, st));
+  int hits = 0;
+  RT_CUDA(c, cudaMemcpyAsync(&hits, m->hits.p, 4, cudaMemcpyDeviceToHost, st));
+  rt_status s = c->check_device_status("rt_model_score");
+  if (hits_out) *hits_out = hits;
+  return s;
+}
+
+rt_status rt_optim_step(rt_model* m, float lr, float max_norm, float beta1, float beta2, float eps, float wd,
+                        float* norm_out) {
+  if (!m) return RT_ERR_BAD_ARG;
+  rt_ctx* c = m->ctx;
+  if (m->n_params == 0) return c->fail(RT_ERR_BAD_ARG, "no adapters attached");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  cudaStream_t st = c->stream;
+  double* part = m->opt_scalars.as<double>();
+  double* sum = part + 1024;
+  float* normd = (float*)(sum + 1);
+  launch_sumsq(m->G.as<float>(), m->n_params, part, sum, st);
+  m->opt_t += 1;
+  const float bc1 = 1.0f - powf(beta1, (float)m->opt_t), bc2 = 1.0f - powf(beta2, (float)m->opt_t);
+  launch_adamw(m->P.as<float>(), m->G.as<float>(), m->Mo.as<float>(), m->Vo.as<float>(), m->n_params, sum, max_norm, lr,
+               beta1, beta2, eps, wd, bc1, bc2, normd, st);
+  for (rt_linear* l : m->lora_order) l->lora.stale = true;
+  float nrm = 0.f;
+  RT_CUDA(c, cudaMemcpyAsync(&nrm, normd, 4, cudaMemcpyDeviceToHost, st));
+  rt_status s = c->check_device_status("rt_optim_step");
+  if (norm_out) *norm_out = nrm;
+  return s;
+}
+
+rt_status rt_optim_state_read(rt_model* m, uint64_t* t_out, float* mh, float* vh) {
+  if (!m) return RT_ERR_BAD_ARG;
+  rt_ctx* c = m->ctx;
+  RT_CUDA(c, cudaSetDevice(c->device));
+  if (t_out) *t_out = m->opt_t;
+  if (mh && m->n_params) RT_CUDA(c, cudaMemcpyAsync(mh, m->Mo.p, m->n_params * 4, cudaMemcpyDeviceToHost, c->stream));
+  if (vh && m->n_params) RT_CUDA(c, cudaMemcpyAsync(vh, m->Vo.p, m->n_params * 4, cudaMemcpyDeviceToHost, c->stream));
+  return c->check_device_status("rt_optim_state_read");
+}
+
+rt_status rt_optim_state_write(rt_model* m, uint64_t t, const float* mh, const float* vh) {
+  if (!m) return RT_ERR_BAD_ARG;
+  rt_ctx* c = m->ctx;
+  RT_CUDA(c, cudaSetDevice(c->device));
+  m->opt_t = t;
+  if (mh && m->n_params) RT_CUDA(c, cudaMemcpyAsync(m->Mo.p, mh, m->n_params * 4, cudaMemcpyHostToDevice, c->stream));
+  if (vh && m->n_params) RT_CUDA(c, cudaMemcpyAsync(m->Vo.p, vh, m->n_params * 4, cudaMemcpyHostToDevice, c->stream));
+  RT_CUDA(c, cudaStreamSynchronize(c->stream));
+  return RT_OK;
+}
+
+}  // extern "C"

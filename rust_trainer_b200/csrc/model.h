@@ -1,0 +1,92 @@
+// Host-side driver objects behind the level-2 (Linear) and level-3 (Model) C ABI.
+// They mirror the reference's Linear (src/linear.rs:38-122), Attention/Mlp/Block
+// (src/attention.rs, src/model.rs:92-218) and Model (src/model.rs:292-687), with every
+// tensor resident in HBM.
+#pragma once
+#include "ctx.h"
+#include <map>
+#include <string>
+#include <vector>
+
+struct DevBuf {
+  void* p = nullptr;
+  size_t bytes = 0;
+  // grow-only; returns false on allocation failure
+  bool reserve(size_t want, bool zero = false);
+  void release();
+  template <class T> T* as() const { return (T*)p; }
+};
+
+struct LoraDev {
+  int rank = 0;
+  float alpha = 0.f;
+  float *a = nullptr, *b = nullptr, *ga = nullptr, *gb = nullptr;  // views into flat f32 buffers
+  __half *a_s = nullptr, *a_h = nullptr, *bp = nullptr, *bt_s = nullptr;  // 16-bit operand copies
+  DevBuf shadows;
+  bool stale = true;  // operand copies need rebuilding from a, b
+  float scale() const { return alpha / (float)rank; }
+};
+
+struct rt_linear {
+  rt_ctx* ctx = nullptr;
+  std::string name;
+  rt_frozen* w = nullptr;
+  bool owns_w = false;
+  float* bias = nullptr;  // device [out] or null
+  bool has_lora = false, lora_enabled = true;
+  LoraDev lora;
+  DevBuf own_params;  // standalone linears own their a|b|ga|gb; model linears point into the model's buffers
+  int in_dim() const { return w->w.cols; }
+  int out_dim() const { return w->w.rows; }
+  bool lora_active() const { return has_lora && lora_enabled; }
+};
+
+// Scratch shared by every Linear call on a ctx (one call at a time per ctx).
+struct LinearScratch {
+  DevBuf hs, gs, grad_ws;
+  int hs_rank = -1, gs_rank = -1;
+};
+
+namespace rt {
+rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16, int M, void* y, int y_dtype,
+                             int accumulate);
+// dy16 is row-normalised f16 with per-row scales `dscale` (null = all ones)
+rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16, const __half* dy16,
+                              const float* dscale, int M, float* dx, int accumulate);
+rt_status lora_refresh(rt_linear* l);
+}  // namespace rt
+
+struct BlockDev {
+  float *input_norm = nullptr, *post_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+  rt_linear* lin[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // q k v o gate up down
+};
+
+struct rt_model {
+  rt_ctx* ctx = nullptr;
+  rt_model_config cfg;
+  bool finalized = false;
+  rt_frozen* embed = nullptr;
+  rt_frozen* lm_head = nullptr;  // == embed when tied
+  float* final_norm = nullptr;
+  std::vector<float> rope_factors;  // host copy of rope_freqs.weight
+  std::vector<BlockDev> blocks;
+  std::vector<void*> owned;  // small device allocations (norms, biases)
+  std::vector<rt_linear*> lora_order;  // adapted linears in parameter order
+
+  // flat LoRA state: [A_0 | B_0 | A_1 | B_1 ...] in parameter order
+  size_t n_params = 0;
+  DevBuf P, G, Mo, Vo, opt_scalars;  // opt_scalars: 1024 f64 partials + 1 f64 sum + 1 f32 norm
+  uint64_t opt_t = 0;
+
+  // RoPE tables
+  DevBuf inv_freq, rope_cos, rope_sin;
+  int rope_max_pos = 0;
+
+  LinearScratch lsc;
+  // activations, sized for `cap_tokens`
+  int cap_tokens = 0, cap_targets = 0, cap_head_rows = 0;
+  DevBuf tokens, pos, seq_start, x, ckpt, h, n1, n2, q_raw, k_raw, v_raw, q16, k16, v16, o16, lse, delta, g16, u16, hm16;
+  DevBuf dx, dy16, sc_y, dhm, dg16, du16, sc_g, sc_u, dn, d_o, dO16, amax, dq, dk, dv, dq16, dk16, dv16, sc_q, sc_k, sc_v;
+  DevBuf tpos, ttok, tw, logp, hits, xs, ns16, logits, dl16, sc_l, dns, dxs;
+  std::vector<int> h_pos, h_seq_start;
+};

@@ -1,23 +1,622 @@
-// Small memory-bound device ops around the frozen matmuls.
+// Memory-bound device ops around the frozen matmuls: RMSNorm, QK-norm + RoPE, SwiGLU,
+// cross-entropy, row gathers, LoRA gradient reductions, AdamW.  One CTA per token row unless
+// noted.  Every kernel that produces the 16-bit input of a backward matmul writes the row
+// divided by its largest magnitude plus that magnitude as a per-row scale: f16 then keeps 11
+// significant bits whatever the size of the gradients, and the matmul's epilogue multiplies
+// the scale back in (the matmul is linear in each token row).
 #include "ctx.h"
+#include "ops.h"
 
 namespace rt {
 
-__global__ void f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, size_t n) {
+// ------------------------------------------------------------------ reductions
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// Block-wide reductions (blockDim.x <= 1024); result broadcast to every thread.
+__device__ float block_sum(float v) {
+  __shared__ float sh[33];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = lane < (int)((blockDim.x + 31) >> 5) ? sh[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) sh[32] = t;
+  }
+  __syncthreads();
+  return sh[32];
+}
+__device__ float block_max(float v) {
+  __shared__ float sh[33];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = lane < (int)((blockDim.x + 31) >> 5) ? sh[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) sh[32] = t;
+  }
+  __syncthreads();
+  return sh[32];
+}
+__device__ double block_sum_d(double v) {
+  __shared__ double sh[33];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  v = warp_sum_d(v);
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    double t = lane < (int)((blockDim.x + 31) >> 5) ? sh[lane] : 0.0;
+    t = warp_sum_d(t);
+    if (lane == 0) sh[32] = t;
+  }
+  __syncthreads();
+  return sh[32];
+}
+
+// ------------------------------------------------------------------ conversions
+template <bool F16>
+__global__ void f32_to_16_kernel(const float* __restrict__ in, uint16_t* __restrict__ out, size_t n) {
   size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i + 3 < n) {
     float4 v = *(const float4*)(in + i);
-    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
-    *(uint2*)(out + i) = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+    uint32_t a, b;
+    if (F16) {
+      __half2 x = __floats2half2_rn(v.x, v.y), y = __floats2half2_rn(v.z, v.w);
+      a = *(uint32_t*)&x; b = *(uint32_t*)&y;
+    } else {
+      __nv_bfloat162 x = __floats2bfloat162_rn(v.x, v.y), y = __floats2bfloat162_rn(v.z, v.w);
+      a = *(uint32_t*)&x; b = *(uint32_t*)&y;
+    }
+    *(uint2*)(out + i) = make_uint2(a, b);
   } else {
-    for (; i < n; ++i) out[i] = __float2bfloat16_rn(in[i]);
+    for (; i < n; ++i) {
+      if (F16) { __half h = __float2half_rn(in[i]); out[i] = *(uint16_t*)&h; }
+      else { __nv_bfloat16 h = __float2bfloat16_rn(in[i]); out[i] = *(uint16_t*)&h; }
+    }
   }
 }
-
-void launch_f32_to_bf16(const float* in, __nv_bfloat16* out, size_t n, cudaStream_t st) {
+void launch_f32_to_16(const float* in, void* out, size_t n, bool to_f16, cudaStream_t st) {
   if (n == 0) return;
   size_t threads = (n + 3) / 4;
-  f32_to_bf16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(in, out, n);
+  unsigned blocks = (unsigned)((threads + 255) / 256);
+  if (to_f16) f32_to_16_kernel<true><<<blocks, 256, 0, st>>>(in, (uint16_t*)out, n);
+  else f32_to_16_kernel<false><<<blocks, 256, 0, st>>>(in, (uint16_t*)out, n);
+}
+
+// Row-normalised f16 copy: y16[r,:] = x[r,:] / amax_r, scale[r] = amax_r (1 if the row is zero).
+__global__ void normalize_rows_kernel(const float* __restrict__ x, int d, __half* __restrict__ y16,
+                                      float* __restrict__ scale) {
+  const size_t r = blockIdx.x;
+  const float* xr = x + r * d;
+  float m = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) m = fmaxf(m, fabsf(xr[i]));
+  m = block_max(m);
+  const float s = m > 0.f ? m : 1.f, inv = 1.f / s;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) y16[r * d + i] = __float2half_rn(xr[i] * inv);
+  if (threadIdx.x == 0) scale[r] = s;
+}
+void launch_normalize_rows(const float* x, int rows, int d, __half* y16, float* scale, cudaStream_t st) {
+  if (rows > 0) normalize_rows_kernel<<<rows, 256, 0, st>>>(x, d, y16, scale);
+}
+
+// ------------------------------------------------------------------ RMSNorm (reference src/ops.rs:8-56)
+// y16 = x * ir * w  with ir = 1/sqrt(mean(x^2) + eps)
+__global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w, int d, float eps,
+                                   __half* __restrict__ y16) {
+  const size_t r = blockIdx.x;
+  const float* xr = x + r * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) ss += xr[i] * xr[i];
+  ss = block_sum(ss);
+  const float ir = 1.0f / sqrtf(ss / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) y16[r * d + i] = __float2half_rn(xr[i] * ir * w[i]);
+}
+void launch_rmsnorm_fwd(const float* x, const float* w, int rows, int d, float eps, __half* y16, cudaStream_t st) {
+  if (rows > 0) rmsnorm_fwd_kernel<<<rows, 256, 0, st>>>(x, w, d, eps, y16);
+}
+
+// dx = g*ir - x*c, g = dn*w, c = dot(g,x)*ir^3/d;  out = (dres ? dres : 0) + dx.
+// Optionally also the row-normalised f16 copy of `out` and its scale.
+__global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                   const float* __restrict__ dn, const float* dres, int d, float eps, float* out,
+                                   __half* __restrict__ out16, float* __restrict__ scale) {
+  const size_t r = blockIdx.x;
+  const float* xr = x + r * d;
+  const float* dnr = dn + r * d;
+  float ss = 0.f, gx = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float xv = xr[i];
+    ss += xv * xv;
+    gx += dnr[i] * w[i] * xv;
+  }
+  ss = block_sum(ss);
+  gx = block_sum(gx);
+  const float ir = 1.0f / sqrtf(ss / (float)d + eps);
+  const float c = gx * ir * ir * ir / (float)d;
+  float m = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = dnr[i] * w[i] * ir - xr[i] * c;
+    if (dres) v += dres[r * d + i];
+    out[r * d + i] = v;
+    m = fmaxf(m, fabsf(v));
+  }
+  if (out16) {
+    m = block_max(m);  // includes a __syncthreads: this thread's stores above are its own re-reads below
+    const float s = m > 0.f ? m : 1.f, inv = 1.f / s;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) out16[r * d + i] = __float2half_rn(out[r * d + i] * inv);
+    if (threadIdx.x == 0) scale[r] = s;
+  }
+}
+void launch_rmsnorm_bwd(const float* x, const float* w, const float* dn, const float* dres, int rows, int d, float eps,
+                        float* out, __half* out16, float* scale, cudaStream_t st) {
+  if (rows > 0) rmsnorm_bwd_kernel<<<rows, 256, 0, st>>>(x, w, dn, dres, d, eps, out, out16, scale);
+}
+
+// ------------------------------------------------------------------ RoPE tables (reference src/ops.rs:118-154)
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, int half, int max_pos, float* __restrict__ cs,
+                                  float* __restrict__ sn) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= max_pos * half) return;
+  int p = i / half, f = i % half;
+  float a = (float)p * inv_freq[f];
+  cs[i] = cosf(a);
+  sn[i] = sinf(a);
+}
+void launch_rope_table(const float* inv_freq, int half, int max_pos, float* cs, float* sn, cudaStream_t st) {
+  int n = max_pos * half;
+  if (n > 0) rope_table_kernel<<<(n + 255) / 256, 256, 0, st>>>(inv_freq, half, max_pos, cs, sn);
+}
+
+// ------------------------------------------------------------------ QK-norm + RoPE + f16 rounding
+// (reference src/attention.rs:170-185).  One CTA per token, one warp per head in turn.
+// Heads 0..nh-1 are q, nh..nh+nkv-1 are k, then nkv heads of v (copied and rounded only).
+__global__ void qk_rope_fwd_kernel(const float* __restrict__ q_raw, const float* __restrict__ k_raw,
+                                   const float* __restrict__ v_raw, const float* __restrict__ qw,
+                                   const float* __restrict__ kw, const int* __restrict__ pos,
+                                   const float* __restrict__ cs, const float* __restrict__ sn, int nh, int nkv, int hd,
+                                   int rot, int neox, float eps, __half* __restrict__ q16, __half* __restrict__ k16,
+                                   __half* __restrict__ v16) {
+  const size_t m = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int half = rot / 2;
+  const int p = pos[m];
+  for (int h = warp; h < nh + 2 * nkv; h += nwarps) {
+    if (h >= nh + nkv) {
+      const int hv = h - nh - nkv;
+      const float* src = v_raw + (m * nkv + hv) * hd;
+      __half* dst = v16 + (m * nkv + hv) * hd;
+      for (int i = lane; i < hd; i += 32) dst[i] = __float2half_rn(src[i]);
+      continue;
+    }
+    const bool is_q = h < nh;
+    const float* src = is_q ? q_raw + (m * nh + h) * hd : k_raw + (m * nkv + (h - nh)) * hd;
+    const float* nw = is_q ? qw : kw;
+    __half* dst = is_q ? q16 + (m * nh + h) * hd : k16 + (m * nkv + (h - nh)) * hd;
+    float ir = 1.f;
+    if (nw) {
+      float ss = 0.f;
+      for (int i = lane; i < hd; i += 32) ss += src[i] * src[i];
+      ss = warp_sum(ss);
+      ir = 1.0f / sqrtf(ss / (float)hd + eps);
+    }
+    // rotate pairs; elements beyond rot pass through
+    for (int i = lane; i < half; i += 32) {
+      const int a = neox ? i : 2 * i, b = neox ? i + half : 2 * i + 1;
+      float x1 = src[a], x2 = src[b];
+      if (nw) { x1 = x1 * (ir * nw[a]); x2 = x2 * (ir * nw[b]); }
+      const float c = cs[(size_t)p * half + i], s = sn[(size_t)p * half + i];
+      dst[a] = __float2half_rn(x1 * c - x2 * s);
+      dst[b] = __float2half_rn(x2 * c + x1 * s);
+    }
+    for (int i = rot + lane; i < hd; i += 32) {
+      float x = src[i];
+      if (nw) x = x * (ir * nw[i]);
+      dst[i] = __float2half_rn(x);
+    }
+  }
+}
+void launch_qk_rope_fwd(const float* q_raw, const float* k_raw, const float* v_raw, const float* qw, const float* kw,
+                        const int* pos, const float* cs, const float* sn, int M, int nh, int nkv, int hd, int rot,
+                        int neox, float eps, __half* q16, __half* k16, __half* v16, cudaStream_t st) {
+  if (M > 0) qk_rope_fwd_kernel<<<M, 256, 0, st>>>(q_raw, k_raw, v_raw, qw, kw, pos, cs, sn, nh, nkv, hd, rot, neox, eps, q16, k16, v16);
+}
+
+// Backward of the above (reference src/attention.rs:331-341): inverse rotation, then the
+// QK-norm backward with the norm's input recomputed from q_raw/k_raw; dv passes through.
+// Outputs are the three row-normalised f16 matrices (+ per-token scales) the q/k/v
+// backward matmuls consume.  Dynamic shared memory: (nh + 2*nkv) * hd floats.
+__global__ void qk_rope_bwd_kernel(const float* __restrict__ dq, const float* __restrict__ dk,
+                                   const float* __restrict__ dv, const float* __restrict__ q_raw,
+                                   const float* __restrict__ k_raw, const float* __restrict__ qw,
+                                   const float* __restrict__ kw, const int* __restrict__ pos,
+                                   const float* __restrict__ cs, const float* __restrict__ sn, int nh, int nkv, int hd,
+                                   int rot, int neox, float eps, __half* __restrict__ dq16, __half* __restrict__ dk16,
+                                   __half* __restrict__ dv16, float* __restrict__ sq, float* __restrict__ sk,
+                                   float* __restrict__ sv) {
+  extern __shared__ float buf[];  // [q heads | k heads | v heads] of this token, f32 results
+  __shared__ float wmax[3][32];
+  const size_t m = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int half = rot / 2;
+  const int p = pos[m];
+  float mx[3] = {0.f, 0.f, 0.f};
+  for (int h = warp; h < nh + 2 * nkv; h += nwarps) {
+    float* out = buf + (size_t)h * hd;
+    if (h >= nh + nkv) {
+      const float* src = dv + (m * nkv + (h - nh - nkv)) * hd;
+      for (int i = lane; i < hd; i += 32) { float v = src[i]; out[i] = v; mx[2] = fmaxf(mx[2], fabsf(v)); }
+      continue;
+    }
+    const bool is_q = h < nh;
+    const float* g = is_q ? dq + (m * nh + h) * hd : dk + (m * nkv + (h - nh)) * hd;
+    const float* xr = is_q ? q_raw + (m * nh + h) * hd : k_raw + (m * nkv + (h - nh)) * hd;
+    const float* nw = is_q ? qw : kw;
+    // inverse rotation into shared memory
+    for (int i = lane; i < half; i += 32) {
+      const int a = neox ? i : 2 * i, b = neox ? i + half : 2 * i + 1;
+      const float c = cs[(size_t)p * half + i], s = -sn[(size_t)p * half + i];
+      const float x1 = g[a], x2 = g[b];
+      out[a] = x1 * c - x2 * s;
+      out[b] = x2 * c + x1 * s;
+    }
+    for (int i = rot + lane; i < hd; i += 32) out[i] = g[i];
+    __syncwarp();
+    if (nw) {
+      float ss = 0.f, gx = 0.f;
+      for (int i = lane; i < hd; i += 32) { float xv = xr[i]; ss += xv * xv; gx += out[i] * nw[i] * xv; }
+      ss = warp_sum(ss);
+      gx = warp_sum(gx);
+      const float ir = 1.0f / sqrtf(ss / (float)hd + eps);
+      const float c = gx * ir * ir * ir / (float)hd;
+      for (int i = lane; i < hd; i += 32) out[i] = out[i] * nw[i] * ir - xr[i] * c;
+    }
+    __syncwarp();
+    float mm = 0.f;
+    for (int i = lane; i < hd; i += 32) mm = fmaxf(mm, fabsf(out[i]));
+    mx[is_q ? 0 : 1] = fmaxf(mx[is_q ? 0 : 1], mm);
+  }
+  for (int k = 0; k < 3; ++k) {
+    float v = warp_max(mx[k]);
+    if (lane == 0) wmax[k][warp] = v;
+  }
+  __syncthreads();
+  float s3[3];
+  for (int k = 0; k < 3; ++k) {
+    float v = 0.f;
+    for (int w = 0; w < nwarps; ++w) v = fmaxf(v, wmax[k][w]);
+    s3[k] = v > 0.f ? v : 1.f;
+  }
+  if (threadIdx.x == 0) { sq[m] = s3[0]; sk[m] = s3[1]; sv[m] = s3[2]; }
+  const int nq = nh * hd, nk = nkv * hd;
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) dq16[m * nq + i] = __float2half_rn(buf[i] / s3[0]);
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) dk16[m * nk + i] = __float2half_rn(buf[nq + i] / s3[1]);
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) dv16[m * nk + i] = __float2half_rn(buf[nq + nk + i] / s3[2]);
+}
+void launch_qk_rope_bwd(const float* dq, const float* dk, const float* dv, const float* q_raw, const float* k_raw,
+                        const float* qw, const float* kw, const int* pos, const float* cs, const float* sn, int M, int nh,
+                        int nkv, int hd, int rot, int neox, float eps, __half* dq16, __half* dk16, __half* dv16,
+                        float* sq, float* sk, float* sv, cudaStream_t st) {
+  if (M <= 0) return;
+  size_t smem = (size_t)(nh + 2 * nkv) * hd * sizeof(float);
+  qk_rope_bwd_kernel<<<M, 256, smem, st>>>(dq, dk, dv, q_raw, k_raw, qw, kw, pos, cs, sn, nh, nkv, hd, rot, neox, eps,
+                                             dq16, dk16, dv16, sq, sk, sv);
+}
+
+// ------------------------------------------------------------------ SwiGLU (reference src/model.rs:113-134, src/tensor.rs:122-143)
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) {
+  if (x >= 0.f) return 1.0f / (1.0f + expf(-x));
+  float e = expf(x);
+  return e / (1.0f + e);
+}
+__global__ void swiglu_fwd_kernel(const __half* __restrict__ g, const __half* __restrict__ u, __half* __restrict__ h,
+                                  size_t n) {
+  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (i + 1 < n) {
+    float2 gv = __half22float2(*(const __half2*)(g + i)), uv = __half22float2(*(const __half2*)(u + i));
+    *(__half2*)(h + i) = __floats2half2_rn(silu_f(gv.x) * uv.x, silu_f(gv.y) * uv.y);
+  } else if (i < n) {
+    h[i] = __float2half_rn(silu_f(__half2float(g[i])) * __half2float(u[i]));
+  }
+}
+void launch_swiglu_fwd(const __half* g, const __half* u, __half* h, size_t n, cudaStream_t st) {
+  if (n == 0) return;
+  size_t threads = (n + 1) / 2;
+  swiglu_fwd_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(g, u, h, n);
+}
+// dg = dh*u*silu'(g), du = dh*silu(g); both written row-normalised in f16 with per-row scales.
+__global__ void swiglu_bwd_kernel(const float* __restrict__ dh, const __half* __restrict__ g,
+                                  const __half* __restrict__ u, int ff, __half* __restrict__ dg16,
+                                  __half* __restrict__ du16, float* __restrict__ sg, float* __restrict__ su) {
+  const size_t r = blockIdx.x;
+  const float* dhr = dh + r * ff;
+  const __half* gr = g + r * ff;
+  const __half* ur = u + r * ff;
+  float mg = 0.f, mu = 0.f;
+  for (int i = threadIdx.x; i < ff; i += blockDim.x) {
+    const float gv = __half2float(gr[i]), uv = __half2float(ur[i]), d = dhr[i];
+    const float s = sigmoid_f(gv);
+    mg = fmaxf(mg, fabsf(d * uv * (s * (1.0f + gv * (1.0f - s)))));
+    mu = fmaxf(mu, fabsf(d * silu_f(gv)));
+  }
+  mg = block_max(mg);
+  mu = block_max(mu);
+  const float s_g = mg > 0.f ? mg : 1.f, s_u = mu > 0.f ? mu : 1.f;
+  const float ig = 1.f / s_g, iu = 1.f / s_u;
+  for (int i = threadIdx.x; i < ff; i += blockDim.x) {
+    const float gv = __half2float(gr[i]), uv = __half2float(ur[i]), d = dhr[i];
+    const float s = sigmoid_f(gv);
+    dg16[r * ff + i] = __float2half_rn(d * uv * (s * (1.0f + gv * (1.0f - s))) * ig);
+    du16[r * ff + i] = __float2half_rn(d * silu_f(gv) * iu);
+  }
+  if (threadIdx.x == 0) { sg[r] = s_g; su[r] = s_u; }
+}
+void launch_swiglu_bwd(const float* dh, const __half* g, const __half* u, int rows, int ff, __half* dg16, __half* du16,
+                       float* sg, float* su, cudaStream_t st) {
+  if (rows > 0) swiglu_bwd_kernel<<<rows, 256, 0, st>>>(dh, g, u, ff, dg16, du16, sg, su);
+}
+
+// ------------------------------------------------------------------ row gather / scatter
+__global__ void gather_f32_rows_kernel(const float* __restrict__ x, const int* __restrict__ idx, int d,
+                                       float* __restrict__ out) {
+  const size_t r = blockIdx.x;
+  const float* src = x + (size_t)idx[r] * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) out[r * d + i] = src[i];
+}
+void launch_gather_f32_rows(const float* x, const int* idx, int rows, int d, float* out, cudaStream_t st) {
+  if (rows > 0) gather_f32_rows_kernel<<<rows, 256, 0, st>>>(x, idx, d, out);
+}
+// dx[idx[r], :] += src[r, :]   (atomic: two targets may name the same position)
+__global__ void scatter_add_rows_kernel(const float* __restrict__ src, const int* __restrict__ idx, int d,
+                                        float* __restrict__ dx) {
+  const size_t r = blockIdx.x;
+  float* dst = dx + (size_t)idx[r] * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(dst + i, src[r * d + i]);
+}
+void launch_scatter_add_rows(const float* src, const int* idx, int rows, int d, float* dx, cudaStream_t st) {
+  if (rows > 0) scatter_add_rows_kernel<<<rows, 256, 0, st>>>(src, idx, d, dx);
+}
+
+// ------------------------------------------------------------------ cross-entropy over one row of logits
+// (reference src/model.rs:579-596, src/ops.rs:238-247): lse with an f64 normaliser, logp of
+// the target, hit = no logit above the target's, and d16 = p - onehot in f16 with the row scale
+// w (so dlogits = w*(p - onehot) exactly as the reference forms it).
+__global__ void ce_row_kernel(const float* __restrict__ logits, int v, const int* __restrict__ target,
+                              const float* __restrict__ weight, float* __restrict__ logp, int* __restrict__ hits,
+                              __half* __restrict__ d16, float* __restrict__ scale, int* status) {
+  const size_t r = blockIdx.x;
+  const float* row = logits + r * v;
+  const int tgt = target[r];
+  if (tgt < 0 || tgt >= v) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, RT_ERR_BAD_INDEX);
+    return;
+  }
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < v; i += blockDim.x) m = fmaxf(m, row[i]);
+  m = block_max(m);
+  double s = 0.0;
+  for (int i = threadIdx.x; i < v; i += blockDim.x) s += (double)expf(row[i] - m);
+  s = block_sum_d(s);
+  const float tl = row[tgt];
+  if (threadIdx.x == 0) {
+    logp[r] = tl - (m + (float)log(s));
+    if (tl >= m) atomicAdd(hits, 1);
+    if (scale) scale[r] = weight[r];
+  }
+  if (d16) {
+    const float inv = (float)(1.0 / s);
+    for (int i = threadIdx.x; i < v; i += blockDim.x) {
+      float p = expf(row[i] - m) * inv;
+      if (i == tgt) p -= 1.0f;
+      d16[r * v + i] = __float2half_rn(p);
+    }
+  }
+}
+void launch_ce_rows(const float* logits, int rows, int v, const int* target, const float* weight, float* logp, int* hits,
+                    __half* d16, float* scale, int* status, cudaStream_t st) {
+  if (rows > 0) ce_row_kernel<<<rows, 1024, 0, st>>>(logits, v, target, weight, logp, hits, d16, scale, status);
+}
+
+// ------------------------------------------------------------------ LoRA shadows and gradients
+// 16-bit operand copies of one adapter, rebuilt after every parameter update:
+//   a_s  [r x K]  f16 = s*A      (weight of Hs = X.(sA)^T)
+//   a_h  [r x K]  f16 = A        (extra rows of the backward matmul: dX += Gs.A)
+//   bp   [N x 64] f16 = B, zero padded (extra columns of the forward matmul: Y += Hs.B^T)
+//   bt_s [r x N]  f16 = s*B^T    (weight of Gs = dY.(sB))
+__global__ void lora_refresh_kernel(const float* __restrict__ a, const float* __restrict__ b, int r, int K, int N,
+                                    float s, __half* a_s, __half* a_h, __half* bp, __half* bt_s) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t na = (size_t)r * K, nb = (size_t)N * 64;
+  if (i < na) {
+    a_s[i] = __float2half_rn(a[i] * s);
+    a_h[i] = __float2half_rn(a[i]);
+  }
+  if (i < nb) {
+    const int n = (int)(i / 64), j = (int)(i % 64);
+    const float v = j < r ? b[(size_t)n * r + j] : 0.f;
+    bp[i] = __float2half_rn(v);
+    if (j < r) bt_s[(size_t)j * N + n] = __float2half_rn(v * s);
+  }
+}
+void launch_lora_refresh(const float* a, const float* b, int r, int K, int N, float s, __half* a_s, __half* a_h,
+                         __half* bp, __half* bt_s, cudaStream_t st) {
+  size_t n = (size_t)r * K > (size_t)N * 64 ? (size_t)r * K : (size_t)N * 64;
+  lora_refresh_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a, b, r, K, N, s, a_s, a_h, bp, bt_s);
+}
+
+// Token-contraction for the LoRA gradients (reference src/linear.rs:108-116):
+//   part[split][i, j] = sum_{m in split} pscale[m] * P[m, i] * qscale[m] * Q[m, j],  i < r, j < C
+// P is [M x 64] f16, Q is [M x C] f16.  A second kernel adds the splits, in order, into
+// out[i*so_i + j*so_j] (deterministic: no float atomics).
+//   dA: P = Gs (unit rows, pscale = row scale of dY), Q = X        -> ga[r x K]: so_i = K, so_j = 1
+//   dB: P = Hs,                       Q = dY (qscale = its scale)  -> gb[N x r]: so_i = 1, so_j = r
+constexpr int LG_TOK = 32;
+__global__ void __launch_bounds__(256)
+lora_grad_partial_kernel(const __half* __restrict__ P, const __half* __restrict__ Q, const float* __restrict__ pscale,
+                         const float* __restrict__ qscale, int M, int C, int r, int tokens_per_split,
+                         float* __restrict__ part) {
+  __shared__ float sP[LG_TOK][65];
+  __shared__ float sQ[LG_TOK][64];
+  const int j0 = blockIdx.x * 64;
+  const int m_begin = blockIdx.y * tokens_per_split;
+  const int m_end = min(M, m_begin + tokens_per_split);
+  const int tj = threadIdx.x & 63, ti = threadIdx.x >> 6;  // column, row group (4 groups)
+  float acc[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) acc[k] = 0.f;
+  const int rows_per = (r + 3) / 4;  // <= 16
+  for (int m0 = m_begin; m0 < m_end; m0 += LG_TOK) {
+    __syncthreads();
+    for (int e = threadIdx.x; e < LG_TOK * 64; e += 256) {
+      const int mm = e >> 6, c = e & 63, m = m0 + mm;
+      float pv = 0.f, qv = 0.f;
+      if (m < m_end) {
+        const float sc = (pscale ? pscale[m] : 1.f) * (qscale ? qscale[m] : 1.f);
+        if (c < r) pv = __half2float(P[(size_t)m * 64 + c]) * sc;
+        if (j0 + c < C) qv = __half2float(Q[(size_t)m * C + j0 + c]);
+      }
+      sP[mm][c] = pv;
+      sQ[mm][c] = qv;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int mm = 0; mm < LG_TOK; ++mm) {
+      const float q = sQ[mm][tj];
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        if (k < rows_per) acc[k] += sP[mm][ti + 4 * k] * q;
+    }
+  }
+  float* dst = part + (size_t)blockIdx.y * r * C;
+  for (int k = 0; k < rows_per; ++k) {
+    const int i = ti + 4 * k;
+    if (i < r && j0 + tj < C) dst[(size_t)i * C + j0 + tj] = acc[k];
+  }
+}
+__global__ void lora_grad_reduce_kernel(const float* __restrict__ part, int splits, int C, int r, size_t so_i,
+                                        size_t so_j, float* __restrict__ out) {
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= (size_t)r * C) return;
+  const int i = (int)(e / C), j = (int)(e % C);
+  float s = 0.f;
+  for (int k = 0; k < splits; ++k) s += part[(size_t)k * r * C + e];
+  out[i * so_i + j * so_j] += s;
+}
+size_t lora_grad_workspace_floats(int M, int C, int r) {
+  int splits = (M + 511) / 512;
+  if (splits < 1) splits = 1;
+  return (size_t)splits * r * C;
+}
+void launch_lora_grad(const __half* P, const __half* Q, const float* pscale, const float* qscale, int M, int C, int r,
+                      size_t so_i, size_t so_j, float* out, float* workspace, cudaStream_t st) {
+  if (M <= 0 || r <= 0) return;
+  int splits = (M + 511) / 512;
+  if (splits < 1) splits = 1;
+  const int tps = ((M + splits - 1) / splits + LG_TOK - 1) / LG_TOK * LG_TOK;
+  splits = (M + tps - 1) / tps;
+  dim3 grid((C + 63) / 64, splits);
+  lora_grad_partial_kernel<<<grid, 256, 0, st>>>(P, Q, pscale, qscale, M, C, r, tps, workspace);
+  const size_t n = (size_t)r * C;
+  lora_grad_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(workspace, splits, C, r, so_i, so_j, out);
+}
+
+// ------------------------------------------------------------------ optimiser (reference src/optim.rs:48-90)
+// Sum of squares in f64: fixed-size blocks write partials, one block adds them in order.
+__global__ void sumsq_partial_kernel(const float* __restrict__ g, size_t n, double* __restrict__ part) {
+  double s = 0.0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    double v = (double)g[i];
+    s += v * v;
+  }
+  s = block_sum_d(s);
+  if (threadIdx.x == 0) part[blockIdx.x] = s;
+}
+__global__ void sumsq_final_kernel(const double* __restrict__ part, int n, double* __restrict__ out) {
+  double s = 0.0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += part[i];
+  s = block_sum_d(s);
+  if (threadIdx.x == 0) out[0] = s;
+}
+void launch_sumsq(const float* g, size_t n, double* part /* >= 1024 */, double* out, cudaStream_t st) {
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 1024) blocks = 1024;
+  if (blocks < 1) blocks = 1;
+  sumsq_partial_kernel<<<blocks, 256, 0, st>>>(g, n, part);
+  sumsq_final_kernel<<<1, 256, 0, st>>>(part, blocks, out);
+}
+// clip (scale read from the device-side norm) fused with the AdamW update.
+__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                             size_t n, const double* __restrict__ sumsq, float max_norm, float lr, float beta1,
+                             float beta2, float eps, float wd, float bc1, float bc2, float* __restrict__ norm_out) {
+  const float norm = (float)sqrt(sumsq[0]);
+  float clip = 1.0f;
+  if (max_norm > 0.f && norm > max_norm) clip = max_norm / (norm + 1e-6f);
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0 && norm_out) norm_out[0] = norm;
+  if (i >= n) return;
+  const float gi = clip != 1.0f ? g[i] * clip : g[i];
+  g[i] = gi;
+  const float mi = beta1 * m[i] + (1.0f - beta1) * gi;
+  const float vi = beta2 * v[i] + (1.0f - beta2) * gi * gi;
+  m[i] = mi;
+  v[i] = vi;
+  const float mh = mi / bc1, vh = vi / bc2;
+  p[i] -= lr * (mh / (sqrtf(vh) + eps) + wd * p[i]);
+}
+void launch_adamw(float* p, float* g, float* m, float* v, size_t n, const double* sumsq, float max_norm, float lr,
+                  float beta1, float beta2, float eps, float wd, float bc1, float bc2, float* norm_out,
+                  cudaStream_t st) {
+  if (n == 0) return;
+  adamw_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p, g, m, v, n, sumsq, max_norm, lr, beta1, beta2, eps, wd,
+                                                             bc1, bc2, norm_out);
+}
+
+// ------------------------------------------------------------------ misc
+__global__ void absmax_kernel(const float* __restrict__ x, size_t n, float* __restrict__ out) {
+  float m = 0.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    m = fmaxf(m, fabsf(x[i]));
+  m = block_max(m);
+  if (threadIdx.x == 0) atomicMax((int*)out, __float_as_int(m));  // non-negative floats order like ints
+}
+// y16 = x / max(amax, tiny); inv/scale read on device
+__global__ void scale_to_f16_kernel(const float* __restrict__ x, size_t n, const float* __restrict__ amax,
+                                    __half* __restrict__ y) {
+  const float a = amax[0];
+  const float inv = a > 0.f ? 1.f / a : 1.f;
+  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (i + 1 < n) {
+    float2 v = *(const float2*)(x + i);
+    *(__half2*)(y + i) = __floats2half2_rn(v.x * inv, v.y * inv);
+  } else if (i < n) y[i] = __float2half_rn(x[i] * inv);
+}
+void launch_global_normalize(const float* x, size_t n, float* amax_dev, __half* y16, cudaStream_t st) {
+  if (n == 0) return;
+  cudaMemsetAsync(amax_dev, 0, sizeof(float), st);
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 1184) blocks = 1184;
+  absmax_kernel<<<blocks, 256, 0, st>>>(x, n, amax_dev);
+  size_t threads = (n + 1) / 2;
+  scale_to_f16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(x, n, amax_dev, y16);
 }
 
 }  // namespace rt

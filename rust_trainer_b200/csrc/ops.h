@@ -1,0 +1,50 @@
+// Launchers of the memory-bound device ops (ops.cu) and attention (attention.cu).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace rt {
+
+void launch_f32_to_16(const float* in, void* out, size_t n, bool to_f16, cudaStream_t st);
+void launch_normalize_rows(const float* x, int rows, int d, __half* y16, float* scale, cudaStream_t st);
+void launch_rmsnorm_fwd(const float* x, const float* w, int rows, int d, float eps, __half* y16, cudaStream_t st);
+void launch_rmsnorm_bwd(const float* x, const float* w, const float* dn, const float* dres, int rows, int d, float eps,
+                        float* out, __half* out16, float* scale, cudaStream_t st);
+void launch_rope_table(const float* inv_freq, int half, int max_pos, float* cs, float* sn, cudaStream_t st);
+void launch_qk_rope_fwd(const float* q_raw, const float* k_raw, const float* v_raw, const float* qw, const float* kw,
+                        const int* pos, const float* cs, const float* sn, int M, int nh, int nkv, int hd, int rot,
+                        int neox, float eps, __half* q16, __half* k16, __half* v16, cudaStream_t st);
+void launch_qk_rope_bwd(const float* dq, const float* dk, const float* dv, const float* q_raw, const float* k_raw,
+                        const float* qw, const float* kw, const int* pos, const float* cs, const float* sn, int M, int nh,
+                        int nkv, int hd, int rot, int neox, float eps, __half* dq16, __half* dk16, __half* dv16,
+                        float* sq, float* sk, float* sv, cudaStream_t st);
+void launch_swiglu_fwd(const __half* g, const __half* u, __half* h, size_t n, cudaStream_t st);
+void launch_swiglu_bwd(const float* dh, const __half* g, const __half* u, int rows, int ff, __half* dg16, __half* du16,
+                       float* sg, float* su, cudaStream_t st);
+void launch_gather_f32_rows(const float* x, const int* idx, int rows, int d, float* out, cudaStream_t st);
+void launch_scatter_add_rows(const float* src, const int* idx, int rows, int d, float* dx, cudaStream_t st);
+void launch_ce_rows(const float* logits, int rows, int v, const int* target, const float* weight, float* logp, int* hits,
+                    __half* d16, float* scale, int* status, cudaStream_t st);
+void launch_lora_refresh(const float* a, const float* b, int r, int K, int N, float s, __half* a_s, __half* a_h,
+                         __half* bp, __half* bt_s, cudaStream_t st);
+size_t lora_grad_workspace_floats(int M, int C, int r);
+void launch_lora_grad(const __half* P, const __half* Q, const float* pscale, const float* qscale, int M, int C, int r,
+                      size_t so_i, size_t so_j, float* out, float* workspace, cudaStream_t st);
+void launch_sumsq(const float* g, size_t n, double* part, double* out, cudaStream_t st);
+void launch_adamw(float* p, float* g, float* m, float* v, size_t n, const double* sumsq, float max_norm, float lr,
+                  float beta1, float beta2, float eps, float wd, float bc1, float bc2, float* norm_out,
+                  cudaStream_t st);
+void launch_global_normalize(const float* x, size_t n, float* amax_dev, __half* y16, cudaStream_t st);
+
+// ---- attention.cu: causal GQA attention over a concatenation of independent sequences.
+// q [M x nh x hd], k/v [M x nkv x hd] f16 (q unscaled; the kernels apply 1/sqrt(hd)).
+// seq_start[m] = index of the first token of m's sequence.  lse is [nh x M].
+int launch_attn_fwd(const __half* q, const __half* k, const __half* v, const int* seq_start, int M, int nh, int nkv,
+                    int hd, __half* o, float* lse, cudaStream_t st);
+// dO16 is dO divided by a global scale (device scalar `do_scale`); outputs are true-scale f32.
+int launch_attn_bwd(const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
+                    const float* do_scale, const float* lse, const int* seq_start, int M, int nh, int nkv, int hd,
+                    float* delta /* [nh x M] scratch */, float* dq, float* dk, float* dv, cudaStream_t st);
+
+}  // namespace rt

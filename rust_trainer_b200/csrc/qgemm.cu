@@ -37,13 +37,15 @@ constexpr int SMEM_BYTES = OFF_BAR + N_BARS * 8 + 16 + 1024;
 
 struct KParams {
   const uint8_t* bricks;
-  int brick_bytes, nbk, fmt, wbf16;
+  int brick_bytes, nbk, fmt;
+  int act_f16;   // activations (and therefore the unpacked weight tile) are f16, else bf16
+  int conv16;    // 16-bit weight whose type differs from the activations': 1 = f16->bf16, 2 = bf16->f16
   int dir, out_rows, M, TN;
   int n_main, lora_mmas;
   int n_row_tiles, n_tok_tiles;
   void* out;
-  __nv_bfloat16* out2;
   int out_dtype, accumulate, ld_out;
+  const float* row_scale;  // optional per-token factor applied to the result
   const float* bias;
   uint32_t idesc_main, idesc_lora;
   int* status;
@@ -306,14 +308,36 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         const int st = it % NS;
         const uint32_t ph = (it / NS) & 1;
         if (!mbar_wait(&stage_empty[st], ph ^ 1, p.status, 201)) { ok = false; break; }
-        if (!is16 && s < p.n_main) {
+        if (is16 && p.conv16 && s < p.n_main) {
+          // The TMA'd 16-bit weight tile has the other 16-bit type: convert it in place
+          // (element-wise, so the swizzled placement is untouched).
+          if (!mbar_wait(&full[st], ph, p.status, 203)) { ok = false; break; }
+          uint4* tile = (uint4*)(sW + st * W_STAGE);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint4 v = tile[t + i * 128];
+            uint32_t* w = (uint32_t*)&v;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (p.conv16 == 1) {
+                __nv_bfloat162 b = __float22bfloat162_rn(__half22float2(*(__half2*)&w[j]));
+                w[j] = *(uint32_t*)&b;
+              } else {
+                __half2 h = __float22half2_rn(__bfloat1622float2(*(__nv_bfloat162*)&w[j]));
+                w[j] = *(uint32_t*)&h;
+              }
+            }
+            tile[t + i * 128] = v;
+          }
+          fence_proxy_async_smem();
+        } else if (!is16 && s < p.n_main) {
           const int rs = rit % NR;
           const uint32_t rph = (rit / NR) & 1;
           if (!mbar_wait(&raw_full[rs], rph, p.status, 202)) { ok = false; break; }
           const uint8_t* raw = sRaw + rs * RAW_STAGE;
           uint8_t* dst = sW + st * W_STAGE;
-          if (p.wbf16) unpack_pair<true>(p.fmt, raw, p.brick_bytes, t, dst);
-          else unpack_pair<false>(p.fmt, raw, p.brick_bytes, t, dst);
+          if (p.act_f16) unpack_pair<false>(p.fmt, raw, p.brick_bytes, t, dst);
+          else unpack_pair<true>(p.fmt, raw, p.brick_bytes, t, dst);
           fence_proxy_async_smem();
           mbar_arrive(&raw_empty[rs]);
           ++rit;
@@ -345,15 +369,18 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
             const int tok = m0 + c * 32 + j;
             if (tok < p.M) {
               const size_t idx = (size_t)tok * p.ld_out + row;
-              float val = __uint_as_float(v[j]) + bias_v;
+              float val = __uint_as_float(v[j]);
+              if (p.row_scale) val *= p.row_scale[tok];
+              val += bias_v;
               if (p.out_dtype == OUT_F32) {
                 float* o = (float*)p.out;
                 if (p.accumulate) val += o[idx];
                 o[idx] = val;
-              } else {
+              } else if (p.out_dtype == OUT_BF16) {
                 ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(val);
+              } else {
+                ((__half*)p.out)[idx] = __float2half_rn(val);
               }
-              if (p.out2) p.out2[idx] = __float2bfloat16_rn(val);
             }
           }
         }
@@ -411,16 +438,10 @@ static int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t co
   return r == CUDA_SUCCESS ? RT_OK : RT_ERR_CUDA;
 }
 
-static int g_force_wbf16 = -1;
-
 int qgemm_launch(const QWeight& w, const QGemmArgs& a, int* status_dev, int num_sms, cudaStream_t st) {
   if (!g_encode) {
     int rc = qgemm_init();
     if (rc) return rc;
-  }
-  if (g_force_wbf16 < 0) {
-    const char* e = getenv("RT_B200_WBF16");
-    g_force_wbf16 = (e && e[0] == '1') ? 1 : 0;
   }
   if (a.M <= 0) return RT_OK;
   const bool is16 = fmt_is_16bit(w.fmt);
@@ -435,7 +456,9 @@ int qgemm_launch(const QWeight& w, const QGemmArgs& a, int* status_dev, int num_
   p.brick_bytes = fmt_brick_bytes(w.fmt);
   p.nbk = w.nbk;
   p.fmt = w.fmt;
-  p.wbf16 = (!is16 && g_force_wbf16) ? 1 : 0;
+  p.act_f16 = a.act_f16 ? 1 : 0;
+  p.conv16 = (w.fmt == GGML_F16 && !a.act_f16) ? 1 : (w.fmt == GGML_BF16 && a.act_f16) ? 2 : 0;
+  p.row_scale = a.row_scale;
   p.dir = a.dir;
   p.out_rows = out_rows;
   p.M = a.M;
@@ -445,18 +468,18 @@ int qgemm_launch(const QWeight& w, const QGemmArgs& a, int* status_dev, int num_
   p.n_row_tiles = (out_rows + 127) / 128;
   p.n_tok_tiles = (a.M + p.TN - 1) / p.TN;
   p.out = a.out;
-  p.out2 = (__nv_bfloat16*)a.out2;
   p.out_dtype = a.out_dtype;
   p.accumulate = a.accumulate;
-  p.ld_out = out_rows;
+  p.ld_out = a.ld_out > 0 ? a.ld_out : out_rows;
   p.bias = a.dir == QG_FWD ? a.bias : nullptr;
-  const int a_fmt = (w.fmt == GGML_BF16 || p.wbf16) ? 1 : 0;
-  p.idesc_main = umma_idesc(a_fmt, 1, a.dir == QG_BWD ? 1 : 0, 0, 128, p.TN);
-  p.idesc_lora = umma_idesc(1, 1, a.dir == QG_BWD ? 1 : 0, 0, 128, p.TN);
+  // tcgen05.mma kind::f16 needs A and B of ONE 16-bit type (f16 x bf16 is an illegal instruction).
+  const int ab_fmt = a.act_f16 ? 0 : 1;
+  p.idesc_main = umma_idesc(ab_fmt, ab_fmt, a.dir == QG_BWD ? 1 : 0, 0, 128, p.TN);
+  p.idesc_lora = p.idesc_main;
   p.status = status_dev;
 
   CUtensorMap tm_act, tm_w16, tm_lact, tm_lw;
-  int rc = make_map(&tm_act, a.act, (uint64_t)a.M, (uint64_t)contract, 64, (uint32_t)p.TN, true);
+  int rc = make_map(&tm_act, a.act, (uint64_t)a.M, (uint64_t)contract, 64, (uint32_t)p.TN, !a.act_f16);
   if (rc) return rc;
   tm_w16 = tm_act;
   tm_lact = tm_act;
@@ -466,10 +489,10 @@ int qgemm_launch(const QWeight& w, const QGemmArgs& a, int* status_dev, int num_
     if (rc) return rc;
   }
   if (a.lora.rank > 0) {
-    rc = make_map(&tm_lact, a.lora.act, (uint64_t)a.M, 64, 64, (uint32_t)p.TN, true);
+    rc = make_map(&tm_lact, a.lora.act, (uint64_t)a.M, 64, 64, (uint32_t)p.TN, !a.act_f16);
     if (rc) return rc;
-    if (a.dir == QG_FWD) rc = make_map(&tm_lw, a.lora.w, (uint64_t)w.rows, 64, 64, 64, true);
-    else rc = make_map(&tm_lw, a.lora.w, (uint64_t)a.lora.rank, (uint64_t)w.cols, 64, 64, true);
+    if (a.dir == QG_FWD) rc = make_map(&tm_lw, a.lora.w, (uint64_t)w.rows, 64, 64, 64, !a.act_f16);
+    else rc = make_map(&tm_lw, a.lora.w, (uint64_t)a.lora.rank, (uint64_t)w.cols, 64, 64, !a.act_f16);
     if (rc) return rc;
   }
   const int n_tiles = p.n_row_tiles * p.n_tok_tiles;

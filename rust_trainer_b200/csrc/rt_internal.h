@@ -19,26 +19,29 @@ void launch_gather_rows(const QWeight& w, const int* ids_dev, int n, float* out,
 
 // ---- qgemm.cu
 enum { QG_FWD = 0, QG_BWD = 1 };
-enum { OUT_F32 = 0, OUT_BF16 = 1 };
+enum { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2 };  // same values as RT_DT_* in the public header
 
 // Extra contraction chunk of rank r <= 64 appended after the frozen weight's own chunks:
 //   forward : Y += Hs[M x 64] . Bp[N x 64]^T      (Hs = s.X.A^T, zero beyond column r)
 //   backward: dX += Gs[M x 64] . A[r x K]          (Gs = s.dY.B,  zero beyond column r)
+// Both operands have the 16-bit type of the call's activations.
 struct LoraSide {
-  const __nv_bfloat16* act = nullptr;  // Hs / Gs, [M x 64] bf16
-  const __nv_bfloat16* w = nullptr;    // forward: Bp [N x 64]; backward: A [r x K]
+  const void* act = nullptr;  // Hs / Gs, [M x 64]
+  const void* w = nullptr;    // forward: Bp [N x 64]; backward: A [r x K]
   int rank = 0;
 };
 
 struct QGemmArgs {
   int dir = QG_FWD;
-  const __nv_bfloat16* act = nullptr;  // forward: X [M x K]; backward: dY [M x N]
+  const void* act = nullptr;           // forward: X [M x K]; backward: dY [M x N]; f16 or bf16
+  int act_f16 = 0;                     // 1: activations are f16, 0: bf16
   int M = 0;
   void* out = nullptr;                 // forward: Y [M x N]; backward: dX [M x K]
   int out_dtype = OUT_F32;
   int accumulate = 0;                  // out += result (f32 only)
+  int ld_out = 0;                      // row pitch of out in elements (0: the output width)
   const float* bias = nullptr;         // forward only, per output feature
-  void* out2 = nullptr;                // optional second copy of the result in bf16
+  const float* row_scale = nullptr;    // optional per-token factor on the result (before bias)
   LoraSide lora;
 };
 
