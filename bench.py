@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Throughput of the LoRA training step on the frozen quantised linears (trained tokens/s).
+
+    python bench.py --gpus N --steps K --warmup W            # the CUDA path (this repository)
+    python bench.py --impl reference --steps K --warmup W    # the CPU algorithm of the reference
+
+One step = zero_grad + forward + recompute + backward over the local batch (+ one all-reduce
+of the flat LoRA-gradient buffer when N > 1) + gradient clipping + AdamW, i.e. one iteration
+of the reference's Trainer::run loop (src/train.rs:316-381).  Prints ONE JSON line on rank 0.
+
+The N = 1 workload is BASELINE.json configs[1]: a synthetic Qwen3-0.6B-shaped GGUF model with
+Q8_0 weights, 16 sequences x 512 uniform-random ids, loss on the last 30 % of each sequence,
+LoRA r=16 alpha=32 on the seven projections, warm-up 2 + cosine LR, recomputation on.  For
+N > 1 every rank holds a replica and its own 16 x 512 batch (weak scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE.json configs[1]
+    "qwen3-0.6b-q8_0-16x512": dict(preset="qwen3-0.6b", quant="Q8_0", n_seq=16, seq_len=512, answer_frac=0.30, rank=16,
+                                   alpha=32.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=2, lr_total=20, min_ratio=0.1),
+    # BASELINE.json configs[0] (the reference's own CPU-runnable case)
+    "qwen3-0.6b-q4_0-4x256": dict(preset="qwen3-0.6b", quant="Q4_0", n_seq=4, seq_len=256, answer_frac=0.50, rank=16,
+                                  alpha=32.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=0, lr_total=1, min_ratio=0.1),
+    # small shape for quick checks of this script
+    "tiny": dict(preset="tiny-qwen3", quant="Q8_0", n_seq=4, seq_len=64, answer_frac=0.5, rank=8, alpha=16.0, lr=1e-4,
+                 wd=0.01, clip=1.0, lr_warmup=2, lr_total=20, min_ratio=0.1),
+}
+DEFAULT_WORKLOAD = "qwen3-0.6b-q8_0-16x512"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(tflops=float(p["bf16_tflops_sustained"]), hbm=float(p["hbm_gbs"]), source="measured")
+    return dict(tflops=1400.0, hbm=6650.0, source="fallback")
+
+
+def make_batch(spec, wl, seed):
+    from rust_trainer_b200 import synth
+
+    toks = synth.token_batch(spec, wl["n_seq"], wl["seq_len"], seed)
+    answer_start = int(np.ceil(wl["seq_len"] * (1.0 - wl["answer_frac"])))
+    tps, tts = [], []
+    for s in range(wl["n_seq"]):
+        tp, tt = synth.answer_targets(toks[s], answer_start)
+        tps.append(tp + s * wl["seq_len"])
+        tts.append(tt)
+    return toks, np.concatenate(tps), np.concatenate(tts), answer_start
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.idx = device_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=max(smax) if smax else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+# ----------------------------------------------------------------------------- reference arm (CPU)
+def cpu_reference_run(wl_name: str, steps: int, warmup: int, sample_tokens: int | None = None):
+    """Times the CPU restatement of the reference's algorithm (oracle/) on a bounded sample of
+    the workload: ONE sequence of `sample_tokens` ids of the same model, same LoRA shape, loss on
+    the same trailing fraction, forward + recompute + backward + clip + AdamW per step."""
+    from oracle import oracle as O
+    from rust_trainer_b200 import synth
+
+    wl = WORKLOADS[wl_name]
+    spec = synth.preset(wl["preset"], quant=wl["quant"], seed=0)
+    tensors = synth.build_tensors(spec)
+    om = O.OracleModel(spec.config(), tensors)
+    om.attach_lora(synth.lora_adapters(spec, wl["rank"], wl["alpha"], seed=1234))
+    if sample_tokens is None:
+        sample_tokens = 128 if (steps + warmup) <= 8 else 64
+    sample_tokens = min(sample_tokens, wl["seq_len"])
+    toks = synth.token_batch(spec, 1, sample_tokens, 99)[0]
+    a0 = int(np.ceil(sample_tokens * (1.0 - wl["answer_frac"])))
+    tp, tt = synth.answer_targets(toks, a0)
+    w = np.full(tp.size, 1.0 / tp.size, np.float32)
+    state = {}
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        om.zero_grad()
+        om.forward_backward(toks, tp, tt, w)
+        om.clip_grad_norm(wl["clip"])
+        om.adamw_step(state, wl["lr"], wd=wl["wd"])
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    ms = 1e3 * float(np.mean(times))
+    cores = O.lib().orc_num_threads()
+    return dict(value=sample_tokens / (ms / 1e3), ms_per_step=ms, cores=cores,
+                sample=f"1 sequence x {sample_tokens} tokens of the same model per step (loss on the last "
+                       f"{int(wl['answer_frac'] * 100)} %), forward + recompute + backward + clip + AdamW"), spec
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    wl = WORKLOADS[args.workload]
+    r, spec = cpu_reference_run(args.workload, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": "trained_tokens_per_s", "value": r["value"], "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "model": wl["preset"], "quant": wl["quant"], "lora_rank": wl["rank"],
+                   "note": "CPU restatement of the reference algorithm (oracle/), not the reference binary: no Rust "
+                           "toolchain and rie-core is not vendored"},
+        "cpu_baseline": {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+        "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ----------------------------------------------------------------------------- CUDA arm
+class DevPtr:
+    """Lets torch view device memory owned by the C library (for the NCCL all-reduce)."""
+
+    def __init__(self, ptr: int, n: int):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+
+def run_ours(args):
+    import torch
+    import rust_trainer_b200 as rt
+    from rust_trainer_b200 import synth
+    from rust_trainer_b200._lib import lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the CUDA path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    wl = WORKLOADS[args.workload]
+    L = lib()
+
+    spec = synth.preset(wl["preset"], quant=wl["quant"], seed=0)
+    tensors = synth.build_tensors(spec)
+    ctx = rt.Context(local_rank)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    L.rt_ctx_set_stream(ctx._h, C.c_void_p(stream.cuda_stream))
+    model = rt.Model(ctx, spec.config(), tensors)
+    n_params = model.attach_lora(wl["rank"], wl["alpha"], None, 1234)
+    model.load_adapters(synth.lora_adapters(spec, wl["rank"], wl["alpha"], seed=1234))
+    del tensors
+
+    toks, tpos, ttok, answer_start = make_batch(spec, wl, seed=100 + rank)
+    n_targets = tpos.size
+    global_targets = n_targets * world
+    tokens_per_step = toks.size * world
+    # pinned host buffers for the end-to-end arm
+    pin = lambda a: torch.from_numpy(a.copy()).pin_memory().numpy()
+    h_toks, h_tpos, h_ttok = pin(toks.reshape(-1)), pin(tpos), pin(ttok)
+    h_w = pin(np.full(n_targets, 1.0 / global_targets, np.float32))
+    h_offs = pin(np.arange(0, toks.size + 1, wl["seq_len"], dtype=np.int32))
+    h_logp = torch.empty(n_targets, dtype=torch.float32).pin_memory().numpy()
+    seqs = [h_toks[i * wl["seq_len"]:(i + 1) * wl["seq_len"]] for i in range(wl["n_seq"])]
+    i32p, f32p = C.POINTER(C.c_int32), C.POINTER(C.c_float)
+    ip = lambda a: a.ctypes.data_as(i32p)
+    fp = lambda a: a.ctypes.data_as(f32p)
+
+    gptr, gn = model.grad_buffer()
+    grad_view = torch.as_tensor(DevPtr(gptr, gn), device=f"cuda:{local_rank}") if world > 1 else None
+    loss_buf = torch.zeros(1, device=f"cuda:{local_rank}")
+    step_no = [0]
+
+    def lr_now():
+        return rt.schedule_lr(wl["lr"], wl["lr_warmup"], wl["lr_total"], wl["min_ratio"], step_no[0] % wl["lr_total"])
+
+    def finish_step():
+        if world > 1:
+            dist.all_reduce(grad_view)  # sum of the LoRA gradients over ranks, NCCL over NVLink
+        model.optim_step(lr_now(), wl["clip"], weight_decay=wl["wd"])
+        step_no[0] += 1
+
+    def step_resident():
+        model.zero_grad()
+        ctx.check(L.rt_model_run_staged(model._h, 1))
+        finish_step()
+
+    def step_e2e():
+        model.zero_grad()
+        hits = C.c_int32()
+        ctx.check(L.rt_model_forward_backward(model._h, ip(h_toks), ip(h_offs), wl["n_seq"], ip(h_tpos), ip(h_ttok), fp(h_w),
+                                              n_targets, fp(h_logp), C.byref(hits)))
+        loss = -float(np.dot(h_logp, h_w))
+        if world > 1:
+            loss_buf.fill_(loss)
+            dist.all_reduce(loss_buf)
+        finish_step()
+        return loss
+
+    def timed(fn, n):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - t0) * 1e3
+        ms = max(e0.elapsed_time(e1), 0.0)
+        t = torch.tensor([ms, wall], device=f"cuda:{local_rank}")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.barrier()
+        return float(t[0]), float(t[1])
+
+    # inputs resident in HBM before the timed region
+    ctx.check(L.rt_model_stage_batch(model._h, ip(h_toks), ip(h_offs), wl["n_seq"], ip(h_tpos), ip(h_ttok), fp(h_w), n_targets))
+    for _ in range(args.warmup):
+        step_resident()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.rt_ctx_launch_count(ctx._h)
+    ms_total, _ = timed(step_resident, args.steps)
+    launches = (L.rt_ctx_launch_count(ctx._h) - launches0) // max(args.steps, 1)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = ms_total / args.steps
+
+    # end to end through the host-buffer call
+    for _ in range(min(args.warmup, 2)):
+        step_e2e()
+    ms_e2e_total, wall_e2e = timed(step_e2e, args.steps)
+    ms_e2e = max(ms_e2e_total, wall_e2e) / args.steps  # host copies are not all on the stream: take the slower clock
+
+    # roofline of the dominant kernel (the frozen matmul): per-launch CUDA events over profiled steps
+    L.rt_ctx_set_profiling(ctx._h, 1)
+    prof_steps = min(args.steps, 2)
+    for _ in range(prof_steps):
+        step_resident()
+    n_l, ms_l, fl, by = C.c_uint64(), C.c_double(), C.c_double(), C.c_double()
+    ctx.check(L.rt_ctx_profile_read(ctx._h, C.byref(n_l), C.byref(ms_l), C.byref(fl), C.byref(by)))
+    L.rt_ctx_set_profiling(ctx._h, 0)
+    peaks = measured_peaks()
+    achieved_tf = fl.value / (ms_l.value * 1e-3) / 1e12 if ms_l.value > 0 else 0.0
+    roofline = {"bound": "tensor", "achieved": achieved_tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                "frac": achieved_tf / peaks["tflops"], "traffic": None, "peak_source": peaks["source"] + " (sustained bf16 cuBLAS)",
+                "kernel": "qgemm_kernel", "launches_per_step": int(n_l.value // prof_steps),
+                "avg_launch_us": 1e3 * ms_l.value / max(n_l.value, 1), "share_of_step": (ms_l.value / prof_steps) / ms_step,
+                "flops_per_step": fl.value / prof_steps}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        r, _ = cpu_reference_run(args.workload, 1, 0, sample_tokens=128)
+        cpu = {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]}
+
+    h2d = h_toks.nbytes + h_offs.nbytes + h_tpos.nbytes + h_ttok.nbytes + h_w.nbytes + 2 * toks.size * 4  # + positions, seq starts
+    d2h = h_logp.nbytes + 4 + 4
+    line = {
+        "metric": "trained_tokens_per_s", "value": tokens_per_step / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, "model": wl["preset"], "quant": wl["quant"], "global_batch": wl["n_seq"] * world,
+                   "seq_len": wl["seq_len"], "answer_targets_per_seq": wl["seq_len"] - answer_start, "lora_rank": wl["rank"],
+                   "lora_params": n_params, "parallelism": f"dp{world}", "recompute": True,
+                   "l2": "activations and logits per step (>1 GB) exceed the 126 MB L2; no explicit flush",
+                   "lora_init": spec.describe()["lora_init"], "seeds": {"weights": 0, "lora": 1234, "tokens": 100}},
+        "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": {"value": tokens_per_step / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h), "ms_per_step": ms_e2e},
+        "gpu_launches": int(launches) * args.steps, "gpu_launches_per_step": int(launches), "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

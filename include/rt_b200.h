@@ -69,6 +69,15 @@ void* rt_ctx_stream(rt_ctx* ctx);
 /* Issue all later calls on `cuda_stream` (a cudaStream_t of the same device) instead of the
  * stream the ctx created, so a host that owns its streams can order and time the work. */
 rt_status rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream);
+/* Measurement aids.  launch_count: kernels this library has launched on the ctx so far.
+ * With profiling on, every frozen-matmul launch is bracketed by CUDA events on the ctx stream;
+ * profile_read waits for them and returns, for the launches since the last read, their number,
+ * their summed device time and their summed algorithmic work 2*tokens*out*in (flops) and
+ * packed-weight + activation + result bytes. */
+uint64_t rt_ctx_launch_count(const rt_ctx* ctx);
+rt_status rt_ctx_set_profiling(rt_ctx* ctx, int enabled);
+rt_status rt_ctx_profile_read(rt_ctx* ctx, uint64_t* n_launches, double* total_ms, double* total_flops,
+                              double* total_bytes);
 /* Bytes of ggml block storage for a [rows x cols] tensor of `ggml_type`; 0 if unsupported. */
 size_t rt_ggml_nbytes(int ggml_type, size_t rows, size_t cols);
 
@@ -195,6 +204,15 @@ rt_status rt_model_forward_backward(rt_model* m, const int32_t* tokens, const in
 rt_status rt_model_score(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
                          const int32_t* target_pos, const int32_t* target_tok, int32_t n_targets, float* logp_out,
                          int32_t* hits_out, float* logits_out);
+/* The same step split for hosts that keep the batch on the device: stage copies tokens,
+ * targets and weights to HBM once; run_staged does the forward + backward (backward != 0) or
+ * the forward alone on the staged batch without touching host memory; read_results copies the
+ * per-target log-probabilities and the hit count back. */
+rt_status rt_model_stage_batch(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
+                               const int32_t* target_pos, const int32_t* target_tok, const float* weights,
+                               int32_t n_targets);
+rt_status rt_model_run_staged(rt_model* m, int backward);
+rt_status rt_model_read_results(rt_model* m, float* logp_out, int32_t n_targets, int32_t* hits_out);
 /* The flat f32 gradient buffer on the device, [A_0 | B_0 | A_1 | B_1 ...] in parameter order:
  * what a data-parallel host all-reduces (sum) across ranks before rt_optim_step. */
 rt_status rt_model_grad_buffer(rt_model* m, void** grads_dev_out, size_t* n_floats_out);

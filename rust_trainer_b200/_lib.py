@@ -97,6 +97,12 @@ def _declare(L: C.CDLL) -> None:
         "rt_model_zero_grad": (i32, [vp]),
         "rt_model_forward_backward": (i32, [vp, i32p, i32p, i32, i32p, i32p, f32p, i32, f32p, i32p]),
         "rt_model_score": (i32, [vp, i32p, i32p, i32, i32p, i32p, i32, f32p, i32p, f32p]),
+        "rt_model_stage_batch": (i32, [vp, i32p, i32p, i32, i32p, i32p, f32p, i32]),
+        "rt_model_run_staged": (i32, [vp, C.c_int]),
+        "rt_model_read_results": (i32, [vp, f32p, i32, i32p]),
+        "rt_ctx_launch_count": (u64, [vp]),
+        "rt_ctx_set_profiling": (i32, [vp, C.c_int]),
+        "rt_ctx_profile_read": (i32, [vp, C.POINTER(u64), C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
         "rt_model_grad_buffer": (i32, [vp, C.POINTER(vp), C.POINTER(sz)]),
         "rt_optim_step": (i32, [vp] + [C.c_float] * 6 + [f32p]),
         "rt_optim_state_read": (i32, [vp, C.POINTER(u64), f32p, f32p]),

@@ -4,6 +4,8 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <map>
+#include <string>
 
 void* rt_ctx::get_scratch(int slot, size_t bytes) {
   if (bytes <= scratch_bytes[slot]) return scratch[slot];
@@ -71,6 +73,7 @@ void rt_ctx_destroy(rt_ctx* c) {
   if (!c) return;
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
+  for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
   for (int i = 0; i < 4; ++i)
     if (c->scratch[i]) cudaFree(c->scratch[i]);
   if (c->status_dev) cudaFree(c->status_dev);
@@ -89,6 +92,49 @@ rt_status rt_ctx_synchronize(rt_ctx* c) {
 rt_status rt_ctx_set_stream(rt_ctx* c, void* s) {
   if (!c) return RT_ERR_BAD_ARG;
   c->stream = (cudaStream_t)s;  // NULL is the legacy default stream, a valid choice
+  return RT_OK;
+}
+
+uint64_t rt_ctx_launch_count(const rt_ctx*) { return (uint64_t)rt::g_launch_count.load(); }
+
+rt_status rt_ctx_set_profiling(rt_ctx* c, int on) {
+  if (!c) return RT_ERR_BAD_ARG;
+  c->profiling = on != 0;
+  return RT_OK;
+}
+
+rt_status rt_ctx_profile_read(rt_ctx* c, uint64_t* n, double* ms, double* flops, double* bytes) {
+  if (!c) return RT_ERR_BAD_ARG;
+  RT_CUDA(c, cudaSetDevice(c->device));
+  RT_CUDA(c, cudaStreamSynchronize(c->stream));
+  double total = 0;
+  const bool verbose = getenv("RT_B200_PROFILE_VERBOSE") != nullptr;
+  std::map<std::string, std::pair<int, double>> table;
+  for (size_t i = 0; i + 1 < c->prof_used; i += 2) {
+    float t = 0;
+    RT_CUDA(c, cudaEventElapsedTime(&t, c->prof_events[i], c->prof_events[i + 1]));
+    total += t;
+    if (verbose && i / 2 < c->prof_recs.size()) {
+      const auto& r = c->prof_recs[i / 2];
+      char key[96];
+      snprintf(key, sizeof key, "cls%d M=%d rows=%d contract=%d", r.cls, r.M, r.rows, r.contract);
+      auto& e = table[key];
+      e.first += 1;
+      e.second += t;
+    }
+  }
+  if (verbose)
+    for (auto& kv : table)
+      fprintf(stderr, "[rt_b200 profile] %-48s n=%5d total=%9.3f ms avg=%8.1f us\n", kv.first.c_str(), kv.second.first,
+              kv.second.second, 1e3 * kv.second.second / kv.second.first);
+  c->prof_recs.clear();
+  if (n) *n = c->prof_used / 2;
+  if (ms) *ms = total;
+  if (flops) *flops = c->prof_flops;
+  if (bytes) *bytes = c->prof_bytes;
+  c->prof_used = 0;
+  c->prof_flops = 0;
+  c->prof_bytes = 0;
   return RT_OK;
 }
 
@@ -186,7 +232,7 @@ static rt_status frozen_matmul_host(rt_frozen* f, int dir, const float* in_host,
   a.out = out_f32;
   a.out_dtype = rt::OUT_F32;
   a.accumulate = accumulate ? 1 : 0;
-  int rc = rt::qgemm_launch(f->w, a, c->status_dev, c->num_sms, c->stream);
+  int rc = rt::qgemm_launch(c, f->w, a);
   if (rc) return c->fail(rc, "qgemm launch failed");
   RT_CUDA(c, cudaMemcpyAsync(out_host, out_f32, t * out_dim * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
   return c->check_device_status("rt_frozen matmul");
@@ -218,7 +264,7 @@ static rt_status frozen_matmul_dev(rt_frozen* f, int dir, const void* in_dev, in
   a.out = out_dev;
   a.out_dtype = out_dtype;
   a.accumulate = accumulate ? 1 : 0;
-  int rc = rt::qgemm_launch(f->w, a, c->status_dev, c->num_sms, c->stream);
+  int rc = rt::qgemm_launch(c, f->w, a);
   if (rc) return c->fail(rc, "qgemm launch failed");
   return RT_OK;
 }

@@ -15,6 +15,7 @@
 // that every output element is written by exactly one thread: no float atomics, same result
 // every run.
 #include "ops.h"
+#include "rt_internal.h"
 #include <cuda_fp16.h>
 #include <stdint.h>
 
@@ -453,7 +454,7 @@ int fwd_impl(const __half* q, const __half* k, const __half* v, const int* seq_s
     attr = true;
   }
   dim3 grid((M + BT - 1) / BT, nh);
-  attn_fwd_kernel<HD><<<grid, 128, smem, st>>>(q, k, v, seq_start, M, nh, nkv, 1.0f / sqrtf((float)HD), o, lse);
+  { attn_fwd_kernel<HD><<<grid, 128, smem, st>>>(q, k, v, seq_start, M, nh, nkv, 1.0f / sqrtf((float)HD), o, lse); RT_COUNT_LAUNCH(1); }
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
@@ -470,10 +471,10 @@ int bwd_impl(const __half* q, const __half* k, const __half* v, const __half* o,
   }
   const float scale = 1.0f / sqrtf((float)HD);
   const int warps = M * nh;
-  attn_delta_kernel<HD><<<(warps * 32 + 255) / 256, 256, 0, st>>>(o, dO, M, nh, delta);
+  { attn_delta_kernel<HD><<<(warps * 32 + 255) / 256, 256, 0, st>>>(o, dO, M, nh, delta); RT_COUNT_LAUNCH(1); }
   dim3 gkv((M + BT - 1) / BT, nkv), gq((M + BT - 1) / BT, nh);
-  attn_bwd_dkdv_kernel<HD><<<gkv, 128, smem_kv, st>>>(q, k, v, dO, do_scale, lse, delta, seq_start, M, nh, nkv, scale, dk, dv);
-  attn_bwd_dq_kernel<HD><<<gq, 128, smem_q, st>>>(q, k, v, dO, do_scale, lse, delta, seq_start, M, nh, nkv, scale, dq);
+  { attn_bwd_dkdv_kernel<HD><<<gkv, 128, smem_kv, st>>>(q, k, v, dO, do_scale, lse, delta, seq_start, M, nh, nkv, scale, dk, dv); RT_COUNT_LAUNCH(1); }
+  { attn_bwd_dq_kernel<HD><<<gq, 128, smem_q, st>>>(q, k, v, dO, do_scale, lse, delta, seq_start, M, nh, nkv, scale, dq); RT_COUNT_LAUNCH(1); }
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 

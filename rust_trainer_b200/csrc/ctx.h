@@ -2,7 +2,9 @@
 #pragma once
 #include "qformat.cuh"
 #include "rt_internal.h"
+#include <map>
 #include <string>
+#include <tuple>
 #include <vector>
 
 struct rt_ctx {
@@ -13,6 +15,15 @@ struct rt_ctx {
   int* status_dev = nullptr;   // device word the kernels report bounded-wait failures into
   int* status_host = nullptr;  // pinned mirror
   std::string err;
+  uint64_t launches = 0;       // kernels launched through this ctx
+  bool profiling = false;
+  std::vector<cudaEvent_t> prof_events;  // start/stop pairs of profiled matmul launches
+  size_t prof_used = 0;
+  double prof_flops = 0, prof_bytes = 0;
+  // encoded TMA descriptors, keyed by (base, rows, cols, box, type): the same buffers recur every layer
+  std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t, bool>, CUtensorMap> tmap_cache;
+  struct ProfRec { int cls, M, rows, contract; };  // cls: 0 fwd, 1 bwd, 2 skinny LoRA helper, 3 token contraction
+  std::vector<ProfRec> prof_recs;
   // grow-only scratch buffers for the host-pointer entry points
   void* scratch[4] = {nullptr, nullptr, nullptr, nullptr};
   size_t scratch_bytes[4] = {0, 0, 0, 0};

@@ -84,13 +84,14 @@ rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16,
     ha.out = hs;
     ha.out_dtype = OUT_F16;
     ha.ld_out = 64;
-    int rc = qgemm_launch(dense_view(l->lora.a_s, r, l->in_dim()), ha, c->status_dev, c->num_sms, c->stream);
+    ha.aux = 1;
+    int rc = qgemm_launch(c, dense_view(l->lora.a_s, r, l->in_dim()), ha);
     if (rc) return c->fail(rc, "lora H matmul launch failed");
     a.lora.act = hs;
     a.lora.w = l->lora.bp;
     a.lora.rank = r;
   }
-  int rc = qgemm_launch(l->w->w, a, c->status_dev, c->num_sms, c->stream);
+  int rc = qgemm_launch(c, l->w->w, a);
   if (rc) return c->fail(rc, "frozen forward matmul launch failed");
   return RT_OK;
 }
@@ -114,8 +115,7 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
     const int r = l->lora.rank;
     __half* hs = lowrank_buf(c, sc.hs, sc.hs_rank, M, r);
     __half* gs = lowrank_buf(c, sc.gs, sc.gs_rank, M, r);
-    size_t wsf = lora_grad_workspace_floats(M, K > N ? K : N, r);
-    if (!hs || !gs || !sc.grad_ws.reserve(wsf * sizeof(float)))
+    if (!hs || !gs)
       return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
     QGemmArgs ha;  // Hs = X . (sA)^T   (recomputed, as src/linear.rs:105 does)
     ha.dir = QG_FWD;
@@ -125,7 +125,8 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
     ha.out = hs;
     ha.out_dtype = OUT_F16;
     ha.ld_out = 64;
-    int rc = qgemm_launch(dense_view(l->lora.a_s, r, K), ha, c->status_dev, c->num_sms, c->stream);
+    ha.aux = 1;
+    int rc = qgemm_launch(c, dense_view(l->lora.a_s, r, K), ha);
     if (rc) return c->fail(rc, "lora H matmul launch failed");
     QGemmArgs ga;  // Gs = dY~ . (sB)   (unit rows: the row scale is applied where Gs is consumed)
     ga.dir = QG_FWD;
@@ -135,16 +136,50 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
     ga.out = gs;
     ga.out_dtype = OUT_F16;
     ga.ld_out = 64;
-    rc = qgemm_launch(dense_view(l->lora.bt_s, r, N), ga, c->status_dev, c->num_sms, c->stream);
+    ga.aux = 1;
+    rc = qgemm_launch(c, dense_view(l->lora.bt_s, r, N), ga);
     if (rc) return c->fail(rc, "lora G matmul launch failed");
-    // gb[N x r] += dY^T . Hs ; ga[r x K] += Gs^T . X
-    launch_lora_grad(hs, dy16, nullptr, dscale, M, N, r, 1, (size_t)r, l->lora.gb, sc.grad_ws.as<float>(), c->stream);
-    launch_lora_grad(gs, x16, dscale, nullptr, M, K, r, (size_t)K, 1, l->lora.ga, sc.grad_ws.as<float>(), c->stream);
+    // gb[N x r] += dY^T . Hs ; ga[r x K] += Gs^T . X   on the tensor cores, contraction over tokens.
+    // The per-token scales of dY move onto the skinny operand (rows * scale / max), the max onto the result.
+    const __half *hs_c = hs, *gs_c = gs;
+    const float* alpha = nullptr;
+    if (dscale) {
+      __half* hs2 = lowrank_buf(c, sc.hs2, sc.hs2_rank, M, r);
+      __half* gs2 = lowrank_buf(c, sc.gs2, sc.gs2_rank, M, r);
+      if (!hs2 || !gs2 || !sc.smax.reserve(16)) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+      launch_rowscale_max(dscale, M, sc.smax.as<float>(), c->stream);
+      launch_scale_lowrank_rows(hs, dscale, sc.smax.as<float>(), M, hs2, c->stream);
+      launch_scale_lowrank_rows(gs, dscale, sc.smax.as<float>(), M, gs2, c->stream);
+      hs_c = hs2;
+      gs_c = gs2;
+      alpha = sc.smax.as<float>();
+    }
+    QGemmArgs ta;
+    ta.dir = QG_BWD;
+    ta.tok_mode = 1;
+    ta.act_f16 = 1;
+    ta.M = r;
+    ta.out_dtype = OUT_F32;
+    ta.accumulate = 1;
+    ta.alpha_dev = alpha;
+    ta.aux = 1;
+    ta.act = hs_c;  // dB[n, i] += sum_m dY[m, n] Hs[m, i]
+    ta.out = l->lora.gb;
+    ta.out_s_tok = 1;
+    ta.out_s_row = (size_t)r;
+    rc = qgemm_launch(c, dense_view(dy16, M, N), ta);
+    if (rc) return c->fail(rc, "lora dB matmul launch failed");
+    ta.act = gs_c;  // dA[i, k] += sum_m Gs[m, i] X[m, k]
+    ta.out = l->lora.ga;
+    ta.out_s_tok = (size_t)K;
+    ta.out_s_row = 1;
+    rc = qgemm_launch(c, dense_view(x16, M, K), ta);
+    if (rc) return c->fail(rc, "lora dA matmul launch failed");
     a.lora.act = gs;
     a.lora.w = l->lora.a_h;
     a.lora.rank = r;
   }
-  int rc = qgemm_launch(l->w->w, a, c->status_dev, c->num_sms, c->stream);
+  int rc = qgemm_launch(c, l->w->w, a);
   if (rc) return c->fail(rc, "frozen backward matmul launch failed");
   return RT_OK;
 }
@@ -388,7 +423,7 @@ void rt_model_destroy(rt_model* m) {
   if (m->embed) rt_frozen_destroy(m->embed);
   for (void* p : m->owned) cudaFree(p);
   DevBuf* bufs[] = {&m->P, &m->G, &m->Mo, &m->Vo, &m->opt_scalars, &m->inv_freq, &m->rope_cos, &m->rope_sin,
-                    &m->lsc.hs, &m->lsc.gs, &m->lsc.grad_ws, &m->tokens, &m->pos, &m->seq_start, &m->x, &m->ckpt, &m->h,
+                    &m->lsc.hs, &m->lsc.gs, &m->lsc.hs2, &m->lsc.gs2, &m->lsc.smax, &m->tokens, &m->pos, &m->seq_start, &m->x, &m->ckpt, &m->h,
                     &m->n1, &m->n2, &m->q_raw, &m->k_raw, &m->v_raw, &m->q16, &m->k16, &m->v16, &m->o16, &m->lse,
                     &m->delta, &m->g16, &m->u16, &m->hm16, &m->dx, &m->dy16, &m->sc_y, &m->dhm, &m->dg16, &m->du16,
                     &m->sc_g, &m->sc_u, &m->dn, &m->d_o, &m->dO16, &m->amax, &m->dq, &m->dk, &m->dv, &m->dq16, &m->dk16,
@@ -811,6 +846,65 @@ static rt_status upload_batch(rt_model* m, const int32_t* tokens, const int32_t*
   return RT_OK;
 }
 
+static rt_status run_staged(rt_model* m, bool backward, float* logits_out_host) {
+  rt_ctx* c = m->ctx;
+  const int M = m->staged_tokens, n_targets = m->staged_targets;
+  if (M <= 0) return c->fail(RT_ERR_BAD_ARG, "no batch staged");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  cudaStream_t st = c->stream;
+  const rt_model_config& g = m->cfg;
+  const size_t xd = (size_t)M * g.hidden;
+  float* x = m->x.as<float>();
+  launch_gather_rows(m->embed->w, m->tokens.as<int>(), M, x, c->status_dev, st);
+  for (int li = 0; li < g.n_layers; ++li) {
+    if (backward) RT_CUDA(c, cudaMemcpyAsync(m->ckpt.as<float>() + (size_t)li * xd, x, xd * 4, cudaMemcpyDeviceToDevice, st));
+    RT_TRY(block_forward(m, li, M, x, x, x));
+  }
+  if (backward) RT_CUDA(c, cudaMemsetAsync(m->dx.p, 0, xd * 4, st));
+  if (n_targets > 0) RT_TRY(model_head(m, M, n_targets, backward, logits_out_host));
+  if (!backward) return RT_OK;
+  launch_normalize_rows(m->dx.as<float>(), M, g.hidden, m->dy16.as<__half>(), m->sc_y.as<float>(), st);
+  for (int li = g.n_layers - 1; li >= 0; --li) {
+    const float* x_in = m->ckpt.as<float>() + (size_t)li * xd;
+    RT_TRY(block_forward(m, li, M, x_in, m->h.as<float>(), nullptr));  // recompute the block's caches
+    RT_TRY(block_backward(m, li, M, x_in));
+  }
+  return RT_OK;
+}
+
+rt_status rt_model_stage_batch(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
+                               const int32_t* tpos, const int32_t* ttok, const float* weights, int32_t n_targets) {
+  if (!m) return RT_ERR_BAD_ARG;
+  int M = 0;
+  m->staged_tokens = 0;
+  RT_TRY(upload_batch(m, tokens, seq_offsets, n_seq, tpos, ttok, weights, n_targets, weights != nullptr, &M));
+  RT_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
+  m->staged_tokens = M;
+  m->staged_targets = n_targets;
+  m->staged_has_weights = weights != nullptr;
+  return RT_OK;
+}
+
+rt_status rt_model_run_staged(rt_model* m, int backward) {
+  if (!m) return RT_ERR_BAD_ARG;
+  if (backward && !m->staged_has_weights) return m->ctx->fail(RT_ERR_BAD_ARG, "the staged batch has no weights");
+  return run_staged(m, backward != 0, nullptr);
+}
+
+rt_status rt_model_read_results(rt_model* m, float* logp_out, int32_t n_targets, int32_t* hits_out) {
+  if (!m) return RT_ERR_BAD_ARG;
+  rt_ctx* c = m->ctx;
+  if (n_targets > m->staged_targets) return c->fail(RT_ERR_BAD_ARG, "more results requested than targets staged");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  cudaStream_t st = c->stream;
+  if (n_targets > 0 && logp_out) RT_CUDA(c, cudaMemcpyAsync(logp_out, m->logp.p, (size_t)n_targets * 4, cudaMemcpyDeviceToHost, st));
+  int hits = 0;
+  RT_CUDA(c, cudaMemcpyAsync(&hits, m->hits.p, 4, cudaMemcpyDeviceToHost, st));
+  rt_status s = c->check_device_status("rt_model_read_results");
+  if (hits_out) *hits_out = hits;
+  return s;
+}
+
 rt_status rt_model_forward_backward(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
                                     const int32_t* tpos, const int32_t* ttok, const float* weights, int32_t n_targets,
                                     float* logp_out, int32_t* hits_out) {
@@ -818,51 +912,27 @@ rt_status rt_model_forward_backward(rt_model* m, const int32_t* tokens, const in
   rt_ctx* c = m->ctx;
   if (n_targets > 0 && !weights) return c->fail(RT_ERR_BAD_ARG, "weights missing");  // model.rs:652 asserts equal lengths
   int M = 0;
+  m->staged_tokens = 0;
   RT_TRY(upload_batch(m, tokens, seq_offsets, n_seq, tpos, ttok, weights, n_targets, true, &M));
-  cudaStream_t st = c->stream;
-  const rt_model_config& g = m->cfg;
-  const size_t xd = (size_t)M * g.hidden;
-  float* x = m->x.as<float>();
-  launch_gather_rows(m->embed->w, m->tokens.as<int>(), M, x, c->status_dev, st);
-  for (int li = 0; li < g.n_layers; ++li) {
-    RT_CUDA(c, cudaMemcpyAsync(m->ckpt.as<float>() + (size_t)li * xd, x, xd * 4, cudaMemcpyDeviceToDevice, st));
-    RT_TRY(block_forward(m, li, M, x, x, x));
-  }
-  RT_CUDA(c, cudaMemsetAsync(m->dx.p, 0, xd * 4, st));
-  if (n_targets > 0) RT_TRY(model_head(m, M, n_targets, true, nullptr));
-  launch_normalize_rows(m->dx.as<float>(), M, g.hidden, m->dy16.as<__half>(), m->sc_y.as<float>(), st);
-  for (int li = g.n_layers - 1; li >= 0; --li) {
-    const float* x_in = m->ckpt.as<float>() + (size_t)li * xd;
-    RT_TRY(block_forward(m, li, M, x_in, m->h.as<float>(), nullptr));  // recompute the block's caches
-    RT_TRY(block_backward(m, li, M, x_in));
-  }
-  if (n_targets > 0 && logp_out) RT_CUDA(c, cudaMemcpyAsync(logp_out, m->logp.p, (size_t)n_targets * 4, cudaMemcpyDeviceToHost, st));
-  int hits = 0;
-  RT_CUDA(c, cudaMemcpyAsync(&hits, m->hits.p, 4, cudaMemcpyDeviceToHost, st));
-  rt_status s = c->check_device_status("rt_model_forward_backward");
-  if (hits_out) *hits_out = hits;
-  return s;
+  m->staged_tokens = M;
+  m->staged_targets = n_targets;
+  m->staged_has_weights = true;
+  RT_TRY(run_staged(m, true, nullptr));
+  return rt_model_read_results(m, logp_out, n_targets, hits_out);
 }
 
 rt_status rt_model_score(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
                          const int32_t* tpos, const int32_t* ttok, int32_t n_targets, float* logp_out,
                          int32_t* hits_out, float* logits_out) {
   if (!m) return RT_ERR_BAD_ARG;
-  rt_ctx* c = m->ctx;
   int M = 0;
+  m->staged_tokens = 0;
   RT_TRY(upload_batch(m, tokens, seq_offsets, n_seq, tpos, ttok, nullptr, n_targets, false, &M));
-  cudaStream_t st = c->stream;
-  const rt_model_config& g = m->cfg;
-  float* x = m->x.as<float>();
-  launch_gather_rows(m->embed->w, m->tokens.as<int>(), M, x, c->status_dev, st);
-  for (int li = 0; li < g.n_layers; ++li) RT_TRY(block_forward(m, li, M, x, x, x));
-  if (n_targets > 0) RT_TRY(model_head(m, M, n_targets, false, logits_out));
-  if (n_targets > 0 && logp_out) RT_CUDA(c, cudaMemcpyAsync(logp_out, m->logp.p, (size_t)n_targets * 4, cudaMemcpyDeviceToHost, st));
-  int hits = 0;
-  RT_CUDA(c, cudaMemcpyAsync(&hits, m->hits.p, 4, cudaMemcpyDeviceToHost, st));
-  rt_status s = c->check_device_status("rt_model_score");
-  if (hits_out) *hits_out = hits;
-  return s;
+  m->staged_tokens = M;
+  m->staged_targets = n_targets;
+  m->staged_has_weights = false;
+  RT_TRY(run_staged(m, false, logits_out));
+  return rt_model_read_results(m, logp_out, n_targets, hits_out);
 }
 
 rt_status rt_optim_step(rt_model* m, float lr, float max_norm, float beta1, float beta2, float eps, float wd,

@@ -43,8 +43,8 @@ struct rt_linear {
 
 // Scratch shared by every Linear call on a ctx (one call at a time per ctx).
 struct LinearScratch {
-  DevBuf hs, gs, grad_ws;
-  int hs_rank = -1, gs_rank = -1;
+  DevBuf hs, gs, hs2, gs2, smax;
+  int hs_rank = -1, gs_rank = -1, hs2_rank = -1, gs2_rank = -1;
 };
 
 namespace rt {
@@ -89,4 +89,6 @@ struct rt_model {
   DevBuf dx, dy16, sc_y, dhm, dg16, du16, sc_g, sc_u, dn, d_o, dO16, amax, dq, dk, dv, dq16, dk16, dv16, sc_q, sc_k, sc_v;
   DevBuf tpos, ttok, tw, logp, hits, xs, ns16, logits, dl16, sc_l, dns, dxs;
   std::vector<int> h_pos, h_seq_start;
+  int staged_tokens = 0, staged_targets = 0;
+  bool staged_has_weights = false;
 };

@@ -98,8 +98,8 @@ void launch_f32_to_16(const float* in, void* out, size_t n, bool to_f16, cudaStr
   if (n == 0) return;
   size_t threads = (n + 3) / 4;
   unsigned blocks = (unsigned)((threads + 255) / 256);
-  if (to_f16) f32_to_16_kernel<true><<<blocks, 256, 0, st>>>(in, (uint16_t*)out, n);
-  else f32_to_16_kernel<false><<<blocks, 256, 0, st>>>(in, (uint16_t*)out, n);
+  if (to_f16) { f32_to_16_kernel<true><<<blocks, 256, 0, st>>>(in, (uint16_t*)out, n); RT_COUNT_LAUNCH(1); }
+  else { f32_to_16_kernel<false><<<blocks, 256, 0, st>>>(in, (uint16_t*)out, n); RT_COUNT_LAUNCH(1); }
 }
 
 // Row-normalised f16 copy: y16[r,:] = x[r,:] / amax_r, scale[r] = amax_r (1 if the row is zero).
@@ -115,7 +115,7 @@ __global__ void normalize_rows_kernel(const float* __restrict__ x, int d, __half
   if (threadIdx.x == 0) scale[r] = s;
 }
 void launch_normalize_rows(const float* x, int rows, int d, __half* y16, float* scale, cudaStream_t st) {
-  if (rows > 0) normalize_rows_kernel<<<rows, 256, 0, st>>>(x, d, y16, scale);
+  if (rows > 0) { normalize_rows_kernel<<<rows, 256, 0, st>>>(x, d, y16, scale); RT_COUNT_LAUNCH(1); }
 }
 
 // ------------------------------------------------------------------ RMSNorm (reference src/ops.rs:8-56)
@@ -131,7 +131,7 @@ __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __r
   for (int i = threadIdx.x; i < d; i += blockDim.x) y16[r * d + i] = __float2half_rn(xr[i] * ir * w[i]);
 }
 void launch_rmsnorm_fwd(const float* x, const float* w, int rows, int d, float eps, __half* y16, cudaStream_t st) {
-  if (rows > 0) rmsnorm_fwd_kernel<<<rows, 256, 0, st>>>(x, w, d, eps, y16);
+  if (rows > 0) { rmsnorm_fwd_kernel<<<rows, 256, 0, st>>>(x, w, d, eps, y16); RT_COUNT_LAUNCH(1); }
 }
 
 // dx = g*ir - x*c, g = dn*w, c = dot(g,x)*ir^3/d;  out = (dres ? dres : 0) + dx.
@@ -168,7 +168,7 @@ __global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __r
 }
 void launch_rmsnorm_bwd(const float* x, const float* w, const float* dn, const float* dres, int rows, int d, float eps,
                         float* out, __half* out16, float* scale, cudaStream_t st) {
-  if (rows > 0) rmsnorm_bwd_kernel<<<rows, 256, 0, st>>>(x, w, dn, dres, d, eps, out, out16, scale);
+  if (rows > 0) { rmsnorm_bwd_kernel<<<rows, 256, 0, st>>>(x, w, dn, dres, d, eps, out, out16, scale); RT_COUNT_LAUNCH(1); }
 }
 
 // ------------------------------------------------------------------ RoPE tables (reference src/ops.rs:118-154)
@@ -183,7 +183,7 @@ __global__ void rope_table_kernel(const float* __restrict__ inv_freq, int half, 
 }
 void launch_rope_table(const float* inv_freq, int half, int max_pos, float* cs, float* sn, cudaStream_t st) {
   int n = max_pos * half;
-  if (n > 0) rope_table_kernel<<<(n + 255) / 256, 256, 0, st>>>(inv_freq, half, max_pos, cs, sn);
+  if (n > 0) { rope_table_kernel<<<(n + 255) / 256, 256, 0, st>>>(inv_freq, half, max_pos, cs, sn); RT_COUNT_LAUNCH(1); }
 }
 
 // ------------------------------------------------------------------ QK-norm + RoPE + f16 rounding
@@ -237,7 +237,7 @@ __global__ void qk_rope_fwd_kernel(const float* __restrict__ q_raw, const float*
 void launch_qk_rope_fwd(const float* q_raw, const float* k_raw, const float* v_raw, const float* qw, const float* kw,
                         const int* pos, const float* cs, const float* sn, int M, int nh, int nkv, int hd, int rot,
                         int neox, float eps, __half* q16, __half* k16, __half* v16, cudaStream_t st) {
-  if (M > 0) qk_rope_fwd_kernel<<<M, 256, 0, st>>>(q_raw, k_raw, v_raw, qw, kw, pos, cs, sn, nh, nkv, hd, rot, neox, eps, q16, k16, v16);
+  if (M > 0) { qk_rope_fwd_kernel<<<M, 256, 0, st>>>(q_raw, k_raw, v_raw, qw, kw, pos, cs, sn, nh, nkv, hd, rot, neox, eps, q16, k16, v16); RT_COUNT_LAUNCH(1); }
 }
 
 // Backward of the above (reference src/attention.rs:331-341): inverse rotation, then the
@@ -317,8 +317,8 @@ void launch_qk_rope_bwd(const float* dq, const float* dk, const float* dv, const
                         float* sq, float* sk, float* sv, cudaStream_t st) {
   if (M <= 0) return;
   size_t smem = (size_t)(nh + 2 * nkv) * hd * sizeof(float);
-  qk_rope_bwd_kernel<<<M, 256, smem, st>>>(dq, dk, dv, q_raw, k_raw, qw, kw, pos, cs, sn, nh, nkv, hd, rot, neox, eps,
-                                             dq16, dk16, dv16, sq, sk, sv);
+  { qk_rope_bwd_kernel<<<M, 256, smem, st>>>(dq, dk, dv, q_raw, k_raw, qw, kw, pos, cs, sn, nh, nkv, hd, rot, neox, eps,
+                                             dq16, dk16, dv16, sq, sk, sv); RT_COUNT_LAUNCH(1); }
 }
 
 // ------------------------------------------------------------------ SwiGLU (reference src/model.rs:113-134, src/tensor.rs:122-143)
@@ -341,7 +341,7 @@ __global__ void swiglu_fwd_kernel(const __half* __restrict__ g, const __half* __
 void launch_swiglu_fwd(const __half* g, const __half* u, __half* h, size_t n, cudaStream_t st) {
   if (n == 0) return;
   size_t threads = (n + 1) / 2;
-  swiglu_fwd_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(g, u, h, n);
+  { swiglu_fwd_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(g, u, h, n); RT_COUNT_LAUNCH(1); }
 }
 // dg = dh*u*silu'(g), du = dh*silu(g); both written row-normalised in f16 with per-row scales.
 __global__ void swiglu_bwd_kernel(const float* __restrict__ dh, const __half* __restrict__ g,
@@ -372,7 +372,7 @@ __global__ void swiglu_bwd_kernel(const float* __restrict__ dh, const __half* __
 }
 void launch_swiglu_bwd(const float* dh, const __half* g, const __half* u, int rows, int ff, __half* dg16, __half* du16,
                        float* sg, float* su, cudaStream_t st) {
-  if (rows > 0) swiglu_bwd_kernel<<<rows, 256, 0, st>>>(dh, g, u, ff, dg16, du16, sg, su);
+  if (rows > 0) { swiglu_bwd_kernel<<<rows, 256, 0, st>>>(dh, g, u, ff, dg16, du16, sg, su); RT_COUNT_LAUNCH(1); }
 }
 
 // ------------------------------------------------------------------ row gather / scatter
@@ -383,7 +383,7 @@ __global__ void gather_f32_rows_kernel(const float* __restrict__ x, const int* _
   for (int i = threadIdx.x; i < d; i += blockDim.x) out[r * d + i] = src[i];
 }
 void launch_gather_f32_rows(const float* x, const int* idx, int rows, int d, float* out, cudaStream_t st) {
-  if (rows > 0) gather_f32_rows_kernel<<<rows, 256, 0, st>>>(x, idx, d, out);
+  if (rows > 0) { gather_f32_rows_kernel<<<rows, 256, 0, st>>>(x, idx, d, out); RT_COUNT_LAUNCH(1); }
 }
 // dx[idx[r], :] += src[r, :]   (atomic: two targets may name the same position)
 __global__ void scatter_add_rows_kernel(const float* __restrict__ src, const int* __restrict__ idx, int d,
@@ -393,7 +393,7 @@ __global__ void scatter_add_rows_kernel(const float* __restrict__ src, const int
   for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(dst + i, src[r * d + i]);
 }
 void launch_scatter_add_rows(const float* src, const int* idx, int rows, int d, float* dx, cudaStream_t st) {
-  if (rows > 0) scatter_add_rows_kernel<<<rows, 256, 0, st>>>(src, idx, d, dx);
+  if (rows > 0) { scatter_add_rows_kernel<<<rows, 256, 0, st>>>(src, idx, d, dx); RT_COUNT_LAUNCH(1); }
 }
 
 // ------------------------------------------------------------------ cross-entropy over one row of logits
@@ -433,7 +433,7 @@ __global__ void ce_row_kernel(const float* __restrict__ logits, int v, const int
 }
 void launch_ce_rows(const float* logits, int rows, int v, const int* target, const float* weight, float* logp, int* hits,
                     __half* d16, float* scale, int* status, cudaStream_t st) {
-  if (rows > 0) ce_row_kernel<<<rows, 1024, 0, st>>>(logits, v, target, weight, logp, hits, d16, scale, status);
+  if (rows > 0) { ce_row_kernel<<<rows, 1024, 0, st>>>(logits, v, target, weight, logp, hits, d16, scale, status); RT_COUNT_LAUNCH(1); }
 }
 
 // ------------------------------------------------------------------ LoRA shadows and gradients
@@ -460,7 +460,7 @@ __global__ void lora_refresh_kernel(const float* __restrict__ a, const float* __
 void launch_lora_refresh(const float* a, const float* b, int r, int K, int N, float s, __half* a_s, __half* a_h,
                          __half* bp, __half* bt_s, cudaStream_t st) {
   size_t n = (size_t)r * K > (size_t)N * 64 ? (size_t)r * K : (size_t)N * 64;
-  lora_refresh_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a, b, r, K, N, s, a_s, a_h, bp, bt_s);
+  { lora_refresh_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a, b, r, K, N, s, a_s, a_h, bp, bt_s); RT_COUNT_LAUNCH(1); }
 }
 
 // Token-contraction for the LoRA gradients (reference src/linear.rs:108-116):
@@ -534,9 +534,35 @@ void launch_lora_grad(const __half* P, const __half* Q, const float* pscale, con
   const int tps = ((M + splits - 1) / splits + LG_TOK - 1) / LG_TOK * LG_TOK;
   splits = (M + tps - 1) / tps;
   dim3 grid((C + 63) / 64, splits);
-  lora_grad_partial_kernel<<<grid, 256, 0, st>>>(P, Q, pscale, qscale, M, C, r, tps, workspace);
+  { lora_grad_partial_kernel<<<grid, 256, 0, st>>>(P, Q, pscale, qscale, M, C, r, tps, workspace); RT_COUNT_LAUNCH(1); }
   const size_t n = (size_t)r * C;
-  lora_grad_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(workspace, splits, C, r, so_i, so_j, out);
+  { lora_grad_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(workspace, splits, C, r, so_i, so_j, out); RT_COUNT_LAUNCH(1); }
+}
+
+// Largest per-token scale of a backward input, and a [M x 64] low-rank operand with each row
+// multiplied by scale[m] / max: the token contractions dA, dB need ONE common scale, so the
+// per-row factors move onto the skinny operand and the common factor onto the result.
+__global__ void rowscale_max_kernel(const float* __restrict__ sc, int M, float* __restrict__ out) {
+  float m = 0.f;
+  for (int i = threadIdx.x; i < M; i += blockDim.x) m = fmaxf(m, sc[i]);
+  m = block_max(m);
+  if (threadIdx.x == 0) out[0] = m > 0.f ? m : 1.f;
+}
+__global__ void scale_lowrank_rows_kernel(const __half* __restrict__ in, const float* __restrict__ sc,
+                                          const float* __restrict__ smax, int M, __half* __restrict__ out) {
+  const size_t e = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (e >= (size_t)M * 64) return;
+  const float f = sc[e >> 6] / smax[0];
+  float2 v = __half22float2(*(const __half2*)(in + e));
+  *(__half2*)(out + e) = __floats2half2_rn(v.x * f, v.y * f);
+}
+void launch_rowscale_max(const float* sc, int M, float* out, cudaStream_t st) {
+  if (M > 0) { rowscale_max_kernel<<<1, 1024, 0, st>>>(sc, M, out); RT_COUNT_LAUNCH(1); }
+}
+void launch_scale_lowrank_rows(const __half* in, const float* sc, const float* smax, int M, __half* out, cudaStream_t st) {
+  if (M <= 0) return;
+  const size_t threads = (size_t)M * 32;
+  { scale_lowrank_rows_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(in, sc, smax, M, out); RT_COUNT_LAUNCH(1); }
 }
 
 // ------------------------------------------------------------------ optimiser (reference src/optim.rs:48-90)
@@ -560,8 +586,8 @@ void launch_sumsq(const float* g, size_t n, double* part /* >= 1024 */, double* 
   int blocks = (int)((n + 255) / 256);
   if (blocks > 1024) blocks = 1024;
   if (blocks < 1) blocks = 1;
-  sumsq_partial_kernel<<<blocks, 256, 0, st>>>(g, n, part);
-  sumsq_final_kernel<<<1, 256, 0, st>>>(part, blocks, out);
+  { sumsq_partial_kernel<<<blocks, 256, 0, st>>>(g, n, part); RT_COUNT_LAUNCH(1); }
+  { sumsq_final_kernel<<<1, 256, 0, st>>>(part, blocks, out); RT_COUNT_LAUNCH(1); }
 }
 // clip (scale read from the device-side norm) fused with the AdamW update.
 __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
@@ -586,8 +612,8 @@ void launch_adamw(float* p, float* g, float* m, float* v, size_t n, const double
                   float beta1, float beta2, float eps, float wd, float bc1, float bc2, float* norm_out,
                   cudaStream_t st) {
   if (n == 0) return;
-  adamw_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p, g, m, v, n, sumsq, max_norm, lr, beta1, beta2, eps, wd,
-                                                             bc1, bc2, norm_out);
+  { adamw_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p, g, m, v, n, sumsq, max_norm, lr, beta1, beta2, eps, wd,
+                                                             bc1, bc2, norm_out); RT_COUNT_LAUNCH(1); }
 }
 
 // ------------------------------------------------------------------ misc
@@ -614,9 +640,9 @@ void launch_global_normalize(const float* x, size_t n, float* amax_dev, __half* 
   cudaMemsetAsync(amax_dev, 0, sizeof(float), st);
   int blocks = (int)((n + 255) / 256);
   if (blocks > 1184) blocks = 1184;
-  absmax_kernel<<<blocks, 256, 0, st>>>(x, n, amax_dev);
+  { absmax_kernel<<<blocks, 256, 0, st>>>(x, n, amax_dev); RT_COUNT_LAUNCH(1); }
   size_t threads = (n + 1) / 2;
-  scale_to_f16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(x, n, amax_dev, y16);
+  { scale_to_f16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(x, n, amax_dev, y16); RT_COUNT_LAUNCH(1); }
 }
 
 }  // namespace rt

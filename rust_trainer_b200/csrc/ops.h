@@ -31,6 +31,8 @@ void launch_lora_refresh(const float* a, const float* b, int r, int K, int N, fl
 size_t lora_grad_workspace_floats(int M, int C, int r);
 void launch_lora_grad(const __half* P, const __half* Q, const float* pscale, const float* qscale, int M, int C, int r,
                       size_t so_i, size_t so_j, float* out, float* workspace, cudaStream_t st);
+void launch_rowscale_max(const float* sc, int M, float* out, cudaStream_t st);
+void launch_scale_lowrank_rows(const __half* in, const float* sc, const float* smax, int M, __half* out, cudaStream_t st);
 void launch_sumsq(const float* g, size_t n, double* part, double* out, cudaStream_t st);
 void launch_adamw(float* p, float* g, float* m, float* v, size_t n, const double* sumsq, float max_norm, float lr,
                   float beta1, float beta2, float eps, float wd, float bc1, float bc2, float* norm_out,

@@ -18,7 +18,7 @@
 // The LoRA low-rank term is one more contraction chunk fed through the same accumulator.
 #include "ptx.cuh"
 #include "qformat.cuh"
-#include "rt_internal.h"
+#include "ctx.h"
 #include <stdio.h>
 
 namespace rt {
@@ -42,6 +42,9 @@ struct KParams {
   int conv16;    // 16-bit weight whose type differs from the activations': 1 = f16->bf16, 2 = bf16->f16
   int dir, out_rows, M, TN;
   int n_main, lora_mmas;
+  int n_splits, steps_per_split;  // split-K: work item = (tile, split); partial results go to `part`
+  int b_mn;                       // token-contraction mode: the B operand is MN-major (tile rows = contraction)
+  float* part;                    // [n_splits][M][out_rows] f32 partials when n_splits > 1 or b_mn
   int n_row_tiles, n_tok_tiles;
   void* out;
   int out_dtype, accumulate, ld_out;
@@ -186,8 +189,15 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool is16 = fmt_is_16bit(p.fmt);
-  const int n_steps = p.n_main + (p.lora_mmas > 0 ? 1 : 0);
   const int n_tiles = p.n_row_tiles * p.n_tok_tiles;
+  const int n_items = n_tiles * p.n_splits;
+// work item -> tile, its range of contraction steps, and whether the LoRA chunk is appended
+#define QG_ITEM_DECODE(item)                                                                  \
+  const int tile = (item) % n_tiles, split = (item) / n_tiles;                                \
+  const int s_begin = split * p.steps_per_split;                                              \
+  const int s_main = min(p.n_main, s_begin + p.steps_per_split) - s_begin;                    \
+  const int n_steps = s_main + ((p.lora_mmas > 0 && split == p.n_splits - 1) ? 1 : 0);        \
+  (void)split
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NS; ++i) { mbar_init(&full[i], 1); mbar_init(&w_ready[i], 128); mbar_init(&stage_empty[i], 1); }
@@ -213,18 +223,21 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     if (lane == 0) {
       uint32_t it = 0, rit = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        QG_ITEM_DECODE(item);
         const int r0 = (tile % p.n_row_tiles) * 128, m0 = (tile / p.n_row_tiles) * p.TN;
-        for (int s = 0; s < n_steps && ok; ++s, ++it) {
+        for (int si = 0; si < n_steps && ok; ++si, ++it) {
+          const int s = s_begin + si;
           const int st = it % NS;
           const uint32_t ph = (it / NS) & 1;
           if (!mbar_wait(&stage_empty[st], ph ^ 1, p.status, 101)) { ok = false; break; }
-          const bool lora = s >= p.n_main;
+          const bool lora = si >= s_main;
           uint8_t* a_dst = sAct + st * ACT_STAGE;
           uint8_t* w_dst = sW + st * W_STAGE;
           mbar_expect_tx(&full[st], (uint32_t)p.TN * 128u + ((is16 || lora) ? (uint32_t)W_STAGE : 0u));
           if (!lora) {
-            tma_load_2d(a_dst, &tm_act, s * 64, m0, &full[st]);
+            if (p.b_mn) tma_load_2d(a_dst, &tm_act, 0, s * 64, &full[st]);  // [64 contraction rows x 64]
+            else tma_load_2d(a_dst, &tm_act, s * 64, m0, &full[st]);
             if (is16) {
               if (p.dir == QG_FWD) {
                 tma_load_2d(w_dst, &tm_w16, s * 64, r0, &full[st]);
@@ -270,7 +283,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     if (lane == 0) {
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++tcount) {
+        QG_ITEM_DECODE(item);
+        (void)tile; (void)s_begin;
         const int acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1;
         if (!mbar_wait(&acc_empty[acc], aph ^ 1, p.status, 301)) { ok = false; break; }
@@ -282,7 +297,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           if (!mbar_wait(&full[st], ph, p.status, 302)) { ok = false; break; }
           if (!mbar_wait(&w_ready[st], ph, p.status, 303)) { ok = false; break; }
           tc_fence_after();
-          const bool lora = s >= p.n_main;
+          const bool lora = s >= s_main;
           const int nm = lora ? p.lora_mmas : 4;
           const uint32_t idesc = lora ? p.idesc_lora : p.idesc_main;
           const uint32_t a_base = smem_u32(sW + st * W_STAGE);
@@ -290,7 +305,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           for (int kk = 0; kk < nm; ++kk) {
             const uint64_t adesc = (p.dir == QG_FWD) ? umma_desc_sw128(a_base + kk * 32, 16, 1024)
                                                      : umma_desc_sw128(a_base + kk * 2048, 8192, 1024);
-            const uint64_t bdesc = umma_desc_sw128(b_base + kk * 32, 16, 1024);
+            const uint64_t bdesc = p.b_mn ? umma_desc_sw128(b_base + kk * 2048, 8192, 1024)
+                                          : umma_desc_sw128(b_base + kk * 32, 16, 1024);
             umma_f16(d_tmem, adesc, bdesc, idesc, (uint32_t)((s | kk) != 0));
           }
           umma_commit(&stage_empty[st]);
@@ -303,12 +319,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     const int t = threadIdx.x - 64;
     uint32_t it = 0, rit = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      QG_ITEM_DECODE(item);
+      (void)tile; (void)s_begin;
       for (int s = 0; s < n_steps; ++s, ++it) {
         const int st = it % NS;
         const uint32_t ph = (it / NS) & 1;
         if (!mbar_wait(&stage_empty[st], ph ^ 1, p.status, 201)) { ok = false; break; }
-        if (is16 && p.conv16 && s < p.n_main) {
+        if (is16 && p.conv16 && s < s_main) {
           // The TMA'd 16-bit weight tile has the other 16-bit type: convert it in place
           // (element-wise, so the swizzled placement is untouched).
           if (!mbar_wait(&full[st], ph, p.status, 203)) { ok = false; break; }
@@ -330,7 +348,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
             tile[t + i * 128] = v;
           }
           fence_proxy_async_smem();
-        } else if (!is16 && s < p.n_main) {
+        } else if (!is16 && s < s_main) {
           const int rs = rit % NR;
           const uint32_t rph = (rit / NR) & 1;
           if (!mbar_wait(&raw_full[rs], rph, p.status, 202)) { ok = false; break; }
@@ -350,7 +368,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     const int wq = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t tcount = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++tcount) {
+      QG_ITEM_DECODE(item);
+      (void)s_begin; (void)n_steps; (void)s_main;
       const int r0 = (tile % p.n_row_tiles) * 128, m0 = (tile / p.n_row_tiles) * p.TN;
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
@@ -364,22 +384,33 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(wq * 32) << 16) + c * 32, v);
         tmem_ld_wait();
         if (row_ok) {
+          if (p.part != nullptr) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int tok = m0 + c * 32 + j;
-            if (tok < p.M) {
-              const size_t idx = (size_t)tok * p.ld_out + row;
-              float val = __uint_as_float(v[j]);
-              if (p.row_scale) val *= p.row_scale[tok];
-              val += bias_v;
-              if (p.out_dtype == OUT_F32) {
-                float* o = (float*)p.out;
-                if (p.accumulate) val += o[idx];
-                o[idx] = val;
-              } else if (p.out_dtype == OUT_BF16) {
-                ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(val);
-              } else {
-                ((__half*)p.out)[idx] = __float2half_rn(val);
+            for (int j = 0; j < 32; ++j) {
+              const int tok = m0 + c * 32 + j;
+              if (tok < p.M) p.part[((size_t)split * p.M + tok) * p.out_rows + row] = __uint_as_float(v[j]);
+            }
+          } else {
+            const size_t base = (size_t)(m0 + c * 32) * p.ld_out + row;
+            const int nvalid = min(32, p.M - (m0 + c * 32));
+            float old[32];
+            if (p.accumulate) {
+              // all loads first: a load-add-store chain per element would serialise on memory latency
+              const float* o = (const float*)p.out + base;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) old[j] = j < nvalid ? o[(size_t)j * p.ld_out] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (j < nvalid) {
+                float val = __uint_as_float(v[j]);
+                if (p.row_scale) val *= p.row_scale[m0 + c * 32 + j];
+                val += bias_v;
+                if (p.accumulate) val += old[j];
+                const size_t idx = base + (size_t)j * p.ld_out;
+                if (p.out_dtype == OUT_F32) ((float*)p.out)[idx] = val;
+                else if (p.out_dtype == OUT_BF16) ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(val);
+                else ((__half*)p.out)[idx] = __float2half_rn(val);
               }
             }
           }
@@ -401,6 +432,27 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+// Sums split-K partials in split order (deterministic) and applies the epilogue the fused path
+// would have applied: per-token scale, scalar factor, bias, accumulate.  Output is f32 at
+// out[tok * s_tok + row * s_row].
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, int splits, int M, int R, float* __restrict__ out,
+                                     size_t s_tok, size_t s_row, const float* __restrict__ row_scale,
+                                     const float* __restrict__ alpha_dev, const float* __restrict__ bias,
+                                     int accumulate) {
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t n = (size_t)M * R;
+  if (e >= n) return;
+  const int tok = (int)(e / R), row = (int)(e % R);
+  float v = 0.f;
+  for (int k = 0; k < splits; ++k) v += part[(size_t)k * n + e];
+  if (row_scale) v *= row_scale[tok];
+  if (alpha_dev) v *= alpha_dev[0];
+  if (bias) v += bias[row];
+  float* o = out + tok * s_tok + row * s_row;
+  if (accumulate) v += *o;
+  *o = v;
 }
 
 // ------------------------------------------------------------------ host side
@@ -425,8 +477,8 @@ int qgemm_init() {
 }
 
 // 2-D row-major 16-bit matrix [rows x cols]; box = box_cols x box_rows, 128-byte swizzle.
-static int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
-                    uint32_t box_rows, bool is_bf16) {
+static int encode_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                      uint32_t box_rows, bool is_bf16) {
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * 2};
   cuuint32_t box[2] = {box_cols, box_rows};
@@ -438,7 +490,28 @@ static int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t co
   return r == CUDA_SUCCESS ? RT_OK : RT_ERR_CUDA;
 }
 
-int qgemm_launch(const QWeight& w, const QGemmArgs& a, int* status_dev, int num_sms, cudaStream_t st) {
+std::atomic<unsigned long long> g_launch_count{0};
+
+static int make_map_cached(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                           uint32_t box_rows, bool is_bf16) {
+  auto key = std::make_tuple(base, rows, cols, box_cols, box_rows, is_bf16);
+  auto it = ctx->tmap_cache.find(key);
+  if (it != ctx->tmap_cache.end()) {
+    *m = it->second;
+    return RT_OK;
+  }
+  int rc = encode_map(m, base, rows, cols, box_cols, box_rows, is_bf16);
+  if (rc) return rc;
+  if (ctx->tmap_cache.size() > 8192) ctx->tmap_cache.clear();
+  ctx->tmap_cache.emplace(key, *m);
+  return RT_OK;
+}
+#define make_map(m, ...) make_map_cached(ctx, m, __VA_ARGS__)
+
+int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
+  int* status_dev = ctx->status_dev;
+  const int num_sms = ctx->num_sms;
+  cudaStream_t st = ctx->stream;
   if (!g_encode) {
     int rc = qgemm_init();
     if (rc) return rc;
@@ -447,7 +520,8 @@ int qgemm_launch(const QWeight& w, const QGemmArgs& a, int* status_dev, int num_
   const bool is16 = fmt_is_16bit(w.fmt);
   const int contract = a.dir == QG_FWD ? w.cols : w.rows;
   const int out_rows = a.dir == QG_FWD ? w.rows : w.cols;
-  if (contract % 8 != 0 || (is16 && w.cols % 8 != 0)) return RT_ERR_BAD_SHAPE;
+  if ((!a.tok_mode && contract % 8 != 0) || (is16 && w.cols % 8 != 0)) return RT_ERR_BAD_SHAPE;
+  if (a.tok_mode && (!is16 || a.dir != QG_BWD || a.M > 64 || a.lora.rank > 0 || a.out_dtype != OUT_F32)) return RT_ERR_BAD_ARG;
   if (a.accumulate && a.out_dtype != OUT_F32) return RT_ERR_BAD_ARG;
   if (a.lora.rank > 64 || (a.lora.rank > 0 && (!a.lora.act || !a.lora.w))) return RT_ERR_BAD_ARG;
 
@@ -463,6 +537,9 @@ int qgemm_launch(const QWeight& w, const QGemmArgs& a, int* status_dev, int num_
   p.out_rows = out_rows;
   p.M = a.M;
   p.TN = a.M > 128 ? 256 : a.M > 64 ? 128 : a.M > 32 ? 64 : 32;
+  // a single 128-row weight tile (the skinny LoRA products): narrow token tiles spread the work over more SMs
+  if (out_rows <= 128 && a.M > 64) p.TN = 64;
+  if (a.tok_mode) p.TN = 64;
   p.n_main = (contract + 63) / 64;
   p.lora_mmas = a.lora.rank > 0 ? (a.lora.rank + 15) / 16 : 0;
   p.n_row_tiles = (out_rows + 127) / 128;
@@ -478,8 +555,10 @@ int qgemm_launch(const QWeight& w, const QGemmArgs& a, int* status_dev, int num_
   p.idesc_lora = p.idesc_main;
   p.status = status_dev;
 
+  if (a.tok_mode) p.idesc_main = p.idesc_lora = umma_idesc(ab_fmt, ab_fmt, 1, 1, 128, 64);
   CUtensorMap tm_act, tm_w16, tm_lact, tm_lw;
-  int rc = make_map(&tm_act, a.act, (uint64_t)a.M, (uint64_t)contract, 64, (uint32_t)p.TN, !a.act_f16);
+  int rc = a.tok_mode ? make_map(&tm_act, a.act, (uint64_t)contract, 64, 64, 64, !a.act_f16)
+                      : make_map(&tm_act, a.act, (uint64_t)a.M, (uint64_t)contract, 64, (uint32_t)p.TN, !a.act_f16);
   if (rc) return rc;
   tm_w16 = tm_act;
   tm_lact = tm_act;
@@ -496,8 +575,52 @@ int qgemm_launch(const QWeight& w, const QGemmArgs& a, int* status_dev, int num_
     if (rc) return rc;
   }
   const int n_tiles = p.n_row_tiles * p.n_tok_tiles;
-  const int grid = n_tiles < num_sms ? n_tiles : num_sms;
+  // split-K when the tiles alone cannot fill the GPU and the contraction is long
+  int splits = 1;
+  if (a.out_dtype == OUT_F32 && n_tiles * 2 <= num_sms && p.n_main >= 8) {
+    splits = num_sms / n_tiles;
+    if (splits > p.n_main / 4) splits = p.n_main / 4;
+    if (splits < 1) splits = 1;
+  }
+  p.steps_per_split = (p.n_main + splits - 1) / splits;
+  p.n_splits = (p.n_main + p.steps_per_split - 1) / p.steps_per_split;
+  p.b_mn = a.tok_mode ? 1 : 0;
+  p.part = nullptr;
+  if (p.n_splits > 1 || a.tok_mode) {
+    p.part = (float*)ctx->get_scratch(3, (size_t)p.n_splits * a.M * out_rows * sizeof(float));
+    if (!p.part) return RT_ERR_CUDA;
+  }
+  const int n_items = n_tiles * p.n_splits;
+  const int grid = n_items < num_sms ? n_items : num_sms;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (ctx->profiling) {
+    if (ctx->prof_used + 2 > ctx->prof_events.size()) {
+      for (int i = 0; i < 256; ++i) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess) return RT_ERR_CUDA;
+        ctx->prof_events.push_back(e);
+      }
+    }
+    e0 = ctx->prof_events[ctx->prof_used++];
+    e1 = ctx->prof_events[ctx->prof_used++];
+    cudaEventRecord(e0, st);
+  }
   qgemm_kernel<<<grid, QG_THREADS, SMEM_BYTES, st>>>(tm_act, tm_w16, tm_lact, tm_lw, p);
+  RT_COUNT_LAUNCH(1);
+  if (p.part) {
+    const size_t n = (size_t)a.M * out_rows;
+    const size_t s_tok = a.tok_mode ? a.out_s_tok : (size_t)p.ld_out, s_row = a.tok_mode ? a.out_s_row : 1;
+    splitk_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.part, p.n_splits, a.M, out_rows, (float*)a.out, s_tok,
+                                                                    s_row, a.row_scale, a.alpha_dev, p.bias, a.accumulate);
+    RT_COUNT_LAUNCH(1);
+  }
+  if (e1) {
+    cudaEventRecord(e1, st);
+    const double out_bytes = a.out_dtype == OUT_F32 ? 4.0 : 2.0;
+    ctx->prof_flops += 2.0 * (double)a.M * (double)w.rows * (double)w.cols;
+    ctx->prof_recs.push_back({a.tok_mode ? 3 : (a.aux ? 2 : a.dir), a.M, out_rows, contract});
+    ctx->prof_bytes += (double)w.dev_nbytes + 2.0 * (double)a.M * contract + out_bytes * (double)a.M * out_rows * (a.accumulate ? 2.0 : 1.0);
+  }
   return cudaGetLastError() == cudaSuccess ? RT_OK : RT_ERR_CUDA;
 }
 

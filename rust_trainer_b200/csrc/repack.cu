@@ -132,7 +132,7 @@ void launch_repack(const uint8_t* raw_dev, const QWeight& w, cudaStream_t st) {
   size_t total = (size_t)w.nbr * 64 * w.nbk * 2;
   int threads = 128;
   size_t blocks = (total + threads - 1) / threads;
-  repack_kernel<<<(unsigned)blocks, threads, 0, st>>>(raw_dev, w);
+  { repack_kernel<<<(unsigned)blocks, threads, 0, st>>>(raw_dev, w); RT_COUNT_LAUNCH(1); }
 }
 
 // out[i, :] = dequantised row ids[i]  (f32, and optionally a bf16 copy)
@@ -150,7 +150,7 @@ __global__ void gather_rows_kernel(QWeight w, const int* __restrict__ ids, int n
 
 void launch_gather_rows(const QWeight& w, const int* ids_dev, int n, float* out, int* status, cudaStream_t st) {
   if (n <= 0) return;
-  gather_rows_kernel<<<n, 256, 0, st>>>(w, ids_dev, n, out, status);
+  { gather_rows_kernel<<<n, 256, 0, st>>>(w, ids_dev, n, out, status); RT_COUNT_LAUNCH(1); }
 }
 
 }  // namespace rt

@@ -9,9 +9,15 @@
 
 #include "../../include/rt_b200.h"  // status codes and public types
 
+#include <atomic>
+
 namespace rt {
 
 struct QWeight;
+
+// Kernels launched by this library in this process (every launcher adds its own).
+extern std::atomic<unsigned long long> g_launch_count;
+#define RT_COUNT_LAUNCH(n) (rt::g_launch_count.fetch_add((n), std::memory_order_relaxed))
 
 // ---- repack.cu
 void launch_repack(const uint8_t* raw_dev, const QWeight& w, cudaStream_t st);
@@ -43,9 +49,15 @@ struct QGemmArgs {
   const float* bias = nullptr;         // forward only, per output feature
   const float* row_scale = nullptr;    // optional per-token factor on the result (before bias)
   LoraSide lora;
+  // token-contraction mode (LoRA gradients): out[i*out_s_tok + j*out_s_row] (+)= alpha * sum_m P[m,i] * Q[m,j]
+  // with Q = the dense 16-bit `w` [tokens x C], P = act [tokens x 64], M = rank (i < M), dir = QG_BWD
+  int tok_mode = 0;
+  size_t out_s_tok = 0, out_s_row = 1;
+  const float* alpha_dev = nullptr;    // optional device scalar factor (split-K / token mode only)
+  int aux = 0;                         // 1: a skinny LoRA helper product (kept apart in the profile)
 };
 
-int qgemm_launch(const QWeight& w, const QGemmArgs& a, int* status_dev, int num_sms, cudaStream_t st);
+int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a);
 size_t qgemm_smem_bytes();
 int qgemm_init();  // resolves the driver entry point for tensor-map encoding; sets smem attributes
 
