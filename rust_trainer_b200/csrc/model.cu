@@ -862,6 +862,7 @@ static rt_status run_staged(rt_model* m, bool backward, float* logits_out_host) 
   }
   if (backward) RT_CUDA(c, cudaMemsetAsync(m->dx.p, 0, xd * 4, st));
   if (n_targets > 0) RT_TRY(model_head(m, M, n_targets, backward, logits_out_host));
+  else RT_CUDA(c, cudaMemsetAsync(m->hits.p, 0, 4, st));
   if (!backward) return RT_OK;
   launch_normalize_rows(m->dx.as<float>(), M, g.hidden, m->dy16.as<__half>(), m->sc_y.as<float>(), st);
   for (int li = g.n_layers - 1; li >= 0; --li) {

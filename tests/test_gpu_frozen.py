@@ -1,0 +1,111 @@
+"""FrozenMatmul on the GPU (through the C ABI) against the CPU oracle.
+
+Mirrors the reference's own checks: backward_input equals the dense dy.W built from row()
+(tests/engine.rs:96-120, tolerance 1e-3), the adjoint identity (src/frozen.rs:218-227), and
+shape refusals (the reference panics; here a status).  Rows are bit exact (byte/integer
+work); matmuls use f16 operands with f32 accumulation, tolerance 2e-3 relative L2.
+"""
+import numpy as np
+import pytest
+
+import rust_trainer_b200 as rt
+from conftest import rel_l2
+from oracle import oracle as O
+from rust_trainer_b200 import quants as Q
+
+pytestmark = pytest.mark.gpu
+
+FORMATS = [Q.F16, Q.BF16, Q.Q8_0, Q.Q4_0, Q.Q4_K, Q.Q6_K]
+MATMUL_TOL = 2e-3
+
+
+def _shapes(t):
+    if t in (Q.Q4_K, Q.Q6_K):
+        return [(128, 256, 40), (384, 512, 300), (1024, 1024, 513)]
+    return [(128, 64, 1), (256, 128, 100), (192, 96, 7), (896, 896, 300), (1024, 1024, 513)]
+
+
+@pytest.mark.parametrize("t", FORMATS, ids=[Q.NAMES[t] for t in FORMATS])
+def test_rows_are_bit_exact(ctx, t):
+    rng = np.random.default_rng(t)
+    n, k = 200, 512
+    packed = Q.quantize((rng.standard_normal((n, k)) * 0.02).astype(np.float32), t)
+    want = O.dequant_rows(t, packed, n, k)
+    f = rt.Frozen(ctx, t, n, k, packed)
+    assert (f.out_dim(), f.in_dim(), f.nbytes()) == (n, k, packed.size)
+    for r in (0, 1, 63, 64, 127, 128, 199):
+        assert np.array_equal(f.row(r), want[r]), r
+    with pytest.raises(rt.RtError) as e:
+        f.row(n)
+    assert e.value.status == 6
+    f.close()
+
+
+@pytest.mark.parametrize("t", FORMATS, ids=[Q.NAMES[t] for t in FORMATS])
+def test_forward_and_backward_input(ctx, t):
+    rng = np.random.default_rng(100 + t)
+    for n, k, m in _shapes(t):
+        packed = Q.quantize((rng.standard_normal((n, k)) * 0.02).astype(np.float32), t)
+        f = rt.Frozen(ctx, t, n, k, packed)
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        assert rel_l2(f.forward(x, m), O.frozen_forward(t, n, k, packed, x, m)) < MATMUL_TOL, (n, k, m)
+        dy = rng.standard_normal((m, n)).astype(np.float32)
+        dx0 = rng.standard_normal((m, k)).astype(np.float32)
+        dx, ref = dx0.copy(), dx0.copy()
+        f.backward_input(dy, m, dx)  # accumulates, like the trait method
+        O.frozen_backward_input(t, n, k, packed, dy, m, ref)
+        assert rel_l2(dx, ref) < MATMUL_TOL, (n, k, m)
+        f.close()
+
+
+@pytest.mark.parametrize("t", [Q.Q8_0, Q.Q4_0, Q.Q6_K])
+def test_adjoint_identity_on_device(ctx, t):
+    rng = np.random.default_rng(7)
+    n, k, m = 384, 512, 33
+    f = rt.Frozen.from_f32(ctx, (rng.standard_normal((n, k)) * 0.1).astype(np.float32), t)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    dy = rng.standard_normal((m, n)).astype(np.float32)
+    y = f.forward(x, m)
+    dx = np.zeros((m, k), np.float32)
+    f.backward_input(dy, m, dx)
+    lhs, rhs = float((dy.astype(np.float64) * y).sum()), float((dx.astype(np.float64) * x).sum())
+    assert abs(lhs - rhs) <= 2e-3 * max(1.0, abs(lhs))
+    f.close()
+
+
+def test_empty_and_refused_inputs(ctx):
+    rng = np.random.default_rng(0)
+    w = (rng.standard_normal((64, 64)) * 0.02).astype(np.float32)
+    f = rt.Frozen.from_f32(ctx, w, Q.Q4_0)
+    assert f.forward(np.zeros((0, 64), np.float32), 0).shape == (0, 64)  # t = 0 is a no-op
+    with pytest.raises(rt.RtError):
+        f.forward(np.zeros((3, 32), np.float32), 3)  # wrong inner dimension
+    f.close()
+    packed = Q.quantize(w, Q.Q4_0)
+    with pytest.raises(rt.RtError) as e:
+        rt.Frozen(ctx, 3, 64, 64, packed)  # Q4_1: unsupported
+    assert e.value.status == 2
+    with pytest.raises(rt.RtError) as e:
+        rt.Frozen(ctx, Q.Q4_0, 64, 64, packed[:-1])  # byte count does not match
+    assert e.value.status == 1
+    with pytest.raises(rt.RtError) as e:
+        rt.Frozen(ctx, Q.Q4_K, 4, 128, np.zeros(4 * 72, np.uint8))  # 128 is not a multiple of 256
+    assert e.value.status == 1
+
+
+def test_full_size_properties(ctx):
+    """BASELINE sizes (ffn_gate of the 0.6B shape, 8192 tokens), checked by properties that do
+    not need the oracle: linearity in x and the adjoint identity."""
+    rng = np.random.default_rng(3)
+    n, k, m = 3072, 1024, 8192
+    f = rt.Frozen.from_f32(ctx, (rng.standard_normal((n, k)) * 0.02).astype(np.float32), Q.Q8_0)
+    x1 = rng.standard_normal((m, k)).astype(np.float32)
+    x2 = rng.standard_normal((m, k)).astype(np.float32)
+    y1, y2, y12 = f.forward(x1, m), f.forward(x2, m), f.forward(x1 + x2, m)
+    assert rel_l2(y12, y1 + y2) < MATMUL_TOL
+    dy = rng.standard_normal((m, n)).astype(np.float32)
+    dx = np.zeros((m, k), np.float32)
+    f.backward_input(dy, m, dx)
+    lhs, rhs = float((dy.astype(np.float64) * y1).sum()), float((dx.astype(np.float64) * x1).sum())
+    assert abs(lhs - rhs) <= 2e-3 * abs(lhs) + 50.0  # inner products of ~2.5e7 random terms
+    f.close()
