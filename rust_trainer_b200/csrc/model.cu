@@ -23,6 +23,12 @@ void DevBuf::release() {
   bytes = 0;
 }
 
+#define RT_TRY(expr)          \
+  do {                        \
+    rt_status s__ = (expr);   \
+    if (s__) return s__;      \
+  } while (0)
+
 namespace rt {
 
 rt_status lora_refresh(rt_linear* l) {
@@ -58,8 +64,25 @@ static QWeight dense_view(const __half* p, int rows, int cols) {
   return w;
 }
 
+rt_status linear_lora_h(rt_linear* l, const __half* x16, int M, __half* hs_out) {
+  rt_ctx* c = l->ctx;
+  lora_refresh(l);
+  QGemmArgs ha;  // Hs = X . (sA)^T
+  ha.dir = QG_FWD;
+  ha.act = x16;
+  ha.act_f16 = 1;
+  ha.M = M;
+  ha.out = hs_out;
+  ha.out_dtype = OUT_F16;
+  ha.ld_out = 64;
+  ha.aux = 1;
+  int rc = qgemm_launch(c, dense_view(l->lora.a_s, l->lora.rank, l->in_dim()), ha);
+  if (rc) return c->fail(rc, "lora H matmul launch failed");
+  return RT_OK;
+}
+
 rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16, int M, void* y, int y_dtype,
-                             int accumulate) {
+                             int accumulate, __half* hs_keep) {
   rt_ctx* c = l->ctx;
   if (M <= 0) return RT_OK;
   QGemmArgs a;
@@ -74,19 +97,9 @@ rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16,
   if (l->lora_active()) {
     lora_refresh(l);
     const int r = l->lora.rank;
-    __half* hs = lowrank_buf(c, sc.hs, sc.hs_rank, M, r);
+    __half* hs = hs_keep ? hs_keep : lowrank_buf(c, sc.hs, sc.hs_rank, M, r);
     if (!hs) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
-    QGemmArgs ha;  // Hs = X . (sA)^T
-    ha.dir = QG_FWD;
-    ha.act = x16;
-    ha.act_f16 = 1;
-    ha.M = M;
-    ha.out = hs;
-    ha.out_dtype = OUT_F16;
-    ha.ld_out = 64;
-    ha.aux = 1;
-    int rc = qgemm_launch(c, dense_view(l->lora.a_s, r, l->in_dim()), ha);
-    if (rc) return c->fail(rc, "lora H matmul launch failed");
+    RT_TRY(linear_lora_h(l, x16, M, hs));
     a.lora.act = hs;
     a.lora.w = l->lora.bp;
     a.lora.rank = r;
@@ -97,7 +110,7 @@ rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16,
 }
 
 rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16, const __half* dy16,
-                              const float* dscale, int M, float* dx, int accumulate) {
+                              const float* dscale, int M, float* dx, int accumulate, const __half* hs_saved) {
   rt_ctx* c = l->ctx;
   if (M <= 0) return RT_OK;
   const int K = l->in_dim(), N = l->out_dim();
@@ -113,21 +126,12 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
   if (l->lora_active()) {
     lora_refresh(l);
     const int r = l->lora.rank;
-    __half* hs = lowrank_buf(c, sc.hs, sc.hs_rank, M, r);
+    __half* hs = hs_saved ? const_cast<__half*>(hs_saved) : lowrank_buf(c, sc.hs, sc.hs_rank, M, r);
     __half* gs = lowrank_buf(c, sc.gs, sc.gs_rank, M, r);
-    if (!hs || !gs)
-      return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
-    QGemmArgs ha;  // Hs = X . (sA)^T   (recomputed, as src/linear.rs:105 does)
-    ha.dir = QG_FWD;
-    ha.act = x16;
-    ha.act_f16 = 1;
-    ha.M = M;
-    ha.out = hs;
-    ha.out_dtype = OUT_F16;
-    ha.ld_out = 64;
-    ha.aux = 1;
-    int rc = qgemm_launch(c, dense_view(l->lora.a_s, r, K), ha);
-    if (rc) return c->fail(rc, "lora H matmul launch failed");
+    if (!hs || !gs) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+    // Hs = X . (sA)^T: recomputed as src/linear.rs:105 does, unless the caller kept it
+    if (!hs_saved) RT_TRY(linear_lora_h(l, x16, M, hs));
+    int rc;
     QGemmArgs ga;  // Gs = dY~ . (sB)   (unit rows: the row scale is applied where Gs is consumed)
     ga.dir = QG_FWD;
     ga.act = dy16;
@@ -430,6 +434,8 @@ void rt_model_destroy(rt_model* m) {
                     &m->dv16, &m->sc_q, &m->sc_k, &m->sc_v, &m->tpos, &m->ttok, &m->tw, &m->logp, &m->hits, &m->xs,
                     &m->ns16, &m->logits, &m->dl16, &m->sc_l, &m->dns, &m->dxs};
   for (DevBuf* b : bufs) b->release();
+  for (int i = 0; i < 7; ++i) m->hs_keep[i].release();
+  for (auto& ge : m->graphs) cudaGraphExecDestroy(ge.exec);
   delete m;
 }
 
@@ -597,6 +603,8 @@ rt_status rt_model_attach_lora(rt_model* m, int rank, float alpha, const char* t
   RT_CUDA(c, cudaMemset(m->Mo.p, 0, bytes));
   RT_CUDA(c, cudaMemset(m->Vo.p, 0, bytes));
   m->opt_t = 0;
+  for (int i = 0; i < 7; ++i)
+    if (m->hs_keep[i].p) RT_CUDA(c, cudaMemset(m->hs_keep[i].p, 0, m->hs_keep[i].bytes));
   if (n_out) *n_out = total;
   return RT_OK;
 }
@@ -649,6 +657,7 @@ static bool ensure_tokens(rt_model* m, int M) {
   ok &= m->dq.reserve(T * qd * 4) && m->dk.reserve(T * kvd * 4) && m->dv.reserve(T * kvd * 4);
   ok &= m->dq16.reserve(T * qd * 2) && m->dk16.reserve(T * kvd * 2) && m->dv16.reserve(T * kvd * 2);
   ok &= m->sc_q.reserve(T * 4) && m->sc_k.reserve(T * 4) && m->sc_v.reserve(T * 4);
+  for (int i = 0; i < 7; ++i) ok &= m->hs_keep[i].reserve(T * 64 * 2, true);  // zero beyond the rank, kept that way
   if (ok) m->cap_tokens = M;
   return ok;
 }
@@ -695,11 +704,7 @@ static rt_status ensure_rope(rt_model* m, int max_pos) {
   return RT_OK;
 }
 
-#define RT_TRY(expr)          \
-  do {                        \
-    rt_status s__ = (expr);   \
-    if (s__) return s__;      \
-  } while (0)
+
 
 // Block::forward (src/model.rs:165-183).  x_in is read only; h receives x_in + attention;
 // when x_out is non-null it receives the block output (h + mlp), and may alias h.
@@ -709,10 +714,11 @@ static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, fl
   BlockDev& b = m->blocks[li];
   cudaStream_t st = c->stream;
   const int d = g.hidden;
+  const bool keep = x_out == nullptr;  // the recompute pass: its Hs are reused by block_backward
   launch_rmsnorm_fwd(x_in, b.input_norm, M, d, g.rms_eps, m->n1.as<__half>(), st);
-  RT_TRY(linear_forward_dev(b.lin[0], m->lsc, m->n1.as<__half>(), M, m->q_raw.p, RT_DT_F32, 0));
-  RT_TRY(linear_forward_dev(b.lin[1], m->lsc, m->n1.as<__half>(), M, m->k_raw.p, RT_DT_F32, 0));
-  RT_TRY(linear_forward_dev(b.lin[2], m->lsc, m->n1.as<__half>(), M, m->v_raw.p, RT_DT_F32, 0));
+  RT_TRY(linear_forward_dev(b.lin[0], m->lsc, m->n1.as<__half>(), M, m->q_raw.p, RT_DT_F32, 0, keep ? m->hs_keep[0].as<__half>() : nullptr));
+  RT_TRY(linear_forward_dev(b.lin[1], m->lsc, m->n1.as<__half>(), M, m->k_raw.p, RT_DT_F32, 0, keep ? m->hs_keep[1].as<__half>() : nullptr));
+  RT_TRY(linear_forward_dev(b.lin[2], m->lsc, m->n1.as<__half>(), M, m->v_raw.p, RT_DT_F32, 0, keep ? m->hs_keep[2].as<__half>() : nullptr));
   launch_qk_rope_fwd(m->q_raw.as<float>(), m->k_raw.as<float>(), m->v_raw.as<float>(), g.qk_norm ? b.q_norm : nullptr,
                      g.qk_norm ? b.k_norm : nullptr, m->pos.as<int>(), m->rope_cos.as<float>(), m->rope_sin.as<float>(), M,
                      g.n_heads, g.n_kv_heads, g.head_dim, g.rot_dim, g.rope_neox, g.rms_eps, m->q16.as<__half>(),
@@ -721,14 +727,16 @@ static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, fl
                       g.n_kv_heads, g.head_dim, m->o16.as<__half>(), m->lse.as<float>(), st))
     return c->fail(RT_ERR_CUDA, "attention forward launch failed");
   if (h != x_in) RT_CUDA(c, cudaMemcpyAsync(h, x_in, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
-  RT_TRY(linear_forward_dev(b.lin[3], m->lsc, m->o16.as<__half>(), M, h, RT_DT_F32, 1));
+  RT_TRY(linear_forward_dev(b.lin[3], m->lsc, m->o16.as<__half>(), M, h, RT_DT_F32, 1, keep ? m->hs_keep[3].as<__half>() : nullptr));
   launch_rmsnorm_fwd(h, b.post_norm, M, d, g.rms_eps, m->n2.as<__half>(), st);
-  RT_TRY(linear_forward_dev(b.lin[4], m->lsc, m->n2.as<__half>(), M, m->g16.p, RT_DT_F16, 0));
-  RT_TRY(linear_forward_dev(b.lin[5], m->lsc, m->n2.as<__half>(), M, m->u16.p, RT_DT_F16, 0));
+  RT_TRY(linear_forward_dev(b.lin[4], m->lsc, m->n2.as<__half>(), M, m->g16.p, RT_DT_F16, 0, keep ? m->hs_keep[4].as<__half>() : nullptr));
+  RT_TRY(linear_forward_dev(b.lin[5], m->lsc, m->n2.as<__half>(), M, m->u16.p, RT_DT_F16, 0, keep ? m->hs_keep[5].as<__half>() : nullptr));
   launch_swiglu_fwd(m->g16.as<__half>(), m->u16.as<__half>(), m->hm16.as<__half>(), (size_t)M * g.ff, st);
   if (x_out) {
     if (x_out != h) RT_CUDA(c, cudaMemcpyAsync(x_out, h, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
     RT_TRY(linear_forward_dev(b.lin[6], m->lsc, m->hm16.as<__half>(), M, x_out, RT_DT_F32, 1));
+  } else if (b.lin[6]->lora_active()) {
+    RT_TRY(linear_lora_h(b.lin[6], m->hm16.as<__half>(), M, m->hs_keep[6].as<__half>()));  // the backward needs it
   }
   return RT_OK;
 }
@@ -744,16 +752,17 @@ static rt_status block_backward(rt_model* m, int li, int M, const float* x_in) {
   float* dx = m->dx.as<float>();
   __half* dy16 = m->dy16.as<__half>();
   float* sc_y = m->sc_y.as<float>();
+#define HS(i) (b.lin[i]->lora_active() ? m->hs_keep[i].as<__half>() : nullptr)
   // Mlp::backward (src/model.rs:120-134)
-  RT_TRY(linear_backward_dev(b.lin[6], m->lsc, m->hm16.as<__half>(), dy16, sc_y, M, m->dhm.as<float>(), 0));
+  RT_TRY(linear_backward_dev(b.lin[6], m->lsc, m->hm16.as<__half>(), dy16, sc_y, M, m->dhm.as<float>(), 0, HS(6)));
   launch_swiglu_bwd(m->dhm.as<float>(), m->g16.as<__half>(), m->u16.as<__half>(), M, g.ff, m->dg16.as<__half>(),
                     m->du16.as<__half>(), m->sc_g.as<float>(), m->sc_u.as<float>(), st);
-  RT_TRY(linear_backward_dev(b.lin[4], m->lsc, m->n2.as<__half>(), m->dg16.as<__half>(), m->sc_g.as<float>(), M, m->dn.as<float>(), 0));
-  RT_TRY(linear_backward_dev(b.lin[5], m->lsc, m->n2.as<__half>(), m->du16.as<__half>(), m->sc_u.as<float>(), M, m->dn.as<float>(), 1));
+  RT_TRY(linear_backward_dev(b.lin[4], m->lsc, m->n2.as<__half>(), m->dg16.as<__half>(), m->sc_g.as<float>(), M, m->dn.as<float>(), 0, HS(4)));
+  RT_TRY(linear_backward_dev(b.lin[5], m->lsc, m->n2.as<__half>(), m->du16.as<__half>(), m->sc_u.as<float>(), M, m->dn.as<float>(), 1, HS(5)));
   // dh = dy + rmsnorm_backward(h, post_norm, dn2)
   launch_rmsnorm_bwd(m->h.as<float>(), b.post_norm, m->dn.as<float>(), dx, M, d, g.rms_eps, dx, dy16, sc_y, st);
   // Attention::backward (src/attention.rs:246-367)
-  RT_TRY(linear_backward_dev(b.lin[3], m->lsc, m->o16.as<__half>(), dy16, sc_y, M, m->d_o.as<float>(), 0));
+  RT_TRY(linear_backward_dev(b.lin[3], m->lsc, m->o16.as<__half>(), dy16, sc_y, M, m->d_o.as<float>(), 0, HS(3)));
   const size_t nqd = (size_t)M * g.n_heads * g.head_dim;
   launch_global_normalize(m->d_o.as<float>(), nqd, m->amax.as<float>(), m->dO16.as<__half>(), st);
   if (launch_attn_bwd(m->q16.as<__half>(), m->k16.as<__half>(), m->v16.as<__half>(), m->o16.as<__half>(), m->dO16.as<__half>(),
@@ -765,11 +774,12 @@ static rt_status block_backward(rt_model* m, int li, int M, const float* x_in) {
                      m->rope_sin.as<float>(), M, g.n_heads, g.n_kv_heads, g.head_dim, g.rot_dim, g.rope_neox, g.rms_eps,
                      m->dq16.as<__half>(), m->dk16.as<__half>(), m->dv16.as<__half>(), m->sc_q.as<float>(), m->sc_k.as<float>(),
                      m->sc_v.as<float>(), st);
-  RT_TRY(linear_backward_dev(b.lin[0], m->lsc, m->n1.as<__half>(), m->dq16.as<__half>(), m->sc_q.as<float>(), M, m->dn.as<float>(), 0));
-  RT_TRY(linear_backward_dev(b.lin[1], m->lsc, m->n1.as<__half>(), m->dk16.as<__half>(), m->sc_k.as<float>(), M, m->dn.as<float>(), 1));
-  RT_TRY(linear_backward_dev(b.lin[2], m->lsc, m->n1.as<__half>(), m->dv16.as<__half>(), m->sc_v.as<float>(), M, m->dn.as<float>(), 1));
+  RT_TRY(linear_backward_dev(b.lin[0], m->lsc, m->n1.as<__half>(), m->dq16.as<__half>(), m->sc_q.as<float>(), M, m->dn.as<float>(), 0, HS(0)));
+  RT_TRY(linear_backward_dev(b.lin[1], m->lsc, m->n1.as<__half>(), m->dk16.as<__half>(), m->sc_k.as<float>(), M, m->dn.as<float>(), 1, HS(1)));
+  RT_TRY(linear_backward_dev(b.lin[2], m->lsc, m->n1.as<__half>(), m->dv16.as<__half>(), m->sc_v.as<float>(), M, m->dn.as<float>(), 1, HS(2)));
   // dx = dh + rmsnorm_backward(x, input_norm, dn1)
   launch_rmsnorm_bwd(x_in, b.input_norm, m->dn.as<float>(), dx, M, d, g.rms_eps, dx, dy16, sc_y, st);
+#undef HS
   return RT_OK;
 }
 
@@ -846,7 +856,7 @@ static rt_status upload_batch(rt_model* m, const int32_t* tokens, const int32_t*
   return RT_OK;
 }
 
-static rt_status run_staged(rt_model* m, bool backward, float* logits_out_host) {
+static rt_status run_staged_body(rt_model* m, bool backward, float* logits_out_host) {
   rt_ctx* c = m->ctx;
   const int M = m->staged_tokens, n_targets = m->staged_targets;
   if (M <= 0) return c->fail(RT_ERR_BAD_ARG, "no batch staged");
@@ -871,6 +881,78 @@ static rt_status run_staged(rt_model* m, bool backward, float* logits_out_host) 
     RT_TRY(block_backward(m, li, M, x_in));
   }
   return RT_OK;
+}
+
+// Everything the captured launches point at: if any buffer moved, the graph is stale.
+static uint64_t buffer_signature(rt_model* m) {
+  uint64_t h = 1469598103934665603ull;
+  auto mix = [&](const void* p) { h = (h ^ (uint64_t)(uintptr_t)p) * 1099511628211ull; };
+  DevBuf* bufs[] = {&m->P, &m->G, &m->rope_cos, &m->rope_sin, &m->lsc.hs, &m->lsc.gs, &m->lsc.hs2, &m->lsc.gs2, &m->lsc.smax,
+                    &m->tokens, &m->pos, &m->seq_start, &m->x, &m->ckpt, &m->h, &m->n1, &m->n2, &m->q_raw, &m->k_raw, &m->v_raw,
+                    &m->q16, &m->k16, &m->v16, &m->o16, &m->lse, &m->delta, &m->g16, &m->u16, &m->hm16, &m->dx, &m->dy16,
+                    &m->sc_y, &m->dhm, &m->dg16, &m->du16, &m->sc_g, &m->sc_u, &m->dn, &m->d_o, &m->dO16, &m->amax, &m->dq,
+                    &m->dk, &m->dv, &m->dq16, &m->dk16, &m->dv16, &m->sc_q, &m->sc_k, &m->sc_v, &m->tpos, &m->ttok, &m->tw,
+                    &m->logp, &m->hits, &m->xs, &m->ns16, &m->logits, &m->dl16, &m->sc_l, &m->dns, &m->dxs};
+  for (DevBuf* b : bufs) mix(b->p);
+  for (int i = 0; i < 7; ++i) mix(m->hs_keep[i].p);
+  for (int i = 0; i < 4; ++i) mix(m->ctx->scratch[i]);
+  mix((const void*)(uintptr_t)m->n_params);
+  for (auto& b : m->blocks)
+    for (int i = 0; i < 7; ++i) mix((const void*)(uintptr_t)(b.lin[i]->lora_active() ? b.lin[i]->lora.rank : 0));
+  return h;
+}
+
+// The staged step replays as ONE CUDA graph once the same shape has run eagerly (the eager run
+// sizes every buffer and encodes every TMA descriptor; capture then records ~3000 launches
+// with no host work between them).
+static rt_status run_staged(rt_model* m, bool backward, float* logits_out_host) {
+  rt_ctx* c = m->ctx;
+  if (m->use_graphs < 0) {
+    const char* e = getenv("RT_B200_NO_GRAPH");
+    m->use_graphs = (e && e[0] == '1') ? 0 : 1;
+  }
+  if (!m->use_graphs || c->profiling || logits_out_host || c->stream == nullptr) return run_staged_body(m, backward, logits_out_host);
+  RT_CUDA(c, cudaSetDevice(c->device));
+  for (rt_linear* l : m->lora_order) lora_refresh(l);  // outside the graph: only after a parameter update
+  const int M = m->staged_tokens, nt = m->staged_targets, bw = backward ? 1 : 0;
+  const uint64_t sig = buffer_signature(m);
+  for (auto& ge : m->graphs)
+    if (ge.M == M && ge.n_targets == nt && ge.backward == bw && ge.sig == sig) {
+      RT_CUDA(c, cudaGraphLaunch(ge.exec, c->stream));
+      RT_COUNT_LAUNCH(ge.kernels);
+      return RT_OK;
+    }
+  if (m->eager_M == M && m->eager_targets == nt && m->eager_backward == bw && m->eager_sig == sig) {
+    const unsigned long long before = g_launch_count.load();
+    cudaGraph_t graph = nullptr;
+    RT_CUDA(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    rt_status st = run_staged_body(m, backward, nullptr);
+    cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+    const unsigned long long kernels = g_launch_count.load() - before;
+    g_launch_count.fetch_sub(kernels);  // nothing ran yet; the replay below counts them
+    cudaGraphExec_t exec = nullptr;
+    if (st == RT_OK && e == cudaSuccess && graph && cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) {
+      cudaGraphDestroy(graph);
+      if (m->graphs.size() >= 8) {
+        cudaGraphExecDestroy(m->graphs.front().exec);
+        m->graphs.erase(m->graphs.begin());
+      }
+      m->graphs.push_back({M, nt, bw, sig, exec, kernels});
+      RT_CUDA(c, cudaGraphLaunch(exec, c->stream));
+      RT_COUNT_LAUNCH(kernels);
+      return RT_OK;
+    }
+    if (graph) cudaGraphDestroy(graph);
+    cudaGetLastError();
+    m->use_graphs = 0;  // capture is not possible here: stay eager
+    return run_staged_body(m, backward, nullptr);
+  }
+  rt_status st = run_staged_body(m, backward, nullptr);
+  m->eager_M = M;
+  m->eager_targets = nt;
+  m->eager_backward = bw;
+  m->eager_sig = buffer_signature(m);
+  return st;
 }
 
 rt_status rt_model_stage_batch(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,

@@ -48,11 +48,16 @@ struct LinearScratch {
 };
 
 namespace rt {
+// hs_keep: optional [M x 64] f16 buffer (zero beyond the rank) that receives Hs = X.(sA)^T so the
+// backward can reuse it instead of recomputing it.
 rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16, int M, void* y, int y_dtype,
-                             int accumulate);
+                             int accumulate, __half* hs_keep = nullptr);
+// Hs alone (the forward of a linear whose output is not needed).
+rt_status linear_lora_h(rt_linear* l, const __half* x16, int M, __half* hs_out);
 // dy16 is row-normalised f16 with per-row scales `dscale` (null = all ones)
 rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16, const __half* dy16,
-                              const float* dscale, int M, float* dx, int accumulate);
+                              const float* dscale, int M, float* dx, int accumulate,
+                              const __half* hs_saved = nullptr);
 rt_status lora_refresh(rt_linear* l);
 }  // namespace rt
 
@@ -83,6 +88,7 @@ struct rt_model {
   int rope_max_pos = 0;
 
   LinearScratch lsc;
+  DevBuf hs_keep[7];  // Hs of the current block's seven linears, kept from the recompute for the backward
   // activations, sized for `cap_tokens`
   int cap_tokens = 0, cap_targets = 0, cap_head_rows = 0;
   DevBuf tokens, pos, seq_start, x, ckpt, h, n1, n2, q_raw, k_raw, v_raw, q16, k16, v16, o16, lse, delta, g16, u16, hm16;
@@ -91,4 +97,10 @@ struct rt_model {
   std::vector<int> h_pos, h_seq_start;
   int staged_tokens = 0, staged_targets = 0;
   bool staged_has_weights = false;
+  // CUDA graphs of the staged step, one per (tokens, targets, backward) once it has run eagerly
+  struct GraphEntry { int M, n_targets, backward; uint64_t sig; cudaGraphExec_t exec; unsigned long long kernels; };
+  std::vector<GraphEntry> graphs;
+  int eager_M = -1, eager_targets = -1, eager_backward = -1;
+  uint64_t eager_sig = 0;
+  int use_graphs = -1;  // -1: decide from the environment on first use
 };

@@ -114,8 +114,13 @@ __device__ __forceinline__ void unpack_q4_k(const uint8_t* brick, int t, uint8_t
   const __half2 dd = ((const __half2*)(brick + 2048))[t >> 1];
   const uchar2 sm = ((const uchar2*)(brick + 2304))[t];
   const float2 ddf = __half22float2(dd);
-  const __half2 dsc = __half2half2(__float2half_rn(ddf.x * (float)sm.x));
-  const __half2 ndm = __half2half2(__float2half_rn(-ddf.y * (float)sm.y));
+  // value = (d*sc)*q - dmin*m is a difference of like-sized terms: each factor is carried as an
+  // f16 pair (hi + lo) so the only rounding that matters is the final one, relative to the value
+  const float dscf = ddf.x * (float)sm.x, ndmf = -ddf.y * (float)sm.y;
+  const __half dsc_h = __float2half_rn(dscf), ndm_h = __float2half_rn(ndmf);
+  const __half2 dsc = __half2half2(dsc_h), ndm = __half2half2(ndm_h);
+  const __half2 dsc_lo = __half2half2(__float2half_rn(dscf - __half2float(dsc_h)));
+  const __half2 ndm_lo = __half2half2(__float2half_rn(ndmf - __half2float(ndm_h)));
   const __half2 off = __floats2half2_rn(1024.f, 1024.f);
   const int r = t >> 1, cb = (t & 1) * 4;
   const uint32_t w[4] = {q.x, q.y, q.z, q.w};
@@ -125,7 +130,8 @@ __device__ __forceinline__ void unpack_q4_k(const uint8_t* brick, int t, uint8_t
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
       uint32_t x = ((w[j] >> (4 * p)) & 0x000F000Fu) | 0x64006400u;
-      o[p] = fin<WBF16>(__hfma2(__hsub2(u32_as_h2(x), off), dsc, ndm));
+      const __half2 qv = __hsub2(u32_as_h2(x), off);
+      o[p] = fin<WBF16>(__hadd2(__hfma2(qv, dsc, ndm), __hfma2(qv, dsc_lo, ndm_lo)));
     }
     store_chunk(dst, r, cb + j, o[0], o[1], o[2], o[3]);
   }
