@@ -344,6 +344,56 @@ def run_ours(args):
     return 0
 
 
+def run_microbench(args):
+    """Frozen-matmul kernel alone on the workload's projection shapes: forward (f16 out) and
+    backward (f32 out) at `--tokens` tokens, CUDA events on the launching stream."""
+    import torch
+    import rust_trainer_b200 as rt
+    from rust_trainer_b200 import quants as Q, synth
+    from rust_trainer_b200._lib import lib
+
+    wl = WORKLOADS[args.workload]
+    spec = synth.preset(wl["preset"], quant=wl["quant"])
+    L = lib()
+    ctx = rt.Context(0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    L.rt_ctx_set_stream(ctx._h, C.c_void_p(stream.cuda_stream))
+    M = args.tokens
+    rng = np.random.default_rng(0)
+    peaks = measured_peaks()
+    rows = []
+    shapes = sorted(set(spec.linear_shapes().values()))
+    if args.shape:
+        n, k = (int(v) for v in args.shape.split("x"))
+        shapes = [(n, k)]
+    for (n, k) in shapes:
+        t = spec.quant_for(k)
+        f = rt.Frozen(ctx, t, n, k, Q.quantize((rng.standard_normal((n, k)) * 0.02).astype(np.float32), t))
+        x = torch.randn(M, k, device="cuda", dtype=torch.float16)
+        dy = torch.randn(M, n, device="cuda", dtype=torch.float16)
+        y = torch.empty(M, n, device="cuda", dtype=torch.float16)
+        dx = torch.empty(M, k, device="cuda", dtype=torch.float32)
+        for name, fn in (("fwd", lambda: L.rt_frozen_forward_dev(f._h, x.data_ptr(), 2, M, y.data_ptr(), 2, 0)),
+                         ("bwd", lambda: L.rt_frozen_backward_input_dev(f._h, dy.data_ptr(), 2, M, dx.data_ptr(), 0, 0))):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(args.steps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ctx.synchronize()
+            us = 1e3 * e0.elapsed_time(e1) / args.steps
+            tf = 2.0 * M * n * k / us / 1e6
+            rows.append(dict(dir=name, out=n, inp=k, tokens=M, quant=Q.NAMES[t], us=us, tflops=tf, frac=tf / peaks["tflops"]))
+        f.close()
+    print(json.dumps({"microbench": "qgemm_kernel", "peak_tflops": peaks["tflops"], "peak_source": peaks["source"], "rows": rows}), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -352,9 +402,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--microbench", action="store_true", help="time the frozen-matmul kernel alone")
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--shape", default="", help="microbench: one OUTxIN shape instead of the workload's")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
+    if args.microbench:
+        return run_microbench(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
