@@ -67,7 +67,12 @@ static QWeight dense_view(const __half* p, int rows, int cols) {
 rt_status linear_lora_h(rt_linear* l, const __half* x16, int M, __half* hs_out) {
   rt_ctx* c = l->ctx;
   lora_refresh(l);
-  QGemmArgs ha;  // Hs = X . (sA)^T
+  {
+    const int rc0 = launch_skinny_nt(x16, l->lora.a_s, M, l->in_dim(), l->lora.rank, hs_out, c->stream);
+    if (rc0 == 0) return RT_OK;
+    if (rc0 != 1) return c->fail(RT_ERR_CUDA, "lora H kernel launch failed");
+  }
+  QGemmArgs ha;  // Hs = X . (sA)^T  (general shapes: through the big kernel)
   ha.dir = QG_FWD;
   ha.act = x16;
   ha.act_f16 = 1;
@@ -131,7 +136,9 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
     if (!hs || !gs) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
     // Hs = X . (sA)^T: recomputed as src/linear.rs:105 does, unless the caller kept it
     if (!hs_saved) RT_TRY(linear_lora_h(l, x16, M, hs));
-    int rc;
+    int rc = launch_skinny_nt(dy16, l->lora.bt_s, M, N, r, gs, c->stream);
+    if (rc > 1) return c->fail(RT_ERR_CUDA, "lora G kernel launch failed");
+    const bool g_done = rc == 0;
     QGemmArgs ga;  // Gs = dY~ . (sB)   (unit rows: the row scale is applied where Gs is consumed)
     ga.dir = QG_FWD;
     ga.act = dy16;
@@ -141,8 +148,10 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
     ga.out_dtype = OUT_F16;
     ga.ld_out = 64;
     ga.aux = 1;
-    rc = qgemm_launch(c, dense_view(l->lora.bt_s, r, N), ga);
-    if (rc) return c->fail(rc, "lora G matmul launch failed");
+    if (!g_done) {
+      rc = qgemm_launch(c, dense_view(l->lora.bt_s, r, N), ga);
+      if (rc) return c->fail(rc, "lora G matmul launch failed");
+    }
     // gb[N x r] += dY^T . Hs ; ga[r x K] += Gs^T . X   on the tensor cores, contraction over tokens.
     // The per-token scales of dY move onto the skinny operand (rows * scale / max), the max onto the result.
     const __half *hs_c = hs, *gs_c = gs;
@@ -158,6 +167,11 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
       gs_c = gs2;
       alpha = sc.smax.as<float>();
     }
+    const size_t wsf = tok_contract_workspace_floats(M, K > N ? K : N, r);
+    if (!sc.grad_ws.reserve(wsf * sizeof(float))) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+    const int rb = launch_tok_contract(hs_c, dy16, M, N, r, 1, (size_t)r, alpha, l->lora.gb, sc.grad_ws.as<float>(), c->stream);
+    const int ra = launch_tok_contract(gs_c, x16, M, K, r, (size_t)K, 1, alpha, l->lora.ga, sc.grad_ws.as<float>(), c->stream);
+    if (rb > 1 || ra > 1) return c->fail(RT_ERR_CUDA, "lora gradient kernel launch failed");
     QGemmArgs ta;
     ta.dir = QG_BWD;
     ta.tok_mode = 1;
@@ -171,14 +185,18 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
     ta.out = l->lora.gb;
     ta.out_s_tok = 1;
     ta.out_s_row = (size_t)r;
-    rc = qgemm_launch(c, dense_view(dy16, M, N), ta);
-    if (rc) return c->fail(rc, "lora dB matmul launch failed");
+    if (rb == 1) {
+      rc = qgemm_launch(c, dense_view(dy16, M, N), ta);
+      if (rc) return c->fail(rc, "lora dB matmul launch failed");
+    }
     ta.act = gs_c;  // dA[i, k] += sum_m Gs[m, i] X[m, k]
     ta.out = l->lora.ga;
     ta.out_s_tok = (size_t)K;
     ta.out_s_row = 1;
-    rc = qgemm_launch(c, dense_view(x16, M, K), ta);
-    if (rc) return c->fail(rc, "lora dA matmul launch failed");
+    if (ra == 1) {
+      rc = qgemm_launch(c, dense_view(x16, M, K), ta);
+      if (rc) return c->fail(rc, "lora dA matmul launch failed");
+    }
     a.lora.act = gs;
     a.lora.w = l->lora.a_h;
     a.lora.rank = r;
@@ -427,7 +445,7 @@ void rt_model_destroy(rt_model* m) {
   if (m->embed) rt_frozen_destroy(m->embed);
   for (void* p : m->owned) cudaFree(p);
   DevBuf* bufs[] = {&m->P, &m->G, &m->Mo, &m->Vo, &m->opt_scalars, &m->inv_freq, &m->rope_cos, &m->rope_sin,
-                    &m->lsc.hs, &m->lsc.gs, &m->lsc.hs2, &m->lsc.gs2, &m->lsc.smax, &m->tokens, &m->pos, &m->seq_start, &m->x, &m->ckpt, &m->h,
+                    &m->lsc.hs, &m->lsc.gs, &m->lsc.hs2, &m->lsc.gs2, &m->lsc.smax, &m->lsc.grad_ws, &m->tokens, &m->pos, &m->seq_start, &m->x, &m->ckpt, &m->h,
                     &m->n1, &m->n2, &m->q_raw, &m->k_raw, &m->v_raw, &m->q16, &m->k16, &m->v16, &m->o16, &m->lse,
                     &m->delta, &m->g16, &m->u16, &m->hm16, &m->dx, &m->dy16, &m->sc_y, &m->dhm, &m->dg16, &m->du16,
                     &m->sc_g, &m->sc_u, &m->dn, &m->d_o, &m->dO16, &m->amax, &m->dq, &m->dk, &m->dv, &m->dq16, &m->dk16,
@@ -887,7 +905,7 @@ static rt_status run_staged_body(rt_model* m, bool backward, float* logits_out_h
 static uint64_t buffer_signature(rt_model* m) {
   uint64_t h = 1469598103934665603ull;
   auto mix = [&](const void* p) { h = (h ^ (uint64_t)(uintptr_t)p) * 1099511628211ull; };
-  DevBuf* bufs[] = {&m->P, &m->G, &m->rope_cos, &m->rope_sin, &m->lsc.hs, &m->lsc.gs, &m->lsc.hs2, &m->lsc.gs2, &m->lsc.smax,
+  DevBuf* bufs[] = {&m->P, &m->G, &m->rope_cos, &m->rope_sin, &m->lsc.hs, &m->lsc.gs, &m->lsc.hs2, &m->lsc.gs2, &m->lsc.smax, &m->lsc.grad_ws,
                     &m->tokens, &m->pos, &m->seq_start, &m->x, &m->ckpt, &m->h, &m->n1, &m->n2, &m->q_raw, &m->k_raw, &m->v_raw,
                     &m->q16, &m->k16, &m->v16, &m->o16, &m->lse, &m->delta, &m->g16, &m->u16, &m->hm16, &m->dx, &m->dy16,
                     &m->sc_y, &m->dhm, &m->dg16, &m->du16, &m->sc_g, &m->sc_u, &m->dn, &m->d_o, &m->dO16, &m->amax, &m->dq,

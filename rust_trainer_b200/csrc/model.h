@@ -43,7 +43,7 @@ struct rt_linear {
 
 // Scratch shared by every Linear call on a ctx (one call at a time per ctx).
 struct LinearScratch {
-  DevBuf hs, gs, hs2, gs2, smax;
+  DevBuf hs, gs, hs2, gs2, smax, grad_ws;
   int hs_rank = -1, gs_rank = -1, hs2_rank = -1, gs2_rank = -1;
 };
 

@@ -39,6 +39,12 @@ void launch_adamw(float* p, float* g, float* m, float* v, size_t n, const double
                   cudaStream_t st);
 void launch_global_normalize(const float* x, size_t n, float* amax_dev, __half* y16, cudaStream_t st);
 
+// ---- lora_kernels.cu: skinny low-rank products (return 1 when the shape is not supported)
+int launch_skinny_nt(const __half* X, const __half* Wt, int M, int K, int r, __half* out64, cudaStream_t st);
+size_t tok_contract_workspace_floats(int M, int C, int r);
+int launch_tok_contract(const __half* P, const __half* Q, int M, int C, int r, size_t so_i, size_t so_j,
+                        const float* alpha_dev, float* out, float* workspace, cudaStream_t st);
+
 // ---- attention.cu: causal GQA attention over a concatenation of independent sequences.
 // q [M x nh x hd], k/v [M x nkv x hd] f16 (q unscaled; the kernels apply 1/sqrt(hd)).
 // seq_start[m] = index of the first token of m's sequence.  lse is [nh x M].

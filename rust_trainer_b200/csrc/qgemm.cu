@@ -23,7 +23,7 @@
 
 namespace rt {
 
-constexpr int NS = 4;                 // activation / unpacked-weight stages
+constexpr int NS = 3;                 // activation / unpacked-weight stages
 constexpr int NR = 3;                 // packed brick-pair stages
 constexpr int ACT_STAGE = 32768;      // 256 tokens x 64 x bf16
 constexpr int W_STAGE = 16384;        // 128 x 64 x 16-bit
@@ -31,7 +31,9 @@ constexpr int RAW_STAGE = 2 * 4352;   // largest brick pair (Q8_0)
 constexpr int QG_THREADS = 320;
 constexpr int OFF_W = NS * ACT_STAGE;
 constexpr int OFF_RAW = OFF_W + NS * W_STAGE;
-constexpr int OFF_BAR = OFF_RAW + NR * RAW_STAGE;
+constexpr int OUT_STAGE = 32 * 128 * 4;  // 32 tokens x 128 output features x f32: the epilogue's TMA-store staging
+constexpr int OFF_OUT = OFF_RAW + NR * RAW_STAGE;
+constexpr int OFF_BAR = OFF_OUT + 2 * OUT_STAGE;
 constexpr int N_BARS = 3 * NS + 2 * NR + 4;
 constexpr int SMEM_BYTES = OFF_BAR + N_BARS * 8 + 16 + 1024;
 
@@ -52,6 +54,8 @@ struct KParams {
   const float* bias;
   uint32_t idesc_main, idesc_lora;
   int* status;
+  int tma_out;  // the epilogue stages [32 tokens x 128] tiles in shared memory and writes them with TMA
+  int dbg;  // measurement aid (RT_B200_DBG): 1 = epilogue skips its stores, 2 = unpack warps skip the conversion
 };
 
 // ------------------------------------------------------------------ unpackers
@@ -177,12 +181,13 @@ __device__ __forceinline__ void unpack_pair(int fmt, const uint8_t* raw, int bb,
 __global__ void __launch_bounds__(QG_THREADS, 1)
 qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_w16,
              const __grid_constant__ CUtensorMap tm_lact, const __grid_constant__ CUtensorMap tm_lw,
-             const KParams p) {
+             const __grid_constant__ CUtensorMap tm_out, const KParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sAct = smem;
   uint8_t* sW = smem + OFF_W;
   uint8_t* sRaw = smem + OFF_RAW;
+  uint8_t* sOut = smem + OFF_OUT;
   uint64_t* bars = (uint64_t*)(smem + OFF_BAR);
   uint64_t* full = bars;                   // [NS] activations (+ TMA'd weight tile) landed
   uint64_t* w_ready = bars + NS;           // [NS] unpack warps done with the weight tile
@@ -214,6 +219,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     prefetch_tmap(&tm_w16);
     prefetch_tmap(&tm_lact);
     prefetch_tmap(&tm_lw);
+    if (p.tma_out) prefetch_tmap(&tm_out);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -360,7 +366,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           if (!mbar_wait(&raw_full[rs], rph, p.status, 202)) { ok = false; break; }
           const uint8_t* raw = sRaw + rs * RAW_STAGE;
           uint8_t* dst = sW + st * W_STAGE;
-          if (p.act_f16) unpack_pair<false>(p.fmt, raw, p.brick_bytes, t, dst);
+          if (p.dbg == 2) {
+          } else if (p.act_f16) unpack_pair<false>(p.fmt, raw, p.brick_bytes, t, dst);
           else unpack_pair<true>(p.fmt, raw, p.brick_bytes, t, dst);
           fence_proxy_async_smem();
           mbar_arrive(&raw_empty[rs]);
@@ -372,7 +379,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
   } else {
     // ------------------------------------------------------------ epilogue
     const int wq = warp & 3;  // TMEM lane quarter this warp may read
-    uint32_t tcount = 0;
+    uint32_t tcount = 0, out_chunk = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++tcount) {
       QG_ITEM_DECODE(item);
@@ -389,7 +396,35 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         uint32_t v[32];
         tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(wq * 32) << 16) + c * 32, v);
         tmem_ld_wait();
-        if (row_ok) {
+        if (p.tma_out && p.dbg != 1) {
+          // Transpose through shared memory: lane = output feature, register j = token, so the
+          // staged tile is [32 tokens][128 features] and one TMA store writes 32 full rows.
+          const int buf = (int)(out_chunk & 1);
+          ++out_chunk;
+          uint8_t* stage = sOut + buf * OUT_STAGE;
+          const bool issuer = warp == 6 && lane == 0;
+          if (issuer) bulk_wait_group_read<1>();  // the store that last read this buffer is done with it
+          named_barrier_sync(1, 128);
+          const int col = wq * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float val = __uint_as_float(v[j]);
+            if (p.row_scale) { const int tok = m0 + c * 32 + j; val *= p.row_scale[tok < p.M ? tok : 0]; }
+            val += bias_v;
+            if (p.out_dtype == OUT_F32) ((float*)stage)[j * 128 + col] = val;
+            else if (p.out_dtype == OUT_BF16) ((__nv_bfloat16*)stage)[j * 128 + col] = __float2bfloat16_rn(val);
+            else ((__half*)stage)[j * 128 + col] = __float2half_rn(val);
+          }
+          fence_proxy_async_smem();
+          named_barrier_sync(1, 128);
+          if (issuer) {
+            if (p.accumulate) tma_reduce_add_2d(&tm_out, r0, m0 + c * 32, stage);
+            else tma_store_2d(&tm_out, r0, m0 + c * 32, stage);
+            bulk_commit_group();
+          }
+          continue;
+        }
+        if (row_ok && p.dbg != 1) {
           if (p.part != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -425,6 +460,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
     }
+    if (p.tma_out && warp == 6 && lane == 0) bulk_wait_group<0>();  // all output writes have landed
   }
 
   // ---------------------------------------------------------------- teardown
@@ -514,6 +550,30 @@ static int make_map_cached(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64
 }
 #define make_map(m, ...) make_map_cached(ctx, m, __VA_ARGS__)
 
+// Output matrix [rows x cols] of f32 / bf16 / f16 with a row pitch of `ld` elements; box = 128 columns x 32 rows,
+// no swizzle (the epilogue writes the staging tile row-major).
+static int make_out_map(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int dtype) {
+  auto key = std::make_tuple(base, rows, cols | (ld << 32), 128u, 32u | ((uint32_t)dtype << 8), true);
+  auto it = ctx->tmap_cache.find(key);
+  if (it != ctx->tmap_cache.end()) {
+    *m = it->second;
+    return RT_OK;
+  }
+  const uint64_t es = dtype == OUT_F32 ? 4 : 2;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * es};
+  cuuint32_t box[2] = {128, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = dtype == OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : dtype == OUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = g_encode(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return RT_ERR_CUDA;
+  if (ctx->tmap_cache.size() > 8192) ctx->tmap_cache.clear();
+  ctx->tmap_cache.emplace(key, *m);
+  return RT_OK;
+}
+
 int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   int* status_dev = ctx->status_dev;
   const int num_sms = ctx->num_sms;
@@ -546,6 +606,17 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   // a single 128-row weight tile (the skinny LoRA products): narrow token tiles spread the work over more SMs
   if (out_rows <= 128 && a.M > 64) p.TN = 64;
   if (a.tok_mode) p.TN = 64;
+  if (p.TN == 256 && !a.tok_mode) {
+    // pick the token-tile width that wastes the least of the last wave of the persistent grid
+    const int row_tiles = (out_rows + 127) / 128;
+    long best_cost = -1;
+    for (int tn = 256; tn >= 128; tn -= 32) {
+      const long tiles = (long)row_tiles * ((a.M + tn - 1) / tn);
+      const long rounds = (tiles + num_sms - 1) / num_sms;
+      const long cost = rounds * (tn + 40);  // + a per-tile fixed cost, in token units
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; p.TN = tn; }
+    }
+  }
   p.n_main = (contract + 63) / 64;
   p.lora_mmas = a.lora.rank > 0 ? (a.lora.rank + 15) / 16 : 0;
   p.n_row_tiles = (out_rows + 127) / 128;
@@ -560,6 +631,11 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   p.idesc_main = umma_idesc(ab_fmt, ab_fmt, a.dir == QG_BWD ? 1 : 0, 0, 128, p.TN);
   p.idesc_lora = p.idesc_main;
   p.status = status_dev;
+  {
+    static int dbg = -1;
+    if (dbg < 0) { const char* e = getenv("RT_B200_DBG"); dbg = e ? atoi(e) : 0; }
+    p.dbg = dbg;
+  }
 
   if (a.tok_mode) p.idesc_main = p.idesc_lora = umma_idesc(ab_fmt, ab_fmt, 1, 1, 128, 64);
   CUtensorMap tm_act, tm_w16, tm_lact, tm_lw;
@@ -596,6 +672,17 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
     p.part = (float*)ctx->get_scratch(3, (size_t)p.n_splits * a.M * out_rows * sizeof(float));
     if (!p.part) return RT_ERR_CUDA;
   }
+  // TMA-store epilogue whenever the output is TMA-addressable (16-byte aligned base and row pitch)
+  CUtensorMap tm_out = tm_act;
+  p.tma_out = 0;
+  {
+    const uint64_t es = a.out_dtype == OUT_F32 ? 4 : 2;
+    if (!p.part && ((uintptr_t)a.out % 16 == 0) && ((uint64_t)p.ld_out * es) % 16 == 0) {
+      rc = make_out_map(ctx, &tm_out, a.out, (uint64_t)a.M, (uint64_t)out_rows, (uint64_t)p.ld_out, a.out_dtype);
+      if (rc) return rc;
+      p.tma_out = 1;
+    }
+  }
   const int n_items = n_tiles * p.n_splits;
   const int grid = n_items < num_sms ? n_items : num_sms;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
@@ -611,7 +698,7 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
     e1 = ctx->prof_events[ctx->prof_used++];
     cudaEventRecord(e0, st);
   }
-  qgemm_kernel<<<grid, QG_THREADS, SMEM_BYTES, st>>>(tm_act, tm_w16, tm_lact, tm_lw, p);
+  qgemm_kernel<<<grid, QG_THREADS, SMEM_BYTES, st>>>(tm_act, tm_w16, tm_lact, tm_lw, tm_out, p);
   RT_COUNT_LAUNCH(1);
   if (p.part) {
     const size_t n = (size_t)a.M * out_rows;
