@@ -38,6 +38,9 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// all but the most recent group have landed
+__device__ __forceinline__ void cp_async_wait_prev() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 // rows [row0, row0+BT) of a [M x heads x HD] tensor, one head, into a swizzled tile
 template <int HD>
@@ -101,12 +104,13 @@ attn_fwd_kernel(const __half* __restrict__ q, const __half* __restrict__ k, cons
                 const int* __restrict__ seq_start, int M, int nh, int nkv, float scale, __half* __restrict__ o,
                 float* __restrict__ lse) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const uint32_t sQ = smem_addr(smem), sK = sQ + BT * HD * 2, sV = sK + BT * HD * 2;
+  const uint32_t sQ = smem_addr(smem), sKV = sQ + BT * HD * 2;  // then two (K, V) buffers
   const int m0 = blockIdx.x * BT, h = blockIdx.y, g = h / (nh / nkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
   const float sl2 = scale * LOG2E;
 
   load_tile<HD>(sQ, q, m0, M, nh, h);
+  cp_async_commit();
   cp_async_wait_all();
   __syncthreads();
   uint32_t qf[HD / 16][4];
@@ -122,11 +126,19 @@ attn_fwd_kernel(const __half* __restrict__ q, const __half* __restrict__ k, cons
 
   const int kbeg = (seq_start[m0] / BT) * BT;
   const int kend = min(m0 + BT, M);
-  for (int n0 = kbeg; n0 < kend; n0 += BT) {
-    __syncthreads();
-    load_tile<HD>(sK, k, n0, M, nkv, g);
-    load_tile<HD>(sV, v, n0, M, nkv, g);
-    cp_async_wait_all();
+  load_tile<HD>(sKV, k, kbeg, M, nkv, g);
+  load_tile<HD>(sKV + BT * HD * 2, v, kbeg, M, nkv, g);
+  cp_async_commit();
+  int it = 0;
+  for (int n0 = kbeg; n0 < kend; n0 += BT, ++it) {
+    const uint32_t sK = sKV + (it & 1) * 2 * BT * HD * 2, sV = sK + BT * HD * 2;
+    if (n0 + BT < kend) {  // prefetch the next key tile while this one is used
+      const uint32_t nK = sKV + ((it & 1) ^ 1) * 2 * BT * HD * 2;
+      load_tile<HD>(nK, k, n0 + BT, M, nkv, g);
+      load_tile<HD>(nK + BT * HD * 2, v, n0 + BT, M, nkv, g);
+    }
+    cp_async_commit();
+    cp_async_wait_prev();
     __syncthreads();
 
     float s[8][4];
@@ -192,6 +204,7 @@ attn_fwd_kernel(const __half* __restrict__ q, const __half* __restrict__ k, cons
         mma16816(oacc[2 * np + 1], a, b + 2);
       }
     }
+    __syncthreads();  // every warp is done with this buffer before the next prefetch overwrites it
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -239,10 +252,8 @@ attn_bwd_dkdv_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
                      const int* __restrict__ seq_start, int M, int nh, int nkv, float scale, float* __restrict__ dk,
                      float* __restrict__ dv) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const uint32_t sK = smem_addr(smem), sV = sK + BT * HD * 2, sQ = sV + BT * HD * 2, sdO = sQ + BT * HD * 2;
-  float* sLse = (float*)(smem + 4 * BT * HD * 2);
-  float* sDel = sLse + BT;
-  int* sSS = (int*)(sDel + BT);
+  const uint32_t sK = smem_addr(smem), sV = sK + BT * HD * 2, sQdO = sV + BT * HD * 2;  // then two (Q, dO) buffers
+  float* sAux = (float*)(smem + 6 * BT * HD * 2);  // two buffers of (lse, delta, seq_start) per query row
   const int n0 = blockIdx.x * BT, g = blockIdx.y, group = nh / nkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
   const float sl2 = scale * LOG2E;
@@ -268,19 +279,35 @@ attn_bwd_dkdv_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
     while (e < M && seq_start[e] == ss_last) ++e;
     qend = e;
   }
-  for (int hh = 0; hh < group; ++hh) {
-    const int h = g * group + hh;
-    for (int m0 = n0; m0 < qend; m0 += BT) {
-      __syncthreads();
-      load_tile<HD>(sQ, q, m0, M, nh, h);
-      load_tile<HD>(sdO, dO, m0, M, nh, h);
-      if (threadIdx.x < BT) {
-        const int m = m0 + threadIdx.x;
-        sLse[threadIdx.x] = m < M ? lse[(size_t)h * M + m] * LOG2E : 0.f;
-        sDel[threadIdx.x] = m < M ? delta[(size_t)h * M + m] : 0.f;
-        sSS[threadIdx.x] = m < M ? seq_start[m] : 0x7fffffff;
-      }
-      cp_async_wait_all();
+  // work list: (query head of the group) x (query tiles that can see these keys); tile idx+1 is
+  // prefetched while tile idx is used
+  const int nqt = qend > n0 ? (qend - n0 + BT - 1) / BT : 0;
+  const int n_work = group * nqt;
+  auto prefetch = [&](int idx, int buf) {
+    const int h = g * group + idx / nqt, m0 = n0 + (idx % nqt) * BT;
+    load_tile<HD>(sQdO + buf * 2 * BT * HD * 2, q, m0, M, nh, h);
+    load_tile<HD>(sQdO + buf * 2 * BT * HD * 2 + BT * HD * 2, dO, m0, M, nh, h);
+    if (threadIdx.x < BT) {
+      const int m = m0 + threadIdx.x;
+      float* aux = sAux + buf * 3 * BT;
+      aux[threadIdx.x] = m < M ? lse[(size_t)h * M + m] * LOG2E : 0.f;
+      aux[BT + threadIdx.x] = m < M ? delta[(size_t)h * M + m] : 0.f;
+      ((int*)aux)[2 * BT + threadIdx.x] = m < M ? seq_start[m] : 0x7fffffff;
+    }
+  };
+  if (n_work > 0) prefetch(0, 0);
+  cp_async_commit();
+  for (int idx = 0; idx < n_work; ++idx) {
+    {
+      const int m0 = n0 + (idx % nqt) * BT;
+      const int buf = idx & 1;
+      const uint32_t sQ = sQdO + buf * 2 * BT * HD * 2, sdO = sQ + BT * HD * 2;
+      const float* sLse = sAux + buf * 3 * BT;
+      const float* sDel = sLse + BT;
+      const int* sSS = (const int*)(sLse + 2 * BT);
+      if (idx + 1 < n_work) prefetch(idx + 1, buf ^ 1);
+      cp_async_commit();
+      cp_async_wait_prev();
       __syncthreads();
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
@@ -339,6 +366,7 @@ attn_bwd_dkdv_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
           }
         }
       }
+      __syncthreads();  // done with this (Q, dO) buffer before the next prefetch reuses it
     }
   }
   const float sc = do_scale[0];
@@ -364,7 +392,7 @@ attn_bwd_dq_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
                    const float* __restrict__ delta, const int* __restrict__ seq_start, int M, int nh, int nkv,
                    float scale, float* __restrict__ dq) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const uint32_t sQ = smem_addr(smem), sdO = sQ + BT * HD * 2, sK = sdO + BT * HD * 2, sV = sK + BT * HD * 2;
+  const uint32_t sQ = smem_addr(smem), sdO = sQ + BT * HD * 2, sKV = sdO + BT * HD * 2;  // then two (K, V) buffers
   const int m0 = blockIdx.x * BT, h = blockIdx.y, g = h / (nh / nkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
   const float sl2 = scale * LOG2E;
@@ -379,11 +407,19 @@ attn_bwd_dq_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
   for (int i = 0; i < HD / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   const int kbeg = (seq_start[m0] / BT) * BT;
   const int kend = min(m0 + BT, M);
-  for (int n0 = kbeg; n0 < kend; n0 += BT) {
-    __syncthreads();
-    load_tile<HD>(sK, k, n0, M, nkv, g);
-    load_tile<HD>(sV, v, n0, M, nkv, g);
-    cp_async_wait_all();
+  load_tile<HD>(sKV, k, kbeg, M, nkv, g);
+  load_tile<HD>(sKV + BT * HD * 2, v, kbeg, M, nkv, g);
+  cp_async_commit();
+  int it = 0;
+  for (int n0 = kbeg; n0 < kend; n0 += BT, ++it) {
+    const uint32_t sK = sKV + (it & 1) * 2 * BT * HD * 2, sV = sK + BT * HD * 2;
+    if (n0 + BT < kend) {
+      const uint32_t nK = sKV + ((it & 1) ^ 1) * 2 * BT * HD * 2;
+      load_tile<HD>(nK, k, n0 + BT, M, nkv, g);
+      load_tile<HD>(nK + BT * HD * 2, v, n0 + BT, M, nkv, g);
+    }
+    cp_async_commit();
+    cp_async_wait_prev();
     __syncthreads();
 #pragma unroll 1
     for (int half = 0; half < 2; ++half) {
@@ -434,6 +470,7 @@ attn_bwd_dq_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
         }
       }
     }
+    __syncthreads();
   }
   const float sc = do_scale[0];
 #pragma unroll
@@ -447,7 +484,7 @@ attn_bwd_dq_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
 template <int HD>
 int fwd_impl(const __half* q, const __half* k, const __half* v, const int* seq_start, int M, int nh, int nkv,
              __half* o, float* lse, cudaStream_t st) {
-  const size_t smem = 3 * BT * HD * 2;
+  const size_t smem = 5 * BT * HD * 2;
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 3;
@@ -462,7 +499,7 @@ template <int HD>
 int bwd_impl(const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO,
              const float* do_scale, const float* lse, const int* seq_start, int M, int nh, int nkv, float* delta,
              float* dq, float* dk, float* dv, cudaStream_t st) {
-  const size_t smem_kv = 4 * BT * HD * 2 + 3 * BT * 4, smem_q = 4 * BT * HD * 2;
+  const size_t smem_kv = 6 * BT * HD * 2 + 2 * 3 * BT * 4, smem_q = 6 * BT * HD * 2;
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(attn_bwd_dkdv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv) != cudaSuccess) return 3;

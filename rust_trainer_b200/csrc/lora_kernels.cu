@@ -53,37 +53,50 @@ __device__ __forceinline__ void load64x64(uint32_t sbase, const __half* g, int r
 
 // ------------------------------------------------------------------ Hs = X . Wt^T
 template <int R16>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(64)
 skinny_nt_kernel(const __half* __restrict__ X, const __half* __restrict__ Wt, int M, int K, int r, __half* __restrict__ out) {
-  __shared__ __align__(128) uint8_t smem[2 * 8192 + 2 * 8192];
-  const uint32_t sX = saddr(smem), sW = sX + 2 * 8192;
-  const int m0 = blockIdx.x * 64;
+  constexpr int NST = 4;                       // stages in flight: the kernel is pure memory latency
+  constexpr int XB = 32 * 128, WB = 16 * R16 * 128, SB = XB + WB;
+  __shared__ __align__(128) uint8_t smem[NST * SB];
+  const uint32_t s0 = saddr(smem);
+  const int m0 = blockIdx.x * 32;  // two warps, 16 token rows each: many small CTAs keep every SM busy
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
   const int mat = lane >> 3, rr = lane & 7;
   float acc[2 * R16][4];
 #pragma unroll
   for (int i = 0; i < 2 * R16; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   const int nk = (K + 63) / 64;
-  load64x64(sX, X, m0, M, 0, K, K);
-  load64x64(sW, Wt, 0, r, 0, K, K, 16 * R16);
-  cpa_commit();
-  for (int kc = 0; kc < nk; ++kc) {
-    const int b = kc & 1;
-    if (kc + 1 < nk) {
-      load64x64(sX + (b ^ 1) * 8192, X, m0, M, (kc + 1) * 64, K, K);
-      load64x64(sW + (b ^ 1) * 8192, Wt, 0, r, (kc + 1) * 64, K, K, 16 * R16);
+  auto load = [&](int kc) {
+    const uint32_t sx = s0 + (kc % NST) * SB, sw = sx + XB;
+    for (int e = threadIdx.x; e < 32 * 8; e += 64) {
+      const int rw = e >> 3, c = e & 7, gr = m0 + rw, gc = kc * 64 + c * 8;
+      const bool ok = gr < M && gc < K;
+      cpa16(sx + toff(rw, c), X + (size_t)(ok ? gr : 0) * K + (ok ? gc : 0), ok);
     }
+    for (int e = threadIdx.x; e < 16 * R16 * 8; e += 64) {
+      const int rw = e >> 3, c = e & 7, gc = kc * 64 + c * 8;
+      const bool ok = rw < r && gc < K;
+      cpa16(sw + toff(rw, c), Wt + (size_t)(ok ? rw : 0) * K + (ok ? gc : 0), ok);
+    }
+  };
+  for (int i = 0; i < NST - 1; ++i) {
+    if (i < nk) load(i);
     cpa_commit();
-    cpa_wait<1>();
+  }
+  for (int kc = 0; kc < nk; ++kc) {
+    if (kc + NST - 1 < nk) load(kc + NST - 1);
+    cpa_commit();
+    cpa_wait<NST - 1>();
     __syncthreads();
+    const uint32_t sx = s0 + (kc % NST) * SB, sw = sx + XB;
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
       uint32_t a[4];
-      ldsm4(sX + b * 8192 + toff(warp * 16 + (mat & 1) * 8 + rr, kk * 2 + (mat >> 1)), a);
+      ldsm4(sx + toff(warp * 16 + (mat & 1) * 8 + rr, kk * 2 + (mat >> 1)), a);
 #pragma unroll
       for (int np = 0; np < R16; ++np) {
         uint32_t bf[4];
-        ldsm4(sW + b * 8192 + toff(np * 16 + (mat >> 1) * 8 + rr, kk * 2 + (mat & 1)), bf);
+        ldsm4(sw + toff(np * 16 + (mat >> 1) * 8 + rr, kk * 2 + (mat & 1)), bf);
         mma(acc[2 * np], a, bf);
         mma(acc[2 * np + 1], a, bf + 2);
       }
@@ -94,7 +107,7 @@ skinny_nt_kernel(const __half* __restrict__ X, const __half* __restrict__ Wt, in
 #pragma unroll
   for (int nt = 0; nt < 2 * R16; ++nt) {
     const int c = nt * 8 + 2 * tq;
-    if (c < r) {  // r is even (a multiple of 2 is enough for the paired store; ranks are)
+    if (c < r) {  // r is even, so the paired store never straddles the rank
       if (i0 < M) *(__half2*)(out + (size_t)i0 * 64 + c) = __floats2half2_rn(acc[nt][0], acc[nt][1]);
       if (i1 < M) *(__half2*)(out + (size_t)i1 * 64 + c) = __floats2half2_rn(acc[nt][2], acc[nt][3]);
     }
@@ -104,10 +117,11 @@ skinny_nt_kernel(const __half* __restrict__ X, const __half* __restrict__ Wt, in
 // ------------------------------------------------------------------ part[split] = P^T . Q over a token range
 template <int R16>
 __global__ void __launch_bounds__(128)
-tok_contract_kernel(const __half* __restrict__ P, const __half* __restrict__ Q, int M, int C, int r, int tokens_per_split,
-                    float* __restrict__ part) {
-  __shared__ __align__(128) uint8_t smem[2 * 8192 + 2 * 16384];
-  const uint32_t sP = saddr(smem), sQ = sP + 2 * 8192;
+tok_contract_kernel(const __half* __restrict__ P, const __half* __restrict__ Q, const float* __restrict__ pscale,
+                    const float* __restrict__ smax, int M, int C, int r, int tokens_per_split, float* __restrict__ part) {
+  constexpr int NST = 3, SB = 8192 + 16384;  // per stage: P chunk, two Q panels
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t s0 = saddr(smem);
   const int j0 = blockIdx.x * 128;
   const int m_begin = blockIdx.y * tokens_per_split, m_end = min(M, m_begin + tokens_per_split);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
@@ -121,19 +135,40 @@ tok_contract_kernel(const __half* __restrict__ P, const __half* __restrict__ Q, 
   const int nchunks = (m_end - m_begin + 63) / 64;
   auto load = [&](int ch, int buf) {
     const int mrow = m_begin + ch * 64;
-    load64x64(sP + buf * 8192, P, mrow, m_end, 0, 64, 64);
-    load64x64(sQ + buf * 16384, Q, mrow, m_end, j0, C, C);
-    load64x64(sQ + buf * 16384 + 8192, Q, mrow, m_end, j0 + 64, C, C);
+    load64x64(s0 + buf * SB, P, mrow, m_end, 0, 64, 64);
+    load64x64(s0 + buf * SB + 8192, Q, mrow, m_end, j0, C, C);
+    load64x64(s0 + buf * SB + 16384, Q, mrow, m_end, j0 + 64, C, C);
   };
-  if (nchunks > 0) load(0, 0);
-  cpa_commit();
-  for (int ch = 0; ch < nchunks; ++ch) {
-    const int b = ch & 1;
-    if (ch + 1 < nchunks) load(ch + 1, b ^ 1);
+  for (int i = 0; i < NST - 1; ++i) {
+    if (i < nchunks) load(i, i);
     cpa_commit();
-    cpa_wait<1>();
+  }
+  for (int ch = 0; ch < nchunks; ++ch) {
+    const int b = ch % NST;
+    if (ch + NST - 1 < nchunks) load(ch + NST - 1, (ch + NST - 1) % NST);
+    cpa_commit();
+    cpa_wait<NST - 1>();
     __syncthreads();
-    const uint32_t q = sQ + b * 16384 + panel * 8192;
+    const uint32_t sP = s0 + b * SB;
+    if (pscale) {
+      // rows of P times scale[m] / max(scale): the per-token factors of dY, normalised so f16 holds them
+      const float inv = 1.0f / smax[0];
+      for (int e = threadIdx.x; e < 64 * 8; e += blockDim.x) {
+        const int row = e >> 3, c = e & 7, mrow = m_begin + ch * 64 + row;
+        const float f = mrow < m_end ? pscale[mrow] * inv : 0.f;
+        uint4* ptr = (uint4*)(smem + b * SB + toff(row, c));
+        uint4 v = *ptr;
+        __half2* h2 = (__half2*)&v;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 x = __half22float2(h2[k]);
+          h2[k] = __floats2half2_rn(x.x * f, x.y * f);
+        }
+        *ptr = v;
+      }
+      __syncthreads();
+    }
+    const uint32_t q = sP + 8192 + panel * 8192;
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
       uint32_t bf[2][4];
@@ -142,7 +177,7 @@ tok_contract_kernel(const __half* __restrict__ P, const __half* __restrict__ Q, 
 #pragma unroll
       for (int mi = 0; mi < R16; ++mi) {
         uint32_t a[4];  // A = P^T: rows i, k = tokens; P is stored [token][i]
-        ldsm4t(sP + b * 8192 + toff(kk * 16 + (mat >> 1) * 8 + rr, mi * 2 + (mat & 1)), a);
+        ldsm4t(sP + toff(kk * 16 + (mat >> 1) * 8 + rr, mi * 2 + (mat & 1)), a);
 #pragma unroll
         for (int np = 0; np < 2; ++np) {
           mma(acc[mi][2 * np], a, bf[np]);
@@ -183,17 +218,17 @@ __global__ void tok_reduce_kernel(const float* __restrict__ part, int splits, in
 int launch_skinny_nt(const __half* X, const __half* Wt, int M, int K, int r, __half* out, cudaStream_t st) {
   if (M <= 0) return 0;
   if (r <= 0 || r > 64 || (r & 1) || K % 8 != 0) return 1;
-  const int grid = (M + 63) / 64;
-  if (r <= 16) skinny_nt_kernel<1><<<grid, 128, 0, st>>>(X, Wt, M, K, r, out);
-  else if (r <= 32) skinny_nt_kernel<2><<<grid, 128, 0, st>>>(X, Wt, M, K, r, out);
-  else skinny_nt_kernel<4><<<grid, 128, 0, st>>>(X, Wt, M, K, r, out);
+  const int grid = (M + 31) / 32;
+  if (r <= 16) skinny_nt_kernel<1><<<grid, 64, 0, st>>>(X, Wt, M, K, r, out);
+  else if (r <= 32) skinny_nt_kernel<2><<<grid, 64, 0, st>>>(X, Wt, M, K, r, out);
+  else skinny_nt_kernel<4><<<grid, 64, 0, st>>>(X, Wt, M, K, r, out);
   RT_COUNT_LAUNCH(1);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
 static void tok_plan(int M, int* tokens_per_split, int* splits) {
-  int tps = 512;
-  if (M < 2048) tps = 256;
+  int tps = 256;
+  if (M < 1024) tps = 128;
   if (M < 512) tps = 64;
   *tokens_per_split = tps;
   *splits = (M + tps - 1) / tps;
@@ -203,16 +238,24 @@ size_t tok_contract_workspace_floats(int M, int C, int r) {
   tok_plan(M, &tps, &splits);
   return (size_t)splits * r * C;
 }
-int launch_tok_contract(const __half* P, const __half* Q, int M, int C, int r, size_t so_i, size_t so_j,
+int launch_tok_contract(const __half* P, const __half* Q, const float* pscale, int M, int C, int r, size_t so_i, size_t so_j,
                         const float* alpha_dev, float* out, float* workspace, cudaStream_t st) {
   if (M <= 0) return 0;
   if (r <= 0 || r > 64 || C % 8 != 0) return 1;
   int tps, splits;
   tok_plan(M, &tps, &splits);
   dim3 grid((C + 127) / 128, splits);
-  if (r <= 16) tok_contract_kernel<1><<<grid, 128, 0, st>>>(P, Q, M, C, r, tps, workspace);
-  else if (r <= 32) tok_contract_kernel<2><<<grid, 128, 0, st>>>(P, Q, M, C, r, tps, workspace);
-  else tok_contract_kernel<4><<<grid, 128, 0, st>>>(P, Q, M, C, r, tps, workspace);
+  constexpr int TOK_SMEM = 3 * (8192 + 16384);
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(tok_contract_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TOK_SMEM);
+    cudaFuncSetAttribute(tok_contract_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TOK_SMEM);
+    cudaFuncSetAttribute(tok_contract_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, TOK_SMEM);
+    attr = true;
+  }
+  if (r <= 16) tok_contract_kernel<1><<<grid, 128, TOK_SMEM, st>>>(P, Q, pscale, alpha_dev, M, C, r, tps, workspace);
+  else if (r <= 32) tok_contract_kernel<2><<<grid, 128, TOK_SMEM, st>>>(P, Q, pscale, alpha_dev, M, C, r, tps, workspace);
+  else tok_contract_kernel<4><<<grid, 128, TOK_SMEM, st>>>(P, Q, pscale, alpha_dev, M, C, r, tps, workspace);
   const size_t n = (size_t)r * C;
   tok_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(workspace, splits, C, r, so_i, so_j, alpha_dev, out);
   RT_COUNT_LAUNCH(2);

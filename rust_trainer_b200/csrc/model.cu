@@ -157,21 +157,24 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
     const __half *hs_c = hs, *gs_c = gs;
     const float* alpha = nullptr;
     if (dscale) {
-      __half* hs2 = lowrank_buf(c, sc.hs2, sc.hs2_rank, M, r);
-      __half* gs2 = lowrank_buf(c, sc.gs2, sc.gs2_rank, M, r);
-      if (!hs2 || !gs2 || !sc.smax.reserve(16)) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+      if (!sc.smax.reserve(16)) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
       launch_rowscale_max(dscale, M, sc.smax.as<float>(), c->stream);
-      launch_scale_lowrank_rows(hs, dscale, sc.smax.as<float>(), M, hs2, c->stream);
-      launch_scale_lowrank_rows(gs, dscale, sc.smax.as<float>(), M, gs2, c->stream);
-      hs_c = hs2;
-      gs_c = gs2;
       alpha = sc.smax.as<float>();
     }
     const size_t wsf = tok_contract_workspace_floats(M, K > N ? K : N, r);
     if (!sc.grad_ws.reserve(wsf * sizeof(float))) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
-    const int rb = launch_tok_contract(hs_c, dy16, M, N, r, 1, (size_t)r, alpha, l->lora.gb, sc.grad_ws.as<float>(), c->stream);
-    const int ra = launch_tok_contract(gs_c, x16, M, K, r, (size_t)K, 1, alpha, l->lora.ga, sc.grad_ws.as<float>(), c->stream);
+    const int rb = launch_tok_contract(hs, dy16, dscale, M, N, r, 1, (size_t)r, alpha, l->lora.gb, sc.grad_ws.as<float>(), c->stream);
+    const int ra = launch_tok_contract(gs, x16, dscale, M, K, r, (size_t)K, 1, alpha, l->lora.ga, sc.grad_ws.as<float>(), c->stream);
     if (rb > 1 || ra > 1) return c->fail(RT_ERR_CUDA, "lora gradient kernel launch failed");
+    if (dscale && (rb == 1 || ra == 1)) {  // general shapes go through the big kernel and need scaled copies
+      __half* hs2 = lowrank_buf(c, sc.hs2, sc.hs2_rank, M, r);
+      __half* gs2 = lowrank_buf(c, sc.gs2, sc.gs2_rank, M, r);
+      if (!hs2 || !gs2) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+      launch_scale_lowrank_rows(hs, dscale, sc.smax.as<float>(), M, hs2, c->stream);
+      launch_scale_lowrank_rows(gs, dscale, sc.smax.as<float>(), M, gs2, c->stream);
+      hs_c = hs2;
+      gs_c = gs2;
+    }
     QGemmArgs ta;
     ta.dir = QG_BWD;
     ta.tok_mode = 1;

@@ -125,6 +125,22 @@ __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __r
   const size_t r = blockIdx.x;
   const float* xr = x + r * d;
   float ss = 0.f;
+  if ((d & 3) == 0) {
+    const float4* x4 = (const float4*)xr;
+    const float4* w4 = (const float4*)w;
+    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+      const float4 v = x4[i];
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = block_sum(ss);
+    const float ir = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+      const float4 v = x4[i], g = w4[i];
+      __half2 a = __floats2half2_rn(v.x * ir * g.x, v.y * ir * g.y), b = __floats2half2_rn(v.z * ir * g.z, v.w * ir * g.w);
+      *(uint2*)(y16 + r * d + 4 * i) = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < d; i += blockDim.x) ss += xr[i] * xr[i];
   ss = block_sum(ss);
   const float ir = 1.0f / sqrtf(ss / (float)d + eps);
@@ -142,7 +158,40 @@ __global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __r
   const size_t r = blockIdx.x;
   const float* xr = x + r * d;
   const float* dnr = dn + r * d;
-  float ss = 0.f, gx = 0.f;
+  float ss = 0.f, gx = 0.f, m = 0.f;
+  if ((d & 3) == 0) {
+    const float4 *x4 = (const float4*)xr, *d4 = (const float4*)dnr, *w4 = (const float4*)w;
+    const float4* r4 = dres ? (const float4*)(dres + r * d) : nullptr;
+    float4* o4 = (float4*)(out + r * d);
+    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+      const float4 xv = x4[i], dv = d4[i], wv = w4[i];
+      ss += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
+      gx += dv.x * wv.x * xv.x + dv.y * wv.y * xv.y + dv.z * wv.z * xv.z + dv.w * wv.w * xv.w;
+    }
+    ss = block_sum(ss);
+    gx = block_sum(gx);
+    const float ir = 1.0f / sqrtf(ss / (float)d + eps);
+    const float c = gx * ir * ir * ir / (float)d;
+    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+      const float4 xv = x4[i], dv = d4[i], wv = w4[i];
+      float4 v = make_float4(dv.x * wv.x * ir - xv.x * c, dv.y * wv.y * ir - xv.y * c, dv.z * wv.z * ir - xv.z * c,
+                             dv.w * wv.w * ir - xv.w * c);
+      if (r4) { const float4 q = r4[i]; v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w; }
+      o4[i] = v;
+      m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    if (out16) {
+      m = block_max(m);
+      const float sc = m > 0.f ? m : 1.f, inv = 1.f / sc;
+      for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+        const float4 v = o4[i];  // this thread's own stores
+        __half2 a = __floats2half2_rn(v.x * inv, v.y * inv), b = __floats2half2_rn(v.z * inv, v.w * inv);
+        *(uint2*)(out16 + r * d + 4 * i) = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+      }
+      if (threadIdx.x == 0) scale[r] = sc;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float xv = xr[i];
     ss += xv * xv;
@@ -152,7 +201,6 @@ __global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __r
   gx = block_sum(gx);
   const float ir = 1.0f / sqrtf(ss / (float)d + eps);
   const float c = gx * ir * ir * ir / (float)d;
-  float m = 0.f;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = dnr[i] * w[i] * ir - xr[i] * c;
     if (dres) v += dres[r * d + i];
@@ -161,9 +209,9 @@ __global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __r
   }
   if (out16) {
     m = block_max(m);  // includes a __syncthreads: this thread's stores above are its own re-reads below
-    const float s = m > 0.f ? m : 1.f, inv = 1.f / s;
+    const float sc = m > 0.f ? m : 1.f, inv = 1.f / sc;
     for (int i = threadIdx.x; i < d; i += blockDim.x) out16[r * d + i] = __float2half_rn(out[r * d + i] * inv);
-    if (threadIdx.x == 0) scale[r] = s;
+    if (threadIdx.x == 0) scale[r] = sc;
   }
 }
 void launch_rmsnorm_bwd(const float* x, const float* w, const float* dn, const float* dres, int rows, int d, float eps,
@@ -199,12 +247,18 @@ __global__ void qk_rope_fwd_kernel(const float* __restrict__ q_raw, const float*
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int half = rot / 2;
   const int p = pos[m];
+  const float* csr = cs + (size_t)p * half;
+  const float* snr = sn + (size_t)p * half;
   for (int h = warp; h < nh + 2 * nkv; h += nwarps) {
     if (h >= nh + nkv) {
       const int hv = h - nh - nkv;
       const float* src = v_raw + (m * nkv + hv) * hd;
       __half* dst = v16 + (m * nkv + hv) * hd;
-      for (int i = lane; i < hd; i += 32) dst[i] = __float2half_rn(src[i]);
+      for (int i = lane * 4; i < hd; i += 128) {
+        const float4 v = *(const float4*)(src + i);
+        __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+        *(uint2*)(dst + i) = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+      }
       continue;
     }
     const bool is_q = h < nh;
@@ -214,18 +268,34 @@ __global__ void qk_rope_fwd_kernel(const float* __restrict__ q_raw, const float*
     float ir = 1.f;
     if (nw) {
       float ss = 0.f;
-      for (int i = lane; i < hd; i += 32) ss += src[i] * src[i];
+      for (int i = lane * 4; i < hd; i += 128) {
+        const float4 v = *(const float4*)(src + i);
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
       ss = warp_sum(ss);
       ir = 1.0f / sqrtf(ss / (float)hd + eps);
     }
-    // rotate pairs; elements beyond rot pass through
-    for (int i = lane; i < half; i += 32) {
-      const int a = neox ? i : 2 * i, b = neox ? i + half : 2 * i + 1;
-      float x1 = src[a], x2 = src[b];
-      if (nw) { x1 = x1 * (ir * nw[a]); x2 = x2 * (ir * nw[b]); }
-      const float c = cs[(size_t)p * half + i], s = sn[(size_t)p * half + i];
-      dst[a] = __float2half_rn(x1 * c - x2 * s);
-      dst[b] = __float2half_rn(x2 * c + x1 * s);
+    // two rotation pairs per lane and round; elements beyond rot pass through
+    for (int i = lane * 2; i < half; i += 64) {
+      const float2 c = *(const float2*)(csr + i), s = *(const float2*)(snr + i);
+      if (neox) {
+        float2 x1 = *(const float2*)(src + i), x2 = *(const float2*)(src + i + half);
+        if (nw) {
+          const float2 w1 = *(const float2*)(nw + i), w2 = *(const float2*)(nw + i + half);
+          x1.x *= ir * w1.x; x1.y *= ir * w1.y; x2.x *= ir * w2.x; x2.y *= ir * w2.y;
+        }
+        *(__half2*)(dst + i) = __floats2half2_rn(x1.x * c.x - x2.x * s.x, x1.y * c.y - x2.y * s.y);
+        *(__half2*)(dst + i + half) = __floats2half2_rn(x2.x * c.x + x1.x * s.x, x2.y * c.y + x1.y * s.y);
+      } else {
+        float4 x = *(const float4*)(src + 2 * i);  // pairs (2i, 2i+1), (2i+2, 2i+3)
+        if (nw) {
+          const float4 w4 = *(const float4*)(nw + 2 * i);
+          x.x *= ir * w4.x; x.y *= ir * w4.y; x.z *= ir * w4.z; x.w *= ir * w4.w;
+        }
+        __half2 a = __floats2half2_rn(x.x * c.x - x.y * s.x, x.y * c.x + x.x * s.x);
+        __half2 b = __floats2half2_rn(x.z * c.y - x.w * s.y, x.w * c.y + x.z * s.y);
+        *(uint2*)(dst + 2 * i) = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+      }
     }
     for (int i = rot + lane; i < hd; i += 32) {
       float x = src[i];
@@ -252,46 +322,70 @@ __global__ void qk_rope_bwd_kernel(const float* __restrict__ dq, const float* __
                                    int rot, int neox, float eps, __half* __restrict__ dq16, __half* __restrict__ dk16,
                                    __half* __restrict__ dv16, float* __restrict__ sq, float* __restrict__ sk,
                                    float* __restrict__ sv) {
-  extern __shared__ float buf[];  // [q heads | k heads | v heads] of this token, f32 results
+  extern __shared__ __align__(16) float buf[];  // [q heads | k heads | v heads] of this token, f32 results
   __shared__ float wmax[3][32];
   const size_t m = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int half = rot / 2;
   const int p = pos[m];
+  const float* csr = cs + (size_t)p * half;
+  const float* snr = sn + (size_t)p * half;
   float mx[3] = {0.f, 0.f, 0.f};
   for (int h = warp; h < nh + 2 * nkv; h += nwarps) {
     float* out = buf + (size_t)h * hd;
     if (h >= nh + nkv) {
       const float* src = dv + (m * nkv + (h - nh - nkv)) * hd;
-      for (int i = lane; i < hd; i += 32) { float v = src[i]; out[i] = v; mx[2] = fmaxf(mx[2], fabsf(v)); }
+      for (int i = lane * 4; i < hd; i += 128) {
+        const float4 v = *(const float4*)(src + i);
+        *(float4*)(out + i) = v;
+        mx[2] = fmaxf(mx[2], fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+      }
       continue;
     }
     const bool is_q = h < nh;
     const float* g = is_q ? dq + (m * nh + h) * hd : dk + (m * nkv + (h - nh)) * hd;
     const float* xr = is_q ? q_raw + (m * nh + h) * hd : k_raw + (m * nkv + (h - nh)) * hd;
     const float* nw = is_q ? qw : kw;
-    // inverse rotation into shared memory
-    for (int i = lane; i < half; i += 32) {
-      const int a = neox ? i : 2 * i, b = neox ? i + half : 2 * i + 1;
-      const float c = cs[(size_t)p * half + i], s = -sn[(size_t)p * half + i];
-      const float x1 = g[a], x2 = g[b];
-      out[a] = x1 * c - x2 * s;
-      out[b] = x2 * c + x1 * s;
+    // inverse rotation (sin negated) into shared memory
+    for (int i = lane * 2; i < half; i += 64) {
+      const float2 c = *(const float2*)(csr + i), s = *(const float2*)(snr + i);
+      if (neox) {
+        const float2 x1 = *(const float2*)(g + i), x2 = *(const float2*)(g + i + half);
+        *(float2*)(out + i) = make_float2(x1.x * c.x + x2.x * s.x, x1.y * c.y + x2.y * s.y);
+        *(float2*)(out + i + half) = make_float2(x2.x * c.x - x1.x * s.x, x2.y * c.y - x1.y * s.y);
+      } else {
+        const float4 x = *(const float4*)(g + 2 * i);
+        *(float4*)(out + 2 * i) = make_float4(x.x * c.x + x.y * s.x, x.y * c.x - x.x * s.x, x.z * c.y + x.w * s.y,
+                                              x.w * c.y - x.z * s.y);
+      }
     }
     for (int i = rot + lane; i < hd; i += 32) out[i] = g[i];
     __syncwarp();
+    float mm = 0.f;
     if (nw) {
       float ss = 0.f, gx = 0.f;
-      for (int i = lane; i < hd; i += 32) { float xv = xr[i]; ss += xv * xv; gx += out[i] * nw[i] * xv; }
+      for (int i = lane * 4; i < hd; i += 128) {
+        const float4 xv = *(const float4*)(xr + i), ov = *(const float4*)(out + i), wv = *(const float4*)(nw + i);
+        ss += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
+        gx += ov.x * wv.x * xv.x + ov.y * wv.y * xv.y + ov.z * wv.z * xv.z + ov.w * wv.w * xv.w;
+      }
       ss = warp_sum(ss);
       gx = warp_sum(gx);
       const float ir = 1.0f / sqrtf(ss / (float)hd + eps);
       const float c = gx * ir * ir * ir / (float)hd;
-      for (int i = lane; i < hd; i += 32) out[i] = out[i] * nw[i] * ir - xr[i] * c;
+      for (int i = lane * 4; i < hd; i += 128) {
+        const float4 xv = *(const float4*)(xr + i), ov = *(const float4*)(out + i), wv = *(const float4*)(nw + i);
+        const float4 v = make_float4(ov.x * wv.x * ir - xv.x * c, ov.y * wv.y * ir - xv.y * c, ov.z * wv.z * ir - xv.z * c,
+                                     ov.w * wv.w * ir - xv.w * c);
+        *(float4*)(out + i) = v;
+        mm = fmaxf(mm, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+      }
+    } else {
+      for (int i = lane * 4; i < hd; i += 128) {
+        const float4 v = *(const float4*)(out + i);
+        mm = fmaxf(mm, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+      }
     }
-    __syncwarp();
-    float mm = 0.f;
-    for (int i = lane; i < hd; i += 32) mm = fmaxf(mm, fabsf(out[i]));
     mx[is_q ? 0 : 1] = fmaxf(mx[is_q ? 0 : 1], mm);
   }
   for (int k = 0; k < 3; ++k) {
@@ -307,9 +401,14 @@ __global__ void qk_rope_bwd_kernel(const float* __restrict__ dq, const float* __
   }
   if (threadIdx.x == 0) { sq[m] = s3[0]; sk[m] = s3[1]; sv[m] = s3[2]; }
   const int nq = nh * hd, nk = nkv * hd;
-  for (int i = threadIdx.x; i < nq; i += blockDim.x) dq16[m * nq + i] = __float2half_rn(buf[i] / s3[0]);
-  for (int i = threadIdx.x; i < nk; i += blockDim.x) dk16[m * nk + i] = __float2half_rn(buf[nq + i] / s3[1]);
-  for (int i = threadIdx.x; i < nk; i += blockDim.x) dv16[m * nk + i] = __float2half_rn(buf[nq + nk + i] / s3[2]);
+  const float i0 = 1.f / s3[0], i1 = 1.f / s3[1], i2 = 1.f / s3[2];
+  for (int i = threadIdx.x * 4; i < nq + 2 * nk; i += blockDim.x * 4) {  // nq, nk are multiples of 4
+    const float4 v = *(const float4*)(buf + i);
+    const float inv = i < nq ? i0 : (i < nq + nk ? i1 : i2);
+    __half* dst = i < nq ? dq16 + m * nq + i : (i < nq + nk ? dk16 + m * nk + (i - nq) : dv16 + m * nk + (i - nq - nk));
+    __half2 a = __floats2half2_rn(v.x * inv, v.y * inv), b = __floats2half2_rn(v.z * inv, v.w * inv);
+    *(uint2*)dst = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+  }
 }
 void launch_qk_rope_bwd(const float* dq, const float* dk, const float* dv, const float* q_raw, const float* k_raw,
                         const float* qw, const float* kw, const int* pos, const float* cs, const float* sn, int M, int nh,
@@ -330,20 +429,87 @@ __device__ __forceinline__ float sigmoid_f(float x) {
 }
 __global__ void swiglu_fwd_kernel(const __half* __restrict__ g, const __half* __restrict__ u, __half* __restrict__ h,
                                   size_t n) {
-  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
-  if (i + 1 < n) {
-    float2 gv = __half22float2(*(const __half2*)(g + i)), uv = __half22float2(*(const __half2*)(u + i));
-    *(__half2*)(h + i) = __floats2half2_rn(silu_f(gv.x) * uv.x, silu_f(gv.y) * uv.y);
-  } else if (i < n) {
-    h[i] = __float2half_rn(silu_f(__half2float(g[i])) * __half2float(u[i]));
+  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i + 7 < n) {
+    const uint4 gv = *(const uint4*)(g + i), uv = *(const uint4*)(u + i);
+    const __half2* g2 = (const __half2*)&gv;
+    const __half2* u2 = (const __half2*)&uv;
+    uint4 o;
+    __half2* o2 = (__half2*)&o;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = __half22float2(g2[k]), b = __half22float2(u2[k]);
+      o2[k] = __floats2half2_rn(__fdividef(a.x, 1.0f + __expf(-a.x)) * b.x, __fdividef(a.y, 1.0f + __expf(-a.y)) * b.y);
+    }
+    *(uint4*)(h + i) = o;
+  } else {
+    for (; i < n; ++i) h[i] = __float2half_rn(silu_f(__half2float(g[i])) * __half2float(u[i]));
   }
 }
 void launch_swiglu_fwd(const __half* g, const __half* u, __half* h, size_t n, cudaStream_t st) {
   if (n == 0) return;
-  size_t threads = (n + 1) / 2;
+  size_t threads = (n + 7) / 8;
   { swiglu_fwd_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(g, u, h, n); RT_COUNT_LAUNCH(1); }
 }
 // dg = dh*u*silu'(g), du = dh*silu(g); both written row-normalised in f16 with per-row scales.
+// The kernel is bound by the exp/divide per element, so sigma is computed once per element with
+// the fast intrinsics (2 ulp, far inside the f16 rounding that follows) and the products are
+// kept in registers between the max pass and the write pass.
+__device__ __forceinline__ void swiglu_grad8(const float* dh, const __half* g, const __half* u, float* dg, float* du) {
+  const float4 d0 = *(const float4*)dh, d1 = *(const float4*)(dh + 4);
+  const uint4 gv = *(const uint4*)g, uv = *(const uint4*)u;
+  const __half2* g2 = (const __half2*)&gv;
+  const __half2* u2 = (const __half2*)&uv;
+  const float d[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 a = __half22float2(g2[k]), b = __half22float2(u2[k]);
+    const float s0 = __fdividef(1.0f, 1.0f + __expf(-a.x)), s1 = __fdividef(1.0f, 1.0f + __expf(-a.y));
+    dg[2 * k] = d[2 * k] * b.x * (s0 * (1.0f + a.x * (1.0f - s0)));
+    dg[2 * k + 1] = d[2 * k + 1] * b.y * (s1 * (1.0f + a.y * (1.0f - s1)));
+    du[2 * k] = d[2 * k] * (a.x * s0);
+    du[2 * k + 1] = d[2 * k + 1] * (a.y * s1);
+  }
+}
+template <int NCH>  // 8-element chunks cached per thread: ff <= NCH * 8 * blockDim.x, ff % 8 == 0
+__global__ void swiglu_bwd_cached_kernel(const float* __restrict__ dh, const __half* __restrict__ g,
+                                         const __half* __restrict__ u, int ff, __half* __restrict__ dg16,
+                                         __half* __restrict__ du16, float* __restrict__ sg, float* __restrict__ su) {
+  const size_t r = blockIdx.x;
+  float a[NCH][8], b[NCH][8];
+  float mg = 0.f, mu = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 8;
+    if (i < ff) {
+      swiglu_grad8(dh + r * ff + i, g + r * ff + i, u + r * ff + i, a[c], b[c]);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { mg = fmaxf(mg, fabsf(a[c][k])); mu = fmaxf(mu, fabsf(b[c][k])); }
+    }
+  }
+  mg = block_max(mg);
+  mu = block_max(mu);
+  const float s_g = mg > 0.f ? mg : 1.f, s_u = mu > 0.f ? mu : 1.f;
+  const float ig = 1.f / s_g, iu = 1.f / s_u;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 8;
+    if (i < ff) {
+      uint4 oa, ob;
+      __half2* pa = (__half2*)&oa;
+      __half2* pb = (__half2*)&ob;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        pa[k] = __floats2half2_rn(a[c][2 * k] * ig, a[c][2 * k + 1] * ig);
+        pb[k] = __floats2half2_rn(b[c][2 * k] * iu, b[c][2 * k + 1] * iu);
+      }
+      *(uint4*)(dg16 + r * ff + i) = oa;
+      *(uint4*)(du16 + r * ff + i) = ob;
+    }
+  }
+  if (threadIdx.x == 0) { sg[r] = s_g; su[r] = s_u; }
+}
+// general row length: scalar, recomputed in the second pass
 __global__ void swiglu_bwd_kernel(const float* __restrict__ dh, const __half* __restrict__ g,
                                   const __half* __restrict__ u, int ff, __half* __restrict__ dg16,
                                   __half* __restrict__ du16, float* __restrict__ sg, float* __restrict__ su) {
@@ -372,7 +538,10 @@ __global__ void swiglu_bwd_kernel(const float* __restrict__ dh, const __half* __
 }
 void launch_swiglu_bwd(const float* dh, const __half* g, const __half* u, int rows, int ff, __half* dg16, __half* du16,
                        float* sg, float* su, cudaStream_t st) {
-  if (rows > 0) { swiglu_bwd_kernel<<<rows, 256, 0, st>>>(dh, g, u, ff, dg16, du16, sg, su); RT_COUNT_LAUNCH(1); }
+  if (rows <= 0) return;
+  if ((ff & 7) == 0 && ff <= 2 * 8 * 256) { swiglu_bwd_cached_kernel<2><<<rows, 256, 0, st>>>(dh, g, u, ff, dg16, du16, sg, su); RT_COUNT_LAUNCH(1); }
+  else if ((ff & 7) == 0 && ff <= 3 * 8 * 512) { swiglu_bwd_cached_kernel<3><<<rows, 512, 0, st>>>(dh, g, u, ff, dg16, du16, sg, su); RT_COUNT_LAUNCH(1); }
+  else { swiglu_bwd_kernel<<<rows, 256, 0, st>>>(dh, g, u, ff, dg16, du16, sg, su); RT_COUNT_LAUNCH(1); }
 }
 
 // ------------------------------------------------------------------ row gather / scatter

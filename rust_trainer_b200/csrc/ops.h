@@ -42,7 +42,8 @@ void launch_global_normalize(const float* x, size_t n, float* amax_dev, __half* 
 // ---- lora_kernels.cu: skinny low-rank products (return 1 when the shape is not supported)
 int launch_skinny_nt(const __half* X, const __half* Wt, int M, int K, int r, __half* out64, cudaStream_t st);
 size_t tok_contract_workspace_floats(int M, int C, int r);
-int launch_tok_contract(const __half* P, const __half* Q, int M, int C, int r, size_t so_i, size_t so_j,
+// pscale (optional): P's rows are multiplied by pscale[m] / alpha_dev[0] on the fly; alpha_dev[0] then scales the result
+int launch_tok_contract(const __half* P, const __half* Q, const float* pscale, int M, int C, int r, size_t so_i, size_t so_j,
                         const float* alpha_dev, float* out, float* workspace, cudaStream_t st);
 
 // ---- attention.cu: causal GQA attention over a concatenation of independent sequences.

@@ -145,7 +145,8 @@ def test_reruns_are_bit_identical_and_batching_is_neutral(ctx):
     for s, (tpl, ttl) in zip(seqs, per_seq):
         lps.append(gm.forward_backward([s], tpl, ttl, w[k:k + tpl.size])[0])
         k += tpl.size
-    assert np.max(np.abs(np.concatenate(lps) - lp1)) < 1e-4
+    # attention tiles fall differently on a sequence that starts mid-tile: f16 roundings of P move
+    assert np.max(np.abs(np.concatenate(lps) - lp1) / np.abs(lp1)) < LOSS_TOL
     assert rel_l2(_gpu_flat(gm, "ga", "gb"), g1) < 2e-3
     gm.close()
     om.close()
