@@ -113,6 +113,24 @@ rt_status rt_frozen_forward_dev(rt_frozen* w, const void* x_dev, int in_dtype, s
                                 int out_dtype, int accumulate);
 rt_status rt_frozen_backward_input_dev(rt_frozen* w, const void* dy_dev, int in_dtype, size_t t, void* dx_dev,
                                        int out_dtype, int accumulate);
+/* The same operation as rt_frozen_backward_input_dev for callers that must not allocate device
+ * memory while they run: a host inside a memory-budgeted serving or training process that has
+ * handed every byte of HBM to its own pool, a real-time loop that cannot take the driver's
+ * allocation lock, or code running where cudaMalloc is simply not permitted.  It has no
+ * counterpart in the reference (the reference never leaves the CPU).  When the contraction is
+ * split over SMs, the partial sums go to a fixed 8 MiB array that is part of the library's
+ * device image (every GPU that loads the library holds it until the process exits) instead of
+ * grow-on-demand scratch; the call makes no cudaMalloc / cudaFree and keeps no descriptor
+ * cache.  Limits and rules:
+ *   - a call whose partial sums need more than 2 Mi floats (splits x t x in_dim) is refused with
+ *     RT_ERR_TOO_LARGE; use fewer rows per call;
+ *   - the FIRST call on a device looks up the array's device address; make that call before
+ *     any stream capture begins;
+ *   - all calls share the one array and it keeps the previous call's contents (nothing in it
+ *     needs to start at zero: every element read was written by the same call); two calls that
+ *     overlap on the GPU (different streams) race on it, so keep them on one stream. */
+rt_status rt_frozen_backward_input_dev_noalloc(rt_frozen* w, const void* dy_dev, int in_dtype, size_t t,
+                                               void* dx_dev, int out_dtype, int accumulate);
 
 /* ------------------------------------------------------------------ level 2: struct Linear / struct Lora
  * src/linear.rs:9-122.  y = W.x + b + (alpha/r).B.A.x forward; dx = W^T.dy + (LoRA term) and

@@ -58,6 +58,7 @@ def _declare(L: C.CDLL) -> None:
         "rt_ctx_set_stream": (i32, [vp, vp]),
         "rt_frozen_forward_dev": (i32, [vp, vp, C.c_int, sz, vp, C.c_int, C.c_int]),
         "rt_frozen_backward_input_dev": (i32, [vp, vp, C.c_int, sz, vp, C.c_int, C.c_int]),
+        "rt_frozen_backward_input_dev_noalloc": (i32, [vp, vp, C.c_int, sz, vp, C.c_int, C.c_int]),
         "rt_ggml_nbytes": (sz, [C.c_int, sz, sz]),
         "rt_frozen_create": (i32, [vp, C.c_int, sz, sz, vp, sz, C.POINTER(vp)]),
         "rt_frozen_destroy": (None, [vp]),

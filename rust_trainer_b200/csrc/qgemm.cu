@@ -536,6 +536,7 @@ std::atomic<unsigned long long> g_launch_count{0};
 
 static int make_map_cached(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
                            uint32_t box_rows, bool is_bf16) {
+  if (!ctx) return encode_map(m, base, rows, cols, box_cols, box_rows, is_bf16);  // no cache: nothing is allocated
   auto key = std::make_tuple(base, rows, cols, box_cols, box_rows, is_bf16);
   auto it = ctx->tmap_cache.find(key);
   if (it != ctx->tmap_cache.end()) {
@@ -548,16 +549,18 @@ static int make_map_cached(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64
   ctx->tmap_cache.emplace(key, *m);
   return RT_OK;
 }
-#define make_map(m, ...) make_map_cached(ctx, m, __VA_ARGS__)
+#define make_map(m, ...) make_map_cached(a.fixed_part ? nullptr : ctx, m, __VA_ARGS__)
 
 // Output matrix [rows x cols] of f32 / bf16 / f16 with a row pitch of `ld` elements; box = 128 columns x 32 rows,
 // no swizzle (the epilogue writes the staging tile row-major).
 static int make_out_map(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int dtype) {
   auto key = std::make_tuple(base, rows, cols | (ld << 32), 128u, 32u | ((uint32_t)dtype << 8), true);
-  auto it = ctx->tmap_cache.find(key);
-  if (it != ctx->tmap_cache.end()) {
-    *m = it->second;
-    return RT_OK;
+  if (ctx) {
+    auto it = ctx->tmap_cache.find(key);
+    if (it != ctx->tmap_cache.end()) {
+      *m = it->second;
+      return RT_OK;
+    }
   }
   const uint64_t es = dtype == OUT_F32 ? 4 : 2;
   cuuint64_t dims[2] = {cols, rows};
@@ -569,6 +572,7 @@ static int make_out_map(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t 
   CUresult r = g_encode(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return RT_ERR_CUDA;
+  if (!ctx) return RT_OK;
   if (ctx->tmap_cache.size() > 8192) ctx->tmap_cache.clear();
   ctx->tmap_cache.emplace(key, *m);
   return RT_OK;
@@ -669,8 +673,14 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   p.b_mn = a.tok_mode ? 1 : 0;
   p.part = nullptr;
   if (p.n_splits > 1 || a.tok_mode) {
-    p.part = (float*)ctx->get_scratch(3, (size_t)p.n_splits * a.M * out_rows * sizeof(float));
-    if (!p.part) return RT_ERR_CUDA;
+    const size_t need = (size_t)p.n_splits * a.M * out_rows;
+    if (a.fixed_part) {
+      if (need > a.fixed_part_floats) return RT_ERR_TOO_LARGE;
+      p.part = a.fixed_part;
+    } else {
+      p.part = (float*)ctx->get_scratch(3, need * sizeof(float));
+      if (!p.part) return RT_ERR_CUDA;
+    }
   }
   // TMA-store epilogue whenever the output is TMA-addressable (16-byte aligned base and row pitch)
   CUtensorMap tm_out = tm_act;
@@ -678,7 +688,7 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   {
     const uint64_t es = a.out_dtype == OUT_F32 ? 4 : 2;
     if (!p.part && ((uintptr_t)a.out % 16 == 0) && ((uint64_t)p.ld_out * es) % 16 == 0) {
-      rc = make_out_map(ctx, &tm_out, a.out, (uint64_t)a.M, (uint64_t)out_rows, (uint64_t)p.ld_out, a.out_dtype);
+      rc = make_out_map(a.fixed_part ? nullptr : ctx, &tm_out, a.out, (uint64_t)a.M, (uint64_t)out_rows, (uint64_t)p.ld_out, a.out_dtype);
       if (rc) return rc;
       p.tma_out = 1;
     }
@@ -686,7 +696,7 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   const int n_items = n_tiles * p.n_splits;
   const int grid = n_items < num_sms ? n_items : num_sms;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
-  if (ctx->profiling) {
+  if (ctx->profiling && !a.fixed_part) {
     if (ctx->prof_used + 2 > ctx->prof_events.size()) {
       for (int i = 0; i < 256; ++i) {
         cudaEvent_t e;
@@ -717,4 +727,52 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   return cudaGetLastError() == cudaSuccess ? RT_OK : RT_ERR_CUDA;
 }
 
+
+// ------------------------------------------------------------------ allocation-free entry point
+// Split-K partial sums of rt_frozen_backward_input_dev_noalloc live here instead of in memory
+// from cudaMalloc.  Every GPU that loads the library holds these 8 MiB until the process exits.
+constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)2 << 20;
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+static float* g_noalloc_scratch_addr[64] = {nullptr};  // device address of the array, per device ordinal
+
+// In host code `g_noalloc_scratch` is only a stand-in for the symbol, not a device address: the
+// address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that
+// device current.
+static int noalloc_scratch_for(int device, float** out) {
+  if (device < 0 || device >= 64) return RT_ERR_BAD_ARG;
+  if (!g_noalloc_scratch_addr[device]) {
+    void* p = nullptr;
+    if (cudaSetDevice(device) != cudaSuccess) return RT_ERR_CUDA;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return RT_ERR_CUDA;
+    g_noalloc_scratch_addr[device] = (float*)p;
+  }
+  *out = g_noalloc_scratch_addr[device];
+  return RT_OK;
+}
+
 }  // namespace rt
+
+extern "C" rt_status rt_frozen_backward_input_dev_noalloc(rt_frozen* f, const void* dy_dev, int in_dtype, size_t t,
+                                                          void* dx_dev, int out_dtype, int accumulate) {
+  if (!f || !dy_dev || !dx_dev) return RT_ERR_BAD_ARG;
+  rt_ctx* c = f->ctx;
+  if (t == 0) return RT_OK;
+  if (t > (1u << 24)) return RT_ERR_BAD_SHAPE;
+  if (in_dtype != RT_DT_F16 && in_dtype != RT_DT_BF16) return RT_ERR_BAD_ARG;
+  if (out_dtype < 0 || out_dtype > 2 || (accumulate && out_dtype != RT_DT_F32)) return RT_ERR_BAD_ARG;
+  if (cudaSetDevice(c->device) != cudaSuccess) return RT_ERR_CUDA;
+  float* scratch = nullptr;
+  int rc = rt::noalloc_scratch_for(c->device, &scratch);  // first call on a device: looks the array up
+  if (rc) return rc;
+  rt::QGemmArgs a;
+  a.dir = rt::QG_BWD;
+  a.act = dy_dev;
+  a.act_f16 = in_dtype == RT_DT_F16;
+  a.M = (int)t;
+  a.out = dx_dev;
+  a.out_dtype = out_dtype;
+  a.accumulate = accumulate ? 1 : 0;
+  a.fixed_part = scratch;
+  a.fixed_part_floats = rt::NOALLOC_SCRATCH_FLOATS;
+  return rt::qgemm_launch(c, f->w, a);
+}

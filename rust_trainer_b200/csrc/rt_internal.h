@@ -54,6 +54,10 @@ struct QGemmArgs {
   int tok_mode = 0;
   size_t out_s_tok = 0, out_s_row = 1;
   const float* alpha_dev = nullptr;    // optional device scalar factor (split-K / token mode only)
+  // split-K partials go to this caller-provided buffer instead of ctx scratch (and nothing is
+  // cached or allocated on the way); a launch that needs more fails with RT_ERR_TOO_LARGE
+  float* fixed_part = nullptr;
+  size_t fixed_part_floats = 0;
   int aux = 0;                         // 1: a skinny LoRA helper product (kept apart in the profile)
 };
 
