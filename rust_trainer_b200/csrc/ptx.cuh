@@ -71,7 +71,7 @@ __device__ __forceinline__ void tc_fence_after() {
 }
 
 // ---------------------------------------------------------------- TMA
-// 2-D tiled load, global -> shared, completion on an mbarrier (no multicast).
+// 2-D tiled load, global -> shared, completion on an mbarrier.
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
