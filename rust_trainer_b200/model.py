@@ -41,6 +41,7 @@ class Model:
 
     # --- adapters
     def attach_lora(self, rank: int, alpha: float, targets: list | None = None, seed: int = 1234) -> int:
+        self.lora_alpha = float(alpha)
         n = C.c_size_t()
         csv = None if targets is None else ",".join(targets).encode()
         self.ctx.check(lib().rt_model_attach_lora(self._h, rank, alpha, csv, seed, C.byref(n)))
@@ -114,6 +115,21 @@ class Model:
         norm = C.c_float()
         self.ctx.check(lib().rt_optim_step(self._h, lr, max_norm, beta1, beta2, eps, weight_decay, C.byref(norm)))
         return norm.value
+
+    def optim_state(self):
+        """(step count, flat Adam m, flat Adam v) in parameter order."""
+        n = self.trainable_params()
+        t = C.c_uint64()
+        m, v = np.empty(n, np.float32), np.empty(n, np.float32)
+        self.ctx.check(lib().rt_optim_state_read(self._h, C.byref(t), _fp(m), _fp(v)))
+        return t.value, m, v
+
+    def set_optim_state(self, t: int, m: np.ndarray, v: np.ndarray) -> None:
+        m = np.ascontiguousarray(m, dtype=np.float32)
+        v = np.ascontiguousarray(v, dtype=np.float32)
+        if m.size != self.trainable_params() or v.size != m.size:
+            raise RtError(1, "optimizer state does not match parameters")  # src/optim.rs:57 asserts
+        self.ctx.check(lib().rt_optim_state_write(self._h, int(t), _fp(m), _fp(v)))
 
     def close(self) -> None:
         if self._h:
