@@ -368,7 +368,7 @@ def run_microbench(args):
         n, k = (int(v) for v in args.shape.split("x"))
         shapes = [(n, k)]
     for (n, k) in shapes:
-        t = spec.quant_for(k)
+        t = spec.quant_for(k) if not args.quant else Q.BY_NAME[args.quant]
         f = rt.Frozen(ctx, t, n, k, Q.quantize((rng.standard_normal((n, k)) * 0.02).astype(np.float32), t))
         x = torch.randn(M, k, device="cuda", dtype=torch.float16)
         dy = torch.randn(M, n, device="cuda", dtype=torch.float16)
@@ -404,6 +404,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--microbench", action="store_true", help="time the frozen-matmul kernel alone")
     ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--quant", default="", help="microbench: weight format instead of the workload's")
     ap.add_argument("--shape", default="", help="microbench: one OUTxIN shape instead of the workload's")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

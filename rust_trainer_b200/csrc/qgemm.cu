@@ -55,7 +55,7 @@ struct KParams {
   uint32_t idesc_main, idesc_lora;
   int* status;
   int tma_out;  // the epilogue stages [32 tokens x 128] tiles in shared memory and writes them with TMA
-  int dbg;  // measurement aid (RT_B200_DBG): 1 = epilogue skips its stores, 2 = unpack warps skip the conversion
+  int dbg;  // measurement aid (RT_B200_DBG bit mask): 1 = epilogue skips its stores, 2 = unpack warps skip the conversion
 };
 
 // ------------------------------------------------------------------ unpackers
@@ -366,10 +366,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           if (!mbar_wait(&raw_full[rs], rph, p.status, 202)) { ok = false; break; }
           const uint8_t* raw = sRaw + rs * RAW_STAGE;
           uint8_t* dst = sW + st * W_STAGE;
-          if (p.dbg == 2) {
+          if (p.dbg & 2) {
           } else if (p.act_f16) unpack_pair<false>(p.fmt, raw, p.brick_bytes, t, dst);
           else unpack_pair<true>(p.fmt, raw, p.brick_bytes, t, dst);
-          fence_proxy_async_smem();
+          if (!(p.dbg & 4)) fence_proxy_async_smem();
           mbar_arrive(&raw_empty[rs]);
           ++rit;
         }
@@ -396,14 +396,20 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         uint32_t v[32];
         tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(wq * 32) << 16) + c * 32, v);
         tmem_ld_wait();
-        if (p.tma_out && p.dbg != 1) {
+        if (p.tma_out && !(p.dbg & 1)) {
           // Transpose through shared memory: lane = output feature, register j = token, so the
           // staged tile is [32 tokens][128 features] and one TMA store writes 32 full rows.
-          const int buf = (int)(out_chunk & 1);
+          // 16-bit outputs need half the staging bytes, so four buffers fit where f32 has two:
+          // a buffer is reused only after the store issued (nbuf) chunks ago has read it
+          const bool wide = p.out_dtype == OUT_F32;
+          const int buf = wide ? (int)(out_chunk & 1) : (int)(out_chunk & 3);
           ++out_chunk;
-          uint8_t* stage = sOut + buf * OUT_STAGE;
+          uint8_t* stage = sOut + buf * (wide ? OUT_STAGE : OUT_STAGE / 2);
           const bool issuer = warp == 6 && lane == 0;
-          if (issuer) bulk_wait_group_read<1>();  // the store that last read this buffer is done with it
+          if (issuer) {
+            if (wide) bulk_wait_group_read<1>();
+            else bulk_wait_group_read<3>();
+          }
           named_barrier_sync(1, 128);
           const int col = wq * 32 + lane;
 #pragma unroll
@@ -415,7 +421,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
             else if (p.out_dtype == OUT_BF16) ((__nv_bfloat16*)stage)[j * 128 + col] = __float2bfloat16_rn(val);
             else ((__half*)stage)[j * 128 + col] = __float2half_rn(val);
           }
-          fence_proxy_async_smem();
+          if (!(p.dbg & 8)) fence_proxy_async_smem();
           named_barrier_sync(1, 128);
           if (issuer) {
             if (p.accumulate) tma_reduce_add_2d(&tm_out, r0, m0 + c * 32, stage);
@@ -424,7 +430,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           }
           continue;
         }
-        if (row_ok && p.dbg != 1) {
+        if (row_ok && !(p.dbg & 1)) {
           if (p.part != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
