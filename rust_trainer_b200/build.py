@@ -48,7 +48,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     def compile_one(job):
         src, obj = job
-        cmd = [nvcc, *NVCC_FLAGS, "-x", "cu", "-c", str(src), "-o", str(obj)]
+        extra = os.environ.get("RT_B200_NVCC_EXTRA", "").split()  # e.g. -DRT_B200_QPROF for the wait-cycle counters
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-x", "cu", "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         return src, r
 

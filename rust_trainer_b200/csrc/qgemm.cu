@@ -9,11 +9,12 @@
 // tile), so the TMEM accumulator is the transposed output tile [128 x tokens].
 //
 // One persistent CTA per SM, warp-specialised:
-//   warp 0      producer : TMA tiles of activations (128B swizzle) + bulk copies of packed bricks
+//   warp 0      producer : TMA tiles of activations (and of 16-bit weights), 128B swizzle
 //   warp 1      MMA      : one thread issues tcgen05.mma (kind::f16, fp32 accumulate in TMEM)
-//   warps 2-5   unpack   : packed bricks -> f16 tile in the UMMA shared-memory layout
+//   warps 2-9   unpack   : packed bricks -> f16 tile in the UMMA shared-memory layout
 //                          (forward reads it K-major, backward reads the same bytes MN-major)
-//   warps 6-9   epilogue : tcgen05.ld the accumulator (double buffered: 2 x 256 TMEM columns),
+//   warp 14     packed-brick producer: runs ahead of warp 0, bounded only by its own ring
+//   warps 10-13 epilogue : tcgen05.ld the accumulator (double buffered: 2 x 256 TMEM columns),
 //                          add bias / accumulate, store f32 and/or bf16
 // The LoRA low-rank term is one more contraction chunk fed through the same accumulator.
 #include "ptx.cuh"
@@ -23,19 +24,28 @@
 
 namespace rt {
 
-constexpr int NS = 3;                 // activation / unpacked-weight stages
-constexpr int NR = 3;                 // packed brick-pair stages
-constexpr int ACT_STAGE = 32768;      // 256 tokens x 64 x bf16
 constexpr int W_STAGE = 16384;        // 128 x 64 x 16-bit
 constexpr int RAW_STAGE = 2 * 4352;   // largest brick pair (Q8_0)
-constexpr int QG_THREADS = 320;
-constexpr int OFF_W = NS * ACT_STAGE;
-constexpr int OFF_RAW = OFF_W + NS * W_STAGE;
+constexpr int QG_THREADS = 480;       // producer, MMA, 8 unpack, 4 epilogue warps, packed-brick producer
+constexpr int UG = 2;                 // unpack groups (a power of two) ...
+constexpr int UTG = 256 / UG;         // ... of this many threads each
 constexpr int OUT_STAGE = 32 * 128 * 4;  // 32 tokens x 128 output features x f32: the epilogue's TMA-store staging
-constexpr int OFF_OUT = OFF_RAW + NR * RAW_STAGE;
-constexpr int OFF_BAR = OFF_OUT + 2 * OUT_STAGE;
-constexpr int N_BARS = 3 * NS + 2 * NR + 4;
-constexpr int SMEM_BYTES = OFF_BAR + N_BARS * 8 + 16 + 1024;
+
+// Shared-memory plan of one CTA.  A CTA of a pair stages half of the token tile, so its stages
+// are a third smaller and five of them fit.
+template <bool PAIR>
+struct QCfg {
+  static constexpr int NS = PAIR ? 5 : 3;                  // activation / unpacked-weight stages
+  static constexpr int NR = PAIR ? 3 : 4;                  // packed brick-pair stages
+  static constexpr int ACT_STAGE = PAIR ? 16384 : 32768;   // 128 or 256 tokens x 64 x 16-bit
+  static constexpr int OFF_W = NS * ACT_STAGE;
+  static constexpr int OFF_RAW = OFF_W + NS * W_STAGE;
+  static constexpr int OFF_OUT = OFF_RAW + NR * RAW_STAGE;
+  static constexpr int OFF_BAR = OFF_OUT + 2 * OUT_STAGE;
+  static constexpr int N_BARS = 3 * NS + 2 * NR + 4;
+  static constexpr int SMEM_BYTES = OFF_BAR + N_BARS * 8 + 16 + 1024;
+};
+static_assert(QCfg<true>::SMEM_BYTES <= 232448 && QCfg<false>::SMEM_BYTES <= 232448, "shared memory plan exceeds one SM");
 
 struct KParams {
   const uint8_t* bricks;
@@ -47,7 +57,7 @@ struct KParams {
   int n_splits, steps_per_split;  // split-K: work item = (tile, split); partial results go to `part`
   int b_mn;                       // token-contraction mode: the B operand is MN-major (tile rows = contraction)
   float* part;                    // [n_splits][M][out_rows] f32 partials when n_splits > 1 or b_mn
-  int n_row_tiles, n_tok_tiles;
+  int n_row_tiles, n_tok_tiles;    // a row tile is 128 weight rows, 256 for a CTA pair
   void* out;
   int out_dtype, accumulate, ld_out;
   const float* row_scale;  // optional per-token factor applied to the result
@@ -55,7 +65,10 @@ struct KParams {
   uint32_t idesc_main, idesc_lora;
   int* status;
   int tma_out;  // the epilogue stages [32 tokens x 128] tiles in shared memory and writes them with TMA
-  int dbg;  // measurement aid (RT_B200_DBG bit mask): 1 = epilogue skips its stores, 2 = unpack warps skip the conversion
+  long long* prof;  // measurement aid (RT_B200_QPROF): per-CTA cycle counts of each role's waits, else null
+  int dbg;  // measurement aid (RT_B200_DBG bit mask): 1 = epilogue skips its stores, 2 = unpack warps skip the conversion,
+            // 16 = no operand loads at all: the MMAs run on whatever shared memory holds (results are garbage),
+            // 32 = no MMAs are issued, 64 = no activation tiles are loaded
 };
 
 // ------------------------------------------------------------------ unpackers
@@ -167,38 +180,79 @@ __device__ __forceinline__ void unpack_q6_k(const uint8_t* brick, int t, uint8_t
   }
 }
 
+// one brick (64 x 64 codes) -> one 8 KB half of the 16-bit weight tile; t = unit 0..127
 template <bool WBF16>
-__device__ __forceinline__ void unpack_pair(int fmt, const uint8_t* raw, int bb, int t, uint8_t* dst) {
+__device__ __forceinline__ void unpack_brick(int fmt, const uint8_t* raw, int t, uint8_t* dst) {
   switch (fmt) {
-    case GGML_Q4_0: unpack_q4_0<WBF16>(raw, t, dst); unpack_q4_0<WBF16>(raw + bb, t, dst + 8192); break;
-    case GGML_Q8_0: unpack_q8_0<WBF16>(raw, t, dst); unpack_q8_0<WBF16>(raw + bb, t, dst + 8192); break;
-    case GGML_Q4_K: unpack_q4_k<WBF16>(raw, t, dst); unpack_q4_k<WBF16>(raw + bb, t, dst + 8192); break;
-    case GGML_Q6_K: unpack_q6_k<WBF16>(raw, t, dst); unpack_q6_k<WBF16>(raw + bb, t, dst + 8192); break;
+    case GGML_Q4_0: unpack_q4_0<WBF16>(raw, t, dst); break;
+    case GGML_Q8_0: unpack_q8_0<WBF16>(raw, t, dst); break;
+    case GGML_Q4_K: unpack_q4_k<WBF16>(raw, t, dst); break;
+    case GGML_Q6_K: unpack_q6_k<WBF16>(raw, t, dst); break;
   }
 }
 
 // ------------------------------------------------------------------ kernel
+// PAIR = false: one CTA per output tile of 128 weight rows x TN tokens.
+// PAIR = true : a cluster of two CTAs shares a tile of 256 weight rows x TN tokens.  Each CTA
+//   holds its own 128 weight rows (unpacked by its own warps) and HALF of the token tile; the
+//   leader CTA (cluster rank 0) issues tcgen05.mma.cta_group::2, which reads both CTAs' shared
+//   memory and writes 128 accumulator rows into each CTA's TMEM.  Per CTA and per MMA cycle this
+//   halves the activation bytes that TMA writes and the tensor core reads, so five stages fit
+//   where the single-CTA kernel has three.  Barriers that gate the MMA (full, w_ready, acc_empty)
+//   live in the leader and are arrived on from both CTAs; barriers the MMA releases
+//   (stage_empty, acc_full) exist in both CTAs and are signalled by one multicast commit.
+// Build with -DRT_B200_QPROF to count, per CTA and role, the cycles spent in each wait (measurement aid).
+#ifdef RT_B200_QPROF
+#define QG_TIMED(slot, expr)                  \
+  do {                                        \
+    const long long t_ = clock64();           \
+    expr;                                     \
+    prof_acc[slot] += clock64() - t_;         \
+  } while (0)
+#define QG_PROF_BEGIN() long long prof_acc[4] = {0, 0, 0, 0}; const long long prof_t0 = clock64(); const uint64_t prof_ns0 = globaltimer_ns()
+#define QG_PROF_END(role)                                                                  \
+  do {                                                                                     \
+    if (p.prof) {                                                                          \
+      prof_acc[3] = clock64() - prof_t0;                                                   \
+      if ((role) == 3) prof_acc[2] = (long long)(globaltimer_ns() - prof_ns0);             \
+      for (int q_ = 0; q_ < 4; ++q_) p.prof[((size_t)blockIdx.x * 4 + (role)) * 4 + q_] = prof_acc[q_]; \
+    }                                                                                      \
+  } while (0)
+#else
+#define QG_TIMED(slot, expr) do { expr; } while (0)
+#define QG_PROF_BEGIN() do { } while (0)
+#define QG_PROF_END(role) do { } while (0)
+#endif
+template <bool PAIR>
 __global__ void __launch_bounds__(QG_THREADS, 1)
 qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_w16,
              const __grid_constant__ CUtensorMap tm_lact, const __grid_constant__ CUtensorMap tm_lw,
              const __grid_constant__ CUtensorMap tm_out, const KParams p) {
+  using C = QCfg<PAIR>;
+  constexpr int NS = C::NS;
+  constexpr int NR = C::NR;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sAct = smem;
-  uint8_t* sW = smem + OFF_W;
-  uint8_t* sRaw = smem + OFF_RAW;
-  uint8_t* sOut = smem + OFF_OUT;
-  uint64_t* bars = (uint64_t*)(smem + OFF_BAR);
-  uint64_t* full = bars;                   // [NS] activations (+ TMA'd weight tile) landed
-  uint64_t* w_ready = bars + NS;           // [NS] unpack warps done with the weight tile
-  uint64_t* stage_empty = bars + 2 * NS;   // [NS] MMAs reading the stage have completed
-  uint64_t* raw_full = bars + 3 * NS;      // [NR]
+  uint8_t* sW = smem + C::OFF_W;
+  uint8_t* sRaw = smem + C::OFF_RAW;
+  uint8_t* sOut = smem + C::OFF_OUT;
+  uint64_t* bars = (uint64_t*)(smem + C::OFF_BAR);
+  uint64_t* full = bars;                   // [NS] activations (+ TMA'd weight tile) landed      (leader's is used)
+  uint64_t* w_ready = bars + NS;           // [NS] unpack warps done with the weight tile         (leader's is used)
+  uint64_t* stage_empty = bars + 2 * NS;   // [NS] MMAs reading the stage have completed          (every CTA)
+  uint64_t* raw_full = bars + 3 * NS;      // [NR]                                                (every CTA)
   uint64_t* raw_empty = raw_full + NR;     // [NR]
-  uint64_t* acc_full = raw_empty + NR;     // [2]
-  uint64_t* acc_empty = acc_full + 2;      // [2]
-  uint32_t* tmem_slot = (uint32_t*)(bars + N_BARS);
+  uint64_t* acc_full = raw_empty + NR;     // [2]                                                 (every CTA)
+  uint64_t* acc_empty = acc_full + 2;      // [2]                                                 (leader's is used)
+  uint32_t* tmem_slot = (uint32_t*)(bars + C::N_BARS);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // 0 = leader
+  const int n_cta = PAIR ? 2 : 1;
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int n_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int tn_cta = PAIR ? p.TN >> 1 : p.TN;  // token rows of the tile this CTA loads
   const bool is16 = fmt_is_16bit(p.fmt);
   const int n_tiles = p.n_row_tiles * p.n_tok_tiles;
   const int n_items = n_tiles * p.n_splits;
@@ -209,11 +263,19 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
   const int s_main = min(p.n_main, s_begin + p.steps_per_split) - s_begin;                    \
   const int n_steps = s_main + ((p.lora_mmas > 0 && split == p.n_splits - 1) ? 1 : 0);        \
   (void)split
+// first weight row (output feature) of this CTA's half of the tile, first token of the tile
+#define QG_TILE_ORIGIN()                                                                      \
+  const int r0 = (tile % p.n_row_tiles) * (128 * n_cta) + (int)rank * 128;                    \
+  const int m0 = (tile / p.n_row_tiles) * p.TN
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NS; ++i) { mbar_init(&full[i], 1); mbar_init(&w_ready[i], 128); mbar_init(&stage_empty[i], 1); }
-    for (int i = 0; i < NR; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 128); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128); }
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&w_ready[i], (8 / UG) * n_cta);  // one arrival per warp of the group that owns the step
+      mbar_init(&stage_empty[i], 1);
+    }
+    for (int i = 0; i < NR; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], UTG); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4 * n_cta); }  // per epilogue warp
     mbar_fence_init();
     prefetch_tmap(&tm_act);
     prefetch_tmap(&tm_w16);
@@ -222,130 +284,152 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     if (p.tma_out) prefetch_tmap(&tm_out);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
+    if (PAIR) { tmem_alloc_pair(tmem_slot, 512); tmem_relinquish_pair(); }
+    else { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   }
   tc_fence_before();
-  __syncthreads();
+  __syncwarp();
+  if (PAIR) cluster_sync_all();  // both CTAs' barriers are initialised and both hold their TMEM columns
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      uint32_t it = 0, rit = 0;
+      uint32_t it = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      QG_PROF_BEGIN();
+      for (int item = worker; item < n_items && ok && !(p.dbg & 16); item += n_workers) {
         QG_ITEM_DECODE(item);
-        const int r0 = (tile % p.n_row_tiles) * 128, m0 = (tile / p.n_row_tiles) * p.TN;
+        QG_TILE_ORIGIN();
+        const int m_cta = m0 + (int)rank * tn_cta;  // this CTA's half of the tokens
         for (int si = 0; si < n_steps && ok; ++si, ++it) {
           const int s = s_begin + si;
           const int st = it % NS;
           const uint32_t ph = (it / NS) & 1;
-          if (!mbar_wait(&stage_empty[st], ph ^ 1, p.status, 101)) { ok = false; break; }
+          { bool w_; QG_TIMED(0, w_ = mbar_wait(&stage_empty[st], ph ^ 1, p.status, 101)); if (!w_) { ok = false; break; } }
           const bool lora = si >= s_main;
-          uint8_t* a_dst = sAct + st * ACT_STAGE;
+          uint8_t* a_dst = sAct + st * C::ACT_STAGE;
           uint8_t* w_dst = sW + st * W_STAGE;
-          mbar_expect_tx(&full[st], (uint32_t)p.TN * 128u + ((is16 || lora) ? (uint32_t)W_STAGE : 0u));
+          // the leader's barrier counts the bytes both CTAs will bring
+          if (rank == 0)
+            mbar_expect_tx(&full[st], ((p.dbg & 64) ? 0u : (uint32_t)p.TN * 128u) + ((is16 || lora) ? (uint32_t)(W_STAGE * n_cta) : 0u));
+          const uint32_t fbar = PAIR ? mapa_u32(smem_u32(&full[st]), 0) : 0u;
+          auto load2d = [&](void* dst, const CUtensorMap* map, int x, int y) {
+            if (PAIR) tma_load_2d_pair(dst, map, x, y, fbar);
+            else tma_load_2d(dst, map, x, y, &full[st]);
+          };
           if (!lora) {
-            if (p.b_mn) tma_load_2d(a_dst, &tm_act, 0, s * 64, &full[st]);  // [64 contraction rows x 64]
-            else tma_load_2d(a_dst, &tm_act, s * 64, m0, &full[st]);
+            if (p.dbg & 64) {
+            } else if (p.b_mn) load2d(a_dst, &tm_act, 0, s * 64);  // [64 contraction rows x 64]
+            else load2d(a_dst, &tm_act, s * 64, m_cta);
             if (is16) {
               if (p.dir == QG_FWD) {
-                tma_load_2d(w_dst, &tm_w16, s * 64, r0, &full[st]);
-                tma_load_2d(w_dst + 8192, &tm_w16, s * 64, r0 + 64, &full[st]);
+                load2d(w_dst, &tm_w16, s * 64, r0);
+                load2d(w_dst + 8192, &tm_w16, s * 64, r0 + 64);
               } else {
-                tma_load_2d(w_dst, &tm_w16, r0, s * 64, &full[st]);
-                tma_load_2d(w_dst + 8192, &tm_w16, r0 + 64, s * 64, &full[st]);
+                load2d(w_dst, &tm_w16, r0, s * 64);
+                load2d(w_dst + 8192, &tm_w16, r0 + 64, s * 64);
               }
-            } else {
-              const int rs = rit % NR;
-              const uint32_t rph = (rit / NR) & 1;
-              if (!mbar_wait(&raw_empty[rs], rph ^ 1, p.status, 102)) { ok = false; break; }
-              const uint32_t bb = (uint32_t)p.brick_bytes;
-              mbar_expect_tx(&raw_full[rs], 2 * bb);
-              const int tr2 = (r0 >> 6);
-              const uint8_t *b0, *b1;
-              if (p.dir == QG_FWD) {
-                b0 = p.bricks + ((size_t)tr2 * p.nbk + s) * bb;
-                b1 = p.bricks + ((size_t)(tr2 + 1) * p.nbk + s) * bb;
-              } else {
-                b0 = p.bricks + ((size_t)s * p.nbk + tr2) * bb;
-                b1 = b0 + bb;
-              }
-              bulk_load_1d(sRaw + rs * RAW_STAGE, b0, bb, &raw_full[rs]);
-              bulk_load_1d(sRaw + rs * RAW_STAGE + bb, b1, bb, &raw_full[rs]);
-              ++rit;
             }
           } else {
-            tma_load_2d(a_dst, &tm_lact, 0, m0, &full[st]);
+            load2d(a_dst, &tm_lact, 0, m_cta);
             if (p.dir == QG_FWD) {
-              tma_load_2d(w_dst, &tm_lw, 0, r0, &full[st]);
-              tma_load_2d(w_dst + 8192, &tm_lw, 0, r0 + 64, &full[st]);
+              load2d(w_dst, &tm_lw, 0, r0);
+              load2d(w_dst + 8192, &tm_lw, 0, r0 + 64);
             } else {
-              tma_load_2d(w_dst, &tm_lw, r0, 0, &full[st]);
-              tma_load_2d(w_dst + 8192, &tm_lw, r0 + 64, 0, &full[st]);
+              load2d(w_dst, &tm_lw, r0, 0);
+              load2d(w_dst + 8192, &tm_lw, r0 + 64, 0);
             }
           }
         }
       }
+      QG_PROF_END(0);
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issue
-    if (lane == 0) {
-      uint32_t it = 0, tcount = 0;
+    // ------------------------------------------------------------ MMA issue (the leader's thread only)
+    if (lane == 0 && rank == 0) {
+      uint32_t tcount = 0;
+      int st = 0;        // stage ring position and its phase, advanced without divisions
+      uint32_t ph = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++tcount) {
+      // Descriptors: the high words are fixed for the launch, the low words are address >> 4 plus
+      // the leading-dimension field; a stage or a K step of 16 only adds a constant to them.
+      const uint64_t a_d0 = (p.dir == QG_FWD) ? umma_desc_sw128(smem_u32(sW), 16, 1024) : umma_desc_sw128(smem_u32(sW), 8192, 1024);
+      const uint64_t b_d0 = p.b_mn ? umma_desc_sw128(smem_u32(sAct), 8192, 1024) : umma_desc_sw128(smem_u32(sAct), 16, 1024);
+      const uint32_t a_hi = (uint32_t)(a_d0 >> 32), b_hi = (uint32_t)(b_d0 >> 32);
+      const uint32_t a_k = (p.dir == QG_FWD) ? (32u >> 4) : (2048u >> 4);  // low-word step per K = 16
+      const uint32_t b_k = p.b_mn ? (2048u >> 4) : (32u >> 4);
+      QG_PROF_BEGIN();
+      for (int item = worker; item < n_items && ok; item += n_workers, ++tcount) {
         QG_ITEM_DECODE(item);
         (void)tile; (void)s_begin;
         const int acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1;
-        if (!mbar_wait(&acc_empty[acc], aph ^ 1, p.status, 301)) { ok = false; break; }
+        { bool w_; QG_TIMED(0, w_ = mbar_wait<false>(&acc_empty[acc], aph ^ 1, p.status, 301)); if (!w_) { ok = false; break; } }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * 256;
-        for (int s = 0; s < n_steps; ++s, ++it) {
-          const int st = it % NS;
-          const uint32_t ph = (it / NS) & 1;
-          if (!mbar_wait(&full[st], ph, p.status, 302)) { ok = false; break; }
-          if (!mbar_wait(&w_ready[st], ph, p.status, 303)) { ok = false; break; }
-          tc_fence_after();
-          const bool lora = s >= s_main;
-          const int nm = lora ? p.lora_mmas : 4;
-          const uint32_t idesc = lora ? p.idesc_lora : p.idesc_main;
-          const uint32_t a_base = smem_u32(sW + st * W_STAGE);
-          const uint32_t b_base = smem_u32(sAct + st * ACT_STAGE);
-          for (int kk = 0; kk < nm; ++kk) {
-            const uint64_t adesc = (p.dir == QG_FWD) ? umma_desc_sw128(a_base + kk * 32, 16, 1024)
-                                                     : umma_desc_sw128(a_base + kk * 2048, 8192, 1024);
-            const uint64_t bdesc = p.b_mn ? umma_desc_sw128(b_base + kk * 2048, 8192, 1024)
-                                          : umma_desc_sw128(b_base + kk * 32, 16, 1024);
-            umma_f16(d_tmem, adesc, bdesc, idesc, (uint32_t)((s | kk) != 0));
+        for (int s = 0; s < n_steps; ++s) {
+          if (!(p.dbg & 16)) {
+            { bool w_; QG_TIMED(1, w_ = mbar_wait<false>(&full[st], ph, p.status, 302)); if (!w_) { ok = false; break; } }
+            { bool w_; QG_TIMED(2, w_ = mbar_wait<false>(&w_ready[st], ph, p.status, 303)); if (!w_) { ok = false; break; } }
           }
-          umma_commit(&stage_empty[st]);
+          tc_fence_after();
+          const uint32_t a_lo = (uint32_t)a_d0 + (uint32_t)st * (W_STAGE >> 4);
+          const uint32_t b_lo = (uint32_t)b_d0 + (uint32_t)st * (C::ACT_STAGE >> 4);
+          if (p.dbg & 32) {
+          } else if (s < s_main) {
+            umma_f16_split<PAIR>(d_tmem, a_lo, a_hi, b_lo, b_hi, p.idesc_main, (uint32_t)(s != 0));
+            umma_f16_split<PAIR>(d_tmem, a_lo + a_k, a_hi, b_lo + b_k, b_hi, p.idesc_main, 1u);
+            umma_f16_split<PAIR>(d_tmem, a_lo + 2 * a_k, a_hi, b_lo + 2 * b_k, b_hi, p.idesc_main, 1u);
+            umma_f16_split<PAIR>(d_tmem, a_lo + 3 * a_k, a_hi, b_lo + 3 * b_k, b_hi, p.idesc_main, 1u);
+          } else {
+            for (int kk = 0; kk < p.lora_mmas; ++kk)
+              umma_f16_split<PAIR>(d_tmem, a_lo + kk * a_k, a_hi, b_lo + kk * b_k, b_hi, p.idesc_lora, (uint32_t)((s | kk) != 0));
+          }
+          if (PAIR) umma_commit_pair(&stage_empty[st], 3);
+          else umma_commit(&stage_empty[st]);
+          if (++st == NS) { st = 0; ph ^= 1; }
         }
-        if (ok) umma_commit(&acc_full[acc]);
+        if (ok) {
+          if (PAIR) umma_commit_pair(&acc_full[acc], 3);
+          else umma_commit(&acc_full[acc]);
+        }
       }
+      QG_PROF_END(1);
     }
-  } else if (warp < 6) {
+  } else if (warp < 10) {
     // ------------------------------------------------------------ unpack
+    // One pass over a weight tile (load codes, convert, store, fence, arrive) is a chain of
+    // dependent shared-memory operations: its latency, not its instruction count, sets the pace.
+    // The eight warps therefore work as UG groups on alternate contraction steps, so UG passes
+    // are in flight at a time.
     const int t = threadIdx.x - 64;
+    const int grp = t / UTG, tg = t % UTG;
     uint32_t it = 0, rit = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    QG_PROF_BEGIN();
+    for (int item = worker; item < n_items && ok && !(p.dbg & 16); item += n_workers) {
       QG_ITEM_DECODE(item);
       (void)tile; (void)s_begin;
       for (int s = 0; s < n_steps; ++s, ++it) {
+        const bool packed_step = !is16 && s < s_main;
+        if ((int)(it & (UG - 1)) != grp) {  // another group's step: only keep the ring positions in step
+          if (packed_step) ++rit;
+          continue;
+        }
         const int st = it % NS;
         const uint32_t ph = (it / NS) & 1;
-        if (!mbar_wait(&stage_empty[st], ph ^ 1, p.status, 201)) { ok = false; break; }
-        if (is16 && p.conv16 && s < s_main) {
+        { bool w_; QG_TIMED(0, w_ = mbar_wait(&stage_empty[st], ph ^ 1, p.status, 201)); if (!w_) { ok = false; break; } }
+        if (!PAIR && is16 && p.conv16 && s < s_main) {
           // The TMA'd 16-bit weight tile has the other 16-bit type: convert it in place
-          // (element-wise, so the swizzled placement is untouched).
+          // (element-wise, so the swizzled placement is untouched).  Single-CTA kernel only.
           if (!mbar_wait(&full[st], ph, p.status, 203)) { ok = false; break; }
           uint4* tile = (uint4*)(sW + st * W_STAGE);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            uint4 v = tile[t + i * 128];
+          for (int i = 0; i < 1024 / UTG; ++i) {
+            uint4 v = tile[tg + i * UTG];
             uint32_t* w = (uint32_t*)&v;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -357,23 +441,70 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
                 w[j] = *(uint32_t*)&h;
               }
             }
-            tile[t + i * 128] = v;
+            tile[tg + i * UTG] = v;
           }
           fence_proxy_async_smem();
-        } else if (!is16 && s < s_main) {
+        } else if (packed_step) {
           const int rs = rit % NR;
           const uint32_t rph = (rit / NR) & 1;
-          if (!mbar_wait(&raw_full[rs], rph, p.status, 202)) { ok = false; break; }
+          { bool w_; QG_TIMED(1, w_ = mbar_wait(&raw_full[rs], rph, p.status, 202)); if (!w_) { ok = false; break; } }
           const uint8_t* raw = sRaw + rs * RAW_STAGE;
           uint8_t* dst = sW + st * W_STAGE;
-          if (p.dbg & 2) {
-          } else if (p.act_f16) unpack_pair<false>(p.fmt, raw, p.brick_bytes, t, dst);
-          else unpack_pair<true>(p.fmt, raw, p.brick_bytes, t, dst);
-          if (!(p.dbg & 4)) fence_proxy_async_smem();
+          QG_TIMED(2, {
+            if (!(p.dbg & 2)) {
+              // 256 units (two bricks of 128) per tile; unit u: brick u >> 7 fills the 8 KB half u >> 7
+#pragma unroll
+              for (int u = tg; u < 256; u += UTG) {
+                if (p.act_f16) unpack_brick<false>(p.fmt, raw + (u >> 7) * p.brick_bytes, u & 127, dst + (u >> 7) * 8192);
+                else unpack_brick<true>(p.fmt, raw + (u >> 7) * p.brick_bytes, u & 127, dst + (u >> 7) * 8192);
+              }
+            }
+            if (!(p.dbg & 4)) fence_proxy_async_smem();
+          });
           mbar_arrive(&raw_empty[rs]);
           ++rit;
         }
-        mbar_arrive(&w_ready[st]);
+        // one arrival per warp, after every lane's writes are fenced towards the tensor core's reads
+        __syncwarp();
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&w_ready[st]), 0));
+          else mbar_arrive(&w_ready[st]);
+        }
+      }
+    }
+    if (t == 0) QG_PROF_END(2);
+  } else if (warp == 14) {
+    // ------------------------------------------------------------ packed-brick producer
+    // Runs ahead of the stage ring: a brick pair is fetched as soon as its slot in the raw ring
+    // is free, so its latency is not added to the time a weight stage is held.
+    if (lane == 0 && !is16 && !(p.dbg & 16)) {
+      uint32_t rit = 0;
+      bool ok = true;
+      QG_PROF_BEGIN();
+      const uint32_t bb = (uint32_t)p.brick_bytes;
+      for (int item = worker; item < n_items && ok; item += n_workers) {
+        QG_ITEM_DECODE(item);
+        (void)n_steps;
+        QG_TILE_ORIGIN();
+        (void)m0;
+        const int tr2 = (r0 >> 6);
+        for (int si = 0; si < s_main; ++si, ++rit) {
+          const int s = s_begin + si;
+          const int rs = rit % NR;
+          const uint32_t rph = (rit / NR) & 1;
+          { bool w_; QG_TIMED(1, w_ = mbar_wait(&raw_empty[rs], rph ^ 1, p.status, 102)); if (!w_) { ok = false; break; } }
+          mbar_expect_tx(&raw_full[rs], 2 * bb);
+          const uint8_t *b0, *b1;
+          if (p.dir == QG_FWD) {
+            b0 = p.bricks + ((size_t)tr2 * p.nbk + s) * bb;
+            b1 = p.bricks + ((size_t)(tr2 + 1) * p.nbk + s) * bb;
+          } else {
+            b0 = p.bricks + ((size_t)s * p.nbk + tr2) * bb;
+            b1 = b0 + bb;
+          }
+          bulk_load_1d(sRaw + rs * RAW_STAGE, b0, bb, &raw_full[rs]);
+          bulk_load_1d(sRaw + rs * RAW_STAGE + bb, b1, bb, &raw_full[rs]);
+        }
       }
     }
   } else {
@@ -381,13 +512,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     const int wq = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t tcount = 0, out_chunk = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++tcount) {
+    QG_PROF_BEGIN();
+    for (int item = worker; item < n_items && ok; item += n_workers, ++tcount) {
       QG_ITEM_DECODE(item);
       (void)s_begin; (void)n_steps; (void)s_main;
-      const int r0 = (tile % p.n_row_tiles) * 128, m0 = (tile / p.n_row_tiles) * p.TN;
+      QG_TILE_ORIGIN();
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
-      if (!mbar_wait(&acc_full[acc], aph, p.status, 401)) { ok = false; break; }
+      { bool w_; QG_TIMED(0, w_ = mbar_wait(&acc_full[acc], aph, p.status, 401)); if (!w_) { ok = false; break; } }
       tc_fence_after();
       const int row = r0 + wq * 32 + lane;
       const bool row_ok = row < p.out_rows;
@@ -405,7 +537,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           const int buf = wide ? (int)(out_chunk & 1) : (int)(out_chunk & 3);
           ++out_chunk;
           uint8_t* stage = sOut + buf * (wide ? OUT_STAGE : OUT_STAGE / 2);
-          const bool issuer = warp == 6 && lane == 0;
+          const bool issuer = warp == 10 && lane == 0;
           if (issuer) {
             if (wide) bulk_wait_group_read<1>();
             else bulk_wait_group_read<3>();
@@ -463,10 +595,16 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           }
         }
       }
+      // the accumulator buffer is free once every epilogue warp of every CTA has read its lanes
       tc_fence_before();
-      mbar_arrive(&acc_empty[acc]);
+      __syncwarp();
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[acc]), 0));
+        else mbar_arrive(&acc_empty[acc]);
+      }
     }
-    if (p.tma_out && warp == 6 && lane == 0) bulk_wait_group<0>();  // all output writes have landed
+    if (p.tma_out && warp == 10 && lane == 0) bulk_wait_group<0>();  // all output writes have landed
+    if (warp == 10 && lane == 0) QG_PROF_END(3);
   }
 
   // ---------------------------------------------------------------- teardown
@@ -475,10 +613,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
   }
   tc_fence_before();
-  __syncthreads();
+  __syncwarp();
+  // a CTA of a pair must not leave while its partner may still signal its barriers or read its memory
+  if (PAIR) cluster_sync_all();
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if (PAIR) tmem_dealloc_pair(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -509,7 +651,10 @@ typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static PFN_encodeTiled g_encode = nullptr;
 
-size_t qgemm_smem_bytes() { return SMEM_BYTES; }
+size_t qgemm_smem_bytes() { return QCfg<true>::SMEM_BYTES > QCfg<false>::SMEM_BYTES ? QCfg<true>::SMEM_BYTES : QCfg<false>::SMEM_BYTES; }
+
+// how many CTA pairs the device runs at once (0: the pair kernel is not used)
+static int g_pair_workers = -1;
 
 int qgemm_init() {
   if (!g_encode) {
@@ -519,8 +664,33 @@ int qgemm_init() {
       return RT_ERR_CUDA;
     g_encode = (PFN_encodeTiled)fn;
   }
-  if (cudaFuncSetAttribute(qgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+  if (cudaFuncSetAttribute(qgemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, QCfg<false>::SMEM_BYTES) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(qgemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, QCfg<true>::SMEM_BYTES) !=
+          cudaSuccess)
     return RT_ERR_CUDA;
+  if (g_pair_workers < 0) {
+    int dev = 0, sms = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3((unsigned)(sms & ~1));
+    cfg.blockDim = dim3(QG_THREADS);
+    cfg.dynamicSmemBytes = QCfg<true>::SMEM_BYTES;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&n, qgemm_kernel<true>, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    const char* e = getenv("RT_B200_NO_PAIR");
+    g_pair_workers = (e && atoi(e)) ? 0 : n;
+  }
   return RT_OK;
 }
 
@@ -627,6 +797,11 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
       if (best_cost < 0 || cost < best_cost) { best_cost = cost; p.TN = tn; }
     }
   }
+#ifdef RT_B200_QPROF
+  static int tn_force = -1;
+  if (tn_force < 0) { const char* e = getenv("RT_B200_TN"); tn_force = e ? atoi(e) : 0; }
+  if (tn_force > 0 && p.TN >= 128 && !a.tok_mode) p.TN = tn_force;
+#endif
   p.n_main = (contract + 63) / 64;
   p.lora_mmas = a.lora.rank > 0 ? (a.lora.rank + 15) / 16 : 0;
   p.n_row_tiles = (out_rows + 127) / 128;
@@ -641,6 +816,13 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   p.idesc_main = umma_idesc(ab_fmt, ab_fmt, a.dir == QG_BWD ? 1 : 0, 0, 128, p.TN);
   p.idesc_lora = p.idesc_main;
   p.status = status_dev;
+  p.prof = nullptr;
+#ifdef RT_B200_QPROF
+  static long long* prof_dev = nullptr;
+  if (!prof_dev) cudaMalloc(&prof_dev, 512 * 16 * sizeof(long long));
+  cudaMemsetAsync(prof_dev, 0, 512 * 16 * sizeof(long long), st);
+  p.prof = prof_dev;
+#endif
   {
     static int dbg = -1;
     if (dbg < 0) { const char* e = getenv("RT_B200_DBG"); dbg = e ? atoi(e) : 0; }
@@ -666,7 +848,7 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
     else rc = make_map(&tm_lw, a.lora.w, (uint64_t)a.lora.rank, (uint64_t)w.cols, 64, 64, !a.act_f16);
     if (rc) return rc;
   }
-  const int n_tiles = p.n_row_tiles * p.n_tok_tiles;
+  int n_tiles = p.n_row_tiles * p.n_tok_tiles;
   // split-K when the tiles alone cannot fill the GPU and the contraction is long
   int splits = 1;
   if (a.out_dtype == OUT_F32 && n_tiles * 2 <= num_sms && p.n_main >= 8) {
@@ -677,6 +859,37 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   p.steps_per_split = (p.n_main + splits - 1) / splits;
   p.n_splits = (p.n_main + p.steps_per_split - 1) / p.steps_per_split;
   p.b_mn = a.tok_mode ? 1 : 0;
+  // CTA pairs: 256 weight rows per tile, each CTA stages half of the tokens.  Needs whole pairs of
+  // row tiles; the other shapes keep the single-CTA kernel.
+  const bool pair = g_pair_workers > 0 && !a.tok_mode && !p.conv16 && p.n_splits == 1 && a.M > 128 &&
+                    out_rows % 256 == 0;
+  if (pair) {
+    p.n_row_tiles = out_rows / 256;
+    long best_cost = -1;
+    for (int tn = 256; tn >= 128; tn -= 32) {
+      const long tiles = (long)p.n_row_tiles * ((a.M + tn - 1) / tn);
+      const long rounds = (tiles + g_pair_workers - 1) / g_pair_workers;
+      const long cost = rounds * (tn + 40);
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; p.TN = tn; }
+    }
+#ifdef RT_B200_QPROF
+    if (tn_force > 0) p.TN = tn_force;
+#endif
+    p.n_tok_tiles = (a.M + p.TN - 1) / p.TN;
+    n_tiles = p.n_row_tiles * p.n_tok_tiles;
+    p.idesc_main = p.idesc_lora = umma_idesc(ab_fmt, ab_fmt, a.dir == QG_BWD ? 1 : 0, 0, 256, p.TN);
+    // each CTA fetches its half of the token tile
+    rc = make_map(&tm_act, a.act, (uint64_t)a.M, (uint64_t)contract, 64, (uint32_t)(p.TN / 2), !a.act_f16);
+    if (rc) return rc;
+    if (!is16) tm_w16 = tm_act;
+    if (a.lora.rank > 0) {
+      rc = make_map(&tm_lact, a.lora.act, (uint64_t)a.M, 64, 64, (uint32_t)(p.TN / 2), !a.act_f16);
+      if (rc) return rc;
+    } else {
+      tm_lact = tm_act;
+      tm_lw = tm_act;
+    }
+  }
   p.part = nullptr;
   if (p.n_splits > 1 || a.tok_mode) {
     const size_t need = (size_t)p.n_splits * a.M * out_rows;
@@ -700,7 +913,8 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
     }
   }
   const int n_items = n_tiles * p.n_splits;
-  const int grid = n_items < num_sms ? n_items : num_sms;
+  const int workers = pair ? g_pair_workers : num_sms;
+  const int grid = (n_items < workers ? n_items : workers) * (pair ? 2 : 1);
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   if (ctx->profiling && !a.fixed_part) {
     if (ctx->prof_used + 2 > ctx->prof_events.size()) {
@@ -714,8 +928,37 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
     e1 = ctx->prof_events[ctx->prof_used++];
     cudaEventRecord(e0, st);
   }
-  qgemm_kernel<<<grid, QG_THREADS, SMEM_BYTES, st>>>(tm_act, tm_w16, tm_lact, tm_lw, tm_out, p);
+  if (pair) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(QG_THREADS);
+    cfg.dynamicSmemBytes = QCfg<true>::SMEM_BYTES;
+    cfg.stream = st;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, qgemm_kernel<true>, tm_act, tm_w16, tm_lact, tm_lw, tm_out, p) != cudaSuccess)
+      return RT_ERR_CUDA;
+  } else {
+    qgemm_kernel<false><<<grid, QG_THREADS, QCfg<false>::SMEM_BYTES, st>>>(tm_act, tm_w16, tm_lact, tm_lw, tm_out, p);
+  }
   RT_COUNT_LAUNCH(1);
+#ifdef RT_B200_QPROF
+  {
+    static long long host[512 * 16];
+    cudaMemcpyAsync(host, prof_dev, sizeof(host), cudaMemcpyDeviceToHost, st);
+    cudaStreamSynchronize(st);
+    double sum[16] = {0};
+    for (int c = 0; c < grid; ++c)
+      for (int q = 0; q < 16; ++q) sum[q] += (double)host[c * 16 + q] / ((q >= 4 && q < 8 && pair) ? grid / 2 : grid);
+    fprintf(stderr, "qprof pair=%d dir=%d TN=%d grid=%d | prod: stage_empty %.0f raw_empty %.0f total %.0f | mma: acc_empty %.0f full %.0f w_ready %.0f total %.0f | unpack: stage_empty %.0f raw_full %.0f work %.0f total %.0f | epi: acc_full %.0f total %.0f = %.0f ns -> %.0f MHz\n",
+            (int)pair, a.dir, p.TN, grid, sum[0], sum[1], sum[3], sum[4], sum[5], sum[6], sum[7], sum[8], sum[9], sum[10], sum[11], sum[12], sum[15], sum[14], sum[15] / sum[14] * 1e3);
+  }
+#endif
   if (p.part) {
     const size_t n = (size_t)a.M * out_rows;
     const size_t s_tok = a.tok_mode ? a.out_s_tok : (size_t)p.ld_out, s_row = a.tok_mode ? a.out_s_row : 1;

@@ -20,9 +20,10 @@ MATMUL_TOL = 2e-3
 
 
 def _shapes(t):
+    pair = [(1024, 512, 2500), (512, 512, 5001)]  # enough 256-row tiles for the CTA-pair kernel
     if t in (Q.Q4_K, Q.Q6_K):
-        return [(128, 256, 40), (384, 512, 300), (1024, 1024, 513)]
-    return [(128, 64, 1), (256, 128, 100), (192, 96, 7), (896, 896, 300), (1024, 1024, 513)]
+        return [(128, 256, 40), (384, 512, 300), (1024, 1024, 513)] + pair
+    return [(128, 64, 1), (256, 128, 100), (192, 96, 7), (896, 896, 300), (1024, 1024, 513)] + pair
 
 
 @pytest.mark.parametrize("t", FORMATS, ids=[Q.NAMES[t] for t in FORMATS])

@@ -14,7 +14,10 @@ from rust_trainer_b200 import quants as Q
 pytestmark = pytest.mark.gpu
 
 CASES = [(Q.Q4_0, 256, 128, 50, 8), (Q.Q8_0, 3072, 1024, 700, 16), (Q.Q6_K, 512, 1024, 300, 32),
-         (Q.F16, 384, 256, 100, 16), (Q.BF16, 256, 256, 65, 4), (Q.Q4_K, 1024, 768, 257, 16), (Q.Q8_0, 128, 896, 1, 64)]
+         (Q.F16, 384, 256, 100, 16), (Q.BF16, 256, 256, 65, 4), (Q.Q4_K, 1024, 768, 257, 16), (Q.Q8_0, 128, 896, 1, 64),
+         # enough 256-row tiles for the CTA-pair kernel, ragged token counts, packed and 16-bit weights
+         (Q.Q8_0, 1024, 512, 2500, 16), (Q.Q4_0, 512, 512, 5001, 8), (Q.F16, 768, 512, 3300, 16),
+         (Q.Q6_K, 512, 1024, 4999, 32), (Q.Q4_K, 1280, 256, 2047, 64)]
 
 
 def _make(ctx, rng, t, n, k, r, bias=True):
