@@ -330,7 +330,7 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
         "config": {"workload": args.workload, "model": wl["preset"], "quant": wl["quant"], "global_batch": wl["n_seq"] * world,
                    "seq_len": wl["seq_len"], "answer_targets_per_seq": wl["seq_len"] - answer_start, "lora_rank": wl["rank"],
-                   "lora_params": n_params, "parallelism": f"dp{world}", "recompute": True,
+                   "lora_params": n_params, "parallelism": f"dp{world}", "recompute": bool(model.checkpointing),
                    "l2": "activations and logits per step (>1 GB) exceed the 126 MB L2; no explicit flush",
                    "lora_init": spec.describe()["lora_init"], "seeds": {"weights": 0, "lora": 1234, "tokens": 100}},
         "roofline": roofline, "cpu_baseline": cpu,
@@ -377,12 +377,12 @@ def run_microbench(args):
         for name, fn in (("fwd", lambda: L.rt_frozen_forward_dev(f._h, x.data_ptr(), 2, M, y.data_ptr(), 2, 0)),
                          ("bwd", lambda: L.rt_frozen_backward_input_dev(f._h, dy.data_ptr(), 2, M, dx.data_ptr(), 0, 0))):
             for _ in range(3):
-                fn()
+                ctx.check(fn())
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
             for _ in range(args.steps):
-                fn()
+                ctx.check(fn())
             e1.record(stream)
             torch.cuda.synchronize()
             ctx.synchronize()

@@ -231,6 +231,13 @@ rt_status rt_model_stage_batch(rt_model* m, const int32_t* tokens, const int32_t
                                int32_t n_targets);
 rt_status rt_model_run_staged(rt_model* m, int backward);
 rt_status rt_model_read_results(rt_model* m, float* logp_out, int32_t n_targets, int32_t* hits_out);
+/* Model.checkpointing (src/model.rs:299, 663-684).  mode 1: keep only each block's input and
+ * run the block's forward again before its backward (the reference's default); mode 0: keep
+ * every block's caches from the forward; mode -1 (the default here): keep the caches when
+ * they fit in 60 % of the free device memory, else recompute.  The same results either way.
+ * rt_model_checkpointing reports the mode the last staged batch used (0 or 1). */
+rt_status rt_model_set_checkpointing(rt_model* m, int32_t mode);
+int32_t rt_model_checkpointing(const rt_model* m);
 /* The flat f32 gradient buffer on the device, [A_0 | B_0 | A_1 | B_1 ...] in parameter order:
  * what a data-parallel host all-reduces (sum) across ranks before rt_optim_step. */
 rt_status rt_model_grad_buffer(rt_model* m, void** grads_dev_out, size_t* n_floats_out);

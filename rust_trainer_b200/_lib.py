@@ -105,6 +105,8 @@ def _declare(L: C.CDLL) -> None:
         "rt_ctx_set_profiling": (i32, [vp, C.c_int]),
         "rt_ctx_profile_read": (i32, [vp, C.POINTER(u64), C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
         "rt_model_grad_buffer": (i32, [vp, C.POINTER(vp), C.POINTER(sz)]),
+        "rt_model_set_checkpointing": (i32, [vp, i32]),
+        "rt_model_checkpointing": (i32, [vp]),
         "rt_optim_step": (i32, [vp] + [C.c_float] * 6 + [f32p]),
         "rt_optim_state_read": (i32, [vp, C.POINTER(u64), f32p, f32p]),
         "rt_optim_state_write": (i32, [vp, u64, f32p, f32p]),

@@ -650,6 +650,15 @@ rt_status rt_model_zero_grad(rt_model* m) {
   return RT_OK;
 }
 
+rt_status rt_model_set_checkpointing(rt_model* m, int32_t mode) {
+  if (!m || mode < -1 || mode > 1) return RT_ERR_BAD_ARG;
+  m->recompute_policy = mode < 0 ? 0 : (mode == 1 ? 1 : 2);
+  m->cap_tokens = 0;  // the next batch decides again and sizes the buffers for its mode
+  return RT_OK;
+}
+
+int32_t rt_model_checkpointing(const rt_model* m) { return (m && m->store_acts) ? 0 : 1; }
+
 rt_status rt_model_grad_buffer(rt_model* m, void** p, size_t* n) {
   if (!m || !p || !n) return RT_ERR_BAD_ARG;
   *p = m->G.p;
@@ -663,14 +672,31 @@ static bool ensure_tokens(rt_model* m, int M) {
   const rt_model_config& g = m->cfg;
   const size_t d = g.hidden, ff = g.ff, qd = (size_t)g.n_heads * g.head_dim, kvd = (size_t)g.n_kv_heads * g.head_dim;
   const size_t T = (size_t)M;
+  // per-layer bytes of everything a block's backward reads from its forward
+  const size_t per_layer = T * (d * 2 * 2 + qd * 4 + kvd * 4 + qd * 2 * 2 + kvd * 2 * 2 + (size_t)g.n_heads * 4 + d * 4 + ff * 2 * 3 + 7 * 64 * 2);
+  if (m->recompute_policy < 0) {
+    const char* e = getenv("RT_B200_RECOMPUTE");
+    m->recompute_policy = (e && e[0] == '1') ? 1 : 0;
+  }
+  m->store_acts = m->recompute_policy == 2;
+  if (m->recompute_policy == 0 && g.n_layers > 1) {
+    size_t free_b = 0, total_b = 0;
+    if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
+      const size_t held = m->n1.bytes + m->n2.bytes + m->q_raw.bytes + m->k_raw.bytes + m->q16.bytes + m->k16.bytes + m->v16.bytes +
+                          m->o16.bytes + m->lse.bytes + m->h.bytes + m->g16.bytes + m->u16.bytes + m->hm16.bytes;
+      const size_t need = per_layer * g.n_layers;
+      m->store_acts = need <= held || (double)(need - held) <= 0.6 * (double)free_b;
+    }
+  }
+  const size_t L = m->store_acts ? (size_t)g.n_layers : 1;
   bool ok = true;
   ok &= m->tokens.reserve(T * 4) && m->pos.reserve(T * 4) && m->seq_start.reserve(T * 4);
-  ok &= m->x.reserve(T * d * 4) && m->ckpt.reserve(T * d * 4 * g.n_layers) && m->h.reserve(T * d * 4);
-  ok &= m->n1.reserve(T * d * 2) && m->n2.reserve(T * d * 2);
-  ok &= m->q_raw.reserve(T * qd * 4) && m->k_raw.reserve(T * kvd * 4) && m->v_raw.reserve(T * kvd * 4);
-  ok &= m->q16.reserve(T * qd * 2) && m->k16.reserve(T * kvd * 2) && m->v16.reserve(T * kvd * 2) && m->o16.reserve(T * qd * 2);
-  ok &= m->lse.reserve(T * g.n_heads * 4) && m->delta.reserve(T * g.n_heads * 4);
-  ok &= m->g16.reserve(T * ff * 2) && m->u16.reserve(T * ff * 2) && m->hm16.reserve(T * ff * 2);
+  ok &= m->x.reserve(T * d * 4) && m->ckpt.reserve(T * d * 4 * g.n_layers) && m->h.reserve(T * d * 4 * L);
+  ok &= m->n1.reserve(T * d * 2 * L) && m->n2.reserve(T * d * 2 * L);
+  ok &= m->q_raw.reserve(T * qd * 4 * L) && m->k_raw.reserve(T * kvd * 4 * L) && m->v_raw.reserve(T * kvd * 4);
+  ok &= m->q16.reserve(T * qd * 2 * L) && m->k16.reserve(T * kvd * 2 * L) && m->v16.reserve(T * kvd * 2 * L) && m->o16.reserve(T * qd * 2 * L);
+  ok &= m->lse.reserve(T * g.n_heads * 4 * L) && m->delta.reserve(T * g.n_heads * 4);
+  ok &= m->g16.reserve(T * ff * 2 * L) && m->u16.reserve(T * ff * 2 * L) && m->hm16.reserve(T * ff * 2 * L);
   ok &= m->dx.reserve(T * d * 4) && m->dy16.reserve(T * d * 2) && m->sc_y.reserve(T * 4);
   ok &= m->dhm.reserve(T * ff * 4) && m->dg16.reserve(T * ff * 2) && m->du16.reserve(T * ff * 2);
   ok &= m->sc_g.reserve(T * 4) && m->sc_u.reserve(T * 4) && m->dn.reserve(T * d * 4);
@@ -678,9 +704,37 @@ static bool ensure_tokens(rt_model* m, int M) {
   ok &= m->dq.reserve(T * qd * 4) && m->dk.reserve(T * kvd * 4) && m->dv.reserve(T * kvd * 4);
   ok &= m->dq16.reserve(T * qd * 2) && m->dk16.reserve(T * kvd * 2) && m->dv16.reserve(T * kvd * 2);
   ok &= m->sc_q.reserve(T * 4) && m->sc_k.reserve(T * 4) && m->sc_v.reserve(T * 4);
-  for (int i = 0; i < 7; ++i) ok &= m->hs_keep[i].reserve(T * 64 * 2, true);  // zero beyond the rank, kept that way
+  for (int i = 0; i < 7; ++i) ok &= m->hs_keep[i].reserve(T * 64 * 2 * L, true);  // zero beyond the rank, kept that way
   if (ok) m->cap_tokens = M;
   return ok;
+}
+
+// One layer's view of the forward state its backward reads.  When every layer's state is kept,
+// layer li owns the li-th slice (of M tokens) of each buffer; otherwise all layers share slice 0.
+struct BlockActs {
+  __half *n1, *n2, *q16, *k16, *v16, *o16, *g16, *u16, *hm16, *hs[7];
+  float *q_raw, *k_raw, *h, *lse;
+};
+static BlockActs block_acts(rt_model* m, int li, int M, bool own_slice) {
+  const rt_model_config& g = m->cfg;
+  const size_t d = g.hidden, ff = g.ff, qd = (size_t)g.n_heads * g.head_dim, kvd = (size_t)g.n_kv_heads * g.head_dim;
+  const size_t o = own_slice ? (size_t)li * (size_t)M : 0;
+  BlockActs a;
+  a.n1 = m->n1.as<__half>() + o * d;
+  a.n2 = m->n2.as<__half>() + o * d;
+  a.q16 = m->q16.as<__half>() + o * qd;
+  a.k16 = m->k16.as<__half>() + o * kvd;
+  a.v16 = m->v16.as<__half>() + o * kvd;
+  a.o16 = m->o16.as<__half>() + o * qd;
+  a.g16 = m->g16.as<__half>() + o * ff;
+  a.u16 = m->u16.as<__half>() + o * ff;
+  a.hm16 = m->hm16.as<__half>() + o * ff;
+  for (int i = 0; i < 7; ++i) a.hs[i] = m->hs_keep[i].as<__half>() + o * 64;
+  a.q_raw = m->q_raw.as<float>() + o * qd;
+  a.k_raw = m->k_raw.as<float>() + o * kvd;
+  a.h = m->h.as<float>() + o * d;
+  a.lse = m->lse.as<float>() + o * g.n_heads;
+  return a;
 }
 
 static bool ensure_targets(rt_model* m, int n, bool backward) {
@@ -728,43 +782,42 @@ static rt_status ensure_rope(rt_model* m, int max_pos) {
 
 
 // Block::forward (src/model.rs:165-183).  x_in is read only; h receives x_in + attention;
-// when x_out is non-null it receives the block output (h + mlp), and may alias h.
-static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, float* h, float* x_out) {
+// when x_out is non-null it receives the block output (h + mlp), and may alias h.  With `keep`
+// the adapters' Hs = X.(sA)^T are left in A.hs for the block's backward.
+static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, float* h, float* x_out, const BlockActs& A,
+                               bool keep) {
   rt_ctx* c = m->ctx;
   const rt_model_config& g = m->cfg;
   BlockDev& b = m->blocks[li];
   cudaStream_t st = c->stream;
   const int d = g.hidden;
-  const bool keep = x_out == nullptr;  // the recompute pass: its Hs are reused by block_backward
-  launch_rmsnorm_fwd(x_in, b.input_norm, M, d, g.rms_eps, m->n1.as<__half>(), st);
-  RT_TRY(linear_forward_dev(b.lin[0], m->lsc, m->n1.as<__half>(), M, m->q_raw.p, RT_DT_F32, 0, keep ? m->hs_keep[0].as<__half>() : nullptr));
-  RT_TRY(linear_forward_dev(b.lin[1], m->lsc, m->n1.as<__half>(), M, m->k_raw.p, RT_DT_F32, 0, keep ? m->hs_keep[1].as<__half>() : nullptr));
-  RT_TRY(linear_forward_dev(b.lin[2], m->lsc, m->n1.as<__half>(), M, m->v_raw.p, RT_DT_F32, 0, keep ? m->hs_keep[2].as<__half>() : nullptr));
-  launch_qk_rope_fwd(m->q_raw.as<float>(), m->k_raw.as<float>(), m->v_raw.as<float>(), g.qk_norm ? b.q_norm : nullptr,
+  launch_rmsnorm_fwd(x_in, b.input_norm, M, d, g.rms_eps, A.n1, st);
+  RT_TRY(linear_forward_dev(b.lin[0], m->lsc, A.n1, M, A.q_raw, RT_DT_F32, 0, keep ? A.hs[0] : nullptr));
+  RT_TRY(linear_forward_dev(b.lin[1], m->lsc, A.n1, M, A.k_raw, RT_DT_F32, 0, keep ? A.hs[1] : nullptr));
+  RT_TRY(linear_forward_dev(b.lin[2], m->lsc, A.n1, M, m->v_raw.p, RT_DT_F32, 0, keep ? A.hs[2] : nullptr));
+  launch_qk_rope_fwd(A.q_raw, A.k_raw, m->v_raw.as<float>(), g.qk_norm ? b.q_norm : nullptr,
                      g.qk_norm ? b.k_norm : nullptr, m->pos.as<int>(), m->rope_cos.as<float>(), m->rope_sin.as<float>(), M,
-                     g.n_heads, g.n_kv_heads, g.head_dim, g.rot_dim, g.rope_neox, g.rms_eps, m->q16.as<__half>(),
-                     m->k16.as<__half>(), m->v16.as<__half>(), st);
-  if (launch_attn_fwd(m->q16.as<__half>(), m->k16.as<__half>(), m->v16.as<__half>(), m->seq_start.as<int>(), M, g.n_heads,
-                      g.n_kv_heads, g.head_dim, m->o16.as<__half>(), m->lse.as<float>(), st))
+                     g.n_heads, g.n_kv_heads, g.head_dim, g.rot_dim, g.rope_neox, g.rms_eps, A.q16, A.k16, A.v16, st);
+  if (launch_attn_fwd(A.q16, A.k16, A.v16, m->seq_start.as<int>(), M, g.n_heads, g.n_kv_heads, g.head_dim, A.o16, A.lse, st))
     return c->fail(RT_ERR_CUDA, "attention forward launch failed");
   if (h != x_in) RT_CUDA(c, cudaMemcpyAsync(h, x_in, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
-  RT_TRY(linear_forward_dev(b.lin[3], m->lsc, m->o16.as<__half>(), M, h, RT_DT_F32, 1, keep ? m->hs_keep[3].as<__half>() : nullptr));
-  launch_rmsnorm_fwd(h, b.post_norm, M, d, g.rms_eps, m->n2.as<__half>(), st);
-  RT_TRY(linear_forward_dev(b.lin[4], m->lsc, m->n2.as<__half>(), M, m->g16.p, RT_DT_F16, 0, keep ? m->hs_keep[4].as<__half>() : nullptr));
-  RT_TRY(linear_forward_dev(b.lin[5], m->lsc, m->n2.as<__half>(), M, m->u16.p, RT_DT_F16, 0, keep ? m->hs_keep[5].as<__half>() : nullptr));
-  launch_swiglu_fwd(m->g16.as<__half>(), m->u16.as<__half>(), m->hm16.as<__half>(), (size_t)M * g.ff, st);
+  RT_TRY(linear_forward_dev(b.lin[3], m->lsc, A.o16, M, h, RT_DT_F32, 1, keep ? A.hs[3] : nullptr));
+  launch_rmsnorm_fwd(h, b.post_norm, M, d, g.rms_eps, A.n2, st);
+  RT_TRY(linear_forward_dev(b.lin[4], m->lsc, A.n2, M, A.g16, RT_DT_F16, 0, keep ? A.hs[4] : nullptr));
+  RT_TRY(linear_forward_dev(b.lin[5], m->lsc, A.n2, M, A.u16, RT_DT_F16, 0, keep ? A.hs[5] : nullptr));
+  launch_swiglu_fwd(A.g16, A.u16, A.hm16, (size_t)M * g.ff, st);
   if (x_out) {
     if (x_out != h) RT_CUDA(c, cudaMemcpyAsync(x_out, h, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
-    RT_TRY(linear_forward_dev(b.lin[6], m->lsc, m->hm16.as<__half>(), M, x_out, RT_DT_F32, 1));
-  } else if (b.lin[6]->lora_active()) {
-    RT_TRY(linear_lora_h(b.lin[6], m->hm16.as<__half>(), M, m->hs_keep[6].as<__half>()));  // the backward needs it
+    RT_TRY(linear_forward_dev(b.lin[6], m->lsc, A.hm16, M, x_out, RT_DT_F32, 1, keep ? A.hs[6] : nullptr));
+  } else if (keep && b.lin[6]->lora_active()) {
+    RT_TRY(linear_lora_h(b.lin[6], A.hm16, M, A.hs[6]));  // the backward needs it
   }
   return RT_OK;
 }
 
 // Block::backward (src/model.rs:185-197).  On entry dx holds the gradient of the block output
 // and (dy16, sc_y) its row-normalised f16 copy; on exit both describe the block input's.
-static rt_status block_backward(rt_model* m, int li, int M, const float* x_in) {
+static rt_status block_backward(rt_model* m, int li, int M, const float* x_in, const BlockActs& A) {
   rt_ctx* c = m->ctx;
   const rt_model_config& g = m->cfg;
   BlockDev& b = m->blocks[li];
@@ -773,31 +826,31 @@ static rt_status block_backward(rt_model* m, int li, int M, const float* x_in) {
   float* dx = m->dx.as<float>();
   __half* dy16 = m->dy16.as<__half>();
   float* sc_y = m->sc_y.as<float>();
-#define HS(i) (b.lin[i]->lora_active() ? m->hs_keep[i].as<__half>() : nullptr)
+#define HS(i) (b.lin[i]->lora_active() ? A.hs[i] : nullptr)
   // Mlp::backward (src/model.rs:120-134)
-  RT_TRY(linear_backward_dev(b.lin[6], m->lsc, m->hm16.as<__half>(), dy16, sc_y, M, m->dhm.as<float>(), 0, HS(6)));
-  launch_swiglu_bwd(m->dhm.as<float>(), m->g16.as<__half>(), m->u16.as<__half>(), M, g.ff, m->dg16.as<__half>(),
+  RT_TRY(linear_backward_dev(b.lin[6], m->lsc, A.hm16, dy16, sc_y, M, m->dhm.as<float>(), 0, HS(6)));
+  launch_swiglu_bwd(m->dhm.as<float>(), A.g16, A.u16, M, g.ff, m->dg16.as<__half>(),
                     m->du16.as<__half>(), m->sc_g.as<float>(), m->sc_u.as<float>(), st);
-  RT_TRY(linear_backward_dev(b.lin[4], m->lsc, m->n2.as<__half>(), m->dg16.as<__half>(), m->sc_g.as<float>(), M, m->dn.as<float>(), 0, HS(4)));
-  RT_TRY(linear_backward_dev(b.lin[5], m->lsc, m->n2.as<__half>(), m->du16.as<__half>(), m->sc_u.as<float>(), M, m->dn.as<float>(), 1, HS(5)));
+  RT_TRY(linear_backward_dev(b.lin[4], m->lsc, A.n2, m->dg16.as<__half>(), m->sc_g.as<float>(), M, m->dn.as<float>(), 0, HS(4)));
+  RT_TRY(linear_backward_dev(b.lin[5], m->lsc, A.n2, m->du16.as<__half>(), m->sc_u.as<float>(), M, m->dn.as<float>(), 1, HS(5)));
   // dh = dy + rmsnorm_backward(h, post_norm, dn2)
-  launch_rmsnorm_bwd(m->h.as<float>(), b.post_norm, m->dn.as<float>(), dx, M, d, g.rms_eps, dx, dy16, sc_y, st);
+  launch_rmsnorm_bwd(A.h, b.post_norm, m->dn.as<float>(), dx, M, d, g.rms_eps, dx, dy16, sc_y, st);
   // Attention::backward (src/attention.rs:246-367)
-  RT_TRY(linear_backward_dev(b.lin[3], m->lsc, m->o16.as<__half>(), dy16, sc_y, M, m->d_o.as<float>(), 0, HS(3)));
+  RT_TRY(linear_backward_dev(b.lin[3], m->lsc, A.o16, dy16, sc_y, M, m->d_o.as<float>(), 0, HS(3)));
   const size_t nqd = (size_t)M * g.n_heads * g.head_dim;
   launch_global_normalize(m->d_o.as<float>(), nqd, m->amax.as<float>(), m->dO16.as<__half>(), st);
-  if (launch_attn_bwd(m->q16.as<__half>(), m->k16.as<__half>(), m->v16.as<__half>(), m->o16.as<__half>(), m->dO16.as<__half>(),
-                      m->amax.as<float>(), m->lse.as<float>(), m->seq_start.as<int>(), M, g.n_heads, g.n_kv_heads, g.head_dim,
+  if (launch_attn_bwd(A.q16, A.k16, A.v16, A.o16, m->dO16.as<__half>(),
+                      m->amax.as<float>(), A.lse, m->seq_start.as<int>(), M, g.n_heads, g.n_kv_heads, g.head_dim,
                       m->delta.as<float>(), m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>(), st))
     return c->fail(RT_ERR_CUDA, "attention backward launch failed");
-  launch_qk_rope_bwd(m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>(), m->q_raw.as<float>(), m->k_raw.as<float>(),
+  launch_qk_rope_bwd(m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>(), A.q_raw, A.k_raw,
                      g.qk_norm ? b.q_norm : nullptr, g.qk_norm ? b.k_norm : nullptr, m->pos.as<int>(), m->rope_cos.as<float>(),
                      m->rope_sin.as<float>(), M, g.n_heads, g.n_kv_heads, g.head_dim, g.rot_dim, g.rope_neox, g.rms_eps,
                      m->dq16.as<__half>(), m->dk16.as<__half>(), m->dv16.as<__half>(), m->sc_q.as<float>(), m->sc_k.as<float>(),
                      m->sc_v.as<float>(), st);
-  RT_TRY(linear_backward_dev(b.lin[0], m->lsc, m->n1.as<__half>(), m->dq16.as<__half>(), m->sc_q.as<float>(), M, m->dn.as<float>(), 0, HS(0)));
-  RT_TRY(linear_backward_dev(b.lin[1], m->lsc, m->n1.as<__half>(), m->dk16.as<__half>(), m->sc_k.as<float>(), M, m->dn.as<float>(), 1, HS(1)));
-  RT_TRY(linear_backward_dev(b.lin[2], m->lsc, m->n1.as<__half>(), m->dv16.as<__half>(), m->sc_v.as<float>(), M, m->dn.as<float>(), 1, HS(2)));
+  RT_TRY(linear_backward_dev(b.lin[0], m->lsc, A.n1, m->dq16.as<__half>(), m->sc_q.as<float>(), M, m->dn.as<float>(), 0, HS(0)));
+  RT_TRY(linear_backward_dev(b.lin[1], m->lsc, A.n1, m->dk16.as<__half>(), m->sc_k.as<float>(), M, m->dn.as<float>(), 1, HS(1)));
+  RT_TRY(linear_backward_dev(b.lin[2], m->lsc, A.n1, m->dv16.as<__half>(), m->sc_v.as<float>(), M, m->dn.as<float>(), 1, HS(2)));
   // dx = dh + rmsnorm_backward(x, input_norm, dn1)
   launch_rmsnorm_bwd(x_in, b.input_norm, m->dn.as<float>(), dx, M, d, g.rms_eps, dx, dy16, sc_y, st);
 #undef HS
@@ -887,9 +940,12 @@ static rt_status run_staged_body(rt_model* m, bool backward, float* logits_out_h
   const size_t xd = (size_t)M * g.hidden;
   float* x = m->x.as<float>();
   launch_gather_rows(m->embed->w, m->tokens.as<int>(), M, x, c->status_dev, st);
+  const bool store = backward && m->store_acts;
   for (int li = 0; li < g.n_layers; ++li) {
     if (backward) RT_CUDA(c, cudaMemcpyAsync(m->ckpt.as<float>() + (size_t)li * xd, x, xd * 4, cudaMemcpyDeviceToDevice, st));
-    RT_TRY(block_forward(m, li, M, x, x, x));
+    const BlockActs A = block_acts(m, li, M, store);
+    if (store) RT_TRY(block_forward(m, li, M, m->ckpt.as<float>() + (size_t)li * xd, A.h, x, A, true));  // keeps h and every Hs
+    else RT_TRY(block_forward(m, li, M, x, x, x, A, false));
   }
   if (backward) RT_CUDA(c, cudaMemsetAsync(m->dx.p, 0, xd * 4, st));
   if (n_targets > 0) RT_TRY(model_head(m, M, n_targets, backward, logits_out_host));
@@ -898,8 +954,9 @@ static rt_status run_staged_body(rt_model* m, bool backward, float* logits_out_h
   launch_normalize_rows(m->dx.as<float>(), M, g.hidden, m->dy16.as<__half>(), m->sc_y.as<float>(), st);
   for (int li = g.n_layers - 1; li >= 0; --li) {
     const float* x_in = m->ckpt.as<float>() + (size_t)li * xd;
-    RT_TRY(block_forward(m, li, M, x_in, m->h.as<float>(), nullptr));  // recompute the block's caches
-    RT_TRY(block_backward(m, li, M, x_in));
+    const BlockActs A = block_acts(m, li, M, store);
+    if (!store) RT_TRY(block_forward(m, li, M, x_in, A.h, nullptr, A, true));  // rebuild the block's caches
+    RT_TRY(block_backward(m, li, M, x_in, A));
   }
   return RT_OK;
 }
@@ -918,6 +975,7 @@ static uint64_t buffer_signature(rt_model* m) {
   for (int i = 0; i < 7; ++i) mix(m->hs_keep[i].p);
   for (int i = 0; i < 4; ++i) mix(m->ctx->scratch[i]);
   mix((const void*)(uintptr_t)m->n_params);
+  mix((const void*)(uintptr_t)(m->store_acts ? 1 : 0));
   for (auto& b : m->blocks)
     for (int i = 0; i < 7; ++i) mix((const void*)(uintptr_t)(b.lin[i]->lora_active() ? b.lin[i]->lora.rank : 0));
   return h;

@@ -88,7 +88,13 @@ struct rt_model {
   int rope_max_pos = 0;
 
   LinearScratch lsc;
-  DevBuf hs_keep[7];  // Hs of the current block's seven linears, kept from the recompute for the backward
+  DevBuf hs_keep[7];  // Hs of a block's seven linears, kept from the forward (or its recompute) for the backward
+  // What a block's backward needs from its forward is either kept for every layer (180 GB of HBM
+  // holds it for the usual fine-tuning shapes) or rebuilt by running the block's forward again
+  // just before its backward.  Decided when the token capacity grows; RT_B200_RECOMPUTE=1 forces
+  // the second.
+  bool store_acts = false;
+  int recompute_policy = -1;  // -1: not read yet, 0: automatic, 1: always recompute, 2: always keep
   // activations, sized for `cap_tokens`
   int cap_tokens = 0, cap_targets = 0, cap_head_rows = 0;
   DevBuf tokens, pos, seq_start, x, ckpt, h, n1, n2, q_raw, k_raw, v_raw, q16, k16, v16, o16, lse, delta, g16, u16, hm16;

@@ -55,16 +55,18 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait. Returns false (and records `code` in *status) after ~2 s.
+// Bounded wait. Returns false (and records `code` in *status) after ~4e9 SM cycles (about two
+// seconds).  The bound counts this SM's own cycle counter, which nothing outside the kernel can
+// step or re-synchronise.
 template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = globaltimer_ns();
+  const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
       if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
-    if (globaltimer_ns() - t0 > 2000000000ull) {
+    if (clock64() - t0 > 4000000000ll) {
       atomicCAS(status, 0, code);
       return false;
     }

@@ -68,6 +68,16 @@ class Model:
     def zero_grad(self) -> None:
         self.ctx.check(lib().rt_model_zero_grad(self._h))
 
+    def set_checkpointing(self, mode: int) -> None:
+        """Model.checkpointing (src/model.rs:299): 1 = recompute each block before its backward,
+        0 = keep every block's caches, -1 = keep them when they fit in device memory."""
+        self.ctx.check(lib().rt_model_set_checkpointing(self._h, int(mode)))
+
+    @property
+    def checkpointing(self) -> bool:
+        """The mode the last staged batch used."""
+        return bool(lib().rt_model_checkpointing(self._h))
+
     def trainable_params(self) -> int:
         return self.grad_buffer()[1]
 

@@ -152,6 +152,31 @@ def test_reruns_are_bit_identical_and_batching_is_neutral(ctx):
     om.close()
 
 
+def test_checkpointing_modes_agree(ctx):
+    """Model.checkpointing (src/model.rs:663-684): keeping every block's caches or rebuilding
+    them before the backward runs the same kernels on the same data, so the results are equal
+    to the bit."""
+    spec, om, gm = _setup(ctx, "tiny-qwen3", "Q4_0")
+    seqs, tp, tt, per_seq = _batch(spec, [90, 41, 64], seed=9)
+    w = np.full(tp.size, 1.0 / tp.size, np.float32)
+    out = {}
+    for mode in (1, 0, -1):
+        gm.set_checkpointing(mode)
+        gm.zero_grad()
+        lp, _ = gm.forward_backward(seqs, tp, tt, w)
+        gm.zero_grad()
+        lp, _ = gm.forward_backward(seqs, tp, tt, w)  # the second run of a shape replays its CUDA graph
+        out[mode] = (lp, _gpu_flat(gm, "ga", "gb"), gm.checkpointing)
+    assert out[1][2] is True and out[0][2] is False and out[-1][2] is False  # tiny model: the caches fit
+    for mode in (0, -1):
+        assert np.array_equal(out[mode][0], out[1][0]) and np.array_equal(out[mode][1], out[1][1])
+    lp_o = _oracle_step(om, seqs, per_seq, w)
+    assert np.max(np.abs(out[0][0] - lp_o) / np.abs(lp_o)) < LOSS_TOL
+    assert rel_l2(out[0][1], _flat(om.lora, "ga", "gb")) < GRAD_TOL
+    gm.close()
+    om.close()
+
+
 def test_adapter_disabled_and_attach_semantics(ctx):
     spec, om, gm = _setup(ctx, "tiny-qwen2", "Q4_0")
     seqs, tp, tt, per_seq = _batch(spec, [40], seed=2)
