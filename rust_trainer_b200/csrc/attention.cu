@@ -248,12 +248,16 @@ template <int HD>
 __global__ void __launch_bounds__(128)
 attn_bwd_dkdv_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const __half* __restrict__ v,
                      const __half* __restrict__ dO, const float* __restrict__ do_scale,
+                     const float* __restrict__ row_scale,
                      const float* __restrict__ lse, const float* __restrict__ delta,
                      const int* __restrict__ seq_start, int M, int nh, int nkv, float scale, float* __restrict__ dk,
                      float* __restrict__ dv) {
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sK = smem_addr(smem), sV = sK + BT * HD * 2, sQdO = sV + BT * HD * 2;  // then two (Q, dO) buffers
-  float* sAux = (float*)(smem + 6 * BT * HD * 2);  // two buffers of (lse, delta, seq_start) per query row
+  float* sAux = (float*)(smem + 6 * BT * HD * 2);  // two buffers of (lse, delta, seq_start, weight) per query row
+  // dO row i stands for row_scale[i] * dO[i] (do_scale[0] = the largest factor): a query row
+  // enters the sums over queries with weight row_scale[i] / do_scale[0] <= 1
+  const float inv_top = row_scale ? 1.0f / fmaxf(do_scale[0], 1e-38f) : 1.0f;
   const int n0 = blockIdx.x * BT, g = blockIdx.y, group = nh / nkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
   const float sl2 = scale * LOG2E;
@@ -289,10 +293,11 @@ attn_bwd_dkdv_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
     load_tile<HD>(sQdO + buf * 2 * BT * HD * 2 + BT * HD * 2, dO, m0, M, nh, h);
     if (threadIdx.x < BT) {
       const int m = m0 + threadIdx.x;
-      float* aux = sAux + buf * 3 * BT;
+      float* aux = sAux + buf * 4 * BT;
       aux[threadIdx.x] = m < M ? lse[(size_t)h * M + m] * LOG2E : 0.f;
       aux[BT + threadIdx.x] = m < M ? delta[(size_t)h * M + m] : 0.f;
       ((int*)aux)[2 * BT + threadIdx.x] = m < M ? seq_start[m] : 0x7fffffff;
+      aux[3 * BT + threadIdx.x] = (row_scale && m < M) ? row_scale[m] * inv_top : 1.0f;
     }
   };
   if (n_work > 0) prefetch(0, 0);
@@ -302,9 +307,10 @@ attn_bwd_dkdv_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
       const int m0 = n0 + (idx % nqt) * BT;
       const int buf = idx & 1;
       const uint32_t sQ = sQdO + buf * 2 * BT * HD * 2, sdO = sQ + BT * HD * 2;
-      const float* sLse = sAux + buf * 3 * BT;
+      const float* sLse = sAux + buf * 4 * BT;
       const float* sDel = sLse + BT;
       const int* sSS = (const int*)(sLse + 2 * BT);
+      const float* sWt = sLse + 3 * BT;
       if (idx + 1 < n_work) prefetch(idx + 1, buf ^ 1);
       cp_async_commit();
       cp_async_wait_prev();
@@ -343,7 +349,7 @@ attn_bwd_dkdv_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
             const int i = m0 + il;
             const int j = (e < 2) ? j0 : j1;
             const bool ok = i < M && j <= i && j >= sSS[il];
-            const float p = ok ? exp2f(st[nt][e] * sl2 - sLse[il]) : 0.f;
+            const float p = ok ? exp2f(st[nt][e] * sl2 - sLse[il]) * sWt[il] : 0.f;
             st[nt][e] = p;
             dp[nt][e] = p * (dp[nt][e] - sDel[il]) * scale;
           }
@@ -388,7 +394,8 @@ attn_bwd_dkdv_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
 template <int HD>
 __global__ void __launch_bounds__(128)
 attn_bwd_dq_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const __half* __restrict__ v,
-                   const __half* __restrict__ dO, const float* __restrict__ do_scale, const float* __restrict__ lse,
+                   const __half* __restrict__ dO, const float* __restrict__ do_scale, const float* __restrict__ row_scale,
+                   const float* __restrict__ lse,
                    const float* __restrict__ delta, const int* __restrict__ seq_start, int M, int nh, int nkv,
                    float scale, float* __restrict__ dq) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -472,12 +479,14 @@ attn_bwd_dq_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
     }
     __syncthreads();
   }
-  const float sc = do_scale[0];
+  // a query row's gradient carries only that row's factor
+  const float sc0 = row_scale ? (i0 < M ? row_scale[i0] : 0.f) : do_scale[0];
+  const float sc1 = row_scale ? (i1 < M ? row_scale[i1] : 0.f) : do_scale[0];
 #pragma unroll
   for (int nt = 0; nt < HD / 8; ++nt) {
     const int c = nt * 8 + 2 * tq;
-    if (i0 < M) *(float2*)(dq + ((size_t)i0 * nh + h) * HD + c) = make_float2(acc[nt][0] * sc, acc[nt][1] * sc);
-    if (i1 < M) *(float2*)(dq + ((size_t)i1 * nh + h) * HD + c) = make_float2(acc[nt][2] * sc, acc[nt][3] * sc);
+    if (i0 < M) *(float2*)(dq + ((size_t)i0 * nh + h) * HD + c) = make_float2(acc[nt][0] * sc0, acc[nt][1] * sc0);
+    if (i1 < M) *(float2*)(dq + ((size_t)i1 * nh + h) * HD + c) = make_float2(acc[nt][2] * sc1, acc[nt][3] * sc1);
   }
 }
 
@@ -497,9 +506,9 @@ int fwd_impl(const __half* q, const __half* k, const __half* v, const int* seq_s
 
 template <int HD>
 int bwd_impl(const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO,
-             const float* do_scale, const float* lse, const int* seq_start, int M, int nh, int nkv, float* delta,
-             float* dq, float* dk, float* dv, cudaStream_t st) {
-  const size_t smem_kv = 6 * BT * HD * 2 + 2 * 3 * BT * 4, smem_q = 6 * BT * HD * 2;
+             const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, int M, int nh, int nkv,
+             float* delta, float* dq, float* dk, float* dv, cudaStream_t st) {
+  const size_t smem_kv = 6 * BT * HD * 2 + 2 * 4 * BT * 4, smem_q = 6 * BT * HD * 2;
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(attn_bwd_dkdv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv) != cudaSuccess) return 3;
@@ -510,8 +519,8 @@ int bwd_impl(const __half* q, const __half* k, const __half* v, const __half* o,
   const int warps = M * nh;
   { attn_delta_kernel<HD><<<(warps * 32 + 255) / 256, 256, 0, st>>>(o, dO, M, nh, delta); RT_COUNT_LAUNCH(1); }
   dim3 gkv((M + BT - 1) / BT, nkv), gq((M + BT - 1) / BT, nh);
-  { attn_bwd_dkdv_kernel<HD><<<gkv, 128, smem_kv, st>>>(q, k, v, dO, do_scale, lse, delta, seq_start, M, nh, nkv, scale, dk, dv); RT_COUNT_LAUNCH(1); }
-  { attn_bwd_dq_kernel<HD><<<gq, 128, smem_q, st>>>(q, k, v, dO, do_scale, lse, delta, seq_start, M, nh, nkv, scale, dq); RT_COUNT_LAUNCH(1); }
+  { attn_bwd_dkdv_kernel<HD><<<gkv, 128, smem_kv, st>>>(q, k, v, dO, do_scale, row_scale, lse, delta, seq_start, M, nh, nkv, scale, dk, dv); RT_COUNT_LAUNCH(1); }
+  { attn_bwd_dq_kernel<HD><<<gq, 128, smem_q, st>>>(q, k, v, dO, do_scale, row_scale, lse, delta, seq_start, M, nh, nkv, scale, dq); RT_COUNT_LAUNCH(1); }
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
@@ -526,11 +535,11 @@ int launch_attn_fwd(const __half* q, const __half* k, const __half* v, const int
 }
 
 int launch_attn_bwd(const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
-                    const float* do_scale, const float* lse, const int* seq_start, int M, int nh, int nkv, int hd,
-                    float* delta, float* dq, float* dk, float* dv, cudaStream_t st) {
+                    const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, int M, int nh,
+                    int nkv, int hd, float* delta, float* dq, float* dk, float* dv, cudaStream_t st) {
   if (M <= 0) return 0;
-  if (hd == 128) return bwd_impl<128>(q, k, v, o, dO16, do_scale, lse, seq_start, M, nh, nkv, delta, dq, dk, dv, st);
-  if (hd == 64) return bwd_impl<64>(q, k, v, o, dO16, do_scale, lse, seq_start, M, nh, nkv, delta, dq, dk, dv, st);
+  if (hd == 128) return bwd_impl<128>(q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, M, nh, nkv, delta, dq, dk, dv, st);
+  if (hd == 64) return bwd_impl<64>(q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, M, nh, nkv, delta, dq, dk, dv, st);
   return 1;
 }
 

@@ -213,6 +213,135 @@ __global__ void tok_reduce_kernel(const float* __restrict__ part, int splits, in
   out[i * so_i + j * so_j] += s;
 }
 
+// ------------------------------------------------------------------ both LoRA gradients of one linear in one launch
+// Blocks [0, nbB) of grid.x work on dB (P = Hs, Q = dY, C = N), the rest on dA (P = Gs, Q = X,
+// C = K); grid.y is the token split.  The per-token factors of dY are applied to the rows of the
+// skinny operand relative to the LARGEST FACTOR OF THE SPLIT (found by the block itself), and
+// that maximum multiplies the split's partial sums, so no pass over all factors comes first.
+struct LoraGradArgs {
+  const __half *Pb, *Qb, *Pa, *Qa;  // Hs, dY, Gs, X
+  const float* pscale;              // per-token factors of dY, or null
+  int M, N, K, r, nbB, tokens_per_split;
+  float *partB, *partA;             // [splits][r x N], [splits][r x K]
+};
+
+template <int R16>
+__global__ void __launch_bounds__(128) lora_grads_kernel(const LoraGradArgs g) {
+  constexpr int NST = 3, SB = 8192 + 16384;  // per stage: P chunk, two Q panels
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ float s_red[4];
+  const uint32_t s0 = saddr(smem);
+  const bool isB = (int)blockIdx.x < g.nbB;
+  const __half* P = isB ? g.Pb : g.Pa;
+  const __half* Q = isB ? g.Qb : g.Qa;
+  const int C = isB ? g.N : g.K;
+  const int j0 = (isB ? (int)blockIdx.x : (int)blockIdx.x - g.nbB) * 128;
+  const int m_begin = blockIdx.y * g.tokens_per_split, m_end = min(g.M, m_begin + g.tokens_per_split);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+  const int mat = lane >> 3, rr = lane & 7;
+  const int panel = warp >> 1, cbase = (warp & 1) * 4;
+  float acc[R16][4][4];
+#pragma unroll
+  for (int a = 0; a < R16; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) acc[a][b][0] = acc[a][b][1] = acc[a][b][2] = acc[a][b][3] = 0.f;
+  const int nchunks = (m_end - m_begin + 63) / 64;
+  auto load = [&](int ch, int buf) {
+    const int mrow = m_begin + ch * 64;
+    load64x64(s0 + buf * SB, P, mrow, m_end, 0, 64, 64);
+    load64x64(s0 + buf * SB + 8192, Q, mrow, m_end, j0, C, C);
+    load64x64(s0 + buf * SB + 16384, Q, mrow, m_end, j0 + 64, C, C);
+  };
+  for (int i = 0; i < NST - 1; ++i) {
+    if (i < nchunks) load(i, i);
+    cpa_commit();
+  }
+  // largest factor of this split (factors are >= 0), while the first tiles are in flight
+  float lmax = 1.0f, inv = 1.0f;
+  if (g.pscale) {
+    float v = 0.f;
+    for (int m = m_begin + threadIdx.x; m < m_end; m += 128) v = fmaxf(v, g.pscale[m]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    lmax = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    inv = lmax > 0.f ? 1.0f / lmax : 0.f;
+  }
+  for (int ch = 0; ch < nchunks; ++ch) {
+    const int b = ch % NST;
+    if (ch + NST - 1 < nchunks) load(ch + NST - 1, (ch + NST - 1) % NST);
+    cpa_commit();
+    cpa_wait<NST - 1>();
+    __syncthreads();
+    const uint32_t sP = s0 + b * SB;
+    if (g.pscale) {
+      for (int e = threadIdx.x; e < 64 * 8; e += blockDim.x) {
+        const int row = e >> 3, c = e & 7, mrow = m_begin + ch * 64 + row;
+        const float f = mrow < m_end ? g.pscale[mrow] * inv : 0.f;
+        uint4* ptr = (uint4*)(smem + b * SB + toff(row, c));
+        uint4 v = *ptr;
+        __half2* h2 = (__half2*)&v;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 x = __half22float2(h2[k]);
+          h2[k] = __floats2half2_rn(x.x * f, x.y * f);
+        }
+        *ptr = v;
+      }
+      __syncthreads();
+    }
+    const uint32_t q = sP + 8192 + panel * 8192;
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t bf[2][4];
+#pragma unroll
+      for (int np = 0; np < 2; ++np) ldsm4t(q + toff(kk * 16 + (mat & 1) * 8 + rr, cbase + 2 * np + (mat >> 1)), bf[np]);
+#pragma unroll
+      for (int mi = 0; mi < R16; ++mi) {
+        uint32_t a[4];  // A = P^T: rows i, k = tokens; P is stored [token][i]
+        ldsm4t(sP + toff(kk * 16 + (mat >> 1) * 8 + rr, mi * 2 + (mat & 1)), a);
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {
+          mma(acc[mi][2 * np], a, bf[np]);
+          mma(acc[mi][2 * np + 1], a, bf[np] + 2);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float* dst = (isB ? g.partB : g.partA) + (size_t)blockIdx.y * g.r * C;
+#pragma unroll
+  for (int mi = 0; mi < R16; ++mi)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int j = j0 + warp * 32 + nt * 8 + 2 * tq;
+      const int i0 = mi * 16 + gq, i1 = i0 + 8;
+      if (j < C) {  // C is a multiple of 8, so j + 1 < C too
+        if (i0 < g.r) *(float2*)(dst + (size_t)i0 * C + j) = make_float2(acc[mi][nt][0] * lmax, acc[mi][nt][1] * lmax);
+        if (i1 < g.r) *(float2*)(dst + (size_t)i1 * C + j) = make_float2(acc[mi][nt][2] * lmax, acc[mi][nt][3] * lmax);
+      }
+    }
+}
+
+// gb[n*r + i] += sum_s partB[s][i, n] ; ga[i*K + k] += sum_s partA[s][i, k]   (splits in order: deterministic)
+__global__ void lora_grads_reduce_kernel(const float* __restrict__ partB, const float* __restrict__ partA, int splits, int N,
+                                         int K, int r, float* __restrict__ gb, float* __restrict__ ga) {
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t nB = (size_t)r * N, nA = (size_t)r * K;
+  if (e < nB) {
+    float s = 0.f;
+    for (int k = 0; k < splits; ++k) s += partB[(size_t)k * nB + e];
+    const int i = (int)(e / N), n = (int)(e % N);
+    gb[(size_t)n * r + i] += s;
+  } else if (e < nB + nA) {
+    const size_t f = e - nB;
+    float s = 0.f;
+    for (int k = 0; k < splits; ++k) s += partA[(size_t)k * nA + f];
+    ga[f] += s;
+  }
+}
+
 }  // namespace
 
 int launch_skinny_nt(const __half* X, const __half* Wt, int M, int K, int r, __half* out, cudaStream_t st) {
@@ -258,6 +387,45 @@ int launch_tok_contract(const __half* P, const __half* Q, const float* pscale, i
   else tok_contract_kernel<4><<<grid, 128, TOK_SMEM, st>>>(P, Q, pscale, alpha_dev, M, C, r, tps, workspace);
   const size_t n = (size_t)r * C;
   tok_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(workspace, splits, C, r, so_i, so_j, alpha_dev, out);
+  RT_COUNT_LAUNCH(2);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+size_t lora_grads_workspace_floats(int M, int N, int K, int r) {
+  int tps, splits;
+  tok_plan(M, &tps, &splits);
+  return (size_t)splits * r * ((size_t)N + (size_t)K);
+}
+
+// dB and dA of one linear: two launches in all.  Returns 1 for shapes these kernels do not cover.
+int launch_lora_grads(const __half* hs, const __half* dy16, const __half* gs, const __half* x16, const float* dscale, int M,
+                      int N, int K, int r, float* gb, float* ga, float* workspace, cudaStream_t st) {
+  if (M <= 0) return 0;
+  if (r <= 0 || r > 64 || N % 8 != 0 || K % 8 != 0) return 1;
+  int tps, splits;
+  tok_plan(M, &tps, &splits);
+  LoraGradArgs g;
+  g.Pb = hs; g.Qb = dy16; g.Pa = gs; g.Qa = x16;
+  g.pscale = dscale;
+  g.M = M; g.N = N; g.K = K; g.r = r;
+  g.nbB = (N + 127) / 128;
+  g.tokens_per_split = tps;
+  g.partB = workspace;
+  g.partA = workspace + (size_t)splits * r * N;
+  dim3 grid(g.nbB + (K + 127) / 128, splits);
+  constexpr int TOK_SMEM = 3 * (8192 + 16384);
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(lora_grads_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TOK_SMEM);
+    cudaFuncSetAttribute(lora_grads_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TOK_SMEM);
+    cudaFuncSetAttribute(lora_grads_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, TOK_SMEM);
+    attr = true;
+  }
+  if (r <= 16) lora_grads_kernel<1><<<grid, 128, TOK_SMEM, st>>>(g);
+  else if (r <= 32) lora_grads_kernel<2><<<grid, 128, TOK_SMEM, st>>>(g);
+  else lora_grads_kernel<4><<<grid, 128, TOK_SMEM, st>>>(g);
+  const size_t n = (size_t)r * ((size_t)N + (size_t)K);
+  lora_grads_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g.partB, g.partA, splits, N, K, r, gb, ga);
   RT_COUNT_LAUNCH(2);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }

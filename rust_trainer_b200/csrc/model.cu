@@ -115,9 +115,11 @@ rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16,
 }
 
 rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16, const __half* dy16,
-                              const float* dscale, int M, float* dx, int accumulate, const __half* hs_saved) {
+                              const float* dscale, int M, void* dx, int accumulate, const __half* hs_saved,
+                              bool unscaled_f16_out) {
   rt_ctx* c = l->ctx;
   if (M <= 0) return RT_OK;
+  if (unscaled_f16_out && accumulate) return c->fail(RT_ERR_BAD_ARG, "an unscaled f16 gradient cannot accumulate");
   const int K = l->in_dim(), N = l->out_dim();
   QGemmArgs a;
   a.dir = QG_BWD;
@@ -125,9 +127,9 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
   a.act_f16 = 1;
   a.M = M;
   a.out = dx;
-  a.out_dtype = OUT_F32;
+  a.out_dtype = unscaled_f16_out ? OUT_F16 : OUT_F32;
   a.accumulate = accumulate;
-  a.row_scale = dscale;
+  a.row_scale = unscaled_f16_out ? nullptr : dscale;
   if (l->lora_active()) {
     lora_refresh(l);
     const int r = l->lora.rank;
@@ -156,16 +158,23 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
     // The per-token scales of dY move onto the skinny operand (rows * scale / max), the max onto the result.
     const __half *hs_c = hs, *gs_c = gs;
     const float* alpha = nullptr;
-    if (dscale) {
-      if (!sc.smax.reserve(16)) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
-      launch_rowscale_max(dscale, M, sc.smax.as<float>(), c->stream);
-      alpha = sc.smax.as<float>();
+    const size_t wsf2 = lora_grads_workspace_floats(M, N, K, r);
+    if (!sc.grad_ws.reserve(wsf2 * sizeof(float))) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+    int rb = launch_lora_grads(hs, dy16, gs, x16, dscale, M, N, K, r, l->lora.gb, l->lora.ga, sc.grad_ws.as<float>(), c->stream);
+    if (rb > 1) return c->fail(RT_ERR_CUDA, "lora gradient kernel launch failed");
+    int ra = rb;
+    if (rb == 1) {  // shapes the fused kernels do not cover: one product at a time
+      if (dscale) {
+        if (!sc.smax.reserve(16)) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+        launch_rowscale_max(dscale, M, sc.smax.as<float>(), c->stream);
+        alpha = sc.smax.as<float>();
+      }
+      const size_t wsf = tok_contract_workspace_floats(M, K > N ? K : N, r);
+      if (!sc.grad_ws.reserve(wsf * sizeof(float))) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+      rb = launch_tok_contract(hs, dy16, dscale, M, N, r, 1, (size_t)r, alpha, l->lora.gb, sc.grad_ws.as<float>(), c->stream);
+      ra = launch_tok_contract(gs, x16, dscale, M, K, r, (size_t)K, 1, alpha, l->lora.ga, sc.grad_ws.as<float>(), c->stream);
+      if (rb > 1 || ra > 1) return c->fail(RT_ERR_CUDA, "lora gradient kernel launch failed");
     }
-    const size_t wsf = tok_contract_workspace_floats(M, K > N ? K : N, r);
-    if (!sc.grad_ws.reserve(wsf * sizeof(float))) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
-    const int rb = launch_tok_contract(hs, dy16, dscale, M, N, r, 1, (size_t)r, alpha, l->lora.gb, sc.grad_ws.as<float>(), c->stream);
-    const int ra = launch_tok_contract(gs, x16, dscale, M, K, r, (size_t)K, 1, alpha, l->lora.ga, sc.grad_ws.as<float>(), c->stream);
-    if (rb > 1 || ra > 1) return c->fail(RT_ERR_CUDA, "lora gradient kernel launch failed");
     if (dscale && (rb == 1 || ra == 1)) {  // general shapes go through the big kernel and need scaled copies
       __half* hs2 = lowrank_buf(c, sc.hs2, sc.hs2_rank, M, r);
       __half* gs2 = lowrank_buf(c, sc.gs2, sc.gs2_rank, M, r);
@@ -698,9 +707,9 @@ static bool ensure_tokens(rt_model* m, int M) {
   ok &= m->lse.reserve(T * g.n_heads * 4 * L) && m->delta.reserve(T * g.n_heads * 4);
   ok &= m->g16.reserve(T * ff * 2 * L) && m->u16.reserve(T * ff * 2 * L) && m->hm16.reserve(T * ff * 2 * L);
   ok &= m->dx.reserve(T * d * 4) && m->dy16.reserve(T * d * 2) && m->sc_y.reserve(T * 4);
-  ok &= m->dhm.reserve(T * ff * 4) && m->dg16.reserve(T * ff * 2) && m->du16.reserve(T * ff * 2);
+  ok &= m->dhm.reserve(T * ff * 2) && m->dg16.reserve(T * ff * 2) && m->du16.reserve(T * ff * 2);
   ok &= m->sc_g.reserve(T * 4) && m->sc_u.reserve(T * 4) && m->dn.reserve(T * d * 4);
-  ok &= m->d_o.reserve(T * qd * 4) && m->dO16.reserve(T * qd * 2);
+  ok &= m->dO16.reserve(T * qd * 2);
   ok &= m->dq.reserve(T * qd * 4) && m->dk.reserve(T * kvd * 4) && m->dv.reserve(T * kvd * 4);
   ok &= m->dq16.reserve(T * qd * 2) && m->dk16.reserve(T * kvd * 2) && m->dv16.reserve(T * kvd * 2);
   ok &= m->sc_q.reserve(T * 4) && m->sc_k.reserve(T * 4) && m->sc_v.reserve(T * 4);
@@ -828,19 +837,21 @@ static rt_status block_backward(rt_model* m, int li, int M, const float* x_in, c
   float* sc_y = m->sc_y.as<float>();
 #define HS(i) (b.lin[i]->lora_active() ? A.hs[i] : nullptr)
   // Mlp::backward (src/model.rs:120-134)
-  RT_TRY(linear_backward_dev(b.lin[6], m->lsc, A.hm16, dy16, sc_y, M, m->dhm.as<float>(), 0, HS(6)));
-  launch_swiglu_bwd(m->dhm.as<float>(), A.g16, A.u16, M, g.ff, m->dg16.as<__half>(),
+  // d(hm) leaves the matmul as f16 rows still lacking sc_y: SwiGLU's backward folds the factor into its own scales
+  RT_TRY(linear_backward_dev(b.lin[6], m->lsc, A.hm16, dy16, sc_y, M, m->dhm.p, 0, HS(6), true));
+  launch_swiglu_bwd(m->dhm.p, 1, sc_y, A.g16, A.u16, M, g.ff, m->dg16.as<__half>(),
                     m->du16.as<__half>(), m->sc_g.as<float>(), m->sc_u.as<float>(), st);
   RT_TRY(linear_backward_dev(b.lin[4], m->lsc, A.n2, m->dg16.as<__half>(), m->sc_g.as<float>(), M, m->dn.as<float>(), 0, HS(4)));
   RT_TRY(linear_backward_dev(b.lin[5], m->lsc, A.n2, m->du16.as<__half>(), m->sc_u.as<float>(), M, m->dn.as<float>(), 1, HS(5)));
   // dh = dy + rmsnorm_backward(h, post_norm, dn2)
   launch_rmsnorm_bwd(A.h, b.post_norm, m->dn.as<float>(), dx, M, d, g.rms_eps, dx, dy16, sc_y, st);
   // Attention::backward (src/attention.rs:246-367)
-  RT_TRY(linear_backward_dev(b.lin[3], m->lsc, A.o16, dy16, sc_y, M, m->d_o.as<float>(), 0, HS(3)));
-  const size_t nqd = (size_t)M * g.n_heads * g.head_dim;
-  launch_global_normalize(m->d_o.as<float>(), nqd, m->amax.as<float>(), m->dO16.as<__half>(), st);
+  // d(attention output) leaves the matmul as f16 rows still lacking sc_y; the attention backward
+  // takes the factors per query row (largest one in amax)
+  RT_TRY(linear_backward_dev(b.lin[3], m->lsc, A.o16, dy16, sc_y, M, m->dO16.p, 0, HS(3), true));
+  launch_rowscale_max(sc_y, M, m->amax.as<float>(), st);
   if (launch_attn_bwd(A.q16, A.k16, A.v16, A.o16, m->dO16.as<__half>(),
-                      m->amax.as<float>(), A.lse, m->seq_start.as<int>(), M, g.n_heads, g.n_kv_heads, g.head_dim,
+                      m->amax.as<float>(), sc_y, A.lse, m->seq_start.as<int>(), M, g.n_heads, g.n_kv_heads, g.head_dim,
                       m->delta.as<float>(), m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>(), st))
     return c->fail(RT_ERR_CUDA, "attention backward launch failed");
   launch_qk_rope_bwd(m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>(), A.q_raw, A.k_raw,

@@ -54,10 +54,12 @@ rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16,
                              int accumulate, __half* hs_keep = nullptr);
 // Hs alone (the forward of a linear whose output is not needed).
 rt_status linear_lora_h(rt_linear* l, const __half* x16, int M, __half* hs_out);
-// dy16 is row-normalised f16 with per-row scales `dscale` (null = all ones)
+// dy16 is row-normalised f16 with per-row scales `dscale` (null = all ones).  With
+// unscaled_f16_out, dx receives f16 rows WITHOUT their factor dscale[row] (the consumer applies
+// it): half the output bytes, no accumulate.
 rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16, const __half* dy16,
-                              const float* dscale, int M, float* dx, int accumulate,
-                              const __half* hs_saved = nullptr);
+                              const float* dscale, int M, void* dx, int accumulate,
+                              const __half* hs_saved = nullptr, bool unscaled_f16_out = false);
 rt_status lora_refresh(rt_linear* l);
 }  // namespace rt
 

@@ -455,12 +455,25 @@ void launch_swiglu_fwd(const __half* g, const __half* u, __half* h, size_t n, cu
 // The kernel is bound by the exp/divide per element, so sigma is computed once per element with
 // the fast intrinsics (2 ulp, far inside the f16 rounding that follows) and the products are
 // kept in registers between the max pass and the write pass.
-__device__ __forceinline__ void swiglu_grad8(const float* dh, const __half* g, const __half* u, float* dg, float* du) {
-  const float4 d0 = *(const float4*)dh, d1 = *(const float4*)(dh + 4);
+__device__ __forceinline__ void load8f(const float* p, float* d) {
+  const float4 d0 = *(const float4*)p, d1 = *(const float4*)(p + 4);
+  d[0] = d0.x; d[1] = d0.y; d[2] = d0.z; d[3] = d0.w; d[4] = d1.x; d[5] = d1.y; d[6] = d1.z; d[7] = d1.w;
+}
+__device__ __forceinline__ void load8f(const __half* p, float* d) {
+  const uint4 v = *(const uint4*)p;
+  const __half2* h = (const __half2*)&v;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h[k]); d[2 * k] = f.x; d[2 * k + 1] = f.y; }
+}
+__device__ __forceinline__ float ld1f(const float* p) { return *p; }
+__device__ __forceinline__ float ld1f(const __half* p) { return __half2float(*p); }
+template <typename DT>
+__device__ __forceinline__ void swiglu_grad8(const DT* dh, const __half* g, const __half* u, float* dg, float* du) {
+  float d[8];
+  load8f(dh, d);
   const uint4 gv = *(const uint4*)g, uv = *(const uint4*)u;
   const __half2* g2 = (const __half2*)&gv;
   const __half2* u2 = (const __half2*)&uv;
-  const float d[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const float2 a = __half22float2(g2[k]), b = __half22float2(u2[k]);
@@ -471,8 +484,11 @@ __device__ __forceinline__ void swiglu_grad8(const float* dh, const __half* g, c
     du[2 * k + 1] = d[2 * k + 1] * (a.y * s1);
   }
 }
-template <int NCH>  // 8-element chunks cached per thread: ff <= NCH * 8 * blockDim.x, ff % 8 == 0
-__global__ void swiglu_bwd_cached_kernel(const float* __restrict__ dh, const __half* __restrict__ g,
+// dh is f32, or f16 rows that still lack their per-row factor in_scale[r] (which then only
+// multiplies the two output scales).
+template <int NCH, typename DT>  // 8-element chunks cached per thread: ff <= NCH * 8 * blockDim.x, ff % 8 == 0
+__global__ void swiglu_bwd_cached_kernel(const DT* __restrict__ dh, const float* __restrict__ in_scale,
+                                         const __half* __restrict__ g,
                                          const __half* __restrict__ u, int ff, __half* __restrict__ dg16,
                                          __half* __restrict__ du16, float* __restrict__ sg, float* __restrict__ su) {
   const size_t r = blockIdx.x;
@@ -507,19 +523,24 @@ __global__ void swiglu_bwd_cached_kernel(const float* __restrict__ dh, const __h
       *(uint4*)(du16 + r * ff + i) = ob;
     }
   }
-  if (threadIdx.x == 0) { sg[r] = s_g; su[r] = s_u; }
+  if (threadIdx.x == 0) {
+    const float f = in_scale ? in_scale[r] : 1.0f;
+    sg[r] = s_g * f;
+    su[r] = s_u * f;
+  }
 }
 // general row length: scalar, recomputed in the second pass
-__global__ void swiglu_bwd_kernel(const float* __restrict__ dh, const __half* __restrict__ g,
+template <typename DT>
+__global__ void swiglu_bwd_kernel(const DT* __restrict__ dh, const float* __restrict__ in_scale, const __half* __restrict__ g,
                                   const __half* __restrict__ u, int ff, __half* __restrict__ dg16,
                                   __half* __restrict__ du16, float* __restrict__ sg, float* __restrict__ su) {
   const size_t r = blockIdx.x;
-  const float* dhr = dh + r * ff;
+  const DT* dhr = dh + r * ff;
   const __half* gr = g + r * ff;
   const __half* ur = u + r * ff;
   float mg = 0.f, mu = 0.f;
   for (int i = threadIdx.x; i < ff; i += blockDim.x) {
-    const float gv = __half2float(gr[i]), uv = __half2float(ur[i]), d = dhr[i];
+    const float gv = __half2float(gr[i]), uv = __half2float(ur[i]), d = ld1f(dhr + i);
     const float s = sigmoid_f(gv);
     mg = fmaxf(mg, fabsf(d * uv * (s * (1.0f + gv * (1.0f - s)))));
     mu = fmaxf(mu, fabsf(d * silu_f(gv)));
@@ -529,19 +550,30 @@ __global__ void swiglu_bwd_kernel(const float* __restrict__ dh, const __half* __
   const float s_g = mg > 0.f ? mg : 1.f, s_u = mu > 0.f ? mu : 1.f;
   const float ig = 1.f / s_g, iu = 1.f / s_u;
   for (int i = threadIdx.x; i < ff; i += blockDim.x) {
-    const float gv = __half2float(gr[i]), uv = __half2float(ur[i]), d = dhr[i];
+    const float gv = __half2float(gr[i]), uv = __half2float(ur[i]), d = ld1f(dhr + i);
     const float s = sigmoid_f(gv);
     dg16[r * ff + i] = __float2half_rn(d * uv * (s * (1.0f + gv * (1.0f - s))) * ig);
     du16[r * ff + i] = __float2half_rn(d * silu_f(gv) * iu);
   }
-  if (threadIdx.x == 0) { sg[r] = s_g; su[r] = s_u; }
+  if (threadIdx.x == 0) {
+    const float f = in_scale ? in_scale[r] : 1.0f;
+    sg[r] = s_g * f;
+    su[r] = s_u * f;
+  }
 }
-void launch_swiglu_bwd(const float* dh, const __half* g, const __half* u, int rows, int ff, __half* dg16, __half* du16,
-                       float* sg, float* su, cudaStream_t st) {
+template <typename DT>
+static void launch_swiglu_bwd_t(const DT* dh, const float* in_scale, const __half* g, const __half* u, int rows, int ff,
+                                __half* dg16, __half* du16, float* sg, float* su, cudaStream_t st) {
+  if ((ff & 7) == 0 && ff <= 2 * 8 * 256) swiglu_bwd_cached_kernel<2, DT><<<rows, 256, 0, st>>>(dh, in_scale, g, u, ff, dg16, du16, sg, su);
+  else if ((ff & 7) == 0 && ff <= 3 * 8 * 512) swiglu_bwd_cached_kernel<3, DT><<<rows, 512, 0, st>>>(dh, in_scale, g, u, ff, dg16, du16, sg, su);
+  else swiglu_bwd_kernel<DT><<<rows, 256, 0, st>>>(dh, in_scale, g, u, ff, dg16, du16, sg, su);
+  RT_COUNT_LAUNCH(1);
+}
+void launch_swiglu_bwd(const void* dh, int dh_f16, const float* in_scale, const __half* g, const __half* u, int rows, int ff,
+                       __half* dg16, __half* du16, float* sg, float* su, cudaStream_t st) {
   if (rows <= 0) return;
-  if ((ff & 7) == 0 && ff <= 2 * 8 * 256) { swiglu_bwd_cached_kernel<2><<<rows, 256, 0, st>>>(dh, g, u, ff, dg16, du16, sg, su); RT_COUNT_LAUNCH(1); }
-  else if ((ff & 7) == 0 && ff <= 3 * 8 * 512) { swiglu_bwd_cached_kernel<3><<<rows, 512, 0, st>>>(dh, g, u, ff, dg16, du16, sg, su); RT_COUNT_LAUNCH(1); }
-  else { swiglu_bwd_kernel<<<rows, 256, 0, st>>>(dh, g, u, ff, dg16, du16, sg, su); RT_COUNT_LAUNCH(1); }
+  if (dh_f16) launch_swiglu_bwd_t((const __half*)dh, in_scale, g, u, rows, ff, dg16, du16, sg, su, st);
+  else launch_swiglu_bwd_t((const float*)dh, in_scale, g, u, rows, ff, dg16, du16, sg, su, st);
 }
 
 // ------------------------------------------------------------------ row gather / scatter

@@ -20,8 +20,9 @@ void launch_qk_rope_bwd(const float* dq, const float* dk, const float* dv, const
                         int nkv, int hd, int rot, int neox, float eps, __half* dq16, __half* dk16, __half* dv16,
                         float* sq, float* sk, float* sv, cudaStream_t st);
 void launch_swiglu_fwd(const __half* g, const __half* u, __half* h, size_t n, cudaStream_t st);
-void launch_swiglu_bwd(const float* dh, const __half* g, const __half* u, int rows, int ff, __half* dg16, __half* du16,
-                       float* sg, float* su, cudaStream_t st);
+// dh: f32 rows, or (dh_f16) f16 rows whose per-row factor in_scale[r] has not been applied yet
+void launch_swiglu_bwd(const void* dh, int dh_f16, const float* in_scale, const __half* g, const __half* u, int rows, int ff,
+                       __half* dg16, __half* du16, float* sg, float* su, cudaStream_t st);
 void launch_gather_f32_rows(const float* x, const int* idx, int rows, int d, float* out, cudaStream_t st);
 void launch_scatter_add_rows(const float* src, const int* idx, int rows, int d, float* dx, cudaStream_t st);
 void launch_ce_rows(const float* logits, int rows, int v, const int* target, const float* weight, float* logp, int* hits,
@@ -42,6 +43,9 @@ void launch_global_normalize(const float* x, size_t n, float* amax_dev, __half* 
 // ---- lora_kernels.cu: skinny low-rank products (return 1 when the shape is not supported)
 int launch_skinny_nt(const __half* X, const __half* Wt, int M, int K, int r, __half* out64, cudaStream_t st);
 size_t tok_contract_workspace_floats(int M, int C, int r);
+size_t lora_grads_workspace_floats(int M, int N, int K, int r);
+int launch_lora_grads(const __half* hs, const __half* dy16, const __half* gs, const __half* x16, const float* dscale, int M,
+                      int N, int K, int r, float* gb, float* ga, float* workspace, cudaStream_t st);
 // pscale (optional): P's rows are multiplied by pscale[m] / alpha_dev[0] on the fly; alpha_dev[0] then scales the result
 int launch_tok_contract(const __half* P, const __half* Q, const float* pscale, int M, int C, int r, size_t so_i, size_t so_j,
                         const float* alpha_dev, float* out, float* workspace, cudaStream_t st);
@@ -52,8 +56,10 @@ int launch_tok_contract(const __half* P, const __half* Q, const float* pscale, i
 int launch_attn_fwd(const __half* q, const __half* k, const __half* v, const int* seq_start, int M, int nh, int nkv,
                     int hd, __half* o, float* lse, cudaStream_t st);
 // dO16 is dO divided by a global scale (device scalar `do_scale`); outputs are true-scale f32.
+// dO row i stands for do_scale[0] * dO16[i], or, with row_scale, for row_scale[i] * dO16[i]
+// (then do_scale[0] must hold the largest row_scale).
 int launch_attn_bwd(const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
-                    const float* do_scale, const float* lse, const int* seq_start, int M, int nh, int nkv, int hd,
-                    float* delta /* [nh x M] scratch */, float* dq, float* dk, float* dv, cudaStream_t st);
+                    const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, int M, int nh,
+                    int nkv, int hd, float* delta /* [nh x M] scratch */, float* dq, float* dk, float* dv, cudaStream_t st);
 
 }  // namespace rt
