@@ -304,10 +304,238 @@ __global__ void qk_rope_fwd_kernel(const float* __restrict__ q_raw, const float*
     }
   }
 }
+
+// Register-resident versions of the two kernels above for the usual shapes (head size 64 or
+// 128, at most 8 heads per warp): a warp holds a whole head, EPL consecutive elements per lane,
+// so every global load of a token's heads is issued before any of them is used, the rotation
+// partner comes from a lane shuffle, and nothing is staged in shared memory.
+template <int EPL>
+struct RopeLane {
+  // what lane `lane` needs to rotate its EPL elements of one head
+  float c[EPL], s[EPL];  // cos, and sin signed for the FORWARD rotation (0 / 1 beyond rot)
+  int src_lane;          // neox: the lane holding the partner elements; interleaved: unused
+  bool rotates;
+};
+template <int EPL>
+__device__ __forceinline__ RopeLane<EPL> rope_lane(int lane, const float* csr, const float* snr, int half, int rot, int neox) {
+  RopeLane<EPL> r;
+  const int e0 = lane * EPL;
+  r.rotates = e0 < rot;
+  r.src_lane = lane;
+#pragma unroll
+  for (int k = 0; k < EPL; ++k) { r.c[k] = 1.f; r.s[k] = 0.f; }
+  if (!r.rotates) return r;
+  if (neox) {
+    const bool first = e0 < half;
+    r.src_lane = first ? lane + half / EPL : lane - half / EPL;
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) {
+      const int i = first ? e0 + k : e0 + k - half;
+      r.c[k] = csr[i];
+      r.s[k] = first ? -snr[i] : snr[i];
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) {
+      const int i = (e0 + k) >> 1;
+      r.c[k] = csr[i];
+      r.s[k] = (k & 1) ? snr[i] : -snr[i];
+    }
+  }
+  return r;
+}
+// out = own*c + partner*s*dir  (dir = +1 forward, -1 inverse)
+template <int EPL>
+__device__ __forceinline__ void rope_apply(const RopeLane<EPL>& r, int neox, float dir, const float* x, float* out) {
+  float partner[EPL];
+  if (neox) {
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) partner[k] = __shfl_sync(0xffffffffu, x[k], r.src_lane);
+  } else {
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) partner[k] = x[k ^ 1];
+  }
+#pragma unroll
+  for (int k = 0; k < EPL; ++k) out[k] = x[k] * r.c[k] + partner[k] * (r.s[k] * dir);
+}
+template <int EPL>
+__device__ __forceinline__ void load_epl(const float* p, float* v) {
+  if (EPL == 4) { const float4 t = *(const float4*)p; v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+  else { const float2 t = *(const float2*)p; v[0] = t.x; v[1] = t.y; }
+}
+template <int EPL>
+__device__ __forceinline__ void store_epl_h(__half* p, const float* v) {
+  if (EPL == 4) {
+    __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
+    *(uint2*)p = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+  } else {
+    *(__half2*)p = __floats2half2_rn(v[0], v[1]);
+  }
+}
+
+template <int EPL, int HPW>
+__global__ void __launch_bounds__(256)
+qk_rope_fwd_reg_kernel(const float* __restrict__ q_raw, const float* __restrict__ k_raw, const float* __restrict__ v_raw,
+                       const float* __restrict__ qw, const float* __restrict__ kw, const int* __restrict__ pos,
+                       const float* __restrict__ cs, const float* __restrict__ sn, int nh, int nkv, int rot, int neox,
+                       float eps, __half* __restrict__ q16, __half* __restrict__ k16, __half* __restrict__ v16) {
+  constexpr int HD = 32 * EPL;
+  const size_t m = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = rot / 2, nheads = nh + 2 * nkv;
+  const int p = pos[m];
+  const RopeLane<EPL> rl = rope_lane<EPL>(lane, cs + (size_t)p * half, sn + (size_t)p * half, half, rot, neox);
+  float x[HPW][EPL];
+#pragma unroll
+  for (int t = 0; t < HPW; ++t) {
+    const int h = warp + t * 8;
+    if (h < nheads) {
+      const float* src = h < nh ? q_raw + (m * nh + h) * HD : (h < nh + nkv ? k_raw + (m * nkv + (h - nh)) * HD
+                                                                           : v_raw + (m * nkv + (h - nh - nkv)) * HD);
+      load_epl<EPL>(src + lane * EPL, x[t]);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < HPW; ++t) {
+    const int h = warp + t * 8;
+    if (h >= nheads) continue;  // uniform in the warp
+    if (h >= nh + nkv) {
+      store_epl_h<EPL>(v16 + (m * nkv + (h - nh - nkv)) * HD + lane * EPL, x[t]);
+      continue;
+    }
+    const bool is_q = h < nh;
+    const float* nw = is_q ? qw : kw;
+    if (nw) {
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) ss += x[t][k] * x[t][k];
+      ss = warp_sum(ss);
+      const float ir = 1.0f / sqrtf(ss / (float)HD + eps);
+      float w[EPL];
+      load_epl<EPL>(nw + lane * EPL, w);
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) x[t][k] *= ir * w[k];
+    }
+    float o[EPL];
+    rope_apply<EPL>(rl, neox, 1.f, x[t], o);
+    __half* dst = is_q ? q16 + (m * nh + h) * HD : k16 + (m * nkv + (h - nh)) * HD;
+    store_epl_h<EPL>(dst + lane * EPL, o);
+  }
+}
+
+template <int EPL, int HPW>
+__global__ void __launch_bounds__(256)
+qk_rope_bwd_reg_kernel(const float* __restrict__ dq, const float* __restrict__ dk, const float* __restrict__ dv,
+                       const float* __restrict__ q_raw, const float* __restrict__ k_raw, const float* __restrict__ qw,
+                       const float* __restrict__ kw, const int* __restrict__ pos, const float* __restrict__ cs,
+                       const float* __restrict__ sn, int nh, int nkv, int rot, int neox, float eps,
+                       __half* __restrict__ dq16, __half* __restrict__ dk16, __half* __restrict__ dv16,
+                       float* __restrict__ sq, float* __restrict__ sk, float* __restrict__ sv) {
+  constexpr int HD = 32 * EPL;
+  __shared__ float wmax[3][8];
+  const size_t m = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = rot / 2, nheads = nh + 2 * nkv;
+  const int p = pos[m];
+  const RopeLane<EPL> rl = rope_lane<EPL>(lane, cs + (size_t)p * half, sn + (size_t)p * half, half, rot, neox);
+  float g[HPW][EPL], xr[HPW][EPL];
+#pragma unroll
+  for (int t = 0; t < HPW; ++t) {
+    const int h = warp + t * 8;
+    if (h < nheads) {
+      const float* src = h < nh ? dq + (m * nh + h) * HD : (h < nh + nkv ? dk + (m * nkv + (h - nh)) * HD
+                                                                        : dv + (m * nkv + (h - nh - nkv)) * HD);
+      load_epl<EPL>(src + lane * EPL, g[t]);
+      const float* nw = h < nh ? qw : (h < nh + nkv ? kw : nullptr);
+      if (nw) load_epl<EPL>((h < nh ? q_raw + (m * nh + h) * HD : k_raw + (m * nkv + (h - nh)) * HD) + lane * EPL, xr[t]);
+    }
+  }
+  float mx[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+  for (int t = 0; t < HPW; ++t) {
+    const int h = warp + t * 8;
+    if (h >= nheads) continue;
+    const int kind = h < nh ? 0 : (h < nh + nkv ? 1 : 2);
+    if (kind < 2) {
+      float o[EPL];
+      rope_apply<EPL>(rl, neox, -1.f, g[t], o);  // inverse rotation
+      const float* nw = kind == 0 ? qw : kw;
+      if (nw) {
+        float w[EPL];
+        load_epl<EPL>(nw + lane * EPL, w);
+        float ss = 0.f, gx = 0.f;
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) { ss += xr[t][k] * xr[t][k]; gx += o[k] * w[k] * xr[t][k]; }
+        ss = warp_sum(ss);
+        gx = warp_sum(gx);
+        const float ir = 1.0f / sqrtf(ss / (float)HD + eps);
+        const float c = gx * ir * ir * ir / (float)HD;
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) o[k] = o[k] * w[k] * ir - xr[t][k] * c;
+      }
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) g[t][k] = o[k];
+    }
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) mx[kind] = fmaxf(mx[kind], fabsf(g[t][k]));
+  }
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    const float v = warp_max(mx[k]);
+    if (lane == 0) wmax[k][warp] = v;
+  }
+  __syncthreads();
+  float s3[3], inv[3];
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) v = fmaxf(v, wmax[k][w]);
+    s3[k] = v > 0.f ? v : 1.f;
+    inv[k] = 1.f / s3[k];
+  }
+  if (threadIdx.x == 0) { sq[m] = s3[0]; sk[m] = s3[1]; sv[m] = s3[2]; }
+#pragma unroll
+  for (int t = 0; t < HPW; ++t) {
+    const int h = warp + t * 8;
+    if (h >= nheads) continue;
+    const int kind = h < nh ? 0 : (h < nh + nkv ? 1 : 2);
+    float o[EPL];
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) o[k] = g[t][k] * inv[kind];
+    __half* dst = kind == 0 ? dq16 + (m * nh + h) * HD : (kind == 1 ? dk16 + (m * nkv + (h - nh)) * HD
+                                                                     : dv16 + (m * nkv + (h - nh - nkv)) * HD);
+    store_epl_h<EPL>(dst + lane * EPL, o);
+  }
+}
+
+// the shapes the register-resident kernels cover
+static bool rope_reg_ok(int nh, int nkv, int hd, int rot, int neox, int* epl, int* hpw) {
+  if (hd != 64 && hd != 128) return false;
+  const int e = hd / 32, half = rot / 2;
+  if (rot <= 0 || rot > hd || (rot & 1) || rot % e != 0) return false;
+  if (neox && half % e != 0) return false;
+  const int heads = nh + 2 * nkv;
+  const int per = (heads + 7) / 8;
+  if (per > 8) return false;
+  *epl = e;
+  *hpw = per <= 4 ? 4 : (per <= 6 ? 6 : 8);
+  return true;
+}
 void launch_qk_rope_fwd(const float* q_raw, const float* k_raw, const float* v_raw, const float* qw, const float* kw,
                         const int* pos, const float* cs, const float* sn, int M, int nh, int nkv, int hd, int rot,
                         int neox, float eps, __half* q16, __half* k16, __half* v16, cudaStream_t st) {
-  if (M > 0) { qk_rope_fwd_kernel<<<M, 256, 0, st>>>(q_raw, k_raw, v_raw, qw, kw, pos, cs, sn, nh, nkv, hd, rot, neox, eps, q16, k16, v16); RT_COUNT_LAUNCH(1); }
+  if (M <= 0) return;
+  int epl = 0, hpw = 0;
+  if (rope_reg_ok(nh, nkv, hd, rot, neox, &epl, &hpw)) {
+#define RT_ROPE_FWD(E, H) qk_rope_fwd_reg_kernel<E, H><<<M, 256, 0, st>>>(q_raw, k_raw, v_raw, qw, kw, pos, cs, sn, nh, nkv, rot, neox, eps, q16, k16, v16)
+    if (epl == 4) { if (hpw == 4) RT_ROPE_FWD(4, 4); else if (hpw == 6) RT_ROPE_FWD(4, 6); else RT_ROPE_FWD(4, 8); }
+    else { if (hpw == 4) RT_ROPE_FWD(2, 4); else if (hpw == 6) RT_ROPE_FWD(2, 6); else RT_ROPE_FWD(2, 8); }
+#undef RT_ROPE_FWD
+  } else {
+    qk_rope_fwd_kernel<<<M, 256, 0, st>>>(q_raw, k_raw, v_raw, qw, kw, pos, cs, sn, nh, nkv, hd, rot, neox, eps, q16, k16, v16);
+  }
+  RT_COUNT_LAUNCH(1);
 }
 
 // Backward of the above (reference src/attention.rs:331-341): inverse rotation, then the
@@ -415,9 +643,18 @@ void launch_qk_rope_bwd(const float* dq, const float* dk, const float* dv, const
                         int nkv, int hd, int rot, int neox, float eps, __half* dq16, __half* dk16, __half* dv16,
                         float* sq, float* sk, float* sv, cudaStream_t st) {
   if (M <= 0) return;
-  size_t smem = (size_t)(nh + 2 * nkv) * hd * sizeof(float);
-  { qk_rope_bwd_kernel<<<M, 256, smem, st>>>(dq, dk, dv, q_raw, k_raw, qw, kw, pos, cs, sn, nh, nkv, hd, rot, neox, eps,
-                                             dq16, dk16, dv16, sq, sk, sv); RT_COUNT_LAUNCH(1); }
+  int epl = 0, hpw = 0;
+  if (rope_reg_ok(nh, nkv, hd, rot, neox, &epl, &hpw)) {
+#define RT_ROPE_BWD(E, H) qk_rope_bwd_reg_kernel<E, H><<<M, 256, 0, st>>>(dq, dk, dv, q_raw, k_raw, qw, kw, pos, cs, sn, nh, nkv, rot, neox, eps, dq16, dk16, dv16, sq, sk, sv)
+    if (epl == 4) { if (hpw == 4) RT_ROPE_BWD(4, 4); else if (hpw == 6) RT_ROPE_BWD(4, 6); else RT_ROPE_BWD(4, 8); }
+    else { if (hpw == 4) RT_ROPE_BWD(2, 4); else if (hpw == 6) RT_ROPE_BWD(2, 6); else RT_ROPE_BWD(2, 8); }
+#undef RT_ROPE_BWD
+  } else {
+    size_t smem = (size_t)(nh + 2 * nkv) * hd * sizeof(float);
+    qk_rope_bwd_kernel<<<M, 256, smem, st>>>(dq, dk, dv, q_raw, k_raw, qw, kw, pos, cs, sn, nh, nkv, hd, rot, neox, eps,
+                                             dq16, dk16, dv16, sq, sk, sv);
+  }
+  RT_COUNT_LAUNCH(1);
 }
 
 // ------------------------------------------------------------------ SwiGLU (reference src/model.rs:113-134, src/tensor.rs:122-143)

@@ -44,6 +44,7 @@ class ModelSpec:
     rope_neox: bool = True
     rope_freq_scale: float = 1.0
     rope_llama3_factor: float = 0.0  # > 0: emit rope_freqs.weight by the llama3 rule
+    rot: int = 0  # rotated elements per head (rope.dimension_count); 0 = the whole head
     rms_eps: float = 1e-6
     quant: str = "Q4_0"
     fallback_quant: str = "Q4_0"
@@ -53,7 +54,7 @@ class ModelSpec:
 
     @property
     def rot_dim(self) -> int:
-        return self.head_dim
+        return self.rot if self.rot > 0 else self.head_dim
 
     def config(self) -> dict:
         return dict(arch=self.arch, vocab=self.vocab, hidden=self.hidden, ff=self.ff, n_layers=self.n_layers,
@@ -103,6 +104,14 @@ PRESETS = {
                        qk_norm=False, attn_bias=True, tie_embeddings=True),
     "tiny-llama": dict(arch="llama", n_layers=2, hidden=256, n_heads=2, n_kv_heads=1, head_dim=128, ff=512, vocab=384,
                        qk_norm=False, tie_embeddings=False, rope_theta=5e5, rope_neox=False, rope_llama3_factor=32.0),
+    # the 0.6B shape's head layout (128-wide heads, QK-norm, rotate-half), partial rotation, and
+    # more heads than the register-resident RoPE kernels take
+    "tiny-qwen3-hd128": dict(arch="qwen3", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=128, ff=512,
+                             vocab=512, qk_norm=True, tie_embeddings=True),
+    "tiny-rot32": dict(arch="qwen3", n_layers=2, hidden=128, n_heads=4, n_kv_heads=2, head_dim=64, ff=256, vocab=512,
+                       qk_norm=True, tie_embeddings=True, rot=32),
+    "tiny-manyheads": dict(arch="qwen3", n_layers=1, hidden=128, n_heads=60, n_kv_heads=6, head_dim=64, ff=256,
+                           vocab=512, qk_norm=True, tie_embeddings=True),
 }
 
 

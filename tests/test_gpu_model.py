@@ -17,7 +17,8 @@ pytestmark = pytest.mark.gpu
 
 LOSS_TOL, LOGITS_TOL, GRAD_TOL, GRAD_COS, ADAPTER_TOL = 1e-3, 1e-2, 1e-2, 0.999, 2e-2
 CASES = [("tiny-qwen3", "Q4_0"), ("tiny-qwen2", "Q8_0"), ("tiny-llama", "Q6_K"), ("tiny-qwen3", "F16"),
-         ("tiny-qwen2", "Q4_K"), ("tiny-llama", "BF16")]
+         ("tiny-qwen2", "Q4_K"), ("tiny-llama", "BF16"), ("tiny-qwen3-hd128", "Q8_0"), ("tiny-rot32", "Q4_0"),
+         ("tiny-manyheads", "Q8_0")]
 
 
 def _flat(lora_list, a, b):
