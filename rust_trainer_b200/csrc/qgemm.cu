@@ -106,10 +106,10 @@ __device__ __forceinline__ void unpack_q4_0(const uint8_t* brick, int t, uint8_t
 }
 
 template <bool WBF16>
-__device__ __forceinline__ void unpack_q8_0(const uint8_t* brick, int t, uint8_t* dst, int noswap = 0) {
+__device__ __forceinline__ void unpack_q8_0(const uint8_t* brick, int t, uint8_t* dst) {
   // units are 32 bytes apart: lanes 4-7 of every eight fetch their halves in the other order, so
   // each 128-bit load of a quarter-warp touches every bank once
-  const int swp = noswap ? 0 : (t >> 2) & 1;
+  const int swp = (t >> 2) & 1;
   const uint4 q0 = *(const uint4*)(brick + t * 32 + swp * 16);
   const uint4 q1 = *(const uint4*)(brick + t * 32 + (swp ^ 1) * 16);
   const uint4 qa = swp ? q1 : q0;
@@ -187,10 +187,10 @@ __device__ __forceinline__ void unpack_q6_k(const uint8_t* brick, int t, uint8_t
 
 // one brick (64 x 64 codes) -> one 8 KB half of the 16-bit weight tile; t = unit 0..127
 template <bool WBF16>
-__device__ __forceinline__ void unpack_brick(int fmt, const uint8_t* raw, int t, uint8_t* dst, int noswap = 0) {
+__device__ __forceinline__ void unpack_brick(int fmt, const uint8_t* raw, int t, uint8_t* dst) {
   switch (fmt) {
     case GGML_Q4_0: unpack_q4_0<WBF16>(raw, t, dst); break;
-    case GGML_Q8_0: unpack_q8_0<WBF16>(raw, t, dst, noswap); break;
+    case GGML_Q8_0: unpack_q8_0<WBF16>(raw, t, dst); break;
     case GGML_Q4_K: unpack_q4_k<WBF16>(raw, t, dst); break;
     case GGML_Q6_K: unpack_q6_k<WBF16>(raw, t, dst); break;
   }
@@ -460,8 +460,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
               // 256 units (two bricks of 128) per tile; unit u: brick u >> 7 fills the 8 KB half u >> 7
 #pragma unroll
               for (int u = tg; u < 256; u += UTG) {
-                if (p.act_f16) unpack_brick<false>(p.fmt, raw + (u >> 7) * p.brick_bytes, u & 127, dst + (u >> 7) * 8192, p.dbg & 128);
-                else unpack_brick<true>(p.fmt, raw + (u >> 7) * p.brick_bytes, u & 127, dst + (u >> 7) * 8192, p.dbg & 128);
+                if (p.act_f16) unpack_brick<false>(p.fmt, raw + (u >> 7) * p.brick_bytes, u & 127, dst + (u >> 7) * 8192);
+                else unpack_brick<true>(p.fmt, raw + (u >> 7) * p.brick_bytes, u & 127, dst + (u >> 7) * 8192);
               }
             }
             if (!(p.dbg & 4)) fence_proxy_async_smem();
@@ -533,40 +533,6 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         uint32_t v[32];
         tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(wq * 32) << 16) + c * 32, v);
         tmem_ld_wait();
-        if (p.tma_out && !(p.dbg & 1) && (p.dbg & 256)) {
-          // Transpose through shared memory: lane = output feature, register j = token, so the
-          // staged tile is [32 tokens][128 features] and one TMA store writes 32 full rows.
-          // 16-bit outputs need half the staging bytes, so four buffers fit where f32 has two:
-          // a buffer is reused only after the store issued (nbuf) chunks ago has read it
-          const bool wide = p.out_dtype == OUT_F32;
-          const int buf = wide ? (int)(out_chunk & 1) : (int)(out_chunk & 3);
-          ++out_chunk;
-          uint8_t* stage = sOut + buf * (wide ? OUT_STAGE : OUT_STAGE / 2);
-          const bool issuer = warp == 10 && lane == 0;
-          if (issuer) {
-            if (wide) bulk_wait_group_read<1>();
-            else bulk_wait_group_read<3>();
-          }
-          named_barrier_sync(1, 128);
-          const int col = wq * 32 + lane;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float val = __uint_as_float(v[j]);
-            if (p.row_scale) { const int tok = m0 + c * 32 + j; val *= p.row_scale[tok < p.M ? tok : 0]; }
-            val += bias_v;
-            if (p.out_dtype == OUT_F32) ((float*)stage)[j * 128 + col] = val;
-            else if (p.out_dtype == OUT_BF16) ((__nv_bfloat16*)stage)[j * 128 + col] = __float2bfloat16_rn(val);
-            else ((__half*)stage)[j * 128 + col] = __float2half_rn(val);
-          }
-          if (!(p.dbg & 8)) fence_proxy_async_smem();
-          named_barrier_sync(1, 128);
-          if (issuer) {
-            if (p.accumulate) tma_reduce_add_2d(&tm_out, r0, m0 + c * 32, stage);
-            else tma_store_2d(&tm_out, r0, m0 + c * 32, stage);
-            bulk_commit_group();
-          }
-          continue;
-        }
         if (p.tma_out && !(p.dbg & 1)) {
           // Transpose through shared memory: lane = output feature, register j = token.  Each
           // warp stages its own [32 tokens][32 features] block and stores it with its own TMA
@@ -581,11 +547,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
             if (wide) bulk_wait_group_read<1>();
             else bulk_wait_group_read<3>();
           }
+          // this chunk's 32 per-token factors: one coalesced load, handed round by shuffles
+          float rs_lane = 1.0f;
+          if (p.row_scale) { const int tok = m0 + c * 32 + lane; rs_lane = tok < p.M ? p.row_scale[tok] : 0.f; }
           __syncwarp();
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             float val = __uint_as_float(v[j]);
-            if (p.row_scale) { const int tok = m0 + c * 32 + j; val *= p.row_scale[tok < p.M ? tok : 0]; }
+            if (p.row_scale) val *= __shfl_sync(0xffffffffu, rs_lane, j);
             val += bias_v;
             if (p.out_dtype == OUT_F32) ((float*)stage)[j * 32 + lane] = val;
             else if (p.out_dtype == OUT_BF16) ((__nv_bfloat16*)stage)[j * 32 + lane] = __float2bfloat16_rn(val);
@@ -641,7 +610,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         else mbar_arrive(&acc_empty[acc]);
       }
     }
-    if (p.tma_out && lane == 0 && (!(p.dbg & 256) || warp == 10)) bulk_wait_group<0>();  // all output writes of this warp have landed
+    if (p.tma_out && lane == 0) bulk_wait_group<0>();  // all output writes of this warp have landed
     if (warp == 10 && lane == 0) QG_PROF_END(3);
   }
 
@@ -767,8 +736,8 @@ static int make_map_cached(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64
 
 // Output matrix [rows x cols] of f32 / bf16 / f16 with a row pitch of `ld` elements; box = 32 columns x 32 rows
 // (one epilogue warp's block), no swizzle (the epilogue writes the staging block row-major).
-static int make_out_map(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int dtype, uint32_t boxw = 32) {
-  auto key = std::make_tuple(base, rows, cols | (ld << 32), boxw, 32u | ((uint32_t)dtype << 8), true);
+static int make_out_map(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int dtype) {
+  auto key = std::make_tuple(base, rows, cols | (ld << 32), 32u, 32u | ((uint32_t)dtype << 8), true);
   if (ctx) {
     auto it = ctx->tmap_cache.find(key);
     if (it != ctx->tmap_cache.end()) {
@@ -779,7 +748,7 @@ static int make_out_map(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t 
   const uint64_t es = dtype == OUT_F32 ? 4 : 2;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld * es};
-  cuuint32_t box[2] = {boxw, 32};
+  cuuint32_t box[2] = {32, 32};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMapDataType dt = dtype == OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                            : dtype == OUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -945,7 +914,7 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   {
     const uint64_t es = a.out_dtype == OUT_F32 ? 4 : 2;
     if (!p.part && ((uintptr_t)a.out % 16 == 0) && ((uint64_t)p.ld_out * es) % 16 == 0) {
-      rc = make_out_map(a.fixed_part ? nullptr : ctx, &tm_out, a.out, (uint64_t)a.M, (uint64_t)out_rows, (uint64_t)p.ld_out, a.out_dtype, (p.dbg & 256) ? 128u : 32u);
+      rc = make_out_map(a.fixed_part ? nullptr : ctx, &tm_out, a.out, (uint64_t)a.M, (uint64_t)out_rows, (uint64_t)p.ld_out, a.out_dtype);
       if (rc) return rc;
       p.tma_out = 1;
     }
