@@ -4,13 +4,17 @@
     python bench.py --gpus N --steps K --warmup W            # the CUDA path (this repository)
     python bench.py --impl reference --steps K --warmup W    # the CPU algorithm of the reference
 
-One step = zero_grad + forward + recompute + backward over the local batch (+ one all-reduce
-of the flat LoRA-gradient buffer when N > 1) + gradient clipping + AdamW, i.e. one iteration
-of the reference's Trainer::run loop (src/train.rs:316-381).  Prints ONE JSON line on rank 0.
+One step = zero_grad + forward + backward over the local batch (+ one all-reduce of the flat
+LoRA-gradient buffer when N > 1) + gradient clipping + AdamW, i.e. one iteration of the
+reference's Trainer::run loop (src/train.rs:316-381).  Prints ONE JSON line on rank 0.
+Model.checkpointing (src/model.rs:299): the CUDA path keeps every block's caches when they fit in
+device memory (they do here: 12.6 GB) and otherwise recomputes each block before its backward;
+`config.recompute` says which ran, RT_B200_RECOMPUTE=1 forces the recomputation.  The CPU arm
+runs the reference's default (recomputation on).
 
 The N = 1 workload is BASELINE.json configs[1]: a synthetic Qwen3-0.6B-shaped GGUF model with
 Q8_0 weights, 16 sequences x 512 uniform-random ids, loss on the last 30 % of each sequence,
-LoRA r=16 alpha=32 on the seven projections, warm-up 2 + cosine LR, recomputation on.  For
+LoRA r=16 alpha=32 on the seven projections, warm-up 2 + cosine LR.  For
 N > 1 every rank holds a replica and its own 16 x 512 batch (weak scaling).
 """
 from __future__ import annotations
