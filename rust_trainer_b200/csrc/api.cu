@@ -196,8 +196,10 @@ rt_status rt_frozen_create(rt_ctx* c, int ggml_type, size_t rows, size_t cols, c
 void rt_frozen_destroy(rt_frozen* f) {
   if (!f) return;
   cudaSetDevice(f->ctx->device);
-  if (f->w.bricks) cudaFree(f->w.bricks);
-  if (f->w.dense16) cudaFree(f->w.dense16);
+  if (!f->borrowed) {
+    if (f->w.bricks) cudaFree(f->w.bricks);
+    if (f->w.dense16) cudaFree(f->w.dense16);
+  }
   delete f;
 }
 

@@ -50,6 +50,7 @@ struct rt_ctx {
 struct rt_frozen {
   rt_ctx* ctx = nullptr;
   rt::QWeight w;
+  bool borrowed = false;  // the weight bytes live in a buffer another object owns (a stacked group of linears)
 };
 
 #include "ops.h"

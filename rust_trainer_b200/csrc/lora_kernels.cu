@@ -222,6 +222,7 @@ struct LoraGradArgs {
   const __half *Pb, *Qb, *Pa, *Qa;  // Hs, dY, Gs, X
   const float* pscale;              // per-token factors of dY, or null
   int M, N, K, r, nbB, tokens_per_split;
+  int ldb;                          // row pitch of dY (>= N: dY may be a column slice of a wider matrix)
   float *partB, *partA;             // [splits][r x N], [splits][r x K]
 };
 
@@ -235,6 +236,7 @@ __global__ void __launch_bounds__(128) lora_grads_kernel(const LoraGradArgs g) {
   const __half* P = isB ? g.Pb : g.Pa;
   const __half* Q = isB ? g.Qb : g.Qa;
   const int C = isB ? g.N : g.K;
+  const int ldq = isB ? g.ldb : g.K;
   const int j0 = (isB ? (int)blockIdx.x : (int)blockIdx.x - g.nbB) * 128;
   const int m_begin = blockIdx.y * g.tokens_per_split, m_end = min(g.M, m_begin + g.tokens_per_split);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
@@ -249,8 +251,8 @@ __global__ void __launch_bounds__(128) lora_grads_kernel(const LoraGradArgs g) {
   auto load = [&](int ch, int buf) {
     const int mrow = m_begin + ch * 64;
     load64x64(s0 + buf * SB, P, mrow, m_end, 0, 64, 64);
-    load64x64(s0 + buf * SB + 8192, Q, mrow, m_end, j0, C, C);
-    load64x64(s0 + buf * SB + 16384, Q, mrow, m_end, j0 + 64, C, C);
+    load64x64(s0 + buf * SB + 8192, Q, mrow, m_end, j0, C, ldq);
+    load64x64(s0 + buf * SB + 16384, Q, mrow, m_end, j0 + 64, C, ldq);
   };
   for (int i = 0; i < NST - 1; ++i) {
     if (i < nchunks) load(i, i);
@@ -398,10 +400,14 @@ size_t lora_grads_workspace_floats(int M, int N, int K, int r) {
 }
 
 // dB and dA of one linear: two launches in all.  Returns 1 for shapes these kernels do not cover.
-int launch_lora_grads(const __half* hs, const __half* dy16, const __half* gs, const __half* x16, const float* dscale, int M,
-                      int N, int K, int r, float* gb, float* ga, float* workspace, cudaStream_t st) {
+// hs / gs are [M x 64] matrices; a pointer into such a matrix at a column offset (a multiple of 8)
+// selects the r columns from there on, and then the 64-wide row reads run past the last row's end
+// by that offset: the caller keeps that much slack behind the matrix.  dy16 has row pitch ld_dy.
+int launch_lora_grads(const __half* hs, const __half* dy16, int ld_dy, const __half* gs, const __half* x16, const float* dscale,
+                      int M, int N, int K, int r, float* gb, float* ga, float* workspace, cudaStream_t st) {
   if (M <= 0) return 0;
-  if (r <= 0 || r > 64 || N % 8 != 0 || K % 8 != 0) return 1;
+  if (ld_dy <= 0) ld_dy = N;
+  if (r <= 0 || r > 64 || N % 8 != 0 || K % 8 != 0 || ld_dy % 8 != 0) return 1;
   int tps, splits;
   tok_plan(M, &tps, &splits);
   LoraGradArgs g;
@@ -409,6 +415,7 @@ int launch_lora_grads(const __half* hs, const __half* dy16, const __half* gs, co
   g.pscale = dscale;
   g.M = M; g.N = N; g.K = K; g.r = r;
   g.nbB = (N + 127) / 128;
+  g.ldb = ld_dy;
   g.tokens_per_split = tps;
   g.partB = workspace;
   g.partA = workspace + (size_t)splits * r * N;

@@ -4,6 +4,7 @@
 // src/optim.rs, plus buffer management.
 #include "model.h"
 #include <math.h>
+#include <algorithm>
 #include <stdio.h>
 #include <string.h>
 
@@ -160,7 +161,7 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
     const float* alpha = nullptr;
     const size_t wsf2 = lora_grads_workspace_floats(M, N, K, r);
     if (!sc.grad_ws.reserve(wsf2 * sizeof(float))) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
-    int rb = launch_lora_grads(hs, dy16, gs, x16, dscale, M, N, K, r, l->lora.gb, l->lora.ga, sc.grad_ws.as<float>(), c->stream);
+    int rb = launch_lora_grads(hs, dy16, N, gs, x16, dscale, M, N, K, r, l->lora.gb, l->lora.ga, sc.grad_ws.as<float>(), c->stream);
     if (rb > 1) return c->fail(RT_ERR_CUDA, "lora gradient kernel launch failed");
     int ra = rb;
     if (rb == 1) {  // shapes the fused kernels do not cover: one product at a time
@@ -218,6 +219,110 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
   return RT_OK;
 }
 
+
+// ---- groups of linears that share their input (see LinGroup)
+static bool group_lora_on(const LinGroup& g, bool* any) {
+  // usable as one product only when every member that has an adapter also has it enabled
+  bool on = false, off = false;
+  for (int i = 0; i < g.n; ++i)
+    if (g.lin[i]->has_lora) (g.lin[i]->lora_enabled ? on : off) = true;
+  *any = on;
+  return !(on && off);
+}
+bool group_usable(const LinGroup& g) {
+  if (!g.stacked) return false;
+  bool any;
+  if (!group_lora_on(g, &any)) return false;
+  return !any || g.lora_ok;
+}
+
+static void group_refresh(LinGroup& g, cudaStream_t st) {
+  const size_t K = (size_t)g.w.cols;
+  for (int i = 0; i < g.n; ++i) {
+    rt_linear* l = g.lin[i];
+    if (!l->has_lora || g.seen[i] == l->lora.version) continue;
+    LoraDev& lo = l->lora;
+    launch_lora_refresh_group(lo.a, lo.b, lo.rank, (int)K, l->out_dim(), lo.scale(), g.a_s + (size_t)g.rank_off[i] * K,
+                              g.a_h + (size_t)g.rank_off[i] * K, g.bp + (size_t)g.row_off[i] * 64 + g.rank_off[i],
+                              g.bt_s + (size_t)g.rank_off[i] * g.rows_total + g.row_off[i], (size_t)g.rows_total, st);
+    g.seen[i] = lo.version;
+  }
+}
+
+// y[M x rows_total] = X . [W_0; W_1; ..]^T (+ stacked bias, + stacked low-rank chunk)
+rt_status group_forward_dev(LinGroup& g, LinearScratch& sc, const __half* x16, int M, void* y, int y_dtype, __half* hs_keep) {
+  rt_ctx* c = g.lin[0]->ctx;
+  if (M <= 0) return RT_OK;
+  QGemmArgs a;
+  a.dir = QG_FWD;
+  a.act = x16;
+  a.act_f16 = 1;
+  a.M = M;
+  a.out = y;
+  a.out_dtype = y_dtype;
+  a.bias = g.bias;
+  bool any;
+  group_lora_on(g, &any);
+  if (any) {
+    group_refresh(g, c->stream);
+    __half* hs = hs_keep ? hs_keep : lowrank_buf(c, sc.hs, sc.hs_rank, M, g.rank_total);
+    if (!hs) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+    if (launch_skinny_nt(x16, g.a_s, M, g.w.cols, g.rank_total, hs, c->stream)) return c->fail(RT_ERR_CUDA, "lora H kernel launch failed");
+    a.lora.act = hs;
+    a.lora.w = g.bp;
+    a.lora.rank = g.rank_total;
+  }
+  int rc = qgemm_launch(c, g.w, a);
+  if (rc) return c->fail(rc, "frozen forward matmul launch failed");
+  return RT_OK;
+}
+
+// dx[M x K] (+)= dY[M x rows_total] . [W_0; W_1; ..] (+ Gs . A), dY row-normalised with ONE factor per token
+// for the whole row; each member's dA, dB from its slices.
+rt_status group_backward_dev(LinGroup& g, LinearScratch& sc, const __half* x16, const __half* dy16, const float* dscale,
+                             int M, float* dx, int accumulate, const __half* hs_saved) {
+  rt_ctx* c = g.lin[0]->ctx;
+  if (M <= 0) return RT_OK;
+  const int K = g.w.cols, NT = g.rows_total;
+  QGemmArgs a;
+  a.dir = QG_BWD;
+  a.act = dy16;
+  a.act_f16 = 1;
+  a.M = M;
+  a.out = dx;
+  a.out_dtype = OUT_F32;
+  a.accumulate = accumulate;
+  a.row_scale = dscale;
+  bool any;
+  group_lora_on(g, &any);
+  if (any) {
+    group_refresh(g, c->stream);
+    const int R = g.rank_total;
+    __half* hs = hs_saved ? const_cast<__half*>(hs_saved) : lowrank_buf(c, sc.hs, sc.hs_rank, M, R);
+    __half* gs = lowrank_buf(c, sc.gs, sc.gs_rank, M, R);
+    if (!hs || !gs) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+    if (!hs_saved && launch_skinny_nt(x16, g.a_s, M, K, R, hs, c->stream)) return c->fail(RT_ERR_CUDA, "lora H kernel launch failed");
+    if (launch_skinny_nt(dy16, g.bt_s, M, NT, R, gs, c->stream)) return c->fail(RT_ERR_CUDA, "lora G kernel launch failed");
+    size_t wsf = 0;
+    for (int i = 0; i < g.n; ++i)
+      if (g.lin[i]->has_lora) wsf = std::max(wsf, lora_grads_workspace_floats(M, g.lin[i]->out_dim(), K, g.lin[i]->lora.rank));
+    if (!sc.grad_ws.reserve(wsf * sizeof(float))) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+    for (int i = 0; i < g.n; ++i) {
+      rt_linear* l = g.lin[i];
+      if (!l->has_lora) continue;
+      if (launch_lora_grads(hs + g.rank_off[i], dy16 + g.row_off[i], NT, gs + g.rank_off[i], x16, dscale, M, l->out_dim(), K,
+                            l->lora.rank, l->lora.gb, l->lora.ga, sc.grad_ws.as<float>(), c->stream))
+        return c->fail(RT_ERR_CUDA, "lora gradient kernel launch failed");
+    }
+    a.lora.act = gs;
+    a.lora.w = g.a_h;
+    a.lora.rank = R;
+  }
+  int rc = qgemm_launch(c, g.w, a);
+  if (rc) return c->fail(rc, "frozen backward matmul launch failed");
+  return RT_OK;
+}
+
 // tensor.rs:155-199 Rng, host side, for Lora::new's A ~ U(-1/sqrt(in), 1/sqrt(in))
 struct SplitMix {
   uint64_t state;
@@ -258,6 +363,7 @@ static rt_status attach_views(rt_linear* l, int rank, float alpha, float* a, flo
   lo.bp = (__half*)(base + 2 * up(n_as));
   lo.bt_s = (__half*)(base + 2 * up(n_as) + up(n_bp));
   lo.stale = true;
+  ++lo.version;
   l->has_lora = true;
   return RT_OK;
 }
@@ -406,6 +512,7 @@ rt_status rt_lora_write(rt_linear* l, const float* a, const float* b) {
   if (b) RT_CUDA(c, cudaMemcpyAsync(l->lora.b, b, nb, cudaMemcpyHostToDevice, c->stream));
   RT_CUDA(c, cudaStreamSynchronize(c->stream));
   l->lora.stale = true;
+  ++l->lora.version;
   return RT_OK;
 }
 
@@ -450,9 +557,12 @@ void rt_model_destroy(rt_model* m) {
   if (!m) return;
   cudaSetDevice(m->ctx->device);
   cudaStreamSynchronize(m->ctx->stream);
-  for (auto& b : m->blocks)
+  for (auto& b : m->blocks) {
     for (int i = 0; i < 7; ++i)
       if (b.lin[i]) rt_linear_destroy(b.lin[i]);
+    b.qkv.store.release(); b.qkv.lora_copies.release();
+    b.gu.store.release(); b.gu.lora_copies.release();
+  }
   if (m->lm_head && m->lm_head != m->embed) rt_frozen_destroy(m->lm_head);
   if (m->embed) rt_frozen_destroy(m->embed);
   for (void* p : m->owned) cudaFree(p);
@@ -559,6 +669,85 @@ rt_status rt_model_set_tensor(rt_model* m, const char* name, int ggml_type, size
   return c->fail(RT_ERR_BAD_ARG, n + ": unknown tensor name");
 }
 
+
+// Stack the packed weights of `n` linears along the output rows (see LinGroup).  The members keep
+// working on their own: their handles point into the stacked buffer afterwards.
+static rt_status build_group(rt_model* m, LinGroup& g, rt_linear** lin, int n) {
+  rt_ctx* c = m->ctx;
+  g = LinGroup();
+  g.n = n;
+  const QWeight& w0 = lin[0]->w->w;
+  size_t bytes = 0;
+  bool has_bias = false;
+  for (int i = 0; i < n; ++i) {
+    g.lin[i] = lin[i];
+    const QWeight& w = lin[i]->w->w;
+    if (w.fmt != w0.fmt || w.cols != w0.cols || w.rows % 128 != 0 || lin[i]->w->borrowed) return RT_OK;  // stays unstacked
+    g.row_off[i] = g.rows_total;
+    g.rows_total += w.rows;
+    bytes += w.dev_nbytes;
+    has_bias |= lin[i]->bias != nullptr;
+  }
+  if (!g.store.reserve(bytes)) return c->fail(RT_ERR_CUDA, "out of device memory (stacked weights)");
+  g.w = w0;
+  g.w.rows = g.rows_total;
+  g.w.dev_nbytes = bytes;
+  g.w.ggml_nbytes = 0;
+  const bool is16 = fmt_is_16bit(w0.fmt);
+  if (is16) g.w.dense16 = g.store.p;
+  else { g.w.bricks = (uint8_t*)g.store.p; g.w.nbr = g.rows_total / 64; }
+  size_t off = 0;
+  for (int i = 0; i < n; ++i) {
+    QWeight& w = lin[i]->w->w;
+    uint8_t* dst = (uint8_t*)g.store.p + off;
+    RT_CUDA(c, cudaMemcpy(dst, is16 ? w.dense16 : (void*)w.bricks, w.dev_nbytes, cudaMemcpyDeviceToDevice));
+    RT_CUDA(c, cudaFree(is16 ? w.dense16 : (void*)w.bricks));
+    if (is16) w.dense16 = dst; else w.bricks = dst;
+    lin[i]->w->borrowed = true;
+    off += w.dev_nbytes;
+  }
+  if (has_bias) {
+    RT_CUDA(c, cudaMalloc(&g.bias, (size_t)g.rows_total * sizeof(float)));
+    m->owned.push_back(g.bias);
+    RT_CUDA(c, cudaMemset(g.bias, 0, (size_t)g.rows_total * sizeof(float)));
+    for (int i = 0; i < n; ++i)
+      if (lin[i]->bias)
+        RT_CUDA(c, cudaMemcpy(g.bias + g.row_off[i], lin[i]->bias, (size_t)lin[i]->out_dim() * sizeof(float), cudaMemcpyDeviceToDevice));
+  }
+  g.stacked = true;
+  g.lora_ok = true;  // no adapters yet
+  return RT_OK;
+}
+
+// After adapters are attached: lay the members' adapters out as one stacked low-rank chunk.
+static rt_status build_group_lora(rt_model* m, LinGroup& g) {
+  rt_ctx* c = m->ctx;
+  if (!g.stacked) return RT_OK;
+  g.rank_total = 0;
+  g.lora_ok = true;
+  for (int i = 0; i < g.n; ++i) {
+    g.seen[i] = 0;
+    g.rank_off[i] = g.rank_total;
+    if (!g.lin[i]->has_lora) continue;
+    const int r = g.lin[i]->lora.rank;
+    if (r % 8 != 0) g.lora_ok = false;  // column offsets must stay 16-byte aligned
+    g.rank_total += r;
+  }
+  if (g.rank_total > 64 || (g.rank_total & 1)) g.lora_ok = false;
+  if (g.rank_total == 0 || !g.lora_ok) return RT_OK;
+  const size_t K = (size_t)g.w.cols, NT = (size_t)g.rows_total, R = (size_t)g.rank_total;
+  auto up = [](size_t n) { return (n * 2 + 255) / 256 * 256; };
+  const size_t total = 2 * up(R * K) + up(NT * 64) + up(R * NT);
+  if (!g.lora_copies.reserve(total)) return c->fail(RT_ERR_CUDA, "out of device memory (stacked adapter copies)");
+  RT_CUDA(c, cudaMemset(g.lora_copies.p, 0, g.lora_copies.bytes));
+  uint8_t* base = (uint8_t*)g.lora_copies.p;
+  g.a_s = (__half*)base;
+  g.a_h = (__half*)(base + up(R * K));
+  g.bp = (__half*)(base + 2 * up(R * K));
+  g.bt_s = (__half*)(base + 2 * up(R * K) + up(NT * 64));
+  return RT_OK;
+}
+
 rt_status rt_model_finalize(rt_model* m) {
   if (!m) return RT_ERR_BAD_ARG;
   rt_ctx* c = m->ctx;
@@ -576,6 +765,15 @@ rt_status rt_model_finalize(rt_model* m) {
   }
   // opt_scalars: [0,1024) f64 partials, [1024] f64 sum, then one f32 norm
   if (!m->opt_scalars.reserve(1025 * sizeof(double) + 16) || !m->amax.reserve(16)) return c->fail(RT_ERR_CUDA, "out of device memory");
+  if (!m->finalized) {
+    const char* e = getenv("RT_B200_NO_GROUPS");  // measurement aid: one matmul per projection
+    if (!(e && e[0] == '1'))
+      for (auto& b : m->blocks) {
+        rt_status st = build_group(m, b.qkv, &b.lin[0], 3);
+        if (!st) st = build_group(m, b.gu, &b.lin[4], 2);
+        if (st) return st;
+      }
+  }
   m->finalized = true;
   return RT_OK;
 }
@@ -611,7 +809,11 @@ rt_status rt_model_attach_lora(rt_model* m, int rank, float alpha, const char* t
       }
     }
   m->n_params = total;
-  if (total == 0) { if (n_out) *n_out = 0; return RT_OK; }
+  if (total == 0) {
+    for (auto& b : m->blocks) { build_group_lora(m, b.qkv); build_group_lora(m, b.gu); }
+    if (n_out) *n_out = 0;
+    return RT_OK;
+  }
   const size_t bytes = total * sizeof(float);
   if (!m->P.reserve(bytes) || !m->G.reserve(bytes) || !m->Mo.reserve(bytes) || !m->Vo.reserve(bytes))
     return c->fail(RT_ERR_CUDA, "out of device memory (adapter state)");
@@ -627,6 +829,11 @@ rt_status rt_model_attach_lora(rt_model* m, int rank, float alpha, const char* t
     rt_status st = attach_views(l, rank, alpha, base + off, base + off + na, gbase + off, gbase + off + na);
     if (st) return st;
     off += na + nb;
+  }
+  for (auto& b : m->blocks) {
+    rt_status st = build_group_lora(m, b.qkv);
+    if (!st) st = build_group_lora(m, b.gu);
+    if (st) return st;
   }
   RT_CUDA(c, cudaMemcpy(m->P.p, host.data(), bytes, cudaMemcpyHostToDevice));
   RT_CUDA(c, cudaMemset(m->G.p, 0, bytes));
@@ -682,7 +889,7 @@ static bool ensure_tokens(rt_model* m, int M) {
   const size_t d = g.hidden, ff = g.ff, qd = (size_t)g.n_heads * g.head_dim, kvd = (size_t)g.n_kv_heads * g.head_dim;
   const size_t T = (size_t)M;
   // per-layer bytes of everything a block's backward reads from its forward
-  const size_t per_layer = T * (d * 2 * 2 + qd * 4 + kvd * 4 + qd * 2 * 2 + kvd * 2 * 2 + (size_t)g.n_heads * 4 + d * 4 + ff * 2 * 3 + 7 * 64 * 2);
+  const size_t per_layer = T * (d * 2 * 2 + (qd + 2 * kvd) * 4 + qd * 2 * 2 + kvd * 2 * 2 + (size_t)g.n_heads * 4 + d * 4 + ff * 2 * 3 + 7 * 64 * 2);
   if (m->recompute_policy < 0) {
     const char* e = getenv("RT_B200_RECOMPUTE");
     m->recompute_policy = (e && e[0] == '1') ? 1 : 0;
@@ -702,18 +909,19 @@ static bool ensure_tokens(rt_model* m, int M) {
   ok &= m->tokens.reserve(T * 4) && m->pos.reserve(T * 4) && m->seq_start.reserve(T * 4);
   ok &= m->x.reserve(T * d * 4) && m->ckpt.reserve(T * d * 4 * g.n_layers) && m->h.reserve(T * d * 4 * L);
   ok &= m->n1.reserve(T * d * 2 * L) && m->n2.reserve(T * d * 2 * L);
-  ok &= m->q_raw.reserve(T * qd * 4 * L) && m->k_raw.reserve(T * kvd * 4 * L) && m->v_raw.reserve(T * kvd * 4);
+  ok &= m->q_raw.reserve(T * (qd + 2 * kvd) * 4 * L);  // q | k | v before RoPE
   ok &= m->q16.reserve(T * qd * 2 * L) && m->k16.reserve(T * kvd * 2 * L) && m->v16.reserve(T * kvd * 2 * L) && m->o16.reserve(T * qd * 2 * L);
   ok &= m->lse.reserve(T * g.n_heads * 4 * L) && m->delta.reserve(T * g.n_heads * 4);
-  ok &= m->g16.reserve(T * ff * 2 * L) && m->u16.reserve(T * ff * 2 * L) && m->hm16.reserve(T * ff * 2 * L);
+  ok &= m->g16.reserve(T * ff * 2 * 2 * L) && m->hm16.reserve(T * ff * 2 * L);  // gate | up
   ok &= m->dx.reserve(T * d * 4) && m->dy16.reserve(T * d * 2) && m->sc_y.reserve(T * 4);
-  ok &= m->dhm.reserve(T * ff * 2) && m->dg16.reserve(T * ff * 2) && m->du16.reserve(T * ff * 2);
+  ok &= m->dhm.reserve(T * ff * 2) && m->dg16.reserve(T * ff * 2 * 2);  // d(gate) | d(up)
   ok &= m->sc_g.reserve(T * 4) && m->sc_u.reserve(T * 4) && m->dn.reserve(T * d * 4);
   ok &= m->dO16.reserve(T * qd * 2);
   ok &= m->dq.reserve(T * qd * 4) && m->dk.reserve(T * kvd * 4) && m->dv.reserve(T * kvd * 4);
-  ok &= m->dq16.reserve(T * qd * 2) && m->dk16.reserve(T * kvd * 2) && m->dv16.reserve(T * kvd * 2);
+  ok &= m->dq16.reserve(T * (qd + 2 * kvd) * 2);  // d(q) | d(k) | d(v)
   ok &= m->sc_q.reserve(T * 4) && m->sc_k.reserve(T * 4) && m->sc_v.reserve(T * 4);
-  for (int i = 0; i < 7; ++i) ok &= m->hs_keep[i].reserve(T * 64 * 2 * L, true);  // zero beyond the rank, kept that way
+  // zero beyond the rank, kept that way; 256 bytes of slack for reads that start at a column offset
+  for (int i = 0; i < 7; ++i) ok &= m->hs_keep[i].reserve(T * 64 * 2 * L + 256, true);
   if (ok) m->cap_tokens = M;
   return ok;
 }
@@ -722,25 +930,35 @@ static bool ensure_tokens(rt_model* m, int M) {
 // layer li owns the li-th slice (of M tokens) of each buffer; otherwise all layers share slice 0.
 struct BlockActs {
   __half *n1, *n2, *q16, *k16, *v16, *o16, *g16, *u16, *hm16, *hs[7];
-  float *q_raw, *k_raw, *h, *lse;
+  float *q_raw, *k_raw, *v_raw, *h, *lse;
+  size_t qkv_pitch, gu_pitch;  // 0: separate matrices; else q|k|v (gate|up) are column slices of one matrix
+  bool qkv_group, gu_group;
 };
 static BlockActs block_acts(rt_model* m, int li, int M, bool own_slice) {
   const rt_model_config& g = m->cfg;
   const size_t d = g.hidden, ff = g.ff, qd = (size_t)g.n_heads * g.head_dim, kvd = (size_t)g.n_kv_heads * g.head_dim;
-  const size_t o = own_slice ? (size_t)li * (size_t)M : 0;
+  const size_t o = own_slice ? (size_t)li * (size_t)M : 0, T = (size_t)M;
+  BlockDev& b = m->blocks[li];
   BlockActs a;
+  a.qkv_group = group_usable(b.qkv) && qk_rope_takes_pitches(g.n_heads, g.n_kv_heads, g.head_dim, g.rot_dim, g.rope_neox);
+  a.gu_group = group_usable(b.gu) && (ff % 8 == 0);
   a.n1 = m->n1.as<__half>() + o * d;
   a.n2 = m->n2.as<__half>() + o * d;
   a.q16 = m->q16.as<__half>() + o * qd;
   a.k16 = m->k16.as<__half>() + o * kvd;
   a.v16 = m->v16.as<__half>() + o * kvd;
   a.o16 = m->o16.as<__half>() + o * qd;
-  a.g16 = m->g16.as<__half>() + o * ff;
-  a.u16 = m->u16.as<__half>() + o * ff;
   a.hm16 = m->hm16.as<__half>() + o * ff;
   for (int i = 0; i < 7; ++i) a.hs[i] = m->hs_keep[i].as<__half>() + o * 64;
-  a.q_raw = m->q_raw.as<float>() + o * qd;
-  a.k_raw = m->k_raw.as<float>() + o * kvd;
+  float* qkv = m->q_raw.as<float>() + o * (qd + 2 * kvd);
+  a.q_raw = qkv;
+  a.k_raw = a.qkv_group ? qkv + qd : qkv + T * qd;
+  a.v_raw = a.qkv_group ? qkv + qd + kvd : qkv + T * (qd + kvd);
+  a.qkv_pitch = a.qkv_group ? qd + 2 * kvd : 0;
+  __half* gu = m->g16.as<__half>() + o * 2 * ff;
+  a.g16 = gu;
+  a.u16 = a.gu_group ? gu + ff : gu + T * ff;
+  a.gu_pitch = a.gu_group ? 2 * ff : 0;
   a.h = m->h.as<float>() + o * d;
   a.lse = m->lse.as<float>() + o * g.n_heads;
   return a;
@@ -801,10 +1019,14 @@ static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, fl
   cudaStream_t st = c->stream;
   const int d = g.hidden;
   launch_rmsnorm_fwd(x_in, b.input_norm, M, d, g.rms_eps, A.n1, st);
-  RT_TRY(linear_forward_dev(b.lin[0], m->lsc, A.n1, M, A.q_raw, RT_DT_F32, 0, keep ? A.hs[0] : nullptr));
-  RT_TRY(linear_forward_dev(b.lin[1], m->lsc, A.n1, M, A.k_raw, RT_DT_F32, 0, keep ? A.hs[1] : nullptr));
-  RT_TRY(linear_forward_dev(b.lin[2], m->lsc, A.n1, M, m->v_raw.p, RT_DT_F32, 0, keep ? A.hs[2] : nullptr));
-  launch_qk_rope_fwd(A.q_raw, A.k_raw, m->v_raw.as<float>(), g.qk_norm ? b.q_norm : nullptr,
+  if (A.qkv_group) {
+    RT_TRY(group_forward_dev(b.qkv, m->lsc, A.n1, M, A.q_raw, RT_DT_F32, keep ? A.hs[0] : nullptr));
+  } else {
+    RT_TRY(linear_forward_dev(b.lin[0], m->lsc, A.n1, M, A.q_raw, RT_DT_F32, 0, keep ? A.hs[0] : nullptr));
+    RT_TRY(linear_forward_dev(b.lin[1], m->lsc, A.n1, M, A.k_raw, RT_DT_F32, 0, keep ? A.hs[1] : nullptr));
+    RT_TRY(linear_forward_dev(b.lin[2], m->lsc, A.n1, M, A.v_raw, RT_DT_F32, 0, keep ? A.hs[2] : nullptr));
+  }
+  launch_qk_rope_fwd(A.q_raw, A.k_raw, A.v_raw, A.qkv_pitch, g.qk_norm ? b.q_norm : nullptr,
                      g.qk_norm ? b.k_norm : nullptr, m->pos.as<int>(), m->rope_cos.as<float>(), m->rope_sin.as<float>(), M,
                      g.n_heads, g.n_kv_heads, g.head_dim, g.rot_dim, g.rope_neox, g.rms_eps, A.q16, A.k16, A.v16, st);
   if (launch_attn_fwd(A.q16, A.k16, A.v16, m->seq_start.as<int>(), M, g.n_heads, g.n_kv_heads, g.head_dim, A.o16, A.lse, st))
@@ -812,9 +1034,13 @@ static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, fl
   if (h != x_in) RT_CUDA(c, cudaMemcpyAsync(h, x_in, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
   RT_TRY(linear_forward_dev(b.lin[3], m->lsc, A.o16, M, h, RT_DT_F32, 1, keep ? A.hs[3] : nullptr));
   launch_rmsnorm_fwd(h, b.post_norm, M, d, g.rms_eps, A.n2, st);
-  RT_TRY(linear_forward_dev(b.lin[4], m->lsc, A.n2, M, A.g16, RT_DT_F16, 0, keep ? A.hs[4] : nullptr));
-  RT_TRY(linear_forward_dev(b.lin[5], m->lsc, A.n2, M, A.u16, RT_DT_F16, 0, keep ? A.hs[5] : nullptr));
-  launch_swiglu_fwd(A.g16, A.u16, A.hm16, (size_t)M * g.ff, st);
+  if (A.gu_group) {
+    RT_TRY(group_forward_dev(b.gu, m->lsc, A.n2, M, A.g16, RT_DT_F16, keep ? A.hs[4] : nullptr));
+  } else {
+    RT_TRY(linear_forward_dev(b.lin[4], m->lsc, A.n2, M, A.g16, RT_DT_F16, 0, keep ? A.hs[4] : nullptr));
+    RT_TRY(linear_forward_dev(b.lin[5], m->lsc, A.n2, M, A.u16, RT_DT_F16, 0, keep ? A.hs[5] : nullptr));
+  }
+  launch_swiglu_fwd(A.g16, A.u16, A.gu_pitch, M, g.ff, A.hm16, st);
   if (x_out) {
     if (x_out != h) RT_CUDA(c, cudaMemcpyAsync(x_out, h, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
     RT_TRY(linear_forward_dev(b.lin[6], m->lsc, A.hm16, M, x_out, RT_DT_F32, 1, keep ? A.hs[6] : nullptr));
@@ -839,10 +1065,17 @@ static rt_status block_backward(rt_model* m, int li, int M, const float* x_in, c
   // Mlp::backward (src/model.rs:120-134)
   // d(hm) leaves the matmul as f16 rows still lacking sc_y: SwiGLU's backward folds the factor into its own scales
   RT_TRY(linear_backward_dev(b.lin[6], m->lsc, A.hm16, dy16, sc_y, M, m->dhm.p, 0, HS(6), true));
-  launch_swiglu_bwd(m->dhm.p, 1, sc_y, A.g16, A.u16, M, g.ff, m->dg16.as<__half>(),
-                    m->du16.as<__half>(), m->sc_g.as<float>(), m->sc_u.as<float>(), st);
-  RT_TRY(linear_backward_dev(b.lin[4], m->lsc, A.n2, m->dg16.as<__half>(), m->sc_g.as<float>(), M, m->dn.as<float>(), 0, HS(4)));
-  RT_TRY(linear_backward_dev(b.lin[5], m->lsc, A.n2, m->du16.as<__half>(), m->sc_u.as<float>(), M, m->dn.as<float>(), 1, HS(5)));
+  const size_t T = (size_t)M, ff = g.ff;
+  __half* dg16 = m->dg16.as<__half>();
+  __half* du16 = A.gu_group ? dg16 + ff : dg16 + T * ff;
+  launch_swiglu_bwd(m->dhm.p, 1, sc_y, A.g16, A.u16, A.gu_pitch, M, g.ff, dg16, du16, A.gu_pitch, m->sc_g.as<float>(),
+                    m->sc_u.as<float>(), st);
+  if (A.gu_group) {
+    RT_TRY(group_backward_dev(b.gu, m->lsc, A.n2, dg16, m->sc_g.as<float>(), M, m->dn.as<float>(), 0, HS(4)));
+  } else {
+    RT_TRY(linear_backward_dev(b.lin[4], m->lsc, A.n2, dg16, m->sc_g.as<float>(), M, m->dn.as<float>(), 0, HS(4)));
+    RT_TRY(linear_backward_dev(b.lin[5], m->lsc, A.n2, du16, m->sc_u.as<float>(), M, m->dn.as<float>(), 1, HS(5)));
+  }
   // dh = dy + rmsnorm_backward(h, post_norm, dn2)
   launch_rmsnorm_bwd(A.h, b.post_norm, m->dn.as<float>(), dx, M, d, g.rms_eps, dx, dy16, sc_y, st);
   // Attention::backward (src/attention.rs:246-367)
@@ -854,14 +1087,21 @@ static rt_status block_backward(rt_model* m, int li, int M, const float* x_in, c
                       m->amax.as<float>(), sc_y, A.lse, m->seq_start.as<int>(), M, g.n_heads, g.n_kv_heads, g.head_dim,
                       m->delta.as<float>(), m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>(), st))
     return c->fail(RT_ERR_CUDA, "attention backward launch failed");
-  launch_qk_rope_bwd(m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>(), A.q_raw, A.k_raw,
+  const size_t qd = (size_t)g.n_heads * g.head_dim, kvd = (size_t)g.n_kv_heads * g.head_dim;
+  __half* dq16 = m->dq16.as<__half>();
+  __half* dk16 = A.qkv_group ? dq16 + qd : dq16 + T * qd;
+  __half* dv16 = A.qkv_group ? dq16 + qd + kvd : dq16 + T * (qd + kvd);
+  launch_qk_rope_bwd(m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>(), A.q_raw, A.k_raw, A.qkv_pitch,
                      g.qk_norm ? b.q_norm : nullptr, g.qk_norm ? b.k_norm : nullptr, m->pos.as<int>(), m->rope_cos.as<float>(),
                      m->rope_sin.as<float>(), M, g.n_heads, g.n_kv_heads, g.head_dim, g.rot_dim, g.rope_neox, g.rms_eps,
-                     m->dq16.as<__half>(), m->dk16.as<__half>(), m->dv16.as<__half>(), m->sc_q.as<float>(), m->sc_k.as<float>(),
-                     m->sc_v.as<float>(), st);
-  RT_TRY(linear_backward_dev(b.lin[0], m->lsc, A.n1, m->dq16.as<__half>(), m->sc_q.as<float>(), M, m->dn.as<float>(), 0, HS(0)));
-  RT_TRY(linear_backward_dev(b.lin[1], m->lsc, A.n1, m->dk16.as<__half>(), m->sc_k.as<float>(), M, m->dn.as<float>(), 1, HS(1)));
-  RT_TRY(linear_backward_dev(b.lin[2], m->lsc, A.n1, m->dv16.as<__half>(), m->sc_v.as<float>(), M, m->dn.as<float>(), 1, HS(2)));
+                     dq16, dk16, dv16, A.qkv_pitch, m->sc_q.as<float>(), m->sc_k.as<float>(), m->sc_v.as<float>(), st);
+  if (A.qkv_group) {
+    RT_TRY(group_backward_dev(b.qkv, m->lsc, A.n1, dq16, m->sc_q.as<float>(), M, m->dn.as<float>(), 0, HS(0)));
+  } else {
+    RT_TRY(linear_backward_dev(b.lin[0], m->lsc, A.n1, dq16, m->sc_q.as<float>(), M, m->dn.as<float>(), 0, HS(0)));
+    RT_TRY(linear_backward_dev(b.lin[1], m->lsc, A.n1, dk16, m->sc_k.as<float>(), M, m->dn.as<float>(), 1, HS(1)));
+    RT_TRY(linear_backward_dev(b.lin[2], m->lsc, A.n1, dv16, m->sc_v.as<float>(), M, m->dn.as<float>(), 1, HS(2)));
+  }
   // dx = dh + rmsnorm_backward(x, input_norm, dn1)
   launch_rmsnorm_bwd(x_in, b.input_norm, m->dn.as<float>(), dx, M, d, g.rms_eps, dx, dy16, sc_y, st);
 #undef HS
@@ -1123,7 +1363,7 @@ rt_status rt_optim_step(rt_model* m, float lr, float max_norm, float beta1, floa
   const float bc1 = 1.0f - powf(beta1, (float)m->opt_t), bc2 = 1.0f - powf(beta2, (float)m->opt_t);
   launch_adamw(m->P.as<float>(), m->G.as<float>(), m->Mo.as<float>(), m->Vo.as<float>(), m->n_params, sum, max_norm, lr,
                beta1, beta2, eps, wd, bc1, bc2, normd, st);
-  for (rt_linear* l : m->lora_order) l->lora.stale = true;
+  for (rt_linear* l : m->lora_order) { l->lora.stale = true; ++l->lora.version; }
   float nrm = 0.f;
   RT_CUDA(c, cudaMemcpyAsync(&nrm, normd, 4, cudaMemcpyDeviceToHost, st));
   rt_status s = c->check_device_status("rt_optim_step");

@@ -24,6 +24,7 @@ struct LoraDev {
   __half *a_s = nullptr, *a_h = nullptr, *bp = nullptr, *bt_s = nullptr;  // 16-bit operand copies
   DevBuf shadows;
   bool stale = true;  // operand copies need rebuilding from a, b
+  uint64_t version = 1;  // bumped with every change of a, b: stacked copies elsewhere compare it
   float scale() const { return alpha / (float)rank; }
 };
 
@@ -63,9 +64,30 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
 rt_status lora_refresh(rt_linear* l);
 }  // namespace rt
 
+// Linears that read the same input (q|k|v, gate|up) as ONE matmul: their packed weights lie
+// stacked along the output rows in one buffer (the members' own handles point into it), so the
+// forward is a single product with the stacked rows as output features and the backward a
+// single product contracting over them, instead of one product per member plus accumulating
+// passes.  The members' adapters become one stacked low-rank chunk: member i owns columns
+// [rank_off[i], rank_off[i] + r_i) of Hs / Gs.
+struct LinGroup {
+  int n = 0;
+  rt_linear* lin[3] = {nullptr, nullptr, nullptr};
+  int row_off[3] = {0, 0, 0}, rank_off[3] = {0, 0, 0};
+  int rows_total = 0, rank_total = 0;
+  bool stacked = false;    // weights share one buffer
+  bool lora_ok = false;    // the members' adapters fit one 64-wide chunk (or there are none)
+  rt::QWeight w;
+  DevBuf store, lora_copies;
+  float* bias = nullptr;   // stacked biases (owned), null when no member has one
+  __half *a_s = nullptr, *a_h = nullptr, *bp = nullptr, *bt_s = nullptr;
+  uint64_t seen[3] = {0, 0, 0};
+};
+
 struct BlockDev {
   float *input_norm = nullptr, *post_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
   rt_linear* lin[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // q k v o gate up down
+  LinGroup qkv, gu;
 };
 
 struct rt_model {
@@ -99,6 +121,8 @@ struct rt_model {
   int recompute_policy = -1;  // -1: not read yet, 0: automatic, 1: always recompute, 2: always keep
   // activations, sized for `cap_tokens`
   int cap_tokens = 0, cap_targets = 0, cap_head_rows = 0;
+  // q_raw holds q|k|v before RoPE (three regions, or one matrix with q, k, v as column slices when the
+  // block runs them as a group); g16 holds gate|up the same way; dq16, dg16 likewise for the gradients
   DevBuf tokens, pos, seq_start, x, ckpt, h, n1, n2, q_raw, k_raw, v_raw, q16, k16, v16, o16, lse, delta, g16, u16, hm16;
   DevBuf dx, dy16, sc_y, dhm, dg16, du16, sc_g, sc_u, dn, d_o, dO16, amax, dq, dk, dv, dq16, dk16, dv16, sc_q, sc_k, sc_v;
   DevBuf tpos, ttok, tw, logp, hits, xs, ns16, logits, dl16, sc_l, dns, dxs;

@@ -376,6 +376,7 @@ __device__ __forceinline__ void store_epl_h(__half* p, const float* v) {
 template <int EPL, int HPW>
 __global__ void __launch_bounds__(256)
 qk_rope_fwd_reg_kernel(const float* __restrict__ q_raw, const float* __restrict__ k_raw, const float* __restrict__ v_raw,
+                       size_t pq, size_t pk, size_t pv,  // row pitches of the three inputs, in elements
                        const float* __restrict__ qw, const float* __restrict__ kw, const int* __restrict__ pos,
                        const float* __restrict__ cs, const float* __restrict__ sn, int nh, int nkv, int rot, int neox,
                        float eps, __half* __restrict__ q16, __half* __restrict__ k16, __half* __restrict__ v16) {
@@ -390,8 +391,8 @@ qk_rope_fwd_reg_kernel(const float* __restrict__ q_raw, const float* __restrict_
   for (int t = 0; t < HPW; ++t) {
     const int h = warp + t * 8;
     if (h < nheads) {
-      const float* src = h < nh ? q_raw + (m * nh + h) * HD : (h < nh + nkv ? k_raw + (m * nkv + (h - nh)) * HD
-                                                                           : v_raw + (m * nkv + (h - nh - nkv)) * HD);
+      const float* src = h < nh ? q_raw + m * pq + h * HD : (h < nh + nkv ? k_raw + m * pk + (h - nh) * HD
+                                                                         : v_raw + m * pv + (h - nh - nkv) * HD);
       load_epl<EPL>(src + lane * EPL, x[t]);
     }
   }
@@ -426,7 +427,9 @@ qk_rope_fwd_reg_kernel(const float* __restrict__ q_raw, const float* __restrict_
 template <int EPL, int HPW>
 __global__ void __launch_bounds__(256)
 qk_rope_bwd_reg_kernel(const float* __restrict__ dq, const float* __restrict__ dk, const float* __restrict__ dv,
-                       const float* __restrict__ q_raw, const float* __restrict__ k_raw, const float* __restrict__ qw,
+                       const float* __restrict__ q_raw, const float* __restrict__ k_raw, size_t pq, size_t pk,
+                       size_t oq, size_t ok, size_t ov, int common,  // output row pitches; one scale for all three
+                       const float* __restrict__ qw,
                        const float* __restrict__ kw, const int* __restrict__ pos, const float* __restrict__ cs,
                        const float* __restrict__ sn, int nh, int nkv, int rot, int neox, float eps,
                        __half* __restrict__ dq16, __half* __restrict__ dk16, __half* __restrict__ dv16,
@@ -447,7 +450,7 @@ qk_rope_bwd_reg_kernel(const float* __restrict__ dq, const float* __restrict__ d
                                                                         : dv + (m * nkv + (h - nh - nkv)) * HD);
       load_epl<EPL>(src + lane * EPL, g[t]);
       const float* nw = h < nh ? qw : (h < nh + nkv ? kw : nullptr);
-      if (nw) load_epl<EPL>((h < nh ? q_raw + (m * nh + h) * HD : k_raw + (m * nkv + (h - nh)) * HD) + lane * EPL, xr[t]);
+      if (nw) load_epl<EPL>((h < nh ? q_raw + m * pq + h * HD : k_raw + m * pk + (h - nh) * HD) + lane * EPL, xr[t]);
     }
   }
   float mx[3] = {0.f, 0.f, 0.f};
@@ -491,7 +494,12 @@ qk_rope_bwd_reg_kernel(const float* __restrict__ dq, const float* __restrict__ d
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) v = fmaxf(v, wmax[k][w]);
-    s3[k] = v > 0.f ? v : 1.f;
+    s3[k] = v;
+  }
+  if (common) s3[0] = s3[1] = s3[2] = fmaxf(s3[0], fmaxf(s3[1], s3[2]));
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    s3[k] = s3[k] > 0.f ? s3[k] : 1.f;
     inv[k] = 1.f / s3[k];
   }
   if (threadIdx.x == 0) { sq[m] = s3[0]; sk[m] = s3[1]; sv[m] = s3[2]; }
@@ -503,8 +511,8 @@ qk_rope_bwd_reg_kernel(const float* __restrict__ dq, const float* __restrict__ d
     float o[EPL];
 #pragma unroll
     for (int k = 0; k < EPL; ++k) o[k] = g[t][k] * inv[kind];
-    __half* dst = kind == 0 ? dq16 + (m * nh + h) * HD : (kind == 1 ? dk16 + (m * nkv + (h - nh)) * HD
-                                                                     : dv16 + (m * nkv + (h - nh - nkv)) * HD);
+    __half* dst = kind == 0 ? dq16 + m * oq + h * HD : (kind == 1 ? dk16 + m * ok + (h - nh) * HD
+                                                                   : dv16 + m * ov + (h - nh - nkv) * HD);
     store_epl_h<EPL>(dst + lane * EPL, o);
   }
 }
@@ -522,13 +530,19 @@ static bool rope_reg_ok(int nh, int nkv, int hd, int rot, int neox, int* epl, in
   *hpw = per <= 4 ? 4 : (per <= 6 ? 6 : 8);
   return true;
 }
-void launch_qk_rope_fwd(const float* q_raw, const float* k_raw, const float* v_raw, const float* qw, const float* kw,
-                        const int* pos, const float* cs, const float* sn, int M, int nh, int nkv, int hd, int rot,
-                        int neox, float eps, __half* q16, __half* k16, __half* v16, cudaStream_t st) {
+bool qk_rope_takes_pitches(int nh, int nkv, int hd, int rot, int neox) {
+  int e, h;
+  return rope_reg_ok(nh, nkv, hd, rot, neox, &e, &h);
+}
+void launch_qk_rope_fwd(const float* q_raw, const float* k_raw, const float* v_raw, size_t raw_pitch, const float* qw,
+                        const float* kw, const int* pos, const float* cs, const float* sn, int M, int nh, int nkv, int hd,
+                        int rot, int neox, float eps, __half* q16, __half* k16, __half* v16, cudaStream_t st) {
   if (M <= 0) return;
   int epl = 0, hpw = 0;
+  // raw_pitch = 0: three separate row-major matrices; else one row pitch for all three (slices of one matrix)
+  const size_t pq = raw_pitch ? raw_pitch : (size_t)nh * hd, pk = raw_pitch ? raw_pitch : (size_t)nkv * hd, pv = pk;
   if (rope_reg_ok(nh, nkv, hd, rot, neox, &epl, &hpw)) {
-#define RT_ROPE_FWD(E, H) qk_rope_fwd_reg_kernel<E, H><<<M, 256, 0, st>>>(q_raw, k_raw, v_raw, qw, kw, pos, cs, sn, nh, nkv, rot, neox, eps, q16, k16, v16)
+#define RT_ROPE_FWD(E, H) qk_rope_fwd_reg_kernel<E, H><<<M, 256, 0, st>>>(q_raw, k_raw, v_raw, pq, pk, pv, qw, kw, pos, cs, sn, nh, nkv, rot, neox, eps, q16, k16, v16)
     if (epl == 4) { if (hpw == 4) RT_ROPE_FWD(4, 4); else if (hpw == 6) RT_ROPE_FWD(4, 6); else RT_ROPE_FWD(4, 8); }
     else { if (hpw == 4) RT_ROPE_FWD(2, 4); else if (hpw == 6) RT_ROPE_FWD(2, 6); else RT_ROPE_FWD(2, 8); }
 #undef RT_ROPE_FWD
@@ -639,13 +653,17 @@ __global__ void qk_rope_bwd_kernel(const float* __restrict__ dq, const float* __
   }
 }
 void launch_qk_rope_bwd(const float* dq, const float* dk, const float* dv, const float* q_raw, const float* k_raw,
-                        const float* qw, const float* kw, const int* pos, const float* cs, const float* sn, int M, int nh,
-                        int nkv, int hd, int rot, int neox, float eps, __half* dq16, __half* dk16, __half* dv16,
-                        float* sq, float* sk, float* sv, cudaStream_t st) {
+                        size_t raw_pitch, const float* qw, const float* kw, const int* pos, const float* cs, const float* sn,
+                        int M, int nh, int nkv, int hd, int rot, int neox, float eps, __half* dq16, __half* dk16,
+                        __half* dv16, size_t out_pitch, float* sq, float* sk, float* sv, cudaStream_t st) {
   if (M <= 0) return;
   int epl = 0, hpw = 0;
+  // out_pitch != 0: the three outputs are slices of one matrix and share ONE scale per token
+  const size_t pq = raw_pitch ? raw_pitch : (size_t)nh * hd, pk = raw_pitch ? raw_pitch : (size_t)nkv * hd;
+  const size_t oq = out_pitch ? out_pitch : (size_t)nh * hd, ok = out_pitch ? out_pitch : (size_t)nkv * hd, ov = ok;
+  const int common = out_pitch ? 1 : 0;
   if (rope_reg_ok(nh, nkv, hd, rot, neox, &epl, &hpw)) {
-#define RT_ROPE_BWD(E, H) qk_rope_bwd_reg_kernel<E, H><<<M, 256, 0, st>>>(dq, dk, dv, q_raw, k_raw, qw, kw, pos, cs, sn, nh, nkv, rot, neox, eps, dq16, dk16, dv16, sq, sk, sv)
+#define RT_ROPE_BWD(E, H) qk_rope_bwd_reg_kernel<E, H><<<M, 256, 0, st>>>(dq, dk, dv, q_raw, k_raw, pq, pk, oq, ok, ov, common, qw, kw, pos, cs, sn, nh, nkv, rot, neox, eps, dq16, dk16, dv16, sq, sk, sv)
     if (epl == 4) { if (hpw == 4) RT_ROPE_BWD(4, 4); else if (hpw == 6) RT_ROPE_BWD(4, 6); else RT_ROPE_BWD(4, 8); }
     else { if (hpw == 4) RT_ROPE_BWD(2, 4); else if (hpw == 6) RT_ROPE_BWD(2, 6); else RT_ROPE_BWD(2, 8); }
 #undef RT_ROPE_BWD
@@ -683,10 +701,33 @@ __global__ void swiglu_fwd_kernel(const __half* __restrict__ g, const __half* __
     for (; i < n; ++i) h[i] = __float2half_rn(silu_f(__half2float(g[i])) * __half2float(u[i]));
   }
 }
-void launch_swiglu_fwd(const __half* g, const __half* u, __half* h, size_t n, cudaStream_t st) {
+// gate and up as column slices of one [rows x pitch] matrix (ff a multiple of 8)
+__global__ void swiglu_fwd_pitched_kernel(const __half* __restrict__ g, const __half* __restrict__ u, size_t pitch, int ff,
+                                          size_t n, __half* __restrict__ h) {
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  const size_t r = i / ff, c = i % ff;
+  const uint4 gv = *(const uint4*)(g + r * pitch + c), uv = *(const uint4*)(u + r * pitch + c);
+  const __half2* g2 = (const __half2*)&gv;
+  const __half2* u2 = (const __half2*)&uv;
+  uint4 o;
+  __half2* o2 = (__half2*)&o;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 a = __half22float2(g2[k]), b = __half22float2(u2[k]);
+    o2[k] = __floats2half2_rn(__fdividef(a.x, 1.0f + __expf(-a.x)) * b.x, __fdividef(a.y, 1.0f + __expf(-a.y)) * b.y);
+  }
+  *(uint4*)(h + i) = o;
+}
+void launch_swiglu_fwd(const __half* g, const __half* u, size_t in_pitch, int rows, int ff, __half* h, cudaStream_t st) {
+  const size_t n = (size_t)rows * ff;
   if (n == 0) return;
   size_t threads = (n + 7) / 8;
-  { swiglu_fwd_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(g, u, h, n); RT_COUNT_LAUNCH(1); }
+  if (in_pitch && in_pitch != (size_t)ff && (ff & 7) == 0)
+    swiglu_fwd_pitched_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(g, u, in_pitch, ff, n, h);
+  else
+    swiglu_fwd_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(g, u, h, n);
+  RT_COUNT_LAUNCH(1);
 }
 // dg = dh*u*silu'(g), du = dh*silu(g); both written row-normalised in f16 with per-row scales.
 // The kernel is bound by the exp/divide per element, so sigma is computed once per element with
@@ -726,8 +767,9 @@ __device__ __forceinline__ void swiglu_grad8(const DT* dh, const __half* g, cons
 template <int NCH, typename DT>  // 8-element chunks cached per thread: ff <= NCH * 8 * blockDim.x, ff % 8 == 0
 __global__ void swiglu_bwd_cached_kernel(const DT* __restrict__ dh, const float* __restrict__ in_scale,
                                          const __half* __restrict__ g,
-                                         const __half* __restrict__ u, int ff, __half* __restrict__ dg16,
-                                         __half* __restrict__ du16, float* __restrict__ sg, float* __restrict__ su) {
+                                         const __half* __restrict__ u, size_t gp, int ff, __half* __restrict__ dg16,
+                                         __half* __restrict__ du16, size_t op, int common, float* __restrict__ sg,
+                                         float* __restrict__ su) {
   const size_t r = blockIdx.x;
   float a[NCH][8], b[NCH][8];
   float mg = 0.f, mu = 0.f;
@@ -735,13 +777,14 @@ __global__ void swiglu_bwd_cached_kernel(const DT* __restrict__ dh, const float*
   for (int c = 0; c < NCH; ++c) {
     const int i = (c * blockDim.x + threadIdx.x) * 8;
     if (i < ff) {
-      swiglu_grad8(dh + r * ff + i, g + r * ff + i, u + r * ff + i, a[c], b[c]);
+      swiglu_grad8(dh + r * ff + i, g + r * gp + i, u + r * gp + i, a[c], b[c]);
 #pragma unroll
       for (int k = 0; k < 8; ++k) { mg = fmaxf(mg, fabsf(a[c][k])); mu = fmaxf(mu, fabsf(b[c][k])); }
     }
   }
   mg = block_max(mg);
   mu = block_max(mu);
+  if (common) mg = mu = fmaxf(mg, mu);  // gate and up gradients form ONE matrix with one scale per row
   const float s_g = mg > 0.f ? mg : 1.f, s_u = mu > 0.f ? mu : 1.f;
   const float ig = 1.f / s_g, iu = 1.f / s_u;
 #pragma unroll
@@ -756,8 +799,8 @@ __global__ void swiglu_bwd_cached_kernel(const DT* __restrict__ dh, const float*
         pa[k] = __floats2half2_rn(a[c][2 * k] * ig, a[c][2 * k + 1] * ig);
         pb[k] = __floats2half2_rn(b[c][2 * k] * iu, b[c][2 * k + 1] * iu);
       }
-      *(uint4*)(dg16 + r * ff + i) = oa;
-      *(uint4*)(du16 + r * ff + i) = ob;
+      *(uint4*)(dg16 + r * op + i) = oa;
+      *(uint4*)(du16 + r * op + i) = ob;
     }
   }
   if (threadIdx.x == 0) {
@@ -769,12 +812,13 @@ __global__ void swiglu_bwd_cached_kernel(const DT* __restrict__ dh, const float*
 // general row length: scalar, recomputed in the second pass
 template <typename DT>
 __global__ void swiglu_bwd_kernel(const DT* __restrict__ dh, const float* __restrict__ in_scale, const __half* __restrict__ g,
-                                  const __half* __restrict__ u, int ff, __half* __restrict__ dg16,
-                                  __half* __restrict__ du16, float* __restrict__ sg, float* __restrict__ su) {
+                                  const __half* __restrict__ u, size_t gp, int ff, __half* __restrict__ dg16,
+                                  __half* __restrict__ du16, size_t op, int common, float* __restrict__ sg,
+                                  float* __restrict__ su) {
   const size_t r = blockIdx.x;
   const DT* dhr = dh + r * ff;
-  const __half* gr = g + r * ff;
-  const __half* ur = u + r * ff;
+  const __half* gr = g + r * gp;
+  const __half* ur = u + r * gp;
   float mg = 0.f, mu = 0.f;
   for (int i = threadIdx.x; i < ff; i += blockDim.x) {
     const float gv = __half2float(gr[i]), uv = __half2float(ur[i]), d = ld1f(dhr + i);
@@ -784,13 +828,14 @@ __global__ void swiglu_bwd_kernel(const DT* __restrict__ dh, const float* __rest
   }
   mg = block_max(mg);
   mu = block_max(mu);
+  if (common) mg = mu = fmaxf(mg, mu);
   const float s_g = mg > 0.f ? mg : 1.f, s_u = mu > 0.f ? mu : 1.f;
   const float ig = 1.f / s_g, iu = 1.f / s_u;
   for (int i = threadIdx.x; i < ff; i += blockDim.x) {
     const float gv = __half2float(gr[i]), uv = __half2float(ur[i]), d = ld1f(dhr + i);
     const float s = sigmoid_f(gv);
-    dg16[r * ff + i] = __float2half_rn(d * uv * (s * (1.0f + gv * (1.0f - s))) * ig);
-    du16[r * ff + i] = __float2half_rn(d * silu_f(gv) * iu);
+    dg16[r * op + i] = __float2half_rn(d * uv * (s * (1.0f + gv * (1.0f - s))) * ig);
+    du16[r * op + i] = __float2half_rn(d * silu_f(gv) * iu);
   }
   if (threadIdx.x == 0) {
     const float f = in_scale ? in_scale[r] : 1.0f;
@@ -799,18 +844,23 @@ __global__ void swiglu_bwd_kernel(const DT* __restrict__ dh, const float* __rest
   }
 }
 template <typename DT>
-static void launch_swiglu_bwd_t(const DT* dh, const float* in_scale, const __half* g, const __half* u, int rows, int ff,
-                                __half* dg16, __half* du16, float* sg, float* su, cudaStream_t st) {
-  if ((ff & 7) == 0 && ff <= 2 * 8 * 256) swiglu_bwd_cached_kernel<2, DT><<<rows, 256, 0, st>>>(dh, in_scale, g, u, ff, dg16, du16, sg, su);
-  else if ((ff & 7) == 0 && ff <= 3 * 8 * 512) swiglu_bwd_cached_kernel<3, DT><<<rows, 512, 0, st>>>(dh, in_scale, g, u, ff, dg16, du16, sg, su);
-  else swiglu_bwd_kernel<DT><<<rows, 256, 0, st>>>(dh, in_scale, g, u, ff, dg16, du16, sg, su);
+static void launch_swiglu_bwd_t(const DT* dh, const float* in_scale, const __half* g, const __half* u, size_t gp, int rows,
+                                int ff, __half* dg16, __half* du16, size_t op, int common, float* sg, float* su,
+                                cudaStream_t st) {
+  if ((ff & 7) == 0 && ff <= 2 * 8 * 256) swiglu_bwd_cached_kernel<2, DT><<<rows, 256, 0, st>>>(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
+  else if ((ff & 7) == 0 && ff <= 3 * 8 * 512) swiglu_bwd_cached_kernel<3, DT><<<rows, 512, 0, st>>>(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
+  else swiglu_bwd_kernel<DT><<<rows, 256, 0, st>>>(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
   RT_COUNT_LAUNCH(1);
 }
-void launch_swiglu_bwd(const void* dh, int dh_f16, const float* in_scale, const __half* g, const __half* u, int rows, int ff,
-                       __half* dg16, __half* du16, float* sg, float* su, cudaStream_t st) {
+void launch_swiglu_bwd(const void* dh, int dh_f16, const float* in_scale, const __half* g, const __half* u, size_t in_pitch,
+                       int rows, int ff, __half* dg16, __half* du16, size_t out_pitch, float* sg, float* su, cudaStream_t st) {
   if (rows <= 0) return;
-  if (dh_f16) launch_swiglu_bwd_t((const __half*)dh, in_scale, g, u, rows, ff, dg16, du16, sg, su, st);
-  else launch_swiglu_bwd_t((const float*)dh, in_scale, g, u, rows, ff, dg16, du16, sg, su, st);
+  // in_pitch / out_pitch = 0: separate row-major matrices; else gate|up (dg|du) are slices of one
+  // matrix with that row pitch, and with out_pitch the two outputs share one scale per row
+  const size_t gp = in_pitch ? in_pitch : (size_t)ff, op = out_pitch ? out_pitch : (size_t)ff;
+  const int common = out_pitch ? 1 : 0;
+  if (dh_f16) launch_swiglu_bwd_t((const __half*)dh, in_scale, g, u, gp, rows, ff, dg16, du16, op, common, sg, su, st);
+  else launch_swiglu_bwd_t((const float*)dh, in_scale, g, u, gp, rows, ff, dg16, du16, op, common, sg, su, st);
 }
 
 // ------------------------------------------------------------------ row gather / scatter
@@ -945,6 +995,30 @@ __global__ void lora_refresh_kernel(const float* __restrict__ a, const float* __
     bp[i] = __float2half_rn(v);
     if (j < r) bt_s[(size_t)j * N + n] = __float2half_rn(v * s);
   }
+}
+// The same copies of one adapter written into the stacked operands of a group of linears that
+// share their input (q|k|v, gate|up): a_s / a_h are this adapter's rows of [R x K]; bp points at
+// (this linear's first row, this adapter's first column) of [N_total x 64]; bt_s at (this
+// adapter's first row, this linear's first column) of [R x N_total], row pitch ldb.
+__global__ void lora_refresh_group_kernel(const float* __restrict__ a, const float* __restrict__ b, int r, int K, int N,
+                                          float s, __half* a_s, __half* a_h, __half* bp, __half* bt_s, size_t ldb) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t na = (size_t)r * K, nb = (size_t)N * r;
+  if (i < na) {
+    a_s[i] = __float2half_rn(a[i] * s);
+    a_h[i] = __float2half_rn(a[i]);
+  }
+  if (i < nb) {
+    const int n = (int)(i / r), j = (int)(i % r);
+    const float v = b[i];
+    bp[(size_t)n * 64 + j] = __float2half_rn(v);
+    bt_s[(size_t)j * ldb + n] = __float2half_rn(v * s);
+  }
+}
+void launch_lora_refresh_group(const float* a, const float* b, int r, int K, int N, float s, __half* a_s, __half* a_h,
+                               __half* bp, __half* bt_s, size_t ldb, cudaStream_t st) {
+  size_t n = (size_t)r * K > (size_t)N * r ? (size_t)r * K : (size_t)N * r;
+  { lora_refresh_group_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a, b, r, K, N, s, a_s, a_h, bp, bt_s, ldb); RT_COUNT_LAUNCH(1); }
 }
 void launch_lora_refresh(const float* a, const float* b, int r, int K, int N, float s, __half* a_s, __half* a_h,
                          __half* bp, __half* bt_s, cudaStream_t st) {

@@ -12,21 +12,27 @@ void launch_rmsnorm_fwd(const float* x, const float* w, int rows, int d, float e
 void launch_rmsnorm_bwd(const float* x, const float* w, const float* dn, const float* dres, int rows, int d, float eps,
                         float* out, __half* out16, float* scale, cudaStream_t st);
 void launch_rope_table(const float* inv_freq, int half, int max_pos, float* cs, float* sn, cudaStream_t st);
-void launch_qk_rope_fwd(const float* q_raw, const float* k_raw, const float* v_raw, const float* qw, const float* kw,
-                        const int* pos, const float* cs, const float* sn, int M, int nh, int nkv, int hd, int rot,
-                        int neox, float eps, __half* q16, __half* k16, __half* v16, cudaStream_t st);
+// raw_pitch / out_pitch = 0: q, k, v are separate row-major matrices.  Otherwise they are column
+// slices of ONE matrix with that row pitch (elements); with out_pitch the three f16 outputs also
+// share one scale per token.  Pitches need the head shapes qk_rope_takes_pitches() accepts.
+bool qk_rope_takes_pitches(int nh, int nkv, int hd, int rot, int neox);
+void launch_qk_rope_fwd(const float* q_raw, const float* k_raw, const float* v_raw, size_t raw_pitch, const float* qw,
+                        const float* kw, const int* pos, const float* cs, const float* sn, int M, int nh, int nkv, int hd,
+                        int rot, int neox, float eps, __half* q16, __half* k16, __half* v16, cudaStream_t st);
 void launch_qk_rope_bwd(const float* dq, const float* dk, const float* dv, const float* q_raw, const float* k_raw,
-                        const float* qw, const float* kw, const int* pos, const float* cs, const float* sn, int M, int nh,
-                        int nkv, int hd, int rot, int neox, float eps, __half* dq16, __half* dk16, __half* dv16,
-                        float* sq, float* sk, float* sv, cudaStream_t st);
-void launch_swiglu_fwd(const __half* g, const __half* u, __half* h, size_t n, cudaStream_t st);
+                        size_t raw_pitch, const float* qw, const float* kw, const int* pos, const float* cs, const float* sn,
+                        int M, int nh, int nkv, int hd, int rot, int neox, float eps, __half* dq16, __half* dk16,
+                        __half* dv16, size_t out_pitch, float* sq, float* sk, float* sv, cudaStream_t st);
+void launch_swiglu_fwd(const __half* g, const __half* u, size_t in_pitch, int rows, int ff, __half* h, cudaStream_t st);
 // dh: f32 rows, or (dh_f16) f16 rows whose per-row factor in_scale[r] has not been applied yet
-void launch_swiglu_bwd(const void* dh, int dh_f16, const float* in_scale, const __half* g, const __half* u, int rows, int ff,
-                       __half* dg16, __half* du16, float* sg, float* su, cudaStream_t st);
+void launch_swiglu_bwd(const void* dh, int dh_f16, const float* in_scale, const __half* g, const __half* u, size_t in_pitch,
+                       int rows, int ff, __half* dg16, __half* du16, size_t out_pitch, float* sg, float* su, cudaStream_t st);
 void launch_gather_f32_rows(const float* x, const int* idx, int rows, int d, float* out, cudaStream_t st);
 void launch_scatter_add_rows(const float* src, const int* idx, int rows, int d, float* dx, cudaStream_t st);
 void launch_ce_rows(const float* logits, int rows, int v, const int* target, const float* weight, float* logp, int* hits,
                     __half* d16, float* scale, int* status, cudaStream_t st);
+void launch_lora_refresh_group(const float* a, const float* b, int r, int K, int N, float s, __half* a_s, __half* a_h,
+                               __half* bp, __half* bt_s, size_t ldb, cudaStream_t st);
 void launch_lora_refresh(const float* a, const float* b, int r, int K, int N, float s, __half* a_s, __half* a_h,
                          __half* bp, __half* bt_s, cudaStream_t st);
 size_t lora_grad_workspace_floats(int M, int C, int r);
@@ -44,8 +50,8 @@ void launch_global_normalize(const float* x, size_t n, float* amax_dev, __half* 
 int launch_skinny_nt(const __half* X, const __half* Wt, int M, int K, int r, __half* out64, cudaStream_t st);
 size_t tok_contract_workspace_floats(int M, int C, int r);
 size_t lora_grads_workspace_floats(int M, int N, int K, int r);
-int launch_lora_grads(const __half* hs, const __half* dy16, const __half* gs, const __half* x16, const float* dscale, int M,
-                      int N, int K, int r, float* gb, float* ga, float* workspace, cudaStream_t st);
+int launch_lora_grads(const __half* hs, const __half* dy16, int ld_dy, const __half* gs, const __half* x16, const float* dscale,
+                      int M, int N, int K, int r, float* gb, float* ga, float* workspace, cudaStream_t st);
 // pscale (optional): P's rows are multiplied by pscale[m] / alpha_dev[0] on the fly; alpha_dev[0] then scales the result
 int launch_tok_contract(const __half* P, const __half* Q, const float* pscale, int M, int C, int r, size_t so_i, size_t so_j,
                         const float* alpha_dev, float* out, float* workspace, cudaStream_t st);

@@ -153,6 +153,30 @@ def test_reruns_are_bit_identical_and_batching_is_neutral(ctx):
     om.close()
 
 
+def test_grouped_and_separate_projections_agree(ctx, monkeypatch):
+    """q|k|v and gate|up run as one stacked matmul each (one scale per token for the whole
+    gradient row); RT_B200_NO_GROUPS=1 keeps one matmul per projection.  Both meet the oracle, and
+    each other far inside the tolerances."""
+    out = {}
+    for flag in ("0", "1"):
+        monkeypatch.setenv("RT_B200_NO_GROUPS", flag)
+        spec, om, gm = _setup(ctx, "tiny-qwen3-hd128", "Q8_0")
+        seqs, tp, tt, per_seq = _batch(spec, [70, 45, 64, 129], seed=21)
+        w = np.full(tp.size, 1.0 / tp.size, np.float32)
+        gm.zero_grad()
+        lp, _ = gm.forward_backward(seqs, tp, tt, w)
+        out[flag] = (lp, _gpu_flat(gm, "ga", "gb"))
+        if flag == "1":
+            lp_o = _oracle_step(om, seqs, per_seq, w)
+            go = _flat(om.lora, "ga", "gb")
+        gm.close()
+        om.close()
+    for flag in ("0", "1"):
+        assert np.max(np.abs(out[flag][0] - lp_o) / np.abs(lp_o)) < LOSS_TOL
+        assert rel_l2(out[flag][1], go) < GRAD_TOL and cosine(out[flag][1], go) > GRAD_COS
+    assert rel_l2(out["0"][1], out["1"][1]) < 3e-3
+
+
 def test_checkpointing_modes_agree(ctx):
     """Model.checkpointing (src/model.rs:663-684): keeping every block's caches or rebuilding
     them before the backward runs the same kernels on the same data, so the results are equal
