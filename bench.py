@@ -298,6 +298,13 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
     ms_step = ms_total / args.steps
 
+    if args.launch_list:
+        if rank == 0:
+            print(json.dumps({"launch_list_run": True, "ms_per_step": ms_step, "gpu_launches_per_step": int(launches)}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
     # end to end through the host-buffer call
     for _ in range(min(args.warmup, 2)):
         step_e2e()
@@ -422,6 +429,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--launch-list", action="store_true",
+                    help="for a profiler's launch list: only the resident steps (no end-to-end, per-kernel or keep-caches "
+                         "phases, fewer warm-up steps allowed); the printed number is not a bench value")
     ap.add_argument("--checkpointing", default="on", choices=["on", "off", "auto"],
                     help="Model.checkpointing for the headline number (the workload says on)")
     ap.add_argument("--microbench", action="store_true", help="time the frozen-matmul kernel alone")
@@ -429,7 +439,7 @@ def main():
     ap.add_argument("--quant", default="", help="microbench: weight format instead of the workload's")
     ap.add_argument("--shape", default="", help="microbench: one OUTxIN shape instead of the workload's")
     args = ap.parse_args()
-    if args.warmup < 3 and args.impl == "ours":
+    if args.warmup < 3 and args.impl == "ours" and not args.launch_list:
         args.warmup = 3
     if args.microbench:
         return run_microbench(args)

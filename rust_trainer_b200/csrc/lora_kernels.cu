@@ -52,14 +52,17 @@ __device__ __forceinline__ void load64x64(uint32_t sbase, const __half* g, int r
 }
 
 // ------------------------------------------------------------------ Hs = X . Wt^T
-template <int R16>
-__global__ void __launch_bounds__(64)
+// MW warps of 16 token rows each per CTA.  The skinny weight is re-read by every CTA, so more rows
+// per CTA mean less traffic; fewer CTAs than SMs would idle some, so the launcher picks MW by M.
+template <int R16, int MW>
+__global__ void __launch_bounds__(32 * MW)
 skinny_nt_kernel(const __half* __restrict__ X, const __half* __restrict__ Wt, int M, int K, int r, __half* __restrict__ out) {
   constexpr int NST = 4;                       // stages in flight: the kernel is pure memory latency
-  constexpr int XB = 32 * 128, WB = 16 * R16 * 128, SB = XB + WB;
-  __shared__ __align__(128) uint8_t smem[NST * SB];
+  constexpr int ROWS = 16 * MW, NT = 32 * MW;
+  constexpr int XB = ROWS * 128, WB = 16 * R16 * 128, SB = XB + WB;
+  extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t s0 = saddr(smem);
-  const int m0 = blockIdx.x * 32;  // two warps, 16 token rows each: many small CTAs keep every SM busy
+  const int m0 = blockIdx.x * ROWS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
   const int mat = lane >> 3, rr = lane & 7;
   float acc[2 * R16][4];
@@ -68,12 +71,12 @@ skinny_nt_kernel(const __half* __restrict__ X, const __half* __restrict__ Wt, in
   const int nk = (K + 63) / 64;
   auto load = [&](int kc) {
     const uint32_t sx = s0 + (kc % NST) * SB, sw = sx + XB;
-    for (int e = threadIdx.x; e < 32 * 8; e += 64) {
+    for (int e = threadIdx.x; e < ROWS * 8; e += NT) {
       const int rw = e >> 3, c = e & 7, gr = m0 + rw, gc = kc * 64 + c * 8;
       const bool ok = gr < M && gc < K;
       cpa16(sx + toff(rw, c), X + (size_t)(ok ? gr : 0) * K + (ok ? gc : 0), ok);
     }
-    for (int e = threadIdx.x; e < 16 * R16 * 8; e += 64) {
+    for (int e = threadIdx.x; e < 16 * R16 * 8; e += NT) {
       const int rw = e >> 3, c = e & 7, gc = kc * 64 + c * 8;
       const bool ok = rw < r && gc < K;
       cpa16(sw + toff(rw, c), Wt + (size_t)(ok ? rw : 0) * K + (ok ? gc : 0), ok);
@@ -218,6 +221,8 @@ __global__ void tok_reduce_kernel(const float* __restrict__ part, int splits, in
 // C = K); grid.y is the token split.  The per-token factors of dY are applied to the rows of the
 // skinny operand relative to the LARGEST FACTOR OF THE SPLIT (found by the block itself), and
 // that maximum multiplies the split's partial sums, so no pass over all factors comes first.
+struct LoraGroupMember { float *gb, *ga; int row_off, rows, rank_off, r; };
+struct LoraGroupTable { int n; LoraGroupMember m[3]; };
 struct LoraGradArgs {
   const __half *Pb, *Qb, *Pa, *Qa;  // Hs, dY, Gs, X
   const float* pscale;              // per-token factors of dY, or null
@@ -344,15 +349,58 @@ __global__ void lora_grads_reduce_kernel(const float* __restrict__ partB, const 
   }
 }
 
+// The same for a group of linears that share X: partB is [splits][R x N_total] with the members'
+// diagonal blocks wanted (member j: rows rank_off..+r of the rank axis, columns row_off..+rows),
+// partA is [splits][R x K] with member j owning rows rank_off..+r.
+__global__ void lora_grads_group_reduce_kernel(const float* __restrict__ partB, const float* __restrict__ partA, int splits,
+                                               int NT, int K, int R, const LoraGroupTable t) {
+  size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t nB = (size_t)R * NT, nA = (size_t)R * K;
+  for (int j = 0; j < t.n; ++j) {
+    const LoraGroupMember& mb = t.m[j];
+    const size_t cb = (size_t)mb.r * mb.rows, ca = (size_t)mb.r * K;
+    if (e < cb) {
+      const int i = (int)(e / mb.rows), n = (int)(e % mb.rows);
+      const size_t src = (size_t)(mb.rank_off + i) * NT + mb.row_off + n;
+      float s = 0.f;
+      for (int k = 0; k < splits; ++k) s += partB[(size_t)k * nB + src];
+      mb.gb[(size_t)n * mb.r + i] += s;
+      return;
+    }
+    e -= cb;
+    if (e < ca) {
+      const size_t src = (size_t)mb.rank_off * K + e;
+      float s = 0.f;
+      for (int k = 0; k < splits; ++k) s += partA[(size_t)k * nA + src];
+      mb.ga[e] += s;
+      return;
+    }
+    e -= ca;
+  }
+}
+
 }  // namespace
 
+template <int R16, int MW>
+static void skinny_launch(const __half* X, const __half* Wt, int M, int K, int r, __half* out, cudaStream_t st) {
+  constexpr int SMEM = 4 * (16 * MW * 128 + 16 * R16 * 128);
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(skinny_nt_kernel<R16, MW>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    attr = true;
+  }
+  skinny_nt_kernel<R16, MW><<<(M + 16 * MW - 1) / (16 * MW), 32 * MW, SMEM, st>>>(X, Wt, M, K, r, out);
+}
 int launch_skinny_nt(const __half* X, const __half* Wt, int M, int K, int r, __half* out, cudaStream_t st) {
   if (M <= 0) return 0;
   if (r <= 0 || r > 64 || (r & 1) || K % 8 != 0) return 1;
-  const int grid = (M + 31) / 32;
-  if (r <= 16) skinny_nt_kernel<1><<<grid, 64, 0, st>>>(X, Wt, M, K, r, out);
-  else if (r <= 32) skinny_nt_kernel<2><<<grid, 64, 0, st>>>(X, Wt, M, K, r, out);
-  else skinny_nt_kernel<4><<<grid, 64, 0, st>>>(X, Wt, M, K, r, out);
+  // 64 rows per CTA once that still gives every SM a CTA; 32 rows below
+  const bool wide = M >= 64 * 120;
+#define RT_SKINNY(R) do { if (wide) skinny_launch<R, 4>(X, Wt, M, K, r, out, st); else skinny_launch<R, 2>(X, Wt, M, K, r, out, st); } while (0)
+  if (r <= 16) RT_SKINNY(1);
+  else if (r <= 32) RT_SKINNY(2);
+  else RT_SKINNY(4);
+#undef RT_SKINNY
   RT_COUNT_LAUNCH(1);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
@@ -433,6 +481,48 @@ int launch_lora_grads(const __half* hs, const __half* dy16, int ld_dy, const __h
   else lora_grads_kernel<4><<<grid, 128, TOK_SMEM, st>>>(g);
   const size_t n = (size_t)r * ((size_t)N + (size_t)K);
   lora_grads_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g.partB, g.partA, splits, N, K, r, gb, ga);
+  RT_COUNT_LAUNCH(2);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+// dA and dB of every member of a stacked group in one product launch and one reduce launch.
+// gb/ga/row_off/rows/rank_off/rank: per member (n <= 3).  Workspace: lora_grads_workspace_floats(M, NT, K, R).
+int launch_lora_grads_group(const __half* hs, const __half* dy16, const __half* gs, const __half* x16, const float* dscale,
+                            int M, int NT, int K, int R, int n, float* const* gb, float* const* ga, const int* row_off,
+                            const int* rows, const int* rank_off, const int* rank, float* workspace, cudaStream_t st) {
+  if (M <= 0 || n <= 0) return 0;
+  if (n > 3 || R <= 0 || R > 64 || NT % 8 != 0 || K % 8 != 0) return 1;
+  int tps, splits;
+  tok_plan(M, &tps, &splits);
+  LoraGradArgs g;
+  g.Pb = hs; g.Qb = dy16; g.Pa = gs; g.Qa = x16;
+  g.pscale = dscale;
+  g.M = M; g.N = NT; g.K = K; g.r = R;
+  g.nbB = (NT + 127) / 128;
+  g.ldb = NT;
+  g.tokens_per_split = tps;
+  g.partB = workspace;
+  g.partA = workspace + (size_t)splits * R * NT;
+  dim3 grid(g.nbB + (K + 127) / 128, splits);
+  constexpr int TOK_SMEM = 3 * (8192 + 16384);
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(lora_grads_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TOK_SMEM);
+    cudaFuncSetAttribute(lora_grads_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TOK_SMEM);
+    cudaFuncSetAttribute(lora_grads_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, TOK_SMEM);
+    attr = true;
+  }
+  if (R <= 16) lora_grads_kernel<1><<<grid, 128, TOK_SMEM, st>>>(g);
+  else if (R <= 32) lora_grads_kernel<2><<<grid, 128, TOK_SMEM, st>>>(g);
+  else lora_grads_kernel<4><<<grid, 128, TOK_SMEM, st>>>(g);
+  LoraGroupTable t;
+  t.n = n;
+  size_t total = 0;
+  for (int j = 0; j < n; ++j) {
+    t.m[j] = LoraGroupMember{gb[j], ga[j], row_off[j], rows[j], rank_off[j], rank[j]};
+    total += (size_t)rank[j] * ((size_t)rows[j] + (size_t)K);
+  }
+  lora_grads_group_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(g.partB, g.partA, splits, NT, K, R, t);
   RT_COUNT_LAUNCH(2);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }

@@ -303,17 +303,20 @@ rt_status group_backward_dev(LinGroup& g, LinearScratch& sc, const __half* x16, 
     if (!hs || !gs) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
     if (!hs_saved && launch_skinny_nt(x16, g.a_s, M, K, R, hs, c->stream)) return c->fail(RT_ERR_CUDA, "lora H kernel launch failed");
     if (launch_skinny_nt(dy16, g.bt_s, M, NT, R, gs, c->stream)) return c->fail(RT_ERR_CUDA, "lora G kernel launch failed");
-    size_t wsf = 0;
-    for (int i = 0; i < g.n; ++i)
-      if (g.lin[i]->has_lora) wsf = std::max(wsf, lora_grads_workspace_floats(M, g.lin[i]->out_dim(), K, g.lin[i]->lora.rank));
-    if (!sc.grad_ws.reserve(wsf * sizeof(float))) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+    if (!sc.grad_ws.reserve(lora_grads_workspace_floats(M, NT, K, R) * sizeof(float)))
+      return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
+    float *gbp[3], *gap[3];
+    int roff[3], rws[3], koff[3], rk[3], nm = 0;
     for (int i = 0; i < g.n; ++i) {
       rt_linear* l = g.lin[i];
       if (!l->has_lora) continue;
-      if (launch_lora_grads(hs + g.rank_off[i], dy16 + g.row_off[i], NT, gs + g.rank_off[i], x16, dscale, M, l->out_dim(), K,
-                            l->lora.rank, l->lora.gb, l->lora.ga, sc.grad_ws.as<float>(), c->stream))
-        return c->fail(RT_ERR_CUDA, "lora gradient kernel launch failed");
+      gbp[nm] = l->lora.gb; gap[nm] = l->lora.ga;
+      roff[nm] = g.row_off[i]; rws[nm] = l->out_dim(); koff[nm] = g.rank_off[i]; rk[nm] = l->lora.rank;
+      ++nm;
     }
+    if (launch_lora_grads_group(hs, dy16, gs, x16, dscale, M, NT, K, R, nm, gbp, gap, roff, rws, koff, rk,
+                                sc.grad_ws.as<float>(), c->stream))
+      return c->fail(RT_ERR_CUDA, "lora gradient kernel launch failed");
     a.lora.act = gs;
     a.lora.w = g.a_h;
     a.lora.rank = R;
