@@ -40,6 +40,11 @@ WORKLOADS = {
     # BASELINE.json configs[0] (the reference's own CPU-runnable case)
     "qwen3-0.6b-q4_0-4x256": dict(preset="qwen3-0.6b", quant="Q4_0", n_seq=4, seq_len=256, answer_frac=0.50, rank=16,
                                   alpha=32.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=0, lr_total=1, min_ratio=0.1),
+    # two layers of configs[1] (the same per-layer shapes and token count, about 1 GB on the device):
+    # the case the per-kernel profiler captures run on
+    "qwen3-0.6b-q8_0-16x512-2layers": dict(preset="qwen3-0.6b", quant="Q8_0", n_seq=16, seq_len=512, answer_frac=0.30, rank=16,
+                                           alpha=32.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=2, lr_total=20, min_ratio=0.1,
+                                           n_layers=2),
     # small shape for quick checks of this script
     "tiny": dict(preset="tiny-qwen3", quant="Q8_0", n_seq=4, seq_len=64, answer_frac=0.5, rank=8, alpha=16.0, lr=1e-4,
                  wd=0.01, clip=1.0, lr_warmup=2, lr_total=20, min_ratio=0.1),
@@ -205,7 +210,8 @@ def run_ours(args):
     wl = WORKLOADS[args.workload]
     L = lib()
 
-    spec = synth.preset(wl["preset"], quant=wl["quant"], seed=0)
+    over = {"n_layers": wl["n_layers"]} if "n_layers" in wl else {}
+    spec = synth.preset(wl["preset"], quant=wl["quant"], seed=0, **over)
     tensors = synth.build_tensors(spec)
     ctx = rt.Context(local_rank)
     stream = torch.cuda.Stream()
