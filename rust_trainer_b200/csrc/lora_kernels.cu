@@ -57,7 +57,7 @@ __device__ __forceinline__ void load64x64(uint32_t sbase, const __half* g, int r
 template <int R16, int MW>
 __global__ void __launch_bounds__(32 * MW)
 skinny_nt_kernel(const __half* __restrict__ X, const __half* __restrict__ Wt, int M, int K, int r, __half* __restrict__ out) {
-  constexpr int NST = 4;                       // stages in flight: the kernel is pure memory latency
+  constexpr int NST = MW >= 4 ? 8 : 4;         // stages in flight: the kernel is pure memory latency
   constexpr int ROWS = 16 * MW, NT = 32 * MW;
   constexpr int XB = ROWS * 128, WB = 16 * R16 * 128, SB = XB + WB;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -383,7 +383,7 @@ __global__ void lora_grads_group_reduce_kernel(const float* __restrict__ partB, 
 
 template <int R16, int MW>
 static void skinny_launch(const __half* X, const __half* Wt, int M, int K, int r, __half* out, cudaStream_t st) {
-  constexpr int SMEM = 4 * (16 * MW * 128 + 16 * R16 * 128);
+  constexpr int SMEM = (MW >= 4 ? 8 : 4) * (16 * MW * 128 + 16 * R16 * 128);
   static bool attr = false;
   if (!attr) {
     cudaFuncSetAttribute(skinny_nt_kernel<R16, MW>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);

@@ -146,8 +146,103 @@ __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __r
   const float ir = 1.0f / sqrtf(ss / (float)d + eps);
   for (int i = threadIdx.x; i < d; i += blockDim.x) y16[r * d + i] = __float2half_rn(xr[i] * ir * w[i]);
 }
+// Warp-per-row versions for rows of up to 1024 floats (a multiple of 128): the row lives in
+// registers, the reductions are warp shuffles, and eight rows per CTA keep far more bytes in
+// flight per SM than one small CTA per row.
+template <int NV>  // float4s per lane: d = 128 * NV
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, int rows, float eps,
+                        __half* __restrict__ y16) {
+  constexpr int D = 128 * NV;
+  const int lane = threadIdx.x & 31;
+  const size_t r = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= (size_t)rows) return;
+  const float4* x4 = (const float4*)(x + r * D);
+  float4 v[NV];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    v[k] = x4[lane + 32 * k];
+    ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+  }
+  ss = warp_sum(ss);
+  const float ir = 1.0f / sqrtf(ss / (float)D + eps);
+  const float4* w4 = (const float4*)w;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const float4 g = w4[lane + 32 * k];
+    __half2 a = __floats2half2_rn(v[k].x * ir * g.x, v[k].y * ir * g.y), b = __floats2half2_rn(v[k].z * ir * g.z, v[k].w * ir * g.w);
+    *(uint2*)(y16 + r * D + 4 * (lane + 32 * k)) = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+  }
+}
+template <int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ dn,
+                        const float* dres, int rows, float eps, float* out, __half* __restrict__ out16,
+                        float* __restrict__ scale) {
+  constexpr int D = 128 * NV;
+  const int lane = threadIdx.x & 31;
+  const size_t r = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= (size_t)rows) return;
+  const float4 *x4 = (const float4*)(x + r * D), *d4 = (const float4*)(dn + r * D), *w4 = (const float4*)w;
+  float4 xv[NV], gv[NV];
+  float ss = 0.f, gx = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    xv[k] = x4[lane + 32 * k];
+    const float4 dv = d4[lane + 32 * k], wv = w4[lane + 32 * k];
+    gv[k] = make_float4(dv.x * wv.x, dv.y * wv.y, dv.z * wv.z, dv.w * wv.w);
+    ss += xv[k].x * xv[k].x + xv[k].y * xv[k].y + xv[k].z * xv[k].z + xv[k].w * xv[k].w;
+    gx += gv[k].x * xv[k].x + gv[k].y * xv[k].y + gv[k].z * xv[k].z + gv[k].w * xv[k].w;
+  }
+  ss = warp_sum(ss);
+  gx = warp_sum(gx);
+  const float ir = 1.0f / sqrtf(ss / (float)D + eps);
+  const float c = gx * ir * ir * ir / (float)D;
+  float m = 0.f;
+  float4* o4 = (float4*)(out + r * D);
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    float4 v = make_float4(gv[k].x * ir - xv[k].x * c, gv[k].y * ir - xv[k].y * c, gv[k].z * ir - xv[k].z * c,
+                           gv[k].w * ir - xv[k].w * c);
+    if (dres) {
+      const float4 q = ((const float4*)(dres + r * D))[lane + 32 * k];
+      v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+    }
+    o4[lane + 32 * k] = v;
+    gv[k] = v;
+    m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+  }
+  if (out16) {
+    m = warp_max(m);
+    const float sc = m > 0.f ? m : 1.f, inv = 1.f / sc;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      __half2 a = __floats2half2_rn(gv[k].x * inv, gv[k].y * inv), b = __floats2half2_rn(gv[k].z * inv, gv[k].w * inv);
+      *(uint2*)(out16 + r * D + 4 * (lane + 32 * k)) = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+    }
+    if (lane == 0) scale[r] = sc;
+  }
+}
 void launch_rmsnorm_fwd(const float* x, const float* w, int rows, int d, float eps, __half* y16, cudaStream_t st) {
-  if (rows > 0) { rmsnorm_fwd_kernel<<<rows, 256, 0, st>>>(x, w, d, eps, y16); RT_COUNT_LAUNCH(1); }
+  if (rows <= 0) return;
+  const int nv = d / 128, grid = (rows + 7) / 8;
+  const bool warp_ok = d % 128 == 0 && nv >= 1 && nv <= 8 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
+  if (warp_ok) {
+    switch (nv) {
+      case 1: rmsnorm_fwd_warp_kernel<1><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
+      case 2: rmsnorm_fwd_warp_kernel<2><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
+      case 3: rmsnorm_fwd_warp_kernel<3><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
+      case 4: rmsnorm_fwd_warp_kernel<4><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
+      case 5: rmsnorm_fwd_warp_kernel<5><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
+      case 6: rmsnorm_fwd_warp_kernel<6><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
+      case 7: rmsnorm_fwd_warp_kernel<7><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
+      default: rmsnorm_fwd_warp_kernel<8><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
+    }
+  } else {
+    rmsnorm_fwd_kernel<<<rows, 256, 0, st>>>(x, w, d, eps, y16);
+  }
+  RT_COUNT_LAUNCH(1);
 }
 
 // dx = g*ir - x*c, g = dn*w, c = dot(g,x)*ir^3/d;  out = (dres ? dres : 0) + dx.
@@ -216,7 +311,27 @@ __global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __r
 }
 void launch_rmsnorm_bwd(const float* x, const float* w, const float* dn, const float* dres, int rows, int d, float eps,
                         float* out, __half* out16, float* scale, cudaStream_t st) {
-  if (rows > 0) { rmsnorm_bwd_kernel<<<rows, 256, 0, st>>>(x, w, dn, dres, d, eps, out, out16, scale); RT_COUNT_LAUNCH(1); }
+  if (rows <= 0) return;
+  const int nv = d / 128, grid = (rows + 7) / 8;
+  const bool warp_ok = d % 128 == 0 && nv >= 1 && nv <= 8 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
+                       ((uintptr_t)dn & 15) == 0 && ((uintptr_t)out & 15) == 0 && (!dres || ((uintptr_t)dres & 15) == 0);
+  if (warp_ok) {
+#define RT_RMSB(N) rmsnorm_bwd_warp_kernel<N><<<grid, 256, 0, st>>>(x, w, dn, dres, rows, eps, out, out16, scale)
+    switch (nv) {
+      case 1: RT_RMSB(1); break;
+      case 2: RT_RMSB(2); break;
+      case 3: RT_RMSB(3); break;
+      case 4: RT_RMSB(4); break;
+      case 5: RT_RMSB(5); break;
+      case 6: RT_RMSB(6); break;
+      case 7: RT_RMSB(7); break;
+      default: RT_RMSB(8); break;
+    }
+#undef RT_RMSB
+  } else {
+    rmsnorm_bwd_kernel<<<rows, 256, 0, st>>>(x, w, dn, dres, d, eps, out, out16, scale);
+  }
+  RT_COUNT_LAUNCH(1);
 }
 
 // ------------------------------------------------------------------ RoPE tables (reference src/ops.rs:118-154)
