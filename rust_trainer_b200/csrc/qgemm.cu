@@ -27,16 +27,23 @@ namespace rt {
 constexpr int W_STAGE = 16384;        // 128 x 64 x 16-bit
 constexpr int RAW_STAGE = 2 * 4352;   // largest brick pair (Q8_0)
 constexpr int QG_THREADS = 480;       // producer, MMA, 8 unpack, 4 epilogue warps, packed-brick producer
-constexpr int UG = 2;                 // unpack groups (a power of two) ...
-constexpr int UTG = 256 / UG;         // ... of this many threads each
 constexpr int OUT_STAGE = 32 * 128 * 4;  // 32 tokens x 128 output features x f32: the epilogue's TMA-store staging
 
 // Shared-memory plan of one CTA.  A CTA of a pair stages half of the token tile, so its stages
-// are a third smaller and five of them fit.
+// are a third smaller, so four of them leave room for the deeper unpack pipeline.
 template <bool PAIR>
 struct QCfg {
-  static constexpr int NS = PAIR ? 5 : 3;                  // activation / unpacked-weight stages
-  static constexpr int NR = PAIR ? 3 : 4;                  // packed brick-pair stages
+  static constexpr int NS = PAIR ? 4 : 3;                  // activation / unpacked-weight stages
+  static constexpr int NR = 4;                             // packed brick-pair stages
+  // The eight unpack warps work as UG groups on alternate contraction steps.  Waits are by phase
+  // parity, which is only sound while a waiter cannot run two phases ahead of its barrier:
+  // UG <= NS keeps a group from reaching a stage before the use two back has been released, and
+  // NR a multiple of UG gives every slot of the brick ring to one group (bulk copies of different
+  // slots may land out of order, so a group sharing a slot could otherwise see the landing of an
+  // older copy as its own).
+  static constexpr int UG = PAIR ? 4 : 2;                  // a power of two
+  static constexpr int UTG = 256 / UG;                     // threads per group
+  static_assert(UG <= NS && NR % UG == 0, "unpack groups would alias barrier phases");
   static constexpr int ACT_STAGE = PAIR ? 16384 : 32768;   // 128 or 256 tokens x 64 x 16-bit
   static constexpr int OFF_W = NS * ACT_STAGE;
   static constexpr int OFF_RAW = OFF_W + NS * W_STAGE;
@@ -202,8 +209,8 @@ __device__ __forceinline__ void unpack_brick(int fmt, const uint8_t* raw, int t,
 //   holds its own 128 weight rows (unpacked by its own warps) and HALF of the token tile; the
 //   leader CTA (cluster rank 0) issues tcgen05.mma.cta_group::2, which reads both CTAs' shared
 //   memory and writes 128 accumulator rows into each CTA's TMEM.  Per CTA and per MMA cycle this
-//   halves the activation bytes that TMA writes and the tensor core reads, so five stages fit
-//   where the single-CTA kernel has three.  Barriers that gate the MMA (full, w_ready, acc_empty)
+//   halves the activation bytes that TMA writes and the tensor core reads, and its smaller stages
+//   leave room for four of them and four unpack groups.  Barriers that gate the MMA (full, w_ready, acc_empty)
 //   live in the leader and are arrived on from both CTAs; barriers the MMA releases
 //   (stage_empty, acc_full) exist in both CTAs and are signalled by one multicast commit.
 // Build with -DRT_B200_QPROF to count, per CTA and role, the cycles spent in each wait (measurement aid).
@@ -214,13 +221,13 @@ __device__ __forceinline__ void unpack_brick(int fmt, const uint8_t* raw, int t,
     expr;                                     \
     prof_acc[slot] += clock64() - t_;         \
   } while (0)
-#define QG_PROF_BEGIN() long long prof_acc[4] = {0, 0, 0, 0}; const long long prof_t0 = clock64(); const uint64_t prof_ns0 = globaltimer_ns()
+#define QG_PROF_BEGIN() long long prof_acc[6] = {0, 0, 0, 0, 0, 0}; const long long prof_t0 = clock64(); const uint64_t prof_ns0 = globaltimer_ns()
 #define QG_PROF_END(role)                                                                  \
   do {                                                                                     \
     if (p.prof) {                                                                          \
       prof_acc[3] = clock64() - prof_t0;                                                   \
       if ((role) == 3) prof_acc[2] = (long long)(globaltimer_ns() - prof_ns0);             \
-      for (int q_ = 0; q_ < 4; ++q_) p.prof[((size_t)blockIdx.x * 4 + (role)) * 4 + q_] = prof_acc[q_]; \
+      for (int q_ = 0; q_ < 6; ++q_) p.prof[((size_t)blockIdx.x * 4 + (role)) * 6 + q_] = prof_acc[q_]; \
     }                                                                                      \
   } while (0)
 #else
@@ -236,6 +243,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
   using C = QCfg<PAIR>;
   constexpr int NS = C::NS;
   constexpr int NR = C::NR;
+  constexpr int UG = C::UG;
+  constexpr int UTG = C::UTG;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sAct = smem;
@@ -385,16 +394,20 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           const uint32_t b_lo = (uint32_t)b_d0 + (uint32_t)st * (C::ACT_STAGE >> 4);
           if (p.dbg & 32) {
           } else if (s < s_main) {
+            QG_TIMED(4, {
             umma_f16_split<PAIR>(d_tmem, a_lo, a_hi, b_lo, b_hi, p.idesc_main, (uint32_t)(s != 0));
             umma_f16_split<PAIR>(d_tmem, a_lo + a_k, a_hi, b_lo + b_k, b_hi, p.idesc_main, 1u);
             umma_f16_split<PAIR>(d_tmem, a_lo + 2 * a_k, a_hi, b_lo + 2 * b_k, b_hi, p.idesc_main, 1u);
             umma_f16_split<PAIR>(d_tmem, a_lo + 3 * a_k, a_hi, b_lo + 3 * b_k, b_hi, p.idesc_main, 1u);
+            });
           } else {
             for (int kk = 0; kk < p.lora_mmas; ++kk)
               umma_f16_split<PAIR>(d_tmem, a_lo + kk * a_k, a_hi, b_lo + kk * b_k, b_hi, p.idesc_lora, (uint32_t)((s | kk) != 0));
           }
+          QG_TIMED(5, {
           if (PAIR) umma_commit_pair(&stage_empty[st], 3);
           else umma_commit(&stage_empty[st]);
+          });
           if (++st == NS) { st = 0; ph ^= 1; }
         }
         if (ok) {
@@ -826,8 +839,8 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   p.prof = nullptr;
 #ifdef RT_B200_QPROF
   static long long* prof_dev = nullptr;
-  if (!prof_dev) cudaMalloc(&prof_dev, 512 * 16 * sizeof(long long));
-  cudaMemsetAsync(prof_dev, 0, 512 * 16 * sizeof(long long), st);
+  if (!prof_dev) cudaMalloc(&prof_dev, 512 * 24 * sizeof(long long));
+  cudaMemsetAsync(prof_dev, 0, 512 * 24 * sizeof(long long), st);
   p.prof = prof_dev;
 #endif
   {
@@ -956,14 +969,14 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   RT_COUNT_LAUNCH(1);
 #ifdef RT_B200_QPROF
   {
-    static long long host[512 * 16];
+    static long long host[512 * 24];
     cudaMemcpyAsync(host, prof_dev, sizeof(host), cudaMemcpyDeviceToHost, st);
     cudaStreamSynchronize(st);
-    double sum[16] = {0};
+    double sum[24] = {0};
     for (int c = 0; c < grid; ++c)
-      for (int q = 0; q < 16; ++q) sum[q] += (double)host[c * 16 + q] / ((q >= 4 && q < 8 && pair) ? grid / 2 : grid);
-    fprintf(stderr, "qprof pair=%d dir=%d TN=%d grid=%d | prod: stage_empty %.0f raw_empty %.0f total %.0f | mma: acc_empty %.0f full %.0f w_ready %.0f total %.0f | unpack: stage_empty %.0f raw_full %.0f work %.0f total %.0f | epi: acc_full %.0f total %.0f = %.0f ns -> %.0f MHz\n",
-            (int)pair, a.dir, p.TN, grid, sum[0], sum[1], sum[3], sum[4], sum[5], sum[6], sum[7], sum[8], sum[9], sum[10], sum[11], sum[12], sum[15], sum[14], sum[15] / sum[14] * 1e3);
+      for (int q = 0; q < 24; ++q) sum[q] += (double)host[c * 24 + q] / ((q >= 6 && q < 12 && pair) ? grid / 2 : grid);
+    fprintf(stderr, "qprof pair=%d dir=%d TN=%d grid=%d | prod: stage_empty %.0f total %.0f | mma: acc_empty %.0f full %.0f w_ready %.0f issue4 %.0f commit %.0f total %.0f | unpack: stage_empty %.0f raw_full %.0f work %.0f total %.0f | epi: acc_full %.0f total %.0f = %.0f ns -> %.0f MHz\n",
+            (int)pair, a.dir, p.TN, grid, sum[0], sum[3], sum[6], sum[7], sum[8], sum[10], sum[11], sum[9], sum[12], sum[13], sum[14], sum[15], sum[18], sum[21], sum[20], sum[21] / sum[20] * 1e3);
   }
 #endif
   if (p.part) {
