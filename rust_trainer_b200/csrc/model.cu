@@ -41,16 +41,24 @@ rt_status lora_refresh(rt_linear* l) {
   return RT_OK;
 }
 
-// Hs / Gs are [M x 64] f16 with zeros beyond column `rank`: only the first `rank` columns are
-// ever written, so the buffer is cleared when it grows or when the rank changes.
+// Hs / Gs are [M x 64] f16.  The low-rank chunk of the big matmul reads whole groups of 16
+// columns, so columns from `rank` up to the next multiple of 16 must hold zeros (or at least
+// finite values against zero weights; zeros keep it exact).  `cur_rank` remembers the widest
+// rank written since the last clear: the buffer is cleared only when stale columns would fall
+// inside the group the new rank reads.
 static __half* lowrank_buf(rt_ctx* c, DevBuf& b, int& cur_rank, int M, int rank) {
   const size_t want = (size_t)M * 64 * sizeof(__half);
+  bool clear = false;
   if (want > b.bytes) {
     if (!b.reserve(want + want / 2)) return nullptr;
-    cur_rank = -1;
+    clear = true;
   }
-  if (cur_rank != rank) {
+  const int read_to = (rank + 15) / 16 * 16;
+  if (cur_rank < 0 || (cur_rank > rank && rank < read_to)) clear = true;
+  if (clear) {
     cudaMemsetAsync(b.p, 0, b.bytes, c->stream);
+    cur_rank = rank;
+  } else if (rank > cur_rank) {
     cur_rank = rank;
   }
   return b.as<__half>();

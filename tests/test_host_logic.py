@@ -58,3 +58,16 @@ def test_shard_sequences_round_robin():
     assert sorted(sum((dp.shard_sequences(7, r, 3) for r in range(3)), [])) == list(range(7))
     with pytest.raises(ValueError):
         dp.shard_sequences(4, 4, 4)
+
+
+def test_objective_helpers():
+    """softplus with torch's threshold (src/tensor.rs:146-153), sigmoid, and the batch layout of
+    answer targets (global positions, per-example spans)."""
+    from rust_trainer_b200 import objectives as obj
+
+    assert abs(obj.softplus(0.0) - np.log(2.0)) < 1e-6 and obj.softplus(25.0) == 25.0 and obj.softplus(-30.0) < 1e-12
+    assert obj.sigmoid(0.0) == 0.5 and abs(obj.sigmoid(2.0) + obj.sigmoid(-2.0) - 1.0) < 1e-6
+    seqs, tp, tt, spans = obj._layout([(np.arange(10), 6), (np.arange(8), 0)])
+    assert [s.size for s in seqs] == [10, 8] and spans == [(0, 4), (4, 11)]
+    assert tp.tolist() == [5, 6, 7, 8] + [10 + i for i in range(7)]  # i >= max(answer_start, 1) predicts from i - 1
+    assert tt.tolist() == [6, 7, 8, 9] + list(range(1, 8))
