@@ -222,6 +222,20 @@ rt_status rt_model_forward_backward(rt_model* m, const int32_t* tokens, const in
 rt_status rt_model_score(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
                          const int32_t* target_pos, const int32_t* target_tok, int32_t n_targets, float* logp_out,
                          int32_t* hits_out, float* logits_out);
+/* Model::forward_backward_packed / the packed scoring of src/eval.rs:176-186: every sequence of
+ * the batch is a Packed group (src/model.rs:234-290): a shared prompt (segments[i] = 0) followed
+ * by the examples' own tokens (segments[i] = k + 1 for example k, in runs), positions[i] = the
+ * token's position within its own example (RoPE).  A token attends to the prompt and to its own
+ * example's earlier tokens only (Rope::allowed, src/ops.rs:156-164).  The result equals running
+ * the examples separately, with the prompt computed once.  Target positions index the packed
+ * token array (Packed::index). */
+rt_status rt_model_forward_backward_layout(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
+                                           const int32_t* positions, const int32_t* segments,
+                                           const int32_t* target_pos, const int32_t* target_tok, const float* weights,
+                                           int32_t n_targets, float* logp_out, int32_t* hits_out);
+rt_status rt_model_score_layout(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
+                                const int32_t* positions, const int32_t* segments, const int32_t* target_pos,
+                                const int32_t* target_tok, int32_t n_targets, float* logp_out, int32_t* hits_out);
 /* The same step split for hosts that keep the batch on the device: stage copies tokens,
  * targets and weights to HBM once; run_staged does the forward + backward (backward != 0) or
  * the forward alone on the staged batch without touching host memory; read_results copies the

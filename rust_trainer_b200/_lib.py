@@ -98,6 +98,8 @@ def _declare(L: C.CDLL) -> None:
         "rt_model_zero_grad": (i32, [vp]),
         "rt_model_forward_backward": (i32, [vp, i32p, i32p, i32, i32p, i32p, f32p, i32, f32p, i32p]),
         "rt_model_score": (i32, [vp, i32p, i32p, i32, i32p, i32p, i32, f32p, i32p, f32p]),
+        "rt_model_forward_backward_layout": (i32, [vp, i32p, i32p, i32, i32p, i32p, i32p, i32p, f32p, i32, f32p, i32p]),
+        "rt_model_score_layout": (i32, [vp, i32p, i32p, i32, i32p, i32p, i32p, i32p, i32, f32p, i32p]),
         "rt_model_stage_batch": (i32, [vp, i32p, i32p, i32, i32p, i32p, f32p, i32]),
         "rt_model_run_staged": (i32, [vp, C.c_int]),
         "rt_model_read_results": (i32, [vp, f32p, i32, i32p]),

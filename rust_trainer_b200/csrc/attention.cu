@@ -8,7 +8,8 @@
 //            query heads that share a KV head
 //
 // A batch is a concatenation of independent sequences; row i attends to keys j with
-// seq_start[i] <= j <= i, which is the reference's `allowed` rule (src/ops.rs:156-164) for
+// seq_start[i] <= j <= i and, when a gap array is given, j outside [gap[i].x, gap[i].y) (the other
+// examples' own tokens of a shared-prompt group), which is the reference's `allowed` rule (src/ops.rs:156-164) for
 // unpacked sequences.  K and V arrive already rounded to f16, as the reference's f16 KV view
 // has them (src/attention.rs:180-185); Q, P and dS are rounded to f16 for the tensor cores,
 // all sums are f32.  The backward is two kernels (dK/dV per key tile, dQ per query tile) so
@@ -101,8 +102,8 @@ constexpr float LOG2E = 1.4426950408889634f;
 template <int HD>
 __global__ void __launch_bounds__(128)
 attn_fwd_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const __half* __restrict__ v,
-                const int* __restrict__ seq_start, int M, int nh, int nkv, float scale, __half* __restrict__ o,
-                float* __restrict__ lse) {
+                const int* __restrict__ seq_start, const int2* __restrict__ gap, int M, int nh, int nkv, float scale,
+                __half* __restrict__ o, float* __restrict__ lse) {
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sQ = smem_addr(smem), sKV = sQ + BT * HD * 2;  // then two (K, V) buffers
   const int m0 = blockIdx.x * BT, h = blockIdx.y, g = h / (nh / nkv);
@@ -119,6 +120,8 @@ attn_fwd_kernel(const __half* __restrict__ q, const __half* __restrict__ k, cons
 
   const int i0 = m0 + warp * 16 + gq, i1 = i0 + 8;
   const int ss0 = i0 < M ? seq_start[i0] : 0x7fffffff, ss1 = i1 < M ? seq_start[i1] : 0x7fffffff;
+  // keys in [gap.x, gap.y) are hidden from the row (other examples' tokens of a packed group)
+  const int2 gp0 = (gap && i0 < M) ? gap[i0] : make_int2(0, 0), gp1 = (gap && i1 < M) ? gap[i1] : make_int2(0, 0);
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float oacc[HD / 8][4];
 #pragma unroll
@@ -161,7 +164,8 @@ attn_fwd_kernel(const __half* __restrict__ q, const __half* __restrict__ k, cons
       for (int e = 0; e < 4; ++e) {
         const int j = n0 + nt * 8 + 2 * tq + (e & 1);
         const int i = (e < 2) ? i0 : i1, ss = (e < 2) ? ss0 : ss1;
-        const bool ok = j <= i && j >= ss;
+        const int2 gp = (e < 2) ? gp0 : gp1;
+        const bool ok = j <= i && j >= ss && (j < gp.x || j >= gp.y);
         const float val = ok ? s[nt][e] * sl2 : -INFINITY;
         s[nt][e] = val;
         mx[e >> 1] = fmaxf(mx[e >> 1], val);
@@ -250,11 +254,11 @@ attn_bwd_dkdv_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
                      const __half* __restrict__ dO, const float* __restrict__ do_scale,
                      const float* __restrict__ row_scale,
                      const float* __restrict__ lse, const float* __restrict__ delta,
-                     const int* __restrict__ seq_start, int M, int nh, int nkv, float scale, float* __restrict__ dk,
-                     float* __restrict__ dv) {
+                     const int* __restrict__ seq_start, const int2* __restrict__ gap, int M, int nh, int nkv, float scale,
+                     float* __restrict__ dk, float* __restrict__ dv) {
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sK = smem_addr(smem), sV = sK + BT * HD * 2, sQdO = sV + BT * HD * 2;  // then two (Q, dO) buffers
-  float* sAux = (float*)(smem + 6 * BT * HD * 2);  // two buffers of (lse, delta, seq_start, weight) per query row
+  float* sAux = (float*)(smem + 6 * BT * HD * 2);  // two buffers of (lse, delta, seq_start, weight, gap) per query row
   // dO row i stands for row_scale[i] * dO[i] (do_scale[0] = the largest factor): a query row
   // enters the sums over queries with weight row_scale[i] / do_scale[0] <= 1
   const float inv_top = row_scale ? 1.0f / fmaxf(do_scale[0], 1e-38f) : 1.0f;
@@ -293,11 +297,14 @@ attn_bwd_dkdv_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
     load_tile<HD>(sQdO + buf * 2 * BT * HD * 2 + BT * HD * 2, dO, m0, M, nh, h);
     if (threadIdx.x < BT) {
       const int m = m0 + threadIdx.x;
-      float* aux = sAux + buf * 4 * BT;
+      float* aux = sAux + buf * 6 * BT;
       aux[threadIdx.x] = m < M ? lse[(size_t)h * M + m] * LOG2E : 0.f;
       aux[BT + threadIdx.x] = m < M ? delta[(size_t)h * M + m] : 0.f;
       ((int*)aux)[2 * BT + threadIdx.x] = m < M ? seq_start[m] : 0x7fffffff;
       aux[3 * BT + threadIdx.x] = (row_scale && m < M) ? row_scale[m] * inv_top : 1.0f;
+      const int2 gp = (gap && m < M) ? gap[m] : make_int2(0, 0);
+      ((int*)aux)[4 * BT + threadIdx.x] = gp.x;
+      ((int*)aux)[5 * BT + threadIdx.x] = gp.y;
     }
   };
   if (n_work > 0) prefetch(0, 0);
@@ -307,10 +314,12 @@ attn_bwd_dkdv_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
       const int m0 = n0 + (idx % nqt) * BT;
       const int buf = idx & 1;
       const uint32_t sQ = sQdO + buf * 2 * BT * HD * 2, sdO = sQ + BT * HD * 2;
-      const float* sLse = sAux + buf * 4 * BT;
+      const float* sLse = sAux + buf * 6 * BT;
       const float* sDel = sLse + BT;
       const int* sSS = (const int*)(sLse + 2 * BT);
       const float* sWt = sLse + 3 * BT;
+      const int* sGlo = (const int*)(sLse + 4 * BT);
+      const int* sGhi = (const int*)(sLse + 5 * BT);
       if (idx + 1 < n_work) prefetch(idx + 1, buf ^ 1);
       cp_async_commit();
       cp_async_wait_prev();
@@ -348,7 +357,7 @@ attn_bwd_dkdv_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
             const int il = qb + nt * 8 + 2 * tq + (e & 1);
             const int i = m0 + il;
             const int j = (e < 2) ? j0 : j1;
-            const bool ok = i < M && j <= i && j >= sSS[il];
+            const bool ok = i < M && j <= i && j >= sSS[il] && (j < sGlo[il] || j >= sGhi[il]);
             const float p = ok ? exp2f(st[nt][e] * sl2 - sLse[il]) * sWt[il] : 0.f;
             st[nt][e] = p;
             dp[nt][e] = p * (dp[nt][e] - sDel[il]) * scale;
@@ -396,8 +405,8 @@ __global__ void __launch_bounds__(128)
 attn_bwd_dq_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const __half* __restrict__ v,
                    const __half* __restrict__ dO, const float* __restrict__ do_scale, const float* __restrict__ row_scale,
                    const float* __restrict__ lse,
-                   const float* __restrict__ delta, const int* __restrict__ seq_start, int M, int nh, int nkv,
-                   float scale, float* __restrict__ dq) {
+                   const float* __restrict__ delta, const int* __restrict__ seq_start, const int2* __restrict__ gap, int M,
+                   int nh, int nkv, float scale, float* __restrict__ dq) {
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sQ = smem_addr(smem), sdO = sQ + BT * HD * 2, sKV = sdO + BT * HD * 2;  // then two (K, V) buffers
   const int m0 = blockIdx.x * BT, h = blockIdx.y, g = h / (nh / nkv);
@@ -407,6 +416,7 @@ attn_bwd_dq_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
   load_tile<HD>(sdO, dO, m0, M, nh, h);
   const int i0 = m0 + warp * 16 + gq, i1 = i0 + 8;
   const int ss0 = i0 < M ? seq_start[i0] : 0x7fffffff, ss1 = i1 < M ? seq_start[i1] : 0x7fffffff;
+  const int2 gp0 = (gap && i0 < M) ? gap[i0] : make_int2(0, 0), gp1 = (gap && i1 < M) ? gap[i1] : make_int2(0, 0);
   const float l0 = i0 < M ? lse[(size_t)h * M + i0] * LOG2E : 0.f, l1 = i1 < M ? lse[(size_t)h * M + i1] * LOG2E : 0.f;
   const float d0 = i0 < M ? delta[(size_t)h * M + i0] : 0.f, d1 = i1 < M ? delta[(size_t)h * M + i1] : 0.f;
   float acc[HD / 8][4];
@@ -459,7 +469,8 @@ attn_bwd_dq_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
         for (int e = 0; e < 4; ++e) {
           const int j = n0 + kb + nt * 8 + 2 * tq + (e & 1);
           const int i = (e < 2) ? i0 : i1, ss = (e < 2) ? ss0 : ss1;
-          const bool ok = i < M && j <= i && j >= ss;
+          const int2 gp = (e < 2) ? gp0 : gp1;
+          const bool ok = i < M && j <= i && j >= ss && (j < gp.x || j >= gp.y);
           const float p = ok ? exp2f(s[nt][e] * sl2 - ((e < 2) ? l0 : l1)) : 0.f;
           dp[nt][e] = p * (dp[nt][e] - ((e < 2) ? d0 : d1)) * scale;
         }
@@ -491,7 +502,7 @@ attn_bwd_dq_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
 }
 
 template <int HD>
-int fwd_impl(const __half* q, const __half* k, const __half* v, const int* seq_start, int M, int nh, int nkv,
+int fwd_impl(const __half* q, const __half* k, const __half* v, const int* seq_start, const int2* gap, int M, int nh, int nkv,
              __half* o, float* lse, cudaStream_t st) {
   const size_t smem = 5 * BT * HD * 2;
   static bool attr = false;
@@ -500,15 +511,15 @@ int fwd_impl(const __half* q, const __half* k, const __half* v, const int* seq_s
     attr = true;
   }
   dim3 grid((M + BT - 1) / BT, nh);
-  { attn_fwd_kernel<HD><<<grid, 128, smem, st>>>(q, k, v, seq_start, M, nh, nkv, 1.0f / sqrtf((float)HD), o, lse); RT_COUNT_LAUNCH(1); }
+  { attn_fwd_kernel<HD><<<grid, 128, smem, st>>>(q, k, v, seq_start, gap, M, nh, nkv, 1.0f / sqrtf((float)HD), o, lse); RT_COUNT_LAUNCH(1); }
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
 template <int HD>
 int bwd_impl(const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO,
-             const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, int M, int nh, int nkv,
-             float* delta, float* dq, float* dk, float* dv, cudaStream_t st) {
-  const size_t smem_kv = 6 * BT * HD * 2 + 2 * 4 * BT * 4, smem_q = 6 * BT * HD * 2;
+             const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int2* gap, int M,
+             int nh, int nkv, float* delta, float* dq, float* dk, float* dv, cudaStream_t st) {
+  const size_t smem_kv = 6 * BT * HD * 2 + 2 * 6 * BT * 4, smem_q = 6 * BT * HD * 2;
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(attn_bwd_dkdv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv) != cudaSuccess) return 3;
@@ -519,27 +530,27 @@ int bwd_impl(const __half* q, const __half* k, const __half* v, const __half* o,
   const int warps = M * nh;
   { attn_delta_kernel<HD><<<(warps * 32 + 255) / 256, 256, 0, st>>>(o, dO, M, nh, delta); RT_COUNT_LAUNCH(1); }
   dim3 gkv((M + BT - 1) / BT, nkv), gq((M + BT - 1) / BT, nh);
-  { attn_bwd_dkdv_kernel<HD><<<gkv, 128, smem_kv, st>>>(q, k, v, dO, do_scale, row_scale, lse, delta, seq_start, M, nh, nkv, scale, dk, dv); RT_COUNT_LAUNCH(1); }
-  { attn_bwd_dq_kernel<HD><<<gq, 128, smem_q, st>>>(q, k, v, dO, do_scale, row_scale, lse, delta, seq_start, M, nh, nkv, scale, dq); RT_COUNT_LAUNCH(1); }
+  { attn_bwd_dkdv_kernel<HD><<<gkv, 128, smem_kv, st>>>(q, k, v, dO, do_scale, row_scale, lse, delta, seq_start, gap, M, nh, nkv, scale, dk, dv); RT_COUNT_LAUNCH(1); }
+  { attn_bwd_dq_kernel<HD><<<gq, 128, smem_q, st>>>(q, k, v, dO, do_scale, row_scale, lse, delta, seq_start, gap, M, nh, nkv, scale, dq); RT_COUNT_LAUNCH(1); }
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
 }  // namespace
 
-int launch_attn_fwd(const __half* q, const __half* k, const __half* v, const int* seq_start, int M, int nh, int nkv,
-                    int hd, __half* o, float* lse, cudaStream_t st) {
+int launch_attn_fwd(const __half* q, const __half* k, const __half* v, const int* seq_start, const int* gap, int M, int nh,
+                    int nkv, int hd, __half* o, float* lse, cudaStream_t st) {
   if (M <= 0) return 0;
-  if (hd == 128) return fwd_impl<128>(q, k, v, seq_start, M, nh, nkv, o, lse, st);
-  if (hd == 64) return fwd_impl<64>(q, k, v, seq_start, M, nh, nkv, o, lse, st);
+  if (hd == 128) return fwd_impl<128>(q, k, v, seq_start, (const int2*)gap, M, nh, nkv, o, lse, st);
+  if (hd == 64) return fwd_impl<64>(q, k, v, seq_start, (const int2*)gap, M, nh, nkv, o, lse, st);
   return 1;  // unsupported head size
 }
 
 int launch_attn_bwd(const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
-                    const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, int M, int nh,
-                    int nkv, int hd, float* delta, float* dq, float* dk, float* dv, cudaStream_t st) {
+                    const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap,
+                    int M, int nh, int nkv, int hd, float* delta, float* dq, float* dk, float* dv, cudaStream_t st) {
   if (M <= 0) return 0;
-  if (hd == 128) return bwd_impl<128>(q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, M, nh, nkv, delta, dq, dk, dv, st);
-  if (hd == 64) return bwd_impl<64>(q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, M, nh, nkv, delta, dq, dk, dv, st);
+  if (hd == 128) return bwd_impl<128>(q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, (const int2*)gap, M, nh, nkv, delta, dq, dk, dv, st);
+  if (hd == 64) return bwd_impl<64>(q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, (const int2*)gap, M, nh, nkv, delta, dq, dk, dv, st);
   return 1;
 }
 

@@ -586,6 +586,7 @@ void rt_model_destroy(rt_model* m) {
                     &m->ns16, &m->logits, &m->dl16, &m->sc_l, &m->dns, &m->dxs};
   for (DevBuf* b : bufs) b->release();
   for (int i = 0; i < 7; ++i) m->hs_keep[i].release();
+  m->gap.release();
   for (auto& ge : m->graphs) cudaGraphExecDestroy(ge.exec);
   delete m;
 }
@@ -1040,7 +1041,8 @@ static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, fl
   launch_qk_rope_fwd(A.q_raw, A.k_raw, A.v_raw, A.qkv_pitch, g.qk_norm ? b.q_norm : nullptr,
                      g.qk_norm ? b.k_norm : nullptr, m->pos.as<int>(), m->rope_cos.as<float>(), m->rope_sin.as<float>(), M,
                      g.n_heads, g.n_kv_heads, g.head_dim, g.rot_dim, g.rope_neox, g.rms_eps, A.q16, A.k16, A.v16, st);
-  if (launch_attn_fwd(A.q16, A.k16, A.v16, m->seq_start.as<int>(), M, g.n_heads, g.n_kv_heads, g.head_dim, A.o16, A.lse, st))
+  if (launch_attn_fwd(A.q16, A.k16, A.v16, m->seq_start.as<int>(), m->staged_gap ? m->gap.as<int>() : nullptr, M, g.n_heads,
+                      g.n_kv_heads, g.head_dim, A.o16, A.lse, st))
     return c->fail(RT_ERR_CUDA, "attention forward launch failed");
   if (h != x_in) RT_CUDA(c, cudaMemcpyAsync(h, x_in, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
   RT_TRY(linear_forward_dev(b.lin[3], m->lsc, A.o16, M, h, RT_DT_F32, 1, keep ? A.hs[3] : nullptr));
@@ -1095,7 +1097,8 @@ static rt_status block_backward(rt_model* m, int li, int M, const float* x_in, c
   RT_TRY(linear_backward_dev(b.lin[3], m->lsc, A.o16, dy16, sc_y, M, m->dO16.p, 0, HS(3), true));
   launch_rowscale_max(sc_y, M, m->amax.as<float>(), st);
   if (launch_attn_bwd(A.q16, A.k16, A.v16, A.o16, m->dO16.as<__half>(),
-                      m->amax.as<float>(), sc_y, A.lse, m->seq_start.as<int>(), M, g.n_heads, g.n_kv_heads, g.head_dim,
+                      m->amax.as<float>(), sc_y, A.lse, m->seq_start.as<int>(), m->staged_gap ? m->gap.as<int>() : nullptr, M,
+                      g.n_heads, g.n_kv_heads, g.head_dim,
                       m->delta.as<float>(), m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>(), st))
     return c->fail(RT_ERR_CUDA, "attention backward launch failed");
   const size_t qd = (size_t)g.n_heads * g.head_dim, kvd = (size_t)g.n_kv_heads * g.head_dim;
@@ -1150,9 +1153,12 @@ static rt_status model_head(rt_model* m, int M, int n_targets, bool backward, fl
   return RT_OK;
 }
 
+// positions / segments (both or neither): the reference's Packed layout (src/model.rs:234-290) for
+// every sequence of the batch: a shared prompt (segment 0) followed by the examples' own tokens
+// (segment k+1 for example k), each token keeping its position within its own example.
 static rt_status upload_batch(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int n_seq,
                               const int32_t* tpos, const int32_t* ttok, const float* tw, int n_targets, bool backward,
-                              int* M_out) {
+                              int* M_out, const int32_t* positions = nullptr, const int32_t* segments = nullptr) {
   rt_ctx* c = m->ctx;
   if (!m->finalized) return c->fail(RT_ERR_BAD_ARG, "finalize the model first");
   if (!tokens || !seq_offsets || n_seq <= 0) return c->fail(RT_ERR_BAD_ARG, "empty batch");
@@ -1160,14 +1166,36 @@ static rt_status upload_batch(rt_model* m, const int32_t* tokens, const int32_t*
   if (seq_offsets[0] != 0) return c->fail(RT_ERR_BAD_ARG, "seq_offsets must start at 0");
   const long long M = seq_offsets[n_seq];
   if (M <= 0 || M > (1 << 24)) return c->fail(RT_ERR_BAD_SHAPE, "token count out of range");
+  if ((positions == nullptr) != (segments == nullptr)) return c->fail(RT_ERR_BAD_ARG, "positions and segments go together");
   m->h_pos.resize(M);
   m->h_seq_start.resize(M);
+  if (positions) m->h_gap.assign((size_t)M * 2, 0);
   int max_len = 0;
   for (int s = 0; s < n_seq; ++s) {
     const int a = seq_offsets[s], e = seq_offsets[s + 1];
     if (e <= a) return c->fail(RT_ERR_BAD_SHAPE, "empty or unordered sequence");
     for (int i = a; i < e; ++i) { m->h_pos[i] = i - a; m->h_seq_start[i] = a; }
     if (e - a > max_len) max_len = e - a;
+    if (positions) {
+      // segments: zeros (the shared prompt), then runs of 1, 2, ...; a token of run k may not see the
+      // other runs, i.e. the keys from the end of the prompt up to the start of its own run
+      int shared = 0;
+      while (a + shared < e && segments[a + shared] == 0) ++shared;
+      int run_start = a + shared, prev = 0;
+      for (int i = a; i < e; ++i) {
+        const int sg = segments[i], ps = positions[i];
+        if (ps < 0 || ps >= (1 << 20)) return c->fail(RT_ERR_BAD_INDEX, "position out of range");
+        if (i >= a + shared) {
+          if (sg <= 0 || sg < prev || sg > prev + 1) return c->fail(RT_ERR_BAD_ARG, "segments must be 0.., then 1, 2, ... in runs");
+          if (sg != prev) run_start = i;
+          prev = sg;
+          m->h_gap[2 * (size_t)i] = a + shared;
+          m->h_gap[2 * (size_t)i + 1] = run_start;
+        }
+        m->h_pos[i] = ps;
+        if (ps + 1 > max_len) max_len = ps + 1;
+      }
+    }
   }
   for (long long i = 0; i < M; ++i)
     if (tokens[i] < 0 || tokens[i] >= m->cfg.vocab) return c->fail(RT_ERR_BAD_INDEX, "token id out of vocabulary");  // model.rs:450 asserts
@@ -1183,6 +1211,11 @@ static rt_status upload_batch(rt_model* m, const int32_t* tokens, const int32_t*
   RT_CUDA(c, cudaMemcpyAsync(m->tokens.p, tokens, M * 4, cudaMemcpyHostToDevice, st));
   RT_CUDA(c, cudaMemcpyAsync(m->pos.p, m->h_pos.data(), M * 4, cudaMemcpyHostToDevice, st));
   RT_CUDA(c, cudaMemcpyAsync(m->seq_start.p, m->h_seq_start.data(), M * 4, cudaMemcpyHostToDevice, st));
+  m->staged_gap = positions != nullptr;
+  if (positions) {
+    if (!m->gap.reserve((size_t)M * 8)) return c->fail(RT_ERR_CUDA, "out of device memory (activations)");
+    RT_CUDA(c, cudaMemcpyAsync(m->gap.p, m->h_gap.data(), (size_t)M * 8, cudaMemcpyHostToDevice, st));
+  }
   if (n_targets > 0) {
     RT_CUDA(c, cudaMemcpyAsync(m->tpos.p, tpos, (size_t)n_targets * 4, cudaMemcpyHostToDevice, st));
     RT_CUDA(c, cudaMemcpyAsync(m->ttok.p, ttok, (size_t)n_targets * 4, cudaMemcpyHostToDevice, st));
@@ -1238,6 +1271,7 @@ static uint64_t buffer_signature(rt_model* m) {
   for (int i = 0; i < 4; ++i) mix(m->ctx->scratch[i]);
   mix((const void*)(uintptr_t)m->n_params);
   mix((const void*)(uintptr_t)(m->store_acts ? 1 : 0));
+  mix(m->staged_gap ? m->gap.p : nullptr);
   for (auto& b : m->blocks)
     for (int i = 0; i < 7; ++i) mix((const void*)(uintptr_t)(b.lin[i]->lora_active() ? b.lin[i]->lora.rank : 0));
   return h;
@@ -1356,6 +1390,37 @@ rt_status rt_model_score(rt_model* m, const int32_t* tokens, const int32_t* seq_
   m->staged_targets = n_targets;
   m->staged_has_weights = false;
   RT_TRY(run_staged(m, false, logits_out));
+  return rt_model_read_results(m, logp_out, n_targets, hits_out);
+}
+
+rt_status rt_model_forward_backward_layout(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
+                                           const int32_t* positions, const int32_t* segments, const int32_t* tpos,
+                                           const int32_t* ttok, const float* weights, int32_t n_targets, float* logp_out,
+                                           int32_t* hits_out) {
+  if (!m) return RT_ERR_BAD_ARG;
+  rt_ctx* c = m->ctx;
+  if (n_targets > 0 && !weights) return c->fail(RT_ERR_BAD_ARG, "weights missing");
+  int M = 0;
+  m->staged_tokens = 0;
+  RT_TRY(upload_batch(m, tokens, seq_offsets, n_seq, tpos, ttok, weights, n_targets, true, &M, positions, segments));
+  m->staged_tokens = M;
+  m->staged_targets = n_targets;
+  m->staged_has_weights = true;
+  RT_TRY(run_staged(m, true, nullptr));
+  return rt_model_read_results(m, logp_out, n_targets, hits_out);
+}
+
+rt_status rt_model_score_layout(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
+                                const int32_t* positions, const int32_t* segments, const int32_t* tpos, const int32_t* ttok,
+                                int32_t n_targets, float* logp_out, int32_t* hits_out) {
+  if (!m) return RT_ERR_BAD_ARG;
+  int M = 0;
+  m->staged_tokens = 0;
+  RT_TRY(upload_batch(m, tokens, seq_offsets, n_seq, tpos, ttok, nullptr, n_targets, false, &M, positions, segments));
+  m->staged_tokens = M;
+  m->staged_targets = n_targets;
+  m->staged_has_weights = false;
+  RT_TRY(run_staged(m, false, nullptr));
   return rt_model_read_results(m, logp_out, n_targets, hits_out);
 }
 

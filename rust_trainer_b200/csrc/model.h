@@ -126,7 +126,9 @@ struct rt_model {
   DevBuf tokens, pos, seq_start, x, ckpt, h, n1, n2, q_raw, k_raw, v_raw, q16, k16, v16, o16, lse, delta, g16, u16, hm16;
   DevBuf dx, dy16, sc_y, dhm, dg16, du16, sc_g, sc_u, dn, d_o, dO16, amax, dq, dk, dv, dq16, dk16, dv16, sc_q, sc_k, sc_v;
   DevBuf tpos, ttok, tw, logp, hits, xs, ns16, logits, dl16, sc_l, dns, dxs;
-  std::vector<int> h_pos, h_seq_start;
+  std::vector<int> h_pos, h_seq_start, h_gap;
+  DevBuf gap;               // per token (first, end) of the key range hidden from it: packed shared-prompt groups
+  bool staged_gap = false;  // the staged batch has such ranges
   int staged_tokens = 0, staged_targets = 0;
   bool staged_has_weights = false;
   // CUDA graphs of the staged step, one per (tokens, targets, backward) once it has run eagerly

@@ -62,13 +62,14 @@ int launch_tok_contract(const __half* P, const __half* Q, const float* pscale, i
 // ---- attention.cu: causal GQA attention over a concatenation of independent sequences.
 // q [M x nh x hd], k/v [M x nkv x hd] f16 (q unscaled; the kernels apply 1/sqrt(hd)).
 // seq_start[m] = index of the first token of m's sequence.  lse is [nh x M].
-int launch_attn_fwd(const __half* q, const __half* k, const __half* v, const int* seq_start, int M, int nh, int nkv,
+int launch_attn_fwd(const __half* q, const __half* k, const __half* v, const int* seq_start, const int* gap /* [M x 2] or null */, int M, int nh, int nkv,
                     int hd, __half* o, float* lse, cudaStream_t st);
 // dO16 is dO divided by a global scale (device scalar `do_scale`); outputs are true-scale f32.
 // dO row i stands for do_scale[0] * dO16[i], or, with row_scale, for row_scale[i] * dO16[i]
 // (then do_scale[0] must hold the largest row_scale).
 int launch_attn_bwd(const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
-                    const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, int M, int nh,
-                    int nkv, int hd, float* delta /* [nh x M] scratch */, float* dq, float* dk, float* dv, cudaStream_t st);
+                    const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap,
+                    int M, int nh, int nkv, int hd, float* delta /* [nh x M] scratch */, float* dq, float* dk, float* dv,
+                    cudaStream_t st);
 
 }  // namespace rt

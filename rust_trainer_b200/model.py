@@ -108,6 +108,37 @@ class Model:
                                                        tp.size, _fp(logp), C.byref(hits)))
         return logp, hits.value
 
+    def _layout(self, groups):
+        toks, offs = self._batch([g.tokens for g in groups])
+        pos = np.ascontiguousarray(np.concatenate([g.positions for g in groups]), dtype=np.int32)
+        seg = np.ascontiguousarray(np.concatenate([g.segments for g in groups]), dtype=np.int32)
+        return toks, offs, pos, seg
+
+    def forward_backward_packed(self, groups, target_pos, target_tok, weights):
+        """Model::forward_backward_packed for a batch of packing.Packed groups laid end to end;
+        target_pos index the concatenation of the groups' packed token arrays."""
+        toks, offs, pos, seg = self._layout(groups)
+        tp = np.ascontiguousarray(target_pos, dtype=np.int32)
+        tt = np.ascontiguousarray(target_tok, dtype=np.int32)
+        w = np.ascontiguousarray(weights, dtype=np.float32)
+        if not (tp.size == tt.size == w.size):
+            raise RtError(1, "targets and weights differ in length")
+        logp = np.empty(tp.size, dtype=np.float32)
+        hits = C.c_int32()
+        self.ctx.check(lib().rt_model_forward_backward_layout(self._h, _ip(toks), _ip(offs), len(groups), _ip(pos), _ip(seg),
+                                                              _ip(tp), _ip(tt), _fp(w), tp.size, _fp(logp), C.byref(hits)))
+        return logp, hits.value
+
+    def score_packed(self, groups, target_pos, target_tok):
+        toks, offs, pos, seg = self._layout(groups)
+        tp = np.ascontiguousarray(target_pos, dtype=np.int32)
+        tt = np.ascontiguousarray(target_tok, dtype=np.int32)
+        logp = np.empty(tp.size, dtype=np.float32)
+        hits = C.c_int32()
+        self.ctx.check(lib().rt_model_score_layout(self._h, _ip(toks), _ip(offs), len(groups), _ip(pos), _ip(seg), _ip(tp),
+                                                   _ip(tt), tp.size, _fp(logp), C.byref(hits)))
+        return logp, hits.value
+
     def score(self, seqs, target_pos, target_tok, want_logits: bool = False):
         toks, offs = self._batch(seqs)
         tp = np.ascontiguousarray(target_pos, dtype=np.int32)

@@ -71,3 +71,21 @@ def test_objective_helpers():
     assert [s.size for s in seqs] == [10, 8] and spans == [(0, 4), (4, 11)]
     assert tp.tolist() == [5, 6, 7, 8] + [10 + i for i in range(7)]  # i >= max(answer_start, 1) predicts from i - 1
     assert tt.tolist() == [6, 7, 8, 9] + list(range(1, 8))
+
+
+def test_pack_shared_prompt():
+    """pack (src/model.rs:266-290): longest common prefix, at least one own token per sequence,
+    a single sequence shares nothing; Packed::index / map_targets."""
+    from rust_trainer_b200 import packing
+
+    a, b, c = np.array([1, 2, 3, 4, 5]), np.array([1, 2, 3, 9]), np.array([1, 2, 3, 7, 8, 6])
+    p = packing.pack([a, b, c])
+    assert p.shared == 3 and p.offsets == [3, 5, 6]
+    assert p.tokens.tolist() == [1, 2, 3, 4, 5, 9, 7, 8, 6]
+    assert p.positions.tolist() == [0, 1, 2, 3, 4, 3, 3, 4, 5]
+    assert p.segments.tolist() == [0, 0, 0, 1, 1, 2, 3, 3, 3]
+    assert p.index(1, 2) == 2 and p.index(1, 3) == 5 and p.index(2, 5) == 8
+    assert packing.pack([a]).shared == 0
+    assert packing.pack([a, a]).shared == 4  # every sequence keeps one token of its own
+    tp, tt = p.map_targets(2, [2, 3, 4], [7, 8, 6])
+    assert tp.tolist() == [2, 6, 7] and tt.tolist() == [7, 8, 6]
