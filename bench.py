@@ -40,6 +40,16 @@ WORKLOADS = {
     # BASELINE.json configs[0] (the reference's own CPU-runnable case)
     "qwen3-0.6b-q4_0-4x256": dict(preset="qwen3-0.6b", quant="Q4_0", n_seq=4, seq_len=256, answer_frac=0.50, rank=16,
                                   alpha=32.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=0, lr_total=1, min_ratio=0.1),
+    # BASELINE.json configs[2]: Qwen2.5-0.5B shape, Q4_K where the row length allows it (ffn_down), Q4_0 elsewhere,
+    # every position a target
+    "qwen2.5-0.5b-q4_k-32x1024": dict(preset="qwen2.5-0.5b", quant="Q4_K", n_seq=32, seq_len=1024, answer_frac=1.0, rank=8,
+                                      alpha=16.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=2, lr_total=20, min_ratio=0.1),
+    # BASELINE.json configs[3]: Llama-3.2-3B shape, Q6_K, every position a target (per GPU: 16 x 2048)
+    "llama-3.2-3b-q6_k-16x2048": dict(preset="llama-3.2-3b", quant="Q6_K", n_seq=16, seq_len=2048, answer_frac=1.0, rank=16,
+                                      alpha=32.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=2, lr_total=20, min_ratio=0.1),
+    # BASELINE.json configs[4] at its 8-GPU share: Qwen3-4B shape, Q4_0, r = 32, 8 x 2048 per GPU, last 25 % targets
+    "qwen3-4b-q4_0-8x2048": dict(preset="qwen3-4b", quant="Q4_0", n_seq=8, seq_len=2048, answer_frac=0.25, rank=32,
+                                 alpha=64.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=2, lr_total=50, min_ratio=0.1),
     # two layers of configs[1] (the same per-layer shapes and token count, about 1 GB on the device):
     # the case the per-kernel profiler captures run on
     "qwen3-0.6b-q8_0-16x512-2layers": dict(preset="qwen3-0.6b", quant="Q8_0", n_seq=16, seq_len=512, answer_frac=0.30, rank=16,
