@@ -75,6 +75,12 @@ rt_status rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream);
  * their summed device time and their summed algorithmic work 2*tokens*out*in (flops) and
  * packed-weight + activation + result bytes. */
 uint64_t rt_ctx_launch_count(const rt_ctx* ctx);
+/* Failure detection without a fault: launches one warp that waits, with the same bounded wait the
+ * matmul kernel uses, on a barrier nothing arrives on.  After `limit_cycles` SM cycles (at most
+ * 2e9, about a second) the wait gives up and the kernel returns; the call then reports
+ * RT_ERR_DEVICE_WAIT_TIMEOUT (site 999) and the context stays usable.  No counterpart in the
+ * reference (its CPU path has no device waits). */
+rt_status rt_ctx_selftest_wait_timeout(rt_ctx* ctx, uint64_t limit_cycles);
 rt_status rt_ctx_set_profiling(rt_ctx* ctx, int enabled);
 rt_status rt_ctx_profile_read(rt_ctx* ctx, uint64_t* n_launches, double* total_ms, double* total_flops,
                               double* total_bytes);

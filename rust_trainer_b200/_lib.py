@@ -104,6 +104,7 @@ def _declare(L: C.CDLL) -> None:
         "rt_model_run_staged": (i32, [vp, C.c_int]),
         "rt_model_read_results": (i32, [vp, f32p, i32, i32p]),
         "rt_ctx_launch_count": (u64, [vp]),
+        "rt_ctx_selftest_wait_timeout": (i32, [vp, u64]),
         "rt_ctx_set_profiling": (i32, [vp, C.c_int]),
         "rt_ctx_profile_read": (i32, [vp, C.POINTER(u64), C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
         "rt_model_grad_buffer": (i32, [vp, C.POINTER(vp), C.POINTER(sz)]),

@@ -58,15 +58,17 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // Bounded wait. Returns false (and records `code` in *status) after ~4e9 SM cycles (about two
 // seconds).  The bound counts this SM's own cycle counter, which nothing outside the kernel can
 // step or re-synchronise.
+constexpr long long MBAR_WAIT_LIMIT_CYCLES = 4000000000ll;
 template <bool CLUSTER = false>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
+                                          long long limit_cycles = MBAR_WAIT_LIMIT_CYCLES) {
   if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
       if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > 4000000000ll) {
+    if (clock64() - t0 > limit_cycles) {
       atomicCAS(status, 0, code);
       return false;
     }

@@ -997,6 +997,20 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
 }
 
 
+// ------------------------------------------------------------------ the bounded wait, exercised on its own
+// One warp waits on a barrier nobody arrives on, with a short limit: the wait gives up, records
+// its site code and the kernel returns normally, which is what every wait of the matmul kernel
+// does when a peer never shows up.  The context stays usable.
+__global__ void wait_selftest_kernel(int* status, long long limit_cycles) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, status, 999, limit_cycles);
+}
+
 // ------------------------------------------------------------------ allocation-free entry point
 // Split-K partial sums of rt_frozen_backward_input_dev_noalloc live here instead of in memory
 // from cudaMalloc.  Every GPU that loads the library holds these 8 MiB until the process exits.
@@ -1020,6 +1034,15 @@ static int noalloc_scratch_for(int device, float** out) {
 }
 
 }  // namespace rt
+
+extern "C" rt_status rt_ctx_selftest_wait_timeout(rt_ctx* c, uint64_t limit_cycles) {
+  if (!c) return RT_ERR_BAD_ARG;
+  if (limit_cycles == 0 || limit_cycles > 2000000000ull) return c->fail(RT_ERR_BAD_ARG, "limit must be 1..2e9 cycles");
+  if (cudaSetDevice(c->device) != cudaSuccess) return RT_ERR_CUDA;
+  rt::wait_selftest_kernel<<<1, 32, 0, c->stream>>>(c->status_dev, (long long)limit_cycles);
+  if (cudaGetLastError() != cudaSuccess) return c->fail(RT_ERR_CUDA, "self-test launch failed");
+  return c->check_device_status("rt_ctx_selftest_wait_timeout");  // expected: RT_ERR_DEVICE_WAIT_TIMEOUT, site 999
+}
 
 extern "C" rt_status rt_frozen_backward_input_dev_noalloc(rt_frozen* f, const void* dy_dev, int in_dtype, size_t t,
                                                           void* dx_dev, int out_dtype, int accumulate) {

@@ -110,3 +110,20 @@ def test_full_size_properties(ctx):
     lhs, rhs = float((dy.astype(np.float64) * y1).sum()), float((dx.astype(np.float64) * x1).sum())
     assert abs(lhs - rhs) <= 2e-3 * abs(lhs) + 50.0  # inner products of ~2.5e7 random terms
     f.close()
+
+
+def test_a_wait_that_runs_out_is_a_status_not_a_hang(ctx):
+    """Every device-side wait is bounded: a barrier nothing arrives on makes the wait give up after
+    its limit (here 2e8 cycles, about 0.1 s), the kernel returns, the host reads
+    RT_ERR_DEVICE_WAIT_TIMEOUT with the wait's site code, and the context keeps working."""
+    from rust_trainer_b200._lib import lib
+
+    st = lib().rt_ctx_selftest_wait_timeout(ctx._h, 200_000_000)
+    assert st == 5  # RT_ERR_DEVICE_WAIT_TIMEOUT
+    assert b"site 999" in lib().rt_last_error(ctx._h)
+    rng = np.random.default_rng(1)
+    w = (rng.standard_normal((128, 64)) * 0.02).astype(np.float32)
+    f = rt.Frozen.from_f32(ctx, w, Q.Q8_0)
+    x = rng.standard_normal((5, 64)).astype(np.float32)
+    assert rel_l2(f.forward(x, 5), x @ O.dequant_rows(Q.Q8_0, Q.quantize(w, Q.Q8_0), 128, 64).T) < MATMUL_TOL
+    f.close()
