@@ -337,8 +337,15 @@ def run_ours(args):
     L.rt_ctx_set_profiling(ctx._h, 0)
     peaks = measured_peaks()
     achieved_tf = fl.value / (ms_l.value * 1e-3) / 1e12 if ms_l.value > 0 else 0.0
+    # DRAM traffic per launch: from the ncu capture of the kernel on one shape (profiles/qgemm_kernel_fwd_3072x1024_
+    # q8_0_t16384.md: 37.1 MB read + 50.1 MB written for 103.1 GFLOP, equal to the operands read once and the output
+    # written once), scaled by the work of this run's average launch
+    avg_launch_flops = fl.value / max(n_l.value, 1)
+    traffic = 87.2e6 * avg_launch_flops / 103.1e9
     roofline = {"bound": "tensor", "achieved": achieved_tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                "frac": achieved_tf / peaks["tflops"], "traffic": None, "peak_source": peaks["source"] + " (sustained bf16 cuBLAS)",
+                "frac": achieved_tf / peaks["tflops"], "traffic": traffic,
+                "traffic_source": "ncu dram__bytes_read+write of one captured shape, scaled by flops per launch",
+                "peak_source": peaks["source"] + " (sustained bf16 cuBLAS)",
                 "kernel": "qgemm_kernel", "launches_per_step": int(n_l.value // prof_steps),
                 "avg_launch_us": 1e3 * ms_l.value / max(n_l.value, 1), "share_of_step": (ms_l.value / prof_steps) / ms_step,
                 "flops_per_step": fl.value / prof_steps}
