@@ -262,6 +262,12 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
   uint32_t* tmem_slot = (uint32_t*)(bars + C::N_BARS);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef RT_B200_QPROF
+#define QG_STAMP(i) do { if (p.prof && blockIdx.x == 0) p.prof[512 * 24 + (i)] = (long long)globaltimer_ns(); } while (0)
+#else
+#define QG_STAMP(i) do { } while (0)
+#endif
+  if (threadIdx.x == 0) QG_STAMP(0);
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // 0 = leader
   const int n_cta = PAIR ? 2 : 1;
   const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
@@ -307,6 +313,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
   else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
+  if (threadIdx.x == 0) QG_STAMP(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -365,6 +372,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     // ------------------------------------------------------------ MMA issue (the leader's thread only)
     if (lane == 0 && rank == 0) {
       uint32_t tcount = 0;
+      bool it_first = true;
       int st = 0;        // stage ring position and its phase, advanced without divisions
       uint32_t ph = 0;
       bool ok = true;
@@ -383,6 +391,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         const uint32_t aph = (tcount >> 1) & 1;
         { bool w_; QG_TIMED(0, w_ = mbar_wait<false>(&acc_empty[acc], aph ^ 1, p.status, 301)); if (!w_) { ok = false; break; } }
         tc_fence_after();
+#ifdef RT_B200_QPROF
+        if (p.prof && blockIdx.x == 0 && tcount < 8) p.prof[512 * 24 + 8 + tcount] = (long long)globaltimer_ns();
+#endif
         const uint32_t d_tmem = tmem_base + acc * 256;
         for (int s = 0; s < n_steps; ++s) {
           if (!(p.dbg & 16)) {
@@ -392,6 +403,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           tc_fence_after();
           const uint32_t a_lo = (uint32_t)a_d0 + (uint32_t)st * (W_STAGE >> 4);
           const uint32_t b_lo = (uint32_t)b_d0 + (uint32_t)st * (C::ACT_STAGE >> 4);
+          if (it_first) { QG_STAMP(2); it_first = false; }
           if (p.dbg & 32) {
           } else if (s < s_main) {
             QG_TIMED(4, {
@@ -415,6 +427,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           else umma_commit(&acc_full[acc]);
         }
       }
+      QG_STAMP(3);
       QG_PROF_END(1);
     }
   } else if (warp < 10) {
@@ -624,7 +637,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       }
     }
     if (p.tma_out && lane == 0) bulk_wait_group<0>();  // all output writes of this warp have landed
-    if (warp == 10 && lane == 0) QG_PROF_END(3);
+    if (warp == 10 && lane == 0) { QG_STAMP(4); QG_PROF_END(3); }
   }
 
   // ---------------------------------------------------------------- teardown
@@ -642,6 +655,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     if (PAIR) tmem_dealloc_pair(tmem_base, 512);
     else tmem_dealloc(tmem_base, 512);
   }
+  if (threadIdx.x == 32) QG_STAMP(5);
 }
 
 // Sums split-K partials in split order (deterministic) and applies the epilogue the fused path
@@ -839,8 +853,8 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   p.prof = nullptr;
 #ifdef RT_B200_QPROF
   static long long* prof_dev = nullptr;
-  if (!prof_dev) cudaMalloc(&prof_dev, 512 * 24 * sizeof(long long));
-  cudaMemsetAsync(prof_dev, 0, 512 * 24 * sizeof(long long), st);
+  if (!prof_dev) cudaMalloc(&prof_dev, (512 * 24 + 16) * sizeof(long long));
+  cudaMemsetAsync(prof_dev, 0, (512 * 24 + 16) * sizeof(long long), st);
   p.prof = prof_dev;
 #endif
   {
@@ -933,7 +947,14 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
     }
   }
   const int n_items = n_tiles * p.n_splits;
-  const int workers = pair ? g_pair_workers : num_sms;
+  int workers = pair ? g_pair_workers : num_sms;
+#ifdef RT_B200_QPROF
+  {
+    static int lim = -1;
+    if (lim < 0) { const char* e = getenv("RT_B200_WORKERS"); lim = e ? atoi(e) : 0; }
+    if (lim > 0 && lim < workers) workers = lim;  // measurement aid: fewer CTAs (pairs) than the device holds
+  }
+#endif
   const int grid = (n_items < workers ? n_items : workers) * (pair ? 2 : 1);
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   if (ctx->profiling && !a.fixed_part) {
@@ -969,9 +990,17 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   RT_COUNT_LAUNCH(1);
 #ifdef RT_B200_QPROF
   {
-    static long long host[512 * 24];
+    static long long host[512 * 24 + 16];
     cudaMemcpyAsync(host, prof_dev, sizeof(host), cudaMemcpyDeviceToHost, st);
     cudaStreamSynchronize(st);
+    {
+      const long long* t = host + 512 * 24;
+      fprintf(stderr, "qstamp CTA0 ns from entry: init %lld first_mma %lld last_mma_issue %lld epilogue_done %lld exit %lld\n",
+              t[1] - t[0], t[2] - t[0], t[3] - t[0], t[4] - t[0], t[5] - t[0]);
+      fprintf(stderr, "qstamp tile starts:");
+      for (int i = 0; i < 8; ++i) if (t[8 + i]) fprintf(stderr, " %lld", t[8 + i] - t[0]);
+      fprintf(stderr, "\n");
+    }
     double sum[24] = {0};
     for (int c = 0; c < grid; ++c)
       for (int q = 0; q < 24; ++q) sum[q] += (double)host[c * 24 + q] / ((q >= 6 && q < 12 && pair) ? grid / 2 : grid);
