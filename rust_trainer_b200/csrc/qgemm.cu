@@ -8,14 +8,14 @@
 // weight rows or columns per tile), the activations are the "B" operand (up to 256 tokens per
 // tile), so the TMEM accumulator is the transposed output tile [128 x tokens].
 //
-// One persistent CTA per SM, warp-specialised:
-//   warp 0      producer : TMA tiles of activations (and of 16-bit weights), 128B swizzle
-//   warp 1      MMA      : one thread issues tcgen05.mma (kind::f16, fp32 accumulate in TMEM)
-//   warps 2-9   unpack   : packed bricks -> f16 tile in the UMMA shared-memory layout
-//                          (forward reads it K-major, backward reads the same bytes MN-major)
-//   warp 14     packed-brick producer: runs ahead of warp 0, bounded only by its own ring
-//   warps 10-13 epilogue : tcgen05.ld the accumulator (double buffered: 2 x 256 TMEM columns),
-//                          add bias / accumulate, store f32 and/or bf16
+// One persistent CTA per SM, warp-specialised (15 warps; roles by warp id, see the kernel):
+//   producer : one thread issues the TMA tiles of activations (and of 16-bit weights), 128B swizzle
+//   bricks   : one thread issues the bulk copies of packed bricks, running ahead in its own ring
+//   MMA      : one thread issues tcgen05.mma (kind::f16, fp32 accumulate in TMEM)
+//   unpack   : eight warps turn packed bricks into the f16 tile in the UMMA shared-memory layout
+//              (forward reads it K-major, backward reads the same bytes MN-major)
+//   epilogue : four warps tcgen05.ld the accumulator (double buffered: 2 x 256 TMEM columns),
+//              add bias / per-token factors, stage and TMA-store f32, bf16 or f16
 // The LoRA low-rank term is one more contraction chunk fed through the same accumulator.
 #include "ptx.cuh"
 #include "qformat.cuh"
@@ -75,7 +75,8 @@ struct KParams {
   long long* prof;  // measurement aid (RT_B200_QPROF): per-CTA cycle counts of each role's waits, else null
   int dbg;  // measurement aid (RT_B200_DBG bit mask): 1 = epilogue skips its stores, 2 = unpack warps skip the conversion,
             // 16 = no operand loads at all: the MMAs run on whatever shared memory holds (results are garbage),
-            // 32 = no MMAs are issued, 64 = no activation tiles are loaded
+            // 32 = no MMAs are issued, 64 = no activation tiles are loaded, 128 = half of the MMAs of a step,
+            // 256 = half of the unpack work of a step
 };
 
 // ------------------------------------------------------------------ unpackers
@@ -267,7 +268,34 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
 #else
 #define QG_STAMP(i) do { } while (0)
 #endif
+#ifdef RT_B200_QPROF
+#define QG_STEPSTAMP(kind, itv) do { if (p.prof && blockIdx.x == 0 && (itv) >= 16 && (itv) < 32) p.prof[512 * 24 + 16 + (kind) * 16 + ((itv) - 16)] = (long long)globaltimer_ns(); } while (0)
+#else
+#define QG_STEPSTAMP(kind, itv) do { } while (0)
+#endif
   if (threadIdx.x == 0) QG_STAMP(0);
+  // Roles by warp.  A warp runs on scheduler (warp % 4).  The MMA-issuing thread's instruction
+  // latency sets the pace of the whole pipeline (every tcgen05.mma and commit goes through it), so
+  // its scheduler (1) hosts only the two single-thread producers and one epilogue warp beside
+  // it (the epilogue needs one warp per residue: a warp reads TMEM lanes 32 * (warp % 4) ..), and
+  // the eight unpack warps share schedulers 0, 2 and 3 with the other epilogue warps.
+  //   warp 1 MMA | 5 activation producer | 9 packed-brick producer | 0, 2, 3, 13 epilogue | rest unpack
+  constexpr int R_PROD = 0, R_MMA = 1, R_UNPACK = 2, R_EPI = 3, R_RAW = 4;
+  int role = R_UNPACK, uidx = 0;  // uidx: 0..7 among the unpack warps, neighbours on different schedulers
+  switch (warp) {
+    case 1: role = R_MMA; break;
+    case 5: role = R_PROD; break;
+    case 9: role = R_RAW; break;
+    case 0: case 2: case 3: case 13: role = R_EPI; break;
+    case 4: uidx = 0; break;
+    case 6: uidx = 1; break;
+    case 7: uidx = 2; break;
+    case 8: uidx = 3; break;
+    case 10: uidx = 4; break;
+    case 11: uidx = 5; break;
+    case 12: uidx = 6; break;
+    default: uidx = 7; break;  // warp 14
+  }
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // 0 = leader
   const int n_cta = PAIR ? 2 : 1;
   const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
@@ -315,7 +343,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
   if (threadIdx.x == 0) QG_STAMP(1);
 
-  if (warp == 0) {
+  if (role == R_PROD) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       uint32_t it = 0;
@@ -368,10 +396,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       }
       QG_PROF_END(0);
     }
-  } else if (warp == 1) {
+  } else if (role == R_MMA) {
     // ------------------------------------------------------------ MMA issue (the leader's thread only)
     if (lane == 0 && rank == 0) {
-      uint32_t tcount = 0;
+      uint32_t tcount = 0, itg = 0;
       bool it_first = true;
       int st = 0;        // stage ring position and its phase, advanced without divisions
       uint32_t ph = 0;
@@ -401,6 +429,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
             { bool w_; QG_TIMED(2, w_ = mbar_wait<false>(&w_ready[st], ph, p.status, 303)); if (!w_) { ok = false; break; } }
           }
           tc_fence_after();
+          QG_STEPSTAMP(0, itg);
           const uint32_t a_lo = (uint32_t)a_d0 + (uint32_t)st * (W_STAGE >> 4);
           const uint32_t b_lo = (uint32_t)b_d0 + (uint32_t)st * (C::ACT_STAGE >> 4);
           if (it_first) { QG_STAMP(2); it_first = false; }
@@ -409,8 +438,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
             QG_TIMED(4, {
             umma_f16_split<PAIR>(d_tmem, a_lo, a_hi, b_lo, b_hi, p.idesc_main, (uint32_t)(s != 0));
             umma_f16_split<PAIR>(d_tmem, a_lo + a_k, a_hi, b_lo + b_k, b_hi, p.idesc_main, 1u);
-            umma_f16_split<PAIR>(d_tmem, a_lo + 2 * a_k, a_hi, b_lo + 2 * b_k, b_hi, p.idesc_main, 1u);
-            umma_f16_split<PAIR>(d_tmem, a_lo + 3 * a_k, a_hi, b_lo + 3 * b_k, b_hi, p.idesc_main, 1u);
+            if (!(p.dbg & 128)) {
+              umma_f16_split<PAIR>(d_tmem, a_lo + 2 * a_k, a_hi, b_lo + 2 * b_k, b_hi, p.idesc_main, 1u);
+              umma_f16_split<PAIR>(d_tmem, a_lo + 3 * a_k, a_hi, b_lo + 3 * b_k, b_hi, p.idesc_main, 1u);
+            }
             });
           } else {
             for (int kk = 0; kk < p.lora_mmas; ++kk)
@@ -420,6 +451,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           if (PAIR) umma_commit_pair(&stage_empty[st], 3);
           else umma_commit(&stage_empty[st]);
           });
+          QG_STEPSTAMP(1, itg);
+          ++itg;
           if (++st == NS) { st = 0; ph ^= 1; }
         }
         if (ok) {
@@ -430,13 +463,13 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       QG_STAMP(3);
       QG_PROF_END(1);
     }
-  } else if (warp < 10) {
+  } else if (role == R_UNPACK) {
     // ------------------------------------------------------------ unpack
     // One pass over a weight tile (load codes, convert, store, fence, arrive) is a chain of
     // dependent shared-memory operations: its latency, not its instruction count, sets the pace.
     // The eight warps therefore work as UG groups on alternate contraction steps, so UG passes
     // are in flight at a time.
-    const int t = threadIdx.x - 64;
+    const int t = uidx * 32 + lane;
     const int grp = t / UTG, tg = t % UTG;
     uint32_t it = 0, rit = 0;
     bool ok = true;
@@ -453,6 +486,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         const int st = it % NS;
         const uint32_t ph = (it / NS) & 1;
         { bool w_; QG_TIMED(0, w_ = mbar_wait(&stage_empty[st], ph ^ 1, p.status, 201)); if (!w_) { ok = false; break; } }
+        if (tg == 0) QG_STEPSTAMP(2, it);
         if (!PAIR && is16 && p.conv16 && s < s_main) {
           // The TMA'd 16-bit weight tile has the other 16-bit type: convert it in place
           // (element-wise, so the swizzled placement is untouched).  Single-CTA kernel only.
@@ -479,13 +513,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           const int rs = rit % NR;
           const uint32_t rph = (rit / NR) & 1;
           { bool w_; QG_TIMED(1, w_ = mbar_wait(&raw_full[rs], rph, p.status, 202)); if (!w_) { ok = false; break; } }
+          if (tg == 0) QG_STEPSTAMP(3, it);
           const uint8_t* raw = sRaw + rs * RAW_STAGE;
           uint8_t* dst = sW + st * W_STAGE;
           QG_TIMED(2, {
             if (!(p.dbg & 2)) {
               // 256 units (two bricks of 128) per tile; unit u: brick u >> 7 fills the 8 KB half u >> 7
 #pragma unroll
-              for (int u = tg; u < 256; u += UTG) {
+              for (int u = tg; u < ((p.dbg & 256) ? 128 : 256); u += UTG) {
                 if (p.act_f16) unpack_brick<false>(p.fmt, raw + (u >> 7) * p.brick_bytes, u & 127, dst + (u >> 7) * 8192);
                 else unpack_brick<true>(p.fmt, raw + (u >> 7) * p.brick_bytes, u & 127, dst + (u >> 7) * 8192);
               }
@@ -501,10 +536,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           if (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&w_ready[st]), 0));
           else mbar_arrive(&w_ready[st]);
         }
+        if (tg == 0) QG_STEPSTAMP(4, it);
       }
     }
     if (t == 0) QG_PROF_END(2);
-  } else if (warp == 14) {
+  } else if (role == R_RAW) {
     // ------------------------------------------------------------ packed-brick producer
     // Runs ahead of the stage ring: a brick pair is fetched as soon as its slot in the raw ring
     // is free, so its latency is not added to the time a weight stage is held.
@@ -637,7 +673,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       }
     }
     if (p.tma_out && lane == 0) bulk_wait_group<0>();  // all output writes of this warp have landed
-    if (warp == 10 && lane == 0) { QG_STAMP(4); QG_PROF_END(3); }
+    if (warp == 0 && lane == 0) { QG_STAMP(4); QG_PROF_END(3); }
   }
 
   // ---------------------------------------------------------------- teardown
@@ -853,8 +889,8 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   p.prof = nullptr;
 #ifdef RT_B200_QPROF
   static long long* prof_dev = nullptr;
-  if (!prof_dev) cudaMalloc(&prof_dev, (512 * 24 + 16) * sizeof(long long));
-  cudaMemsetAsync(prof_dev, 0, (512 * 24 + 16) * sizeof(long long), st);
+  if (!prof_dev) cudaMalloc(&prof_dev, (512 * 24 + 16 + 80) * sizeof(long long));
+  cudaMemsetAsync(prof_dev, 0, (512 * 24 + 16 + 80) * sizeof(long long), st);
   p.prof = prof_dev;
 #endif
   {
@@ -990,13 +1026,18 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   RT_COUNT_LAUNCH(1);
 #ifdef RT_B200_QPROF
   {
-    static long long host[512 * 24 + 16];
+    static long long host[512 * 24 + 16 + 80];
     cudaMemcpyAsync(host, prof_dev, sizeof(host), cudaMemcpyDeviceToHost, st);
     cudaStreamSynchronize(st);
     {
       const long long* t = host + 512 * 24;
       fprintf(stderr, "qstamp CTA0 ns from entry: init %lld first_mma %lld last_mma_issue %lld epilogue_done %lld exit %lld\n",
               t[1] - t[0], t[2] - t[0], t[3] - t[0], t[4] - t[0], t[5] - t[0]);
+      const long long* u = host + 512 * 24 + 16;
+      for (int i = 4; i < 12; ++i)
+        fprintf(stderr, "qstep %d: unpack wake %lld raw %lld done %lld | mma ready %lld commit %lld   (ns after commit of step %d: wake %lld, ready-done %lld)\n",
+                16 + i, u[32 + i] - t[0], u[48 + i] - t[0], u[64 + i] - t[0], u[i] - t[0], u[16 + i] - t[0], 16 + i - 4,
+                u[32 + i] - u[16 + i - 4], u[i] - u[64 + i]);
       fprintf(stderr, "qstamp tile starts:");
       for (int i = 0; i < 8; ++i) if (t[8 + i]) fprintf(stderr, " %lld", t[8 + i] - t[0]);
       fprintf(stderr, "\n");
