@@ -343,6 +343,69 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
   if (threadIdx.x == 0) QG_STAMP(1);
 
+  // One [32 tokens x 32 features] block of an accumulator -> staging -> TMA store / reduce-add.
+  // Transposes through shared memory (lane = output feature, register j = token); `stage_base`
+  // is 8 KB private to the calling warp: two f32 blocks or four 16-bit ones, a block is reused
+  // only after the store issued (nbuf) chunks ago has read it.
+  auto tma_chunk = [&](int acc, int wq, int c, int r0, int m0, float bias_v, uint8_t* stage_base, uint32_t& cnt) {
+    uint32_t v[32];
+    tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(wq * 32) << 16) + c * 32, v);
+    tmem_ld_wait();
+    const bool wide = p.out_dtype == OUT_F32;
+    const int buf = wide ? (int)(cnt & 1) : (int)(cnt & 3);
+    ++cnt;
+    uint8_t* stage = stage_base + buf * (wide ? 4096 : 2048);
+    if (lane == 0) {
+      if (wide) bulk_wait_group_read<1>();
+      else bulk_wait_group_read<3>();
+    }
+    // this chunk's 32 per-token factors: one coalesced load, handed round by shuffles
+    float rs_lane = 1.0f;
+    if (p.row_scale) { const int tok = m0 + c * 32 + lane; rs_lane = tok < p.M ? p.row_scale[tok] : 0.f; }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float val = __uint_as_float(v[j]);
+      if (p.row_scale) val *= __shfl_sync(0xffffffffu, rs_lane, j);
+      val += bias_v;
+      if (p.out_dtype == OUT_F32) ((float*)stage)[j * 32 + lane] = val;
+      else if (p.out_dtype == OUT_BF16) ((__nv_bfloat16*)stage)[j * 32 + lane] = __float2bfloat16_rn(val);
+      else ((__half*)stage)[j * 32 + lane] = __float2half_rn(val);
+    }
+    if (!(p.dbg & 8)) fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (p.accumulate) tma_reduce_add_2d(&tm_out, r0 + wq * 32, m0 + c * 32, stage);
+      else tma_store_2d(&tm_out, r0 + wq * 32, m0 + c * 32, stage);
+      bulk_commit_group();
+    }
+  };
+  // The epilogue of a CTA's LAST tile has nothing to hide behind, so the warps whose own work
+  // is over by then help: every warp with residue q (mod 4) may read TMEM lane quarter q.
+  // Quarter q's blocks go round-robin over its epilogue warp (turn 0) and its helpers (turns
+  // 1..): residues 0 and 2 have three unpack warps each, residue 3 two, residue 1 the two
+  // producer warps.  Helpers stage in the operand stages, which are idle once the last
+  // accumulator is complete.
+  const int n_my = worker < n_items ? (n_items - worker + n_workers - 1) / n_workers : 0;
+  const bool tail_help = p.tma_out && n_my > 0 && !(p.dbg & (1 | 512));
+  const int q_res = warp & 3;
+  const int q_turns = (q_res == 0 || q_res == 2) ? 4 : 3;  // epilogue warp + helpers of this residue
+  auto tail_helper = [&](int turn, int hslot) {
+    if (!tail_help) return;
+    const int tc_last = n_my - 1, item = worker + tc_last * n_workers;
+    QG_ITEM_DECODE(item);
+    (void)s_begin; (void)n_steps; (void)s_main;
+    QG_TILE_ORIGIN();
+    const int acc = tc_last & 1;
+    if (!mbar_wait(&acc_full[acc], (uint32_t)((tc_last >> 1) & 1), p.status, 402)) return;
+    tc_fence_after();
+    const int row = r0 + q_res * 32 + lane;
+    const float bias_v = (p.bias != nullptr && row < p.out_rows) ? p.bias[row] : 0.f;
+    uint32_t cnt = 0;
+    for (int c = turn; c < p.TN / 32; c += q_turns) tma_chunk(acc, q_res, c, r0, m0, bias_v, smem + hslot * 8192, cnt);
+    if (lane == 0) bulk_wait_group_read<0>();  // staging may go once read; the writes land by the end of the grid
+  };
+
   if (role == R_PROD) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
@@ -396,6 +459,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       }
       QG_PROF_END(0);
     }
+    __syncwarp();
+    tail_helper(warp >> 2, warp - 4);
   } else if (role == R_MMA) {
     // ------------------------------------------------------------ MMA issue (the leader's thread only)
     if (lane == 0 && rank == 0) {
@@ -540,6 +605,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       }
     }
     if (t == 0) QG_PROF_END(2);
+    tail_helper(warp >> 2, warp - 4);
   } else if (role == R_RAW) {
     // ------------------------------------------------------------ packed-brick producer
     // Runs ahead of the stage ring: a brick pair is fetched as soon as its slot in the raw ring
@@ -574,6 +640,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         }
       }
     }
+    __syncwarp();
+    tail_helper(warp >> 2, warp - 4);
   } else {
     // ------------------------------------------------------------ epilogue
     const int wq = warp & 3;  // TMEM lane quarter this warp may read
@@ -592,45 +660,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       const bool row_ok = row < p.out_rows;
       const float bias_v = (p.bias != nullptr && row_ok) ? p.bias[row] : 0.f;
       for (int c = 0; c < p.TN / 32; ++c) {
+        if (p.tma_out && !(p.dbg & 1)) {
+          if (tail_help && (int)tcount == n_my - 1 && (c % q_turns) != 0) continue;  // a helper's block
+          tma_chunk(acc, wq, c, r0, m0, bias_v, sOut + wq * (2 * OUT_STAGE / 4), out_chunk);
+          continue;
+        }
         uint32_t v[32];
         tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(wq * 32) << 16) + c * 32, v);
         tmem_ld_wait();
-        if (p.tma_out && !(p.dbg & 1)) {
-          // Transpose through shared memory: lane = output feature, register j = token.  Each
-          // warp stages its own [32 tokens][32 features] block and stores it with its own TMA
-          // copy, so the four warps never wait for one another.  A warp's 8 KB of staging holds
-          // two f32 blocks or four 16-bit ones; a block is reused only after the store issued
-          // (nbuf) chunks ago has read it.
-          const bool wide = p.out_dtype == OUT_F32;
-          const int buf = wide ? (int)(out_chunk & 1) : (int)(out_chunk & 3);
-          ++out_chunk;
-          uint8_t* stage = sOut + wq * (2 * OUT_STAGE / 4) + buf * (wide ? 4096 : 2048);
-          if (lane == 0) {
-            if (wide) bulk_wait_group_read<1>();
-            else bulk_wait_group_read<3>();
-          }
-          // this chunk's 32 per-token factors: one coalesced load, handed round by shuffles
-          float rs_lane = 1.0f;
-          if (p.row_scale) { const int tok = m0 + c * 32 + lane; rs_lane = tok < p.M ? p.row_scale[tok] : 0.f; }
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float val = __uint_as_float(v[j]);
-            if (p.row_scale) val *= __shfl_sync(0xffffffffu, rs_lane, j);
-            val += bias_v;
-            if (p.out_dtype == OUT_F32) ((float*)stage)[j * 32 + lane] = val;
-            else if (p.out_dtype == OUT_BF16) ((__nv_bfloat16*)stage)[j * 32 + lane] = __float2bfloat16_rn(val);
-            else ((__half*)stage)[j * 32 + lane] = __float2half_rn(val);
-          }
-          if (!(p.dbg & 8)) fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (p.accumulate) tma_reduce_add_2d(&tm_out, r0 + wq * 32, m0 + c * 32, stage);
-            else tma_store_2d(&tm_out, r0 + wq * 32, m0 + c * 32, stage);
-            bulk_commit_group();
-          }
-          continue;
-        }
         if (row_ok && !(p.dbg & 1)) {
           if (p.part != nullptr) {
 #pragma unroll
@@ -672,7 +709,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         else mbar_arrive(&acc_empty[acc]);
       }
     }
-    if (p.tma_out && lane == 0) bulk_wait_group<0>();  // all output writes of this warp have landed
+    if (p.tma_out && lane == 0) bulk_wait_group_read<0>();  // staging may go once read; the writes land by the end of the grid
     if (warp == 0 && lane == 0) { QG_STAMP(4); QG_PROF_END(3); }
   }
 
