@@ -76,7 +76,9 @@ struct KParams {
   int dbg;  // measurement aid (RT_B200_DBG bit mask): 1 = epilogue skips its stores, 2 = unpack warps skip the conversion,
             // 16 = no operand loads at all: the MMAs run on whatever shared memory holds (results are garbage),
             // 32 = no MMAs are issued, 64 = no activation tiles are loaded, 128 = half of the MMAs of a step,
-            // 256 = half of the unpack work of a step
+            // 256 = half of the unpack work of a step, 512 = no helpers for the last tile's epilogue,
+            // 1024 = staged blocks are not stored, 2048 = blocks are stored without being staged,
+            // 4096 = 16-bit outputs take the scalar staging path
 };
 
 // ------------------------------------------------------------------ unpackers
@@ -348,33 +350,91 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
   // is 8 KB private to the calling warp: two f32 blocks or four 16-bit ones, a block is reused
   // only after the store issued (nbuf) chunks ago has read it.
   auto tma_chunk = [&](int acc, int wq, int c, int r0, int m0, float bias_v, uint8_t* stage_base, uint32_t& cnt) {
-    uint32_t v[32];
-    tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(wq * 32) << 16) + c * 32, v);
-    tmem_ld_wait();
     const bool wide = p.out_dtype == OUT_F32;
     const int buf = wide ? (int)(cnt & 1) : (int)(cnt & 3);
     ++cnt;
     uint8_t* stage = stage_base + buf * (wide ? 4096 : 2048);
-    if (lane == 0) {
-      if (wide) bulk_wait_group_read<1>();
-      else bulk_wait_group_read<3>();
-    }
-    // this chunk's 32 per-token factors: one coalesced load, handed round by shuffles
-    float rs_lane = 1.0f;
-    if (p.row_scale) { const int tok = m0 + c * 32 + lane; rs_lane = tok < p.M ? p.row_scale[tok] : 0.f; }
-    __syncwarp();
+    const uint32_t tcol = tmem_base + acc * 256 + ((uint32_t)(wq * 32) << 16) + c * 32;
+    if (!wide && !(p.dbg & 4096)) {
+      // 16-bit output: the accumulator block arrives in mma-fragment layout (a thread holds two
+      // neighbouring tokens of one feature), is rounded to pairs and written with transposing
+      // matrix stores into a [32 tokens][32 features] block of 64-byte rows, 16-byte units
+      // XOR-swizzled by (token / 2) % 4 as the output map's 64-byte swizzle expects.
+      uint32_t v[2][16];
+      tmem_ld_16x256b_x4(tcol, v[0]);
+      tmem_ld_16x256b_x4(tcol + (16u << 16), v[1]);
+      float2 rs[4];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      float val = __uint_as_float(v[j]);
-      if (p.row_scale) val *= __shfl_sync(0xffffffffu, rs_lane, j);
-      val += bias_v;
-      if (p.out_dtype == OUT_F32) ((float*)stage)[j * 32 + lane] = val;
-      else if (p.out_dtype == OUT_BF16) ((__nv_bfloat16*)stage)[j * 32 + lane] = __float2bfloat16_rn(val);
-      else ((__half*)stage)[j * 32 + lane] = __float2half_rn(val);
+      for (int k = 0; k < 4; ++k) {
+        const int tok = m0 + c * 32 + 8 * k + 2 * (lane & 3);
+        rs[k] = make_float2(1.f, 1.f);
+        if (p.row_scale) {
+          rs[k].x = tok < p.M ? p.row_scale[tok] : 0.f;
+          rs[k].y = tok + 1 < p.M ? p.row_scale[tok + 1] : 0.f;
+        }
+      }
+      float bv[4] = {0.f, 0.f, 0.f, 0.f};  // features 16h + lane/4 + 8e -> bv[2h + e]
+      if (p.bias) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int row = r0 + wq * 32 + 8 * e + (lane >> 2);
+          bv[e] = row < p.out_rows ? p.bias[row] : 0.f;
+        }
+      }
+      if (lane == 0) bulk_wait_group_read<3>();
+      tmem_ld_wait();
+      __syncwarp();
+      uint32_t pk[2][8];  // [h][2k + e]: tokens 8k.., features 16h + 8e..
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float lo = __uint_as_float(v[h][4 * k + 2 * e]) * rs[k].x + bv[2 * h + e];
+            const float hi = __uint_as_float(v[h][4 * k + 2 * e + 1]) * rs[k].y + bv[2 * h + e];
+            if (p.out_dtype == OUT_BF16) { __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi); pk[h][2 * k + e] = *(uint32_t*)&b; }
+            else { __half2 b = __floats2half2_rn(lo, hi); pk[h][2 * k + e] = *(uint32_t*)&b; }
+          }
+      // matrix mi = lane / 8 of a store: tokens 8(2kp + mi/2).., feature unit 2h + (mi & 1); this lane addresses row lane % 8
+      const uint32_t sbase = smem_u32(stage);
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int kp = 0; kp < 2; ++kp) {
+          const int mi = lane >> 3;
+          const int tok = 8 * (2 * kp + (mi >> 1)) + (lane & 7);
+          const int unit = 2 * h + (mi & 1);
+          const uint32_t addr = sbase + tok * 64 + ((unit ^ ((tok >> 1) & 3)) << 4);
+          stmatrix_x4_trans(addr, pk[h][4 * kp], pk[h][4 * kp + 1], pk[h][4 * kp + 2], pk[h][4 * kp + 3]);
+        }
+    } else {
+      uint32_t v[32];
+      tmem_ld32(tcol, v);
+      tmem_ld_wait();
+      if (lane == 0) {
+        if (wide) bulk_wait_group_read<1>();
+        else bulk_wait_group_read<3>();
+      }
+      // this chunk's 32 per-token factors: one coalesced load, handed round by shuffles
+      float rs_lane = 1.0f;
+      if (p.row_scale) { const int tok = m0 + c * 32 + lane; rs_lane = tok < p.M ? p.row_scale[tok] : 0.f; }
+      __syncwarp();
+      if (!(p.dbg & 2048)) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float val = __uint_as_float(v[j]);
+          if (p.row_scale) val *= __shfl_sync(0xffffffffu, rs_lane, j);
+          val += bias_v;
+          if (p.out_dtype == OUT_F32) ((float*)stage)[j * 32 + lane] = val;
+          else if (p.out_dtype == OUT_BF16) ((__nv_bfloat16*)stage)[j * 32 + lane] = __float2bfloat16_rn(val);
+          else ((__half*)stage)[j * 32 + lane] = __float2half_rn(val);
+        }
+      }
     }
     if (!(p.dbg & 8)) fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0) {
+    if (lane == 0 && !(p.dbg & 1024)) {
       if (p.accumulate) tma_reduce_add_2d(&tm_out, r0 + wq * 32, m0 + c * 32, stage);
       else tma_store_2d(&tm_out, r0 + wq * 32, m0 + c * 32, stage);
       bulk_commit_group();
@@ -836,8 +896,9 @@ static int make_map_cached(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64
 
 // Output matrix [rows x cols] of f32 / bf16 / f16 with a row pitch of `ld` elements; box = 32 columns x 32 rows
 // (one epilogue warp's block), no swizzle (the epilogue writes the staging block row-major).
-static int make_out_map(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int dtype) {
-  auto key = std::make_tuple(base, rows, cols | (ld << 32), 32u, 32u | ((uint32_t)dtype << 8), true);
+static int make_out_map(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int dtype,
+                        bool swizzle64) {
+  auto key = std::make_tuple(base, rows, cols | (ld << 32), 32u, 32u | ((uint32_t)dtype << 8) | (swizzle64 ? 1u << 16 : 0u), true);
   if (ctx) {
     auto it = ctx->tmap_cache.find(key);
     if (it != ctx->tmap_cache.end()) {
@@ -853,7 +914,8 @@ static int make_out_map(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t 
   CUtensorMapDataType dt = dtype == OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                            : dtype == OUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = g_encode(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return RT_ERR_CUDA;
   if (!ctx) return RT_OK;
   if (ctx->tmap_cache.size() > 8192) ctx->tmap_cache.clear();
@@ -1014,7 +1076,8 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   {
     const uint64_t es = a.out_dtype == OUT_F32 ? 4 : 2;
     if (!p.part && ((uintptr_t)a.out % 16 == 0) && ((uint64_t)p.ld_out * es) % 16 == 0) {
-      rc = make_out_map(a.fixed_part ? nullptr : ctx, &tm_out, a.out, (uint64_t)a.M, (uint64_t)out_rows, (uint64_t)p.ld_out, a.out_dtype);
+      rc = make_out_map(a.fixed_part ? nullptr : ctx, &tm_out, a.out, (uint64_t)a.M, (uint64_t)out_rows, (uint64_t)p.ld_out, a.out_dtype,
+                        a.out_dtype != OUT_F32 && !(p.dbg & 4096));
       if (rc) return rc;
       p.tma_out = 1;
     }
