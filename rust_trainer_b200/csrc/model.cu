@@ -257,6 +257,77 @@ static void group_refresh(LinGroup& g, cudaStream_t st) {
   }
 }
 
+// Rebuilds, in one launch, every 16-bit adapter copy the next pass over the model will read and
+// that is older than its adapter: the stacked copies of usable groups, the own copies of the
+// linears outside them.  Runs before a pass (never inside a captured one: a copy that happened
+// to be fresh at capture time would otherwise never be rebuilt by the replays).
+rt_status refresh_adapter_copies(rt_model* m) {
+  rt_ctx* c = m->ctx;
+  std::vector<LoraRefreshJob>& jobs = m->refresh_jobs;
+  jobs.clear();
+  unsigned blocks = 0;
+  auto add = [&](LoraRefreshJob j) {
+    j.first_block = blocks;
+    blocks += lora_refresh_job_blocks(j);
+    jobs.push_back(j);
+  };
+  for (auto& b : m->blocks) {
+    bool grouped[7] = {false, false, false, false, false, false, false};
+    LinGroup* gs[2] = {&b.qkv, &b.gu};
+    for (LinGroup* g : gs) {
+      if (!group_usable(*g)) continue;
+      bool any;
+      group_lora_on(*g, &any);
+      const size_t K = (size_t)g->w.cols;
+      for (int i = 0; i < g->n; ++i) {
+        rt_linear* l = g->lin[i];
+        for (int k = 0; k < 7; ++k)
+          if (b.lin[k] == l) grouped[k] = true;
+        if (!any || !l->has_lora || g->seen[i] == l->lora.version) continue;
+        const LoraDev& lo = l->lora;
+        LoraRefreshJob j{lo.a, lo.b, g->a_s + (size_t)g->rank_off[i] * K, g->a_h + (size_t)g->rank_off[i] * K,
+                         g->bp + (size_t)g->row_off[i] * 64 + g->rank_off[i],
+                         g->bt_s + (size_t)g->rank_off[i] * g->rows_total + g->row_off[i],
+                         (unsigned long long)g->rows_total, lo.rank, (int)K, l->out_dim(), 0, lo.scale(), 0u};
+        add(j);
+      }
+    }
+    for (int k = 0; k < 7; ++k) {
+      rt_linear* l = b.lin[k];
+      if (!l || grouped[k] || !l->lora_active() || !l->lora.stale) continue;
+      const LoraDev& lo = l->lora;
+      LoraRefreshJob j{lo.a, lo.b, lo.a_s, lo.a_h, lo.bp, lo.bt_s, (unsigned long long)l->out_dim(),
+                       lo.rank, l->in_dim(), l->out_dim(), 1, lo.scale(), 0u};
+      add(j);
+    }
+  }
+  if (jobs.empty()) return RT_OK;
+  const size_t bytes = jobs.size() * sizeof(LoraRefreshJob);
+  if (m->refresh_sent.size() != jobs.size() || memcmp(m->refresh_sent.data(), jobs.data(), bytes) != 0) {
+    if (!m->refresh_tab.reserve(bytes)) return c->fail(RT_ERR_CUDA, "out of device memory (adapter refresh table)");
+    RT_CUDA(c, cudaMemcpyAsync(m->refresh_tab.p, jobs.data(), bytes, cudaMemcpyHostToDevice, c->stream));
+    m->refresh_sent = jobs;
+  }
+  launch_lora_refresh_table(m->refresh_tab.as<LoraRefreshJob>(), (int)jobs.size(), blocks, c->stream);
+  for (auto& b : m->blocks) {
+    LinGroup* gs[2] = {&b.qkv, &b.gu};
+    bool grouped[7] = {false, false, false, false, false, false, false};
+    for (LinGroup* g : gs) {
+      if (!group_usable(*g)) continue;
+      bool any;
+      group_lora_on(*g, &any);
+      for (int i = 0; i < g->n; ++i) {
+        for (int k = 0; k < 7; ++k)
+          if (b.lin[k] == g->lin[i]) grouped[k] = true;
+        if (any && g->lin[i]->has_lora) g->seen[i] = g->lin[i]->lora.version;
+      }
+    }
+    for (int k = 0; k < 7; ++k)
+      if (b.lin[k] && !grouped[k] && b.lin[k]->lora_active()) b.lin[k]->lora.stale = false;
+  }
+  return RT_OK;
+}
+
 // y[M x rows_total] = X . [W_0; W_1; ..]^T (+ stacked bias, + stacked low-rank chunk)
 rt_status group_forward_dev(LinGroup& g, LinearScratch& sc, const __half* x16, int M, void* y, int y_dtype, __half* hs_keep) {
   rt_ctx* c = g.lin[0]->ctx;
@@ -1282,13 +1353,14 @@ static uint64_t buffer_signature(rt_model* m) {
 // with no host work between them).
 static rt_status run_staged(rt_model* m, bool backward, float* logits_out_host) {
   rt_ctx* c = m->ctx;
+  RT_CUDA(c, cudaSetDevice(c->device));
+  RT_TRY(refresh_adapter_copies(m));  // outside the graph: only after a parameter update
   if (m->use_graphs < 0) {
     const char* e = getenv("RT_B200_NO_GRAPH");
     m->use_graphs = (e && e[0] == '1') ? 0 : 1;
   }
   if (!m->use_graphs || c->profiling || logits_out_host || c->stream == nullptr) return run_staged_body(m, backward, logits_out_host);
   RT_CUDA(c, cudaSetDevice(c->device));
-  for (rt_linear* l : m->lora_order) lora_refresh(l);  // outside the graph: only after a parameter update
   const int M = m->staged_tokens, nt = m->staged_targets, bw = backward ? 1 : 0;
   const uint64_t sig = buffer_signature(m);
   for (auto& ge : m->graphs)

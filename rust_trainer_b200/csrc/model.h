@@ -4,6 +4,7 @@
 // tensor resident in HBM.
 #pragma once
 #include "ctx.h"
+#include "ops.h"
 #include <map>
 #include <string>
 #include <vector>
@@ -127,6 +128,8 @@ struct rt_model {
   DevBuf dx, dy16, sc_y, dhm, dg16, du16, sc_g, sc_u, dn, d_o, dO16, amax, dq, dk, dv, dq16, dk16, dv16, sc_q, sc_k, sc_v;
   DevBuf tpos, ttok, tw, logp, hits, xs, ns16, logits, dl16, sc_l, dns, dxs;
   std::vector<int> h_pos, h_seq_start, h_gap;
+  DevBuf refresh_tab;       // device copy of refresh_sent
+  std::vector<rt::LoraRefreshJob> refresh_jobs, refresh_sent;
   DevBuf gap;               // per token (first, end) of the key range hidden from it: packed shared-prompt groups
   bool staged_gap = false;  // the staged batch has such ranges
   int staged_tokens = 0, staged_targets = 0;

@@ -1130,6 +1130,46 @@ __global__ void lora_refresh_group_kernel(const float* __restrict__ a, const flo
     bt_s[(size_t)j * ldb + n] = __float2half_rn(v * s);
   }
 }
+// Every stale adapter of a model in one launch: a block finds its row of the table by bisection
+// on first_block, then does what the two kernels above do for one adapter.
+__global__ void lora_refresh_table_kernel(const LoraRefreshJob* __restrict__ jobs, int n_jobs) {
+  __shared__ int s_job;
+  if (threadIdx.x == 0) {
+    int lo = 0, hi = n_jobs - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (jobs[mid].first_block <= blockIdx.x) lo = mid;
+      else hi = mid - 1;
+    }
+    s_job = lo;
+  }
+  __syncthreads();
+  const LoraRefreshJob j = jobs[s_job];
+  const size_t i = (size_t)(blockIdx.x - j.first_block) * blockDim.x + threadIdx.x;
+  const size_t na = (size_t)j.r * j.K;
+  if (i < na) {
+    const float v = j.a[i];
+    j.a_s[i] = __float2half_rn(v * j.s);
+    j.a_h[i] = __float2half_rn(v);
+  }
+  if (j.pad64) {
+    if (i < (size_t)j.N * 64) {
+      const int n = (int)(i / 64), c = (int)(i % 64);
+      const float v = c < j.r ? j.b[(size_t)n * j.r + c] : 0.f;
+      j.bp[i] = __float2half_rn(v);
+      if (c < j.r) j.bt_s[(size_t)c * j.ldb + n] = __float2half_rn(v * j.s);
+    }
+  } else if (i < (size_t)j.N * j.r) {
+    const int n = (int)(i / j.r), c = (int)(i % j.r);
+    const float v = j.b[i];
+    j.bp[(size_t)n * 64 + c] = __float2half_rn(v);
+    j.bt_s[(size_t)c * j.ldb + n] = __float2half_rn(v * j.s);
+  }
+}
+void launch_lora_refresh_table(const LoraRefreshJob* jobs_dev, int n_jobs, unsigned total_blocks, cudaStream_t st) {
+  if (n_jobs <= 0 || total_blocks == 0) return;
+  { lora_refresh_table_kernel<<<total_blocks, 256, 0, st>>>(jobs_dev, n_jobs); RT_COUNT_LAUNCH(1); }
+}
 void launch_lora_refresh_group(const float* a, const float* b, int r, int K, int N, float s, __half* a_s, __half* a_h,
                                __half* bp, __half* bt_s, size_t ldb, cudaStream_t st) {
   size_t n = (size_t)r * K > (size_t)N * r ? (size_t)r * K : (size_t)N * r;

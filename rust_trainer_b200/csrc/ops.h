@@ -35,6 +35,23 @@ void launch_lora_refresh_group(const float* a, const float* b, int r, int K, int
                                __half* bp, __half* bt_s, size_t ldb, cudaStream_t st);
 void launch_lora_refresh(const float* a, const float* b, int r, int K, int N, float s, __half* a_s, __half* a_h,
                          __half* bp, __half* bt_s, cudaStream_t st);
+// One adapter's operand copies as a row of a device table: every stale adapter of a model is
+// rebuilt by ONE launch.  pad64 = 1: bp is this adapter's own [N x 64] block, columns from r up
+// are zeroed, bt_s has row pitch N; pad64 = 0: bp / bt_s point into stacked operands (bp row
+// pitch 64, only columns < r are written; bt_s row pitch ldb).
+struct LoraRefreshJob {
+  const float *a, *b;
+  __half *a_s, *a_h, *bp, *bt_s;
+  unsigned long long ldb;
+  int r, K, N, pad64;
+  float s;
+  unsigned first_block;  // of this job in the grid; jobs are in increasing order
+};
+inline unsigned lora_refresh_job_blocks(const LoraRefreshJob& j) {
+  const size_t na = (size_t)j.r * j.K, nb = (size_t)j.N * (j.pad64 ? 64 : j.r);
+  return (unsigned)(((na > nb ? na : nb) + 255) / 256);
+}
+void launch_lora_refresh_table(const LoraRefreshJob* jobs_dev, int n_jobs, unsigned total_blocks, cudaStream_t st);
 size_t lora_grad_workspace_floats(int M, int C, int r);
 void launch_lora_grad(const __half* P, const __half* Q, const float* pscale, const float* qscale, int M, int C, int r,
                       size_t so_i, size_t so_j, float* out, float* workspace, cudaStream_t st);

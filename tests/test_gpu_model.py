@@ -177,6 +177,34 @@ def test_grouped_and_separate_projections_agree(ctx, monkeypatch):
     assert rel_l2(out["0"][1], out["1"][1]) < 3e-3
 
 
+def test_graph_replay_sees_updated_adapters(ctx, monkeypatch):
+    """A pass captured while the adapters' 16-bit copies were fresh must still read the new
+    values after an optimizer step: the copies are rebuilt before every pass, outside the
+    captured graph.  Same schedule with graphs off (plain launches) gives the same bits."""
+    out = {}
+    for flag in ("0", "1"):
+        monkeypatch.setenv("RT_B200_NO_GRAPH", flag)
+        spec, om, gm = _setup(ctx, "tiny-qwen3", "Q8_0")
+        om.close()
+        seqs, tp, tt, _ = _batch(spec, [80, 48, 64], seed=13)
+        w = np.full(tp.size, 1.0 / tp.size, np.float32)
+        gm.zero_grad()
+        gm.forward_backward(seqs, tp, tt, w)          # eager: sizes the buffers
+        gm.forward_backward(seqs, tp, tt, w)          # captured with nothing stale
+        s1 = gm.score(seqs, tp, tt)[0]
+        s1 = gm.score(seqs, tp, tt)[0]                # forward-only graph, captured the same way
+        gm.optim_step(5e-2, 1.0, weight_decay=0.0)    # a large step: stale copies would show
+        gm.zero_grad()
+        lp, _ = gm.forward_backward(seqs, tp, tt, w)  # replay
+        s2 = gm.score(seqs, tp, tt)[0]                # replay
+        out[flag] = (lp, s2, _gpu_flat(gm, "ga", "gb"))
+        assert not np.array_equal(s1, s2)
+        assert np.allclose(lp, s2, rtol=1e-5, atol=1e-6)
+        gm.close()
+    for k in range(3):
+        assert np.array_equal(out["0"][k], out["1"][k])
+
+
 def test_checkpointing_modes_agree(ctx):
     """Model.checkpointing (src/model.rs:663-684): keeping every block's caches or rebuilding
     them before the backward runs the same kernels on the same data, so the results are equal
