@@ -27,13 +27,15 @@ namespace rt {
 constexpr int W_STAGE = 16384;        // 128 x 64 x 16-bit
 constexpr int RAW_STAGE = 2 * 4352;   // largest brick pair (Q8_0)
 constexpr int QG_THREADS = 480;       // producer, MMA, 8 unpack, 4 epilogue warps, packed-brick producer
-constexpr int OUT_STAGE = 32 * 128 * 4;  // 32 tokens x 128 output features x f32: the epilogue's TMA-store staging
 
 // Shared-memory plan of one CTA.  A CTA of a pair stages half of the token tile, so its stages
 // are a third smaller, so four of them leave room for the deeper unpack pipeline.
 template <bool PAIR>
 struct QCfg {
-  static constexpr int NS = PAIR ? 4 : 3;                  // activation / unpacked-weight stages
+#ifndef RT_B200_PAIR_NS
+#define RT_B200_PAIR_NS 4
+#endif
+  static constexpr int NS = PAIR ? RT_B200_PAIR_NS : 3;    // activation / unpacked-weight stages
   static constexpr int NR = 4;                             // packed brick-pair stages
   // The eight unpack warps work as UG groups on alternate contraction steps.  Waits are by phase
   // parity, which is only sound while a waiter cannot run two phases ahead of its barrier:
@@ -48,7 +50,11 @@ struct QCfg {
   static constexpr int OFF_W = NS * ACT_STAGE;
   static constexpr int OFF_RAW = OFF_W + NS * W_STAGE;
   static constexpr int OFF_OUT = OFF_RAW + NR * RAW_STAGE;
-  static constexpr int OFF_BAR = OFF_OUT + 2 * OUT_STAGE;
+  // Epilogue staging per warp: blocks of [32 tokens x 32 features], 2 KB (16-bit) or 4 KB (f32).
+  // (A pair kernel built with five operand stages, a measurement variant, keeps half as many.)
+  static constexpr int OUT_WARP = (PAIR && NS > 4) ? 4096 : 8192;
+  static constexpr int OUT_BUFS16 = OUT_WARP / 2048, OUT_BUFS32 = OUT_WARP / 4096;
+  static constexpr int OFF_BAR = OFF_OUT + 4 * OUT_WARP;
   static constexpr int N_BARS = 3 * NS + 2 * NR + 4;
   static constexpr int SMEM_BYTES = OFF_BAR + N_BARS * 8 + 16 + 1024;
 };
@@ -78,7 +84,9 @@ struct KParams {
             // 32 = no MMAs are issued, 64 = no activation tiles are loaded, 128 = half of the MMAs of a step,
             // 256 = half of the unpack work of a step, 512 = no helpers for the last tile's epilogue,
             // 1024 = staged blocks are not stored, 2048 = blocks are stored without being staged,
-            // 4096 = 16-bit outputs take the scalar staging path
+            // 4096 = 16-bit outputs take the scalar staging path.  (There is deliberately no switch that
+            // removes the MMA thread's operand waits while the loads run: without that back-pressure the
+            // producers overrun the ring and the barriers' byte counts, and the launch faults.)
 };
 
 // ------------------------------------------------------------------ unpackers
@@ -351,7 +359,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
   // only after the store issued (nbuf) chunks ago has read it.
   auto tma_chunk = [&](int acc, int wq, int c, int r0, int m0, float bias_v, uint8_t* stage_base, uint32_t& cnt) {
     const bool wide = p.out_dtype == OUT_F32;
-    const int buf = wide ? (int)(cnt & 1) : (int)(cnt & 3);
+    const int buf = wide ? (int)(cnt % C::OUT_BUFS32) : (int)(cnt % C::OUT_BUFS16);
     ++cnt;
     uint8_t* stage = stage_base + buf * (wide ? 4096 : 2048);
     const uint32_t tcol = tmem_base + acc * 256 + ((uint32_t)(wq * 32) << 16) + c * 32;
@@ -381,7 +389,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           bv[e] = row < p.out_rows ? p.bias[row] : 0.f;
         }
       }
-      if (lane == 0) bulk_wait_group_read<3>();
+      if (lane == 0) bulk_wait_group_read<C::OUT_BUFS16 - 1>();
       tmem_ld_wait();
       __syncwarp();
       uint32_t pk[2][8];  // [h][2k + e]: tokens 8k.., features 16h + 8e..
@@ -413,8 +421,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       tmem_ld32(tcol, v);
       tmem_ld_wait();
       if (lane == 0) {
-        if (wide) bulk_wait_group_read<1>();
-        else bulk_wait_group_read<3>();
+        if (wide) bulk_wait_group_read<C::OUT_BUFS32 - 1>();
+        else bulk_wait_group_read<C::OUT_BUFS16 - 1>();
       }
       // this chunk's 32 per-token factors: one coalesced load, handed round by shuffles
       float rs_lane = 1.0f;
@@ -551,6 +559,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         for (int s = 0; s < n_steps; ++s) {
           if (!(p.dbg & 16)) {
             { bool w_; QG_TIMED(1, w_ = mbar_wait<false>(&full[st], ph, p.status, 302)); if (!w_) { ok = false; break; } }
+            QG_STEPSTAMP(5, itg);
             { bool w_; QG_TIMED(2, w_ = mbar_wait<false>(&w_ready[st], ph, p.status, 303)); if (!w_) { ok = false; break; } }
           }
           tc_fence_after();
@@ -722,7 +731,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       for (int c = 0; c < p.TN / 32; ++c) {
         if (p.tma_out && !(p.dbg & 1)) {
           if (tail_help && (int)tcount == n_my - 1 && (c % q_turns) != 0) continue;  // a helper's block
-          tma_chunk(acc, wq, c, r0, m0, bias_v, sOut + wq * (2 * OUT_STAGE / 4), out_chunk);
+          tma_chunk(acc, wq, c, r0, m0, bias_v, sOut + wq * C::OUT_WARP, out_chunk);
           continue;
         }
         uint32_t v[32];
@@ -988,8 +997,8 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   p.prof = nullptr;
 #ifdef RT_B200_QPROF
   static long long* prof_dev = nullptr;
-  if (!prof_dev) cudaMalloc(&prof_dev, (512 * 24 + 16 + 80) * sizeof(long long));
-  cudaMemsetAsync(prof_dev, 0, (512 * 24 + 16 + 80) * sizeof(long long), st);
+  if (!prof_dev) cudaMalloc(&prof_dev, (512 * 24 + 16 + 96) * sizeof(long long));
+  cudaMemsetAsync(prof_dev, 0, (512 * 24 + 16 + 96) * sizeof(long long), st);
   p.prof = prof_dev;
 #endif
   {
@@ -1126,7 +1135,7 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   RT_COUNT_LAUNCH(1);
 #ifdef RT_B200_QPROF
   {
-    static long long host[512 * 24 + 16 + 80];
+    static long long host[512 * 24 + 16 + 96];
     cudaMemcpyAsync(host, prof_dev, sizeof(host), cudaMemcpyDeviceToHost, st);
     cudaStreamSynchronize(st);
     {
@@ -1135,8 +1144,8 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
               t[1] - t[0], t[2] - t[0], t[3] - t[0], t[4] - t[0], t[5] - t[0]);
       const long long* u = host + 512 * 24 + 16;
       for (int i = 4; i < 12; ++i)
-        fprintf(stderr, "qstep %d: unpack wake %lld raw %lld done %lld | mma ready %lld commit %lld   (ns after commit of step %d: wake %lld, ready-done %lld)\n",
-                16 + i, u[32 + i] - t[0], u[48 + i] - t[0], u[64 + i] - t[0], u[i] - t[0], u[16 + i] - t[0], 16 + i - 4,
+        fprintf(stderr, "qstep %d: unpack wake %lld raw %lld done %lld | mma full %lld ready %lld commit %lld   (ns after commit of step %d: wake %lld, ready-done %lld)\n",
+                16 + i, u[32 + i] - t[0], u[48 + i] - t[0], u[64 + i] - t[0], u[80 + i] - t[0], u[i] - t[0], u[16 + i] - t[0], 16 + i - 4,
                 u[32 + i] - u[16 + i - 4], u[i] - u[64 + i]);
       fprintf(stderr, "qstamp tile starts:");
       for (int i = 0; i < 8; ++i) if (t[8 + i]) fprintf(stderr, " %lld", t[8 + i] - t[0]);
