@@ -328,8 +328,12 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NS; ++i) {
-      mbar_init(&full[i], 1);
-      mbar_init(&w_ready[i], (8 / UG) * n_cta);  // one arrival per warp of the group that owns the step
+      // One barrier gates a step's MMAs: the producer's expect-tx arrival (with the bytes TMA brings)
+      // plus one arrival per warp of the unpack group that owns the step, from every CTA of the pair.
+      // Only the in-place 16-bit conversion needs the landing and the conversion told apart: then
+      // the warps wait on `full` themselves and report on `w_ready`.
+      mbar_init(&full[i], p.conv16 ? 1 : 1 + (8 / UG) * n_cta);
+      mbar_init(&w_ready[i], (8 / UG) * n_cta);
       mbar_init(&stage_empty[i], 1);
     }
     for (int i = 0; i < NR; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], UTG); }
@@ -560,7 +564,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           if (!(p.dbg & 16)) {
             { bool w_; QG_TIMED(1, w_ = mbar_wait<false>(&full[st], ph, p.status, 302)); if (!w_) { ok = false; break; } }
             QG_STEPSTAMP(5, itg);
-            { bool w_; QG_TIMED(2, w_ = mbar_wait<false>(&w_ready[st], ph, p.status, 303)); if (!w_) { ok = false; break; } }
+            if (p.conv16) { bool w_; QG_TIMED(2, w_ = mbar_wait<false>(&w_ready[st], ph, p.status, 303)); if (!w_) { ok = false; break; } }
           }
           tc_fence_after();
           QG_STEPSTAMP(0, itg);
@@ -667,8 +671,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         // one arrival per warp, after every lane's writes are fenced towards the tensor core's reads
         __syncwarp();
         if (lane == 0) {
-          if (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&w_ready[st]), 0));
-          else mbar_arrive(&w_ready[st]);
+          uint64_t* ready = p.conv16 ? &w_ready[st] : &full[st];
+          if (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(ready), 0));
+          else mbar_arrive(ready);
         }
         if (tg == 0) QG_STEPSTAMP(4, it);
       }
