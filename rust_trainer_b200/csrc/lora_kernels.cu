@@ -12,6 +12,7 @@
 #include "rt_internal.h"
 #include <cuda_fp16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace rt {
 namespace {
@@ -57,7 +58,7 @@ __device__ __forceinline__ void load64x64(uint32_t sbase, const __half* g, int r
 template <int R16, int MW>
 __global__ void __launch_bounds__(32 * MW)
 skinny_nt_kernel(const __half* __restrict__ X, const __half* __restrict__ Wt, int M, int K, int r, __half* __restrict__ out) {
-  constexpr int NST = MW >= 4 ? 8 : 4;         // stages in flight: the kernel is pure memory latency
+  constexpr int NST = 8;                       // stages in flight: the kernel is pure memory latency
   constexpr int ROWS = 16 * MW, NT = 32 * MW;
   constexpr int XB = ROWS * 128, WB = 16 * R16 * 128, SB = XB + WB;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -383,7 +384,7 @@ __global__ void lora_grads_group_reduce_kernel(const float* __restrict__ partB, 
 
 template <int R16, int MW>
 static void skinny_launch(const __half* X, const __half* Wt, int M, int K, int r, __half* out, cudaStream_t st) {
-  constexpr int SMEM = (MW >= 4 ? 8 : 4) * (16 * MW * 128 + 16 * R16 * 128);
+  constexpr int SMEM = 8 * (16 * MW * 128 + 16 * R16 * 128);
   static bool attr = false;
   if (!attr) {
     cudaFuncSetAttribute(skinny_nt_kernel<R16, MW>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -395,7 +396,9 @@ int launch_skinny_nt(const __half* X, const __half* Wt, int M, int K, int r, __h
   if (M <= 0) return 0;
   if (r <= 0 || r > 64 || (r & 1) || K % 8 != 0) return 1;
   // 64 rows per CTA once that still gives every SM a CTA; 32 rows below
-  const bool wide = M >= 64 * 120;
+  static int force = -1;  // measurement aid: RT_B200_SKINNY_ROWS=32|64 overrides the choice
+  if (force < 0) { const char* e = getenv("RT_B200_SKINNY_ROWS"); force = e ? atoi(e) : 0; }
+  const bool wide = force ? force == 64 : M >= 64 * 120;
 #define RT_SKINNY(R) do { if (wide) skinny_launch<R, 4>(X, Wt, M, K, r, out, st); else skinny_launch<R, 2>(X, Wt, M, K, r, out, st); } while (0)
   if (r <= 16) RT_SKINNY(1);
   else if (r <= 32) RT_SKINNY(2);
