@@ -316,7 +316,8 @@ def run_ours(args):
 
     if args.launch_list:
         if rank == 0:
-            print(json.dumps({"launch_list_run": True, "ms_per_step": ms_step, "gpu_launches_per_step": int(launches)}), flush=True)
+            print(json.dumps({"launch_list_run": True, "ms_per_step": ms_step, "gpu_launches_per_step": int(launches),
+                              "gpu_launches_before_timed": int(launches0)}), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return 0
