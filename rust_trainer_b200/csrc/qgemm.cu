@@ -36,7 +36,10 @@ struct QCfg {
 #define RT_B200_PAIR_NS 4
 #endif
   static constexpr int NS = PAIR ? RT_B200_PAIR_NS : 3;    // activation / unpacked-weight stages
-  static constexpr int NR = 4;                             // packed brick-pair stages
+#ifndef RT_B200_PAIR_NR
+#define RT_B200_PAIR_NR 4
+#endif
+  static constexpr int NR = PAIR ? RT_B200_PAIR_NR : 4;    // packed brick-pair stages
   // The eight unpack warps work as UG groups on alternate contraction steps.  Waits are by phase
   // parity, which is only sound while a waiter cannot run two phases ahead of its barrier:
   // UG <= NS keeps a group from reaching a stage before the use two back has been released, and
@@ -52,7 +55,7 @@ struct QCfg {
   static constexpr int OFF_OUT = OFF_RAW + NR * RAW_STAGE;
   // Epilogue staging per warp: blocks of [32 tokens x 32 features], 2 KB (16-bit) or 4 KB (f32).
   // (A pair kernel built with five operand stages, a measurement variant, keeps half as many.)
-  static constexpr int OUT_WARP = (PAIR && NS > 4) ? 4096 : 8192;
+  static constexpr int OUT_WARP = (PAIR && (NS > 4 || NR > 4)) ? 4096 : 8192;
   static constexpr int OUT_BUFS16 = OUT_WARP / 2048, OUT_BUFS32 = OUT_WARP / 4096;
   static constexpr int OFF_BAR = OFF_OUT + 4 * OUT_WARP;
   static constexpr int N_BARS = 3 * NS + 2 * NR + 4;
@@ -566,7 +569,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
             QG_STEPSTAMP(5, itg);
             if (p.conv16) { bool w_; QG_TIMED(2, w_ = mbar_wait<false>(&w_ready[st], ph, p.status, 303)); if (!w_) { ok = false; break; } }
           }
-          tc_fence_after();
+          tc_fence_after();  // (measured free: the step time is the same without it)
           QG_STEPSTAMP(0, itg);
           const uint32_t a_lo = (uint32_t)a_d0 + (uint32_t)st * (W_STAGE >> 4);
           const uint32_t b_lo = (uint32_t)b_d0 + (uint32_t)st * (C::ACT_STAGE >> 4);
