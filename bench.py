@@ -342,7 +342,7 @@ def run_ours(args):
     # q8_0_t16384.md: 37.1 MB read + 50.1 MB written for 103.1 GFLOP, equal to the operands read once and the output
     # written once), scaled by the work of this run's average launch
     avg_launch_flops = fl.value / max(n_l.value, 1)
-    traffic = 87.2e6 * avg_launch_flops / 103.1e9
+    traffic = 87.8e6 * avg_launch_flops / 103.1e9
     roofline = {"bound": "tensor", "achieved": achieved_tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
                 "frac": achieved_tf / peaks["tflops"], "traffic": traffic,
                 "traffic_source": "ncu dram__bytes_read+write of one captured shape, scaled by flops per launch",
