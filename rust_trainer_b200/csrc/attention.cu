@@ -99,18 +99,23 @@ __device__ __forceinline__ void frag_b_kn(uint32_t sbase, int k0, int nc, uint32
 constexpr float LOG2E = 1.4426950408889634f;
 
 // ------------------------------------------------------------------ forward
+// K and V are single-buffered (48 KB per CTA with Q, so three CTAs fit an SM): V(n) is fetched
+// while Q.K(n)^T runs, K(n+1) while the softmax and P.V(n) run.
 template <int HD>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, HD == 128 ? 3 : 4)
 attn_fwd_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const __half* __restrict__ v,
                 const int* __restrict__ seq_start, const int2* __restrict__ gap, int M, int nh, int nkv, float scale,
                 __half* __restrict__ o, float* __restrict__ lse) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const uint32_t sQ = smem_addr(smem), sKV = sQ + BT * HD * 2;  // then two (K, V) buffers
+  const uint32_t sQ = smem_addr(smem), sK = sQ + BT * HD * 2, sV = sK + BT * HD * 2;
   const int m0 = blockIdx.x * BT, h = blockIdx.y, g = h / (nh / nkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
   const float sl2 = scale * LOG2E;
 
+  const int kbeg = (seq_start[m0] / BT) * BT;
+  const int kend = min(m0 + BT, M);
   load_tile<HD>(sQ, q, m0, M, nh, h);
+  load_tile<HD>(sK, k, kbeg, M, nkv, g);
   cp_async_commit();
   cp_async_wait_all();
   __syncthreads();
@@ -127,22 +132,10 @@ attn_fwd_kernel(const __half* __restrict__ q, const __half* __restrict__ k, cons
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
 
-  const int kbeg = (seq_start[m0] / BT) * BT;
-  const int kend = min(m0 + BT, M);
-  load_tile<HD>(sKV, k, kbeg, M, nkv, g);
-  load_tile<HD>(sKV + BT * HD * 2, v, kbeg, M, nkv, g);
-  cp_async_commit();
-  int it = 0;
-  for (int n0 = kbeg; n0 < kend; n0 += BT, ++it) {
-    const uint32_t sK = sKV + (it & 1) * 2 * BT * HD * 2, sV = sK + BT * HD * 2;
-    if (n0 + BT < kend) {  // prefetch the next key tile while this one is used
-      const uint32_t nK = sKV + ((it & 1) ^ 1) * 2 * BT * HD * 2;
-      load_tile<HD>(nK, k, n0 + BT, M, nkv, g);
-      load_tile<HD>(nK + BT * HD * 2, v, n0 + BT, M, nkv, g);
-    }
+  for (int n0 = kbeg; n0 < kend; n0 += BT) {
+    // K(n) is in shared memory and every warp is past P.V(n-1): V(n) may overwrite the V buffer
+    load_tile<HD>(sV, v, n0, M, nkv, g);
     cp_async_commit();
-    cp_async_wait_prev();
-    __syncthreads();
 
     float s[8][4];
 #pragma unroll
@@ -157,6 +150,10 @@ attn_fwd_kernel(const __half* __restrict__ q, const __half* __restrict__ k, cons
         mma16816(s[2 * np + 1], qf[kk], b + 2);
       }
     }
+    cp_async_wait_all();
+    __syncthreads();  // V(n) has landed; every warp is done with K(n)
+    if (n0 + BT < kend) load_tile<HD>(sK, k, n0 + BT, M, nkv, g);
+    cp_async_commit();
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
@@ -208,7 +205,8 @@ attn_fwd_kernel(const __half* __restrict__ q, const __half* __restrict__ k, cons
         mma16816(oacc[2 * np + 1], a, b + 2);
       }
     }
-    __syncthreads();  // every warp is done with this buffer before the next prefetch overwrites it
+    cp_async_wait_all();
+    __syncthreads();  // K(n+1) has landed; every warp is done with V(n)
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -504,7 +502,7 @@ attn_bwd_dq_kernel(const __half* __restrict__ q, const __half* __restrict__ k, c
 template <int HD>
 int fwd_impl(const __half* q, const __half* k, const __half* v, const int* seq_start, const int2* gap, int M, int nh, int nkv,
              __half* o, float* lse, cudaStream_t st) {
-  const size_t smem = 5 * BT * HD * 2;
+  const size_t smem = 3 * BT * HD * 2;
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 3;
