@@ -74,6 +74,33 @@ def test_adjoint_identity_on_device(ctx, t):
     f.close()
 
 
+@pytest.mark.parametrize("n,k,tokens", [(512, 256, 300), (384, 256, 1000), (1024, 128, 4133)])
+def test_16_bit_outputs_are_the_rounded_f32_outputs(ctx, n, k, tokens):
+    """The device entry points write f32, f16 or bf16.  The 16-bit epilogue (fragment-layout TMEM
+    loads, paired rounding, transposing matrix stores, swizzled TMA store) must give exactly the
+    f32 result rounded once, for the CTA-pair kernel (a multiple of 256 features), the single-CTA
+    one, and token counts that end inside a tile and inside a 32-token block."""
+    import torch
+
+    from rust_trainer_b200._lib import DT_BF16, DT_F16, DT_F32, lib
+
+    L = lib()
+    rng = np.random.default_rng(n + tokens)
+    f = rt.Frozen.from_f32(ctx, (rng.standard_normal((n, k)) * 0.05).astype(np.float32), Q.Q8_0)
+    x = torch.randn(tokens, k, device="cuda", dtype=torch.float16)
+    y32 = torch.full((tokens, n), float("nan"), device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    ctx.check(L.rt_frozen_forward_dev(f._h, x.data_ptr(), DT_F16, tokens, y32.data_ptr(), DT_F32, 0))
+    for dt, tdt in ((DT_F16, torch.float16), (DT_BF16, torch.bfloat16)):
+        y16 = torch.full((tokens + 1, n), 7.0, device="cuda", dtype=tdt)  # one guard row behind the output
+        torch.cuda.synchronize()
+        ctx.check(L.rt_frozen_forward_dev(f._h, x.data_ptr(), DT_F16, tokens, y16.data_ptr(), dt, 0))
+        ctx.synchronize()
+        assert torch.equal(y16[:tokens], y32.to(tdt)), (dt, float((y16[:tokens].float() - y32).abs().max()))
+        assert bool((y16[tokens] == 7.0).all())  # nothing written past the last token
+    f.close()
+
+
 def test_empty_and_refused_inputs(ctx):
     rng = np.random.default_rng(0)
     w = (rng.standard_normal((64, 64)) * 0.02).astype(np.float32)
