@@ -41,6 +41,7 @@ enum {
 
 /* ggml tensor types accepted for frozen weights (numeric values are GGUF's). */
 enum {
+  RT_GGML_F32 = 0, /* FrozenWeight::F32 (src/frozen.rs:33-38); also what norms, biases and rope_freqs are */
   RT_GGML_F16 = 1,
   RT_GGML_Q4_0 = 2,
   RT_GGML_Q8_0 = 8,
@@ -94,6 +95,11 @@ size_t rt_ggml_nbytes(int ggml_type, size_t rows, size_t cols);
  * GGUF file, rows of ggml blocks. */
 rt_status rt_frozen_create(rt_ctx* ctx, int ggml_type, size_t rows, size_t cols, const void* packed_host,
                            size_t nbytes, rt_frozen** out);
+/* FrozenWeight::Q8_0 (src/frozen.rs:39-73), the trainer's own 8-bit storage: one f32 scale per
+ * 32 columns (scales_host, rows*cols/32 values, row-major) and signed bytes (qs_host, rows*cols).
+ * Not ggml's Q8_0 block, whose scale is f16.  row() returns scale*q exactly as the reference's. */
+rt_status rt_frozen_create_q8_0(rt_ctx* ctx, size_t rows, size_t cols, const float* scales_host,
+                                const int8_t* qs_host, rt_frozen** out);
 void rt_frozen_destroy(rt_frozen* w);
 /* FrozenMatmul::out_dim / in_dim / nbytes (src/frozen.rs:15-16,24). nbytes is the ggml size. */
 size_t rt_frozen_out_dim(const rt_frozen* w);
@@ -137,6 +143,55 @@ rt_status rt_frozen_backward_input_dev(rt_frozen* w, const void* dy_dev, int in_
  *     overlap on the GPU (different streams) race on it, so keep them on one stream. */
 rt_status rt_frozen_backward_input_dev_noalloc(rt_frozen* w, const void* dy_dev, int in_dtype, size_t t,
                                                void* dx_dev, int out_dtype, int accumulate);
+
+/* ------------------------------------------------------------------ op level: src/ops.rs, src/attention.rs
+ * The device kernels of the per-row operations and of the attention core, one operation per call
+ * with HOST buffers (copy in, launch, copy out, synchronise).  The training step never calls
+ * these: it chains the same kernels on the device.  They are for checking one operation against
+ * the CPU path.  Activations that feed a matmul leave the kernels as f16 (gradients: f16 rows
+ * times one f32 factor per row), which is what the f32 results returned here were rounded to. */
+
+/* rmsnorm (src/ops.rs:8-35): y[rows x d] = x * inv_rms(x) * w. */
+rt_status rt_op_rmsnorm(rt_ctx* ctx, const float* x_host, const float* w_host, size_t rows, size_t d, float eps,
+                        float* y_host);
+/* rmsnorm_backward (src/ops.rs:39-56): dx from dy; the weight has no gradient (frozen). */
+rt_status rt_op_rmsnorm_backward(rt_ctx* ctx, const float* x_host, const float* w_host, const float* dy_host, size_t rows,
+                                 size_t d, float eps, float* dx_host);
+/* What Attention::forward does between the projections and the scores (src/attention.rs:170-185):
+ * per-head RMSNorm of q and k with the fused-scale rounding order (weights NULL: none), RoPE at
+ * `positions` (Rope::with / at_positions / apply, src/ops.rs:99-184; NEOX pairs (i, i+rot/2) or
+ * interleaved pairs; `factors` = rope_freqs divisors or NULL), then rounding to f16, which is the
+ * reference's f16 K/V view for k and v.  q [M x nh x hd], k, v [M x nkv x hd]. */
+rt_status rt_op_qk_norm_rope(rt_ctx* ctx, const float* q_raw_host, const float* k_raw_host, const float* v_raw_host,
+                             const int32_t* positions, size_t M, int nh, int nkv, int hd, int rot, int neox, float theta,
+                             float freq_scale, const float* factors, int n_factors, const float* q_norm_w,
+                             const float* k_norm_w, float eps, float* q_host, float* k_host, float* v_host);
+/* Its backward (src/attention.rs:330-358): inverse rotation, then the norm's backward. */
+rt_status rt_op_qk_norm_rope_backward(rt_ctx* ctx, const float* dq_host, const float* dk_host, const float* dv_host,
+                                      const float* q_raw_host, const float* k_raw_host, const int32_t* positions,
+                                      size_t M, int nh, int nkv, int hd, int rot, int neox, float theta, float freq_scale,
+                                      const float* factors, int n_factors, const float* q_norm_w, const float* k_norm_w,
+                                      float eps, float* dq_raw_host, float* dk_raw_host, float* dv_host_out);
+/* The attention core (src/attention.rs:187-230): causal softmax(q.k^T / sqrt(hd)).v per head with
+ * grouped KV heads, over a concatenation of sequences (row i sees keys seq_start[i] .. i).
+ * lse_host (optional) is [nh x M]. */
+rt_status rt_op_attention(rt_ctx* ctx, const float* q_host, const float* k_host, const float* v_host,
+                          const int32_t* seq_start, size_t M, int nh, int nkv, int hd, float* o_host, float* lse_host);
+/* Its backward (src/attention.rs:246-329): dq, dk, dv from d(o), the KV gradients summed over the
+ * query heads of a group. */
+rt_status rt_op_attention_backward(rt_ctx* ctx, const float* q_host, const float* k_host, const float* v_host,
+                                   const float* do_host, const int32_t* seq_start, size_t M, int nh, int nkv, int hd,
+                                   float* dq_host, float* dk_host, float* dv_host);
+/* Mlp's activation (src/model.rs:113-134, src/tensor.rs:122-143): h = silu(gate) * up and its backward. */
+rt_status rt_op_swiglu(rt_ctx* ctx, const float* gate_host, const float* up_host, size_t rows, size_t ff, float* h_host);
+rt_status rt_op_swiglu_backward(rt_ctx* ctx, const float* gate_host, const float* up_host, const float* dh_host, size_t rows,
+                                size_t ff, float* dgate_host, float* dup_host);
+/* The head's per-row arithmetic (src/model.rs:579-596 over softmax_row, src/ops.rs:238-247): log-
+ * probability of the target with an f64 normaliser, hit count (no logit above the target's),
+ * optionally the argmax (last index on ties) and dlogits = w * (p - onehot). */
+rt_status rt_op_cross_entropy(rt_ctx* ctx, const float* logits_host, size_t rows, size_t vocab, const int32_t* target,
+                              const float* weight, float* logp_host, int32_t* hits_out, int32_t* argmax_host,
+                              float* dlogits_host);
 
 /* ------------------------------------------------------------------ level 2: struct Linear / struct Lora
  * src/linear.rs:9-122.  y = W.x + b + (alpha/r).B.A.x forward; dx = W^T.dy + (LoRA term) and
@@ -242,6 +297,14 @@ rt_status rt_model_forward_backward_layout(rt_model* m, const int32_t* tokens, c
 rt_status rt_model_score_layout(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
                                 const int32_t* positions, const int32_t* segments, const int32_t* target_pos,
                                 const int32_t* target_tok, int32_t n_targets, float* logp_out, int32_t* hits_out);
+/* greedy_prefix / greedy_prefix_batch (src/eval.rs:156-221): the greedy token, i.e. the argmax of
+ * the logits (the last index on ties, as the reference's max_by gives), at each target position
+ * of one forward-only pass.  positions / segments are NULL for plain sequences or describe
+ * Packed groups as in rt_model_score_layout.  The caller counts, per example, how many leading
+ * answer positions reproduce the example's tokens. */
+rt_status rt_model_argmax_layout(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
+                                 const int32_t* positions, const int32_t* segments, const int32_t* target_pos,
+                                 int32_t n_targets, int32_t* argmax_out);
 /* The same step split for hosts that keep the batch on the device: stage copies tokens,
  * targets and weights to HBM once; run_staged does the forward + backward (backward != 0) or
  * the forward alone on the staged batch without touching host memory; read_results copies the
@@ -261,6 +324,27 @@ int32_t rt_model_checkpointing(const rt_model* m);
 /* The flat f32 gradient buffer on the device, [A_0 | B_0 | A_1 | B_1 ...] in parameter order:
  * what a data-parallel host all-reduces (sum) across ranks before rt_optim_step. */
 rt_status rt_model_grad_buffer(rt_model* m, void** grads_dev_out, size_t* n_floats_out);
+/* ------------------------------------------------------------------ data parallelism
+ * No counterpart in the reference (one process, one device; src/train.rs:339-351 accumulates a
+ * batch's examples one after the other).  Ranks hold replicas and take the batch's sequences in
+ * turn; each weights its targets with the GLOBAL 1/batch_tokens (src/train.rs:330), so the SUM of
+ * the ranks' gradient buffers is the batch gradient.  One NCCL communicator per ctx:
+ *   rank 0: rt_comm_unique_id(id) and hands the 128 bytes to the other ranks by any means;
+ *   every rank: rt_comm_init_rank(ctx, nranks, rank, id)   (collective: all ranks call it);
+ *   per step: forward_backward ... ; rt_model_allreduce_grads(m); rt_optim_step(m, ...).
+ * The all-reduce runs on the ctx stream, in place, asynchronously.  Without a communicator (a
+ * world of one) it does nothing.  Failures are RT_ERR_NCCL with the library's message. */
+#define RT_COMM_ID_BYTES 128
+rt_status rt_comm_unique_id(uint8_t* id_out, size_t id_bytes);
+rt_status rt_comm_init_rank(rt_ctx* ctx, int nranks, int rank, const uint8_t* id, size_t id_bytes);
+rt_status rt_comm_destroy(rt_ctx* ctx);
+int rt_comm_size(const rt_ctx* ctx);
+int rt_comm_rank(const rt_ctx* ctx);
+/* Sum over ranks, in place, of n floats in device memory (the loss, a token count, ...). */
+rt_status rt_comm_allreduce_f32(rt_ctx* ctx, float* buf_dev, size_t n);
+/* Sum over ranks of the flat LoRA-gradient buffer (rt_model_grad_buffer). */
+rt_status rt_model_allreduce_grads(rt_model* m);
+
 /* clip_grad_norm (src/optim.rs:73-90) followed by AdamW::step (src/optim.rs:48-69) on the
  * device; returns the pre-clip gradient norm. */
 rt_status rt_optim_step(rt_model* m, float lr, float max_norm, float beta1, float beta2, float eps,

@@ -108,6 +108,17 @@ static float silu_gradf(float x) {
   return s * (1.0f + x * (1.0f - s));
 }
 
+/* Mlp's activation, model.rs:113-134 */
+void orc_swiglu(const float* g, const float* u, size_t n, float* h) {
+  for (size_t i = 0; i < n; ++i) h[i] = siluf(g[i]) * u[i];
+}
+void orc_swiglu_backward(const float* g, const float* u, const float* dh, size_t n, float* dg, float* du) {
+  for (size_t i = 0; i < n; ++i) {
+    dg[i] = dh[i] * u[i] * silu_gradf(g[i]);
+    du[i] = dh[i] * siluf(g[i]);
+  }
+}
+
 /* ------------------------------------------------------------------ ggml block decode
  * Weight::dequant_row at the call sites src/rie.rs:97,123. */
 size_t orc_row_bytes(int type, int cols) {
@@ -204,10 +215,36 @@ void orc_frozen_row(const orc_frozen* w, int r, float* out) {
   orc_dequant_row(w->type, w->data + (size_t)r * w->row_bytes, w->cols, out);
 }
 
-/* rie.rs:74-82 forward, "smooth" mode: y[t x rows] = x[t x cols] . W^T from dequantised rows
- * (the engine's int8 activation rounding is not restated; the reference's own backward ignores it). */
+/* Mode (ii), "engine-like": rie.rs:77-80 hands x to QuantActs::prepare before kernels::matmul, i.e.
+ * the engine rounds the activations to 8 bits per block before every QUANTISED forward matmul
+ * (the backward is straight-through f32).  Which activation format formats_for picks per weight
+ * type is not in the tree (rie-core is absent); this switch applies the two ggml conventions:
+ * blocks of 32 (Q8_0-style: d = amax/127, round to nearest) for Q8_0 / Q4_0 weights, blocks of 256
+ * (Q8_K-style: d = amax/127) for the K-quants.  Informative only: it bounds how much of the GPU
+ * path's distance from the reference that rounding can explain.  Off by default (mode (i)). */
+static int g_act_int8 = 0;
+void orc_set_act_int8(int on) { g_act_int8 = on; }
+static void round_acts_int8(const float* x, int n, int block, float* out) {
+  for (int b = 0; b < n; b += block) {
+    int len = n - b < block ? n - b : block;
+    float amax = 0;
+    for (int i = 0; i < len; ++i) { float a = fabsf(x[b + i]); amax = a > amax ? a : amax; }
+    float d = amax / 127.0f, id = d > 0 ? 1.0f / d : 0.0f;
+    for (int i = 0; i < len; ++i) out[b + i] = nearbyintf(x[b + i] * id) * d;
+  }
+}
+
+/* rie.rs:74-82 forward: y[t x rows] = x[t x cols] . W^T from dequantised rows.  Mode (i) "smooth"
+ * (the default) leaves x in f32, as the reference's own backward assumes; mode (ii) rounds it. */
 void orc_frozen_forward(const orc_frozen* w, const float* x, int t, float* y) {
   const int R = w->rows, K = w->cols;
+  float* xq = NULL;
+  if (g_act_int8 && (w->type == T_Q8_0 || w->type == T_Q4_0 || w->type == T_Q4_K || w->type == T_Q6_K)) {
+    const int block = (w->type == T_Q4_K || w->type == T_Q6_K) ? 256 : 32;
+    xq = (float*)malloc((size_t)t * K * sizeof(float));
+    for (int ti = 0; ti < t; ++ti) round_acts_int8(x + (size_t)ti * K, K, block, xq + (size_t)ti * K);
+    x = xq;
+  }
 #pragma omp parallel
   {
     float* buf = (float*)malloc((size_t)K * sizeof(float));
@@ -218,6 +255,7 @@ void orc_frozen_forward(const orc_frozen* w, const float* x, int t, float* y) {
     }
     free(buf);
   }
+  free(xq);
 }
 
 /* rie.rs:84-120 backward_input: dx[t x cols] += dy[t x rows] . W, 32 rows dequantised at a time
@@ -436,6 +474,88 @@ typedef struct {
 
 static float* falloc(size_t n) { return (float*)calloc(n ? n : 1, sizeof(float)); }
 
+/* attention.rs:187-230: the scores, softmax and P.V of every head.  q [t x nh x hd], k, v
+ * [t x nkv x hd]; probs [nh x t x t] (zero where masked); o [t x nh x hd] must come in zeroed. */
+void orc_attn_core_forward(const float* q, const float* k, const float* v, int t, int nh, int nkv, int hd,
+                           const int* seg_start, float* probs, float* o) {
+  const float scale = 1.0f / sqrtf((float)hd);
+  const int group = nh / nkv;
+#pragma omp parallel for schedule(dynamic)
+  for (int h = 0; h < nh; ++h) {
+    int g = h / group;
+    float* qs = (float*)malloc((size_t)hd * sizeof(float));
+    for (int i = 0; i < t; ++i) {
+      const float* qi = q + ((size_t)i * nh + h) * hd;
+      for (int d = 0; d < hd; ++d) qs[d] = qi[d] * scale;
+      float* row = probs + ((size_t)h * t + i) * t;
+      float m = -INFINITY;
+      int j0 = seg_start ? seg_start[i] : 0;
+      for (int j = j0; j <= i; ++j) {
+        row[j] = dotf(qs, k + ((size_t)j * nkv + g) * hd, hd);
+        m = row[j] > m ? row[j] : m;
+      }
+      float s = 0;
+      for (int j = j0; j <= i; ++j) { row[j] = expf(row[j] - m); s += row[j]; }
+      float inv = 1.0f / s;
+      float* oi = o + ((size_t)i * nh + h) * hd;
+      for (int j = j0; j <= i; ++j) {
+        row[j] *= inv;
+        axpyf(row[j], v + ((size_t)j * nkv + g) * hd, oi, hd);
+      }
+    }
+    free(qs);
+  }
+}
+
+/* attention.rs:246-329: dq [t x nh x hd], dk, dv [t x nkv x hd] (all zeroed on entry) from d_o and
+ * the forward's probabilities; the KV gradients are summed over the query heads of a group. */
+void orc_attn_core_backward(const float* q, const float* k, const float* v, const float* probs, const float* d_o, int t,
+                            int nh, int nkv, int hd, const int* seg_start, float* dq, float* dk, float* dv) {
+  const float scale = 1.0f / sqrtf((float)hd);
+  const int group = nh / nkv;
+  float* dkh = falloc((size_t)nh * t * hd);
+  float* dvh = falloc((size_t)nh * t * hd);
+#pragma omp parallel for schedule(dynamic)
+  for (int h = 0; h < nh; ++h) {
+    int g = h / group;
+    const float* p = probs + (size_t)h * t * t;
+    float* dp = (float*)malloc((size_t)t * sizeof(float));
+    float* dkl = dkh + (size_t)h * t * hd;
+    float* dvl = dvh + (size_t)h * t * hd;
+    for (int i = 0; i < t; ++i) {
+      const float* doi = d_o + ((size_t)i * nh + h) * hd;
+      int j0 = seg_start ? seg_start[i] : 0;
+      float sum = 0;
+      for (int j = j0; j <= i; ++j) {
+        dp[j] = dotf(doi, v + ((size_t)j * nkv + g) * hd, hd);
+        float pij = p[(size_t)i * t + j];
+        sum += pij * dp[j];
+        for (int d = 0; d < hd; ++d) dvl[(size_t)j * hd + d] += pij * doi[d];
+      }
+      const float* qi = q + ((size_t)i * nh + h) * hd;
+      float* dqi = dq + ((size_t)i * nh + h) * hd;
+      for (int j = j0; j <= i; ++j) {
+        float ds = p[(size_t)i * t + j] * (dp[j] - sum) * scale;
+        if (ds == 0.0f) continue;
+        const float* kj = k + ((size_t)j * nkv + g) * hd;
+        for (int d = 0; d < hd; ++d) dqi[d] += ds * kj[d];
+        for (int d = 0; d < hd; ++d) dkl[(size_t)j * hd + d] += ds * qi[d];
+      }
+    }
+    free(dp);
+  }
+  for (int h = 0; h < nh; ++h) { /* GQA: sum over the group, attention.rs:320-328 */
+    int g = h / group;
+    for (int i = 0; i < t; ++i)
+      for (int d = 0; d < hd; ++d) {
+        dk[((size_t)i * nkv + g) * hd + d] += dkh[((size_t)h * t + i) * hd + d];
+        dv[((size_t)i * nkv + g) * hd + d] += dvh[((size_t)h * t + i) * hd + d];
+      }
+  }
+  free(dkh);
+  free(dvh);
+}
+
 /* attention.rs:162-244.  seg_start[i] = first position of the sequence token i belongs to:
  * the reference runs one sequence per call; a batch here is a concatenation of independent
  * sequences, token i attends to j in [seg_start[i], i]. */
@@ -466,35 +586,9 @@ void orc_attn_forward(const orc_attn* a, const float* x, int t, const orc_rope* 
   if (a->kv_f16) {
     for (size_t i = 0; i < (size_t)t * nkv * hd; ++i) { c->k[i] = orc_round_f16(c->k[i]); c->v[i] = orc_round_f16(c->v[i]); }
   }
-  const float scale = 1.0f / sqrtf((float)hd);
-  const int group = nh / nkv;
   c->probs = falloc((size_t)nh * t * t);
   c->o = falloc((size_t)t * nh * hd);
-#pragma omp parallel for schedule(dynamic)
-  for (int h = 0; h < nh; ++h) {
-    int g = h / group;
-    float* qs = (float*)malloc((size_t)hd * sizeof(float));
-    for (int i = 0; i < t; ++i) {
-      const float* qi = c->q + ((size_t)i * nh + h) * hd;
-      for (int d = 0; d < hd; ++d) qs[d] = qi[d] * scale;
-      float* row = c->probs + ((size_t)h * t + i) * t;
-      float m = -INFINITY;
-      int j0 = seg_start ? seg_start[i] : 0;
-      for (int j = j0; j <= i; ++j) {
-        row[j] = dotf(qs, c->k + ((size_t)j * nkv + g) * hd, hd);
-        m = row[j] > m ? row[j] : m;
-      }
-      float s = 0;
-      for (int j = j0; j <= i; ++j) { row[j] = expf(row[j] - m); s += row[j]; }
-      float inv = 1.0f / s;
-      float* oi = c->o + ((size_t)i * nh + h) * hd;
-      for (int j = j0; j <= i; ++j) {
-        row[j] *= inv;
-        axpyf(row[j], c->v + ((size_t)j * nkv + g) * hd, oi, hd);
-      }
-    }
-    free(qs);
-  }
+  orc_attn_core_forward(c->q, c->k, c->v, t, nh, nkv, hd, seg_start, c->probs, c->o);
   orc_linear_forward(&a->o, c->o, t, y);
 }
 
@@ -509,52 +603,10 @@ void orc_attn_backward(orc_attn* a, orc_attn_cache* c, const float* dy, int t, c
   const int nh = a->n_heads, nkv = a->n_kv_heads, hd = a->head_dim, hidden = a->q.w.cols;
   float* d_o = falloc((size_t)t * nh * hd);
   orc_linear_backward(&a->o, c->o, dy, t, d_o);
-  const float scale = 1.0f / sqrtf((float)hd);
-  const int group = nh / nkv;
   float* dq = falloc((size_t)t * nh * hd);
   float* dk = falloc((size_t)t * nkv * hd);
   float* dv = falloc((size_t)t * nkv * hd);
-  float* dkh = falloc((size_t)nh * t * hd);
-  float* dvh = falloc((size_t)nh * t * hd);
-#pragma omp parallel for schedule(dynamic)
-  for (int h = 0; h < nh; ++h) {
-    int g = h / group;
-    const float* p = c->probs + (size_t)h * t * t;
-    float* dp = (float*)malloc((size_t)t * sizeof(float));
-    float* dkl = dkh + (size_t)h * t * hd;
-    float* dvl = dvh + (size_t)h * t * hd;
-    for (int i = 0; i < t; ++i) {
-      const float* doi = d_o + ((size_t)i * nh + h) * hd;
-      int j0 = seg_start ? seg_start[i] : 0;
-      float sum = 0;
-      for (int j = j0; j <= i; ++j) {
-        dp[j] = dotf(doi, c->v + ((size_t)j * nkv + g) * hd, hd);
-        float pij = p[(size_t)i * t + j];
-        sum += pij * dp[j];
-        for (int d = 0; d < hd; ++d) dvl[(size_t)j * hd + d] += pij * doi[d];
-      }
-      const float* qi = c->q + ((size_t)i * nh + h) * hd;
-      float* dqi = dq + ((size_t)i * nh + h) * hd;
-      for (int j = j0; j <= i; ++j) {
-        float ds = p[(size_t)i * t + j] * (dp[j] - sum) * scale;
-        if (ds == 0.0f) continue;
-        const float* kj = c->k + ((size_t)j * nkv + g) * hd;
-        for (int d = 0; d < hd; ++d) dqi[d] += ds * kj[d];
-        for (int d = 0; d < hd; ++d) dkl[(size_t)j * hd + d] += ds * qi[d];
-      }
-    }
-    free(dp);
-  }
-  for (int h = 0; h < nh; ++h) { /* GQA: sum over the group, attention.rs:320-328 */
-    int g = h / group;
-    for (int i = 0; i < t; ++i)
-      for (int d = 0; d < hd; ++d) {
-        dk[((size_t)i * nkv + g) * hd + d] += dkh[((size_t)h * t + i) * hd + d];
-        dv[((size_t)i * nkv + g) * hd + d] += dvh[((size_t)h * t + i) * hd + d];
-      }
-  }
-  free(dkh);
-  free(dvh);
+  orc_attn_core_backward(c->q, c->k, c->v, c->probs, d_o, t, nh, nkv, hd, seg_start, dq, dk, dv);
   orc_rope_apply(rope, dq, t, nh, hd, 1);
   orc_rope_apply(rope, dk, t, nkv, hd, 1);
   float *dq_raw = dq, *dk_raw = dk;
@@ -617,7 +669,7 @@ static void block_forward(const orc_block* b, const float* x, int t, int d, int 
   c->g = falloc((size_t)t * ff); c->u = falloc((size_t)t * ff); c->hm = falloc((size_t)t * ff);
   orc_linear_forward(&b->mlp.gate, c->n2, t, c->g);
   orc_linear_forward(&b->mlp.up, c->n2, t, c->u);
-  for (size_t i = 0; i < (size_t)t * ff; ++i) c->hm[i] = siluf(c->g[i]) * c->u[i];
+  orc_swiglu(c->g, c->u, (size_t)t * ff, c->hm);
   orc_linear_forward(&b->mlp.down, c->hm, t, m);
   for (size_t i = 0; i < (size_t)t * d; ++i) y[i] = c->h[i] + m[i];
   free(m);
@@ -633,10 +685,7 @@ static void block_backward(orc_block* b, orc_block_cache* c, const float* dy, in
   orc_linear_backward(&b->mlp.down, c->hm, dy, t, dhm);
   float* dg = falloc((size_t)t * ff);
   float* du = falloc((size_t)t * ff);
-  for (size_t i = 0; i < (size_t)t * ff; ++i) {
-    dg[i] = dhm[i] * c->u[i] * silu_gradf(c->g[i]);
-    du[i] = dhm[i] * siluf(c->g[i]);
-  }
+  orc_swiglu_backward(c->g, c->u, dhm, (size_t)t * ff, dg, du);
   float* dn2 = falloc((size_t)t * d);
   float* dxu = falloc((size_t)t * d);
   orc_linear_backward(&b->mlp.gate, c->n2, dg, t, dn2);

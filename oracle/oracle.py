@@ -20,6 +20,12 @@ F32P = C.POINTER(C.c_float)
 I32P = C.POINTER(C.c_int)
 
 
+class _Rope(C.Structure):
+    """struct orc_rope of oracle.c."""
+
+    _fields_ = [("rot_dim", C.c_int), ("neox", C.c_int), ("t", C.c_int), ("cos", F32P), ("sin", F32P)]
+
+
 def _host_tag() -> str:
     """Identifies the CPU the library was built for (-march=native code must not travel)."""
     try:
@@ -93,6 +99,16 @@ def lib() -> C.CDLL:
         L.orc_linear_forward_raw.argtypes = [C.c_int] * 3 + [C.c_void_p, F32P, C.c_int, C.c_float, F32P, F32P, F32P, C.c_int, F32P]
         L.orc_linear_backward_raw.argtypes = [C.c_int] * 3 + [C.c_void_p, C.c_int, C.c_float] + [F32P] * 6 + [C.c_int, F32P]
         L.orc_num_threads.restype = C.c_int
+        L.orc_set_act_int8.argtypes = [C.c_int]
+        L.orc_rmsnorm.argtypes = [F32P, F32P, C.c_int, C.c_int, C.c_float, C.c_int, F32P, F32P]
+        L.orc_rmsnorm_backward.argtypes = [F32P, F32P, F32P, F32P, C.c_int, C.c_int, F32P]
+        L.orc_rope_init.argtypes = [C.POINTER(_Rope), I32P, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, F32P, C.c_int]
+        L.orc_rope_free.argtypes = [C.POINTER(_Rope)]
+        L.orc_rope_apply.argtypes = [C.POINTER(_Rope), F32P, C.c_int, C.c_int, C.c_int, C.c_int]
+        L.orc_attn_core_forward.argtypes = [F32P, F32P, F32P, C.c_int, C.c_int, C.c_int, C.c_int, I32P, F32P, F32P]
+        L.orc_attn_core_backward.argtypes = [F32P] * 5 + [C.c_int] * 4 + [I32P] + [F32P] * 3
+        L.orc_swiglu.argtypes = [F32P, F32P, C.c_size_t, F32P]
+        L.orc_swiglu_backward.argtypes = [F32P, F32P, F32P, C.c_size_t, F32P, F32P]
         _lib = L
     return _lib
 
@@ -166,6 +182,79 @@ def softmax_row(logits: np.ndarray):
     p = np.empty_like(logits)
     lse = lib().orc_softmax_row(fp(logits), logits.size, fp(p))
     return float(lse), p
+
+
+def set_act_int8(on: bool) -> None:
+    """Mode (ii) of the oracle: round activations to 8 bits per block before every quantised
+    forward matmul, as the engine does (src/rie.rs:77-80).  Process-wide; off by default."""
+    lib().orc_set_act_int8(int(on))
+
+
+def rmsnorm(x, w, eps, fused_scale=False):
+    """ops.rs:8-35; returns (y, inv_rms per row)."""
+    x, w = _f32(x), _f32(w)
+    rows, d = x.shape
+    y, inv = np.empty_like(x), np.empty(rows, np.float32)
+    lib().orc_rmsnorm(fp(x), fp(w), rows, d, eps, int(fused_scale), fp(y), fp(inv))
+    return y, inv
+
+
+def rmsnorm_backward(x, w, inv, dy):
+    x, w, inv, dy = _f32(x), _f32(w), _f32(inv), _f32(dy)
+    rows, d = x.shape
+    dx = np.empty_like(x)
+    lib().orc_rmsnorm_backward(fp(x), fp(w), fp(inv), fp(dy), rows, d, fp(dx))
+    return dx
+
+
+def rope_apply(x, positions, rot_dim, neox, base, freq_scale=1.0, factors=None, inverse=False):
+    """Rope::at_positions + Rope::apply (ops.rs:112-184) on x [t x heads x head_dim]; returns a copy."""
+    x = _f32(x).copy()
+    t, heads, hd = x.shape
+    pos = np.ascontiguousarray(positions, dtype=np.int32)
+    f = None if factors is None else _f32(factors)
+    r = _Rope()
+    lib().orc_rope_init(C.byref(r), ip(pos), t, rot_dim, int(bool(neox)), base, freq_scale, fp(f), 0 if f is None else f.size)
+    lib().orc_rope_apply(C.byref(r), fp(x), t, heads, hd, int(inverse))
+    lib().orc_rope_free(C.byref(r))
+    return x
+
+
+def attn_core_forward(q, k, v, seq_start):
+    """attention.rs:187-230; q [t x nh x hd], k, v [t x nkv x hd]; returns (o, probs [nh x t x t])."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    t, nh, hd = q.shape
+    nkv = k.shape[1]
+    ss = np.ascontiguousarray(seq_start, dtype=np.int32)
+    probs = np.zeros((nh, t, t), np.float32)
+    o = np.zeros_like(q)
+    lib().orc_attn_core_forward(fp(q), fp(k), fp(v), t, nh, nkv, hd, ip(ss), fp(probs), fp(o))
+    return o, probs
+
+
+def attn_core_backward(q, k, v, probs, d_o, seq_start):
+    """attention.rs:246-329; returns (dq, dk, dv)."""
+    q, k, v, probs, d_o = _f32(q), _f32(k), _f32(v), _f32(probs), _f32(d_o)
+    t, nh, hd = q.shape
+    nkv = k.shape[1]
+    ss = np.ascontiguousarray(seq_start, dtype=np.int32)
+    dq, dk, dv = np.zeros_like(q), np.zeros_like(k), np.zeros_like(v)
+    lib().orc_attn_core_backward(fp(q), fp(k), fp(v), fp(probs), fp(d_o), t, nh, nkv, hd, ip(ss), fp(dq), fp(dk), fp(dv))
+    return dq, dk, dv
+
+
+def swiglu(g, u):
+    g, u = _f32(g), _f32(u)
+    h = np.empty_like(g)
+    lib().orc_swiglu(fp(g), fp(u), g.size, fp(h))
+    return h
+
+
+def swiglu_backward(g, u, dh):
+    g, u, dh = _f32(g), _f32(u), _f32(dh)
+    dg, du = np.empty_like(g), np.empty_like(g)
+    lib().orc_swiglu_backward(fp(g), fp(u), fp(dh), g.size, fp(dg), fp(du))
+    return dg, du
 
 
 class Rng:

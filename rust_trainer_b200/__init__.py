@@ -1,5 +1,5 @@
 """B200-native frozen-quantised-linear LoRA training path (host-side mirror over a C ABI)."""
-from . import adapter, dp, objectives, packing, quants, synth  # noqa: F401
+from . import adapter, dp, evalgate, objectives, ops, packing, quants, synth  # noqa: F401
 from ._lib import RtError, lib  # noqa: F401
 from .frozen import Context, Frozen  # noqa: F401
 from .linear import Linear  # noqa: F401

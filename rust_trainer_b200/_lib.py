@@ -114,6 +114,30 @@ def _declare(L: C.CDLL) -> None:
         "rt_optim_state_read": (i32, [vp, C.POINTER(u64), f32p, f32p]),
         "rt_optim_state_write": (i32, [vp, u64, f32p, f32p]),
     })
+    i8p, u8p = C.POINTER(C.c_int8), C.POINTER(C.c_uint8)
+    ci, cf = C.c_int, C.c_float
+    sig.update({
+        "rt_frozen_create_q8_0": (i32, [vp, sz, sz, f32p, i8p, C.POINTER(vp)]),
+        "rt_model_argmax_layout": (i32, [vp, i32p, i32p, i32, i32p, i32p, i32p, i32, i32p]),
+        "rt_comm_unique_id": (i32, [u8p, sz]),
+        "rt_comm_init_rank": (i32, [vp, ci, ci, u8p, sz]),
+        "rt_comm_destroy": (i32, [vp]),
+        "rt_comm_size": (ci, [vp]),
+        "rt_comm_rank": (ci, [vp]),
+        "rt_comm_allreduce_f32": (i32, [vp, vp, sz]),
+        "rt_model_allreduce_grads": (i32, [vp]),
+        "rt_op_rmsnorm": (i32, [vp, f32p, f32p, sz, sz, cf, f32p]),
+        "rt_op_rmsnorm_backward": (i32, [vp, f32p, f32p, f32p, sz, sz, cf, f32p]),
+        "rt_op_qk_norm_rope": (i32, [vp, f32p, f32p, f32p, i32p, sz, ci, ci, ci, ci, ci, cf, cf, f32p, ci, f32p, f32p, cf,
+                                     f32p, f32p, f32p]),
+        "rt_op_qk_norm_rope_backward": (i32, [vp, f32p, f32p, f32p, f32p, f32p, i32p, sz, ci, ci, ci, ci, ci, cf, cf, f32p, ci,
+                                              f32p, f32p, cf, f32p, f32p, f32p]),
+        "rt_op_attention": (i32, [vp, f32p, f32p, f32p, i32p, sz, ci, ci, ci, f32p, f32p]),
+        "rt_op_attention_backward": (i32, [vp, f32p, f32p, f32p, f32p, i32p, sz, ci, ci, ci, f32p, f32p, f32p]),
+        "rt_op_swiglu": (i32, [vp, f32p, f32p, sz, sz, f32p]),
+        "rt_op_swiglu_backward": (i32, [vp, f32p, f32p, f32p, sz, sz, f32p, f32p]),
+        "rt_op_cross_entropy": (i32, [vp, f32p, sz, sz, i32p, f32p, f32p, i32p, i32p, f32p]),
+    })
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
         fn.restype = res

@@ -6,6 +6,7 @@
 #include <string.h>
 #include <map>
 #include <string>
+#include <vector>
 
 void* rt_ctx::get_scratch(int slot, size_t bytes) {
   if (bytes <= scratch_bytes[slot]) return scratch[slot];
@@ -36,6 +37,21 @@ rt_status rt_ctx::check_device_status(const char* where) {
   return RT_ERR_DEVICE_WAIT_TIMEOUT;
 }
 
+namespace rt {
+int frozen_matmul_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
+  int rc = qgemm_launch(ctx, w, a);
+  if (rc || !w.dense16_lo || a.out_dtype != OUT_F32 || a.tok_mode) return rc;
+  QWeight lo = w;
+  lo.dense16 = w.dense16_lo;
+  lo.dense16_lo = nullptr;
+  QGemmArgs b = a;  // the low term adds into the result; bias and the adapter chunk went in with the high term
+  b.accumulate = 1;
+  b.bias = nullptr;
+  b.lora = LoraSide();
+  return qgemm_launch(ctx, lo, b);
+}
+}  // namespace rt
+
 extern "C" {
 
 rt_status rt_ctx_create(int device, rt_ctx** out) {
@@ -58,6 +74,7 @@ rt_status rt_ctx_create(int device, rt_ctx** out) {
   c->stream = c->own_stream;
   if (e == cudaSuccess) e = cudaMalloc(&c->status_dev, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(c->status_dev, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();  // the clear ran on the legacy stream; own_stream does not wait for it
   if (e == cudaSuccess) e = cudaMallocHost(&c->status_host, sizeof(int));
   if (e != cudaSuccess || rt::qgemm_init() != RT_OK) {
     fprintf(stderr, "rt_b200: context creation failed: %s\n", cudaGetErrorString(e));
@@ -73,6 +90,7 @@ void rt_ctx_destroy(rt_ctx* c) {
   if (!c) return;
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
+  rt_comm_destroy(c);
   for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
   for (int i = 0; i < 4; ++i)
     if (c->scratch[i]) cudaFree(c->scratch[i]);
@@ -141,15 +159,51 @@ rt_status rt_ctx_profile_read(rt_ctx* c, uint64_t* n, double* ms, double* flops,
 void* rt_ctx_stream(rt_ctx* c) { return c ? (void*)c->stream : nullptr; }
 
 size_t rt_ggml_nbytes(int t, size_t rows, size_t cols) {
+  if (t == RT_GGML_F32) return rows * cols * 4;
   int be = rt::fmt_block_elems(t), bb = rt::fmt_block_bytes(t);
   if (bb == 0 || cols % be != 0) return 0;
   return rows * (cols / be) * bb;
+}
+
+// FrozenWeight::F32 (src/frozen.rs:33-52): the f32 matrix stays on the device for row(), and its
+// two-term f16 split feeds the tensor cores.
+static rt_status frozen_create_f32(rt_ctx* c, size_t rows, size_t cols, const float* w_host, size_t nbytes, rt_frozen** out) {
+  if (rows == 0 || cols == 0 || rows > (1u << 30) || cols > (1u << 30)) return c->fail(RT_ERR_BAD_SHAPE, "empty or oversized weight");
+  if (cols % 8 != 0) return c->fail(RT_ERR_BAD_SHAPE, "f32 rows must be a multiple of 8 long");
+  if (nbytes != rows * cols * 4) return c->fail(RT_ERR_BAD_SHAPE, "nbytes does not match type and shape");
+  RT_CUDA(c, cudaSetDevice(c->device));
+  rt_frozen* f = new rt_frozen();
+  f->ctx = c;
+  rt::QWeight& w = f->w;
+  w.fmt = rt::GGML_F16;
+  w.rows = (int)rows;
+  w.cols = (int)cols;
+  w.ggml_nbytes = nbytes;
+  w.dev_nbytes = rows * cols * 2;
+  float* w32 = nullptr;
+  cudaError_t e = cudaMalloc(&w32, nbytes);
+  w.f32 = w32;
+  if (e == cudaSuccess) e = cudaMalloc(&w.dense16, rows * cols * 2);
+  if (e == cudaSuccess) e = cudaMalloc(&w.dense16_lo, rows * cols * 2);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(w32, w_host, nbytes, cudaMemcpyHostToDevice, c->stream);
+  if (e == cudaSuccess) {
+    rt::launch_split_f32_hi_lo(w32, rows * cols, (__half*)w.dense16, (__half*)w.dense16_lo, c->stream);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+  if (e != cudaSuccess) {
+    rt_frozen_destroy(f);
+    return c->cuda_fail(e, "rt_frozen_create (f32)");
+  }
+  *out = f;
+  return RT_OK;
 }
 
 rt_status rt_frozen_create(rt_ctx* c, int ggml_type, size_t rows, size_t cols, const void* packed_host,
                            size_t nbytes, rt_frozen** out) {
   if (!c || !out || !packed_host) return RT_ERR_BAD_ARG;
   *out = nullptr;
+  if (ggml_type == RT_GGML_F32) return frozen_create_f32(c, rows, cols, (const float*)packed_host, nbytes, out);
   if (rt::fmt_block_bytes(ggml_type) == 0) return c->fail(RT_ERR_UNSUPPORTED_TYPE, "unsupported ggml tensor type");
   if (rows == 0 || cols == 0 || rows > (1u << 30) || cols > (1u << 30)) return c->fail(RT_ERR_BAD_SHAPE, "empty or oversized weight");
   const int be = rt::fmt_block_elems(ggml_type);
@@ -193,6 +247,21 @@ rt_status rt_frozen_create(rt_ctx* c, int ggml_type, size_t rows, size_t cols, c
   return RT_OK;
 }
 
+// FrozenWeight::Q8_0 (src/frozen.rs:39-73): f32 scale per 32 columns + signed bytes.  The scale is
+// f32, which ggml's Q8_0 block (f16 scale) cannot hold, so the values d*q go through the f32
+// storage above: q is exact in f16 and d*q splits into two f16 terms like any f32 weight.
+rt_status rt_frozen_create_q8_0(rt_ctx* c, size_t rows, size_t cols, const float* scales_host, const int8_t* qs_host,
+                                rt_frozen** out) {
+  if (!c || !out || !scales_host || !qs_host) return RT_ERR_BAD_ARG;
+  *out = nullptr;
+  if (rows == 0 || cols == 0 || cols % 32 != 0) return c->fail(RT_ERR_BAD_SHAPE, "Q8_0 rows must be a multiple of 32 long");
+  std::vector<float> w(rows * cols);
+  for (size_t i = 0; i < rows * cols; ++i) w[i] = scales_host[i / 32] * (float)qs_host[i];
+  rt_status st = frozen_create_f32(c, rows, cols, w.data(), rows * cols * 4, out);
+  if (st == RT_OK) (*out)->w.ggml_nbytes = rows * cols / 32 * 4 + rows * cols;  // FrozenWeight::nbytes, src/frozen.rs:181-186
+  return st;
+}
+
 void rt_frozen_destroy(rt_frozen* f) {
   if (!f) return;
   cudaSetDevice(f->ctx->device);
@@ -200,6 +269,8 @@ void rt_frozen_destroy(rt_frozen* f) {
     if (f->w.bricks) cudaFree(f->w.bricks);
     if (f->w.dense16) cudaFree(f->w.dense16);
   }
+  if (f->w.dense16_lo) cudaFree(f->w.dense16_lo);
+  if (f->w.f32) cudaFree((void*)f->w.f32);
   delete f;
 }
 
@@ -234,7 +305,7 @@ static rt_status frozen_matmul_host(rt_frozen* f, int dir, const float* in_host,
   a.out = out_f32;
   a.out_dtype = rt::OUT_F32;
   a.accumulate = accumulate ? 1 : 0;
-  int rc = rt::qgemm_launch(c, f->w, a);
+  int rc = rt::frozen_matmul_launch(c, f->w, a);
   if (rc) return c->fail(rc, "qgemm launch failed");
   RT_CUDA(c, cudaMemcpyAsync(out_host, out_f32, t * out_dim * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
   return c->check_device_status("rt_frozen matmul");
@@ -266,7 +337,7 @@ static rt_status frozen_matmul_dev(rt_frozen* f, int dir, const void* in_dev, in
   a.out = out_dev;
   a.out_dtype = out_dtype;
   a.accumulate = accumulate ? 1 : 0;
-  int rc = rt::qgemm_launch(c, f->w, a);
+  int rc = rt::frozen_matmul_launch(c, f->w, a);
   if (rc) return c->fail(rc, "qgemm launch failed");
   return RT_OK;
 }

@@ -24,6 +24,9 @@ struct rt_ctx {
   std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t, bool>, CUtensorMap> tmap_cache;
   struct ProfRec { int cls, M, rows, contract; };  // cls: 0 fwd, 1 bwd, 2 skinny LoRA helper, 3 token contraction
   std::vector<ProfRec> prof_recs;
+  // data-parallel communicator (an ncclComm_t once rt_comm_init_rank has run; a world of one otherwise)
+  void* comm = nullptr;
+  int comm_ranks = 1, comm_rank = 0;
   // grow-only scratch buffers for the host-pointer entry points
   void* scratch[4] = {nullptr, nullptr, nullptr, nullptr};
   size_t scratch_bytes[4] = {0, 0, 0, 0};

@@ -15,7 +15,12 @@ bool DevBuf::reserve(size_t want, bool zero) {
   bytes = 0;
   if (cudaMalloc(&p, want) != cudaSuccess) return false;
   bytes = want;
-  if (zero) cudaMemset(p, 0, want);
+  if (zero) {
+    // the clear runs on the legacy stream, the kernels on the ctx's non-blocking stream: nothing
+    // else orders the two, so finish the clear before anyone can launch on the buffer
+    cudaMemset(p, 0, want);
+    cudaDeviceSynchronize();
+  }
   return true;
 }
 void DevBuf::release() {
@@ -43,9 +48,10 @@ rt_status lora_refresh(rt_linear* l) {
 
 // Hs / Gs are [M x 64] f16.  The low-rank chunk of the big matmul reads whole groups of 16
 // columns, so columns from `rank` up to the next multiple of 16 must hold zeros (or at least
-// finite values against zero weights; zeros keep it exact).  `cur_rank` remembers the widest
-// rank written since the last clear: the buffer is cleared only when stale columns would fall
-// inside the group the new rank reads.
+// finite values against zero weights; zeros keep it exact).  When the rank is not a multiple of
+// 16 the buffer is cleared on every call: a decision taken from what earlier calls left behind
+// would be frozen into a captured graph and replayed after a different history.  `cur_rank`
+// only records that the buffer has been cleared once since it was (re)allocated.
 static __half* lowrank_buf(rt_ctx* c, DevBuf& b, int& cur_rank, int M, int rank) {
   const size_t want = (size_t)M * 64 * sizeof(__half);
   bool clear = false;
@@ -53,14 +59,9 @@ static __half* lowrank_buf(rt_ctx* c, DevBuf& b, int& cur_rank, int M, int rank)
     if (!b.reserve(want + want / 2)) return nullptr;
     clear = true;
   }
-  const int read_to = (rank + 15) / 16 * 16;
-  if (cur_rank < 0 || (cur_rank > rank && rank < read_to)) clear = true;
-  if (clear) {
-    cudaMemsetAsync(b.p, 0, b.bytes, c->stream);
-    cur_rank = rank;
-  } else if (rank > cur_rank) {
-    cur_rank = rank;
-  }
+  if (cur_rank < 0 || rank % 16 != 0) clear = true;
+  if (clear) cudaMemsetAsync(b.p, 0, want, c->stream);
+  cur_rank = rank;
   return b.as<__half>();
 }
 
@@ -118,7 +119,7 @@ rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16,
     a.lora.w = l->lora.bp;
     a.lora.rank = r;
   }
-  int rc = qgemm_launch(c, l->w->w, a);
+  int rc = frozen_matmul_launch(c, l->w->w, a);
   if (rc) return c->fail(rc, "frozen forward matmul launch failed");
   return RT_OK;
 }
@@ -222,7 +223,7 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
     a.lora.w = l->lora.a_h;
     a.lora.rank = r;
   }
-  int rc = qgemm_launch(c, l->w->w, a);
+  int rc = frozen_matmul_launch(c, l->w->w, a);
   if (rc) return c->fail(rc, "frozen backward matmul launch failed");
   return RT_OK;
 }
@@ -658,6 +659,7 @@ void rt_model_destroy(rt_model* m) {
   for (DevBuf* b : bufs) b->release();
   for (int i = 0; i < 7; ++i) m->hs_keep[i].release();
   m->gap.release();
+  m->argmax.release();
   for (auto& ge : m->graphs) cudaGraphExecDestroy(ge.exec);
   delete m;
 }
@@ -765,7 +767,7 @@ static rt_status build_group(rt_model* m, LinGroup& g, rt_linear** lin, int n) {
   for (int i = 0; i < n; ++i) {
     g.lin[i] = lin[i];
     const QWeight& w = lin[i]->w->w;
-    if (w.fmt != w0.fmt || w.cols != w0.cols || w.rows % 128 != 0 || lin[i]->w->borrowed) return RT_OK;  // stays unstacked
+    if (w.fmt != w0.fmt || w.cols != w0.cols || w.rows % 128 != 0 || lin[i]->w->borrowed || w.f32) return RT_OK;  // stays unstacked
     g.row_off[i] = g.rows_total;
     g.rows_total += w.rows;
     bytes += w.dev_nbytes;
@@ -867,8 +869,10 @@ rt_status rt_model_attach_lora(rt_model* m, int rank, float alpha, const char* t
   if (!m->finalized) return c->fail(RT_ERR_BAD_ARG, "finalize the model first");
   if (rank <= 0 || rank > 64) return c->fail(RT_ERR_BAD_ARG, "LoRA rank must be in 1..64");
   RT_CUDA(c, cudaSetDevice(c->device));
-  bool sel[7];
-  for (int i = 0; i < 7; ++i) sel[i] = targets == nullptr;
+  // a target is a projection type (GGUF or HF short name: every layer's) or one module by its full
+  // GGUF name ("blk.3.attn_q"), which is how an adapter file names what it holds
+  const int NL = m->cfg.n_layers;
+  std::vector<char> sel((size_t)NL * 7, targets == nullptr ? 1 : 0);
   if (targets) {
     std::string t(targets);
     size_t p = 0;
@@ -876,21 +880,36 @@ rt_status rt_model_attach_lora(rt_model* m, int rank, float alpha, const char* t
       size_t e = t.find(',', p);
       if (e == std::string::npos) e = t.size();
       std::string tok = t.substr(p, e - p);
+      bool known = tok.empty();
       for (int i = 0; i < 7; ++i)
-        if (tok == LIN_NAMES[i] || tok == HF_NAMES[i]) sel[i] = true;
+        if (tok == LIN_NAMES[i] || tok == HF_NAMES[i]) {
+          for (int li = 0; li < NL; ++li) sel[(size_t)li * 7 + i] = 1;
+          known = true;
+        }
+      int li = -1, off = 0;
+      if (!known && sscanf(tok.c_str(), "blk.%d.%n", &li, &off) >= 1 && off > 0 && li >= 0 && li < NL)
+        for (int i = 0; i < 7; ++i)
+          if (tok.substr(off) == LIN_NAMES[i]) {
+            sel[(size_t)li * 7 + i] = 1;
+            known = true;
+          }
+      (void)known;  // a name that matches nothing is skipped, as Model::attach_lora does (its default list names DeltaNet projections too)
       p = e + 1;
     }
   }
   m->lora_order.clear();
   size_t total = 0;
-  for (auto& b : m->blocks)
+  for (int li = 0; li < NL; ++li) {
+    BlockDev& b = m->blocks[li];
     for (int i = 0; i < 7; ++i) {
       b.lin[i]->has_lora = false;
-      if (sel[i]) {
+      b.lin[i]->lora_enabled = true;
+      if (sel[(size_t)li * 7 + i]) {
         m->lora_order.push_back(b.lin[i]);
         total += (size_t)rank * (b.lin[i]->in_dim() + b.lin[i]->out_dim());
       }
     }
+  }
   m->n_params = total;
   if (total == 0) {
     for (auto& b : m->blocks) { build_group_lora(m, b.qkv); build_group_lora(m, b.gu); }
@@ -925,6 +944,9 @@ rt_status rt_model_attach_lora(rt_model* m, int rank, float alpha, const char* t
   m->opt_t = 0;
   for (int i = 0; i < 7; ++i)
     if (m->hs_keep[i].p) RT_CUDA(c, cudaMemset(m->hs_keep[i].p, 0, m->hs_keep[i].bytes));
+  // the copies and clears above went through the legacy stream; the first pass launches on the
+  // ctx's non-blocking stream, which nothing orders after them except this
+  RT_CUDA(c, cudaDeviceSynchronize());
   if (n_out) *n_out = total;
   return RT_OK;
 }
@@ -1056,13 +1078,15 @@ static bool ensure_targets(rt_model* m, int n, bool backward) {
     if (ok) m->cap_targets = n;
   }
   const int R = n < g.head_rows ? n : g.head_rows;
-  if (R > m->cap_head_rows || (backward && m->dl16.bytes == 0)) {
-    const size_t d = g.hidden, V = g.vocab;
+  const size_t d = g.hidden, V = g.vocab;
+  if (R > m->cap_head_rows) {
     ok &= m->xs.reserve((size_t)R * d * 4) && m->ns16.reserve((size_t)R * d * 2) && m->logits.reserve((size_t)R * V * 4);
     ok &= m->sc_l.reserve((size_t)R * 4) && m->dns.reserve((size_t)R * d * 4) && m->dxs.reserve((size_t)R * d * 4);
-    if (backward) ok &= m->dl16.reserve((size_t)R * V * 2);
-    if (ok && R > m->cap_head_rows) m->cap_head_rows = R;
+    if (ok) m->cap_head_rows = R;
   }
+  // the logit gradients exist only for backward passes and are sized on their own: a forward-only
+  // call may have raised cap_head_rows past what an earlier backward pass allocated here
+  if (backward) ok &= m->dl16.reserve((size_t)R * V * 2);
   return ok;
 }
 
@@ -1214,7 +1238,7 @@ static rt_status model_head(rt_model* m, int M, int n_targets, bool backward, fl
       RT_CUDA(c, cudaMemcpyAsync(logits_out_host + (size_t)c0 * V, m->logits.p, (size_t)R * V * 4, cudaMemcpyDeviceToHost, st));
     launch_ce_rows(m->logits.as<float>(), R, V, m->ttok.as<int>() + c0, m->tw.as<float>() + c0, m->logp.as<float>() + c0,
                    m->hits.as<int>(), backward ? m->dl16.as<__half>() : nullptr, backward ? m->sc_l.as<float>() : nullptr,
-                   c->status_dev, st);
+                   m->want_argmax ? m->argmax.as<int>() + c0 : nullptr, c->status_dev, st);
     if (backward) {
       RT_TRY(linear_backward_dev(&head, m->lsc, m->ns16.as<__half>(), m->dl16.as<__half>(), m->sc_l.as<float>(), R, m->dns.as<float>(), 0));
       launch_rmsnorm_bwd(m->xs.as<float>(), m->final_norm, m->dns.as<float>(), nullptr, R, d, g.rms_eps, m->dxs.as<float>(), nullptr, nullptr, st);
@@ -1359,7 +1383,8 @@ static rt_status run_staged(rt_model* m, bool backward, float* logits_out_host) 
     const char* e = getenv("RT_B200_NO_GRAPH");
     m->use_graphs = (e && e[0] == '1') ? 0 : 1;
   }
-  if (!m->use_graphs || c->profiling || logits_out_host || c->stream == nullptr) return run_staged_body(m, backward, logits_out_host);
+  if (!m->use_graphs || c->profiling || logits_out_host || m->want_argmax || c->stream == nullptr)
+    return run_staged_body(m, backward, logits_out_host);
   RT_CUDA(c, cudaSetDevice(c->device));
   const int M = m->staged_tokens, nt = m->staged_targets, bw = backward ? 1 : 0;
   const uint64_t sig = buffer_signature(m);
@@ -1494,6 +1519,31 @@ rt_status rt_model_score_layout(rt_model* m, const int32_t* tokens, const int32_
   m->staged_has_weights = false;
   RT_TRY(run_staged(m, false, nullptr));
   return rt_model_read_results(m, logp_out, n_targets, hits_out);
+}
+
+// The greedy token at each target position of a forward-only pass (src/eval.rs:156-221:
+// greedy_prefix asks logits_at for whole rows and takes their argmax on the host; here only the
+// argmax leaves the device).
+rt_status rt_model_argmax_layout(rt_model* m, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq,
+                                 const int32_t* positions, const int32_t* segments, const int32_t* tpos, int32_t n_targets,
+                                 int32_t* argmax_out) {
+  if (!m || !argmax_out) return RT_ERR_BAD_ARG;
+  rt_ctx* c = m->ctx;
+  if (n_targets <= 0) return RT_OK;
+  std::vector<int32_t> ttok((size_t)n_targets, 0);  // the pass scores against a target token; any valid id does
+  int M = 0;
+  m->staged_tokens = 0;
+  RT_TRY(upload_batch(m, tokens, seq_offsets, n_seq, tpos, ttok.data(), nullptr, n_targets, false, &M, positions, segments));
+  if (!m->argmax.reserve((size_t)n_targets * 4)) return c->fail(RT_ERR_CUDA, "out of device memory (argmax)");
+  m->staged_tokens = M;
+  m->staged_targets = n_targets;
+  m->staged_has_weights = false;
+  m->want_argmax = true;
+  rt_status st = run_staged(m, false, nullptr);
+  m->want_argmax = false;
+  if (st) return st;
+  RT_CUDA(c, cudaMemcpyAsync(argmax_out, m->argmax.p, (size_t)n_targets * 4, cudaMemcpyDeviceToHost, c->stream));
+  return c->check_device_status("rt_model_argmax_layout");
 }
 
 rt_status rt_optim_step(rt_model* m, float lr, float max_norm, float beta1, float beta2, float eps, float wd,

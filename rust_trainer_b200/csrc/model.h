@@ -127,6 +127,8 @@ struct rt_model {
   DevBuf tokens, pos, seq_start, x, ckpt, h, n1, n2, q_raw, k_raw, v_raw, q16, k16, v16, o16, lse, delta, g16, u16, hm16;
   DevBuf dx, dy16, sc_y, dhm, dg16, du16, sc_g, sc_u, dn, d_o, dO16, amax, dq, dk, dv, dq16, dk16, dv16, sc_q, sc_k, sc_v;
   DevBuf tpos, ttok, tw, logp, hits, xs, ns16, logits, dl16, sc_l, dns, dxs;
+  DevBuf argmax;            // per target, the greedy token of the last pass that asked for it
+  bool want_argmax = false;
   std::vector<int> h_pos, h_seq_start, h_gap;
   DevBuf refresh_tab;       // device copy of refresh_sent
   std::vector<rt::LoraRefreshJob> refresh_jobs, refresh_sent;

@@ -102,6 +102,20 @@ void launch_f32_to_16(const float* in, void* out, size_t n, bool to_f16, cudaStr
   else { f32_to_16_kernel<false><<<blocks, 256, 0, st>>>(in, (uint16_t*)out, n); RT_COUNT_LAUNCH(1); }
 }
 
+__global__ void split_f32_hi_lo_kernel(const float* __restrict__ w, size_t n, __half* __restrict__ hi, __half* __restrict__ lo) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = w[i];
+  const __half h = __float2half_rn(v);
+  hi[i] = h;
+  lo[i] = __float2half_rn(v - __half2float(h));
+}
+void launch_split_f32_hi_lo(const float* w, size_t n, __half* hi, __half* lo, cudaStream_t st) {
+  if (n == 0) return;
+  split_f32_hi_lo_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w, n, hi, lo);
+  RT_COUNT_LAUNCH(1);
+}
+
 // Row-normalised f16 copy: y16[r,:] = x[r,:] / amax_r, scale[r] = amax_r (1 if the row is zero).
 __global__ void normalize_rows_kernel(const float* __restrict__ x, int d, __half* __restrict__ y16,
                                       float* __restrict__ scale) {
@@ -1003,9 +1017,29 @@ void launch_scatter_add_rows(const float* src, const int* idx, int rows, int d, 
 // (reference src/model.rs:579-596, src/ops.rs:238-247): lse with an f64 normaliser, logp of
 // the target, hit = no logit above the target's, and d16 = p - onehot in f16 with the row scale
 // w (so dlogits = w*(p - onehot) exactly as the reference forms it).
+// The greedy token of a row: the LAST index holding the maximum, which is what the reference's
+// Iterator::max_by(total_cmp) returns on ties (src/eval.rs:167).  One more read of the row.
+__device__ void ce_row_argmax(const float* __restrict__ row, int v, float m, int* __restrict__ out) {
+  __shared__ int s_arg[32];
+  int best = -1;
+  for (int i = threadIdx.x; i < v; i += blockDim.x)
+    if (row[i] == m) best = i;  // i grows: the thread keeps its last
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, off));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) s_arg[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = threadIdx.x < (blockDim.x + 31) / 32 ? s_arg[threadIdx.x] : -1;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, off));
+    if (threadIdx.x == 0) *out = best;
+  }
+}
+
 __global__ void ce_row_kernel(const float* __restrict__ logits, int v, const int* __restrict__ target,
                               const float* __restrict__ weight, float* __restrict__ logp, int* __restrict__ hits,
-                              __half* __restrict__ d16, float* __restrict__ scale, int* status) {
+                              __half* __restrict__ d16, float* __restrict__ scale, int* __restrict__ argmax, int* status) {
   const size_t r = blockIdx.x;
   const float* row = logits + r * v;
   const int tgt = target[r];
@@ -1025,6 +1059,7 @@ __global__ void ce_row_kernel(const float* __restrict__ logits, int v, const int
     if (tl >= m) atomicAdd(hits, 1);
     if (scale) scale[r] = weight[r];
   }
+  if (argmax) ce_row_argmax(row, v, m, argmax + r);
   if (d16) {
     const float inv = (float)(1.0 / s);
     for (int i = threadIdx.x; i < v; i += blockDim.x) {
@@ -1041,7 +1076,7 @@ __global__ void ce_row_kernel(const float* __restrict__ logits, int v, const int
 __global__ void __launch_bounds__(1024)
 ce_row_vec_kernel(const float* __restrict__ logits, int v, const int* __restrict__ target,
                   const float* __restrict__ weight, float* __restrict__ logp, int* __restrict__ hits,
-                  __half* __restrict__ d16, float* __restrict__ scale, int* status) {
+                  __half* __restrict__ d16, float* __restrict__ scale, int* __restrict__ argmax, int* status) {
   const size_t r = blockIdx.x;
   const float4* row4 = (const float4*)(logits + r * v);
   const int n4 = v >> 2;
@@ -1065,6 +1100,7 @@ ce_row_vec_kernel(const float* __restrict__ logits, int v, const int* __restrict
     if (tl >= m) atomicAdd(hits, 1);
     if (scale) scale[r] = weight[r];
   }
+  if (argmax) ce_row_argmax(logits + r * v, v, m, argmax + r);
   if (d16) {
     const float inv = (float)(1.0 / s);
     uint2* out = (uint2*)(d16 + r * v);
@@ -1081,12 +1117,12 @@ ce_row_vec_kernel(const float* __restrict__ logits, int v, const int* __restrict
   }
 }
 void launch_ce_rows(const float* logits, int rows, int v, const int* target, const float* weight, float* logp, int* hits,
-                    __half* d16, float* scale, int* status, cudaStream_t st) {
+                    __half* d16, float* scale, int* argmax, int* status, cudaStream_t st) {
   if (rows <= 0) return;
   if ((v & 3) == 0 && ((uintptr_t)logits & 15) == 0 && (d16 == nullptr || ((uintptr_t)d16 & 7) == 0))
-    ce_row_vec_kernel<<<rows, 1024, 0, st>>>(logits, v, target, weight, logp, hits, d16, scale, status);
+    ce_row_vec_kernel<<<rows, 1024, 0, st>>>(logits, v, target, weight, logp, hits, d16, scale, argmax, status);
   else
-    ce_row_kernel<<<rows, 1024, 0, st>>>(logits, v, target, weight, logp, hits, d16, scale, status);
+    ce_row_kernel<<<rows, 1024, 0, st>>>(logits, v, target, weight, logp, hits, d16, scale, argmax, status);
   RT_COUNT_LAUNCH(1);
 }
 

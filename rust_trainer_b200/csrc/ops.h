@@ -6,6 +6,8 @@
 
 namespace rt {
 
+// hi = f16(w), lo = f16(w - hi): the two-term split of f32 frozen weights
+void launch_split_f32_hi_lo(const float* w, size_t n, __half* hi, __half* lo, cudaStream_t st);
 void launch_f32_to_16(const float* in, void* out, size_t n, bool to_f16, cudaStream_t st);
 void launch_normalize_rows(const float* x, int rows, int d, __half* y16, float* scale, cudaStream_t st);
 void launch_rmsnorm_fwd(const float* x, const float* w, int rows, int d, float eps, __half* y16, cudaStream_t st);
@@ -29,8 +31,9 @@ void launch_swiglu_bwd(const void* dh, int dh_f16, const float* in_scale, const 
                        int rows, int ff, __half* dg16, __half* du16, size_t out_pitch, float* sg, float* su, cudaStream_t st);
 void launch_gather_f32_rows(const float* x, const int* idx, int rows, int d, float* out, cudaStream_t st);
 void launch_scatter_add_rows(const float* src, const int* idx, int rows, int d, float* dx, cudaStream_t st);
+// argmax (optional): per row, the last index holding the row's maximum
 void launch_ce_rows(const float* logits, int rows, int v, const int* target, const float* weight, float* logp, int* hits,
-                    __half* d16, float* scale, int* status, cudaStream_t st);
+                    __half* d16, float* scale, int* argmax, int* status, cudaStream_t st);
 void launch_lora_refresh_group(const float* a, const float* b, int r, int K, int N, float s, __half* a_s, __half* a_h,
                                __half* bp, __half* bt_s, size_t ldb, cudaStream_t st);
 void launch_lora_refresh(const float* a, const float* b, int r, int K, int N, float s, __half* a_s, __half* a_h,

@@ -64,6 +64,11 @@ struct QWeight {
   int nbr = 0, nbk = 0;          // brick grid (each padded to an even count)
   uint8_t* bricks = nullptr;     // quantised formats
   void* dense16 = nullptr;       // F16 / BF16: row-major [rows x cols]
+  // f32 weights (the reference's FrozenWeight::F32, src/frozen.rs:33-38): the exact values for
+  // row(), and their two-term f16 split W = hi + lo for the tensor cores (hi in dense16 with
+  // fmt = F16, lo = f16(W - hi) here: 17 to 22 significant bits together)
+  const float* f32 = nullptr;
+  void* dense16_lo = nullptr;
   size_t ggml_nbytes = 0;        // size of the original ggml tensor
   size_t dev_nbytes = 0;
 };
@@ -71,6 +76,7 @@ struct QWeight {
 // Exact (f32) value of element (r, k) from the brick store; mirrors ggml's dequantisation
 // arithmetic operation for operation so rows come out bit-identical to a CPU dequantise.
 __device__ inline float brick_value(const QWeight& w, int r, int k) {
+  if (w.f32) return w.f32[(size_t)r * w.cols + k];
   if (w.fmt == GGML_F16) return __half2float(((const __half*)w.dense16)[(size_t)r * w.cols + k]);
   if (w.fmt == GGML_BF16) return __bfloat162float(((const __nv_bfloat16*)w.dense16)[(size_t)r * w.cols + k]);
   const uint8_t* b = w.bricks + ((size_t)(r >> 6) * w.nbk + (k >> 6)) * fmt_brick_bytes(w.fmt);

@@ -62,6 +62,10 @@ struct QGemmArgs {
 };
 
 int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a);
+// The product with a frozen weight of any storage: one qgemm launch, or, for f32 weights held as
+// a two-term f16 split, the high term followed by the low term accumulated into an f32 result
+// (a 16-bit result cannot resolve the low term and skips it).
+int frozen_matmul_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a);
 size_t qgemm_smem_bytes();
 int qgemm_init();  // resolves the driver entry point for tensor-map encoding; sets smem attributes
 

@@ -54,6 +54,15 @@ class Model:
             out.append(Linear(lib().rt_linear_name(h).decode(), None, _handle=h, _ctx=self.ctx))
         return out
 
+    def linear_shapes(self) -> list:
+        """(GGUF module name, in_dim, out_dim) of every block's seven projections, in
+        Block::linears order (src/model.rs:199-218), whether adapted or not."""
+        c = self.cfg
+        d, q, kv, ff = c["hidden"], c["n_heads"] * c["head_dim"], c["n_kv_heads"] * c["head_dim"], c["ff"]
+        dims = [("attn_q", d, q), ("attn_k", d, kv), ("attn_v", d, kv), ("attn_output", q, d),
+                ("ffn_gate", d, ff), ("ffn_up", d, ff), ("ffn_down", ff, d)]
+        return [(f"blk.{li}.{nm}", i, o) for li in range(c["n_layers"]) for nm, i, o in dims]
+
     def load_adapters(self, adapters: list) -> None:
         """Overwrites A and B of every adapter (same order as lora_linears())."""
         lins = self.lora_linears()
@@ -149,6 +158,27 @@ class Model:
         self.ctx.check(lib().rt_model_score(self._h, _ip(toks), _ip(offs), len(seqs), _ip(tp), _ip(tt), tp.size, _fp(logp),
                                             C.byref(hits), None if logits is None else _fp(logits)))
         return logp, hits.value, logits
+
+    def argmax_at(self, seqs, target_pos) -> np.ndarray:
+        """Greedy token at each (global) position of a forward-only pass (src/eval.rs:162-167)."""
+        toks, offs = self._batch(seqs)
+        tp = np.ascontiguousarray(target_pos, dtype=np.int32)
+        out = np.empty(tp.size, dtype=np.int32)
+        self.ctx.check(lib().rt_model_argmax_layout(self._h, _ip(toks), _ip(offs), len(seqs), None, None, _ip(tp), tp.size,
+                                                    _ip(out)))
+        return out
+
+    def argmax_at_packed(self, groups, target_pos) -> np.ndarray:
+        toks, offs, pos, seg = self._layout(groups)
+        tp = np.ascontiguousarray(target_pos, dtype=np.int32)
+        out = np.empty(tp.size, dtype=np.int32)
+        self.ctx.check(lib().rt_model_argmax_layout(self._h, _ip(toks), _ip(offs), len(groups), _ip(pos), _ip(seg), _ip(tp),
+                                                    tp.size, _ip(out)))
+        return out
+
+    def allreduce_grads(self) -> None:
+        """Sum of the flat LoRA-gradient buffer over the ranks of the context's communicator."""
+        self.ctx.check(lib().rt_model_allreduce_grads(self._h))
 
     def optim_step(self, lr: float, max_norm: float = 1.0, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
                    weight_decay: float = 0.0) -> float:
