@@ -12,10 +12,16 @@ as the CPU arm runs it: each block's forward runs again before its backward.  Th
 default keeps every block's caches when they fit in device memory (here 12.6 GB); that variant
 of the same step is timed in the same run and reported as `keep_caches`.
 
-The N = 1 workload is BASELINE.json configs[1]: a synthetic Qwen3-0.6B-shaped GGUF model with
-Q8_0 weights, 16 sequences x 512 uniform-random ids, loss on the last 30 % of each sequence,
-LoRA r=16 alpha=32 on the seven projections, warm-up 2 + cosine LR.  For
-N > 1 every rank holds a replica and its own 16 x 512 batch (weak scaling).
+The headline workload: a synthetic Qwen3-0.6B-shaped GGUF model (28 layers, hidden 1024, 16 Q /
+8 KV heads of 128, SwiGLU 3072, vocabulary 151 936, tied) with Q8_0 weights, 16 sequences x 512
+uniform-random ids per GPU, loss on the last 30 % of each sequence, LoRA r=16 alpha=32 on the
+seven projections, warm-up 2 + cosine LR.  For N > 1 every rank holds a replica; the global batch
+is N x 16 sequences dealt round-robin (weak scaling), every target weighted with the GLOBAL
+1/batch_tokens, and the ranks' gradient buffers are summed by the library's own NCCL all-reduce
+(rt_model_allreduce_grads).  Before the timed region a fixed global batch is run both sharded
+over the N ranks and whole on every rank, and the two gradients are compared (`dp_check`); after
+it, the fixed-global-batch workload (Qwen2.5-0.5B shape, 32 x 1024, every position a target) is
+timed at this N (`strong`).
 """
 from __future__ import annotations
 
@@ -34,23 +40,23 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE.json configs[1]
+    # the headline: Qwen3-0.6B shape, Q8_0, 16 x 512 per GPU, recomputation on
     "qwen3-0.6b-q8_0-16x512": dict(preset="qwen3-0.6b", quant="Q8_0", n_seq=16, seq_len=512, answer_frac=0.30, rank=16,
                                    alpha=32.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=2, lr_total=20, min_ratio=0.1),
-    # BASELINE.json configs[0] (the reference's own CPU-runnable case)
+    # the reference's own CPU-runnable case: the same shape in Q4_0, 4 x 256, one AdamW step
     "qwen3-0.6b-q4_0-4x256": dict(preset="qwen3-0.6b", quant="Q4_0", n_seq=4, seq_len=256, answer_frac=0.50, rank=16,
                                   alpha=32.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=0, lr_total=1, min_ratio=0.1),
-    # BASELINE.json configs[2]: Qwen2.5-0.5B shape, Q4_K where the row length allows it (ffn_down), Q4_0 elsewhere,
+    # Qwen2.5-0.5B shape (24 layers, hidden 896, 14 Q / 2 KV heads of 64, q/k/v bias), Q4_K where the row length allows it (ffn_down), Q4_0 elsewhere,
     # every position a target
     "qwen2.5-0.5b-q4_k-32x1024": dict(preset="qwen2.5-0.5b", quant="Q4_K", n_seq=32, seq_len=1024, answer_frac=1.0, rank=8,
                                       alpha=16.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=2, lr_total=20, min_ratio=0.1),
-    # BASELINE.json configs[3]: Llama-3.2-3B shape, Q6_K, every position a target (per GPU: 16 x 2048)
+    # Llama-3.2-3B shape, Q6_K, every position a target (per GPU: 16 x 2048)
     "llama-3.2-3b-q6_k-16x2048": dict(preset="llama-3.2-3b", quant="Q6_K", n_seq=16, seq_len=2048, answer_frac=1.0, rank=16,
                                       alpha=32.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=2, lr_total=20, min_ratio=0.1),
-    # BASELINE.json configs[4] at its 8-GPU share: Qwen3-4B shape, Q4_0, r = 32, 8 x 2048 per GPU, last 25 % targets
+    # Qwen3-4B shape, Q4_0, r = 32, last 25 % targets: the 64 x 2048 batch at its 8-GPU share
     "qwen3-4b-q4_0-8x2048": dict(preset="qwen3-4b", quant="Q4_0", n_seq=8, seq_len=2048, answer_frac=0.25, rank=32,
                                  alpha=64.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=2, lr_total=50, min_ratio=0.1),
-    # two layers of configs[1] (the same per-layer shapes and token count, about 1 GB on the device):
+    # two layers of the headline model (the same per-layer shapes and token count, about 1 GB on the device):
     # the case the per-kernel profiler captures run on
     "qwen3-0.6b-q8_0-16x512-2layers": dict(preset="qwen3-0.6b", quant="Q8_0", n_seq=16, seq_len=512, answer_frac=0.30, rank=16,
                                            alpha=32.0, lr=1e-4, wd=0.01, clip=1.0, lr_warmup=2, lr_total=20, min_ratio=0.1,
@@ -60,6 +66,7 @@ WORKLOADS = {
                  wd=0.01, clip=1.0, lr_warmup=2, lr_total=20, min_ratio=0.1),
 }
 DEFAULT_WORKLOAD = "qwen3-0.6b-q8_0-16x512"
+STRONG_WORKLOAD = "qwen2.5-0.5b-q4_k-32x1024"  # fixed GLOBAL batch, split over the ranks
 
 
 def measured_peaks():
@@ -133,21 +140,24 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- reference arm (CPU)
-def cpu_reference_run(wl_name: str, steps: int, warmup: int, sample_tokens: int | None = None):
+CPU_SAMPLE_TOKENS = 128  # the same bounded sample whatever --steps says
+
+
+def cpu_reference_run(wl_name: str, steps: int, warmup: int):
     """Times the CPU restatement of the reference's algorithm (oracle/) on a bounded sample of
-    the workload: ONE sequence of `sample_tokens` ids of the same model, same LoRA shape, loss on
-    the same trailing fraction, forward + recompute + backward + clip + AdamW per step."""
+    the workload: ONE sequence of 128 ids of the same model, same LoRA shape, loss on the same
+    trailing fraction, forward + recompute + backward + clip + AdamW per step, on every host core
+    (a launcher's OMP_NUM_THREADS=1 is overridden)."""
     from oracle import oracle as O
     from rust_trainer_b200 import synth
 
     wl = WORKLOADS[wl_name]
+    cores = O.set_num_threads(os.cpu_count() or 1)
     spec = synth.preset(wl["preset"], quant=wl["quant"], seed=0)
     tensors = synth.build_tensors(spec)
     om = O.OracleModel(spec.config(), tensors)
     om.attach_lora(synth.lora_adapters(spec, wl["rank"], wl["alpha"], seed=1234))
-    if sample_tokens is None:
-        sample_tokens = 128 if (steps + warmup) <= 8 else 64
-    sample_tokens = min(sample_tokens, wl["seq_len"])
+    sample_tokens = min(CPU_SAMPLE_TOKENS, wl["seq_len"])
     toks = synth.token_batch(spec, 1, sample_tokens, 99)[0]
     a0 = int(np.ceil(sample_tokens * (1.0 - wl["answer_frac"])))
     tp, tt = synth.answer_targets(toks, a0)
@@ -164,21 +174,21 @@ def cpu_reference_run(wl_name: str, steps: int, warmup: int, sample_tokens: int 
         if i >= warmup:
             times.append(dt)
     ms = 1e3 * float(np.mean(times))
-    cores = O.lib().orc_num_threads()
     return dict(value=sample_tokens / (ms / 1e3), ms_per_step=ms, cores=cores,
                 sample=f"1 sequence x {sample_tokens} tokens of the same model per step (loss on the last "
                        f"{int(wl['answer_frac'] * 100)} %), forward + recompute + backward + clip + AdamW"), spec
 
 
 def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return 0
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0  # under a multi-rank launcher rank 0 alone runs the CPU arm
     wl = WORKLOADS[args.workload]
-    r, spec = cpu_reference_run(args.workload, args.steps, args.warmup)
+    # a few steps are enough for a CPU loop without caches to warm; bounded so the arm ends in about a minute
+    steps, warmup = min(args.steps, 5), min(args.warmup, 1)
+    r, spec = cpu_reference_run(args.workload, steps, warmup)
     line = {
         "impl": "reference", "metric": "trained_tokens_per_s", "value": r["value"], "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": r["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "model": wl["preset"], "quant": wl["quant"], "lora_rank": wl["rank"],
                    "note": "CPU restatement of the reference algorithm (oracle/), not the reference binary: no Rust "
@@ -192,17 +202,118 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------- CUDA arm
-class DevPtr:
-    """Lets torch view device memory owned by the C library (for the NCCL all-reduce)."""
+class StepRunner:
+    """One replica of one workload on this rank's GPU: the local share of a global batch staged in
+    HBM (or passed from pinned host buffers for the end-to-end arm), and the step around it."""
 
-    def __init__(self, ptr: int, n: int):
-        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+    def __init__(self, rt, ctx, wl, world, rank, checkpointing):
+        from rust_trainer_b200 import dp, synth
+
+        self.rt, self.ctx, self.wl, self.world, self.rank = rt, ctx, wl, world, rank
+        over = {"n_layers": wl["n_layers"]} if "n_layers" in wl else {}
+        self.spec = synth.preset(wl["preset"], quant=wl["quant"], seed=0, **over)
+        tensors = synth.build_tensors(self.spec)
+        self.model = rt.Model(ctx, self.spec.config(), tensors)
+        self.n_params = self.model.attach_lora(wl["rank"], wl["alpha"], None, 1234)
+        self.model.load_adapters(synth.lora_adapters(self.spec, wl["rank"], wl["alpha"], seed=1234))
+        del tensors
+        self.model.set_checkpointing({"on": 1, "off": 0, "auto": -1}[checkpointing])
+        self.step_no = 0
+        self.dp = dp
+
+    def global_examples(self, n_seq_global, seed):
+        from rust_trainer_b200 import synth
+
+        wl = self.wl
+        toks = synth.token_batch(self.spec, n_seq_global, wl["seq_len"], seed)
+        self.answer_start = int(np.ceil(wl["seq_len"] * (1.0 - wl["answer_frac"])))
+        return [(toks[i], self.answer_start) for i in range(n_seq_global)]
+
+    def set_batch(self, examples, rank, world):
+        """This rank's round-robin share of `examples` with the global 1/batch_tokens weights, in
+        pinned host buffers."""
+        import torch
+
+        b = self.dp.local_batch(examples, rank, world)
+        pin = lambda a: torch.from_numpy(np.ascontiguousarray(a).copy()).pin_memory().numpy()
+        self.batch = b
+        self.h_toks = pin(np.concatenate(b.seqs))
+        offs = np.zeros(len(b.seqs) + 1, np.int32)
+        offs[1:] = np.cumsum([s.size for s in b.seqs])
+        self.h_offs, self.h_tpos, self.h_ttok, self.h_w = pin(offs), pin(b.target_pos), pin(b.target_tok), pin(b.weights)
+        self.h_logp = torch.empty(b.target_pos.size, dtype=torch.float32).pin_memory().numpy()
+        self.local_tokens = int(self.h_toks.size)
+
+    def stage(self):
+        L, m = self.L, self.model
+        self.ctx.check(L.rt_model_stage_batch(m._h, _ip(self.h_toks), _ip(self.h_offs), len(self.batch.seqs), _ip(self.h_tpos),
+                                              _ip(self.h_ttok), _fp(self.h_w), self.h_tpos.size))
+
+    @property
+    def L(self):
+        from rust_trainer_b200._lib import lib
+
+        return lib()
+
+    def lr_now(self):
+        wl = self.wl
+        return self.rt.schedule_lr(wl["lr"], wl["lr_warmup"], wl["lr_total"], wl["min_ratio"], self.step_no % wl["lr_total"])
+
+    def finish_step(self):
+        self.model.allreduce_grads()  # sum over ranks on the ctx stream (nothing to do in a world of one)
+        self.model.optim_step(self.lr_now(), self.wl["clip"], weight_decay=self.wl["wd"])
+        self.step_no += 1
+
+    def step_resident(self):
+        self.model.zero_grad()
+        self.ctx.check(self.L.rt_model_run_staged(self.model._h, 1))
+        self.finish_step()
+
+    def step_e2e(self):
+        """The call a host makes: tokens, targets and weights from (pinned) host memory in, per-target
+        log-probabilities back out, every step."""
+        self.model.zero_grad()
+        hits = C.c_int32()
+        self.ctx.check(self.L.rt_model_forward_backward(self.model._h, _ip(self.h_toks), _ip(self.h_offs), len(self.batch.seqs),
+                                                        _ip(self.h_tpos), _ip(self.h_ttok), _fp(self.h_w), self.h_tpos.size,
+                                                        _fp(self.h_logp), C.byref(hits)))
+        loss = self.dp.step_loss(self.h_logp, self.batch)
+        self.finish_step()
+        return loss
+
+    def grads(self):
+        return np.concatenate([np.concatenate([lo["ga"].ravel(), lo["gb"].ravel()])
+                               for lo in (l.lora() for l in self.model.lora_linears())])
+
+    def close(self):
+        self.model.close()
+
+
+def _ip(a):
+    return a.ctypes.data_as(C.POINTER(C.c_int32))
+
+
+def _fp(a):
+    return a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+def dram_bytes_per_flop():
+    """DRAM traffic of the frozen-matmul kernel per algorithmic flop, from the committed summary of
+    its ncu capture (dram__bytes_read.sum + dram__bytes_write.sum of one launch over that launch's
+    2*tokens*out*in); None when no summary of the current kernel is there."""
+    path = os.path.join(ROOT, "profiles", "qgemm_kernel_dram_traffic.txt")
+    try:
+        for line in open(path):
+            if line.startswith("dram_bytes_per_flop:"):
+                return float(line.split(":", 1)[1].split()[0]), os.path.relpath(path, ROOT)
+    except (OSError, ValueError):
+        pass
+    return None, None
 
 
 def run_ours(args):
     import torch
     import rust_trainer_b200 as rt
-    from rust_trainer_b200 import synth
     from rust_trainer_b200._lib import lib
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -211,76 +322,25 @@ def run_ours(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the CUDA path has no CPU fallback")
     torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
 
-        dist = dist_mod
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod  # plumbing only: barriers, the max over ranks of the timings, handing out the communicator id
+        dist.init_process_group("nccl", device_id=dev)
     wl = WORKLOADS[args.workload]
     L = lib()
-
-    over = {"n_layers": wl["n_layers"]} if "n_layers" in wl else {}
-    spec = synth.preset(wl["preset"], quant=wl["quant"], seed=0, **over)
-    tensors = synth.build_tensors(spec)
     ctx = rt.Context(local_rank)
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
     L.rt_ctx_set_stream(ctx._h, C.c_void_p(stream.cuda_stream))
-    model = rt.Model(ctx, spec.config(), tensors)
-    n_params = model.attach_lora(wl["rank"], wl["alpha"], None, 1234)
-    model.load_adapters(synth.lora_adapters(spec, wl["rank"], wl["alpha"], seed=1234))
-    del tensors
-    # BASELINE.json configs[1] says "activation recomputation on": the headline keeps that mode
-    # (Model.checkpointing = true, the reference's default); the same job with every block's
-    # caches kept in HBM instead is timed afterwards and reported beside it.
-    model.set_checkpointing({"on": 1, "off": 0, "auto": -1}[args.checkpointing])
-
-    toks, tpos, ttok, answer_start = make_batch(spec, wl, seed=100 + rank)
-    n_targets = tpos.size
-    global_targets = n_targets * world
-    tokens_per_step = toks.size * world
-    # pinned host buffers for the end-to-end arm
-    pin = lambda a: torch.from_numpy(a.copy()).pin_memory().numpy()
-    h_toks, h_tpos, h_ttok = pin(toks.reshape(-1)), pin(tpos), pin(ttok)
-    h_w = pin(np.full(n_targets, 1.0 / global_targets, np.float32))
-    h_offs = pin(np.arange(0, toks.size + 1, wl["seq_len"], dtype=np.int32))
-    h_logp = torch.empty(n_targets, dtype=torch.float32).pin_memory().numpy()
-    seqs = [h_toks[i * wl["seq_len"]:(i + 1) * wl["seq_len"]] for i in range(wl["n_seq"])]
-    i32p, f32p = C.POINTER(C.c_int32), C.POINTER(C.c_float)
-    ip = lambda a: a.ctypes.data_as(i32p)
-    fp = lambda a: a.ctypes.data_as(f32p)
-
-    gptr, gn = model.grad_buffer()
-    grad_view = torch.as_tensor(DevPtr(gptr, gn), device=f"cuda:{local_rank}") if world > 1 else None
-    loss_buf = torch.zeros(1, device=f"cuda:{local_rank}")
-    step_no = [0]
-
-    def lr_now():
-        return rt.schedule_lr(wl["lr"], wl["lr_warmup"], wl["lr_total"], wl["min_ratio"], step_no[0] % wl["lr_total"])
-
-    def finish_step():
-        if world > 1:
-            dist.all_reduce(grad_view)  # sum of the LoRA gradients over ranks, NCCL over NVLink
-        model.optim_step(lr_now(), wl["clip"], weight_decay=wl["wd"])
-        step_no[0] += 1
-
-    def step_resident():
-        model.zero_grad()
-        ctx.check(L.rt_model_run_staged(model._h, 1))
-        finish_step()
-
-    def step_e2e():
-        model.zero_grad()
-        hits = C.c_int32()
-        ctx.check(L.rt_model_forward_backward(model._h, ip(h_toks), ip(h_offs), wl["n_seq"], ip(h_tpos), ip(h_ttok), fp(h_w),
-                                              n_targets, fp(h_logp), C.byref(hits)))
-        loss = -float(np.dot(h_logp, h_w))
-        if world > 1:
-            loss_buf.fill_(loss)
-            dist.all_reduce(loss_buf)
-        finish_step()
-        return loss
+    if world > 1:
+        uid = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            uid.copy_(torch.frombuffer(bytearray(rt.Context.comm_unique_id()), dtype=torch.uint8))
+        dist.broadcast(uid, 0)
+        ctx.comm_init_rank(world, rank, bytes(uid.cpu().numpy().tobytes()))
 
     def timed(fn, n):
         if world > 1:
@@ -295,21 +355,55 @@ def run_ours(args):
         torch.cuda.synchronize()
         wall = (time.perf_counter() - t0) * 1e3
         ms = max(e0.elapsed_time(e1), 0.0)
-        t = torch.tensor([ms, wall], device=f"cuda:{local_rank}")
+        t = torch.tensor([ms, wall], device=dev)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dist.barrier()
         return float(t[0]), float(t[1])
 
-    # inputs resident in HBM before the timed region
-    ctx.check(L.rt_model_stage_batch(model._h, ip(h_toks), ip(h_offs), wl["n_seq"], ip(h_tpos), ip(h_ttok), fp(h_w), n_targets))
+    run = StepRunner(rt, ctx, wl, world, rank, args.checkpointing)
+    model = run.model
+
+    # ---- N ranks on ONE global batch against one rank on the whole of it (before anything is timed)
+    dp_check = None
+    if world > 1:
+        fixed = run.global_examples(wl["n_seq"], seed=7)
+        run.set_batch(fixed, rank, world)
+        model.zero_grad()
+        hits = C.c_int32()
+        ctx.check(L.rt_model_forward_backward(model._h, _ip(run.h_toks), _ip(run.h_offs), len(run.batch.seqs), _ip(run.h_tpos),
+                                              _ip(run.h_ttok), _fp(run.h_w), run.h_tpos.size, _fp(run.h_logp), C.byref(hits)))
+        loss_dp = torch.tensor([run.dp.step_loss(run.h_logp, run.batch)], dtype=torch.float64, device=dev)
+        dist.all_reduce(loss_dp)
+        model.allreduce_grads()
+        ctx.synchronize()
+        g_dp = run.grads()
+        run.set_batch(fixed, 0, 1)  # the whole batch on this rank alone
+        model.zero_grad()
+        ctx.check(L.rt_model_forward_backward(model._h, _ip(run.h_toks), _ip(run.h_offs), len(run.batch.seqs), _ip(run.h_tpos),
+                                              _ip(run.h_ttok), _fp(run.h_w), run.h_tpos.size, _fp(run.h_logp), C.byref(hits)))
+        loss_one = run.dp.step_loss(run.h_logp, run.batch)
+        g_one = run.grads()
+        rel = float(np.linalg.norm(g_dp.astype(np.float64) - g_one) / np.linalg.norm(g_one.astype(np.float64)))
+        t = torch.tensor([rel, abs(float(loss_dp[0]) - loss_one) / abs(loss_one)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dp_check = {"grad_rel_l2": float(t[0]), "loss_rel": float(t[1]), "global_batch": f"{wl['n_seq']} x {wl['seq_len']}",
+                    "what": "gradient buffer after the NCCL sum of N shards vs the whole batch on one rank, max over ranks"}
+        model.zero_grad()
+
+    # ---- the timed job: N x n_seq sequences dealt round-robin, inputs resident in HBM
+    examples = run.global_examples(wl["n_seq"] * world, seed=100)
+    run.set_batch(examples, rank, world)
+    n_targets = run.h_tpos.size
+    tokens_per_step = sum(int(t.size) for t, _ in examples)
+    run.stage()
     for _ in range(args.warmup):
-        step_resident()
+        run.step_resident()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     launches0 = L.rt_ctx_launch_count(ctx._h)
-    ms_total, _ = timed(step_resident, args.steps)
+    ms_total, _ = timed(run.step_resident, args.steps)
     launches = (L.rt_ctx_launch_count(ctx._h) - launches0) // max(args.steps, 1)
     clocks = sampler.stop() if rank == 0 else None
     ms_step = ms_total / args.steps
@@ -322,30 +416,28 @@ def run_ours(args):
             dist.destroy_process_group()
         return 0
 
-    # end to end through the host-buffer call
+    # ---- end to end through the host-buffer call
     for _ in range(min(args.warmup, 2)):
-        step_e2e()
-    ms_e2e_total, wall_e2e = timed(step_e2e, args.steps)
+        run.step_e2e()
+    ms_e2e_total, wall_e2e = timed(run.step_e2e, args.steps)
     ms_e2e = max(ms_e2e_total, wall_e2e) / args.steps  # host copies are not all on the stream: take the slower clock
 
-    # roofline of the dominant kernel (the frozen matmul): per-launch CUDA events over profiled steps
+    # ---- roofline of the dominant kernel (the frozen matmul): per-launch CUDA events over profiled steps
+    run.stage()
     L.rt_ctx_set_profiling(ctx._h, 1)
     prof_steps = min(args.steps, 2)
     for _ in range(prof_steps):
-        step_resident()
+        run.step_resident()
     n_l, ms_l, fl, by = C.c_uint64(), C.c_double(), C.c_double(), C.c_double()
     ctx.check(L.rt_ctx_profile_read(ctx._h, C.byref(n_l), C.byref(ms_l), C.byref(fl), C.byref(by)))
     L.rt_ctx_set_profiling(ctx._h, 0)
     peaks = measured_peaks()
     achieved_tf = fl.value / (ms_l.value * 1e-3) / 1e12 if ms_l.value > 0 else 0.0
-    # DRAM traffic per launch: from the ncu capture of the kernel on one shape (profiles/qgemm_kernel_fwd_3072x1024_
-    # q8_0_t16384.md: 37.1 MB read + 50.1 MB written for 103.1 GFLOP, equal to the operands read once and the output
-    # written once), scaled by the work of this run's average launch
+    bpf, bpf_src = dram_bytes_per_flop()
     avg_launch_flops = fl.value / max(n_l.value, 1)
-    traffic = 87.8e6 * avg_launch_flops / 103.1e9
     roofline = {"bound": "tensor", "achieved": achieved_tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                "frac": achieved_tf / peaks["tflops"], "traffic": traffic,
-                "traffic_source": "ncu dram__bytes_read+write of one captured shape, scaled by flops per launch",
+                "frac": achieved_tf / peaks["tflops"], "traffic": None if bpf is None else bpf * avg_launch_flops,
+                "traffic_source": None if bpf is None else f"{bpf_src}: ncu DRAM bytes per flop of one captured launch x flops of this run's average launch",
                 "peak_source": peaks["source"] + " (sustained bf16 cuBLAS)",
                 "kernel": "qgemm_kernel", "launches_per_step": int(n_l.value // prof_steps),
                 "avg_launch_us": 1e3 * ms_l.value / max(n_l.value, 1), "share_of_step": (ms_l.value / prof_steps) / ms_step,
@@ -355,26 +447,52 @@ def run_ours(args):
     keep = None
     if args.checkpointing == "on":
         model.set_checkpointing(0)
-        ctx.check(L.rt_model_stage_batch(model._h, ip(h_toks), ip(h_offs), wl["n_seq"], ip(h_tpos), ip(h_ttok), fp(h_w), n_targets))
+        run.stage()
         for _ in range(args.warmup):
-            step_resident()
-        ms_keep, _ = timed(step_resident, args.steps)
+            run.step_resident()
+        ms_keep, _ = timed(run.step_resident, args.steps)
         if not model.checkpointing:
             keep = {"value": tokens_per_step / (ms_keep / args.steps * 1e-3), "unit": "tokens/s", "ms_per_step": ms_keep / args.steps,
                     "what": "same step with Model.checkpointing off: every block's caches stay in HBM, no second forward"}
+    n_params, lora_init = run.n_params, run.spec.describe()["lora_init"]
+    h2d = run.h_toks.nbytes + run.h_offs.nbytes + run.h_tpos.nbytes + run.h_ttok.nbytes + run.h_w.nbytes + 2 * run.h_toks.size * 4
+    d2h = run.h_logp.nbytes + 4 + 4
+    answer_start = run.answer_start
+    run.close()
+
+    # ---- strong scaling: ONE fixed global batch split over the ranks
+    strong = None
+    if args.strong and args.workload == DEFAULT_WORKLOAD:
+        swl = WORKLOADS[STRONG_WORKLOAD]
+        if swl["n_seq"] % world == 0:
+            srun = StepRunner(rt, ctx, swl, world, rank, args.checkpointing)
+            sex = srun.global_examples(swl["n_seq"], seed=100)
+            srun.set_batch(sex, rank, world)
+            srun.stage()
+            for _ in range(3):
+                srun.step_resident()
+            s_steps = min(args.steps, 5)
+            ms_s, _ = timed(srun.step_resident, s_steps)
+            stoks = swl["n_seq"] * swl["seq_len"]
+            strong = {"workload": STRONG_WORKLOAD, "global_batch": f"{swl['n_seq']} x {swl['seq_len']}", "tokens_per_gpu": stoks // world,
+                      "value": stoks / (ms_s / s_steps * 1e-3), "unit": "tokens/s", "ms_per_step": ms_s / s_steps, "steps": s_steps,
+                      "recompute": bool(srun.model.checkpointing), "scaling": "strong"}
+            srun.close()
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return 0
 
+    shapes = None
+    if world == 1 and args.shape_table:
+        shapes = qgemm_shape_table(rt, ctx, stream, peaks)
+
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        r, _ = cpu_reference_run(args.workload, 1, 0, sample_tokens=128)
+        r, _ = cpu_reference_run(args.workload, 1, 0)
         cpu = {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]}
 
-    h2d = h_toks.nbytes + h_offs.nbytes + h_tpos.nbytes + h_ttok.nbytes + h_w.nbytes + 2 * toks.size * 4  # + positions, seq starts
-    d2h = h_logp.nbytes + 4 + 4
     line = {
         "metric": "trained_tokens_per_s", "value": tokens_per_step / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -383,16 +501,65 @@ def run_ours(args):
                    "seq_len": wl["seq_len"], "answer_targets_per_seq": wl["seq_len"] - answer_start, "lora_rank": wl["rank"],
                    "lora_params": n_params, "parallelism": f"dp{world}", "recompute": recompute_ran,
                    "l2": "activations and logits per step (>1 GB) exceed the 126 MB L2; no explicit flush",
-                   "lora_init": spec.describe()["lora_init"], "seeds": {"weights": 0, "lora": 1234, "tokens": 100}},
+                   "lora_init": lora_init, "seeds": {"weights": 0, "lora": 1234, "tokens": 100}},
         "roofline": roofline, "cpu_baseline": cpu, "keep_caches": keep,
         "e2e": {"value": tokens_per_step / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h), "ms_per_step": ms_e2e},
         "gpu_launches": int(launches) * args.steps, "gpu_launches_per_step": int(launches), "clocks": clocks,
+        "dp_check": dp_check, "strong": strong, "qgemm_shapes": shapes,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def qgemm_shape_table(rt, ctx, stream, peaks, token_counts=(4096, 8192), iters=10):
+    """The frozen-matmul kernel alone on every projection shape of the five model configurations in
+    its weight format, forward (f16 out) and backward (f32 out), CUDA events on the launching
+    stream: [model, quant, dir, out, in, tokens, us, TFLOP/s, fraction of the measured peak]."""
+    import torch
+    from rust_trainer_b200 import quants as Q, synth
+    from rust_trainer_b200._lib import lib
+
+    L = lib()
+    rng = np.random.default_rng(0)
+    cases = [("qwen3-0.6b", "Q4_0"), ("qwen3-0.6b", "Q8_0"), ("qwen2.5-0.5b", "Q4_K"), ("llama-3.2-3b", "Q6_K"), ("qwen3-4b", "Q4_0")]
+    rows = []
+    seen = {}
+    for preset, quant in cases:
+        spec = synth.preset(preset, quant=quant)
+        for (n, k) in sorted(set(spec.linear_shapes().values())):
+            t = spec.quant_for(k)
+            key = (n, k, t)
+            if key not in seen:
+                f = rt.Frozen(ctx, t, n, k, Q.quantize((rng.standard_normal((n, k)) * 0.02).astype(np.float32), t))
+                res = []
+                for M in token_counts:
+                    x = torch.randn(M, k, device="cuda", dtype=torch.float16)
+                    dy = torch.randn(M, n, device="cuda", dtype=torch.float16)
+                    y = torch.empty(M, n, device="cuda", dtype=torch.float16)
+                    dx = torch.empty(M, k, device="cuda", dtype=torch.float32)
+                    for name, fn in (("fwd", lambda: L.rt_frozen_forward_dev(f._h, x.data_ptr(), 2, M, y.data_ptr(), 2, 0)),
+                                     ("bwd", lambda: L.rt_frozen_backward_input_dev(f._h, dy.data_ptr(), 2, M, dx.data_ptr(), 0, 0))):
+                        for _ in range(3):
+                            ctx.check(fn())
+                        torch.cuda.synchronize()
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(stream)
+                        for _ in range(iters):
+                            ctx.check(fn())
+                        e1.record(stream)
+                        torch.cuda.synchronize()
+                        us = 1e3 * e0.elapsed_time(e1) / iters
+                        res.append((name, M, us))
+                f.close()
+                seen[key] = res
+            for name, M, us in seen[key]:
+                tf = 2.0 * M * n * k / us / 1e6
+                rows.append([preset, Q.NAMES[t], name, n, k, M, round(us, 1), round(tf, 1), round(tf / peaks["tflops"], 3)])
+    return {"columns": ["model", "quant", "dir", "out", "in", "tokens", "us", "tflops", "frac_of_peak"],
+            "peak_tflops": peaks["tflops"], "peak_source": peaks["source"] + " (sustained bf16 cuBLAS)", "rows": rows}
 
 
 def run_microbench(args):
@@ -458,6 +625,10 @@ def main():
                          "phases, fewer warm-up steps allowed); the printed number is not a bench value")
     ap.add_argument("--checkpointing", default="on", choices=["on", "off", "auto"],
                     help="Model.checkpointing for the headline number (the workload says on)")
+    ap.add_argument("--no-strong", dest="strong", action="store_false",
+                    help="skip the fixed-global-batch (strong scaling) workload after the headline")
+    ap.add_argument("--no-shape-table", dest="shape_table", action="store_false",
+                    help="skip the per-shape table of the frozen-matmul kernel (N = 1 only)")
     ap.add_argument("--microbench", action="store_true", help="time the frozen-matmul kernel alone")
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--quant", default="", help="microbench: weight format instead of the workload's")

@@ -950,6 +950,15 @@ void orc_linear_backward_raw(int type, int rows, int cols, const void* data, int
   l.rank = rank; l.alpha = alpha; l.a = (float*)a; l.b = (float*)b; l.ga = ga; l.gb = gb; l.lora_enabled = 1;
   orc_linear_backward(&l, x, dy, t, dx);
 }
+/* A launcher may have exported OMP_NUM_THREADS=1 (torchrun does); the timed CPU baseline asks for
+ * the host's cores itself. */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
 int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -100,6 +100,7 @@ def lib() -> C.CDLL:
         L.orc_linear_backward_raw.argtypes = [C.c_int] * 3 + [C.c_void_p, C.c_int, C.c_float] + [F32P] * 6 + [C.c_int, F32P]
         L.orc_num_threads.restype = C.c_int
         L.orc_set_act_int8.argtypes = [C.c_int]
+        L.orc_set_num_threads.argtypes = [C.c_int]
         L.orc_rmsnorm.argtypes = [F32P, F32P, C.c_int, C.c_int, C.c_float, C.c_int, F32P, F32P]
         L.orc_rmsnorm_backward.argtypes = [F32P, F32P, F32P, F32P, C.c_int, C.c_int, F32P]
         L.orc_rope_init.argtypes = [C.POINTER(_Rope), I32P, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, F32P, C.c_int]
@@ -182,6 +183,12 @@ def softmax_row(logits: np.ndarray):
     p = np.empty_like(logits)
     lse = lib().orc_softmax_row(fp(logits), logits.size, fp(p))
     return float(lse), p
+
+
+def set_num_threads(n: int) -> int:
+    """Worker threads of the oracle's row/head loops; returns the count in effect."""
+    lib().orc_set_num_threads(int(n))
+    return int(lib().orc_num_threads())
 
 
 def set_act_int8(on: bool) -> None:

@@ -274,6 +274,8 @@ __global__ void __launch_bounds__(128) lora_grads_kernel(const LoraGradArgs g) {
     if (lane == 0) s_red[warp] = v;
     __syncthreads();
     lmax = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    // up to a power of two: the f16 roundings below then do not depend on which tokens share the split
+    lmax = __int_as_float((__float_as_int(lmax) + 0x007FFFFF) & 0x7F800000);
     inv = lmax > 0.f ? 1.0f / lmax : 0.f;
   }
   for (int ch = 0; ch < nchunks; ++ch) {

@@ -1300,7 +1300,10 @@ __global__ void rowscale_max_kernel(const float* __restrict__ sc, int M, float* 
   float m = 0.f;
   for (int i = threadIdx.x; i < M; i += blockDim.x) m = fmaxf(m, sc[i]);
   m = block_max(m);
-  if (threadIdx.x == 0) out[0] = m > 0.f ? m : 1.f;
+  // rounded up to a power of two: dividing by it changes no mantissa, so what a row rounds to in
+  // f16 does not depend on which other rows share the batch (N ranks on shards of a batch then
+  // reproduce one rank on the whole of it up to the order of f32 sums)
+  if (threadIdx.x == 0) out[0] = m > 0.f ? __int_as_float((__float_as_int(m) + 0x007FFFFF) & 0x7F800000) : 1.f;
 }
 __global__ void scale_lowrank_rows_kernel(const __half* __restrict__ in, const float* __restrict__ sc,
                                           const float* __restrict__ smax, int M, __half* __restrict__ out) {

@@ -82,7 +82,7 @@ struct KParams {
   int* status;
   int tma_out;  // the epilogue stages [32 tokens x 128] tiles in shared memory and writes them with TMA
   long long* prof;  // measurement aid (RT_B200_QPROF): per-CTA cycle counts of each role's waits, else null
-  int dbg;  // measurement aid (RT_B200_DBG bit mask): 1 = epilogue skips its stores, 2 = unpack warps skip the conversion,
+  int dbg;  // measurement aid, only in builds with -DRT_B200_QPROF (RT_B200_DBG bit mask; the default build compiles every test of it out): 1 = epilogue skips its stores, 2 = unpack warps skip the conversion,
             // 16 = no operand loads at all: the MMAs run on whatever shared memory holds (results are garbage),
             // 32 = no MMAs are issued, 64 = no activation tiles are loaded, 128 = half of the MMAs of a step,
             // 256 = half of the unpack work of a step, 512 = no helpers for the last tile's epilogue,
@@ -91,6 +91,14 @@ struct KParams {
             // removes the MMA thread's operand waits while the loads run: without that back-pressure the
             // producers overrun the ring and the barriers' byte counts, and the launch faults.)
 };
+
+// Knock-out switches exist only in measurement builds: in the default build every test is the
+// constant 0 and the branches vanish from the roles' loops (the MMA-issuing thread's included).
+#ifdef RT_B200_QPROF
+#define QDBG(p, m) (((p).dbg & (m)) != 0)
+#else
+#define QDBG(p, m) false
+#endif
 
 // ------------------------------------------------------------------ unpackers
 __device__ __forceinline__ void store_chunk(uint8_t* dst, int r, int c, uint32_t a, uint32_t b, uint32_t c2,
@@ -386,7 +394,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     ++cnt;
     uint8_t* stage = stage_base + buf * (wide ? 4096 : 2048);
     const uint32_t tcol = tmem_base + acc * 256 + ((uint32_t)(wq * 32) << 16) + c * 32;
-    if (!wide && !(p.dbg & 4096)) {
+    if (!wide && !QDBG(p, 4096)) {
       // 16-bit output: the accumulator block arrives in mma-fragment layout (a thread holds two
       // neighbouring tokens of one feature), is rounded to pairs and written with transposing
       // matrix stores into a [32 tokens][32 features] block of 64-byte rows, 16-byte units
@@ -451,7 +459,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       float rs_lane = 1.0f;
       if (p.row_scale) { const int tok = m0 + c * 32 + lane; rs_lane = tok < p.M ? p.row_scale[tok] : 0.f; }
       __syncwarp();
-      if (!(p.dbg & 2048)) {
+      if (!QDBG(p, 2048)) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           float val = __uint_as_float(v[j]);
@@ -463,9 +471,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         }
       }
     }
-    if (!(p.dbg & 8)) fence_proxy_async_smem();
+    if (!QDBG(p, 8)) fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0 && !(p.dbg & 1024)) {
+    if (lane == 0 && !QDBG(p, 1024)) {
       if (p.accumulate) tma_reduce_add_2d(&tm_out, r0 + wq * 32, m0 + c * 32, stage);
       else tma_store_2d(&tm_out, r0 + wq * 32, m0 + c * 32, stage);
       bulk_commit_group();
@@ -478,7 +486,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
   // producer warps.  Helpers stage in the operand stages, which are idle once the last
   // accumulator is complete.
   const int n_my = worker < n_items ? (n_items - worker + n_workers - 1) / n_workers : 0;
-  const bool tail_help = p.tma_out && n_my > 0 && !(p.dbg & (1 | 512));
+  const bool tail_help = p.tma_out && n_my > 0 && !QDBG(p, (1 | 512));
   const int q_res = warp & 3;
   const int q_turns = (q_res == 0 || q_res == 2) ? 4 : 3;  // epilogue warp + helpers of this residue
   auto tail_helper = [&](int turn, int hslot) {
@@ -503,7 +511,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       uint32_t it = 0;
       bool ok = true;
       QG_PROF_BEGIN();
-      for (int item = worker; item < n_items && ok && !(p.dbg & 16); item += n_workers) {
+      for (int item = worker; item < n_items && ok && !QDBG(p, 16); item += n_workers) {
         QG_ITEM_DECODE(item);
         QG_TILE_ORIGIN();
         const int m_cta = m0 + (int)rank * tn_cta;  // this CTA's half of the tokens
@@ -517,14 +525,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           uint8_t* w_dst = sW + st * W_STAGE;
           // the leader's barrier counts the bytes both CTAs will bring
           if (rank == 0)
-            mbar_expect_tx(&full[st], ((p.dbg & 64) ? 0u : (uint32_t)p.TN * 128u) + ((is16 || lora) ? (uint32_t)(W_STAGE * n_cta) : 0u));
+            mbar_expect_tx(&full[st], (QDBG(p, 64) ? 0u : (uint32_t)p.TN * 128u) + ((is16 || lora) ? (uint32_t)(W_STAGE * n_cta) : 0u));
           const uint32_t fbar = PAIR ? mapa_u32(smem_u32(&full[st]), 0) : 0u;
           auto load2d = [&](void* dst, const CUtensorMap* map, int x, int y) {
             if (PAIR) tma_load_2d_pair(dst, map, x, y, fbar);
             else tma_load_2d(dst, map, x, y, &full[st]);
           };
           if (!lora) {
-            if (p.dbg & 64) {
+            if (QDBG(p, 64)) {
             } else if (p.b_mn) load2d(a_dst, &tm_act, 0, s * 64);  // [64 contraction rows x 64]
             else load2d(a_dst, &tm_act, s * 64, m_cta);
             if (is16) {
@@ -580,7 +588,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
 #endif
         const uint32_t d_tmem = tmem_base + acc * 256;
         for (int s = 0; s < n_steps; ++s) {
-          if (!(p.dbg & 16)) {
+          if (!QDBG(p, 16)) {
             { bool w_; QG_TIMED(1, w_ = mbar_wait<false>(&full[st], ph, p.status, 302)); if (!w_) { ok = false; break; } }
             QG_STEPSTAMP(5, itg);
             if (p.conv16) { bool w_; QG_TIMED(2, w_ = mbar_wait<false>(&w_ready[st], ph, p.status, 303)); if (!w_) { ok = false; break; } }
@@ -590,12 +598,12 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           const uint32_t a_lo = (uint32_t)a_d0 + (uint32_t)st * (W_STAGE >> 4);
           const uint32_t b_lo = (uint32_t)b_d0 + (uint32_t)st * (C::ACT_STAGE >> 4);
           if (it_first) { QG_STAMP(2); it_first = false; }
-          if (p.dbg & 32) {
+          if (QDBG(p, 32)) {
           } else if (s < s_main) {
             QG_TIMED(4, {
             umma_f16_split<PAIR>(d_tmem, a_lo, a_hi, b_lo, b_hi, p.idesc_main, (uint32_t)(s != 0));
             umma_f16_split<PAIR>(d_tmem, a_lo + a_k, a_hi, b_lo + b_k, b_hi, p.idesc_main, 1u);
-            if (!(p.dbg & 128)) {
+            if (!QDBG(p, 128)) {
               umma_f16_split<PAIR>(d_tmem, a_lo + 2 * a_k, a_hi, b_lo + 2 * b_k, b_hi, p.idesc_main, 1u);
               umma_f16_split<PAIR>(d_tmem, a_lo + 3 * a_k, a_hi, b_lo + 3 * b_k, b_hi, p.idesc_main, 1u);
             }
@@ -631,7 +639,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     uint32_t it = 0, rit = 0;
     bool ok = true;
     QG_PROF_BEGIN();
-    for (int item = worker; item < n_items && ok && !(p.dbg & 16); item += n_workers) {
+    for (int item = worker; item < n_items && ok && !QDBG(p, 16); item += n_workers) {
       QG_ITEM_DECODE(item);
       (void)tile; (void)s_begin;
       for (int s = 0; s < n_steps; ++s, ++it) {
@@ -674,10 +682,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
           const uint8_t* raw = sRaw + rs * RAW_STAGE;
           uint8_t* dst = sW + st * W_STAGE;
           QG_TIMED(2, {
-            if (!(p.dbg & 2)) {
+            if (!QDBG(p, 2)) {
               // 256 units (two bricks of 128) per tile; unit u: brick u >> 7 fills the 8 KB half u >> 7
-              if ((p.dbg & (256 | 32768)) || !p.act_f16 || (p.fmt != GGML_Q4_0 && p.fmt != GGML_Q4_K)) {
-                for (int u = tg; u < ((p.dbg & 256) ? 128 : 256); u += UTG) {
+              if (QDBG(p, (256 | 32768)) || !p.act_f16 || (p.fmt != GGML_Q4_0 && p.fmt != GGML_Q4_K)) {
+                for (int u = tg; u < (QDBG(p, 256) ? 128 : 256); u += UTG) {
                   if (p.act_f16) unpack_brick<false>(p.fmt, raw + (u >> 7) * p.brick_bytes, u & 127, dst + (u >> 7) * 8192);
                   else unpack_brick<true>(p.fmt, raw + (u >> 7) * p.brick_bytes, u & 127, dst + (u >> 7) * 8192);
                 }
@@ -689,7 +697,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
                 (unpack_units_f16<256 / UTG, UTG>(p.fmt, raw, p.brick_bytes, tg, dst));
               }
             }
-            if (!(p.dbg & 4)) fence_proxy_async_smem();
+            if (!QDBG(p, 4)) fence_proxy_async_smem();
           });
           mbar_arrive(&raw_empty[rs]);
           ++rit;
@@ -710,7 +718,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
     // ------------------------------------------------------------ packed-brick producer
     // Runs ahead of the stage ring: a brick pair is fetched as soon as its slot in the raw ring
     // is free, so its latency is not added to the time a weight stage is held.
-    if (lane == 0 && !is16 && !(p.dbg & 16)) {
+    if (lane == 0 && !is16 && !QDBG(p, 16)) {
       uint32_t rit = 0;
       bool ok = true;
       QG_PROF_BEGIN();
@@ -760,7 +768,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
       const bool row_ok = row < p.out_rows;
       const float bias_v = (p.bias != nullptr && row_ok) ? p.bias[row] : 0.f;
       for (int c = 0; c < p.TN / 32; ++c) {
-        if (p.tma_out && !(p.dbg & 1)) {
+        if (p.tma_out && !QDBG(p, 1)) {
           if (tail_help && (int)tcount == n_my - 1 && (c % q_turns) != 0) continue;  // a helper's block
           tma_chunk(acc, wq, c, r0, m0, bias_v, sOut + wq * C::OUT_WARP, out_chunk);
           continue;
@@ -768,7 +776,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
         uint32_t v[32];
         tmem_ld32(tmem_base + acc * 256 + ((uint32_t)(wq * 32) << 16) + c * 32, v);
         tmem_ld_wait();
-        if (row_ok && !(p.dbg & 1)) {
+        if (row_ok && !QDBG(p, 1)) {
           if (p.part != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -1032,11 +1040,14 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   cudaMemsetAsync(prof_dev, 0, (512 * 24 + 16 + 96) * sizeof(long long), st);
   p.prof = prof_dev;
 #endif
+  p.dbg = 0;
+#ifdef RT_B200_QPROF
   {
     static int dbg = -1;
     if (dbg < 0) { const char* e = getenv("RT_B200_DBG"); dbg = e ? atoi(e) : 0; }
     p.dbg = dbg;
   }
+#endif
 
   if (a.tok_mode) p.idesc_main = p.idesc_lora = umma_idesc(ab_fmt, ab_fmt, 1, 1, 128, 64);
   CUtensorMap tm_act, tm_w16, tm_lact, tm_lw;
@@ -1117,7 +1128,7 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
     const uint64_t es = a.out_dtype == OUT_F32 ? 4 : 2;
     if (!p.part && ((uintptr_t)a.out % 16 == 0) && ((uint64_t)p.ld_out * es) % 16 == 0) {
       rc = make_out_map(a.fixed_part ? nullptr : ctx, &tm_out, a.out, (uint64_t)a.M, (uint64_t)out_rows, (uint64_t)p.ld_out, a.out_dtype,
-                        a.out_dtype != OUT_F32 && !(p.dbg & 4096));
+                        a.out_dtype != OUT_F32 && !QDBG(p, 4096));
       if (rc) return rc;
       p.tma_out = 1;
     }

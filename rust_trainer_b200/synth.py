@@ -84,17 +84,17 @@ class ModelSpec:
 
 
 PRESETS = {
-    # BASELINE.json configs[0], [1]: Qwen3-0.6B shape
+    # Qwen3-0.6B shape
     "qwen3-0.6b": dict(arch="qwen3", n_layers=28, hidden=1024, n_heads=16, n_kv_heads=8, head_dim=128, ff=3072,
                        vocab=151936, qk_norm=True, tie_embeddings=True, rope_theta=1e6, rope_neox=True),
-    # configs[2]: Qwen2.5-0.5B shape
+    # Qwen2.5-0.5B shape
     "qwen2.5-0.5b": dict(arch="qwen2", n_layers=24, hidden=896, n_heads=14, n_kv_heads=2, head_dim=64, ff=4864,
                          vocab=151936, qk_norm=False, attn_bias=True, tie_embeddings=True, rope_theta=1e6),
-    # configs[3]: Llama-3.2-3B shape
+    # Llama-3.2-3B shape
     "llama-3.2-3b": dict(arch="llama", n_layers=28, hidden=3072, n_heads=24, n_kv_heads=8, head_dim=128, ff=8192,
                          vocab=128256, qk_norm=False, tie_embeddings=True, rope_theta=5e5, rope_neox=False,
                          rope_llama3_factor=32.0),
-    # configs[4]: Qwen3-4B shape
+    # Qwen3-4B shape
     "qwen3-4b": dict(arch="qwen3", n_layers=36, hidden=2560, n_heads=32, n_kv_heads=8, head_dim=128, ff=9728,
                      vocab=151936, qk_norm=True, tie_embeddings=False, rope_theta=1e6),
     # small shapes for tests (same code paths, seconds on the CPU oracle)

@@ -122,8 +122,8 @@ def test_empty_and_refused_inputs(ctx):
 
 
 def test_full_size_properties(ctx):
-    """BASELINE sizes (ffn_gate of the 0.6B shape, 8192 tokens), checked by properties that do
-    not need the oracle: linearity in x and the adjoint identity."""
+    """The benchmark's sizes (ffn_gate of the 0.6B shape, 3072 x 1024, at 8192 tokens), checked by
+    properties that do not need the oracle: linearity in x and the adjoint identity."""
     rng = np.random.default_rng(3)
     n, k, m = 3072, 1024, 8192
     f = rt.Frozen.from_f32(ctx, (rng.standard_normal((n, k)) * 0.02).astype(np.float32), Q.Q8_0)
@@ -154,3 +154,47 @@ def test_a_wait_that_runs_out_is_a_status_not_a_hang(ctx):
     x = rng.standard_normal((5, 64)).astype(np.float32)
     assert rel_l2(f.forward(x, 5), x @ O.dequant_rows(Q.Q8_0, Q.quantize(w, Q.Q8_0), 128, 64).T) < MATMUL_TOL
     f.close()
+
+
+def test_builtin_f32_and_q8_0_weights(ctx):
+    """FrozenWeight::{F32, Q8_0} (src/frozen.rs:33-187) with the reference's own unit test
+    (src/frozen.rs:206-228): Q8_0 forward within 0.02 of f32, and the adjoint identity
+    <dy, x.W^T> == <dy.W, x> to 1e-3 for both storages; plus exact rows and the oracle."""
+    r = O.Rng(3)
+    out, inp, t = 8, 64, 3  # the reference's test has 6 rows; 16-bit operand rows must be a multiple of 8 long here
+    w = r.vec_normal(out * inp, 0.1).reshape(out, inp)
+    x = r.vec_normal(t * inp, 1.0).reshape(t, inp)
+    dy = r.vec_normal(t * out, 1.0).reshape(t, out)
+    f = rt.Frozen.f32(ctx, w)
+    q = rt.Frozen.q8_0(ctx, w)
+    assert f.nbytes() == out * inp * 4 and q.nbytes() == out * inp // 32 * 4 + out * inp  # src/frozen.rs:181-186
+    yf, yq = f.forward(x, t), q.forward(x, t)
+    assert np.max(np.abs(yf - yq)) < 0.02
+    assert rel_l2(yf, x @ w.T) < 1e-3
+    for wq in (f, q):
+        y = wq.forward(x, t)
+        dx = np.zeros((t, inp), np.float32)
+        wq.backward_input(dy, t, dx)
+        lhs, rhs = float((dy * y).sum()), float((dx * x).sum())
+        assert abs(lhs - rhs) < 1e-3 * max(abs(lhs), 1.0)
+    assert np.array_equal(f.row(4), w[4])
+    from rust_trainer_b200.frozen import quantize_q8_0_f32scale
+
+    d, qs = quantize_q8_0_f32scale(w)
+    deq = (np.repeat(d, 32) * qs.astype(np.float32)).reshape(out, inp)
+    assert np.array_equal(q.row(5), deq[5])
+    f.close()
+    q.close()
+    # a wide f32 weight against the oracle's F32 rows, both directions
+    rng = np.random.default_rng(9)
+    n, k, m = 384, 1024, 300
+    w2 = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    x2 = rng.standard_normal((m, k)).astype(np.float32)
+    dy2 = rng.standard_normal((m, n)).astype(np.float32)
+    f2 = rt.Frozen.f32(ctx, w2)
+    assert rel_l2(f2.forward(x2, m), O.frozen_forward(0, n, k, w2, x2, m)) < MATMUL_TOL
+    dx, ref = np.zeros((m, k), np.float32), np.zeros((m, k), np.float32)
+    f2.backward_input(dy2, m, dx)
+    O.frozen_backward_input(0, n, k, w2, dy2, m, ref)
+    assert rel_l2(dx, ref) < MATMUL_TOL
+    f2.close()

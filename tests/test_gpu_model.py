@@ -269,3 +269,102 @@ def test_bad_batches_are_refused(ctx):
     assert lp.size == 0 and hits == 0
     gm.close()
     om.close()
+
+
+def test_target_counts_may_grow_between_training_and_scoring(ctx):
+    """A forward-only call with more targets than any earlier backward pass, followed by a
+    backward pass with a count in between: every buffer of the head is sized for the call at
+    hand, and the gradients equal those of a fresh model."""
+    spec, om, gm = _setup(ctx, "tiny-qwen3", "Q4_0")
+    om.close()
+    toks = synth.token_batch(spec, 1, 120, 4)[0]
+
+    def targets(n):
+        tp, tt = synth.answer_targets(toks, toks.size - n)
+        return tp, tt, np.full(tp.size, 1.0 / tp.size, np.float32)
+
+    tp, tt, w = targets(20)
+    gm.zero_grad()
+    gm.forward_backward([toks], tp, tt, w)
+    tp, tt, _ = targets(100)
+    gm.score([toks], tp, tt)
+    tp, tt, w = targets(60)
+    gm.zero_grad()
+    lp, _ = gm.forward_backward([toks], tp, tt, w)
+    g = _gpu_flat(gm, "ga", "gb")
+    gm.close()
+    spec2, om2, fresh = _setup(ctx, "tiny-qwen3", "Q4_0")
+    om2.close()
+    fresh.zero_grad()
+    lp2, _ = fresh.forward_backward([toks], tp, tt, w)
+    assert np.array_equal(lp, lp2) and np.array_equal(g, _gpu_flat(fresh, "ga", "gb"))
+    fresh.close()
+
+
+def test_greedy_prefix_and_packing_rule(ctx):
+    """greedy_prefix / greedy_prefix_batch / worth_packing (src/eval.rs:152-221): the argmax under
+    teacher forcing, per example or over a packed shared prompt, against the oracle's logits."""
+    from rust_trainer_b200 import evalgate
+
+    spec, om, gm = _setup(ctx, "tiny-qwen3", "Q8_0")
+    rng = np.random.default_rng(8)
+    prompt = rng.integers(0, spec.vocab, 30, dtype=np.int32)
+    exs = [(np.concatenate([prompt, rng.integers(0, spec.vocab, n, dtype=np.int32)]), 30) for n in (9, 14, 5)]
+
+    def oracle_prefix(tokens, start):
+        tp, tt = synth.answer_targets(tokens, start)
+        logits = om.score(tokens, tp, tt, want_logits=True)[2]
+        am = logits.shape[1] - 1 - np.argmax(logits[:, ::-1], axis=1)  # last maximum, as max_by gives
+        ok = 0
+        for a, t in zip(am, tt):
+            if a != t:
+                break
+            ok += 1
+        return ok, tp.size, am
+
+    # make the model right on a prefix: teach it nothing, but pick answers that ARE its argmax
+    toks0, start0 = exs[0]
+    _, _, am0 = oracle_prefix(toks0, start0)
+    toks0 = toks0.copy()
+    toks0[start0] = am0[0]  # first answer token = the greedy token after the prompt
+    exs[0] = (toks0, start0)
+    want = [oracle_prefix(t, s)[:2] for t, s in exs]
+    assert want[0][0] >= 1
+    assert [evalgate.greedy_prefix(gm, t, s) for t, s in exs] == want
+    assert evalgate.worth_packing([t for t, _ in exs]) is not None     # the prompt is most of every example
+    assert evalgate.greedy_prefix_batch(gm, exs) == want
+    far = [(rng.integers(0, spec.vocab, 20, dtype=np.int32), 10) for _ in range(2)]
+    assert evalgate.worth_packing([t for t, _ in far]) is None         # nothing shared: one batched pass instead
+    assert evalgate.greedy_prefix_batch(gm, far) == [oracle_prefix(t, s)[:2] for t, s in far]
+    assert evalgate.greedy_prefix(gm, prompt, 40) == (0, 0)            # answer_start beyond the tokens
+    gm.close()
+    om.close()
+
+
+def test_communicator_of_one_rank(ctx):
+    """rt_comm_*: a world of one goes through NCCL and leaves the gradient buffer as it was; a
+    second communicator on the same context is refused; without one the all-reduce is a no-op."""
+    spec, om, gm = _setup(ctx, "tiny-qwen3", "Q4_0")
+    om.close()
+    seqs, tp, tt, _ = _batch(spec, [50], seed=3)
+    w = np.full(tp.size, 1.0 / tp.size, np.float32)
+    gm.zero_grad()
+    gm.forward_backward(seqs, tp, tt, w)
+    g0 = _gpu_flat(gm, "ga", "gb")
+    gm.allreduce_grads()  # no communicator yet
+    assert np.array_equal(_gpu_flat(gm, "ga", "gb"), g0)
+    uid = rt.Context.comm_unique_id()
+    assert len(uid) == 128
+    ctx.comm_init_rank(1, 0, uid)
+    try:
+        assert ctx.comm_size() == 1
+        gm.allreduce_grads()
+        ctx.synchronize()
+        assert np.array_equal(_gpu_flat(gm, "ga", "gb"), g0)
+        with pytest.raises(rt.RtError):
+            ctx.comm_init_rank(1, 0, uid)
+    finally:
+        from rust_trainer_b200._lib import lib
+
+        lib().rt_comm_destroy(ctx._h)
+    gm.close()

@@ -1,0 +1,96 @@
+"""Parity against the CPU oracle at the sizes the benchmark runs, not only on toy shapes.
+
+  * the first configuration whole: Qwen3-0.6B shape, Q4_0, 28 layers, 4 x 256 tokens, loss on the
+    last half, LoRA r = 16 on all seven projections, one AdamW step (lr 1e-4, wd 0.01, clip 1.0),
+    the procedure of src/train.rs:316-381;
+  * two-layer cuts at the FULL widths and FULL vocabulary of all four model shapes, one sequence
+    of 512 or 2048 tokens, 96 targets, r = 16 and r = 32: long-sequence attention, the
+    cross-entropy and both head matmuls at 151 936 / 128 256 rows, Q6_K at 3072 columns, the
+    Q4_K + Q4_0 mix at hidden 896, and the r = 32 projections that do not share one low-rank chunk.
+
+Tolerances are the stated ones: per-token loss rel <= 1e-3, LoRA gradients cos >= 0.999 and
+rel-L2 <= 1e-2, adapter after the step rel-L2 <= 2e-2.
+"""
+import numpy as np
+import pytest
+
+import rust_trainer_b200 as rt
+from conftest import cosine, rel_l2
+from oracle import oracle as O
+from rust_trainer_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _flat(items, a, b):
+    return np.concatenate([np.concatenate([e[a].ravel(), e[b].ravel()]) for e in items])
+
+
+def _compare_step(ctx, spec, rank, alpha, seqs, answer_start, lr, wd, n_targets_cap=None):
+    tensors = synth.build_tensors(spec)
+    ads = synth.lora_adapters(spec, rank, alpha, seed=1234)
+    tps, tts, per_seq, off = [], [], [], 0
+    for s in seqs:
+        tp, tt = synth.answer_targets(s, answer_start)
+        if n_targets_cap:
+            tp, tt = tp[-n_targets_cap:], tt[-n_targets_cap:]
+        per_seq.append((tp, tt))
+        tps.append(tp + off)
+        tts.append(tt)
+        off += s.size
+    tp, tt = np.concatenate(tps), np.concatenate(tts)
+    w = np.full(tp.size, 1.0 / tp.size, np.float32)  # 1/batch_tokens, src/train.rs:330
+
+    gm = rt.Model(ctx, spec.config(), tensors)
+    gm.attach_lora(rank, alpha, None, 1234)
+    gm.load_adapters(ads)
+    gm.zero_grad()
+    lp_g, _ = gm.forward_backward(seqs, tp, tt, w)
+    g_g = _flat([l.lora() for l in gm.lora_linears()], "ga", "gb")
+    gm.optim_step(lr, 1.0, weight_decay=wd)
+    p_g = _flat([l.lora() for l in gm.lora_linears()], "a", "b")
+    gm.close()
+
+    om = O.OracleModel(spec.config(), tensors)
+    om.attach_lora(ads)
+    om.zero_grad()
+    lp_o, k = [], 0
+    for s, (tp_s, tt_s) in zip(seqs, per_seq):  # one sequence at a time, as the trainer does
+        lp_o.append(om.forward_backward(s, tp_s, tt_s, w[k:k + tp_s.size])[0])
+        k += tp_s.size
+    lp_o = np.concatenate(lp_o)
+    g_o = _flat(om.lora, "ga", "gb")
+    p_before = _flat(om.lora, "a", "b")
+    om.clip_grad_norm(1.0)
+    om.adamw_step({}, lr, wd=wd)
+    p_o = _flat(om.lora, "a", "b")
+    om.close()
+
+    assert np.max(np.abs(lp_g - lp_o) / np.abs(lp_o)) < 1e-3
+    assert rel_l2(g_g, g_o) < 1e-2 and cosine(g_g, g_o) > 0.999
+    assert rel_l2(p_g, p_o) < 2e-2
+    # the step itself, not only the parameters it started from
+    assert rel_l2(p_g - p_before, p_o - p_before) < 5e-2
+
+
+def test_first_configuration_whole(ctx):
+    spec = synth.preset("qwen3-0.6b", quant="Q4_0", seed=0)
+    toks = synth.token_batch(spec, 4, 256, 100)
+    _compare_step(ctx, spec, 16, 32.0, [toks[i] for i in range(4)], 128, lr=1e-4, wd=0.01)
+
+
+CUTS = [
+    # preset, quant, sequence length, rank
+    ("qwen3-0.6b", "Q8_0", 512, 16),
+    ("qwen2.5-0.5b", "Q4_K", 2048, 16),   # Q4_K where rows allow it (ffn_down), Q4_0 elsewhere
+    ("llama-3.2-3b", "Q6_K", 512, 16),    # Q6_K at 3072 and 8192 columns, rope_freqs divisors
+    ("qwen3-4b", "Q4_0", 512, 32),        # r = 32: q|k|v adapters do not fit one 64-wide chunk; untied head
+    ("qwen3-0.6b", "Q4_0", 2048, 32),
+]
+
+
+@pytest.mark.parametrize("name,quant,seq,rank", CUTS, ids=[f"{n}-{q}-T{s}-r{r}" for n, q, s, r in CUTS])
+def test_two_layer_cuts_at_full_width_and_vocabulary(ctx, name, quant, seq, rank):
+    spec = synth.preset(name, quant=quant, seed=1, n_layers=2)
+    toks = synth.token_batch(spec, 1, seq, 7)
+    _compare_step(ctx, spec, rank, 2.0 * rank, [toks[0]], 1, lr=1e-3, wd=0.0, n_targets_cap=96)
