@@ -288,23 +288,33 @@ static rt_status frozen_matmul_host(rt_frozen* f, int dir, const float* in_host,
   const size_t in_dim = dir == rt::QG_FWD ? f->w.cols : f->w.rows;
   const size_t out_dim = dir == rt::QG_FWD ? f->w.rows : f->w.cols;
   float* in_f32 = (float*)c->get_scratch(0, t * in_dim * sizeof(float));
-  __nv_bfloat16* in_bf = (__nv_bfloat16*)c->get_scratch(1, t * in_dim * sizeof(__nv_bfloat16));
+  // the 16-bit copy of the input and, behind it, one f32 factor per row
+  const size_t in16_bytes = (t * in_dim * sizeof(__half) + 255) / 256 * 256;
+  __nv_bfloat16* in_bf = (__nv_bfloat16*)c->get_scratch(1, in16_bytes + t * sizeof(float));
   float* out_f32 = (float*)c->get_scratch(2, t * out_dim * sizeof(float));
   if (!in_f32 || !in_bf || !out_f32) return c->fail(RT_ERR_CUDA, "out of device memory");
   RT_CUDA(c, cudaMemcpyAsync(in_f32, in_host, t * in_dim * sizeof(float), cudaMemcpyHostToDevice, c->stream));
   if (accumulate)
     RT_CUDA(c, cudaMemcpyAsync(out_f32, out_host, t * out_dim * sizeof(float), cudaMemcpyHostToDevice, c->stream));
-  // forward activations go in as f16 (11 significant bits); gradients as bf16 (f32's range)
-  const bool f16 = dir == rt::QG_FWD;
-  rt::launch_f32_to_16(in_f32, in_bf, t * in_dim, f16, c->stream);
+  // forward activations go in as f16 (11 significant bits); gradients as f16 rows divided by their
+  // largest magnitude, with that factor multiplied back onto the result row (f32's range, f16's bits)
+  const bool fwd = dir == rt::QG_FWD;
+  float* row_scale = nullptr;
+  if (fwd) {
+    rt::launch_f32_to_16(in_f32, in_bf, t * in_dim, true, c->stream);
+  } else {
+    row_scale = (float*)((uint8_t*)in_bf + in16_bytes);  // (scratch slot 3 holds the matmul's split-K partial sums)
+    rt::launch_normalize_rows(in_f32, (int)t, (int)in_dim, (__half*)in_bf, row_scale, c->stream);
+  }
   rt::QGemmArgs a;
   a.dir = dir;
   a.act = in_bf;
-  a.act_f16 = f16;
+  a.act_f16 = 1;
   a.M = (int)t;
   a.out = out_f32;
   a.out_dtype = rt::OUT_F32;
   a.accumulate = accumulate ? 1 : 0;
+  a.row_scale = row_scale;
   int rc = rt::frozen_matmul_launch(c, f->w, a);
   if (rc) return c->fail(rc, "qgemm launch failed");
   RT_CUDA(c, cudaMemcpyAsync(out_host, out_f32, t * out_dim * sizeof(float), cudaMemcpyDeviceToHost, c->stream));

@@ -65,6 +65,15 @@ static __half* lowrank_buf(rt_ctx* c, DevBuf& b, int& cur_rank, int M, int rank)
   return b.as<__half>();
 }
 
+// RT_B200_ATTN_LEGACY=1 keeps the mma.sync attention forward (an A/B switch while both exist)
+int attn_forward(rt_ctx* c, const __half* q, const __half* k, const __half* v, const int* seq_start, const int* gap, int M, int nh,
+                 int nkv, int hd, __half* o, float* lse) {
+  static int legacy = -1;
+  if (legacy < 0) { const char* e = getenv("RT_B200_ATTN_LEGACY"); legacy = (e && e[0] == '1') ? 1 : 0; }
+  if (legacy) return launch_attn_fwd(q, k, v, seq_start, gap, M, nh, nkv, hd, o, lse, c->stream);
+  return launch_attn_fwd_tc(c, q, k, v, seq_start, gap, M, nh, nkv, hd, o, lse);
+}
+
 static QWeight dense_view(const __half* p, int rows, int cols) {
   QWeight w;
   w.fmt = GGML_F16;
@@ -1136,8 +1145,8 @@ static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, fl
   launch_qk_rope_fwd(A.q_raw, A.k_raw, A.v_raw, A.qkv_pitch, g.qk_norm ? b.q_norm : nullptr,
                      g.qk_norm ? b.k_norm : nullptr, m->pos.as<int>(), m->rope_cos.as<float>(), m->rope_sin.as<float>(), M,
                      g.n_heads, g.n_kv_heads, g.head_dim, g.rot_dim, g.rope_neox, g.rms_eps, A.q16, A.k16, A.v16, st);
-  if (launch_attn_fwd(A.q16, A.k16, A.v16, m->seq_start.as<int>(), m->staged_gap ? m->gap.as<int>() : nullptr, M, g.n_heads,
-                      g.n_kv_heads, g.head_dim, A.o16, A.lse, st))
+  if (attn_forward(c, A.q16, A.k16, A.v16, m->seq_start.as<int>(), m->staged_gap ? m->gap.as<int>() : nullptr, M, g.n_heads,
+                   g.n_kv_heads, g.head_dim, A.o16, A.lse))
     return c->fail(RT_ERR_CUDA, "attention forward launch failed");
   if (h != x_in) RT_CUDA(c, cudaMemcpyAsync(h, x_in, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
   RT_TRY(linear_forward_dev(b.lin[3], m->lsc, A.o16, M, h, RT_DT_F32, 1, keep ? A.hs[3] : nullptr));

@@ -63,6 +63,8 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
                               const float* dscale, int M, void* dx, int accumulate,
                               const __half* hs_saved = nullptr, bool unscaled_f16_out = false);
 rt_status lora_refresh(rt_linear* l);
+int attn_forward(rt_ctx* c, const __half* q, const __half* k, const __half* v, const int* seq_start, const int* gap, int M, int nh,
+                 int nkv, int hd, __half* o, float* lse);
 }  // namespace rt
 
 // Linears that read the same input (q|k|v, gate|up) as ONE matmul: their packed weights lie

@@ -126,7 +126,10 @@ __global__ void normalize_rows_kernel(const float* __restrict__ x, int d, __half
   m = block_max(m);
   const float s = m > 0.f ? m : 1.f, inv = 1.f / s;
   for (int i = threadIdx.x; i < d; i += blockDim.x) y16[r * d + i] = __float2half_rn(xr[i] * inv);
-  if (threadIdx.x == 0) scale[r] = s;
+  // an all-zero row reports the factor 0, not 1: consumers that weigh rows by factor / largest
+  // factor (attention backward, the token contractions) must not see a 1 that towers over the
+  // real rows' small factors and pushes their f16 products into the subnormals
+  if (threadIdx.x == 0) scale[r] = m;
 }
 void launch_normalize_rows(const float* x, int rows, int d, __half* y16, float* scale, cudaStream_t st) {
   if (rows > 0) { normalize_rows_kernel<<<rows, 256, 0, st>>>(x, d, y16, scale); RT_COUNT_LAUNCH(1); }
@@ -235,7 +238,7 @@ rmsnorm_bwd_warp_kernel(const float* __restrict__ x, const float* __restrict__ w
       __half2 a = __floats2half2_rn(gv[k].x * inv, gv[k].y * inv), b = __floats2half2_rn(gv[k].z * inv, gv[k].w * inv);
       *(uint2*)(out16 + r * D + 4 * (lane + 32 * k)) = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
     }
-    if (lane == 0) scale[r] = sc;
+    if (lane == 0) scale[r] = m;
   }
 }
 void launch_rmsnorm_fwd(const float* x, const float* w, int rows, int d, float eps, __half* y16, cudaStream_t st) {
@@ -297,7 +300,7 @@ __global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __r
         __half2 a = __floats2half2_rn(v.x * inv, v.y * inv), b = __floats2half2_rn(v.z * inv, v.w * inv);
         *(uint2*)(out16 + r * d + 4 * i) = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
       }
-      if (threadIdx.x == 0) scale[r] = sc;
+      if (threadIdx.x == 0) scale[r] = m;
     }
     return;
   }
@@ -320,7 +323,7 @@ __global__ void rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __r
     m = block_max(m);  // includes a __syncthreads: this thread's stores above are its own re-reads below
     const float sc = m > 0.f ? m : 1.f, inv = 1.f / sc;
     for (int i = threadIdx.x; i < d; i += blockDim.x) out16[r * d + i] = __float2half_rn(out[r * d + i] * inv);
-    if (threadIdx.x == 0) scale[r] = sc;
+    if (threadIdx.x == 0) scale[r] = m;
   }
 }
 void launch_rmsnorm_bwd(const float* x, const float* w, const float* dn, const float* dres, int rows, int d, float eps,
@@ -627,11 +630,12 @@ qk_rope_bwd_reg_kernel(const float* __restrict__ dq, const float* __restrict__ d
   }
   if (common) s3[0] = s3[1] = s3[2] = fmaxf(s3[0], fmaxf(s3[1], s3[2]));
 #pragma unroll
+  if (threadIdx.x == 0) { sq[m] = s3[0]; sk[m] = s3[1]; sv[m] = s3[2]; }  // 0 for an all-zero row
+#pragma unroll
   for (int k = 0; k < 3; ++k) {
     s3[k] = s3[k] > 0.f ? s3[k] : 1.f;
     inv[k] = 1.f / s3[k];
   }
-  if (threadIdx.x == 0) { sq[m] = s3[0]; sk[m] = s3[1]; sv[m] = s3[2]; }
 #pragma unroll
   for (int t = 0; t < HPW; ++t) {
     const int h = warp + t * 8;
@@ -768,9 +772,10 @@ __global__ void qk_rope_bwd_kernel(const float* __restrict__ dq, const float* __
   for (int k = 0; k < 3; ++k) {
     float v = 0.f;
     for (int w = 0; w < nwarps; ++w) v = fmaxf(v, wmax[k][w]);
-    s3[k] = v > 0.f ? v : 1.f;
+    s3[k] = v;
   }
-  if (threadIdx.x == 0) { sq[m] = s3[0]; sk[m] = s3[1]; sv[m] = s3[2]; }
+  if (threadIdx.x == 0) { sq[m] = s3[0]; sk[m] = s3[1]; sv[m] = s3[2]; }  // 0 for an all-zero row
+  for (int k = 0; k < 3; ++k) s3[k] = s3[k] > 0.f ? s3[k] : 1.f;
   const int nq = nh * hd, nk = nkv * hd;
   const float i0 = 1.f / s3[0], i1 = 1.f / s3[1], i2 = 1.f / s3[2];
   for (int i = threadIdx.x * 4; i < nq + 2 * nk; i += blockDim.x * 4) {  // nq, nk are multiples of 4
@@ -934,8 +939,8 @@ __global__ void swiglu_bwd_cached_kernel(const DT* __restrict__ dh, const float*
   }
   if (threadIdx.x == 0) {
     const float f = in_scale ? in_scale[r] : 1.0f;
-    sg[r] = s_g * f;
-    su[r] = s_u * f;
+    sg[r] = mg * f;  // 0 for an all-zero row
+    su[r] = mu * f;
   }
 }
 // general row length: scalar, recomputed in the second pass
@@ -968,8 +973,8 @@ __global__ void swiglu_bwd_kernel(const DT* __restrict__ dh, const float* __rest
   }
   if (threadIdx.x == 0) {
     const float f = in_scale ? in_scale[r] : 1.0f;
-    sg[r] = s_g * f;
-    su[r] = s_u * f;
+    sg[r] = mg * f;  // 0 for an all-zero row
+    su[r] = mu * f;
   }
 }
 template <typename DT>

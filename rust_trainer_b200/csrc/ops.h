@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 
+struct rt_ctx;
+
 namespace rt {
 
 // hi = f16(w), lo = f16(w - hi): the two-term split of f32 frozen weights
@@ -91,5 +93,9 @@ int launch_attn_bwd(const __half* q, const __half* k, const __half* v, const __h
                     const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap,
                     int M, int nh, int nkv, int hd, float* delta /* [nh x M] scratch */, float* dq, float* dk, float* dv,
                     cudaStream_t st);
+
+// ---- attention_tc.cu: the same forward on tcgen05 / TMEM / TMA (waits report through the ctx status word)
+int launch_attn_fwd_tc(rt_ctx* c, const __half* q, const __half* k, const __half* v, const int* seq_start, const int* gap, int M,
+                       int nh, int nkv, int hd, __half* o, float* lse);
 
 }  // namespace rt

@@ -194,7 +194,7 @@ rt_status rt_op_attention(rt_ctx* c, const float* q, const float* k, const float
   launch_f32_to_16(qd, q16, nq, true, c->stream);
   launch_f32_to_16(kd, k16, nk, true, c->stream);
   launch_f32_to_16(vd, v16, nk, true, c->stream);
-  if (launch_attn_fwd(q16, k16, v16, ss, nullptr, (int)M, nh, nkv, hd, o16, lsed, c->stream))
+  if (attn_forward(c, q16, k16, v16, ss, nullptr, (int)M, nh, nkv, hd, o16, lsed))
     return c->fail(RT_ERR_CUDA, "attention forward launch failed");
   rt_status s = down_f16(c, o16, nullptr, 1, nq, o, t);
   if (s) return s;
@@ -224,7 +224,7 @@ rt_status rt_op_attention_backward(rt_ctx* c, const float* q, const float* k, co
   launch_f32_to_16(qd, q16, nq, true, c->stream);
   launch_f32_to_16(kd, k16, nk, true, c->stream);
   launch_f32_to_16(vd, v16, nk, true, c->stream);
-  if (launch_attn_fwd(q16, k16, v16, ss, nullptr, (int)M, nh, nkv, hd, o16, lsed, c->stream))
+  if (attn_forward(c, q16, k16, v16, ss, nullptr, (int)M, nh, nkv, hd, o16, lsed))
     return c->fail(RT_ERR_CUDA, "attention forward launch failed");
   // dO as the model passes it: f16 rows divided by their largest magnitude, factors beside them
   launch_normalize_rows(dod, (int)M, nh * hd, do16, sc, c->stream);

@@ -942,6 +942,15 @@ static int make_map_cached(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64
 }
 #define make_map(m, ...) make_map_cached(a.fixed_part ? nullptr : ctx, m, __VA_ARGS__)
 
+int tensor_map_f16_2d(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                      uint32_t box_rows) {
+  if (!g_encode) {
+    int rc = qgemm_init();
+    if (rc) return rc;
+  }
+  return make_map_cached(ctx, m, base, rows, cols, box_cols, box_rows, false);
+}
+
 // Output matrix [rows x cols] of f32 / bf16 / f16 with a row pitch of `ld` elements; box = 32 columns x 32 rows
 // (one epilogue warp's block), no swizzle (the epilogue writes the staging block row-major).
 static int make_out_map(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int dtype,

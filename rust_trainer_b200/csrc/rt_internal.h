@@ -66,6 +66,10 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a);
 // a two-term f16 split, the high term followed by the low term accumulated into an f32 result
 // (a 16-bit result cannot resolve the low term and skips it).
 int frozen_matmul_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a);
+// Tiled TMA descriptor of a row-major f16 matrix [rows x cols], box = box_cols x box_rows elements,
+// 128-byte swizzle (box_cols = 64); cached per ctx by (base, shape, box).
+int tensor_map_f16_2d(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                      uint32_t box_rows);
 size_t qgemm_smem_bytes();
 int qgemm_init();  // resolves the driver entry point for tensor-map encoding; sets smem attributes
 

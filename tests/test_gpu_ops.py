@@ -16,10 +16,11 @@ from rust_trainer_b200 import ops
 pytestmark = pytest.mark.gpu
 
 
-def _close16(got, want, tol=2e-3):
+def _close16(got, want, tol=2e-3, floor=0.0):
+    """`floor`: absolute slack for values below what an f16 row times its factor can hold."""
     scale = float(np.abs(want).max()) + 1e-30
-    assert float(np.abs(got - want).max()) <= tol * scale, (float(np.abs(got - want).max()), scale)
-    assert rel_l2(got, want) < 1e-3
+    assert float(np.abs(got - want).max()) <= tol * scale + floor, (float(np.abs(got - want).max()), scale)
+    assert np.linalg.norm(got.astype(np.float64) - want) <= 1e-3 * np.linalg.norm(want.astype(np.float64)) + floor * np.sqrt(got.size)
 
 
 @pytest.mark.parametrize("rows,d", [(1, 128), (37, 896), (64, 1024), (5, 2560), (33, 3072), (3, 100)])
@@ -161,6 +162,8 @@ def test_cross_entropy_rows_at_full_vocabulary(ctx, vocab):
         d = p.copy()
         d[target[r]] -= 1.0
         d *= weight[r]
-        _close16(res["dlogits"][r], d)
+        # p - onehot leaves the kernel as f16 (smallest step 6e-8) times the row's weight: a row the
+        # model is sure of has a gradient below that step, which comes out as exact zeros
+        _close16(res["dlogits"][r], d, floor=6e-8 * float(weight[r]))
         assert res["argmax"][r] == vocab - 1 - int(np.argmax(logits[r][::-1]))
     assert res["hits"] == hits
