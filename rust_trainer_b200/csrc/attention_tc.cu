@@ -44,7 +44,11 @@ struct FwdLayout {
   static constexpr uint32_t Q_BYTES = PAN * Q_PANEL, KV_BYTES = PAN * KV_PANEL, P_BYTES = BM * 128;
   static constexpr uint32_t OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + 2 * KV_BYTES;
   static constexpr uint32_t OFF_BAR = OFF_P + P_BYTES;
-  static constexpr uint32_t TOTAL = OFF_BAR + 256 + 1024;  // barriers, alignment slack
+  // Two CTAs must fit an SM's 228 KB (each also pays 1 KB of system shared memory), so the slack for
+  // rounding the base up to a 1 KB boundary is 768 bytes: enough for any base that is 256-byte
+  // aligned (the kernel checks, and reports a status instead of running, if it ever is not).
+  static constexpr uint32_t USED = OFF_BAR + 256;
+  static constexpr uint32_t TOTAL = USED + 768;
   static constexpr uint32_t TMEM_COLS = 256;               // S[2] (64 each) + O (hd <= 128)
   static constexpr uint32_t COL_S = 0, COL_O = 2 * BN;
 };
@@ -57,13 +61,18 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 template <int HD>
 __global__ void __launch_bounds__(192, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const int* __restrict__ seq_start,
-                   const int2* __restrict__ gap, int M, int nh, int nkv, float scale, __half* __restrict__ o,
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                   const int* __restrict__ seq_start, const int2* __restrict__ gap, int M, int nh, int nkv, float scale,
                    float* __restrict__ lse, int* status) {
   using L = FwdLayout<HD>;
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
-  uint8_t* sm = smem_raw + (((raw + 1023u) & ~1023u) - raw);  // 128-byte-swizzled tiles start on 1 KB boundaries
+  const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;  // 128-byte-swizzled tiles start on 1 KB boundaries
+  if (pad + L::USED > L::TOTAL) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, RT_ERR_CUDA);
+    return;
+  }
+  uint8_t* sm = smem_raw + pad;
   uint64_t* bars = (uint64_t*)(sm + L::OFF_BAR);
   uint64_t* q_full = bars + 0;
   uint64_t* k_full = bars + 1;   // [2]
@@ -77,7 +86,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint32_t* tmem_slot = (uint32_t*)(bars + 16);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * BM, h = blockIdx.y, g = h / (nh / nkv);
+  // the last query tiles of a sequence see the most keys: start them first
+  const int m0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BM, h = blockIdx.y, g = h / (nh / nkv);
   const int kbeg = seq_start[m0];
   const int kend = min(m0 + BM, M);
   const int ntiles = (kend - kbeg + BN - 1) / BN;
@@ -98,6 +108,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     prefetch_tmap(&tm_q);
     prefetch_tmap(&tm_k);
     prefetch_tmap(&tm_v);
+    prefetch_tmap(&tm_o);
   }
   if (warp == 5) {
     tmem_alloc(tmem_slot, L::TMEM_COLS);
@@ -193,38 +204,44 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tc_fence_before();
       mbar_arrive(&s_free[b]);
       // a tile wholly below the diagonal of every row, inside every row's sequence, needs no mask
-      const bool need_mask = (n0 + BN - 1 > m0) || (n0 < ss_last) || gap != nullptr;
-      float mx = -INFINITY;
-      if (need_mask) {
+      const bool need_mask = (n0 + BN - 1 > m0) || (n0 < ss_last);
+      // four interleaved chains for the maximum and for the sum: a thread is alone on its row, so the
+      // instruction-level parallelism has to come from inside the row
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (need_mask || gap != nullptr) {
+        // valid keys of this row inside the tile: columns [c_lo, c_hi], minus the hidden range
+        const int c_lo = ss_i - n0, c_hi = i - n0;
+        const int g_lo = gp.x - n0, g_hi = gp.y - n0;
 #pragma unroll
         for (int c = 0; c < BN; ++c) {
-          const int j = n0 + c;
-          const bool valid = j <= i && j >= ss_i && (j < gp.x || j >= gp.y);
+          const bool valid = c >= c_lo && c <= c_hi && (c < g_lo || c >= g_hi);
           const float s = valid ? __uint_as_float(v[c]) * sl2 : -INFINITY;
           v[c] = __float_as_uint(s);
-          mx = fmaxf(mx, s);
+          mx4[c & 3] = fmaxf(mx4[c & 3], s);
         }
       } else {
 #pragma unroll
         for (int c = 0; c < BN; ++c) {
           const float s = __uint_as_float(v[c]) * sl2;
           v[c] = __float_as_uint(s);
-          mx = fmaxf(mx, s);
+          mx4[c & 3] = fmaxf(mx4[c & 3], s);
         }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const bool grow = mx > m_used + RESCALE_THRESHOLD;  // also the first tile that shows the row a key
       const float m_new = grow ? mx : m_used;
       const float corr = grow ? ex2_approx(m_used - m_new) : 1.0f;  // 0 when the row had seen nothing
       const float mref = m_new == -INFINITY ? 0.f : m_new;
       l_run *= corr;
       uint32_t ph[BN / 2];
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < BN; c += 2) {
         const float p0 = ex2_approx(__uint_as_float(v[c]) - mref), p1 = ex2_approx(__uint_as_float(v[c + 1]) - mref);
-        sum += p0 + p1;
+        sum4[(c >> 1) & 3] += p0 + p1;
         ph[c >> 1] = pack_h2(p0, p1);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l_run += sum;
       m_used = m_new;
       // P's buffer is free, and O is at rest, once the previous tile's P.V has completed
@@ -254,27 +271,36 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_arrive(p_full);
     }
     if (ok && mbar_wait(pv_done, (uint32_t)(ntiles - 1) & 1, status, SITE_PVDONE)) {
+      // O / l as f16 into Q's shared memory (every product that read Q has completed), in the
+      // layout of a swizzled TMA box, then one bulk store per 64-column panel: rows past the end of
+      // the batch are clipped by the tensor map
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-      __half* orow = o + ((size_t)i * nh + h) * HD;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t t[32];
         tmem_ld32(lane_addr + L::COL_O + c * 32, t);
         tmem_ld_wait();
-        if (i < M) {
+        uint8_t* orow = sm + L::OFF_Q + (c >> 1) * L::Q_PANEL + r * 128;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            uint4 w;
-            w.x = pack_h2(__uint_as_float(t[8 * k]) * inv, __uint_as_float(t[8 * k + 1]) * inv);
-            w.y = pack_h2(__uint_as_float(t[8 * k + 2]) * inv, __uint_as_float(t[8 * k + 3]) * inv);
-            w.z = pack_h2(__uint_as_float(t[8 * k + 4]) * inv, __uint_as_float(t[8 * k + 5]) * inv);
-            w.w = pack_h2(__uint_as_float(t[8 * k + 6]) * inv, __uint_as_float(t[8 * k + 7]) * inv);
-            *(uint4*)(orow + c * 32 + k * 8) = w;
-          }
+        for (int k = 0; k < 4; ++k) {
+          uint4 w;
+          w.x = pack_h2(__uint_as_float(t[8 * k]) * inv, __uint_as_float(t[8 * k + 1]) * inv);
+          w.y = pack_h2(__uint_as_float(t[8 * k + 2]) * inv, __uint_as_float(t[8 * k + 3]) * inv);
+          w.z = pack_h2(__uint_as_float(t[8 * k + 4]) * inv, __uint_as_float(t[8 * k + 5]) * inv);
+          w.w = pack_h2(__uint_as_float(t[8 * k + 6]) * inv, __uint_as_float(t[8 * k + 7]) * inv);
+          const int chunk = (c & 1) * 4 + k;
+          *(uint4*)(orow + ((chunk ^ (r & 7)) << 4)) = w;
         }
       }
       if (i < M) lse[(size_t)h * M + i] = m_used / LOG2E + logf(l_run);
+      fence_proxy_async_smem();
+      named_barrier_sync(1, 128);  // the four softmax warps only
+      if (threadIdx.x == 0) {
+        for (int p = 0; p < L::PAN; ++p) tma_store_2d(&tm_o, h * HD + p * 64, m0, sm + L::OFF_Q + p * L::Q_PANEL);
+        bulk_commit_group();
+        bulk_wait_group_read<0>();  // shared memory may go once the store has read it
+      }
     }
   }
 
@@ -300,14 +326,573 @@ int fwd_tc_impl(rt_ctx* c, const __half* q, const __half* k, const __half* v, co
     if (cudaFuncSetAttribute(attn_fwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::TOTAL) != cudaSuccess) return 3;
     attr = true;
   }
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   if (tensor_map_f16_2d(c, &tq, q, (uint64_t)M, (uint64_t)nh * HD, 64, BM)) return 3;
+  if (tensor_map_f16_2d(c, &to, o, (uint64_t)M, (uint64_t)nh * HD, 64, BM)) return 3;
   if (tensor_map_f16_2d(c, &tk, k, (uint64_t)M, (uint64_t)nkv * HD, 64, BN)) return 3;
   if (tensor_map_f16_2d(c, &tv, v, (uint64_t)M, (uint64_t)nkv * HD, 64, BN)) return 3;
   dim3 grid((M + BM - 1) / BM, nh);
-  attn_fwd_tc_kernel<HD><<<grid, 192, L::TOTAL, c->stream>>>(tq, tk, tv, seq_start, gap, M, nh, nkv, 1.0f / sqrtf((float)HD), o,
+  attn_fwd_tc_kernel<HD><<<grid, 192, L::TOTAL, c->stream>>>(tq, tk, tv, to, seq_start, gap, M, nh, nkv, 1.0f / sqrtf((float)HD),
                                                             lse, c->status_dev);
   RT_COUNT_LAUNCH(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+
+// ==================================================================== backward
+//   (reference src/attention.rs:272-328)  dV = P^T.dO, dP = dO.V^T, dS = P*(dP - rowsum(P*dP))/sqrt(hd),
+//   dQ = dS.K, dK = dS^T.Q, the K/V gradients summed over the query heads that share a KV head.
+// Two kernels, so that every output element has exactly one writer (no float atomics: the same
+// bits every run).  P is recomputed from the forward's log-sum-exp.  dO arrives as f16 rows
+// divided by a per-row factor; a query row enters the sums over queries with weight
+// factor / top (top = a power of two >= the largest factor, so the weights change no mantissa),
+// and dQ rows get their own factor back.
+
+// ------------------------------------------------------------------ dK, dV: one CTA per (128 keys, KV head)
+// Thread = key row = TMEM lane.  K and V stay in shared memory; the (query head of the group) x
+// (query tiles of 64 rows that can see these keys) work list streams through double buffers.
+// Per item: S^T = K.Q^T and dP^T = V.dO^T into TMEM (two buffers each), the threads turn them
+// into P^T and dS^T (f16, shared memory), then dV += P^T.dO and dK += dS^T.Q with Q and dO read
+// MN-major from the same tiles.  TMEM: 2 x 64 + 2 x 64 + hd + hd columns (512 for hd = 128).
+constexpr int BQ = 64;  // query rows per work item
+enum { SITE_B_KV = 451, SITE_B_QFREE, SITE_B_QFULL, SITE_B_STFREE, SITE_B_PFULL, SITE_B_SFULL, SITE_B_PDDONE, SITE_B_END };
+
+template <int HD>
+struct DkvLayout {
+  static constexpr int PAN = HD / 64;
+  static constexpr uint32_t KV_PANEL = 128 * 128, Q_PANEL = BQ * 128;
+  static constexpr uint32_t KV_BYTES = PAN * KV_PANEL, Q_BYTES = PAN * Q_PANEL, P_BYTES = 128 * 128;
+  static constexpr uint32_t OFF_K = 0, OFF_V = KV_BYTES, OFF_Q = 2 * KV_BYTES, OFF_DO = OFF_Q + 2 * Q_BYTES;
+  static constexpr uint32_t OFF_PT = OFF_DO + 2 * Q_BYTES, OFF_DST = OFF_PT + P_BYTES, OFF_AUX = OFF_DST + P_BYTES;
+  static constexpr uint32_t AUX_BYTES = 6 * BQ * 4;  // lse, delta, weight, seq_start, gap.x, gap.y per query row
+  static constexpr uint32_t OFF_BAR = OFF_AUX + 2 * AUX_BYTES;
+  static constexpr uint32_t USED = OFF_BAR + 256, TOTAL = USED + 1024;
+  static constexpr uint32_t COL_ST = 0, COL_DPT = 2 * BQ, COL_DV = 4 * BQ, COL_DK = 4 * BQ + HD;
+  static constexpr uint32_t TMEM_COLS = 512;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                        const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                        const float* __restrict__ do_scale, const float* __restrict__ row_scale,
+                        const float* __restrict__ lse, const float* __restrict__ delta, const int* __restrict__ seq_start,
+                        const int2* __restrict__ gap, int M, int nh, int nkv, float scale, float* __restrict__ dk,
+                        float* __restrict__ dv, int* status) {
+  using L = DkvLayout<HD>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* sm = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  uint64_t* bars = (uint64_t*)(sm + L::OFF_BAR);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* q_full = bars + 1;    // [2]  Q, dO and the per-query vectors of an item
+  uint64_t* q_free = bars + 3;    // [2]
+  uint64_t* s_full = bars + 5;    // [2]  S^T and dP^T of an item are in TMEM
+  uint64_t* st_free = bars + 7;   // [2]  ... and have been read
+  uint64_t* p_full = bars + 9;    //      P^T and dS^T are in shared memory
+  uint64_t* pd_done = bars + 10;  //      the item's dV, dK products have completed
+  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * 128, g = blockIdx.y, group = nh / nkv;
+  // queries that can see these keys: [n0, end of the sequence holding the tile's last key)
+  const int last_key = min(n0 + 128, M) - 1;
+  int qend;
+  {
+    const int ss_last = seq_start[last_key];
+    int e = last_key + 1;
+    while (e + 128 <= M && seq_start[e + 127] == ss_last) e += 128;
+    while (e < M && seq_start[e] == ss_last) ++e;
+    qend = e;
+  }
+  const int nqt = (qend - n0 + BQ - 1) / BQ;
+  const int n_items = group * nqt;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1 + 32);  // the expect-tx arrival + one per producer lane (the vectors)
+      mbar_init(&q_free[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&st_free[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(pd_done, 1);
+    mbar_fence_init();
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_do);
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, L::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
+  const float inv_top = row_scale ? 1.0f / fmaxf(do_scale[0], 1e-38f) : 1.0f;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer: TMA + the per-query vectors
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * L::KV_BYTES);
+      for (int p = 0; p < L::PAN; ++p) {
+        tma_load_2d(sm + L::OFF_K + p * L::KV_PANEL, &tm_k, g * HD + p * 64, n0, kv_full);
+        tma_load_2d(sm + L::OFF_V + p * L::KV_PANEL, &tm_v, g * HD + p * 64, n0, kv_full);
+      }
+    }
+    for (int it = 0; it < n_items; ++it) {
+      const int b = it & 1;
+      const int h = g * group + it / nqt, m0 = n0 + (it % nqt) * BQ;
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(&q_free[b], (((uint32_t)it >> 1) & 1) ^ 1, status, SITE_B_QFREE);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane == 0) {
+        mbar_expect_tx(&q_full[b], 2 * L::Q_BYTES);
+        for (int p = 0; p < L::PAN; ++p) {
+          tma_load_2d(sm + L::OFF_Q + b * L::Q_BYTES + p * L::Q_PANEL, &tm_q, h * HD + p * 64, m0, &q_full[b]);
+          tma_load_2d(sm + L::OFF_DO + b * L::Q_BYTES + p * L::Q_PANEL, &tm_do, h * HD + p * 64, m0, &q_full[b]);
+        }
+      }
+      float* aux = (float*)(sm + L::OFF_AUX + b * L::AUX_BYTES);
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int il = lane + 32 * k, m = m0 + il;
+        const bool in = m < M;
+        aux[il] = in ? lse[(size_t)h * M + m] * LOG2E : 0.f;
+        aux[BQ + il] = in ? delta[(size_t)h * M + m] : 0.f;
+        aux[2 * BQ + il] = in ? (row_scale ? row_scale[m] * inv_top : 1.0f) : 0.f;
+        ((int*)aux)[3 * BQ + il] = in ? seq_start[m] : 0x7fffffff;
+        const int2 gp = (gap && in) ? gap[m] : make_int2(0, 0);
+        ((int*)aux)[4 * BQ + il] = gp.x;
+        ((int*)aux)[5 * BQ + il] = gp.y;
+      }
+      mbar_arrive(&q_full[b]);  // (release: the vectors above are visible to whoever passes the barrier)
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ MMA issue (one thread)
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc(0, 0, 0, 0, 128, BQ);
+      const uint32_t idesc_g = umma_idesc(0, 0, 0, 1, 128, HD);
+      const uint32_t sK = smem_u32(sm + L::OFF_K), sV = smem_u32(sm + L::OFF_V), sQ = smem_u32(sm + L::OFF_Q);
+      const uint32_t sDO = smem_u32(sm + L::OFF_DO), sPt = smem_u32(sm + L::OFF_PT), sDSt = smem_u32(sm + L::OFF_DST);
+      bool ok = n_items == 0 || mbar_wait(kv_full, 0, status, SITE_B_KV);
+      auto issue_s = [&](int it) -> bool {
+        const int b = it & 1;
+        const uint32_t u = ((uint32_t)it >> 1) & 1;
+        if (!mbar_wait(&q_full[b], u, status, SITE_B_QFULL)) return false;
+        if (!mbar_wait(&st_free[b], u ^ 1, status, SITE_B_STFREE)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint64_t ad = umma_desc_sw128(sK + (kk >> 2) * L::KV_PANEL + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(sQ + b * L::Q_BYTES + (kk >> 2) * L::Q_PANEL + (kk & 3) * 32, 16, 1024);
+          umma_f16(tmem_base + L::COL_ST + b * BQ, ad, bd, idesc_s, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint64_t ad = umma_desc_sw128(sV + (kk >> 2) * L::KV_PANEL + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(sDO + b * L::Q_BYTES + (kk >> 2) * L::Q_PANEL + (kk & 3) * 32, 16, 1024);
+          umma_f16(tmem_base + L::COL_DPT + b * BQ, ad, bd, idesc_s, kk != 0);
+        }
+        umma_commit(&s_full[b]);
+        return true;
+      };
+      if (ok && n_items > 0) ok = issue_s(0);
+      for (int it = 0; it < n_items && ok; ++it) {
+        if (it + 1 < n_items && !issue_s(it + 1)) { ok = false; break; }
+        const int b = it & 1;
+        if (!mbar_wait(p_full, (uint32_t)it & 1, status, SITE_B_PFULL)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk) {
+          // dO / Q tiles: rows are queries (the contraction), 64-column panels Q_PANEL bytes apart are hd (N)
+          const uint64_t ap = umma_desc_sw128(sPt + kk * 32, 16, 1024);
+          const uint64_t bo = umma_desc_sw128(sDO + b * L::Q_BYTES + kk * 2048, L::Q_PANEL, 1024);
+          umma_f16(tmem_base + L::COL_DV, ap, bo, idesc_g, (it | kk) != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk) {
+          const uint64_t ad = umma_desc_sw128(sDSt + kk * 32, 16, 1024);
+          const uint64_t bq = umma_desc_sw128(sQ + b * L::Q_BYTES + kk * 2048, L::Q_PANEL, 1024);
+          umma_f16(tmem_base + L::COL_DK, ad, bq, idesc_g, (it | kk) != 0);
+        }
+        umma_commit(pd_done);
+        umma_commit(&q_free[b]);
+      }
+      if (ok && n_items > 0) mbar_wait(&q_free[(n_items - 1) & 1], ((uint32_t)(n_items - 1) >> 1) & 1, status, SITE_B_END);
+    }
+  } else {
+    // ------------------------------------------------------------ thread = key row = TMEM lane
+    const int r = warp * 32 + lane;
+    const int j = n0 + r;
+    const float sl2 = scale * LOG2E;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    bool ok = true;
+    for (int it = 0; it < n_items; ++it) {
+      const int b = it & 1;
+      const int m0 = n0 + (it % nqt) * BQ;
+      if (!mbar_wait(&s_full[b], ((uint32_t)it >> 1) & 1, status, SITE_B_SFULL)) { ok = false; break; }
+      // (completed long ago; passing it orders the producer lanes' per-query vectors before the reads below)
+      if (!mbar_wait(&q_full[b], ((uint32_t)it >> 1) & 1, status, SITE_B_QFULL)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t st[BQ], dp[BQ];
+      tmem_ld32(lane_addr + L::COL_ST + b * BQ, st);
+      tmem_ld32(lane_addr + L::COL_ST + b * BQ + 32, st + 32);
+      tmem_ld32(lane_addr + L::COL_DPT + b * BQ, dp);
+      tmem_ld32(lane_addr + L::COL_DPT + b * BQ + 32, dp + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&st_free[b]);
+      const float* aux = (const float*)(sm + L::OFF_AUX + b * L::AUX_BYTES);
+      const int* auxi = (const int*)aux;
+      // element (key row j, query column i): P^T (weighted) and dS^T
+      uint32_t ph[BQ / 2], dh[BQ / 2];
+      // a tile whose queries all lie past these keys, inside one sequence, without hidden ranges, needs no mask
+      const bool need_mask = (m0 < n0 + 127) || gap != nullptr || auxi[3 * BQ + BQ - 1] > n0;  // (rows past the batch carry INT_MAX)
+#pragma unroll
+      for (int c = 0; c < BQ; c += 2) {
+        float pv[2], dsv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int il = c + e;
+          float p = ex2_approx(__uint_as_float(st[il]) * sl2 - aux[il]) * aux[2 * BQ + il];
+          if (need_mask) {
+            const int i = m0 + il;
+            const bool valid = j <= i && j >= auxi[3 * BQ + il] && (j < auxi[4 * BQ + il] || j >= auxi[5 * BQ + il]);
+            p = valid ? p : 0.f;
+          }
+          pv[e] = p;
+          dsv[e] = p * (__uint_as_float(dp[il]) - aux[BQ + il]) * scale;
+        }
+        ph[c >> 1] = pack_h2(pv[0], pv[1]);
+        dh[c >> 1] = pack_h2(dsv[0], dsv[1]);
+      }
+      if (it > 0) {
+        if (!mbar_wait(pd_done, (uint32_t)(it - 1) & 1, status, SITE_B_PDDONE)) { ok = false; break; }
+      }
+      uint8_t* prow = sm + L::OFF_PT + r * 128;
+      uint8_t* drow = sm + L::OFF_DST + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = make_uint4(ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
+        *(uint4*)(drow + ((c ^ (r & 7)) << 4)) = make_uint4(dh[4 * c], dh[4 * c + 1], dh[4 * c + 2], dh[4 * c + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    // write this key row's gradients (zeros when no query sees these keys)
+    const float sc = do_scale[0];
+    if (n_items > 0 && ok) ok = mbar_wait(pd_done, (uint32_t)(n_items - 1) & 1, status, SITE_B_PDDONE);
+    if (ok) {
+      tc_fence_after();
+      float* dkrow = dk + ((size_t)j * nkv + g) * HD;
+      float* dvrow = dv + ((size_t)j * nkv + g) * HD;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t a[32], bb[32];
+        if (n_items > 0) {
+          tmem_ld32(lane_addr + L::COL_DK + c * 32, a);
+          tmem_ld32(lane_addr + L::COL_DV + c * 32, bb);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) a[k] = bb[k] = 0u;
+        }
+        if (j < M) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            *(float4*)(dkrow + c * 32 + 4 * k) = make_float4(__uint_as_float(a[4 * k]) * sc, __uint_as_float(a[4 * k + 1]) * sc,
+                                                             __uint_as_float(a[4 * k + 2]) * sc, __uint_as_float(a[4 * k + 3]) * sc);
+            *(float4*)(dvrow + c * 32 + 4 * k) = make_float4(__uint_as_float(bb[4 * k]) * sc, __uint_as_float(bb[4 * k + 1]) * sc,
+                                                             __uint_as_float(bb[4 * k + 2]) * sc, __uint_as_float(bb[4 * k + 3]) * sc);
+          }
+        }
+      }
+    }
+  }
+
+  if (*(volatile int*)status != 0) {
+    for (int k = 0; k < 1000; ++k) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, L::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ dQ: one CTA per (128 query rows, head)
+// Thread = query row = TMEM lane.  Q and dO stay in shared memory; per key tile of 64:
+// S = Q.K^T and dP = dO.V^T into TMEM, dS = P*(dP - delta)*scale to shared memory in f16, then
+// dQ += dS.K with K read MN-major from the tile that just served Q.K^T.  Single K/V buffers: two
+// CTAs share an SM (112 KB, 256 TMEM columns each) and fill each other's waits.
+enum { SITE_Q_QDO = 471, SITE_Q_KFREE, SITE_Q_VFREE, SITE_Q_KFULL, SITE_Q_VFULL, SITE_Q_SFREE, SITE_Q_DSFULL, SITE_Q_SFULL, SITE_Q_DQDONE, SITE_Q_END };
+
+template <int HD>
+struct DqLayout {
+  static constexpr int PAN = HD / 64;
+  static constexpr uint32_t Q_PANEL = BM * 128, KV_PANEL = BN * 128;
+  static constexpr uint32_t Q_BYTES = PAN * Q_PANEL, KV_BYTES = PAN * KV_PANEL, DS_BYTES = BM * 128;
+  static constexpr uint32_t OFF_Q = 0, OFF_DO = Q_BYTES, OFF_K = 2 * Q_BYTES, OFF_V = OFF_K + KV_BYTES, OFF_DS = OFF_V + KV_BYTES;
+  static constexpr uint32_t OFF_BAR = OFF_DS + DS_BYTES;
+  static constexpr uint32_t USED = OFF_BAR + 256, TOTAL = USED + 768;
+  static constexpr uint32_t COL_S = 0, COL_DP = BN, COL_DQ = 2 * BN, TMEM_COLS = 256;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(192, 2)
+attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                      const float* __restrict__ do_scale, const float* __restrict__ row_scale, const float* __restrict__ lse,
+                      const float* __restrict__ delta, const int* __restrict__ seq_start, const int2* __restrict__ gap, int M,
+                      int nh, int nkv, float scale, float* __restrict__ dq, int* status) {
+  using L = DqLayout<HD>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
+  if (pad + L::USED > L::TOTAL) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, RT_ERR_CUDA);
+    return;
+  }
+  uint8_t* sm = smem_raw + pad;
+  uint64_t* bars = (uint64_t*)(sm + L::OFF_BAR);
+  uint64_t* qdo_full = bars + 0;
+  uint64_t* k_full = bars + 1;
+  uint64_t* v_full = bars + 2;
+  uint64_t* k_free = bars + 3;
+  uint64_t* v_free = bars + 4;
+  uint64_t* s_full = bars + 5;
+  uint64_t* s_free = bars + 6;
+  uint64_t* ds_full = bars + 7;
+  uint64_t* dq_done = bars + 8;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the last query tiles of a sequence see the most keys: start them first
+  const int m0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BM, h = blockIdx.y, g = h / (nh / nkv);
+  const int kbeg = seq_start[m0];
+  const int kend = min(m0 + BM, M);
+  const int ntiles = (kend - kbeg + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    mbar_init(k_full, 1);
+    mbar_init(v_full, 1);
+    mbar_init(k_free, 1);
+    mbar_init(v_free, 1);
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 128);
+    mbar_init(ds_full, 128);
+    mbar_init(dq_done, 1);
+    mbar_fence_init();
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_do);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, L::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(qdo_full, 2 * L::Q_BYTES);
+      for (int p = 0; p < L::PAN; ++p) {
+        tma_load_2d(sm + L::OFF_Q + p * L::Q_PANEL, &tm_q, h * HD + p * 64, m0, qdo_full);
+        tma_load_2d(sm + L::OFF_DO + p * L::Q_PANEL, &tm_do, h * HD + p * 64, m0, qdo_full);
+      }
+      for (int n = 0; n < ntiles; ++n) {
+        const uint32_t free_parity = ((uint32_t)n & 1) ^ 1;
+        const int n0 = kbeg + n * BN;
+        if (!mbar_wait(v_free, free_parity, status, SITE_Q_VFREE)) break;
+        mbar_expect_tx(v_full, L::KV_BYTES);
+        for (int p = 0; p < L::PAN; ++p) tma_load_2d(sm + L::OFF_V + p * L::KV_PANEL, &tm_v, g * HD + p * 64, n0, v_full);
+        if (!mbar_wait(k_free, free_parity, status, SITE_Q_KFREE)) break;
+        mbar_expect_tx(k_full, L::KV_BYTES);
+        for (int p = 0; p < L::PAN; ++p) tma_load_2d(sm + L::OFF_K + p * L::KV_PANEL, &tm_k, g * HD + p * 64, n0, k_full);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc(0, 0, 0, 0, BM, BN);
+      const uint32_t idesc_g = umma_idesc(0, 0, 0, 1, BM, HD);
+      const uint32_t sQ = smem_u32(sm + L::OFF_Q), sDO = smem_u32(sm + L::OFF_DO), sK = smem_u32(sm + L::OFF_K);
+      const uint32_t sV = smem_u32(sm + L::OFF_V), sDS = smem_u32(sm + L::OFF_DS);
+      bool ok = mbar_wait(qdo_full, 0, status, SITE_Q_QDO);
+      for (int n = 0; n < ntiles && ok; ++n) {
+        const uint32_t ph = (uint32_t)n & 1;
+        if (!mbar_wait(k_full, ph, status, SITE_Q_KFULL) || !mbar_wait(v_full, ph, status, SITE_Q_VFULL) ||
+            !mbar_wait(s_free, ph ^ 1, status, SITE_Q_SFREE)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint64_t ad = umma_desc_sw128(sDO + (kk >> 2) * L::Q_PANEL + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(sV + (kk >> 2) * L::KV_PANEL + (kk & 3) * 32, 16, 1024);
+          umma_f16(tmem_base + L::COL_DP, ad, bd, idesc_s, kk != 0);
+        }
+        umma_commit(v_free);  // V served dP only: its next tile may load under the rest of this one
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint64_t ad = umma_desc_sw128(sQ + (kk >> 2) * L::Q_PANEL + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(sK + (kk >> 2) * L::KV_PANEL + (kk & 3) * 32, 16, 1024);
+          umma_f16(tmem_base + L::COL_S, ad, bd, idesc_s, kk != 0);
+        }
+        umma_commit(s_full);
+        if (!mbar_wait(ds_full, ph, status, SITE_Q_DSFULL)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint64_t ad = umma_desc_sw128(sDS + kk * 32, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(sK + kk * 2048, L::KV_PANEL, 1024);  // K tile read MN-major: rows are keys
+          umma_f16(tmem_base + L::COL_DQ, ad, bd, idesc_g, (n | kk) != 0);
+        }
+        umma_commit(dq_done);
+        umma_commit(k_free);
+      }
+      if (ok) mbar_wait(k_free, (uint32_t)(ntiles - 1) & 1, status, SITE_Q_END);
+    }
+  } else {
+    const int r = warp * 32 + lane;
+    const int i = m0 + r;
+    const int ss_i = i < M ? seq_start[i] : 0x7fffffff;
+    const int2 gp = (gap && i < M) ? gap[i] : make_int2(0, 0);
+    const int ss_last = seq_start[kend - 1];
+    const float l2 = i < M ? lse[(size_t)h * M + i] * LOG2E : 0.f;
+    const float dl = i < M ? delta[(size_t)h * M + i] : 0.f;
+    const float sl2 = scale * LOG2E;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    bool ok = true;
+    for (int n = 0; n < ntiles; ++n) {
+      const uint32_t ph = (uint32_t)n & 1;
+      const int n0 = kbeg + n * BN;
+      if (!mbar_wait(s_full, ph, status, SITE_Q_SFULL)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sv[BN], dp[BN];
+      tmem_ld32(lane_addr + L::COL_S, sv);
+      tmem_ld32(lane_addr + L::COL_S + 32, sv + 32);
+      tmem_ld32(lane_addr + L::COL_DP, dp);
+      tmem_ld32(lane_addr + L::COL_DP + 32, dp + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(s_free);
+      const bool need_mask = (n0 + BN - 1 > m0) || (n0 < ss_last) || gap != nullptr;
+      const int c_lo = ss_i - n0, c_hi = i - n0, g_lo = gp.x - n0, g_hi = gp.y - n0;
+      uint32_t dh[BN / 2];
+#pragma unroll
+      for (int c = 0; c < BN; c += 2) {
+        float dsv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int cc = c + e;
+          float p = ex2_approx(__uint_as_float(sv[cc]) * sl2 - l2);
+          if (need_mask) p = (cc >= c_lo && cc <= c_hi && (cc < g_lo || cc >= g_hi)) ? p : 0.f;
+          dsv[e] = p * (__uint_as_float(dp[cc]) - dl) * scale;
+        }
+        dh[c >> 1] = pack_h2(dsv[0], dsv[1]);
+      }
+      if (n > 0) {
+        if (!mbar_wait(dq_done, (uint32_t)(n - 1) & 1, status, SITE_Q_DQDONE)) { ok = false; break; }
+      }
+      uint8_t* drow = sm + L::OFF_DS + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *(uint4*)(drow + ((c ^ (r & 7)) << 4)) = make_uint4(dh[4 * c], dh[4 * c + 1], dh[4 * c + 2], dh[4 * c + 3]);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(ds_full);
+    }
+    if (ok && mbar_wait(dq_done, (uint32_t)(ntiles - 1) & 1, status, SITE_Q_DQDONE)) {
+      tc_fence_after();
+      // a query row's gradient carries only that row's factor
+      const float sc = row_scale ? (i < M ? row_scale[i] : 0.f) : do_scale[0];
+      float* qrow = dq + ((size_t)i * nh + h) * HD;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t a[32];
+        tmem_ld32(lane_addr + L::COL_DQ + c * 32, a);
+        tmem_ld_wait();
+        if (i < M) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            *(float4*)(qrow + c * 32 + 4 * k) = make_float4(__uint_as_float(a[4 * k]) * sc, __uint_as_float(a[4 * k + 1]) * sc,
+                                                            __uint_as_float(a[4 * k + 2]) * sc, __uint_as_float(a[4 * k + 3]) * sc);
+        }
+      }
+    }
+  }
+
+  if (*(volatile int*)status != 0) {
+    for (int k = 0; k < 1000; ++k) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, L::TMEM_COLS);
+  }
+}
+
+// delta[h, m] = sum_d O * dO (the row sum of P * dP, src/attention.rs:282-287)
+template <int HD>
+__global__ void attn_delta_tc_kernel(const __half* __restrict__ o, const __half* __restrict__ dO, int M, int nh,
+                                     float* __restrict__ delta) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= M * nh) return;
+  const int m = w / nh, h = w % nh;
+  const __half* a = o + ((size_t)m * nh + h) * HD;
+  const __half* b = dO + ((size_t)m * nh + h) * HD;
+  float s = 0.f;
+  for (int i = lane * 2; i < HD; i += 64) {
+    float2 x = __half22float2(*(const __half2*)(a + i)), y = __half22float2(*(const __half2*)(b + i));
+    s += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) delta[(size_t)h * M + m] = s;
+}
+
+template <int HD>
+int bwd_tc_impl(rt_ctx* c, const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO,
+                const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int2* gap, int M,
+                int nh, int nkv, float* delta, float* dq, float* dk, float* dv) {
+  using LK = DkvLayout<HD>;
+  using LQ = DqLayout<HD>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(attn_bwd_dkdv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LK::TOTAL) != cudaSuccess) return 3;
+    if (cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LQ::TOTAL) != cudaSuccess) return 3;
+    attr = true;
+  }
+  CUtensorMap tq128, tdo128, tk64, tv64, tk128, tv128, tq64, tdo64;
+  if (tensor_map_f16_2d(c, &tq128, q, (uint64_t)M, (uint64_t)nh * HD, 64, 128)) return 3;
+  if (tensor_map_f16_2d(c, &tdo128, dO, (uint64_t)M, (uint64_t)nh * HD, 64, 128)) return 3;
+  if (tensor_map_f16_2d(c, &tq64, q, (uint64_t)M, (uint64_t)nh * HD, 64, 64)) return 3;
+  if (tensor_map_f16_2d(c, &tdo64, dO, (uint64_t)M, (uint64_t)nh * HD, 64, 64)) return 3;
+  if (tensor_map_f16_2d(c, &tk128, k, (uint64_t)M, (uint64_t)nkv * HD, 64, 128)) return 3;
+  if (tensor_map_f16_2d(c, &tv128, v, (uint64_t)M, (uint64_t)nkv * HD, 64, 128)) return 3;
+  if (tensor_map_f16_2d(c, &tk64, k, (uint64_t)M, (uint64_t)nkv * HD, 64, 64)) return 3;
+  if (tensor_map_f16_2d(c, &tv64, v, (uint64_t)M, (uint64_t)nkv * HD, 64, 64)) return 3;
+  const float scale = 1.0f / sqrtf((float)HD);
+  cudaStream_t st = c->stream;
+  const int warps = M * nh;
+  attn_delta_tc_kernel<HD><<<(warps * 32 + 255) / 256, 256, 0, st>>>(o, dO, M, nh, delta);
+  dim3 gkv((M + 127) / 128, nkv), gq((M + BM - 1) / BM, nh);
+  attn_bwd_dkdv_tc_kernel<HD><<<gkv, 192, LK::TOTAL, st>>>(tk128, tv128, tq64, tdo64, do_scale, row_scale, lse, delta, seq_start, gap,
+                                                          M, nh, nkv, scale, dk, dv, c->status_dev);
+  attn_bwd_dq_tc_kernel<HD><<<gq, 192, LQ::TOTAL, st>>>(tq128, tdo128, tk64, tv64, do_scale, row_scale, lse, delta, seq_start, gap, M,
+                                                       nh, nkv, scale, dq, c->status_dev);
+  RT_COUNT_LAUNCH(3);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
@@ -318,6 +903,15 @@ int launch_attn_fwd_tc(rt_ctx* c, const __half* q, const __half* k, const __half
   if (M <= 0) return 0;
   if (hd == 128) return fwd_tc_impl<128>(c, q, k, v, seq_start, (const int2*)gap, M, nh, nkv, o, lse);
   if (hd == 64) return fwd_tc_impl<64>(c, q, k, v, seq_start, (const int2*)gap, M, nh, nkv, o, lse);
+  return 1;
+}
+
+int launch_attn_bwd_tc(rt_ctx* c, const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
+                       const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap,
+                       int M, int nh, int nkv, int hd, float* delta, float* dq, float* dk, float* dv) {
+  if (M <= 0) return 0;
+  if (hd == 128) return bwd_tc_impl<128>(c, q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, (const int2*)gap, M, nh, nkv, delta, dq, dk, dv);
+  if (hd == 64) return bwd_tc_impl<64>(c, q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, (const int2*)gap, M, nh, nkv, delta, dq, dk, dv);
   return 1;
 }
 

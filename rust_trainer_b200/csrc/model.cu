@@ -74,6 +74,15 @@ int attn_forward(rt_ctx* c, const __half* q, const __half* k, const __half* v, c
   return launch_attn_fwd_tc(c, q, k, v, seq_start, gap, M, nh, nkv, hd, o, lse);
 }
 
+int attn_backward(rt_ctx* c, const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
+                  const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap, int M,
+                  int nh, int nkv, int hd, float* delta, float* dq, float* dk, float* dv) {
+  static int legacy = -1;
+  if (legacy < 0) { const char* e = getenv("RT_B200_ATTN_LEGACY"); legacy = (e && e[0] == '1') ? 1 : 0; }
+  if (legacy) return launch_attn_bwd(q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, gap, M, nh, nkv, hd, delta, dq, dk, dv, c->stream);
+  return launch_attn_bwd_tc(c, q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, gap, M, nh, nkv, hd, delta, dq, dk, dv);
+}
+
 static QWeight dense_view(const __half* p, int rows, int cols) {
   QWeight w;
   w.fmt = GGML_F16;
@@ -1200,10 +1209,10 @@ static rt_status block_backward(rt_model* m, int li, int M, const float* x_in, c
   // takes the factors per query row (largest one in amax)
   RT_TRY(linear_backward_dev(b.lin[3], m->lsc, A.o16, dy16, sc_y, M, m->dO16.p, 0, HS(3), true));
   launch_rowscale_max(sc_y, M, m->amax.as<float>(), st);
-  if (launch_attn_bwd(A.q16, A.k16, A.v16, A.o16, m->dO16.as<__half>(),
-                      m->amax.as<float>(), sc_y, A.lse, m->seq_start.as<int>(), m->staged_gap ? m->gap.as<int>() : nullptr, M,
-                      g.n_heads, g.n_kv_heads, g.head_dim,
-                      m->delta.as<float>(), m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>(), st))
+  if (attn_backward(c, A.q16, A.k16, A.v16, A.o16, m->dO16.as<__half>(),
+                    m->amax.as<float>(), sc_y, A.lse, m->seq_start.as<int>(), m->staged_gap ? m->gap.as<int>() : nullptr, M,
+                    g.n_heads, g.n_kv_heads, g.head_dim,
+                    m->delta.as<float>(), m->dq.as<float>(), m->dk.as<float>(), m->dv.as<float>()))
     return c->fail(RT_ERR_CUDA, "attention backward launch failed");
   const size_t qd = (size_t)g.n_heads * g.head_dim, kvd = (size_t)g.n_kv_heads * g.head_dim;
   __half* dq16 = m->dq16.as<__half>();

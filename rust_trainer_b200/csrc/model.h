@@ -63,6 +63,9 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
                               const float* dscale, int M, void* dx, int accumulate,
                               const __half* hs_saved = nullptr, bool unscaled_f16_out = false);
 rt_status lora_refresh(rt_linear* l);
+int attn_backward(rt_ctx* c, const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
+                  const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap, int M,
+                  int nh, int nkv, int hd, float* delta, float* dq, float* dk, float* dv);
 int attn_forward(rt_ctx* c, const __half* q, const __half* k, const __half* v, const int* seq_start, const int* gap, int M, int nh,
                  int nkv, int hd, __half* o, float* lse);
 }  // namespace rt

@@ -95,6 +95,9 @@ int launch_attn_bwd(const __half* q, const __half* k, const __half* v, const __h
                     cudaStream_t st);
 
 // ---- attention_tc.cu: the same forward on tcgen05 / TMEM / TMA (waits report through the ctx status word)
+int launch_attn_bwd_tc(rt_ctx* c, const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
+                       const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap,
+                       int M, int nh, int nkv, int hd, float* delta, float* dq, float* dk, float* dv);
 int launch_attn_fwd_tc(rt_ctx* c, const __half* q, const __half* k, const __half* v, const int* seq_start, const int* gap, int M,
                        int nh, int nkv, int hd, __half* o, float* lse);
 

@@ -229,7 +229,7 @@ rt_status rt_op_attention_backward(rt_ctx* c, const float* q, const float* k, co
   // dO as the model passes it: f16 rows divided by their largest magnitude, factors beside them
   launch_normalize_rows(dod, (int)M, nh * hd, do16, sc, c->stream);
   launch_rowscale_max(sc, (int)M, amax, c->stream);
-  if (launch_attn_bwd(q16, k16, v16, o16, do16, amax, sc, lsed, ss, nullptr, (int)M, nh, nkv, hd, delta, dqd, dkd, dvd, c->stream))
+  if (attn_backward(c, q16, k16, v16, o16, do16, amax, sc, lsed, ss, nullptr, (int)M, nh, nkv, hd, delta, dqd, dkd, dvd))
     return c->fail(RT_ERR_CUDA, "attention backward launch failed");
   RT_CUDA(c, cudaMemcpyAsync(dq, dqd, nq * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
   RT_CUDA(c, cudaMemcpyAsync(dk, dkd, nk * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
