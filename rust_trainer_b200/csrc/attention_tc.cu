@@ -53,6 +53,24 @@ struct FwdLayout {
   static constexpr uint32_t COL_S = 0, COL_O = 2 * BN;
 };
 
+// Timeline stamps of one CTA's first softmax thread, measurement builds only (-DRT_B200_QPROF).
+#ifdef RT_B200_QPROF
+__device__ unsigned long long g_attn_prof[512];
+#define AT_STAMP(slot)                                                                     \
+  do {                                                                                     \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && (slot) < 512) g_attn_prof[(slot)] = globaltimer_ns(); \
+  } while (0)
+#ifndef RT_B200_ATTN_PROF_KERNEL
+#define RT_B200_ATTN_PROF_KERNEL 0  // 0: forward, 1: dK/dV, 2: dQ
+#endif
+#else
+#define AT_STAMP(slot) do { } while (0)
+#define RT_B200_ATTN_PROF_KERNEL -1
+#endif
+#define AT_STAMP_F(slot) do { if (RT_B200_ATTN_PROF_KERNEL == 0) AT_STAMP(slot); } while (0)
+#define AT_STAMP_K(slot) do { if (RT_B200_ATTN_PROF_KERNEL == 1) AT_STAMP(slot); } while (0)
+#define AT_STAMP_Q(slot) do { if (RT_B200_ATTN_PROF_KERNEL == 2) AT_STAMP(slot); } while (0)
+
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *(uint32_t*)&h;
@@ -100,9 +118,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_init(&k_free[i], 1);
       mbar_init(&v_free[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 128);
+      mbar_init(&s_free[i], 4);   // one arrival per softmax warp
     }
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 4);
     mbar_init(pv_done, 1);
     mbar_fence_init();
     prefetch_tmap(&tm_q);
@@ -192,17 +210,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
+    AT_STAMP_F(0);
     for (int n = 0; n < ntiles; ++n) {
       const int b = n & 1;
       const int n0 = kbeg + n * BN;
       if (!mbar_wait(&s_full[b], (uint32_t)(n >> 1) & 1, status, SITE_SFULL)) { ok = false; break; }
+      AT_STAMP_F(1 + 6 * n);
       tc_fence_after();
       uint32_t v[BN];
       tmem_ld32(lane_addr + L::COL_S + b * BN, v);
       tmem_ld32(lane_addr + L::COL_S + b * BN + 32, v + 32);
       tmem_ld_wait();
+      AT_STAMP_F(2 + 6 * n);
       tc_fence_before();
-      mbar_arrive(&s_free[b]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[b]);
       // a tile wholly below the diagonal of every row, inside every row's sequence, needs no mask
       const bool need_mask = (n0 + BN - 1 > m0) || (n0 < ss_last);
       // four interleaved chains for the maximum and for the sum: a thread is alone on its row, so the
@@ -245,8 +267,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       l_run += sum;
       m_used = m_new;
       // P's buffer is free, and O is at rest, once the previous tile's P.V has completed
+      AT_STAMP_F(3 + 6 * n);
       if (n > 0) {
         if (!mbar_wait(pv_done, (uint32_t)(n - 1) & 1, status, SITE_PVDONE)) { ok = false; break; }
+        AT_STAMP_F(4 + 6 * n);
         tc_fence_after();
         if (__any_sync(0xffffffffu, grow && corr != 1.0f)) {
 #pragma unroll
@@ -266,10 +290,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
       for (int c = 0; c < 8; ++c)
         *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = make_uint4(ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
+      AT_STAMP_F(5 + 6 * n);
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      AT_STAMP_F(6 + 6 * n);
     }
+    AT_STAMP_F(500);
     if (ok && mbar_wait(pv_done, (uint32_t)(ntiles - 1) & 1, status, SITE_PVDONE)) {
       // O / l as f16 into Q's shared memory (every product that read Q has completed), in the
       // layout of a swizzled TMA box, then one bulk store per 64-column panel: rows past the end of
@@ -301,6 +329,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         bulk_commit_group();
         bulk_wait_group_read<0>();  // shared memory may go once the store has read it
       }
+      AT_STAMP_F(501);
     }
   }
 
@@ -355,6 +384,7 @@ int fwd_tc_impl(rt_ctx* c, const __half* q, const __half* k, const __half* v, co
 // into P^T and dS^T (f16, shared memory), then dV += P^T.dO and dK += dS^T.Q with Q and dO read
 // MN-major from the same tiles.  TMEM: 2 x 64 + 2 x 64 + hd + hd columns (512 for hd = 128).
 constexpr int BQ = 64;  // query rows per work item
+constexpr int BWD_THREADS = 320, BWD_TMA_WARP = 8, BWD_MMA_WARP = 9;  // warps 0-7 compute
 enum { SITE_B_KV = 451, SITE_B_QFREE, SITE_B_QFULL, SITE_B_STFREE, SITE_B_PFULL, SITE_B_SFULL, SITE_B_PDDONE, SITE_B_END };
 
 template <int HD>
@@ -362,17 +392,20 @@ struct DkvLayout {
   static constexpr int PAN = HD / 64;
   static constexpr uint32_t KV_PANEL = 128 * 128, Q_PANEL = BQ * 128;
   static constexpr uint32_t KV_BYTES = PAN * KV_PANEL, Q_BYTES = PAN * Q_PANEL, P_BYTES = 128 * 128;
-  static constexpr uint32_t OFF_K = 0, OFF_V = KV_BYTES, OFF_Q = 2 * KV_BYTES, OFF_DO = OFF_Q + 2 * Q_BYTES;
-  static constexpr uint32_t OFF_PT = OFF_DO + 2 * Q_BYTES, OFF_DST = OFF_PT + P_BYTES, OFF_AUX = OFF_DST + P_BYTES;
+  // Q, dO and the per-query vectors go through a ring of NS items: a slot is released by the item's
+  // last product, so with three slots the fetch of item n+2 runs under all of item n+1
+  static constexpr int NS = 3;
+  static constexpr uint32_t OFF_K = 0, OFF_V = KV_BYTES, OFF_Q = 2 * KV_BYTES, OFF_DO = OFF_Q + NS * Q_BYTES;
+  static constexpr uint32_t OFF_PT = OFF_DO + NS * Q_BYTES, OFF_DST = OFF_PT + P_BYTES, OFF_AUX = OFF_DST + P_BYTES;
   static constexpr uint32_t AUX_BYTES = 6 * BQ * 4;  // lse, delta, weight, seq_start, gap.x, gap.y per query row
-  static constexpr uint32_t OFF_BAR = OFF_AUX + 2 * AUX_BYTES;
+  static constexpr uint32_t OFF_BAR = OFF_AUX + NS * AUX_BYTES;
   static constexpr uint32_t USED = OFF_BAR + 256, TOTAL = USED + 1024;
   static constexpr uint32_t COL_ST = 0, COL_DPT = 2 * BQ, COL_DV = 4 * BQ, COL_DK = 4 * BQ + HD;
   static constexpr uint32_t TMEM_COLS = 512;
 };
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                         const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                         const float* __restrict__ do_scale, const float* __restrict__ row_scale,
@@ -385,13 +418,14 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   uint8_t* sm = smem_raw + (((raw + 1023u) & ~1023u) - raw);
   uint64_t* bars = (uint64_t*)(sm + L::OFF_BAR);
   uint64_t* kv_full = bars + 0;
-  uint64_t* q_full = bars + 1;    // [2]  Q, dO and the per-query vectors of an item
-  uint64_t* q_free = bars + 3;    // [2]
-  uint64_t* s_full = bars + 5;    // [2]  S^T and dP^T of an item are in TMEM
-  uint64_t* st_free = bars + 7;   // [2]  ... and have been read
-  uint64_t* p_full = bars + 9;    //      P^T and dS^T are in shared memory
-  uint64_t* pd_done = bars + 10;  //      the item's dV, dK products have completed
-  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+  uint64_t* q_full = bars + 1;    // [NS] Q, dO and the per-query vectors of an item
+  uint64_t* q_free = bars + 4;    // [NS]
+  uint64_t* s_full = bars + 7;    // [2]  S^T and dP^T of an item are in TMEM
+  uint64_t* st_free = bars + 9;   // [2]  ... and have been read
+  uint64_t* p_full = bars + 11;   //      P^T and dS^T are in shared memory
+  uint64_t* pd_done = bars + 12;  //      the item's dV, dK products have completed
+  uint32_t* tmem_slot = (uint32_t*)(bars + 14);
+  constexpr int NS = L::NS;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * 128, g = blockIdx.y, group = nh / nkv;
@@ -410,13 +444,15 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&q_full[i], 1 + 32);  // the expect-tx arrival + one per producer lane (the vectors)
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&q_full[i], 2);  // the expect-tx arrival + the producer warp's arrival after the vectors
       mbar_init(&q_free[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&st_free[i], 128);
     }
-    mbar_init(p_full, 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&st_free[i], 8);  // one arrival per compute warp
+    }
+    mbar_init(p_full, 8);
     mbar_init(pd_done, 1);
     mbar_fence_init();
     prefetch_tmap(&tm_k);
@@ -424,7 +460,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     prefetch_tmap(&tm_q);
     prefetch_tmap(&tm_do);
   }
-  if (warp == 5) {
+  if (warp == BWD_MMA_WARP) {
     tmem_alloc(tmem_slot, L::TMEM_COLS);
     tmem_relinquish();
   }
@@ -434,7 +470,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
   const float inv_top = row_scale ? 1.0f / fmaxf(do_scale[0], 1e-38f) : 1.0f;
 
-  if (warp == 4) {
+  if (warp == BWD_TMA_WARP) {
     // ------------------------------------------------------------ producer: TMA + the per-query vectors
     if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * L::KV_BYTES);
@@ -444,10 +480,10 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       }
     }
     for (int it = 0; it < n_items; ++it) {
-      const int b = it & 1;
+      const int b = it % NS;
       const int h = g * group + it / nqt, m0 = n0 + (it % nqt) * BQ;
       bool ok = true;
-      if (lane == 0) ok = mbar_wait(&q_free[b], (((uint32_t)it >> 1) & 1) ^ 1, status, SITE_B_QFREE);
+      if (lane == 0) ok = mbar_wait(&q_free[b], (((uint32_t)(it / NS)) & 1) ^ 1, status, SITE_B_QFREE);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (lane == 0) {
@@ -470,9 +506,10 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         ((int*)aux)[4 * BQ + il] = gp.x;
         ((int*)aux)[5 * BQ + il] = gp.y;
       }
-      mbar_arrive(&q_full[b]);  // (release: the vectors above are visible to whoever passes the barrier)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_full[b]);  // (release: the warp's vectors are visible to whoever passes the barrier)
     }
-  } else if (warp == 5) {
+  } else if (warp == BWD_MMA_WARP) {
     // ------------------------------------------------------------ MMA issue (one thread)
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc(0, 0, 0, 0, 128, BQ);
@@ -481,21 +518,21 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       const uint32_t sDO = smem_u32(sm + L::OFF_DO), sPt = smem_u32(sm + L::OFF_PT), sDSt = smem_u32(sm + L::OFF_DST);
       bool ok = n_items == 0 || mbar_wait(kv_full, 0, status, SITE_B_KV);
       auto issue_s = [&](int it) -> bool {
-        const int b = it & 1;
+        const int b = it & 1, rb = it % NS;  // TMEM buffer, ring slot
         const uint32_t u = ((uint32_t)it >> 1) & 1;
-        if (!mbar_wait(&q_full[b], u, status, SITE_B_QFULL)) return false;
+        if (!mbar_wait(&q_full[rb], (uint32_t)(it / NS) & 1, status, SITE_B_QFULL)) return false;
         if (!mbar_wait(&st_free[b], u ^ 1, status, SITE_B_STFREE)) return false;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint64_t ad = umma_desc_sw128(sK + (kk >> 2) * L::KV_PANEL + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(sQ + b * L::Q_BYTES + (kk >> 2) * L::Q_PANEL + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(sQ + rb * L::Q_BYTES + (kk >> 2) * L::Q_PANEL + (kk & 3) * 32, 16, 1024);
           umma_f16(tmem_base + L::COL_ST + b * BQ, ad, bd, idesc_s, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint64_t ad = umma_desc_sw128(sV + (kk >> 2) * L::KV_PANEL + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(sDO + b * L::Q_BYTES + (kk >> 2) * L::Q_PANEL + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(sDO + rb * L::Q_BYTES + (kk >> 2) * L::Q_PANEL + (kk & 3) * 32, 16, 1024);
           umma_f16(tmem_base + L::COL_DPT + b * BQ, ad, bd, idesc_s, kk != 0);
         }
         umma_commit(&s_full[b]);
@@ -504,7 +541,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       if (ok && n_items > 0) ok = issue_s(0);
       for (int it = 0; it < n_items && ok; ++it) {
         if (it + 1 < n_items && !issue_s(it + 1)) { ok = false; break; }
-        const int b = it & 1;
+        const int b = it % NS;
         if (!mbar_wait(p_full, (uint32_t)it & 1, status, SITE_B_PFULL)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
@@ -523,68 +560,95 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         umma_commit(pd_done);
         umma_commit(&q_free[b]);
       }
-      if (ok && n_items > 0) mbar_wait(&q_free[(n_items - 1) & 1], ((uint32_t)(n_items - 1) >> 1) & 1, status, SITE_B_END);
+      if (ok && n_items > 0) mbar_wait(&q_free[(n_items - 1) % NS], (uint32_t)((n_items - 1) / NS) & 1, status, SITE_B_END);
     }
   } else {
-    // ------------------------------------------------------------ thread = key row = TMEM lane
-    const int r = warp * 32 + lane;
+    // ------------------------------------------------------------ eight warps: key row = TMEM lane, two threads per row
+    // warps w and w + 4 read TMEM lane quarter w (a warp reaches the quarter warp % 4 only) and
+    // take 32 of an item's 64 query columns each: two warps per scheduler hide each other's latencies
+    const int quarter = warp & 3, hf = warp >> 2;
+    const int r = quarter * 32 + lane;
     const int j = n0 + r;
     const float sl2 = scale * LOG2E;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     bool ok = true;
+    AT_STAMP_K(0);
     for (int it = 0; it < n_items; ++it) {
       const int b = it & 1;
       const int m0 = n0 + (it % nqt) * BQ;
       if (!mbar_wait(&s_full[b], ((uint32_t)it >> 1) & 1, status, SITE_B_SFULL)) { ok = false; break; }
+      AT_STAMP_K(1 + 6 * it);
       // (completed long ago; passing it orders the producer lanes' per-query vectors before the reads below)
-      if (!mbar_wait(&q_full[b], ((uint32_t)it >> 1) & 1, status, SITE_B_QFULL)) { ok = false; break; }
+      if (!mbar_wait(&q_full[it % NS], (uint32_t)(it / NS) & 1, status, SITE_B_QFULL)) { ok = false; break; }
       tc_fence_after();
-      uint32_t st[BQ], dp[BQ];
-      tmem_ld32(lane_addr + L::COL_ST + b * BQ, st);
-      tmem_ld32(lane_addr + L::COL_ST + b * BQ + 32, st + 32);
-      tmem_ld32(lane_addr + L::COL_DPT + b * BQ, dp);
-      tmem_ld32(lane_addr + L::COL_DPT + b * BQ + 32, dp + 32);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(&st_free[b]);
-      const float* aux = (const float*)(sm + L::OFF_AUX + b * L::AUX_BYTES);
+      const float* aux = (const float*)(sm + L::OFF_AUX + (it % NS) * L::AUX_BYTES);
       const int* auxi = (const int*)aux;
       // element (key row j, query column i): P^T (weighted) and dS^T
-      uint32_t ph[BQ / 2], dh[BQ / 2];
+      uint32_t ph[16], dh[16];  // this thread's 32 columns
       // a tile whose queries all lie past these keys, inside one sequence, without hidden ranges, needs no mask
-      const bool need_mask = (m0 < n0 + 127) || gap != nullptr || auxi[3 * BQ + BQ - 1] > n0;  // (rows past the batch carry INT_MAX)
+      const bool need_mask = (m0 < n0 + 127) || auxi[3 * BQ + BQ - 1] > n0;  // (rows past the batch carry INT_MAX)
+      // 32 query columns at a time (fewer live registers), the per-query vectors fetched four at a
+      // time with 128-bit shared loads ahead of their use: a thread is alone on its scheduler most
+      // of the time, so one 32-bit shared load per use would put its latency on every element
+      {
+        uint32_t st[32], dp[32];
+        tmem_ld32(lane_addr + L::COL_ST + b * BQ + hf * 32, st);
+        tmem_ld32(lane_addr + L::COL_DPT + b * BQ + hf * 32, dp);
+        tmem_ld_wait();
+        AT_STAMP_K(2 + 6 * it);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&st_free[b]);
 #pragma unroll
-      for (int c = 0; c < BQ; c += 2) {
-        float pv[2], dsv[2];
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const int il0 = hf * 32 + c4 * 4;
+          const float4 ls = *(const float4*)(aux + il0), de = *(const float4*)(aux + BQ + il0), wt = *(const float4*)(aux + 2 * BQ + il0);
+          const float lsv[4] = {ls.x, ls.y, ls.z, ls.w}, dev[4] = {de.x, de.y, de.z, de.w}, wtv[4] = {wt.x, wt.y, wt.z, wt.w};
+          float pv[4], dsv[4];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int il = c + e;
-          float p = ex2_approx(__uint_as_float(st[il]) * sl2 - aux[il]) * aux[2 * BQ + il];
+          for (int e = 0; e < 4; ++e)
+            pv[e] = ex2_approx(__uint_as_float(st[c4 * 4 + e]) * sl2 - lsv[e]) * wtv[e];
           if (need_mask) {
-            const int i = m0 + il;
-            const bool valid = j <= i && j >= auxi[3 * BQ + il] && (j < auxi[4 * BQ + il] || j >= auxi[5 * BQ + il]);
-            p = valid ? p : 0.f;
+            const int4 sq = *(const int4*)(auxi + 3 * BQ + il0);
+            const int sqv[4] = {sq.x, sq.y, sq.z, sq.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pv[e] = (j <= m0 + il0 + e && j >= sqv[e]) ? pv[e] : 0.f;
           }
-          pv[e] = p;
-          dsv[e] = p * (__uint_as_float(dp[il]) - aux[BQ + il]) * scale;
+          if (gap != nullptr) {
+            const int4 ga = *(const int4*)(auxi + 4 * BQ + il0), gb = *(const int4*)(auxi + 5 * BQ + il0);
+            const int gav[4] = {ga.x, ga.y, ga.z, ga.w}, gbv[4] = {gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pv[e] = (j < gav[e] || j >= gbv[e]) ? pv[e] : 0.f;
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) dsv[e] = pv[e] * (__uint_as_float(dp[c4 * 4 + e]) - dev[e]) * scale;
+          ph[2 * c4] = pack_h2(pv[0], pv[1]);
+          ph[2 * c4 + 1] = pack_h2(pv[2], pv[3]);
+          dh[2 * c4] = pack_h2(dsv[0], dsv[1]);
+          dh[2 * c4 + 1] = pack_h2(dsv[2], dsv[3]);
         }
-        ph[c >> 1] = pack_h2(pv[0], pv[1]);
-        dh[c >> 1] = pack_h2(dsv[0], dsv[1]);
       }
+      AT_STAMP_K(3 + 6 * it);
       if (it > 0) {
         if (!mbar_wait(pd_done, (uint32_t)(it - 1) & 1, status, SITE_B_PDDONE)) { ok = false; break; }
       }
+      AT_STAMP_K(4 + 6 * it);
       uint8_t* prow = sm + L::OFF_PT + r * 128;
       uint8_t* drow = sm + L::OFF_DST + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = make_uint4(ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
-        *(uint4*)(drow + ((c ^ (r & 7)) << 4)) = make_uint4(dh[4 * c], dh[4 * c + 1], dh[4 * c + 2], dh[4 * c + 3]);
+      for (int c = 0; c < 4; ++c) {  // this thread's four 16-byte chunks of the row
+        const int ch = hf * 4 + c;
+        *(uint4*)(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
+        *(uint4*)(drow + ((ch ^ (r & 7)) << 4)) = make_uint4(dh[4 * c], dh[4 * c + 1], dh[4 * c + 2], dh[4 * c + 3]);
       }
+      AT_STAMP_K(5 + 6 * it);
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      AT_STAMP_K(6 + 6 * it);
     }
+    AT_STAMP_K(500);
     // write this key row's gradients (zeros when no query sees these keys)
     const float sc = do_scale[0];
     if (n_items > 0 && ok) ok = mbar_wait(pd_done, (uint32_t)(n_items - 1) & 1, status, SITE_B_PDDONE);
@@ -593,7 +657,8 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       float* dkrow = dk + ((size_t)j * nkv + g) * HD;
       float* dvrow = dv + ((size_t)j * nkv + g) * HD;
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int cc = 0; cc < HD / 64; ++cc) {  // each of the row's two threads writes half of its columns
+        const int c = hf * (HD / 64) + cc;
         uint32_t a[32], bb[32];
         if (n_items > 0) {
           tmem_ld32(lane_addr + L::COL_DK + c * 32, a);
@@ -621,7 +686,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == BWD_MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, L::TMEM_COLS);
   }
@@ -630,8 +695,9 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
 // ------------------------------------------------------------------ dQ: one CTA per (128 query rows, head)
 // Thread = query row = TMEM lane.  Q and dO stay in shared memory; per key tile of 64:
 // S = Q.K^T and dP = dO.V^T into TMEM, dS = P*(dP - delta)*scale to shared memory in f16, then
-// dQ += dS.K with K read MN-major from the tile that just served Q.K^T.  Single K/V buffers: two
-// CTAs share an SM (112 KB, 256 TMEM columns each) and fill each other's waits.
+// dQ += dS.K with K read MN-major from the tile that just served Q.K^T.  K and V tiles go through
+// a ring of three slots (a K slot is released by the tile's dQ product, so the fetch of tile n+2
+// runs under all of tile n+1); S and dP have two TMEM buffers each and are issued one tile ahead.
 enum { SITE_Q_QDO = 471, SITE_Q_KFREE, SITE_Q_VFREE, SITE_Q_KFULL, SITE_Q_VFULL, SITE_Q_SFREE, SITE_Q_DSFULL, SITE_Q_SFULL, SITE_Q_DQDONE, SITE_Q_END };
 
 template <int HD>
@@ -639,14 +705,15 @@ struct DqLayout {
   static constexpr int PAN = HD / 64;
   static constexpr uint32_t Q_PANEL = BM * 128, KV_PANEL = BN * 128;
   static constexpr uint32_t Q_BYTES = PAN * Q_PANEL, KV_BYTES = PAN * KV_PANEL, DS_BYTES = BM * 128;
-  static constexpr uint32_t OFF_Q = 0, OFF_DO = Q_BYTES, OFF_K = 2 * Q_BYTES, OFF_V = OFF_K + KV_BYTES, OFF_DS = OFF_V + KV_BYTES;
+  static constexpr int NS = 3;
+  static constexpr uint32_t OFF_Q = 0, OFF_DO = Q_BYTES, OFF_K = 2 * Q_BYTES, OFF_V = OFF_K + NS * KV_BYTES, OFF_DS = OFF_V + NS * KV_BYTES;
   static constexpr uint32_t OFF_BAR = OFF_DS + DS_BYTES;
-  static constexpr uint32_t USED = OFF_BAR + 256, TOTAL = USED + 768;
-  static constexpr uint32_t COL_S = 0, COL_DP = BN, COL_DQ = 2 * BN, TMEM_COLS = 256;
+  static constexpr uint32_t USED = OFF_BAR + 256, TOTAL = USED + 1024;
+  static constexpr uint32_t COL_S = 0, COL_DP = 2 * BN, COL_DQ = 4 * BN, TMEM_COLS = 512;
 };
 
 template <int HD>
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const float* __restrict__ do_scale, const float* __restrict__ row_scale, const float* __restrict__ lse,
@@ -655,23 +722,19 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   using L = DqLayout<HD>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
-  if (pad + L::USED > L::TOTAL) {
-    if (threadIdx.x == 0) atomicCAS(status, 0, RT_ERR_CUDA);
-    return;
-  }
-  uint8_t* sm = smem_raw + pad;
+  uint8_t* sm = smem_raw + (((raw + 1023u) & ~1023u) - raw);
   uint64_t* bars = (uint64_t*)(sm + L::OFF_BAR);
+  constexpr int NS = L::NS;
   uint64_t* qdo_full = bars + 0;
-  uint64_t* k_full = bars + 1;
-  uint64_t* v_full = bars + 2;
-  uint64_t* k_free = bars + 3;
-  uint64_t* v_free = bars + 4;
-  uint64_t* s_full = bars + 5;
-  uint64_t* s_free = bars + 6;
-  uint64_t* ds_full = bars + 7;
-  uint64_t* dq_done = bars + 8;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+  uint64_t* k_full = bars + 1;    // [NS]
+  uint64_t* v_full = bars + 4;    // [NS]
+  uint64_t* k_free = bars + 7;    // [NS]
+  uint64_t* v_free = bars + 10;   // [NS]
+  uint64_t* s_full = bars + 13;   // [2]
+  uint64_t* s_free = bars + 15;   // [2]
+  uint64_t* ds_full = bars + 17;
+  uint64_t* dq_done = bars + 18;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 20);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the last query tiles of a sequence see the most keys: start them first
@@ -682,13 +745,17 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    mbar_init(k_full, 1);
-    mbar_init(v_full, 1);
-    mbar_init(k_free, 1);
-    mbar_init(v_free, 1);
-    mbar_init(s_full, 1);
-    mbar_init(s_free, 128);
-    mbar_init(ds_full, 128);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&k_free[i], 1);
+      mbar_init(&v_free[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 8);
+    }
+    mbar_init(ds_full, 8);
     mbar_init(dq_done, 1);
     mbar_fence_init();
     prefetch_tmap(&tm_q);
@@ -696,16 +763,18 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     prefetch_tmap(&tm_k);
     prefetch_tmap(&tm_v);
   }
-  if (warp == 5) {
+  if (warp == BWD_MMA_WARP) {
     tmem_alloc(tmem_slot, L::TMEM_COLS);
     tmem_relinquish();
   }
+  AT_STAMP_Q(510);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
+  AT_STAMP_Q(511);
 
-  if (warp == 4) {
+  if (warp == BWD_TMA_WARP) {
     if (lane == 0) {
       mbar_expect_tx(qdo_full, 2 * L::Q_BYTES);
       for (int p = 0; p < L::PAN; ++p) {
@@ -713,57 +782,70 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         tma_load_2d(sm + L::OFF_DO + p * L::Q_PANEL, &tm_do, h * HD + p * 64, m0, qdo_full);
       }
       for (int n = 0; n < ntiles; ++n) {
-        const uint32_t free_parity = ((uint32_t)n & 1) ^ 1;
+        const int rb = n % NS;
+        const uint32_t free_parity = ((uint32_t)(n / NS) & 1) ^ 1;
         const int n0 = kbeg + n * BN;
-        if (!mbar_wait(v_free, free_parity, status, SITE_Q_VFREE)) break;
-        mbar_expect_tx(v_full, L::KV_BYTES);
-        for (int p = 0; p < L::PAN; ++p) tma_load_2d(sm + L::OFF_V + p * L::KV_PANEL, &tm_v, g * HD + p * 64, n0, v_full);
-        if (!mbar_wait(k_free, free_parity, status, SITE_Q_KFREE)) break;
-        mbar_expect_tx(k_full, L::KV_BYTES);
-        for (int p = 0; p < L::PAN; ++p) tma_load_2d(sm + L::OFF_K + p * L::KV_PANEL, &tm_k, g * HD + p * 64, n0, k_full);
+        if (!mbar_wait(&v_free[rb], free_parity, status, SITE_Q_VFREE)) break;
+        mbar_expect_tx(&v_full[rb], L::KV_BYTES);
+        for (int p = 0; p < L::PAN; ++p)
+          tma_load_2d(sm + L::OFF_V + rb * L::KV_BYTES + p * L::KV_PANEL, &tm_v, g * HD + p * 64, n0, &v_full[rb]);
+        if (!mbar_wait(&k_free[rb], free_parity, status, SITE_Q_KFREE)) break;
+        mbar_expect_tx(&k_full[rb], L::KV_BYTES);
+        for (int p = 0; p < L::PAN; ++p)
+          tma_load_2d(sm + L::OFF_K + rb * L::KV_BYTES + p * L::KV_PANEL, &tm_k, g * HD + p * 64, n0, &k_full[rb]);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == BWD_MMA_WARP) {
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc(0, 0, 0, 0, BM, BN);
       const uint32_t idesc_g = umma_idesc(0, 0, 0, 1, BM, HD);
       const uint32_t sQ = smem_u32(sm + L::OFF_Q), sDO = smem_u32(sm + L::OFF_DO), sK = smem_u32(sm + L::OFF_K);
       const uint32_t sV = smem_u32(sm + L::OFF_V), sDS = smem_u32(sm + L::OFF_DS);
       bool ok = mbar_wait(qdo_full, 0, status, SITE_Q_QDO);
-      for (int n = 0; n < ntiles && ok; ++n) {
-        const uint32_t ph = (uint32_t)n & 1;
-        if (!mbar_wait(k_full, ph, status, SITE_Q_KFULL) || !mbar_wait(v_full, ph, status, SITE_Q_VFULL) ||
-            !mbar_wait(s_free, ph ^ 1, status, SITE_Q_SFREE)) { ok = false; break; }
+      auto issue_s = [&](int n) -> bool {
+        const int b = n & 1, rb = n % NS;  // TMEM buffer, ring slot
+        const uint32_t rph = (uint32_t)(n / NS) & 1;
+        if (!mbar_wait(&k_full[rb], rph, status, SITE_Q_KFULL) || !mbar_wait(&v_full[rb], rph, status, SITE_Q_VFULL) ||
+            !mbar_wait(&s_free[b], (((uint32_t)n >> 1) & 1) ^ 1, status, SITE_Q_SFREE))
+          return false;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint64_t ad = umma_desc_sw128(sDO + (kk >> 2) * L::Q_PANEL + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(sV + (kk >> 2) * L::KV_PANEL + (kk & 3) * 32, 16, 1024);
-          umma_f16(tmem_base + L::COL_DP, ad, bd, idesc_s, kk != 0);
+          const uint64_t bd = umma_desc_sw128(sV + rb * L::KV_BYTES + (kk >> 2) * L::KV_PANEL + (kk & 3) * 32, 16, 1024);
+          umma_f16(tmem_base + L::COL_DP + b * BN, ad, bd, idesc_s, kk != 0);
         }
-        umma_commit(v_free);  // V served dP only: its next tile may load under the rest of this one
+        umma_commit(&v_free[rb]);  // V served dP only
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint64_t ad = umma_desc_sw128(sQ + (kk >> 2) * L::Q_PANEL + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(sK + (kk >> 2) * L::KV_PANEL + (kk & 3) * 32, 16, 1024);
-          umma_f16(tmem_base + L::COL_S, ad, bd, idesc_s, kk != 0);
+          const uint64_t bd = umma_desc_sw128(sK + rb * L::KV_BYTES + (kk >> 2) * L::KV_PANEL + (kk & 3) * 32, 16, 1024);
+          umma_f16(tmem_base + L::COL_S + b * BN, ad, bd, idesc_s, kk != 0);
         }
-        umma_commit(s_full);
-        if (!mbar_wait(ds_full, ph, status, SITE_Q_DSFULL)) { ok = false; break; }
+        umma_commit(&s_full[b]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int n = 0; n < ntiles && ok; ++n) {
+        if (n + 1 < ntiles && !issue_s(n + 1)) { ok = false; break; }
+        const int rb = n % NS;
+        if (!mbar_wait(ds_full, (uint32_t)n & 1, status, SITE_Q_DSFULL)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           const uint64_t ad = umma_desc_sw128(sDS + kk * 32, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(sK + kk * 2048, L::KV_PANEL, 1024);  // K tile read MN-major: rows are keys
+          const uint64_t bd = umma_desc_sw128(sK + rb * L::KV_BYTES + kk * 2048, L::KV_PANEL, 1024);  // K tile read MN-major: rows are keys
           umma_f16(tmem_base + L::COL_DQ, ad, bd, idesc_g, (n | kk) != 0);
         }
         umma_commit(dq_done);
-        umma_commit(k_free);
+        umma_commit(&k_free[rb]);
       }
-      if (ok) mbar_wait(k_free, (uint32_t)(ntiles - 1) & 1, status, SITE_Q_END);
+      if (ok) mbar_wait(&k_free[(ntiles - 1) % NS], (uint32_t)((ntiles - 1) / NS) & 1, status, SITE_Q_END);
     }
   } else {
-    const int r = warp * 32 + lane;
+    // eight warps: warps w and w + 4 share TMEM lane quarter w and take 32 of a tile's 64 key columns each
+    const int quarter = warp & 3, hf = warp >> 2;
+    const int r = quarter * 32 + lane;
     const int i = m0 + r;
     const int ss_i = i < M ? seq_start[i] : 0x7fffffff;
     const int2 gp = (gap && i < M) ? gap[i] : make_int2(0, 0);
@@ -771,54 +853,68 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const float l2 = i < M ? lse[(size_t)h * M + i] * LOG2E : 0.f;
     const float dl = i < M ? delta[(size_t)h * M + i] : 0.f;
     const float sl2 = scale * LOG2E;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     bool ok = true;
+    AT_STAMP_Q(0);
     for (int n = 0; n < ntiles; ++n) {
-      const uint32_t ph = (uint32_t)n & 1;
+      const int b = n & 1;
       const int n0 = kbeg + n * BN;
-      if (!mbar_wait(s_full, ph, status, SITE_Q_SFULL)) { ok = false; break; }
+      if (!mbar_wait(&s_full[b], ((uint32_t)n >> 1) & 1, status, SITE_Q_SFULL)) { ok = false; break; }
+      AT_STAMP_Q(1 + 6 * n);
       tc_fence_after();
-      uint32_t sv[BN], dp[BN];
-      tmem_ld32(lane_addr + L::COL_S, sv);
-      tmem_ld32(lane_addr + L::COL_S + 32, sv + 32);
-      tmem_ld32(lane_addr + L::COL_DP, dp);
-      tmem_ld32(lane_addr + L::COL_DP + 32, dp + 32);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(s_free);
-      const bool need_mask = (n0 + BN - 1 > m0) || (n0 < ss_last) || gap != nullptr;
+      const bool need_mask = (n0 + BN - 1 > m0) || (n0 < ss_last);
       const int c_lo = ss_i - n0, c_hi = i - n0, g_lo = gp.x - n0, g_hi = gp.y - n0;
-      uint32_t dh[BN / 2];
+      uint32_t dh[16];  // this thread's 32 columns
+      {
+        uint32_t sv[32], dp[32];
+        tmem_ld32(lane_addr + L::COL_S + b * BN + hf * 32, sv);
+        tmem_ld32(lane_addr + L::COL_DP + b * BN + hf * 32, dp);
+        tmem_ld_wait();
+        AT_STAMP_Q(2 + 6 * n);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[b]);
 #pragma unroll
-      for (int c = 0; c < BN; c += 2) {
-        float dsv[2];
+        for (int c = 0; c < 32; c += 2) {
+          float dsv[2];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int cc = c + e;
-          float p = ex2_approx(__uint_as_float(sv[cc]) * sl2 - l2);
-          if (need_mask) p = (cc >= c_lo && cc <= c_hi && (cc < g_lo || cc >= g_hi)) ? p : 0.f;
-          dsv[e] = p * (__uint_as_float(dp[cc]) - dl) * scale;
+          for (int e = 0; e < 2; ++e) {
+            const int cc = hf * 32 + c + e;
+            float p = ex2_approx(__uint_as_float(sv[c + e]) * sl2 - l2);
+            if (need_mask) p = (cc >= c_lo && cc <= c_hi) ? p : 0.f;
+            if (gap != nullptr) p = (cc < g_lo || cc >= g_hi) ? p : 0.f;
+            dsv[e] = p * (__uint_as_float(dp[c + e]) - dl) * scale;
+          }
+          dh[c >> 1] = pack_h2(dsv[0], dsv[1]);
         }
-        dh[c >> 1] = pack_h2(dsv[0], dsv[1]);
       }
+      AT_STAMP_Q(3 + 6 * n);
       if (n > 0) {
         if (!mbar_wait(dq_done, (uint32_t)(n - 1) & 1, status, SITE_Q_DQDONE)) { ok = false; break; }
       }
+      AT_STAMP_Q(4 + 6 * n);
       uint8_t* drow = sm + L::OFF_DS + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *(uint4*)(drow + ((c ^ (r & 7)) << 4)) = make_uint4(dh[4 * c], dh[4 * c + 1], dh[4 * c + 2], dh[4 * c + 3]);
+      for (int c = 0; c < 4; ++c) {
+        const int ch = hf * 4 + c;
+        *(uint4*)(drow + ((ch ^ (r & 7)) << 4)) = make_uint4(dh[4 * c], dh[4 * c + 1], dh[4 * c + 2], dh[4 * c + 3]);
+      }
+      AT_STAMP_Q(5 + 6 * n);
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(ds_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+      AT_STAMP_Q(6 + 6 * n);
     }
+    AT_STAMP_Q(500);
     if (ok && mbar_wait(dq_done, (uint32_t)(ntiles - 1) & 1, status, SITE_Q_DQDONE)) {
       tc_fence_after();
       // a query row's gradient carries only that row's factor
       const float sc = row_scale ? (i < M ? row_scale[i] : 0.f) : do_scale[0];
       float* qrow = dq + ((size_t)i * nh + h) * HD;
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int cc = 0; cc < HD / 64; ++cc) {
+        const int c = hf * (HD / 64) + cc;
         uint32_t a[32];
         tmem_ld32(lane_addr + L::COL_DQ + c * 32, a);
         tmem_ld_wait();
@@ -829,6 +925,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                                                             __uint_as_float(a[4 * k + 2]) * sc, __uint_as_float(a[4 * k + 3]) * sc);
         }
       }
+      AT_STAMP_Q(501);
     }
   }
 
@@ -837,7 +934,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == BWD_MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, L::TMEM_COLS);
   }
@@ -888,9 +985,9 @@ int bwd_tc_impl(rt_ctx* c, const __half* q, const __half* k, const __half* v, co
   const int warps = M * nh;
   attn_delta_tc_kernel<HD><<<(warps * 32 + 255) / 256, 256, 0, st>>>(o, dO, M, nh, delta);
   dim3 gkv((M + 127) / 128, nkv), gq((M + BM - 1) / BM, nh);
-  attn_bwd_dkdv_tc_kernel<HD><<<gkv, 192, LK::TOTAL, st>>>(tk128, tv128, tq64, tdo64, do_scale, row_scale, lse, delta, seq_start, gap,
+  attn_bwd_dkdv_tc_kernel<HD><<<gkv, BWD_THREADS, LK::TOTAL, st>>>(tk128, tv128, tq64, tdo64, do_scale, row_scale, lse, delta, seq_start, gap,
                                                           M, nh, nkv, scale, dk, dv, c->status_dev);
-  attn_bwd_dq_tc_kernel<HD><<<gq, 192, LQ::TOTAL, st>>>(tq128, tdo128, tk64, tv64, do_scale, row_scale, lse, delta, seq_start, gap, M,
+  attn_bwd_dq_tc_kernel<HD><<<gq, BWD_THREADS, LQ::TOTAL, st>>>(tq128, tdo128, tk64, tv64, do_scale, row_scale, lse, delta, seq_start, gap, M,
                                                        nh, nkv, scale, dq, c->status_dev);
   RT_COUNT_LAUNCH(3);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
@@ -905,6 +1002,12 @@ int launch_attn_fwd_tc(rt_ctx* c, const __half* q, const __half* k, const __half
   if (hd == 64) return fwd_tc_impl<64>(c, q, k, v, seq_start, (const int2*)gap, M, nh, nkv, o, lse);
   return 1;
 }
+
+#ifdef RT_B200_QPROF
+extern "C" int rt_debug_attn_prof(unsigned long long* out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, g_attn_prof, sizeof(unsigned long long) * (n < 512 ? n : 512));
+}
+#endif
 
 int launch_attn_bwd_tc(rt_ctx* c, const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
                        const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap,

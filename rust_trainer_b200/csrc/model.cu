@@ -65,21 +65,13 @@ static __half* lowrank_buf(rt_ctx* c, DevBuf& b, int& cur_rank, int M, int rank)
   return b.as<__half>();
 }
 
-// RT_B200_ATTN_LEGACY=1 keeps the mma.sync attention forward (an A/B switch while both exist)
 int attn_forward(rt_ctx* c, const __half* q, const __half* k, const __half* v, const int* seq_start, const int* gap, int M, int nh,
                  int nkv, int hd, __half* o, float* lse) {
-  static int legacy = -1;
-  if (legacy < 0) { const char* e = getenv("RT_B200_ATTN_LEGACY"); legacy = (e && e[0] == '1') ? 1 : 0; }
-  if (legacy) return launch_attn_fwd(q, k, v, seq_start, gap, M, nh, nkv, hd, o, lse, c->stream);
   return launch_attn_fwd_tc(c, q, k, v, seq_start, gap, M, nh, nkv, hd, o, lse);
 }
-
 int attn_backward(rt_ctx* c, const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
                   const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap, int M,
                   int nh, int nkv, int hd, float* delta, float* dq, float* dk, float* dv) {
-  static int legacy = -1;
-  if (legacy < 0) { const char* e = getenv("RT_B200_ATTN_LEGACY"); legacy = (e && e[0] == '1') ? 1 : 0; }
-  if (legacy) return launch_attn_bwd(q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, gap, M, nh, nkv, hd, delta, dq, dk, dv, c->stream);
   return launch_attn_bwd_tc(c, q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, gap, M, nh, nkv, hd, delta, dq, dk, dv);
 }
 

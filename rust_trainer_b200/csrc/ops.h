@@ -81,20 +81,12 @@ int launch_lora_grads(const __half* hs, const __half* dy16, int ld_dy, const __h
 int launch_tok_contract(const __half* P, const __half* Q, const float* pscale, int M, int C, int r, size_t so_i, size_t so_j,
                         const float* alpha_dev, float* out, float* workspace, cudaStream_t st);
 
-// ---- attention.cu: causal GQA attention over a concatenation of independent sequences.
+// ---- attention_tc.cu: causal GQA attention over a concatenation of independent sequences, on
+// tcgen05 / TMEM / TMA (waits report through the ctx status word).
 // q [M x nh x hd], k/v [M x nkv x hd] f16 (q unscaled; the kernels apply 1/sqrt(hd)).
-// seq_start[m] = index of the first token of m's sequence.  lse is [nh x M].
-int launch_attn_fwd(const __half* q, const __half* k, const __half* v, const int* seq_start, const int* gap /* [M x 2] or null */, int M, int nh, int nkv,
-                    int hd, __half* o, float* lse, cudaStream_t st);
-// dO16 is dO divided by a global scale (device scalar `do_scale`); outputs are true-scale f32.
-// dO row i stands for do_scale[0] * dO16[i], or, with row_scale, for row_scale[i] * dO16[i]
-// (then do_scale[0] must hold the largest row_scale).
-int launch_attn_bwd(const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
-                    const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap,
-                    int M, int nh, int nkv, int hd, float* delta /* [nh x M] scratch */, float* dq, float* dk, float* dv,
-                    cudaStream_t st);
-
-// ---- attention_tc.cu: the same forward on tcgen05 / TMEM / TMA (waits report through the ctx status word)
+// seq_start[m] = index of the first token of m's sequence; gap [M x 2] or null; lse is [nh x M].
+// Backward: dO row i stands for do_scale[0] * dO16[i], or, with row_scale, for row_scale[i] *
+// dO16[i] (then do_scale[0] holds a power of two >= the largest row_scale); outputs are true-scale f32.
 int launch_attn_bwd_tc(rt_ctx* c, const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
                        const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap,
                        int M, int nh, int nkv, int hd, float* delta, float* dq, float* dk, float* dv);
