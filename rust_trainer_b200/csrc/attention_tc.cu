@@ -383,6 +383,12 @@ int fwd_tc_impl(rt_ctx* c, const __half* q, const __half* k, const __half* v, co
 // Per item: S^T = K.Q^T and dP^T = V.dO^T into TMEM (two buffers each), the threads turn them
 // into P^T and dS^T (f16, shared memory), then dV += P^T.dO and dK += dS^T.Q with Q and dO read
 // MN-major from the same tiles.  TMEM: 2 x 64 + 2 x 64 + hd + hd columns (512 for hd = 128).
+// P (<= 1, times a row weight <= 1) and dS are handed to the tensor cores in f16, whose normal
+// range ends at 6e-5: attention probabilities of long rows and the gradients of lightly weighted
+// rows live below that.  They are therefore stored times a power of two (exact), which the f32
+// results are divided by again: 2^14 keeps P.w <= 16384, 2^10 keeps dS inside f16 for |dP - delta|
+// up to ~700.
+constexpr float P_BOOST = 16384.0f, DS_BOOST = 1024.0f;
 constexpr int BQ = 64;  // query rows per work item
 constexpr int BWD_THREADS = 320, BWD_TMA_WARP = 8, BWD_MMA_WARP = 9;  // warps 0-7 compute
 enum { SITE_B_KV = 451, SITE_B_QFREE, SITE_B_QFULL, SITE_B_STFREE, SITE_B_PFULL, SITE_B_SFULL, SITE_B_PDDONE, SITE_B_END };
@@ -500,7 +506,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         const bool in = m < M;
         aux[il] = in ? lse[(size_t)h * M + m] * LOG2E : 0.f;
         aux[BQ + il] = in ? delta[(size_t)h * M + m] : 0.f;
-        aux[2 * BQ + il] = in ? (row_scale ? row_scale[m] * inv_top : 1.0f) : 0.f;
+        aux[2 * BQ + il] = in ? (row_scale ? row_scale[m] * inv_top : 1.0f) * P_BOOST : 0.f;
         ((int*)aux)[3 * BQ + il] = in ? seq_start[m] : 0x7fffffff;
         const int2 gp = (gap && in) ? gap[m] : make_int2(0, 0);
         ((int*)aux)[4 * BQ + il] = gp.x;
@@ -621,7 +627,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
             for (int e = 0; e < 4; ++e) pv[e] = (j < gav[e] || j >= gbv[e]) ? pv[e] : 0.f;
           }
 #pragma unroll
-          for (int e = 0; e < 4; ++e) dsv[e] = pv[e] * (__uint_as_float(dp[c4 * 4 + e]) - dev[e]) * scale;
+          for (int e = 0; e < 4; ++e) dsv[e] = pv[e] * (__uint_as_float(dp[c4 * 4 + e]) - dev[e]) * (scale * (DS_BOOST / P_BOOST));
           ph[2 * c4] = pack_h2(pv[0], pv[1]);
           ph[2 * c4 + 1] = pack_h2(pv[2], pv[3]);
           dh[2 * c4] = pack_h2(dsv[0], dsv[1]);
@@ -650,7 +656,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     }
     AT_STAMP_K(500);
     // write this key row's gradients (zeros when no query sees these keys)
-    const float sc = do_scale[0];
+    const float sc_v = do_scale[0] * (1.0f / P_BOOST), sc_k = do_scale[0] * (1.0f / DS_BOOST);
     if (n_items > 0 && ok) ok = mbar_wait(pd_done, (uint32_t)(n_items - 1) & 1, status, SITE_B_PDDONE);
     if (ok) {
       tc_fence_after();
@@ -671,10 +677,10 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         if (j < M) {
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
-            *(float4*)(dkrow + c * 32 + 4 * k) = make_float4(__uint_as_float(a[4 * k]) * sc, __uint_as_float(a[4 * k + 1]) * sc,
-                                                             __uint_as_float(a[4 * k + 2]) * sc, __uint_as_float(a[4 * k + 3]) * sc);
-            *(float4*)(dvrow + c * 32 + 4 * k) = make_float4(__uint_as_float(bb[4 * k]) * sc, __uint_as_float(bb[4 * k + 1]) * sc,
-                                                             __uint_as_float(bb[4 * k + 2]) * sc, __uint_as_float(bb[4 * k + 3]) * sc);
+            *(float4*)(dkrow + c * 32 + 4 * k) = make_float4(__uint_as_float(a[4 * k]) * sc_k, __uint_as_float(a[4 * k + 1]) * sc_k,
+                                                             __uint_as_float(a[4 * k + 2]) * sc_k, __uint_as_float(a[4 * k + 3]) * sc_k);
+            *(float4*)(dvrow + c * 32 + 4 * k) = make_float4(__uint_as_float(bb[4 * k]) * sc_v, __uint_as_float(bb[4 * k + 1]) * sc_v,
+                                                             __uint_as_float(bb[4 * k + 2]) * sc_v, __uint_as_float(bb[4 * k + 3]) * sc_v);
           }
         }
       }
@@ -883,7 +889,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             float p = ex2_approx(__uint_as_float(sv[c + e]) * sl2 - l2);
             if (need_mask) p = (cc >= c_lo && cc <= c_hi) ? p : 0.f;
             if (gap != nullptr) p = (cc < g_lo || cc >= g_hi) ? p : 0.f;
-            dsv[e] = p * (__uint_as_float(dp[c + e]) - dl) * scale;
+            dsv[e] = p * (__uint_as_float(dp[c + e]) - dl) * (scale * DS_BOOST);
           }
           dh[c >> 1] = pack_h2(dsv[0], dsv[1]);
         }
@@ -910,7 +916,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if (ok && mbar_wait(dq_done, (uint32_t)(ntiles - 1) & 1, status, SITE_Q_DQDONE)) {
       tc_fence_after();
       // a query row's gradient carries only that row's factor
-      const float sc = row_scale ? (i < M ? row_scale[i] : 0.f) : do_scale[0];
+      const float sc = (row_scale ? (i < M ? row_scale[i] : 0.f) : do_scale[0]) * (1.0f / DS_BOOST);
       float* qrow = dq + ((size_t)i * nh + h) * HD;
 #pragma unroll
       for (int cc = 0; cc < HD / 64; ++cc) {

@@ -1086,6 +1086,12 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
     if (splits < 1) splits = 1;
   }
   p.steps_per_split = (p.n_main + splits - 1) / splits;
+  // A very long contraction (the head's backward runs over the whole vocabulary) is accumulated
+  // in pieces of a FIXED 8192 elements whose f32 partial sums are added afterwards: the tensor
+  // core's accumulator does not round to nearest, so the error of one chain grows with its
+  // length (about 3e-4 relative over 150 000 elements), and a piece length that depended on the
+  // batch would make the result depend on how a batch is split over ranks.
+  if (!a.tok_mode && a.out_dtype == OUT_F32 && !a.fixed_part && p.n_main > 256 && p.steps_per_split > 128) p.steps_per_split = 128;
   p.n_splits = (p.n_main + p.steps_per_split - 1) / p.steps_per_split;
   p.b_mn = a.tok_mode ? 1 : 0;
   // CTA pairs: 256 weight rows per tile, each CTA stages half of the tokens.  Needs whole pairs of

@@ -101,3 +101,30 @@ def test_two_layer_cuts_at_full_width_and_vocabulary(ctx, name, quant, seq, rank
     spec = synth.preset(name, quant=quant, seed=1, n_layers=2)
     toks = synth.token_batch(spec, 1, seq, 7)
     _compare_step(ctx, spec, rank, 2.0 * rank, [toks[0]], 1, lr=1e-3, wd=0.0, n_targets_cap=96)
+
+
+def test_shards_of_a_batch_sum_to_the_whole_batch(ctx):
+    """Data parallelism rests on it: the gradients of a batch's round-robin shards (each with the
+    GLOBAL 1/batch_tokens weight) add up to the gradient of the whole batch, to the order of f32
+    sums (rel-L2 <= 1e-5), at the full vocabulary, where the head's backward contracts over 151 936
+    elements.  Nothing a row is rounded with may depend on which other rows share its batch."""
+    from rust_trainer_b200 import dp
+
+    spec = synth.preset("qwen3-0.6b", quant="Q8_0", seed=0, n_layers=2)
+    gm = rt.Model(ctx, spec.config(), synth.build_tensors(spec))
+    gm.attach_lora(16, 32.0, None, 1234)
+    gm.load_adapters(synth.lora_adapters(spec, 16, 32.0, seed=1234))
+    toks = synth.token_batch(spec, 6, 512, 7)
+    examples = [(toks[i], 359) for i in range(6)]
+
+    def grads(rank, world):
+        b = dp.local_batch(examples, rank, world)
+        gm.zero_grad()
+        lp, _ = gm.forward_backward(b.seqs, b.target_pos, b.target_tok, b.weights)
+        return _flat([l.lora() for l in gm.lora_linears()], "ga", "gb").astype(np.float64), dp.step_loss(lp, b)
+
+    whole, loss = grads(0, 1)
+    parts = [grads(r, 3) for r in range(3)]
+    assert rel_l2(sum(p[0] for p in parts), whole) < 1e-5
+    assert abs(sum(p[1] for p in parts) - loss) < 1e-6 * abs(loss)
+    gm.close()
