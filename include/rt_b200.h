@@ -130,11 +130,12 @@ rt_status rt_frozen_backward_input_dev(rt_frozen* w, const void* dy_dev, int in_
  * handed every byte of HBM to its own pool, a real-time loop that cannot take the driver's
  * allocation lock, or code running where cudaMalloc is simply not permitted.  It has no
  * counterpart in the reference (the reference never leaves the CPU).  When the contraction is
- * split over SMs, the partial sums go to a fixed 8 MiB array that is part of the library's
+ * accumulated in pieces (more than 16384 weight rows: one piece per 8192), the partial sums go
+ * to a fixed 8 MiB array that is part of the library's
  * device image (every GPU that loads the library holds it until the process exits) instead of
  * grow-on-demand scratch; the call makes no cudaMalloc / cudaFree and keeps no descriptor
  * cache.  Limits and rules:
- *   - a call whose partial sums need more than 2 Mi floats (splits x t x in_dim) is refused with
+ *   - a call whose partial sums need more than 2 Mi floats (pieces x t x in_dim) is refused with
  *     RT_ERR_TOO_LARGE; use fewer rows per call;
  *   - the FIRST call on a device looks up the array's device address; make that call before
  *     any stream capture begins;

@@ -7,6 +7,8 @@
 #include <map>
 #include <string>
 #include <vector>
+#include <mutex>
+#include <set>
 
 void* rt_ctx::get_scratch(int slot, size_t bytes) {
   if (bytes <= scratch_bytes[slot]) return scratch[slot];
@@ -38,6 +40,18 @@ rt_status rt_ctx::check_device_status(const char* where) {
 }
 
 namespace rt {
+static std::mutex g_ctx_mutex;
+static std::set<const rt_ctx*> g_live_ctx;
+bool ctx_alive(const rt_ctx* c) {
+  std::lock_guard<std::mutex> lock(g_ctx_mutex);
+  return g_live_ctx.count(c) != 0;
+}
+static void ctx_register(const rt_ctx* c, bool live) {
+  std::lock_guard<std::mutex> lock(g_ctx_mutex);
+  if (live) g_live_ctx.insert(c);
+  else g_live_ctx.erase(c);
+}
+
 int frozen_matmul_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   int rc = qgemm_launch(ctx, w, a);
   if (rc || !w.dense16_lo || a.out_dtype != OUT_F32 || a.tok_mode) return rc;
@@ -82,12 +96,14 @@ rt_status rt_ctx_create(int device, rt_ctx** out) {
     return RT_ERR_CUDA;
   }
   c->num_sms = prop.multiProcessorCount;
+  rt::ctx_register(c, true);
   *out = c;
   return RT_OK;
 }
 
 void rt_ctx_destroy(rt_ctx* c) {
-  if (!c) return;
+  if (!c || !rt::ctx_alive(c)) return;
+  rt::ctx_register(c, false);
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
   rt_comm_destroy(c);
@@ -174,6 +190,7 @@ static rt_status frozen_create_f32(rt_ctx* c, size_t rows, size_t cols, const fl
   RT_CUDA(c, cudaSetDevice(c->device));
   rt_frozen* f = new rt_frozen();
   f->ctx = c;
+  f->device = c->device;
   rt::QWeight& w = f->w;
   w.fmt = rt::GGML_F16;
   w.rows = (int)rows;
@@ -213,6 +230,7 @@ rt_status rt_frozen_create(rt_ctx* c, int ggml_type, size_t rows, size_t cols, c
   RT_CUDA(c, cudaSetDevice(c->device));
   rt_frozen* f = new rt_frozen();
   f->ctx = c;
+  f->device = c->device;
   rt::QWeight& w = f->w;
   w.fmt = ggml_type;
   w.rows = (int)rows;
@@ -264,7 +282,8 @@ rt_status rt_frozen_create_q8_0(rt_ctx* c, size_t rows, size_t cols, const float
 
 void rt_frozen_destroy(rt_frozen* f) {
   if (!f) return;
-  cudaSetDevice(f->ctx->device);
+  cudaSetDevice(f->device);
+  if (!rt::ctx_alive(f->ctx)) cudaDeviceSynchronize();  // the context's stream is gone: finish whatever still reads the weight
   if (!f->borrowed) {
     if (f->w.bricks) cudaFree(f->w.bricks);
     if (f->w.dense16) cudaFree(f->w.dense16);

@@ -50,8 +50,15 @@ struct rt_ctx {
     if (e__ != cudaSuccess) return (ctx)->cuda_fail(e__, #call);  \
   } while (0)
 
+namespace rt {
+// Handles outlive their context when a host tears things down out of order (a garbage collector
+// does).  Destroy functions ask before they touch the context.
+bool ctx_alive(const rt_ctx* c);
+}
+
 struct rt_frozen {
   rt_ctx* ctx = nullptr;
+  int device = 0;
   rt::QWeight w;
   bool borrowed = false;  // the weight bytes live in a buffer another object owns (a stacked group of linears)
 };

@@ -2,7 +2,6 @@
 // are memory bound (rank <= 64 against thousands of tokens and features), as small
 // warp-level tensor-core kernels:
 //
-//   skinny_nt : Hs[M x 64] = X[M x K] . Wt[r x K]^T      (Hs = X.(sA)^T, Gs = dY.(sB))
 //   tok_contract : part[split][r x C] = sum_{m in split} P[m, i] * Q[m, j]
 //                  (dA = Gs^T.X, dB = dY^T.Hs), summed over splits in order by a second kernel
 //
@@ -49,72 +48,6 @@ __device__ __forceinline__ void load64x64(uint32_t sbase, const __half* g, int r
     const int gr = row0 + r, gc = col0 + c * 8;
     const bool ok = r < row_limit && gr < rows && gc < cols;
     cpa16(sbase + toff(r, c), g + (size_t)(ok ? gr : 0) * ld + (ok ? gc : 0), ok);
-  }
-}
-
-// ------------------------------------------------------------------ Hs = X . Wt^T
-// MW warps of 16 token rows each per CTA.  The skinny weight is re-read by every CTA, so more rows
-// per CTA mean less traffic; fewer CTAs than SMs would idle some, so the launcher picks MW by M.
-template <int R16, int MW>
-__global__ void __launch_bounds__(32 * MW)
-skinny_nt_kernel(const __half* __restrict__ X, const __half* __restrict__ Wt, int M, int K, int r, __half* __restrict__ out) {
-  constexpr int NST = 8;                       // stages in flight: the kernel is pure memory latency
-  constexpr int ROWS = 16 * MW, NT = 32 * MW;
-  constexpr int XB = ROWS * 128, WB = 16 * R16 * 128, SB = XB + WB;
-  extern __shared__ __align__(128) uint8_t smem[];
-  const uint32_t s0 = saddr(smem);
-  const int m0 = blockIdx.x * ROWS;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-  const int mat = lane >> 3, rr = lane & 7;
-  float acc[2 * R16][4];
-#pragma unroll
-  for (int i = 0; i < 2 * R16; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  const int nk = (K + 63) / 64;
-  auto load = [&](int kc) {
-    const uint32_t sx = s0 + (kc % NST) * SB, sw = sx + XB;
-    for (int e = threadIdx.x; e < ROWS * 8; e += NT) {
-      const int rw = e >> 3, c = e & 7, gr = m0 + rw, gc = kc * 64 + c * 8;
-      const bool ok = gr < M && gc < K;
-      cpa16(sx + toff(rw, c), X + (size_t)(ok ? gr : 0) * K + (ok ? gc : 0), ok);
-    }
-    for (int e = threadIdx.x; e < 16 * R16 * 8; e += NT) {
-      const int rw = e >> 3, c = e & 7, gc = kc * 64 + c * 8;
-      const bool ok = rw < r && gc < K;
-      cpa16(sw + toff(rw, c), Wt + (size_t)(ok ? rw : 0) * K + (ok ? gc : 0), ok);
-    }
-  };
-  for (int i = 0; i < NST - 1; ++i) {
-    if (i < nk) load(i);
-    cpa_commit();
-  }
-  for (int kc = 0; kc < nk; ++kc) {
-    if (kc + NST - 1 < nk) load(kc + NST - 1);
-    cpa_commit();
-    cpa_wait<NST - 1>();
-    __syncthreads();
-    const uint32_t sx = s0 + (kc % NST) * SB, sw = sx + XB;
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-      uint32_t a[4];
-      ldsm4(sx + toff(warp * 16 + (mat & 1) * 8 + rr, kk * 2 + (mat >> 1)), a);
-#pragma unroll
-      for (int np = 0; np < R16; ++np) {
-        uint32_t bf[4];
-        ldsm4(sw + toff(np * 16 + (mat >> 1) * 8 + rr, kk * 2 + (mat & 1)), bf);
-        mma(acc[2 * np], a, bf);
-        mma(acc[2 * np + 1], a, bf + 2);
-      }
-    }
-    __syncthreads();
-  }
-  const int i0 = m0 + warp * 16 + gq, i1 = i0 + 8;
-#pragma unroll
-  for (int nt = 0; nt < 2 * R16; ++nt) {
-    const int c = nt * 8 + 2 * tq;
-    if (c < r) {  // r is even, so the paired store never straddles the rank
-      if (i0 < M) *(__half2*)(out + (size_t)i0 * 64 + c) = __floats2half2_rn(acc[nt][0], acc[nt][1]);
-      if (i1 < M) *(__half2*)(out + (size_t)i1 * 64 + c) = __floats2half2_rn(acc[nt][2], acc[nt][3]);
-    }
   }
 }
 
@@ -383,32 +316,6 @@ __global__ void lora_grads_group_reduce_kernel(const float* __restrict__ partB, 
 }
 
 }  // namespace
-
-template <int R16, int MW>
-static void skinny_launch(const __half* X, const __half* Wt, int M, int K, int r, __half* out, cudaStream_t st) {
-  constexpr int SMEM = 8 * (16 * MW * 128 + 16 * R16 * 128);
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(skinny_nt_kernel<R16, MW>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-    attr = true;
-  }
-  skinny_nt_kernel<R16, MW><<<(M + 16 * MW - 1) / (16 * MW), 32 * MW, SMEM, st>>>(X, Wt, M, K, r, out);
-}
-int launch_skinny_nt(const __half* X, const __half* Wt, int M, int K, int r, __half* out, cudaStream_t st) {
-  if (M <= 0) return 0;
-  if (r <= 0 || r > 64 || (r & 1) || K % 8 != 0) return 1;
-  // 64 rows per CTA once that still gives every SM a CTA; 32 rows below
-  static int force = -1;  // measurement aid: RT_B200_SKINNY_ROWS=32|64 overrides the choice
-  if (force < 0) { const char* e = getenv("RT_B200_SKINNY_ROWS"); force = e ? atoi(e) : 0; }
-  const bool wide = force ? force == 64 : M >= 64 * 120;
-#define RT_SKINNY(R) do { if (wide) skinny_launch<R, 4>(X, Wt, M, K, r, out, st); else skinny_launch<R, 2>(X, Wt, M, K, r, out, st); } while (0)
-  if (r <= 16) RT_SKINNY(1);
-  else if (r <= 32) RT_SKINNY(2);
-  else RT_SKINNY(4);
-#undef RT_SKINNY
-  RT_COUNT_LAUNCH(1);
-  return cudaGetLastError() == cudaSuccess ? 0 : 3;
-}
 
 static void tok_plan(int M, int* tokens_per_split, int* splits) {
   int tps = 256;

@@ -75,6 +75,11 @@ int attn_backward(rt_ctx* c, const __half* q, const __half* k, const __half* v, 
   return launch_attn_bwd_tc(c, q, k, v, o, dO16, do_scale, row_scale, lse, seq_start, gap, M, nh, nkv, hd, delta, dq, dk, dv);
 }
 
+// out[M x 64] = X[M x K] . Wt[r x K]^T: the tcgen05 stream kernel, or (return 1) a shape it does not take
+static int lowrank_product(rt_ctx* c, const __half* X, const __half* Wt, int M, int K, int r, __half* out64) {
+  return launch_lowrank_tc(c, X, Wt, M, K, r, out64);
+}
+
 static QWeight dense_view(const __half* p, int rows, int cols) {
   QWeight w;
   w.fmt = GGML_F16;
@@ -88,7 +93,7 @@ rt_status linear_lora_h(rt_linear* l, const __half* x16, int M, __half* hs_out) 
   rt_ctx* c = l->ctx;
   lora_refresh(l);
   {
-    const int rc0 = launch_skinny_nt(x16, l->lora.a_s, M, l->in_dim(), l->lora.rank, hs_out, c->stream);
+    const int rc0 = lowrank_product(c, x16, l->lora.a_s, M, l->in_dim(), l->lora.rank, hs_out);
     if (rc0 == 0) return RT_OK;
     if (rc0 != 1) return c->fail(RT_ERR_CUDA, "lora H kernel launch failed");
   }
@@ -107,7 +112,7 @@ rt_status linear_lora_h(rt_linear* l, const __half* x16, int M, __half* hs_out) 
 }
 
 rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16, int M, void* y, int y_dtype,
-                             int accumulate, __half* hs_keep) {
+                             int accumulate, __half* hs_keep, bool hs_ready) {
   rt_ctx* c = l->ctx;
   if (M <= 0) return RT_OK;
   QGemmArgs a;
@@ -124,7 +129,7 @@ rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16,
     const int r = l->lora.rank;
     __half* hs = hs_keep ? hs_keep : lowrank_buf(c, sc.hs, sc.hs_rank, M, r);
     if (!hs) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
-    RT_TRY(linear_lora_h(l, x16, M, hs));
+    if (!(hs_keep && hs_ready)) RT_TRY(linear_lora_h(l, x16, M, hs));
     a.lora.act = hs;
     a.lora.w = l->lora.bp;
     a.lora.rank = r;
@@ -158,7 +163,7 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
     if (!hs || !gs) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
     // Hs = X . (sA)^T: recomputed as src/linear.rs:105 does, unless the caller kept it
     if (!hs_saved) RT_TRY(linear_lora_h(l, x16, M, hs));
-    int rc = launch_skinny_nt(dy16, l->lora.bt_s, M, N, r, gs, c->stream);
+    int rc = lowrank_product(c, dy16, l->lora.bt_s, M, N, r, gs);
     if (rc > 1) return c->fail(RT_ERR_CUDA, "lora G kernel launch failed");
     const bool g_done = rc == 0;
     QGemmArgs ga;  // Gs = dY~ . (sB)   (unit rows: the row scale is applied where Gs is consumed)
@@ -340,7 +345,8 @@ rt_status refresh_adapter_copies(rt_model* m) {
 }
 
 // y[M x rows_total] = X . [W_0; W_1; ..]^T (+ stacked bias, + stacked low-rank chunk)
-rt_status group_forward_dev(LinGroup& g, LinearScratch& sc, const __half* x16, int M, void* y, int y_dtype, __half* hs_keep) {
+rt_status group_forward_dev(LinGroup& g, LinearScratch& sc, const __half* x16, int M, void* y, int y_dtype, __half* hs_keep,
+                            bool hs_ready) {
   rt_ctx* c = g.lin[0]->ctx;
   if (M <= 0) return RT_OK;
   QGemmArgs a;
@@ -357,7 +363,8 @@ rt_status group_forward_dev(LinGroup& g, LinearScratch& sc, const __half* x16, i
     group_refresh(g, c->stream);
     __half* hs = hs_keep ? hs_keep : lowrank_buf(c, sc.hs, sc.hs_rank, M, g.rank_total);
     if (!hs) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
-    if (launch_skinny_nt(x16, g.a_s, M, g.w.cols, g.rank_total, hs, c->stream)) return c->fail(RT_ERR_CUDA, "lora H kernel launch failed");
+    if (!(hs_keep && hs_ready) && lowrank_product(c, x16, g.a_s, M, g.w.cols, g.rank_total, hs))
+      return c->fail(RT_ERR_CUDA, "lora H kernel launch failed");
     a.lora.act = hs;
     a.lora.w = g.bp;
     a.lora.rank = g.rank_total;
@@ -391,8 +398,8 @@ rt_status group_backward_dev(LinGroup& g, LinearScratch& sc, const __half* x16, 
     __half* hs = hs_saved ? const_cast<__half*>(hs_saved) : lowrank_buf(c, sc.hs, sc.hs_rank, M, R);
     __half* gs = lowrank_buf(c, sc.gs, sc.gs_rank, M, R);
     if (!hs || !gs) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
-    if (!hs_saved && launch_skinny_nt(x16, g.a_s, M, K, R, hs, c->stream)) return c->fail(RT_ERR_CUDA, "lora H kernel launch failed");
-    if (launch_skinny_nt(dy16, g.bt_s, M, NT, R, gs, c->stream)) return c->fail(RT_ERR_CUDA, "lora G kernel launch failed");
+    if (!hs_saved && lowrank_product(c, x16, g.a_s, M, K, R, hs)) return c->fail(RT_ERR_CUDA, "lora H kernel launch failed");
+    if (lowrank_product(c, dy16, g.bt_s, M, NT, R, gs)) return c->fail(RT_ERR_CUDA, "lora G kernel launch failed");
     if (!sc.grad_ws.reserve(lora_grads_workspace_floats(M, NT, K, R) * sizeof(float)))
       return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
     float *gbp[3], *gap[3];
@@ -470,6 +477,7 @@ rt_status rt_linear_create(rt_ctx* c, rt_frozen* w, const float* bias_host, cons
   RT_CUDA(c, cudaSetDevice(c->device));
   rt_linear* l = new rt_linear();
   l->ctx = c;
+  l->device = c->device;
   l->w = w;
   l->name = name ? name : "";
   if (bias_host) {
@@ -486,7 +494,7 @@ rt_status rt_linear_create(rt_ctx* c, rt_frozen* w, const float* bias_host, cons
 
 void rt_linear_destroy(rt_linear* l) {
   if (!l) return;
-  cudaSetDevice(l->ctx->device);
+  cudaSetDevice(l->device);
   if (l->bias) cudaFree(l->bias);
   l->lora.shadows.release();
   l->own_params.release();
@@ -639,6 +647,7 @@ rt_status rt_model_create(rt_ctx* c, const rt_model_config* cfg, rt_model** out)
   if (cfg->rot_dim <= 0 || cfg->rot_dim > cfg->head_dim || cfg->rot_dim % 2) return c->fail(RT_ERR_BAD_SHAPE, "bad rot_dim");
   rt_model* m = new rt_model();
   m->ctx = c;
+  m->device = c->device;
   m->cfg = *cfg;
   if (m->cfg.head_rows <= 0) m->cfg.head_rows = 1024;
   m->blocks.resize(cfg->n_layers);
@@ -648,8 +657,9 @@ rt_status rt_model_create(rt_ctx* c, const rt_model_config* cfg, rt_model** out)
 
 void rt_model_destroy(rt_model* m) {
   if (!m) return;
-  cudaSetDevice(m->ctx->device);
-  cudaStreamSynchronize(m->ctx->stream);
+  cudaSetDevice(m->device);
+  if (rt::ctx_alive(m->ctx)) cudaStreamSynchronize(m->ctx->stream);
+  else cudaDeviceSynchronize();  // destroyed after its context: the stream is gone, the device is not
   for (auto& b : m->blocks) {
     for (int i = 0; i < 7; ++i)
       if (b.lin[i]) rt_linear_destroy(b.lin[i]);
@@ -1036,7 +1046,9 @@ static bool ensure_tokens(rt_model* m, int M) {
   ok &= m->dq16.reserve(T * (qd + 2 * kvd) * 2);  // d(q) | d(k) | d(v)
   ok &= m->sc_q.reserve(T * 4) && m->sc_k.reserve(T * 4) && m->sc_v.reserve(T * 4);
   // zero beyond the rank, kept that way; 256 bytes of slack for reads that start at a column offset
-  for (int i = 0; i < 7; ++i) ok &= m->hs_keep[i].reserve(T * 64 * 2 * L + 256, true);
+  // every layer keeps its own Hs (128 bytes per token, layer and linear) whether or not the other
+  // caches are kept: a recomputed forward then reuses it instead of running the low-rank products again
+  for (int i = 0; i < 7; ++i) ok &= m->hs_keep[i].reserve(T * 64 * 2 * (size_t)g.n_layers + 256, true);
   if (ok) m->cap_tokens = M;
   return ok;
 }
@@ -1064,7 +1076,7 @@ static BlockActs block_acts(rt_model* m, int li, int M, bool own_slice) {
   a.v16 = m->v16.as<__half>() + o * kvd;
   a.o16 = m->o16.as<__half>() + o * qd;
   a.hm16 = m->hm16.as<__half>() + o * ff;
-  for (int i = 0; i < 7; ++i) a.hs[i] = m->hs_keep[i].as<__half>() + o * 64;
+  for (int i = 0; i < 7; ++i) a.hs[i] = m->hs_keep[i].as<__half>() + (size_t)li * T * 64;
   float* qkv = m->q_raw.as<float>() + o * (qd + 2 * kvd);
   a.q_raw = qkv;
   a.k_raw = a.qkv_group ? qkv + qd : qkv + T * qd;
@@ -1128,8 +1140,11 @@ static rt_status ensure_rope(rt_model* m, int max_pos) {
 // Block::forward (src/model.rs:165-183).  x_in is read only; h receives x_in + attention;
 // when x_out is non-null it receives the block output (h + mlp), and may alias h.  With `keep`
 // the adapters' Hs = X.(sA)^T are left in A.hs for the block's backward.
+// hs: 0 = the adapters' Hs go to scratch (forward-only passes), 1 = they are left in A.hs for the
+// block's backward, 2 = A.hs already holds them (the block's second forward when its caches are rebuilt).
 static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, float* h, float* x_out, const BlockActs& A,
-                               bool keep) {
+                               int hs) {
+  const bool keep = hs != 0, hs_ready = hs == 2;
   rt_ctx* c = m->ctx;
   const rt_model_config& g = m->cfg;
   BlockDev& b = m->blocks[li];
@@ -1137,11 +1152,11 @@ static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, fl
   const int d = g.hidden;
   launch_rmsnorm_fwd(x_in, b.input_norm, M, d, g.rms_eps, A.n1, st);
   if (A.qkv_group) {
-    RT_TRY(group_forward_dev(b.qkv, m->lsc, A.n1, M, A.q_raw, RT_DT_F32, keep ? A.hs[0] : nullptr));
+    RT_TRY(group_forward_dev(b.qkv, m->lsc, A.n1, M, A.q_raw, RT_DT_F32, keep ? A.hs[0] : nullptr, hs_ready));
   } else {
-    RT_TRY(linear_forward_dev(b.lin[0], m->lsc, A.n1, M, A.q_raw, RT_DT_F32, 0, keep ? A.hs[0] : nullptr));
-    RT_TRY(linear_forward_dev(b.lin[1], m->lsc, A.n1, M, A.k_raw, RT_DT_F32, 0, keep ? A.hs[1] : nullptr));
-    RT_TRY(linear_forward_dev(b.lin[2], m->lsc, A.n1, M, A.v_raw, RT_DT_F32, 0, keep ? A.hs[2] : nullptr));
+    RT_TRY(linear_forward_dev(b.lin[0], m->lsc, A.n1, M, A.q_raw, RT_DT_F32, 0, keep ? A.hs[0] : nullptr, hs_ready));
+    RT_TRY(linear_forward_dev(b.lin[1], m->lsc, A.n1, M, A.k_raw, RT_DT_F32, 0, keep ? A.hs[1] : nullptr, hs_ready));
+    RT_TRY(linear_forward_dev(b.lin[2], m->lsc, A.n1, M, A.v_raw, RT_DT_F32, 0, keep ? A.hs[2] : nullptr, hs_ready));
   }
   launch_qk_rope_fwd(A.q_raw, A.k_raw, A.v_raw, A.qkv_pitch, g.qk_norm ? b.q_norm : nullptr,
                      g.qk_norm ? b.k_norm : nullptr, m->pos.as<int>(), m->rope_cos.as<float>(), m->rope_sin.as<float>(), M,
@@ -1150,19 +1165,19 @@ static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, fl
                    g.n_kv_heads, g.head_dim, A.o16, A.lse))
     return c->fail(RT_ERR_CUDA, "attention forward launch failed");
   if (h != x_in) RT_CUDA(c, cudaMemcpyAsync(h, x_in, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
-  RT_TRY(linear_forward_dev(b.lin[3], m->lsc, A.o16, M, h, RT_DT_F32, 1, keep ? A.hs[3] : nullptr));
+  RT_TRY(linear_forward_dev(b.lin[3], m->lsc, A.o16, M, h, RT_DT_F32, 1, keep ? A.hs[3] : nullptr, hs_ready));
   launch_rmsnorm_fwd(h, b.post_norm, M, d, g.rms_eps, A.n2, st);
   if (A.gu_group) {
-    RT_TRY(group_forward_dev(b.gu, m->lsc, A.n2, M, A.g16, RT_DT_F16, keep ? A.hs[4] : nullptr));
+    RT_TRY(group_forward_dev(b.gu, m->lsc, A.n2, M, A.g16, RT_DT_F16, keep ? A.hs[4] : nullptr, hs_ready));
   } else {
-    RT_TRY(linear_forward_dev(b.lin[4], m->lsc, A.n2, M, A.g16, RT_DT_F16, 0, keep ? A.hs[4] : nullptr));
-    RT_TRY(linear_forward_dev(b.lin[5], m->lsc, A.n2, M, A.u16, RT_DT_F16, 0, keep ? A.hs[5] : nullptr));
+    RT_TRY(linear_forward_dev(b.lin[4], m->lsc, A.n2, M, A.g16, RT_DT_F16, 0, keep ? A.hs[4] : nullptr, hs_ready));
+    RT_TRY(linear_forward_dev(b.lin[5], m->lsc, A.n2, M, A.u16, RT_DT_F16, 0, keep ? A.hs[5] : nullptr, hs_ready));
   }
   launch_swiglu_fwd(A.g16, A.u16, A.gu_pitch, M, g.ff, A.hm16, st);
   if (x_out) {
     if (x_out != h) RT_CUDA(c, cudaMemcpyAsync(x_out, h, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
-    RT_TRY(linear_forward_dev(b.lin[6], m->lsc, A.hm16, M, x_out, RT_DT_F32, 1, keep ? A.hs[6] : nullptr));
-  } else if (keep && b.lin[6]->lora_active()) {
+    RT_TRY(linear_forward_dev(b.lin[6], m->lsc, A.hm16, M, x_out, RT_DT_F32, 1, keep ? A.hs[6] : nullptr, hs_ready));
+  } else if (keep && !hs_ready && b.lin[6]->lora_active()) {
     RT_TRY(linear_lora_h(b.lin[6], A.hm16, M, A.hs[6]));  // the backward needs it
   }
   return RT_OK;
@@ -1344,8 +1359,8 @@ static rt_status run_staged_body(rt_model* m, bool backward, float* logits_out_h
   for (int li = 0; li < g.n_layers; ++li) {
     if (backward) RT_CUDA(c, cudaMemcpyAsync(m->ckpt.as<float>() + (size_t)li * xd, x, xd * 4, cudaMemcpyDeviceToDevice, st));
     const BlockActs A = block_acts(m, li, M, store);
-    if (store) RT_TRY(block_forward(m, li, M, m->ckpt.as<float>() + (size_t)li * xd, A.h, x, A, true));  // keeps h and every Hs
-    else RT_TRY(block_forward(m, li, M, x, x, x, A, false));
+    if (store) RT_TRY(block_forward(m, li, M, m->ckpt.as<float>() + (size_t)li * xd, A.h, x, A, 1));  // keeps h and every Hs
+    else RT_TRY(block_forward(m, li, M, x, x, x, A, backward ? 1 : 0));  // a training pass keeps every Hs for the second forward
   }
   if (backward) RT_CUDA(c, cudaMemsetAsync(m->dx.p, 0, xd * 4, st));
   if (n_targets > 0) RT_TRY(model_head(m, M, n_targets, backward, logits_out_host));
@@ -1355,7 +1370,7 @@ static rt_status run_staged_body(rt_model* m, bool backward, float* logits_out_h
   for (int li = g.n_layers - 1; li >= 0; --li) {
     const float* x_in = m->ckpt.as<float>() + (size_t)li * xd;
     const BlockActs A = block_acts(m, li, M, store);
-    if (!store) RT_TRY(block_forward(m, li, M, x_in, A.h, nullptr, A, true));  // rebuild the block's caches
+    if (!store) RT_TRY(block_forward(m, li, M, x_in, A.h, nullptr, A, 2));  // rebuild the block's caches (Hs is still there)
     RT_TRY(block_backward(m, li, M, x_in, A));
   }
   return RT_OK;

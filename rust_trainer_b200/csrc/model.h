@@ -31,6 +31,7 @@ struct LoraDev {
 
 struct rt_linear {
   rt_ctx* ctx = nullptr;
+  int device = 0;
   std::string name;
   rt_frozen* w = nullptr;
   bool owns_w = false;
@@ -53,7 +54,7 @@ namespace rt {
 // hs_keep: optional [M x 64] f16 buffer (zero beyond the rank) that receives Hs = X.(sA)^T so the
 // backward can reuse it instead of recomputing it.
 rt_status linear_forward_dev(rt_linear* l, LinearScratch& sc, const __half* x16, int M, void* y, int y_dtype,
-                             int accumulate, __half* hs_keep = nullptr);
+                             int accumulate, __half* hs_keep = nullptr, bool hs_ready = false);
 // Hs alone (the forward of a linear whose output is not needed).
 rt_status linear_lora_h(rt_linear* l, const __half* x16, int M, __half* hs_out);
 // dy16 is row-normalised f16 with per-row scales `dscale` (null = all ones).  With
@@ -98,6 +99,7 @@ struct BlockDev {
 
 struct rt_model {
   rt_ctx* ctx = nullptr;
+  int device = 0;
   rt_model_config cfg;
   bool finalized = false;
   rt_frozen* embed = nullptr;

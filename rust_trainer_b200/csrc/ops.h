@@ -69,7 +69,8 @@ void launch_adamw(float* p, float* g, float* m, float* v, size_t n, const double
 void launch_global_normalize(const float* x, size_t n, float* amax_dev, __half* y16, cudaStream_t st);
 
 // ---- lora_kernels.cu: skinny low-rank products (return 1 when the shape is not supported)
-int launch_skinny_nt(const __half* X, const __half* Wt, int M, int K, int r, __half* out64, cudaStream_t st);
+// ---- lowrank_tc.cu: out64[M x 64] (f16, zero from column r up) = X[M x K] . Wt[r x K]^T on tcgen05; 1 = shape not taken
+int launch_lowrank_tc(rt_ctx* c, const __half* X, const __half* Wt, int M, int K, int r, __half* out64);
 size_t tok_contract_workspace_floats(int M, int C, int r);
 size_t lora_grads_workspace_floats(int M, int N, int K, int r);
 int launch_lora_grads_group(const __half* hs, const __half* dy16, const __half* gs, const __half* x16, const float* dscale,

@@ -1078,20 +1078,23 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
     if (rc) return rc;
   }
   int n_tiles = p.n_row_tiles * p.n_tok_tiles;
-  // split-K when the tiles alone cannot fill the GPU and the contraction is long
-  int splits = 1;
-  if (a.out_dtype == OUT_F32 && n_tiles * 2 <= num_sms && p.n_main >= 8) {
-    splits = num_sms / n_tiles;
+  // How the contraction is cut into accumulation chains depends on the weight's shape ONLY, never
+  // on the number of tokens: the tensor core's accumulator does not round to nearest, so two
+  // partitions of one sum differ by a few 1e-6 relative, which the next 16-bit rounding of the
+  // activations amplifies a hundredfold.  With a token-dependent split-K a sequence's result
+  // depended on its batch mates (a shard of one or two sequences against the whole batch: 7e-4
+  // on the gradients); with a fixed partition it is bit-identical in any batch.
+  // A very long contraction (the head's backward runs over the whole vocabulary) is accumulated
+  // in pieces of a FIXED 8192 elements whose f32 partial sums are added afterwards: the error of
+  // one chain grows with its length (about 3e-4 relative over 150 000 elements).
+  p.steps_per_split = p.n_main;
+  if (!a.tok_mode && a.out_dtype == OUT_F32 && p.n_main > 256) p.steps_per_split = 128;
+  if (a.tok_mode) {
+    int splits = num_sms / (n_tiles > 0 ? n_tiles : 1);
     if (splits > p.n_main / 4) splits = p.n_main / 4;
     if (splits < 1) splits = 1;
+    p.steps_per_split = (p.n_main + splits - 1) / splits;
   }
-  p.steps_per_split = (p.n_main + splits - 1) / splits;
-  // A very long contraction (the head's backward runs over the whole vocabulary) is accumulated
-  // in pieces of a FIXED 8192 elements whose f32 partial sums are added afterwards: the tensor
-  // core's accumulator does not round to nearest, so the error of one chain grows with its
-  // length (about 3e-4 relative over 150 000 elements), and a piece length that depended on the
-  // batch would make the result depend on how a batch is split over ranks.
-  if (!a.tok_mode && a.out_dtype == OUT_F32 && !a.fixed_part && p.n_main > 256 && p.steps_per_split > 128) p.steps_per_split = 128;
   p.n_splits = (p.n_main + p.steps_per_split - 1) / p.steps_per_split;
   p.b_mn = a.tok_mode ? 1 : 0;
   // CTA pairs: 256 weight rows per tile, each CTA stages half of the tokens.  Needs whole pairs of
@@ -1248,8 +1251,8 @@ __global__ void wait_selftest_kernel(int* status, long long limit_cycles) {
 }
 
 // ------------------------------------------------------------------ allocation-free entry point
-// Split-K partial sums of rt_frozen_backward_input_dev_noalloc live here instead of in memory
-// from cudaMalloc.  Every GPU that loads the library holds these 8 MiB until the process exits.
+// The partial sums of a contraction that is accumulated in pieces (more than 16384 weight rows)
+// live here for rt_frozen_backward_input_dev_noalloc instead of in memory from cudaMalloc.  Every GPU that loads the library holds these 8 MiB until the process exits.
 constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)2 << 20;
 static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
 static float* g_noalloc_scratch_addr[64] = {nullptr};  // device address of the array, per device ordinal

@@ -368,3 +368,17 @@ def test_communicator_of_one_rank(ctx):
 
         lib().rt_comm_destroy(ctx._h)
     gm.close()
+
+
+def test_handles_may_outlive_their_context():
+    """A host that tears down out of order (a garbage collector does) destroys a model after its
+    context: the destroy calls must notice and not touch the context."""
+    c2 = rt.Context(0)
+    spec = synth.preset("tiny-qwen3", quant="Q4_0", seed=3, w_std=0.05)
+    gm = rt.Model(c2, spec.config(), synth.build_tensors(spec))
+    gm.attach_lora(4, 8.0, None, 1)
+    f = rt.Frozen.f32(c2, np.ones((8, 64), np.float32))
+    c2.close()
+    gm.close()
+    f.close()
+    c2.close()  # twice is fine

@@ -2,9 +2,9 @@
 
 Some hosts cannot let a library call cudaMalloc while they run (all of HBM belongs to their own
 pool, or they sit in a loop that must not block on the driver's allocator).  For them
-rt_frozen_backward_input_dev_noalloc keeps its split-K partial sums in a fixed array inside the
-library instead of grow-on-demand scratch.  The shape below forces a split contraction (long
-contraction, few output tiles), so the array is really used; both entry points run the same
+rt_frozen_backward_input_dev_noalloc keeps the partial sums of a long contraction in a fixed array
+inside the library instead of grow-on-demand scratch.  The shape below is accumulated in pieces
+(more than 16384 weight rows to contract), so the array is really used; both entry points run the same
 kernel, so the results must agree to the last bit.  Two calls in a row check that the second
 call is not disturbed by what the first left in the shared array.  Collected last on purpose.
 """
@@ -25,7 +25,7 @@ def test_no_alloc_matches_regular_entry_point_twice(ctx):
 
     L = lib()
     rng = np.random.default_rng(42)
-    n, k = 8192, 256  # contraction over 8192 weight rows, only two output tiles: split-K territory
+    n, k = 32768, 256  # contraction over 32768 weight rows: four pieces of 8192 whose partial sums are added
     f = rt.Frozen.from_f32(ctx, (rng.standard_normal((n, k)) * 0.02).astype(np.float32), Q.Q8_0)
     for call, t in enumerate((200, 77)):
         dy = torch.randn(t, n, device="cuda", dtype=torch.float16)
@@ -57,9 +57,9 @@ def test_no_alloc_refuses_more_than_its_array_holds(ctx):
 
     L = lib()
     rng = np.random.default_rng(43)
-    # 8192 weight rows to contract, two output tiles of 128, 384 rows: the kernel would use 22 splits,
-    # 22 x 384 x 256 floats = 2.06 Mi floats of partial sums, more than the 2 Mi the array holds
-    n, k, t = 8192, 256, 384
+    # 32768 weight rows to contract in four pieces, 2304 rows: 4 x 2304 x 256 floats = 2.25 Mi floats
+    # of partial sums, more than the 2 Mi the array holds
+    n, k, t = 32768, 256, 2304
     f = rt.Frozen.from_f32(ctx, (rng.standard_normal((n, k)) * 0.02).astype(np.float32), Q.Q8_0)
     dy = torch.zeros(t, n, device="cuda", dtype=torch.float16)
     dx = torch.zeros(t, k, device="cuda", dtype=torch.float32)
