@@ -172,3 +172,31 @@ def test_loss_is_linear_in_weights():
     m.zero_grad()
     m.forward_backward(toks, tp, tt, np.full(tp.size, 0.5, np.float32))
     assert rel_l2(m.lora[0]["ga"], 2 * g1) < 1e-5
+
+
+@pytest.mark.parametrize("t", [Q.Q8_0, Q.Q4_0, Q.Q4_K, Q.Q6_K, Q.F16])
+def test_int8_activation_mode_bounds_the_rounding(t):
+    # src/rie.rs:77-80: the engine's forward rounds activations to 8 bits per block.  Mode (ii)
+    # restates that rounding; it moves a forward product by at most the rounding's own size
+    # (half a step of amax/127 per element: about 0.5 % of the row in rel-L2), leaves 16-bit
+    # weights and the backward alone, and is off again afterwards.
+    rng = np.random.default_rng(5)
+    n, k, m = 64, 512, 7
+    packed = Q.quantize((rng.standard_normal((n, k)) * 0.1).astype(np.float32), t)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    smooth = O.frozen_forward(t, n, k, packed, x, m)
+    try:
+        O.set_act_int8(True)
+        rounded = O.frozen_forward(t, n, k, packed, x, m)
+        dx = np.zeros((m, k), np.float32)
+        O.frozen_backward_input(t, n, k, packed, smooth, m, dx)
+    finally:
+        O.set_act_int8(False)
+    if t == Q.F16:
+        assert np.array_equal(rounded, smooth)
+    else:
+        assert 1e-4 < rel_l2(rounded, smooth) < 2e-2
+    dx0 = np.zeros((m, k), np.float32)
+    O.frozen_backward_input(t, n, k, packed, smooth, m, dx0)
+    assert np.array_equal(dx, dx0)
+    assert np.array_equal(O.frozen_forward(t, n, k, packed, x, m), smooth)
