@@ -20,6 +20,7 @@
 // reference's `allowed` rule for packed shared-prompt groups, src/ops.rs:156-164).
 // Every wait is bounded and reports through the ctx status word.
 #include "ctx.h"
+#include "pdl.cuh"
 #include "ptx.cuh"
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -86,7 +87,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;  // 128-byte-swizzled tiles start on 1 KB boundaries
+  pdl_launch_dependents();
   if (pad + L::USED > L::TOTAL) {
+    pdl_wait();
     if (threadIdx.x == 0) atomicCAS(status, 0, RT_ERR_CUDA);
     return;
   }
@@ -136,6 +139,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
+  pdl_wait();  // seq_start, read above, is an input of the whole pass, not a predecessor's output
 
   if (warp == 4) {
     // ------------------------------------------------------------ TMA producer
@@ -361,7 +365,7 @@ int fwd_tc_impl(rt_ctx* c, const __half* q, const __half* k, const __half* v, co
   if (tensor_map_f16_2d(c, &tk, k, (uint64_t)M, (uint64_t)nkv * HD, 64, BN)) return 3;
   if (tensor_map_f16_2d(c, &tv, v, (uint64_t)M, (uint64_t)nkv * HD, 64, BN)) return 3;
   dim3 grid((M + BM - 1) / BM, nh);
-  attn_fwd_tc_kernel<HD><<<grid, 192, L::TOTAL, c->stream>>>(tq, tk, tv, to, seq_start, gap, M, nh, nkv, 1.0f / sqrtf((float)HD),
+  pdl(attn_fwd_tc_kernel<HD>, grid, 192, L::TOTAL, c->stream)(tq, tk, tv, to, seq_start, gap, M, nh, nkv, 1.0f / sqrtf((float)HD),
                                                             lse, c->status_dev);
   RT_COUNT_LAUNCH(1);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
@@ -422,6 +426,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* sm = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  pdl_launch_dependents();
   uint64_t* bars = (uint64_t*)(sm + L::OFF_BAR);
   uint64_t* kv_full = bars + 0;
   uint64_t* q_full = bars + 1;    // [NS] Q, dO and the per-query vectors of an item
@@ -474,6 +479,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
+  pdl_wait();
   const float inv_top = row_scale ? 1.0f / fmaxf(do_scale[0], 1e-38f) : 1.0f;
 
   if (warp == BWD_TMA_WARP) {
@@ -729,6 +735,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* sm = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  pdl_launch_dependents();
   uint64_t* bars = (uint64_t*)(sm + L::OFF_BAR);
   constexpr int NS = L::NS;
   uint64_t* qdo_full = bars + 0;
@@ -778,6 +785,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
+  pdl_wait();
   AT_STAMP_Q(511);
 
   if (warp == BWD_TMA_WARP) {
@@ -950,6 +958,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 template <int HD>
 __global__ void attn_delta_tc_kernel(const __half* __restrict__ o, const __half* __restrict__ dO, int M, int nh,
                                      float* __restrict__ delta) {
+  pdl_entry();
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= M * nh) return;
   const int m = w / nh, h = w % nh;
@@ -989,11 +998,11 @@ int bwd_tc_impl(rt_ctx* c, const __half* q, const __half* k, const __half* v, co
   const float scale = 1.0f / sqrtf((float)HD);
   cudaStream_t st = c->stream;
   const int warps = M * nh;
-  attn_delta_tc_kernel<HD><<<(warps * 32 + 255) / 256, 256, 0, st>>>(o, dO, M, nh, delta);
+  pdl(attn_delta_tc_kernel<HD>, (warps * 32 + 255) / 256, 256, 0, st)(o, dO, M, nh, delta);
   dim3 gkv((M + 127) / 128, nkv), gq((M + BM - 1) / BM, nh);
-  attn_bwd_dkdv_tc_kernel<HD><<<gkv, BWD_THREADS, LK::TOTAL, st>>>(tk128, tv128, tq64, tdo64, do_scale, row_scale, lse, delta, seq_start, gap,
+  pdl(attn_bwd_dkdv_tc_kernel<HD>, gkv, BWD_THREADS, LK::TOTAL, st)(tk128, tv128, tq64, tdo64, do_scale, row_scale, lse, delta, seq_start, gap,
                                                           M, nh, nkv, scale, dk, dv, c->status_dev);
-  attn_bwd_dq_tc_kernel<HD><<<gq, BWD_THREADS, LQ::TOTAL, st>>>(tq128, tdo128, tk64, tv64, do_scale, row_scale, lse, delta, seq_start, gap, M,
+  pdl(attn_bwd_dq_tc_kernel<HD>, gq, BWD_THREADS, LQ::TOTAL, st)(tq128, tdo128, tk64, tv64, do_scale, row_scale, lse, delta, seq_start, gap, M,
                                                        nh, nkv, scale, dq, c->status_dev);
   RT_COUNT_LAUNCH(3);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;

@@ -8,6 +8,7 @@
 // Operands are f16, accumulation f32.  Tiles are 64 halves wide (128-byte rows) with the
 // 16-byte chunks XOR-swizzled by row, loaded with cp.async and double buffered.
 #include "ops.h"
+#include "pdl.cuh"
 #include "rt_internal.h"
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -270,6 +271,7 @@ __global__ void __launch_bounds__(128) lora_grads_kernel(const LoraGradArgs g) {
 // gb[n*r + i] += sum_s partB[s][i, n] ; ga[i*K + k] += sum_s partA[s][i, k]   (splits in order: deterministic)
 __global__ void lora_grads_reduce_kernel(const float* __restrict__ partB, const float* __restrict__ partA, int splits, int N,
                                          int K, int r, float* __restrict__ gb, float* __restrict__ ga) {
+  pdl_entry();
   const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t nB = (size_t)r * N, nA = (size_t)r * K;
   if (e < nB) {
@@ -290,6 +292,7 @@ __global__ void lora_grads_reduce_kernel(const float* __restrict__ partB, const 
 // partA is [splits][R x K] with member j owning rows rank_off..+r.
 __global__ void lora_grads_group_reduce_kernel(const float* __restrict__ partB, const float* __restrict__ partA, int splits,
                                                int NT, int K, int R, const LoraGroupTable t) {
+  pdl_entry();
   size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t nB = (size_t)R * NT, nA = (size_t)R * K;
   for (int j = 0; j < t.n; ++j) {
@@ -363,12 +366,25 @@ size_t lora_grads_workspace_floats(int M, int N, int K, int r) {
 // hs / gs are [M x 64] matrices; a pointer into such a matrix at a column offset (a multiple of 8)
 // selects the r columns from there on, and then the 64-wide row reads run past the last row's end
 // by that offset: the caller keeps that much slack behind the matrix.  dy16 has row pitch ld_dy.
-int launch_lora_grads(const __half* hs, const __half* dy16, int ld_dy, const __half* gs, const __half* x16, const float* dscale,
-                      int M, int N, int K, int r, float* gb, float* ga, float* workspace, cudaStream_t st) {
+int launch_lora_grads(rt_ctx* c, const __half* hs, const __half* dy16, int ld_dy, const __half* gs, const __half* x16,
+                      const float* dscale, int M, int N, int K, int r, float* gb, float* ga, float* workspace, cudaStream_t st) {
   if (M <= 0) return 0;
   if (ld_dy <= 0) ld_dy = N;
   if (r <= 0 || r > 64 || N % 8 != 0 || K % 8 != 0 || ld_dy % 8 != 0) return 1;
   int tps, splits;
+  {  // the tcgen05 kernel takes every shape whose pointers are 16-byte aligned
+    const int tps_tc = lora_grads_tc_tokens_per_split(M), splits_tc = (M + tps_tc - 1) / tps_tc;
+    float* pB = workspace;
+    float* pA = workspace + (size_t)splits_tc * r * N;
+    const int rc = launch_lora_grads_tc(c, hs, dy16, ld_dy, gs, x16, dscale, M, N, K, r, pB, pA);
+    if (rc == 3) return 3;
+    if (rc == 0) {
+      const size_t n = (size_t)r * ((size_t)N + (size_t)K);
+      pdl(lora_grads_reduce_kernel, (unsigned)((n + 255) / 256), 256, 0, st)(pB, pA, splits_tc, N, K, r, gb, ga);
+      RT_COUNT_LAUNCH(1);
+      return cudaGetLastError() == cudaSuccess ? 0 : 3;
+    }
+  }
   tok_plan(M, &tps, &splits);
   LoraGradArgs g;
   g.Pb = hs; g.Qb = dy16; g.Pa = gs; g.Qa = x16;
@@ -392,19 +408,39 @@ int launch_lora_grads(const __half* hs, const __half* dy16, int ld_dy, const __h
   else if (r <= 32) lora_grads_kernel<2><<<grid, 128, TOK_SMEM, st>>>(g);
   else lora_grads_kernel<4><<<grid, 128, TOK_SMEM, st>>>(g);
   const size_t n = (size_t)r * ((size_t)N + (size_t)K);
-  lora_grads_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g.partB, g.partA, splits, N, K, r, gb, ga);
+  pdl(lora_grads_reduce_kernel, (unsigned)((n + 255) / 256), 256, 0, st)(g.partB, g.partA, splits, N, K, r, gb, ga);
   RT_COUNT_LAUNCH(2);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
 // dA and dB of every member of a stacked group in one product launch and one reduce launch.
 // gb/ga/row_off/rows/rank_off/rank: per member (n <= 3).  Workspace: lora_grads_workspace_floats(M, NT, K, R).
-int launch_lora_grads_group(const __half* hs, const __half* dy16, const __half* gs, const __half* x16, const float* dscale,
-                            int M, int NT, int K, int R, int n, float* const* gb, float* const* ga, const int* row_off,
-                            const int* rows, const int* rank_off, const int* rank, float* workspace, cudaStream_t st) {
+int launch_lora_grads_group(rt_ctx* c, const __half* hs, const __half* dy16, const __half* gs, const __half* x16,
+                            const float* dscale, int M, int NT, int K, int R, int n, float* const* gb, float* const* ga,
+                            const int* row_off, const int* rows, const int* rank_off, const int* rank, float* workspace,
+                            cudaStream_t st) {
   if (M <= 0 || n <= 0) return 0;
   if (n > 3 || R <= 0 || R > 64 || NT % 8 != 0 || K % 8 != 0) return 1;
   int tps, splits;
+  {
+    const int tps_tc = lora_grads_tc_tokens_per_split(M), splits_tc = (M + tps_tc - 1) / tps_tc;
+    float* pB = workspace;
+    float* pA = workspace + (size_t)splits_tc * R * NT;
+    const int rc = launch_lora_grads_tc(c, hs, dy16, NT, gs, x16, dscale, M, NT, K, R, pB, pA);
+    if (rc == 3) return 3;
+    if (rc == 0) {
+      LoraGroupTable t;
+      t.n = n;
+      size_t total = 0;
+      for (int j = 0; j < n; ++j) {
+        t.m[j] = LoraGroupMember{gb[j], ga[j], row_off[j], rows[j], rank_off[j], rank[j]};
+        total += (size_t)rank[j] * ((size_t)rows[j] + (size_t)K);
+      }
+      pdl(lora_grads_group_reduce_kernel, (unsigned)((total + 255) / 256), 256, 0, st)(pB, pA, splits_tc, NT, K, R, t);
+      RT_COUNT_LAUNCH(1);
+      return cudaGetLastError() == cudaSuccess ? 0 : 3;
+    }
+  }
   tok_plan(M, &tps, &splits);
   LoraGradArgs g;
   g.Pb = hs; g.Qb = dy16; g.Pa = gs; g.Qa = x16;
@@ -434,7 +470,7 @@ int launch_lora_grads_group(const __half* hs, const __half* dy16, const __half* 
     t.m[j] = LoraGroupMember{gb[j], ga[j], row_off[j], rows[j], rank_off[j], rank[j]};
     total += (size_t)rank[j] * ((size_t)rows[j] + (size_t)K);
   }
-  lora_grads_group_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(g.partB, g.partA, splits, NT, K, R, t);
+  pdl(lora_grads_group_reduce_kernel, (unsigned)((total + 255) / 256), 256, 0, st)(g.partB, g.partA, splits, NT, K, R, t);
   RT_COUNT_LAUNCH(2);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }

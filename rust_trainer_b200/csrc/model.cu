@@ -185,7 +185,7 @@ rt_status linear_backward_dev(rt_linear* l, LinearScratch& sc, const __half* x16
     const float* alpha = nullptr;
     const size_t wsf2 = lora_grads_workspace_floats(M, N, K, r);
     if (!sc.grad_ws.reserve(wsf2 * sizeof(float))) return c->fail(RT_ERR_CUDA, "out of device memory (lora scratch)");
-    int rb = launch_lora_grads(hs, dy16, N, gs, x16, dscale, M, N, K, r, l->lora.gb, l->lora.ga, sc.grad_ws.as<float>(), c->stream);
+    int rb = launch_lora_grads(c, hs, dy16, N, gs, x16, dscale, M, N, K, r, l->lora.gb, l->lora.ga, sc.grad_ws.as<float>(), c->stream);
     if (rb > 1) return c->fail(RT_ERR_CUDA, "lora gradient kernel launch failed");
     int ra = rb;
     if (rb == 1) {  // shapes the fused kernels do not cover: one product at a time
@@ -411,7 +411,7 @@ rt_status group_backward_dev(LinGroup& g, LinearScratch& sc, const __half* x16, 
       roff[nm] = g.row_off[i]; rws[nm] = l->out_dim(); koff[nm] = g.rank_off[i]; rk[nm] = l->lora.rank;
       ++nm;
     }
-    if (launch_lora_grads_group(hs, dy16, gs, x16, dscale, M, NT, K, R, nm, gbp, gap, roff, rws, koff, rk,
+    if (launch_lora_grads_group(c, hs, dy16, gs, x16, dscale, M, NT, K, R, nm, gbp, gap, roff, rws, koff, rk,
                                 sc.grad_ws.as<float>(), c->stream))
       return c->fail(RT_ERR_CUDA, "lora gradient kernel launch failed");
     a.lora.act = gs;

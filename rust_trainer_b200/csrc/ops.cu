@@ -6,6 +6,7 @@
 // the scale back in (the matmul is linear in each token row).
 #include "ctx.h"
 #include "ops.h"
+#include "pdl.cuh"
 
 namespace rt {
 
@@ -119,6 +120,7 @@ void launch_split_f32_hi_lo(const float* w, size_t n, __half* hi, __half* lo, cu
 // Row-normalised f16 copy: y16[r,:] = x[r,:] / amax_r, scale[r] = amax_r (1 if the row is zero).
 __global__ void normalize_rows_kernel(const float* __restrict__ x, int d, __half* __restrict__ y16,
                                       float* __restrict__ scale) {
+  pdl_entry();
   const size_t r = blockIdx.x;
   const float* xr = x + r * d;
   float m = 0.f;
@@ -132,7 +134,7 @@ __global__ void normalize_rows_kernel(const float* __restrict__ x, int d, __half
   if (threadIdx.x == 0) scale[r] = m;
 }
 void launch_normalize_rows(const float* x, int rows, int d, __half* y16, float* scale, cudaStream_t st) {
-  if (rows > 0) { normalize_rows_kernel<<<rows, 256, 0, st>>>(x, d, y16, scale); RT_COUNT_LAUNCH(1); }
+  if (rows > 0) { pdl(normalize_rows_kernel, rows, 256, 0, st)(x, d, y16, scale); RT_COUNT_LAUNCH(1); }
 }
 
 // ------------------------------------------------------------------ RMSNorm (reference src/ops.rs:8-56)
@@ -170,6 +172,7 @@ template <int NV>  // float4s per lane: d = 128 * NV
 __global__ void __launch_bounds__(256)
 rmsnorm_fwd_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, int rows, float eps,
                         __half* __restrict__ y16) {
+  pdl_entry();
   constexpr int D = 128 * NV;
   const int lane = threadIdx.x & 31;
   const size_t r = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -197,6 +200,7 @@ __global__ void __launch_bounds__(256)
 rmsnorm_bwd_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ dn,
                         const float* dres, int rows, float eps, float* out, __half* __restrict__ out16,
                         float* __restrict__ scale) {
+  pdl_entry();
   constexpr int D = 128 * NV;
   const int lane = threadIdx.x & 31;
   const size_t r = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -247,14 +251,14 @@ void launch_rmsnorm_fwd(const float* x, const float* w, int rows, int d, float e
   const bool warp_ok = d % 128 == 0 && nv >= 1 && nv <= 8 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
   if (warp_ok) {
     switch (nv) {
-      case 1: rmsnorm_fwd_warp_kernel<1><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
-      case 2: rmsnorm_fwd_warp_kernel<2><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
-      case 3: rmsnorm_fwd_warp_kernel<3><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
-      case 4: rmsnorm_fwd_warp_kernel<4><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
-      case 5: rmsnorm_fwd_warp_kernel<5><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
-      case 6: rmsnorm_fwd_warp_kernel<6><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
-      case 7: rmsnorm_fwd_warp_kernel<7><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
-      default: rmsnorm_fwd_warp_kernel<8><<<grid, 256, 0, st>>>(x, w, rows, eps, y16); break;
+      case 1: pdl(rmsnorm_fwd_warp_kernel<1>, grid, 256, 0, st)(x, w, rows, eps, y16); break;
+      case 2: pdl(rmsnorm_fwd_warp_kernel<2>, grid, 256, 0, st)(x, w, rows, eps, y16); break;
+      case 3: pdl(rmsnorm_fwd_warp_kernel<3>, grid, 256, 0, st)(x, w, rows, eps, y16); break;
+      case 4: pdl(rmsnorm_fwd_warp_kernel<4>, grid, 256, 0, st)(x, w, rows, eps, y16); break;
+      case 5: pdl(rmsnorm_fwd_warp_kernel<5>, grid, 256, 0, st)(x, w, rows, eps, y16); break;
+      case 6: pdl(rmsnorm_fwd_warp_kernel<6>, grid, 256, 0, st)(x, w, rows, eps, y16); break;
+      case 7: pdl(rmsnorm_fwd_warp_kernel<7>, grid, 256, 0, st)(x, w, rows, eps, y16); break;
+      default: pdl(rmsnorm_fwd_warp_kernel<8>, grid, 256, 0, st)(x, w, rows, eps, y16); break;
     }
   } else {
     rmsnorm_fwd_kernel<<<rows, 256, 0, st>>>(x, w, d, eps, y16);
@@ -333,7 +337,7 @@ void launch_rmsnorm_bwd(const float* x, const float* w, const float* dn, const f
   const bool warp_ok = d % 128 == 0 && nv >= 1 && nv <= 8 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
                        ((uintptr_t)dn & 15) == 0 && ((uintptr_t)out & 15) == 0 && (!dres || ((uintptr_t)dres & 15) == 0);
   if (warp_ok) {
-#define RT_RMSB(N) rmsnorm_bwd_warp_kernel<N><<<grid, 256, 0, st>>>(x, w, dn, dres, rows, eps, out, out16, scale)
+#define RT_RMSB(N) pdl(rmsnorm_bwd_warp_kernel<N>, grid, 256, 0, st)(x, w, dn, dres, rows, eps, out, out16, scale)
     switch (nv) {
       case 1: RT_RMSB(1); break;
       case 2: RT_RMSB(2); break;
@@ -512,6 +516,7 @@ qk_rope_fwd_reg_kernel(const float* __restrict__ q_raw, const float* __restrict_
                        const float* __restrict__ qw, const float* __restrict__ kw, const int* __restrict__ pos,
                        const float* __restrict__ cs, const float* __restrict__ sn, int nh, int nkv, int rot, int neox,
                        float eps, __half* __restrict__ q16, __half* __restrict__ k16, __half* __restrict__ v16) {
+  pdl_entry();
   constexpr int HD = 32 * EPL;
   const size_t m = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -566,6 +571,7 @@ qk_rope_bwd_reg_kernel(const float* __restrict__ dq, const float* __restrict__ d
                        const float* __restrict__ sn, int nh, int nkv, int rot, int neox, float eps,
                        __half* __restrict__ dq16, __half* __restrict__ dk16, __half* __restrict__ dv16,
                        float* __restrict__ sq, float* __restrict__ sk, float* __restrict__ sv) {
+  pdl_entry();
   constexpr int HD = 32 * EPL;
   __shared__ float wmax[3][8];
   const size_t m = blockIdx.x;
@@ -675,7 +681,7 @@ void launch_qk_rope_fwd(const float* q_raw, const float* k_raw, const float* v_r
   // raw_pitch = 0: three separate row-major matrices; else one row pitch for all three (slices of one matrix)
   const size_t pq = raw_pitch ? raw_pitch : (size_t)nh * hd, pk = raw_pitch ? raw_pitch : (size_t)nkv * hd, pv = pk;
   if (rope_reg_ok(nh, nkv, hd, rot, neox, &epl, &hpw)) {
-#define RT_ROPE_FWD(E, H) qk_rope_fwd_reg_kernel<E, H><<<M, 256, 0, st>>>(q_raw, k_raw, v_raw, pq, pk, pv, qw, kw, pos, cs, sn, nh, nkv, rot, neox, eps, q16, k16, v16)
+#define RT_ROPE_FWD(E, H) pdl(qk_rope_fwd_reg_kernel<E, H>, M, 256, 0, st)(q_raw, k_raw, v_raw, pq, pk, pv, qw, kw, pos, cs, sn, nh, nkv, rot, neox, eps, q16, k16, v16)
     if (epl == 4) { if (hpw == 4) RT_ROPE_FWD(4, 4); else if (hpw == 6) RT_ROPE_FWD(4, 6); else RT_ROPE_FWD(4, 8); }
     else { if (hpw == 4) RT_ROPE_FWD(2, 4); else if (hpw == 6) RT_ROPE_FWD(2, 6); else RT_ROPE_FWD(2, 8); }
 #undef RT_ROPE_FWD
@@ -797,7 +803,7 @@ void launch_qk_rope_bwd(const float* dq, const float* dk, const float* dv, const
   const size_t oq = out_pitch ? out_pitch : (size_t)nh * hd, ok = out_pitch ? out_pitch : (size_t)nkv * hd, ov = ok;
   const int common = out_pitch ? 1 : 0;
   if (rope_reg_ok(nh, nkv, hd, rot, neox, &epl, &hpw)) {
-#define RT_ROPE_BWD(E, H) qk_rope_bwd_reg_kernel<E, H><<<M, 256, 0, st>>>(dq, dk, dv, q_raw, k_raw, pq, pk, oq, ok, ov, common, qw, kw, pos, cs, sn, nh, nkv, rot, neox, eps, dq16, dk16, dv16, sq, sk, sv)
+#define RT_ROPE_BWD(E, H) pdl(qk_rope_bwd_reg_kernel<E, H>, M, 256, 0, st)(dq, dk, dv, q_raw, k_raw, pq, pk, oq, ok, ov, common, qw, kw, pos, cs, sn, nh, nkv, rot, neox, eps, dq16, dk16, dv16, sq, sk, sv)
     if (epl == 4) { if (hpw == 4) RT_ROPE_BWD(4, 4); else if (hpw == 6) RT_ROPE_BWD(4, 6); else RT_ROPE_BWD(4, 8); }
     else { if (hpw == 4) RT_ROPE_BWD(2, 4); else if (hpw == 6) RT_ROPE_BWD(2, 6); else RT_ROPE_BWD(2, 8); }
 #undef RT_ROPE_BWD
@@ -818,6 +824,7 @@ __device__ __forceinline__ float sigmoid_f(float x) {
 }
 __global__ void swiglu_fwd_kernel(const __half* __restrict__ g, const __half* __restrict__ u, __half* __restrict__ h,
                                   size_t n) {
+  pdl_entry();
   size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i + 7 < n) {
     const uint4 gv = *(const uint4*)(g + i), uv = *(const uint4*)(u + i);
@@ -838,6 +845,7 @@ __global__ void swiglu_fwd_kernel(const __half* __restrict__ g, const __half* __
 // gate and up as column slices of one [rows x pitch] matrix (ff a multiple of 8)
 __global__ void swiglu_fwd_pitched_kernel(const __half* __restrict__ g, const __half* __restrict__ u, size_t pitch, int ff,
                                           size_t n, __half* __restrict__ h) {
+  pdl_entry();
   const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= n) return;
   const size_t r = i / ff, c = i % ff;
@@ -858,9 +866,9 @@ void launch_swiglu_fwd(const __half* g, const __half* u, size_t in_pitch, int ro
   if (n == 0) return;
   size_t threads = (n + 7) / 8;
   if (in_pitch && in_pitch != (size_t)ff && (ff & 7) == 0)
-    swiglu_fwd_pitched_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(g, u, in_pitch, ff, n, h);
+    pdl(swiglu_fwd_pitched_kernel, (unsigned)((threads + 255) / 256), 256, 0, st)(g, u, in_pitch, ff, n, h);
   else
-    swiglu_fwd_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(g, u, h, n);
+    pdl(swiglu_fwd_kernel, (unsigned)((threads + 255) / 256), 256, 0, st)(g, u, h, n);
   RT_COUNT_LAUNCH(1);
 }
 // dg = dh*u*silu'(g), du = dh*silu(g); both written row-normalised in f16 with per-row scales.
@@ -904,6 +912,7 @@ __global__ void swiglu_bwd_cached_kernel(const DT* __restrict__ dh, const float*
                                          const __half* __restrict__ u, size_t gp, int ff, __half* __restrict__ dg16,
                                          __half* __restrict__ du16, size_t op, int common, float* __restrict__ sg,
                                          float* __restrict__ su) {
+  pdl_entry();
   const size_t r = blockIdx.x;
   float a[NCH][8], b[NCH][8];
   float mg = 0.f, mu = 0.f;
@@ -981,8 +990,8 @@ template <typename DT>
 static void launch_swiglu_bwd_t(const DT* dh, const float* in_scale, const __half* g, const __half* u, size_t gp, int rows,
                                 int ff, __half* dg16, __half* du16, size_t op, int common, float* sg, float* su,
                                 cudaStream_t st) {
-  if ((ff & 7) == 0 && ff <= 2 * 8 * 256) swiglu_bwd_cached_kernel<2, DT><<<rows, 256, 0, st>>>(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
-  else if ((ff & 7) == 0 && ff <= 3 * 8 * 512) swiglu_bwd_cached_kernel<3, DT><<<rows, 512, 0, st>>>(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
+  if ((ff & 7) == 0 && ff <= 2 * 8 * 256) pdl(swiglu_bwd_cached_kernel<2, DT>, rows, 256, 0, st)(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
+  else if ((ff & 7) == 0 && ff <= 3 * 8 * 512) pdl(swiglu_bwd_cached_kernel<3, DT>, rows, 512, 0, st)(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
   else swiglu_bwd_kernel<DT><<<rows, 256, 0, st>>>(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
   RT_COUNT_LAUNCH(1);
 }
@@ -1000,22 +1009,24 @@ void launch_swiglu_bwd(const void* dh, int dh_f16, const float* in_scale, const 
 // ------------------------------------------------------------------ row gather / scatter
 __global__ void gather_f32_rows_kernel(const float* __restrict__ x, const int* __restrict__ idx, int d,
                                        float* __restrict__ out) {
+  pdl_entry();
   const size_t r = blockIdx.x;
   const float* src = x + (size_t)idx[r] * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x) out[r * d + i] = src[i];
 }
 void launch_gather_f32_rows(const float* x, const int* idx, int rows, int d, float* out, cudaStream_t st) {
-  if (rows > 0) { gather_f32_rows_kernel<<<rows, 256, 0, st>>>(x, idx, d, out); RT_COUNT_LAUNCH(1); }
+  if (rows > 0) { pdl(gather_f32_rows_kernel, rows, 256, 0, st)(x, idx, d, out); RT_COUNT_LAUNCH(1); }
 }
 // dx[idx[r], :] += src[r, :]   (atomic: two targets may name the same position)
 __global__ void scatter_add_rows_kernel(const float* __restrict__ src, const int* __restrict__ idx, int d,
                                         float* __restrict__ dx) {
+  pdl_entry();
   const size_t r = blockIdx.x;
   float* dst = dx + (size_t)idx[r] * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(dst + i, src[r * d + i]);
 }
 void launch_scatter_add_rows(const float* src, const int* idx, int rows, int d, float* dx, cudaStream_t st) {
-  if (rows > 0) { scatter_add_rows_kernel<<<rows, 256, 0, st>>>(src, idx, d, dx); RT_COUNT_LAUNCH(1); }
+  if (rows > 0) { pdl(scatter_add_rows_kernel, rows, 256, 0, st)(src, idx, d, dx); RT_COUNT_LAUNCH(1); }
 }
 
 // ------------------------------------------------------------------ cross-entropy over one row of logits
@@ -1045,6 +1056,7 @@ __device__ void ce_row_argmax(const float* __restrict__ row, int v, float m, int
 __global__ void ce_row_kernel(const float* __restrict__ logits, int v, const int* __restrict__ target,
                               const float* __restrict__ weight, float* __restrict__ logp, int* __restrict__ hits,
                               __half* __restrict__ d16, float* __restrict__ scale, int* __restrict__ argmax, int* status) {
+  pdl_entry();
   const size_t r = blockIdx.x;
   const float* row = logits + r * v;
   const int tgt = target[r];
@@ -1082,6 +1094,7 @@ __global__ void __launch_bounds__(1024)
 ce_row_vec_kernel(const float* __restrict__ logits, int v, const int* __restrict__ target,
                   const float* __restrict__ weight, float* __restrict__ logp, int* __restrict__ hits,
                   __half* __restrict__ d16, float* __restrict__ scale, int* __restrict__ argmax, int* status) {
+  pdl_entry();
   const size_t r = blockIdx.x;
   const float4* row4 = (const float4*)(logits + r * v);
   const int n4 = v >> 2;
@@ -1125,9 +1138,9 @@ void launch_ce_rows(const float* logits, int rows, int v, const int* target, con
                     __half* d16, float* scale, int* argmax, int* status, cudaStream_t st) {
   if (rows <= 0) return;
   if ((v & 3) == 0 && ((uintptr_t)logits & 15) == 0 && (d16 == nullptr || ((uintptr_t)d16 & 7) == 0))
-    ce_row_vec_kernel<<<rows, 1024, 0, st>>>(logits, v, target, weight, logp, hits, d16, scale, argmax, status);
+    pdl(ce_row_vec_kernel, rows, 1024, 0, st)(logits, v, target, weight, logp, hits, d16, scale, argmax, status);
   else
-    ce_row_kernel<<<rows, 1024, 0, st>>>(logits, v, target, weight, logp, hits, d16, scale, argmax, status);
+    pdl(ce_row_kernel, rows, 1024, 0, st)(logits, v, target, weight, logp, hits, d16, scale, argmax, status);
   RT_COUNT_LAUNCH(1);
 }
 
@@ -1302,6 +1315,7 @@ void launch_lora_grad(const __half* P, const __half* Q, const float* pscale, con
 // multiplied by scale[m] / max: the token contractions dA, dB need ONE common scale, so the
 // per-row factors move onto the skinny operand and the common factor onto the result.
 __global__ void rowscale_max_kernel(const float* __restrict__ sc, int M, float* __restrict__ out) {
+  pdl_entry();
   float m = 0.f;
   for (int i = threadIdx.x; i < M; i += blockDim.x) m = fmaxf(m, sc[i]);
   m = block_max(m);
@@ -1319,7 +1333,7 @@ __global__ void scale_lowrank_rows_kernel(const __half* __restrict__ in, const f
   *(__half2*)(out + e) = __floats2half2_rn(v.x * f, v.y * f);
 }
 void launch_rowscale_max(const float* sc, int M, float* out, cudaStream_t st) {
-  if (M > 0) { rowscale_max_kernel<<<1, 1024, 0, st>>>(sc, M, out); RT_COUNT_LAUNCH(1); }
+  if (M > 0) { pdl(rowscale_max_kernel, 1, 1024, 0, st)(sc, M, out); RT_COUNT_LAUNCH(1); }
 }
 void launch_scale_lowrank_rows(const __half* in, const float* sc, const float* smax, int M, __half* out, cudaStream_t st) {
   if (M <= 0) return;

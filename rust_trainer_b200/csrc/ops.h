@@ -73,10 +73,14 @@ void launch_global_normalize(const float* x, size_t n, float* amax_dev, __half* 
 int launch_lowrank_tc(rt_ctx* c, const __half* X, const __half* Wt, int M, int K, int r, __half* out64);
 size_t tok_contract_workspace_floats(int M, int C, int r);
 size_t lora_grads_workspace_floats(int M, int N, int K, int r);
-int launch_lora_grads_group(const __half* hs, const __half* dy16, const __half* gs, const __half* x16, const float* dscale,
+// lora_grads_tc.cu: the product kernel on tcgen05 (partial sums per split of lora_grads_tc_tokens_per_split(M) tokens)
+int lora_grads_tc_tokens_per_split(int M);
+int launch_lora_grads_tc(rt_ctx* c, const __half* hs, const __half* dy16, int ld_dy, const __half* gs, const __half* x16,
+                         const float* dscale, int M, int N, int K, int r, float* partB, float* partA);
+int launch_lora_grads_group(rt_ctx* c, const __half* hs, const __half* dy16, const __half* gs, const __half* x16, const float* dscale,
                             int M, int NT, int K, int R, int n, float* const* gb, float* const* ga, const int* row_off,
                             const int* rows, const int* rank_off, const int* rank, float* workspace, cudaStream_t st);
-int launch_lora_grads(const __half* hs, const __half* dy16, int ld_dy, const __half* gs, const __half* x16, const float* dscale,
+int launch_lora_grads(rt_ctx* c, const __half* hs, const __half* dy16, int ld_dy, const __half* gs, const __half* x16, const float* dscale,
                       int M, int N, int K, int r, float* gb, float* ga, float* workspace, cudaStream_t st);
 // pscale (optional): P's rows are multiplied by pscale[m] / alpha_dev[0] on the fly; alpha_dev[0] then scales the result
 int launch_tok_contract(const __half* P, const __half* Q, const float* pscale, int M, int C, int r, size_t so_i, size_t so_j,

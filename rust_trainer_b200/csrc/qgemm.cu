@@ -17,6 +17,7 @@
 //   epilogue : four warps tcgen05.ld the accumulator (double buffered: 2 x 256 TMEM columns),
 //              add bias / per-token factors, stage and TMA-store f32, bf16 or f16
 // The LoRA low-rank term is one more contraction chunk fed through the same accumulator.
+#include "pdl.cuh"
 #include "ptx.cuh"
 #include "qformat.cuh"
 #include "ctx.h"
@@ -298,6 +299,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
   uint64_t* acc_full = raw_empty + NR;     // [2]                                                 (every CTA)
   uint64_t* acc_empty = acc_full + 2;      // [2]                                                 (leader's is used)
   uint32_t* tmem_slot = (uint32_t*)(bars + C::N_BARS);
+  pdl_launch_dependents();
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef RT_B200_QPROF
@@ -382,6 +384,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__
   else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
+  // barriers, TMEM and descriptors are set up; from here on the kernel reads what its predecessor wrote
+  pdl_wait();
   if (threadIdx.x == 0) QG_STAMP(1);
 
   // One [32 tokens x 32 features] block of an accumulator -> staging -> TMA store / reduce-add.
@@ -846,6 +850,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, int splits,
                                      size_t s_tok, size_t s_row, const float* __restrict__ row_scale,
                                      const float* __restrict__ alpha_dev, const float* __restrict__ bias,
                                      int accumulate) {
+  pdl_entry();
   const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t n = (size_t)M * R;
   if (e >= n) return;
@@ -911,9 +916,9 @@ int qgemm_init() {
 
 // 2-D row-major 16-bit matrix [rows x cols]; box = box_cols x box_rows, 128-byte swizzle.
 static int encode_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
-                      uint32_t box_rows, bool is_bf16) {
+                      uint32_t box_rows, bool is_bf16, uint64_t ld = 0) {
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
+  cuuint64_t strides[1] = {(ld ? ld : cols) * 2};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode(m, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
@@ -926,15 +931,16 @@ static int encode_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t 
 std::atomic<unsigned long long> g_launch_count{0};
 
 static int make_map_cached(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
-                           uint32_t box_rows, bool is_bf16) {
-  if (!ctx) return encode_map(m, base, rows, cols, box_cols, box_rows, is_bf16);  // no cache: nothing is allocated
-  auto key = std::make_tuple(base, rows, cols, box_cols, box_rows, is_bf16);
+                           uint32_t box_rows, bool is_bf16, uint64_t ld = 0) {
+  if (ld == cols) ld = 0;
+  if (!ctx) return encode_map(m, base, rows, cols, box_cols, box_rows, is_bf16, ld);  // no cache: nothing is allocated
+  auto key = std::make_tuple(base, rows, cols | (ld << 32), box_cols, box_rows, is_bf16);
   auto it = ctx->tmap_cache.find(key);
   if (it != ctx->tmap_cache.end()) {
     *m = it->second;
     return RT_OK;
   }
-  int rc = encode_map(m, base, rows, cols, box_cols, box_rows, is_bf16);
+  int rc = encode_map(m, base, rows, cols, box_cols, box_rows, is_bf16, ld);
   if (rc) return rc;
   if (ctx->tmap_cache.size() > 8192) ctx->tmap_cache.clear();
   ctx->tmap_cache.emplace(key, *m);
@@ -949,6 +955,15 @@ int tensor_map_f16_2d(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t ro
     if (rc) return rc;
   }
   return make_map_cached(ctx, m, base, rows, cols, box_cols, box_rows, false);
+}
+
+int tensor_map_f16_2d_ld(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                         uint32_t box_cols, uint32_t box_rows) {
+  if (!g_encode) {
+    int rc = qgemm_init();
+    if (rc) return rc;
+  }
+  return make_map_cached(ctx, m, base, rows, cols, box_cols, box_rows, false, ld);
 }
 
 // Output matrix [rows x cols] of f32 / bf16 / f16 with a row pitch of `ld` elements; box = 32 columns x 32 rows
@@ -1176,21 +1191,23 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   }
   if (pair) {
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = 2;
     at[0].val.clusterDim.y = 1;
     at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(QG_THREADS);
     cfg.dynamicSmemBytes = QCfg<true>::SMEM_BYTES;
     cfg.stream = st;
     cfg.attrs = at;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     if (cudaLaunchKernelEx(&cfg, qgemm_kernel<true>, tm_act, tm_w16, tm_lact, tm_lw, tm_out, p) != cudaSuccess)
       return RT_ERR_CUDA;
   } else {
-    qgemm_kernel<false><<<grid, QG_THREADS, QCfg<false>::SMEM_BYTES, st>>>(tm_act, tm_w16, tm_lact, tm_lw, tm_out, p);
+    pdl(qgemm_kernel<false>, grid, QG_THREADS, QCfg<false>::SMEM_BYTES, st)(tm_act, tm_w16, tm_lact, tm_lw, tm_out, p);
   }
   RT_COUNT_LAUNCH(1);
 #ifdef RT_B200_QPROF
@@ -1221,7 +1238,7 @@ int qgemm_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a) {
   if (p.part) {
     const size_t n = (size_t)a.M * out_rows;
     const size_t s_tok = a.tok_mode ? a.out_s_tok : (size_t)p.ld_out, s_row = a.tok_mode ? a.out_s_row : 1;
-    splitk_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.part, p.n_splits, a.M, out_rows, (float*)a.out, s_tok,
+    pdl(splitk_reduce_kernel, (unsigned)((n + 255) / 256), 256, 0, st)(p.part, p.n_splits, a.M, out_rows, (float*)a.out, s_tok,
                                                                     s_row, a.row_scale, a.alpha_dev, p.bias, a.accumulate);
     RT_COUNT_LAUNCH(1);
   }

@@ -17,7 +17,12 @@ struct QWeight;
 
 // Kernels launched by this library in this process (every launcher adds its own).
 extern std::atomic<unsigned long long> g_launch_count;
+#ifdef RT_B200_SITEPROF
+void prof_mark(const char* file, int line);  // site_prof.cu
+#define RT_COUNT_LAUNCH(n) (rt::g_launch_count.fetch_add((n), std::memory_order_relaxed), rt::prof_mark(__FILE__, __LINE__))
+#else
 #define RT_COUNT_LAUNCH(n) (rt::g_launch_count.fetch_add((n), std::memory_order_relaxed))
+#endif
 
 // ---- repack.cu
 void launch_repack(const uint8_t* raw_dev, const QWeight& w, cudaStream_t st);
@@ -70,6 +75,9 @@ int frozen_matmul_launch(rt_ctx* ctx, const QWeight& w, const QGemmArgs& a);
 // 128-byte swizzle (box_cols = 64); cached per ctx by (base, shape, box).
 int tensor_map_f16_2d(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
                       uint32_t box_rows);
+// The same with a row pitch of `ld` elements (a column slice of a wider matrix).
+int tensor_map_f16_2d_ld(rt_ctx* ctx, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                         uint32_t box_cols, uint32_t box_rows);
 size_t qgemm_smem_bytes();
 int qgemm_init();  // resolves the driver entry point for tensor-map encoding; sets smem attributes
 
