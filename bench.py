@@ -612,6 +612,35 @@ def run_microbench(args):
     return 0
 
 
+def run_attention_case(args):
+    """The attention kernels alone on NSEQ sequences of T tokens (the workload's head geometry),
+    through the one-op host entry points: forward, then backward.  For a profiler (the host calls
+    copy their operands, so the wall time printed here is not a kernel time)."""
+    import rust_trainer_b200 as rt
+    from rust_trainer_b200 import ops, synth
+
+    wl = WORKLOADS[args.workload]
+    cfg = synth.preset(wl["preset"], quant=wl["quant"]).config()
+    nseq, T = (int(v) for v in args.attention_case.split("x"))
+    nh, nkv, hd = cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"]
+    M = nseq * T
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((M, nh, hd), dtype=np.float32)
+    k = rng.standard_normal((M, nkv, hd), dtype=np.float32)
+    v = rng.standard_normal((M, nkv, hd), dtype=np.float32)
+    d_o = rng.standard_normal((M, nh, hd), dtype=np.float32)
+    ss = np.repeat(np.arange(nseq, dtype=np.int32) * T, T)
+    ctx = rt.Context(0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        ops.attention(ctx, q, k, v, ss)
+        ops.attention_backward(ctx, q, k, v, d_o, ss)
+    ctx.synchronize()
+    print(json.dumps({"attention_case": args.attention_case, "heads": nh, "kv_heads": nkv, "head_dim": hd, "steps": args.steps,
+                      "host_ms_per_step_with_copies": 1e3 * (time.perf_counter() - t0) / args.steps}), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -630,12 +659,15 @@ def main():
     ap.add_argument("--no-shape-table", dest="shape_table", action="store_false",
                     help="skip the per-shape table of the frozen-matmul kernel (N = 1 only)")
     ap.add_argument("--microbench", action="store_true", help="time the frozen-matmul kernel alone")
+    ap.add_argument("--attention-case", default="", help="NSEQxT: run the attention kernels alone (for a profiler)")
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--quant", default="", help="microbench: weight format instead of the workload's")
     ap.add_argument("--shape", default="", help="microbench: one OUTxIN shape instead of the workload's")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours" and not args.launch_list:
         args.warmup = 3
+    if args.attention_case:
+        return run_attention_case(args)
     if args.microbench:
         return run_microbench(args)
     if args.impl == "reference":

@@ -10,11 +10,16 @@
  * implements the public ggml block formats; the decoders below restate those published
  * formats and are pinned against the independent `gguf` Python package in tests/.
  *
- * Parity status: block decode pinned against gguf-py (bit exact); LR schedule, f16 rounding
- * and the adjoint identity pinned against the reference's own known-answer tests; whole-model
- * numbers are NOT pinned against the reference binary (no Rust toolchain here): "parity
- * unpinned" for those, mode (i) of the survey ("smooth": dequantised f32 weights, f32
- * activations, f16 K/V rounding) is what is restated.
+ * Parity status: PINNED.  Block decode against gguf-py (bit exact); LR schedule, f16 rounding
+ * and the adjoint identity against the reference's own known-answer tests; whole-model loss and
+ * LoRA gradients against the reference's own float64 checker (tools/reference_check.py, run
+ * unmodified on a file in the layout of examples/export_reference.rs that
+ * tests/golden/make_reference_export.py writes from this oracle's numbers; its float64 outputs
+ * are committed as tests/golden/reference_check_float64.npz).  The reference binary itself
+ * cannot run here (no Rust toolchain).  What is restated is the "smooth" mode the reference's
+ * backward and its checker assume (dequantised f32 weights, f32 activations, f16 K/V
+ * rounding); orc_set_act_int8(1) adds the engine's per-block 8-bit rounding of forward
+ * activations (src/rie.rs:77-80) as an informative second mode.
  *
  * Build: gcc -O3 -march=native -fopenmp -shared -fPIC oracle.c -o liboracle.so -lm
  */

@@ -47,7 +47,10 @@ struct QCfg {
   // NR a multiple of UG gives every slot of the brick ring to one group (bulk copies of different
   // slots may land out of order, so a group sharing a slot could otherwise see the landing of an
   // older copy as its own).
-  static constexpr int UG = PAIR ? 4 : 2;                  // a power of two
+#ifndef RT_B200_PAIR_UG
+#define RT_B200_PAIR_UG 4
+#endif
+  static constexpr int UG = PAIR ? RT_B200_PAIR_UG : 2;    // a power of two
   static constexpr int UTG = 256 / UG;                     // threads per group
   static_assert(UG <= NS && NR % UG == 0, "unpack groups would alias barrier phases");
   static constexpr int ACT_STAGE = PAIR ? 16384 : 32768;   // 128 or 256 tokens x 64 x 16-bit
