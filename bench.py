@@ -387,7 +387,8 @@ def run_ours(args):
         rel = float(np.linalg.norm(g_dp.astype(np.float64) - g_one) / np.linalg.norm(g_one.astype(np.float64)))
         t = torch.tensor([rel, abs(float(loss_dp[0]) - loss_one) / abs(loss_one)], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dp_check = {"grad_rel_l2": float(t[0]), "loss_rel": float(t[1]), "global_batch": f"{wl['n_seq']} x {wl['seq_len']}",
+        dp_check = {"grad_rel_l2": float(t[0]), "loss_rel": float(t[1]), "bound": 1e-5, "ok": bool(float(t[0]) <= 1e-5),
+                    "global_batch": f"{wl['n_seq']} x {wl['seq_len']}",
                     "what": "gradient buffer after the NCCL sum of N shards vs the whole batch on one rank, max over ranks"}
         model.zero_grad()
 

@@ -480,7 +480,6 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *(volatile uint32_t*)tmem_slot;
   pdl_wait();
-  const float inv_top = row_scale ? 1.0f / fmaxf(do_scale[0], 1e-38f) : 1.0f;
 
   if (warp == BWD_TMA_WARP) {
     // ------------------------------------------------------------ producer: TMA + the per-query vectors
@@ -512,7 +511,8 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         const bool in = m < M;
         aux[il] = in ? lse[(size_t)h * M + m] * LOG2E : 0.f;
         aux[BQ + il] = in ? delta[(size_t)h * M + m] : 0.f;
-        aux[2 * BQ + il] = in ? (row_scale ? row_scale[m] * inv_top : 1.0f) * P_BOOST : 0.f;
+        // with per-row factors do_scale[m] is the largest factor (a power of two) of m's own sequence
+        aux[2 * BQ + il] = in ? (row_scale ? row_scale[m] / fmaxf(do_scale[m], 1e-38f) : 1.0f) * P_BOOST : 0.f;
         ((int*)aux)[3 * BQ + il] = in ? seq_start[m] : 0x7fffffff;
         const int2 gp = (gap && in) ? gap[m] : make_int2(0, 0);
         ((int*)aux)[4 * BQ + il] = gp.x;
@@ -662,7 +662,9 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     }
     AT_STAMP_K(500);
     // write this key row's gradients (zeros when no query sees these keys)
-    const float sc_v = do_scale[0] * (1.0f / P_BOOST), sc_k = do_scale[0] * (1.0f / DS_BOOST);
+    // a key row only ever meets queries of its own sequence, so its sums are in units of that sequence's largest factor
+    const float top_j = row_scale ? do_scale[j < M ? j : M - 1] : do_scale[0];
+    const float sc_v = top_j * (1.0f / P_BOOST), sc_k = top_j * (1.0f / DS_BOOST);
     if (n_items > 0 && ok) ok = mbar_wait(pd_done, (uint32_t)(n_items - 1) & 1, status, SITE_B_PDDONE);
     if (ok) {
       tc_fence_after();

@@ -1041,7 +1041,7 @@ static bool ensure_tokens(rt_model* m, int M) {
   ok &= m->dx.reserve(T * d * 4) && m->dy16.reserve(T * d * 2) && m->sc_y.reserve(T * 4);
   ok &= m->dhm.reserve(T * ff * 2) && m->dg16.reserve(T * ff * 2 * 2);  // d(gate) | d(up)
   ok &= m->sc_g.reserve(T * 4) && m->sc_u.reserve(T * 4) && m->dn.reserve(T * d * 4);
-  ok &= m->dO16.reserve(T * qd * 2);
+  ok &= m->dO16.reserve(T * qd * 2) && m->amax.reserve(T * 4 + 16);  // amax: per token, its sequence's largest factor
   ok &= m->dq.reserve(T * qd * 4) && m->dk.reserve(T * kvd * 4) && m->dv.reserve(T * kvd * 4);
   ok &= m->dq16.reserve(T * (qd + 2 * kvd) * 2);  // d(q) | d(k) | d(v)
   ok &= m->sc_q.reserve(T * 4) && m->sc_k.reserve(T * 4) && m->sc_v.reserve(T * 4);
@@ -1213,9 +1213,10 @@ static rt_status block_backward(rt_model* m, int li, int M, const float* x_in, c
   launch_rmsnorm_bwd(A.h, b.post_norm, m->dn.as<float>(), dx, M, d, g.rms_eps, dx, dy16, sc_y, st);
   // Attention::backward (src/attention.rs:246-367)
   // d(attention output) leaves the matmul as f16 rows still lacking sc_y; the attention backward
-  // takes the factors per query row (largest one in amax)
+  // takes the factors per query row (in amax, for every token, the largest one of its own sequence:
+  // nothing a sequence's backward sees may depend on its batch mates)
   RT_TRY(linear_backward_dev(b.lin[3], m->lsc, A.o16, dy16, sc_y, M, m->dO16.p, 0, HS(3), true));
-  launch_rowscale_max(sc_y, M, m->amax.as<float>(), st);
+  launch_rowscale_seqmax(sc_y, m->seq_start.as<int>(), M, m->amax.as<float>(), st);
   if (attn_backward(c, A.q16, A.k16, A.v16, A.o16, m->dO16.as<__half>(),
                     m->amax.as<float>(), sc_y, A.lse, m->seq_start.as<int>(), m->staged_gap ? m->gap.as<int>() : nullptr, M,
                     g.n_heads, g.n_kv_heads, g.head_dim,

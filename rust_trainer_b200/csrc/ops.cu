@@ -1332,6 +1332,26 @@ __global__ void scale_lowrank_rows_kernel(const __half* __restrict__ in, const f
   float2 v = __half22float2(*(const __half2*)(in + e));
   *(__half2*)(out + e) = __floats2half2_rn(v.x * f, v.y * f);
 }
+// The same per SEQUENCE: out[m] = largest scale among the tokens of m's sequence (seq_start[m] =
+// first token of it), rounded up to a power of two; 1 where the whole sequence is zero.  A
+// sequence's backward then never sees a number that depends on its batch mates.  One block:
+// the slot of a sequence is out[first token]; converting a slot is idempotent, so a reader may
+// meet it before or after its own token converted it.
+__global__ void rowscale_seqmax_kernel(const float* __restrict__ sc, const int* __restrict__ seq_start, int M,
+                                       float* __restrict__ out) {
+  pdl_entry();
+  for (int i = threadIdx.x; i < M; i += blockDim.x) out[i] = 0.f;
+  __syncthreads();
+  for (int i = threadIdx.x; i < M; i += blockDim.x) atomicMax((int*)out + seq_start[i], __float_as_int(fmaxf(sc[i], 0.f)));
+  __syncthreads();
+  for (int i = threadIdx.x; i < M; i += blockDim.x) {
+    const float m = out[seq_start[i]];
+    out[i] = m > 0.f ? __int_as_float((__float_as_int(m) + 0x007FFFFF) & 0x7F800000) : 1.f;
+  }
+}
+void launch_rowscale_seqmax(const float* sc, const int* seq_start, int M, float* out, cudaStream_t st) {
+  if (M > 0) { pdl(rowscale_seqmax_kernel, 1, 1024, 0, st)(sc, seq_start, M, out); RT_COUNT_LAUNCH(1); }
+}
 void launch_rowscale_max(const float* sc, int M, float* out, cudaStream_t st) {
   if (M > 0) { pdl(rowscale_max_kernel, 1, 1024, 0, st)(sc, M, out); RT_COUNT_LAUNCH(1); }
 }

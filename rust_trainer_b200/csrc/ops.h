@@ -61,6 +61,8 @@ size_t lora_grad_workspace_floats(int M, int C, int r);
 void launch_lora_grad(const __half* P, const __half* Q, const float* pscale, const float* qscale, int M, int C, int r,
                       size_t so_i, size_t so_j, float* out, float* workspace, cudaStream_t st);
 void launch_rowscale_max(const float* sc, int M, float* out, cudaStream_t st);
+// out[m] = largest sc of m's sequence (power of two, 1 for an all-zero sequence)
+void launch_rowscale_seqmax(const float* sc, const int* seq_start, int M, float* out, cudaStream_t st);
 void launch_scale_lowrank_rows(const __half* in, const float* sc, const float* smax, int M, __half* out, cudaStream_t st);
 void launch_sumsq(const float* g, size_t n, double* part, double* out, cudaStream_t st);
 void launch_adamw(float* p, float* g, float* m, float* v, size_t n, const double* sumsq, float max_norm, float lr,
@@ -91,7 +93,8 @@ int launch_tok_contract(const __half* P, const __half* Q, const float* pscale, i
 // q [M x nh x hd], k/v [M x nkv x hd] f16 (q unscaled; the kernels apply 1/sqrt(hd)).
 // seq_start[m] = index of the first token of m's sequence; gap [M x 2] or null; lse is [nh x M].
 // Backward: dO row i stands for do_scale[0] * dO16[i], or, with row_scale, for row_scale[i] *
-// dO16[i] (then do_scale[0] holds a power of two >= the largest row_scale); outputs are true-scale f32.
+// dO16[i] (then do_scale is an array [M]: for each token a power of two >= the largest row_scale of
+// its own sequence, see launch_rowscale_seqmax); outputs are true-scale f32.
 int launch_attn_bwd_tc(rt_ctx* c, const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
                        const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap,
                        int M, int nh, int nkv, int hd, float* delta, float* dq, float* dk, float* dv);

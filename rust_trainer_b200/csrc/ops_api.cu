@@ -217,7 +217,7 @@ rt_status rt_op_attention_backward(rt_ctx* c, const float* q, const float* k, co
   float *qd = t.up(q, nq, c->stream), *kd = t.up(k, nk, c->stream), *vd = t.up(v, nk, c->stream), *dod = t.up(d_o, nq, c->stream);
   int* ss = t.up((const int*)seq_start, M, c->stream);
   __half *q16 = t.get<__half>(nq), *k16 = t.get<__half>(nk), *v16 = t.get<__half>(nk), *o16 = t.get<__half>(nq), *do16 = t.get<__half>(nq);
-  float *lsed = t.get<float>(M * nh), *delta = t.get<float>(M * nh), *sc = t.get<float>(M), *amax = t.get<float>(4);
+  float *lsed = t.get<float>(M * nh), *delta = t.get<float>(M * nh), *sc = t.get<float>(M), *amax = t.get<float>(M + 4);
   float *dqd = t.get<float>(nq), *dkd = t.get<float>(nk), *dvd = t.get<float>(nk);
   if (!qd || !kd || !vd || !dod || !ss || !q16 || !k16 || !v16 || !o16 || !do16 || !lsed || !delta || !sc || !amax || !dqd || !dkd || !dvd)
     return c->fail(RT_ERR_CUDA, "out of device memory");
@@ -228,7 +228,7 @@ rt_status rt_op_attention_backward(rt_ctx* c, const float* q, const float* k, co
     return c->fail(RT_ERR_CUDA, "attention forward launch failed");
   // dO as the model passes it: f16 rows divided by their largest magnitude, factors beside them
   launch_normalize_rows(dod, (int)M, nh * hd, do16, sc, c->stream);
-  launch_rowscale_max(sc, (int)M, amax, c->stream);
+  launch_rowscale_seqmax(sc, ss, (int)M, amax, c->stream);
   if (attn_backward(c, q16, k16, v16, o16, do16, amax, sc, lsed, ss, nullptr, (int)M, nh, nkv, hd, delta, dqd, dkd, dvd))
     return c->fail(RT_ERR_CUDA, "attention backward launch failed");
   RT_CUDA(c, cudaMemcpyAsync(dq, dqd, nq * sizeof(float), cudaMemcpyDeviceToHost, c->stream));

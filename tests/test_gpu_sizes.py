@@ -103,19 +103,23 @@ def test_two_layer_cuts_at_full_width_and_vocabulary(ctx, name, quant, seq, rank
     _compare_step(ctx, spec, rank, 2.0 * rank, [toks[0]], 1, lr=1e-3, wd=0.0, n_targets_cap=96)
 
 
-def test_shards_of_a_batch_sum_to_the_whole_batch(ctx):
+@pytest.mark.parametrize("n_seq,world", [(6, 3), (16, 2)])
+def test_shards_of_a_batch_sum_to_the_whole_batch(ctx, n_seq, world):
     """Data parallelism rests on it: the gradients of a batch's round-robin shards (each with the
     GLOBAL 1/batch_tokens weight) add up to the gradient of the whole batch, to the order of f32
     sums (rel-L2 <= 1e-5), at the full vocabulary, where the head's backward contracts over 151 936
-    elements.  Nothing a row is rounded with may depend on which other rows share its batch."""
+    elements.  Nothing a row is rounded with may depend on which other rows share its batch.
+    (6, 3): shards of two sequences, where a token-dependent split of the matmuls once showed;
+    (16, 2): the benchmark's own check, where the token contractions of dA / dB group the sequences
+    of a shard differently from those of the whole batch."""
     from rust_trainer_b200 import dp
 
     spec = synth.preset("qwen3-0.6b", quant="Q8_0", seed=0, n_layers=2)
     gm = rt.Model(ctx, spec.config(), synth.build_tensors(spec))
     gm.attach_lora(16, 32.0, None, 1234)
     gm.load_adapters(synth.lora_adapters(spec, 16, 32.0, seed=1234))
-    toks = synth.token_batch(spec, 6, 512, 7)
-    examples = [(toks[i], 359) for i in range(6)]
+    toks = synth.token_batch(spec, n_seq, 512, 7)
+    examples = [(toks[i], 359) for i in range(n_seq)]
 
     def grads(rank, world):
         b = dp.local_batch(examples, rank, world)
@@ -124,7 +128,7 @@ def test_shards_of_a_batch_sum_to_the_whole_batch(ctx):
         return _flat([l.lora() for l in gm.lora_linears()], "ga", "gb").astype(np.float64), dp.step_loss(lp, b)
 
     whole, loss = grads(0, 1)
-    parts = [grads(r, 3) for r in range(3)]
+    parts = [grads(r, world) for r in range(world)]
     assert rel_l2(sum(p[0] for p in parts), whole) < 1e-5
     assert abs(sum(p[1] for p in parts) - loss) < 1e-6 * abs(loss)
     gm.close()
