@@ -36,7 +36,8 @@ enum {
   RT_ERR_DEVICE_WAIT_TIMEOUT = 5,
   RT_ERR_BAD_INDEX = 6,
   RT_ERR_BAD_ARG = 7,
-  RT_ERR_TOO_LARGE = 8
+  RT_ERR_TOO_LARGE = 8,
+  RT_ERR_NONFINITE = 9 /* a 16-bit activation overflowed: silu(gate) * up beyond 65504 (the reference holds it in f32) */
 };
 
 /* ggml tensor types accepted for frozen weights (numeric values are GGUF's). */

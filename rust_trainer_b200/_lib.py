@@ -15,7 +15,7 @@ OK = 0
 DT_F32, DT_BF16, DT_F16 = 0, 1, 2
 STATUS_NAMES = {
     0: "RT_OK", 1: "RT_ERR_BAD_SHAPE", 2: "RT_ERR_UNSUPPORTED_TYPE", 3: "RT_ERR_CUDA", 4: "RT_ERR_NCCL",
-    5: "RT_ERR_DEVICE_WAIT_TIMEOUT", 6: "RT_ERR_BAD_INDEX", 7: "RT_ERR_BAD_ARG", 8: "RT_ERR_TOO_LARGE",
+    5: "RT_ERR_DEVICE_WAIT_TIMEOUT", 6: "RT_ERR_BAD_INDEX", 7: "RT_ERR_BAD_ARG", 8: "RT_ERR_TOO_LARGE", 9: "RT_ERR_NONFINITE",
 }
 
 

@@ -34,6 +34,11 @@ rt_status rt_ctx::check_device_status(const char* where) {
     err = buf;
     return RT_ERR_BAD_INDEX;
   }
+  if (s == RT_ERR_NONFINITE) {
+    snprintf(buf, sizeof buf, "%s: silu(gate) * up left the range of f16 (an activation beyond 65504)", where);
+    err = buf;
+    return RT_ERR_NONFINITE;
+  }
   snprintf(buf, sizeof buf, "%s: device wait timed out at site %d", where, s);
   err = buf;
   return RT_ERR_DEVICE_WAIT_TIMEOUT;

@@ -512,7 +512,8 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         aux[il] = in ? lse[(size_t)h * M + m] * LOG2E : 0.f;
         aux[BQ + il] = in ? delta[(size_t)h * M + m] : 0.f;
         // with per-row factors do_scale[m] is the largest factor (a power of two) of m's own sequence
-        aux[2 * BQ + il] = in ? (row_scale ? row_scale[m] / fmaxf(do_scale[m], 1e-38f) : 1.0f) * P_BOOST : 0.f;
+        // and do_scale[M + m] the row's weight against it
+        aux[2 * BQ + il] = in ? (row_scale ? do_scale[M + m] : 1.0f) * P_BOOST : 0.f;
         ((int*)aux)[3 * BQ + il] = in ? seq_start[m] : 0x7fffffff;
         const int2 gp = (gap && in) ? gap[m] : make_int2(0, 0);
         ((int*)aux)[4 * BQ + il] = gp.x;

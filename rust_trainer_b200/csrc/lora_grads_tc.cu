@@ -12,9 +12,8 @@
 //   D[column (lane), i] in 64 TMEM columns.
 // Warps: 0-3 scale the Small tiles and run the epilogue, 4, 6, 7 are TMA producers, 5 issues the MMAs.
 // dY arrives row-normalised with one factor per token.  The factors go onto the Small rows
-// relative to the split's largest factor and boosted to the top of f16's range (both by powers of
-// two, so what a row rounds to does not depend on its split mates), and the inverse multiplies
-// the split's sums.
+// relative to the split's largest factor (rounded up to a power of two, so what a row rounds to
+// does not depend on its split mates), and the largest factor multiplies the split's sums.
 // Partial sums of the splits are added in order by the reduce kernels of lora_kernels.cu:
 // deterministic, no atomics.
 #include "ctx.h"
@@ -38,8 +37,6 @@ constexpr uint32_t LG_TOTAL = LG_OFF_BAR + 256 + 1024;
 enum { SITE_LG_FREE = 495, SITE_LG_FULL, SITE_LG_READY, SITE_LG_DONE };
 
 struct LoraGradTcArgs {
-  const __half* Pb;     // Small operands as plain pointers (the factor pass reads their magnitudes)
-  const __half* Pa;
   const float* pscale;  // [M] or null
   int M, N, K, r, nbB, tps;
   float* partB;  // [splits][r x N]
@@ -60,7 +57,7 @@ lora_grads_tc_kernel(const __grid_constant__ CUtensorMap tm_pb, const __grid_con
   uint64_t* empty = bars + 2 * LG_NS;  // [NS] MMAs retired
   uint64_t* done = bars + 3 * LG_NS;
   uint32_t* tmem_slot = (uint32_t*)(bars + 3 * LG_NS + 2);
-  __shared__ float s_red[8];
+  __shared__ float s_red[4];
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool isB = (int)blockIdx.x < g.nbB;
@@ -127,42 +124,24 @@ lora_grads_tc_kernel(const __grid_constant__ CUtensorMap tm_pb, const __grid_con
   } else {
     // ---- 128 threads: factors of the split, Small tiles scaled in place, then the epilogue
     const int tid = threadIdx.x;
-    // out_mul: what the split's sums are multiplied by at the end (largest factor / boost)
+    // out_mul: what the split's sums are multiplied by at the end (the split's largest factor)
     float out_mul = 1.0f;
     if (g.pscale) {
-      // Largest factor of the split (factors are >= 0) and largest magnitude of its Small rows, both
-      // rounded up to powers of two: rows are stored as  small * factor / largest factor * boost  with
-      // boost = 2^14 / largest magnitude, so the largest stored value is 2^14 and a row that weighs
-      // 2^-20 of the heaviest one still lands in f16's normal range.  (Without the boost lightly
-      // weighted rows went subnormal, and which rows those were depended on the split's other rows:
-      // shards of a batch summed to the whole batch only to 3e-4.)  Powers of two change no mantissa.
+      // Largest factor of the split (factors are >= 0), rounded up to a power of two so that
+      // dividing by it changes no mantissa.  (Lifting the rows further, to the top of f16's range by
+      // the largest magnitude of the split's Small rows, was tried: it needs a pass over those
+      // rows before the first tile can be scaled, 6 us of a 22 us launch, and changed no digit of
+      // the shards-against-whole-batch check once the attention backward weighed rows per sequence.)
       float v = 0.f;
       for (int m = m_begin + tid; m < m_end; m += 128) v = fmaxf(v, g.pscale[m]);
-      __half2 hm2 = __float2half2_rn(0.f);
-      {
-        const uint4* P = (const uint4*)((isB ? g.Pb : g.Pa) + (size_t)m_begin * 64);
-        const int n16 = (m_end - m_begin) * 8;
-        for (int e = tid; e < n16; e += 128) {
-          const uint4 w = P[e];
-          const __half2* h2 = (const __half2*)&w;
-          hm2 = __hmax2(hm2, __hmax2(__hmax2(__habs2(h2[0]), __habs2(h2[1])), __hmax2(__habs2(h2[2]), __habs2(h2[3]))));
-        }
-      }
-      float hm = fmaxf(__low2float(hm2), __high2float(hm2));
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-        hm = fmaxf(hm, __shfl_xor_sync(0xffffffffu, hm, o));
-      }
-      if (lane == 0) { s_red[warp] = v; s_red[4 + warp] = hm; }
+      for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+      if (lane == 0) s_red[warp] = v;
       named_barrier_sync(1, 128);
       float lmax = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
-      hm = fmaxf(fmaxf(s_red[4], s_red[5]), fmaxf(s_red[6], s_red[7]));
       lmax = __int_as_float((__float_as_int(lmax) + 0x007FFFFF) & 0x7F800000);
-      hm = __int_as_float((__float_as_int(hm) + 0x007FFFFF) & 0x7F800000);
-      const float boost = (hm > 0.f && hm < 3.0e38f) ? 16384.0f / hm : 1.0f;
-      const float inv = lmax > 0.f ? boost / lmax : 0.f;
-      out_mul = lmax / boost;
+      const float inv = lmax > 0.f ? 1.0f / lmax : 0.f;
+      out_mul = lmax;
       for (int m = tid; m < nchunks * 64; m += 128) s_scale[m] = (m_begin + m < m_end) ? g.pscale[m_begin + m] * inv : 0.f;
       named_barrier_sync(1, 128);
     }
@@ -240,8 +219,6 @@ int launch_lora_grads_tc(rt_ctx* c, const __half* hs, const __half* dy16, int ld
   if (tensor_map_f16_2d_ld(c, &tpa, gs, (uint64_t)M, 64, 64, 64, 64)) return 3;
   if (tensor_map_f16_2d_ld(c, &tqa, x16, (uint64_t)M, (uint64_t)K, (uint64_t)K, 64, 64)) return 3;
   LoraGradTcArgs g;
-  g.Pb = hs;
-  g.Pa = gs;
   g.pscale = dscale;
   g.M = M; g.N = N; g.K = K; g.r = r;
   g.nbB = (N + 127) / 128;

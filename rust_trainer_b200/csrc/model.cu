@@ -1041,7 +1041,7 @@ static bool ensure_tokens(rt_model* m, int M) {
   ok &= m->dx.reserve(T * d * 4) && m->dy16.reserve(T * d * 2) && m->sc_y.reserve(T * 4);
   ok &= m->dhm.reserve(T * ff * 2) && m->dg16.reserve(T * ff * 2 * 2);  // d(gate) | d(up)
   ok &= m->sc_g.reserve(T * 4) && m->sc_u.reserve(T * 4) && m->dn.reserve(T * d * 4);
-  ok &= m->dO16.reserve(T * qd * 2) && m->amax.reserve(T * 4 + 16);  // amax: per token, its sequence's largest factor
+  ok &= m->dO16.reserve(T * qd * 2) && m->amax.reserve(2 * T * 4 + 16);  // amax: per token, its sequence's largest factor, then its weight against it
   ok &= m->dq.reserve(T * qd * 4) && m->dk.reserve(T * kvd * 4) && m->dv.reserve(T * kvd * 4);
   ok &= m->dq16.reserve(T * (qd + 2 * kvd) * 2);  // d(q) | d(k) | d(v)
   ok &= m->sc_q.reserve(T * 4) && m->sc_k.reserve(T * 4) && m->sc_v.reserve(T * 4);
@@ -1173,7 +1173,7 @@ static rt_status block_forward(rt_model* m, int li, int M, const float* x_in, fl
     RT_TRY(linear_forward_dev(b.lin[4], m->lsc, A.n2, M, A.g16, RT_DT_F16, 0, keep ? A.hs[4] : nullptr, hs_ready));
     RT_TRY(linear_forward_dev(b.lin[5], m->lsc, A.n2, M, A.u16, RT_DT_F16, 0, keep ? A.hs[5] : nullptr, hs_ready));
   }
-  launch_swiglu_fwd(A.g16, A.u16, A.gu_pitch, M, g.ff, A.hm16, st);
+  launch_swiglu_fwd(A.g16, A.u16, A.gu_pitch, M, g.ff, A.hm16, c->status_dev, st);
   if (x_out) {
     if (x_out != h) RT_CUDA(c, cudaMemcpyAsync(x_out, h, (size_t)M * d * 4, cudaMemcpyDeviceToDevice, st));
     RT_TRY(linear_forward_dev(b.lin[6], m->lsc, A.hm16, M, x_out, RT_DT_F32, 1, keep ? A.hs[6] : nullptr, hs_ready));

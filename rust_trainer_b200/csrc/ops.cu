@@ -206,13 +206,19 @@ rmsnorm_bwd_warp_kernel(const float* __restrict__ x, const float* __restrict__ w
   const size_t r = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (r >= (size_t)rows) return;
   const float4 *x4 = (const float4*)(x + r * D), *d4 = (const float4*)(dn + r * D), *w4 = (const float4*)w;
-  float4 xv[NV], gv[NV];
+  float4 xv[NV], gv[NV], rv[NV];
   float ss = 0.f, gx = 0.f;
+  // every load of the row is issued before the first reduction: one round of memory latency, not two
 #pragma unroll
   for (int k = 0; k < NV; ++k) {
     xv[k] = x4[lane + 32 * k];
-    const float4 dv = d4[lane + 32 * k], wv = w4[lane + 32 * k];
-    gv[k] = make_float4(dv.x * wv.x, dv.y * wv.y, dv.z * wv.z, dv.w * wv.w);
+    gv[k] = d4[lane + 32 * k];
+    rv[k] = dres ? ((const float4*)(dres + r * D))[lane + 32 * k] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const float4 wv = w4[lane + 32 * k];
+    gv[k] = make_float4(gv[k].x * wv.x, gv[k].y * wv.y, gv[k].z * wv.z, gv[k].w * wv.w);
     ss += xv[k].x * xv[k].x + xv[k].y * xv[k].y + xv[k].z * xv[k].z + xv[k].w * xv[k].w;
     gx += gv[k].x * xv[k].x + gv[k].y * xv[k].y + gv[k].z * xv[k].z + gv[k].w * xv[k].w;
   }
@@ -226,10 +232,7 @@ rmsnorm_bwd_warp_kernel(const float* __restrict__ x, const float* __restrict__ w
   for (int k = 0; k < NV; ++k) {
     float4 v = make_float4(gv[k].x * ir - xv[k].x * c, gv[k].y * ir - xv[k].y * c, gv[k].z * ir - xv[k].z * c,
                            gv[k].w * ir - xv[k].w * c);
-    if (dres) {
-      const float4 q = ((const float4*)(dres + r * D))[lane + 32 * k];
-      v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
-    }
+    v.x += rv[k].x; v.y += rv[k].y; v.z += rv[k].z; v.w += rv[k].w;
     o4[lane + 32 * k] = v;
     gv[k] = v;
     m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
@@ -521,8 +524,7 @@ qk_rope_fwd_reg_kernel(const float* __restrict__ q_raw, const float* __restrict_
   const size_t m = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = rot / 2, nheads = nh + 2 * nkv;
-  const int p = pos[m];
-  const RopeLane<EPL> rl = rope_lane<EPL>(lane, cs + (size_t)p * half, sn + (size_t)p * half, half, rot, neox);
+  // the rows first: the position -> cos/sin table chain is two dependent loads, which then run under them
   float x[HPW][EPL];
 #pragma unroll
   for (int t = 0; t < HPW; ++t) {
@@ -533,6 +535,8 @@ qk_rope_fwd_reg_kernel(const float* __restrict__ q_raw, const float* __restrict_
       load_epl<EPL>(src + lane * EPL, x[t]);
     }
   }
+  const int p = pos[m];
+  const RopeLane<EPL> rl = rope_lane<EPL>(lane, cs + (size_t)p * half, sn + (size_t)p * half, half, rot, neox);
 #pragma unroll
   for (int t = 0; t < HPW; ++t) {
     const int h = warp + t * 8;
@@ -562,7 +566,7 @@ qk_rope_fwd_reg_kernel(const float* __restrict__ q_raw, const float* __restrict_
 }
 
 template <int EPL, int HPW>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 qk_rope_bwd_reg_kernel(const float* __restrict__ dq, const float* __restrict__ dk, const float* __restrict__ dv,
                        const float* __restrict__ q_raw, const float* __restrict__ k_raw, size_t pq, size_t pk,
                        size_t oq, size_t ok, size_t ov, int common,  // output row pitches; one scale for all three
@@ -577,8 +581,6 @@ qk_rope_bwd_reg_kernel(const float* __restrict__ dq, const float* __restrict__ d
   const size_t m = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = rot / 2, nheads = nh + 2 * nkv;
-  const int p = pos[m];
-  const RopeLane<EPL> rl = rope_lane<EPL>(lane, cs + (size_t)p * half, sn + (size_t)p * half, half, rot, neox);
   float g[HPW][EPL], xr[HPW][EPL];
 #pragma unroll
   for (int t = 0; t < HPW; ++t) {
@@ -591,6 +593,9 @@ qk_rope_bwd_reg_kernel(const float* __restrict__ dq, const float* __restrict__ d
       if (nw) load_epl<EPL>((h < nh ? q_raw + m * pq + h * HD : k_raw + m * pk + (h - nh) * HD) + lane * EPL, xr[t]);
     }
   }
+  // after the rows: the position -> cos/sin table chain (two dependent loads) runs under them
+  const int p = pos[m];
+  const RopeLane<EPL> rl = rope_lane<EPL>(lane, cs + (size_t)p * half, sn + (size_t)p * half, half, rot, neox);
   float mx[3] = {0.f, 0.f, 0.f};
 #pragma unroll
   for (int t = 0; t < HPW; ++t) {
@@ -822,8 +827,17 @@ __device__ __forceinline__ float sigmoid_f(float x) {
   float e = expf(x);
   return e / (1.0f + e);
 }
+// true when one of the eight f16 values is inf or NaN: the product left f16's range (the reference
+// computes it in f32); the host gets RT_ERR_NONFINITE instead of a NaN loss
+__device__ __forceinline__ bool any_nonfinite_f16x8(const uint4& o) {
+  const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+  bool bad = false;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) bad |= ((w[k] & 0x7C00u) == 0x7C00u) | ((w[k] & 0x7C000000u) == 0x7C000000u);
+  return bad;
+}
 __global__ void swiglu_fwd_kernel(const __half* __restrict__ g, const __half* __restrict__ u, __half* __restrict__ h,
-                                  size_t n) {
+                                  size_t n, int* status) {
   pdl_entry();
   size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i + 7 < n) {
@@ -838,13 +852,18 @@ __global__ void swiglu_fwd_kernel(const __half* __restrict__ g, const __half* __
       o2[k] = __floats2half2_rn(__fdividef(a.x, 1.0f + __expf(-a.x)) * b.x, __fdividef(a.y, 1.0f + __expf(-a.y)) * b.y);
     }
     *(uint4*)(h + i) = o;
+    if (status && any_nonfinite_f16x8(o)) atomicCAS(status, 0, RT_ERR_NONFINITE);
   } else {
-    for (; i < n; ++i) h[i] = __float2half_rn(silu_f(__half2float(g[i])) * __half2float(u[i]));
+    for (; i < n; ++i) {
+      const __half v = __float2half_rn(silu_f(__half2float(g[i])) * __half2float(u[i]));
+      h[i] = v;
+      if (status && (__hisinf(v) || __hisnan(v))) atomicCAS(status, 0, RT_ERR_NONFINITE);
+    }
   }
 }
 // gate and up as column slices of one [rows x pitch] matrix (ff a multiple of 8)
 __global__ void swiglu_fwd_pitched_kernel(const __half* __restrict__ g, const __half* __restrict__ u, size_t pitch, int ff,
-                                          size_t n, __half* __restrict__ h) {
+                                          size_t n, __half* __restrict__ h, int* status) {
   pdl_entry();
   const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= n) return;
@@ -860,15 +879,17 @@ __global__ void swiglu_fwd_pitched_kernel(const __half* __restrict__ g, const __
     o2[k] = __floats2half2_rn(__fdividef(a.x, 1.0f + __expf(-a.x)) * b.x, __fdividef(a.y, 1.0f + __expf(-a.y)) * b.y);
   }
   *(uint4*)(h + i) = o;
+  if (status && any_nonfinite_f16x8(o)) atomicCAS(status, 0, RT_ERR_NONFINITE);
 }
-void launch_swiglu_fwd(const __half* g, const __half* u, size_t in_pitch, int rows, int ff, __half* h, cudaStream_t st) {
+void launch_swiglu_fwd(const __half* g, const __half* u, size_t in_pitch, int rows, int ff, __half* h, int* status,
+                       cudaStream_t st) {
   const size_t n = (size_t)rows * ff;
   if (n == 0) return;
   size_t threads = (n + 7) / 8;
   if (in_pitch && in_pitch != (size_t)ff && (ff & 7) == 0)
-    pdl(swiglu_fwd_pitched_kernel, (unsigned)((threads + 255) / 256), 256, 0, st)(g, u, in_pitch, ff, n, h);
+    pdl(swiglu_fwd_pitched_kernel, (unsigned)((threads + 255) / 256), 256, 0, st)(g, u, in_pitch, ff, n, h, status);
   else
-    pdl(swiglu_fwd_kernel, (unsigned)((threads + 255) / 256), 256, 0, st)(g, u, h, n);
+    pdl(swiglu_fwd_kernel, (unsigned)((threads + 255) / 256), 256, 0, st)(g, u, h, n, status);
   RT_COUNT_LAUNCH(1);
 }
 // dg = dh*u*silu'(g), du = dh*silu(g); both written row-normalised in f16 with per-row scales.
@@ -1333,8 +1354,9 @@ __global__ void scale_lowrank_rows_kernel(const __half* __restrict__ in, const f
   *(__half2*)(out + e) = __floats2half2_rn(v.x * f, v.y * f);
 }
 // The same per SEQUENCE: out[m] = largest scale among the tokens of m's sequence (seq_start[m] =
-// first token of it), rounded up to a power of two; 1 where the whole sequence is zero.  A
-// sequence's backward then never sees a number that depends on its batch mates.  One block:
+// first token of it), rounded up to a power of two; 1 where the whole sequence is zero; and
+// out[M + m] = sc[m] / out[m], the weight of row m among its sequence's rows.  A sequence's
+// backward then never sees a number that depends on its batch mates.  One block:
 // the slot of a sequence is out[first token]; converting a slot is idempotent, so a reader may
 // meet it before or after its own token converted it.
 __global__ void rowscale_seqmax_kernel(const float* __restrict__ sc, const int* __restrict__ seq_start, int M,
@@ -1346,7 +1368,9 @@ __global__ void rowscale_seqmax_kernel(const float* __restrict__ sc, const int* 
   __syncthreads();
   for (int i = threadIdx.x; i < M; i += blockDim.x) {
     const float m = out[seq_start[i]];
-    out[i] = m > 0.f ? __int_as_float((__float_as_int(m) + 0x007FFFFF) & 0x7F800000) : 1.f;
+    const float top = m > 0.f ? __int_as_float((__float_as_int(m) + 0x007FFFFF) & 0x7F800000) : 1.f;
+    out[i] = top;
+    out[M + i] = fmaxf(sc[i], 0.f) / top;
   }
 }
 void launch_rowscale_seqmax(const float* sc, const int* seq_start, int M, float* out, cudaStream_t st) {

@@ -27,7 +27,9 @@ void launch_qk_rope_bwd(const float* dq, const float* dk, const float* dv, const
                         size_t raw_pitch, const float* qw, const float* kw, const int* pos, const float* cs, const float* sn,
                         int M, int nh, int nkv, int hd, int rot, int neox, float eps, __half* dq16, __half* dk16,
                         __half* dv16, size_t out_pitch, float* sq, float* sk, float* sv, cudaStream_t st);
-void launch_swiglu_fwd(const __half* g, const __half* u, size_t in_pitch, int rows, int ff, __half* h, cudaStream_t st);
+// status (optional): set to RT_ERR_NONFINITE when a product leaves f16's range
+void launch_swiglu_fwd(const __half* g, const __half* u, size_t in_pitch, int rows, int ff, __half* h, int* status,
+                       cudaStream_t st);
 // dh: f32 rows, or (dh_f16) f16 rows whose per-row factor in_scale[r] has not been applied yet
 void launch_swiglu_bwd(const void* dh, int dh_f16, const float* in_scale, const __half* g, const __half* u, size_t in_pitch,
                        int rows, int ff, __half* dg16, __half* du16, size_t out_pitch, float* sg, float* su, cudaStream_t st);
@@ -61,7 +63,7 @@ size_t lora_grad_workspace_floats(int M, int C, int r);
 void launch_lora_grad(const __half* P, const __half* Q, const float* pscale, const float* qscale, int M, int C, int r,
                       size_t so_i, size_t so_j, float* out, float* workspace, cudaStream_t st);
 void launch_rowscale_max(const float* sc, int M, float* out, cudaStream_t st);
-// out[m] = largest sc of m's sequence (power of two, 1 for an all-zero sequence)
+// out[m] = largest sc of m's sequence (power of two, 1 for an all-zero sequence), out[M + m] = sc[m] / out[m]
 void launch_rowscale_seqmax(const float* sc, const int* seq_start, int M, float* out, cudaStream_t st);
 void launch_scale_lowrank_rows(const __half* in, const float* sc, const float* smax, int M, __half* out, cudaStream_t st);
 void launch_sumsq(const float* g, size_t n, double* part, double* out, cudaStream_t st);
@@ -93,8 +95,8 @@ int launch_tok_contract(const __half* P, const __half* Q, const float* pscale, i
 // q [M x nh x hd], k/v [M x nkv x hd] f16 (q unscaled; the kernels apply 1/sqrt(hd)).
 // seq_start[m] = index of the first token of m's sequence; gap [M x 2] or null; lse is [nh x M].
 // Backward: dO row i stands for do_scale[0] * dO16[i], or, with row_scale, for row_scale[i] *
-// dO16[i] (then do_scale is an array [M]: for each token a power of two >= the largest row_scale of
-// its own sequence, see launch_rowscale_seqmax); outputs are true-scale f32.
+// dO16[i] (then do_scale is the array [2 M] of launch_rowscale_seqmax: for each token a power of two >=
+// the largest row_scale of its own sequence, then each row's weight against it); outputs are true-scale f32.
 int launch_attn_bwd_tc(rt_ctx* c, const __half* q, const __half* k, const __half* v, const __half* o, const __half* dO16,
                        const float* do_scale, const float* row_scale, const float* lse, const int* seq_start, const int* gap,
                        int M, int nh, int nkv, int hd, float* delta, float* dq, float* dk, float* dv);

@@ -217,7 +217,7 @@ rt_status rt_op_attention_backward(rt_ctx* c, const float* q, const float* k, co
   float *qd = t.up(q, nq, c->stream), *kd = t.up(k, nk, c->stream), *vd = t.up(v, nk, c->stream), *dod = t.up(d_o, nq, c->stream);
   int* ss = t.up((const int*)seq_start, M, c->stream);
   __half *q16 = t.get<__half>(nq), *k16 = t.get<__half>(nk), *v16 = t.get<__half>(nk), *o16 = t.get<__half>(nq), *do16 = t.get<__half>(nq);
-  float *lsed = t.get<float>(M * nh), *delta = t.get<float>(M * nh), *sc = t.get<float>(M), *amax = t.get<float>(M + 4);
+  float *lsed = t.get<float>(M * nh), *delta = t.get<float>(M * nh), *sc = t.get<float>(M), *amax = t.get<float>(2 * M + 4);
   float *dqd = t.get<float>(nq), *dkd = t.get<float>(nk), *dvd = t.get<float>(nk);
   if (!qd || !kd || !vd || !dod || !ss || !q16 || !k16 || !v16 || !o16 || !do16 || !lsed || !delta || !sc || !amax || !dqd || !dkd || !dvd)
     return c->fail(RT_ERR_CUDA, "out of device memory");
@@ -249,7 +249,7 @@ rt_status rt_op_swiglu(rt_ctx* c, const float* gate, const float* up, size_t row
   if (!gd || !ud || !g16 || !u16 || !h16) return c->fail(RT_ERR_CUDA, "out of device memory");
   launch_f32_to_16(gd, g16, n, true, c->stream);
   launch_f32_to_16(ud, u16, n, true, c->stream);
-  launch_swiglu_fwd(g16, u16, 0, (int)rows, (int)ff, h16, c->stream);
+  launch_swiglu_fwd(g16, u16, 0, (int)rows, (int)ff, h16, c->status_dev, c->stream);
   rt_status s = down_f16(c, h16, nullptr, 1, n, h, t);
   if (s) return s;
   return c->check_device_status("rt_op_swiglu");

@@ -167,3 +167,20 @@ def test_cross_entropy_rows_at_full_vocabulary(ctx, vocab):
         _close16(res["dlogits"][r], d, floor=6e-8 * float(weight[r]))
         assert res["argmax"][r] == vocab - 1 - int(np.argmax(logits[r][::-1]))
     assert res["hits"] == hits
+
+
+@pytest.mark.parametrize("ff", [3072, 100])
+def test_swiglu_product_beyond_f16_is_an_error_not_a_nan(ctx, ff):
+    """silu(gate) * up is stored in 16 bits as the input of down_proj (the reference keeps f32,
+    src/model.rs Mlp::forward); a product beyond 65504 must come back as a status the host can act
+    on, and the context must keep working afterwards."""
+    from rust_trainer_b200._lib import RtError
+
+    g = np.full((4, ff), 1.0, np.float32)
+    u = np.full((4, ff), 2.0, np.float32)
+    g[2, ff // 2], u[2, ff // 2] = 300.0, 300.0  # silu(300) * 300 = 90 000
+    with pytest.raises(RtError) as e:
+        ops.swiglu(ctx, g, u)
+    assert e.value.status == 9
+    g[2, ff // 2] = 1.0
+    _close16(ops.swiglu(ctx, g, u), O.swiglu(g, u))
