@@ -184,3 +184,32 @@ def test_swiglu_product_beyond_f16_is_an_error_not_a_nan(ctx, ff):
     assert e.value.status == 9
     g[2, ff // 2] = 1.0
     _close16(ops.swiglu(ctx, g, u), O.swiglu(g, u))
+
+
+@pytest.mark.parametrize("lens,nh,nkv,hd,exact", [([256, 384], 4, 2, 128, True), ([128, 512, 128], 4, 4, 64, True),
+                                                   ([200, 330], 4, 2, 128, False), ([64, 1, 447], 4, 4, 64, False)])
+def test_attention_backward_of_a_sequence_ignores_its_batch_mates(ctx, lens, nh, nkv, hd, exact):
+    """What a sequence's backward computes may not depend on the other sequences of the batch: rows
+    are weighed against the largest gradient factor of their OWN sequence.  The sequences differ in
+    gradient magnitude by decades.  To the last bit when every sequence starts on a tile boundary
+    (128 tokens: the kernels tile the batch, not the sequence); otherwise a sequence's tiles fall
+    differently and the f32 sums differ in their last digits."""
+    rng = np.random.default_rng(sum(lens))
+    M = sum(lens)
+    ss = _seq_start(lens)
+    q = rng.standard_normal((M, nh, hd)).astype(np.float32)
+    k = rng.standard_normal((M, nkv, hd)).astype(np.float32)
+    v = rng.standard_normal((M, nkv, hd)).astype(np.float32)
+    d_o = rng.standard_normal((M, nh, hd)).astype(np.float32) * rng.uniform(0.1, 1.0, (M, 1, 1)).astype(np.float32)
+    starts = np.cumsum([0] + lens)
+    for i in range(len(lens)):
+        d_o[starts[i]:starts[i + 1]] *= np.float32(10.0 ** (-1.5 * i))
+    whole = ops.attention_backward(ctx, q, k, v, d_o, ss)
+    for i, n in enumerate(lens):
+        a, b = starts[i], starts[i + 1]
+        alone = ops.attention_backward(ctx, q[a:b], k[a:b], v[a:b], d_o[a:b], np.zeros(n, np.int32))
+        for w, s in zip(whole, alone):
+            if exact:
+                assert np.array_equal(w[a:b], s), (i, float(np.abs(w[a:b] - s).max()))
+            else:
+                assert rel_l2(w[a:b], s) < 1e-5, (i, rel_l2(w[a:b], s))
