@@ -565,6 +565,83 @@ qk_rope_fwd_reg_kernel(const float* __restrict__ q_raw, const float* __restrict_
   }
 }
 
+// The same for the common geometry with nothing left to decide per head: full rotation
+// (rot == head_dim), query and KV head counts that are multiples of the CTA's eight warps (warp w
+// owns query heads w, w + 8, .. and KV heads w, w + 8, ..), both norms present or both absent.  The
+// general kernel above spends more issue slots on choosing pointers and on uniform branches than on
+// arithmetic; it is bound by instruction issue, not by bytes.
+template <int EPL, int QPW, int KPW, bool NEOX, bool NORM>
+__global__ void __launch_bounds__(256)
+qk_rope_fwd_fast_kernel(const float* __restrict__ q_raw, const float* __restrict__ k_raw, const float* __restrict__ v_raw,
+                        size_t pq, size_t pk, size_t pv, const float* __restrict__ qw, const float* __restrict__ kw,
+                        const int* __restrict__ pos, const float* __restrict__ cs, const float* __restrict__ sn, float eps,
+                        __half* __restrict__ q16, __half* __restrict__ k16, __half* __restrict__ v16) {
+  pdl_entry();
+  constexpr int HD = 32 * EPL, HALF = HD / 2, NH = 8 * QPW, NKV = 8 * KPW;
+  const size_t m = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e0 = lane * EPL;
+  const float* qs = q_raw + m * pq + warp * HD + e0;
+  const float* ks = k_raw + m * pk + warp * HD + e0;
+  const float* vs = v_raw + m * pv + warp * HD + e0;
+  float xq[QPW][EPL], xk[KPW][EPL], xv[KPW][EPL];
+#pragma unroll
+  for (int t = 0; t < QPW; ++t) load_epl<EPL>(qs + t * 8 * HD, xq[t]);
+#pragma unroll
+  for (int t = 0; t < KPW; ++t) load_epl<EPL>(ks + t * 8 * HD, xk[t]);
+#pragma unroll
+  for (int t = 0; t < KPW; ++t) load_epl<EPL>(vs + t * 8 * HD, xv[t]);
+  float wq[EPL], wk[EPL];
+  if (NORM) {
+    load_epl<EPL>(qw + e0, wq);
+    load_epl<EPL>(kw + e0, wk);
+  }
+  // the position -> cos/sin chain (two dependent loads) runs under the row loads
+  const int p = pos[m];
+  const float* csr = cs + (size_t)p * HALF;
+  const float* snr = sn + (size_t)p * HALF;
+  float c[EPL], sg[EPL];
+  if (NEOX) {
+    const bool first = e0 < HALF;
+    float sv_[EPL];
+    load_epl<EPL>(csr + (first ? e0 : e0 - HALF), c);
+    load_epl<EPL>(snr + (first ? e0 : e0 - HALF), sv_);
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) sg[k] = first ? -sv_[k] : sv_[k];
+  } else {
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) {
+      c[k] = csr[(e0 + k) >> 1];
+      const float t = snr[(e0 + k) >> 1];
+      sg[k] = (k & 1) ? t : -t;
+    }
+  }
+  auto finish = [&](float* x, const float* w, __half* dst) {
+    if (NORM) {
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) ss += x[k] * x[k];
+      ss = warp_sum(ss);
+      const float ir = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) x[k] *= ir * w[k];
+    }
+    float o[EPL];
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) {
+      const float partner = NEOX ? __shfl_xor_sync(0xffffffffu, x[k], 16) : x[k ^ 1];
+      o[k] = x[k] * c[k] + partner * sg[k];
+    }
+    store_epl_h<EPL>(dst, o);
+  };
+#pragma unroll
+  for (int t = 0; t < QPW; ++t) finish(xq[t], wq, q16 + (m * NH + warp + 8 * t) * HD + e0);
+#pragma unroll
+  for (int t = 0; t < KPW; ++t) finish(xk[t], wk, k16 + (m * NKV + warp + 8 * t) * HD + e0);
+#pragma unroll
+  for (int t = 0; t < KPW; ++t) store_epl_h<EPL>(v16 + (m * NKV + warp + 8 * t) * HD + e0, xv[t]);
+}
+
 template <int EPL, int HPW>
 __global__ void __launch_bounds__(256, 4)
 qk_rope_bwd_reg_kernel(const float* __restrict__ dq, const float* __restrict__ dk, const float* __restrict__ dv,
@@ -661,6 +738,129 @@ qk_rope_bwd_reg_kernel(const float* __restrict__ dq, const float* __restrict__ d
   }
 }
 
+// Backward for the same common geometry as qk_rope_fwd_fast_kernel (full rotation, head counts
+// that are multiples of eight, both norms or none): no per-head decisions left.
+template <int EPL, int QPW, int KPW, bool NEOX, bool NORM>
+__global__ void __launch_bounds__(256, (QPW + 2 * KPW <= 4) ? 4 : ((QPW + 2 * KPW <= 6) ? 3 : 2))
+qk_rope_bwd_fast_kernel(const float* __restrict__ dq, const float* __restrict__ dk, const float* __restrict__ dv,
+                        const float* __restrict__ q_raw, const float* __restrict__ k_raw, size_t pq, size_t pk, size_t oq,
+                        size_t ok, size_t ov, int common, const float* __restrict__ qw, const float* __restrict__ kw,
+                        const int* __restrict__ pos, const float* __restrict__ cs, const float* __restrict__ sn, float eps,
+                        __half* __restrict__ dq16, __half* __restrict__ dk16, __half* __restrict__ dv16,
+                        float* __restrict__ sq, float* __restrict__ sk, float* __restrict__ sv) {
+  pdl_entry();
+  constexpr int HD = 32 * EPL, HALF = HD / 2, NH = 8 * QPW, NKV = 8 * KPW;
+  __shared__ float wmax[3][8];
+  const size_t m = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e0 = lane * EPL;
+  float gq[QPW][EPL], gk[KPW][EPL], gv[KPW][EPL], xq[QPW][EPL], xk[KPW][EPL];
+#pragma unroll
+  for (int t = 0; t < QPW; ++t) {
+    load_epl<EPL>(dq + (m * NH + warp + 8 * t) * HD + e0, gq[t]);
+    if (NORM) load_epl<EPL>(q_raw + m * pq + (warp + 8 * t) * HD + e0, xq[t]);
+  }
+#pragma unroll
+  for (int t = 0; t < KPW; ++t) {
+    load_epl<EPL>(dk + (m * NKV + warp + 8 * t) * HD + e0, gk[t]);
+    load_epl<EPL>(dv + (m * NKV + warp + 8 * t) * HD + e0, gv[t]);
+    if (NORM) load_epl<EPL>(k_raw + m * pk + (warp + 8 * t) * HD + e0, xk[t]);
+  }
+  float wq[EPL], wk[EPL];
+  if (NORM) {
+    load_epl<EPL>(qw + e0, wq);
+    load_epl<EPL>(kw + e0, wk);
+  }
+  const int p = pos[m];
+  const float* csr = cs + (size_t)p * HALF;
+  const float* snr = sn + (size_t)p * HALF;
+  float c[EPL], sg[EPL];  // sin signed for the FORWARD rotation; the inverse subtracts
+  if (NEOX) {
+    const bool first = e0 < HALF;
+    float sv_[EPL];
+    load_epl<EPL>(csr + (first ? e0 : e0 - HALF), c);
+    load_epl<EPL>(snr + (first ? e0 : e0 - HALF), sv_);
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) sg[k] = first ? -sv_[k] : sv_[k];
+  } else {
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) {
+      c[k] = csr[(e0 + k) >> 1];
+      const float t = snr[(e0 + k) >> 1];
+      sg[k] = (k & 1) ? t : -t;
+    }
+  }
+  auto back = [&](float* g, const float* xr, const float* w) -> float {
+    float o[EPL];
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) {
+      const float partner = NEOX ? __shfl_xor_sync(0xffffffffu, g[k], 16) : g[k ^ 1];
+      o[k] = g[k] * c[k] + partner * (sg[k] * -1.f);
+    }
+    if (NORM) {
+      float ss = 0.f, gx = 0.f;
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) { ss += xr[k] * xr[k]; gx += o[k] * w[k] * xr[k]; }
+      ss = warp_sum(ss);
+      gx = warp_sum(gx);
+      const float ir = 1.0f / sqrtf(ss / (float)HD + eps);
+      const float cc = gx * ir * ir * ir / (float)HD;
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) o[k] = o[k] * w[k] * ir - xr[k] * cc;
+    }
+    float mx = 0.f;
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) { g[k] = o[k]; mx = fmaxf(mx, fabsf(o[k])); }
+    return mx;
+  };
+  float mx[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+  for (int t = 0; t < QPW; ++t) mx[0] = fmaxf(mx[0], back(gq[t], xq[t], wq));
+#pragma unroll
+  for (int t = 0; t < KPW; ++t) mx[1] = fmaxf(mx[1], back(gk[t], xk[t], wk));
+#pragma unroll
+  for (int t = 0; t < KPW; ++t)
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) mx[2] = fmaxf(mx[2], fabsf(gv[t][k]));
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    const float v = warp_max(mx[k]);
+    if (lane == 0) wmax[k][warp] = v;
+  }
+  __syncthreads();
+  float s3[3], inv[3];
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) v = fmaxf(v, wmax[k][w]);
+    s3[k] = v;
+  }
+  if (common) s3[0] = s3[1] = s3[2] = fmaxf(s3[0], fmaxf(s3[1], s3[2]));
+  if (threadIdx.x == 0) { sq[m] = s3[0]; sk[m] = s3[1]; sv[m] = s3[2]; }  // 0 for an all-zero row
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    s3[k] = s3[k] > 0.f ? s3[k] : 1.f;
+    inv[k] = 1.f / s3[k];
+  }
+  float o[EPL];
+#pragma unroll
+  for (int t = 0; t < QPW; ++t) {
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) o[k] = gq[t][k] * inv[0];
+    store_epl_h<EPL>(dq16 + m * oq + (warp + 8 * t) * HD + e0, o);
+  }
+#pragma unroll
+  for (int t = 0; t < KPW; ++t) {
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) o[k] = gk[t][k] * inv[1];
+    store_epl_h<EPL>(dk16 + m * ok + (warp + 8 * t) * HD + e0, o);
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) o[k] = gv[t][k] * inv[2];
+    store_epl_h<EPL>(dv16 + m * ov + (warp + 8 * t) * HD + e0, o);
+  }
+}
+
 // the shapes the register-resident kernels cover
 static bool rope_reg_ok(int nh, int nkv, int hd, int rot, int neox, int* epl, int* hpw) {
   if (hd != 64 && hd != 128) return false;
@@ -685,6 +885,27 @@ void launch_qk_rope_fwd(const float* q_raw, const float* k_raw, const float* v_r
   int epl = 0, hpw = 0;
   // raw_pitch = 0: three separate row-major matrices; else one row pitch for all three (slices of one matrix)
   const size_t pq = raw_pitch ? raw_pitch : (size_t)nh * hd, pk = raw_pitch ? raw_pitch : (size_t)nkv * hd, pv = pk;
+  if (hd == 128 && rot == hd && (qw != nullptr) == (kw != nullptr) && nh % 8 == 0 && nkv % 8 == 0) {
+    const int qpw = nh / 8, kpw = nkv / 8;
+#define RT_ROPE_FAST(Q, K)                                                                                                        \
+  if (qpw == Q && kpw == K) {                                                                                                     \
+    if (neox) {                                                                                                                   \
+      if (qw) pdl(qk_rope_fwd_fast_kernel<4, Q, K, true, true>, M, 256, 0, st)(q_raw, k_raw, v_raw, pq, pk, pv, qw, kw, pos, cs, sn, eps, q16, k16, v16);   \
+      else pdl(qk_rope_fwd_fast_kernel<4, Q, K, true, false>, M, 256, 0, st)(q_raw, k_raw, v_raw, pq, pk, pv, qw, kw, pos, cs, sn, eps, q16, k16, v16);     \
+    } else {                                                                                                                      \
+      if (qw) pdl(qk_rope_fwd_fast_kernel<4, Q, K, false, true>, M, 256, 0, st)(q_raw, k_raw, v_raw, pq, pk, pv, qw, kw, pos, cs, sn, eps, q16, k16, v16);  \
+      else pdl(qk_rope_fwd_fast_kernel<4, Q, K, false, false>, M, 256, 0, st)(q_raw, k_raw, v_raw, pq, pk, pv, qw, kw, pos, cs, sn, eps, q16, k16, v16);    \
+    }                                                                                                                             \
+    RT_COUNT_LAUNCH(1);                                                                                                           \
+    return;                                                                                                                       \
+  }
+    RT_ROPE_FAST(2, 1)
+    RT_ROPE_FAST(3, 1)
+    RT_ROPE_FAST(4, 1)
+    RT_ROPE_FAST(4, 2)
+    RT_ROPE_FAST(1, 1)
+#undef RT_ROPE_FAST
+  }
   if (rope_reg_ok(nh, nkv, hd, rot, neox, &epl, &hpw)) {
 #define RT_ROPE_FWD(E, H) pdl(qk_rope_fwd_reg_kernel<E, H>, M, 256, 0, st)(q_raw, k_raw, v_raw, pq, pk, pv, qw, kw, pos, cs, sn, nh, nkv, rot, neox, eps, q16, k16, v16)
     if (epl == 4) { if (hpw == 4) RT_ROPE_FWD(4, 4); else if (hpw == 6) RT_ROPE_FWD(4, 6); else RT_ROPE_FWD(4, 8); }
@@ -807,6 +1028,29 @@ void launch_qk_rope_bwd(const float* dq, const float* dk, const float* dv, const
   const size_t pq = raw_pitch ? raw_pitch : (size_t)nh * hd, pk = raw_pitch ? raw_pitch : (size_t)nkv * hd;
   const size_t oq = out_pitch ? out_pitch : (size_t)nh * hd, ok = out_pitch ? out_pitch : (size_t)nkv * hd, ov = ok;
   const int common = out_pitch ? 1 : 0;
+  if (hd == 128 && rot == hd && (qw != nullptr) == (kw != nullptr) && nh % 8 == 0 && nkv % 8 == 0) {
+    const int qpw = nh / 8, kpw = nkv / 8;
+#define RT_ROPE_BFAST_ARGS (dq, dk, dv, q_raw, k_raw, pq, pk, oq, ok, ov, common, qw, kw, pos, cs, sn, eps, dq16, dk16, dv16, sq, sk, sv)
+#define RT_ROPE_BFAST(Q, K)                                                                            \
+  if (qpw == Q && kpw == K) {                                                                          \
+    if (neox) {                                                                                        \
+      if (qw) pdl(qk_rope_bwd_fast_kernel<4, Q, K, true, true>, M, 256, 0, st) RT_ROPE_BFAST_ARGS;     \
+      else pdl(qk_rope_bwd_fast_kernel<4, Q, K, true, false>, M, 256, 0, st) RT_ROPE_BFAST_ARGS;       \
+    } else {                                                                                           \
+      if (qw) pdl(qk_rope_bwd_fast_kernel<4, Q, K, false, true>, M, 256, 0, st) RT_ROPE_BFAST_ARGS;    \
+      else pdl(qk_rope_bwd_fast_kernel<4, Q, K, false, false>, M, 256, 0, st) RT_ROPE_BFAST_ARGS;      \
+    }                                                                                                  \
+    RT_COUNT_LAUNCH(1);                                                                                \
+    return;                                                                                            \
+  }
+    RT_ROPE_BFAST(2, 1)
+    RT_ROPE_BFAST(3, 1)
+    RT_ROPE_BFAST(4, 1)
+    RT_ROPE_BFAST(4, 2)
+    RT_ROPE_BFAST(1, 1)
+#undef RT_ROPE_BFAST
+#undef RT_ROPE_BFAST_ARGS
+  }
   if (rope_reg_ok(nh, nkv, hd, rot, neox, &epl, &hpw)) {
 #define RT_ROPE_BWD(E, H) pdl(qk_rope_bwd_reg_kernel<E, H>, M, 256, 0, st)(dq, dk, dv, q_raw, k_raw, pq, pk, oq, ok, ov, common, qw, kw, pos, cs, sn, nh, nkv, rot, neox, eps, dq16, dk16, dv16, sq, sk, sv)
     if (epl == 4) { if (hpw == 4) RT_ROPE_BWD(4, 4); else if (hpw == 6) RT_ROPE_BWD(4, 6); else RT_ROPE_BWD(4, 8); }
@@ -946,8 +1190,16 @@ __global__ void swiglu_bwd_cached_kernel(const DT* __restrict__ dh, const float*
       for (int k = 0; k < 8; ++k) { mg = fmaxf(mg, fabsf(a[c][k])); mu = fmaxf(mu, fabsf(b[c][k])); }
     }
   }
-  mg = block_max(mg);
-  mu = block_max(mu);
+  {  // both row maxima through one barrier (magnitudes: 0 is the identity)
+    __shared__ float shg[32], shu[32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (int)(blockDim.x >> 5);
+    mg = warp_max(mg);
+    mu = warp_max(mu);
+    if (lane == 0) { shg[w] = mg; shu[w] = mu; }
+    __syncthreads();
+    mg = mu = 0.f;
+    for (int k = 0; k < nw; ++k) { mg = fmaxf(mg, shg[k]); mu = fmaxf(mu, shu[k]); }
+  }
   if (common) mg = mu = fmaxf(mg, mu);  // gate and up gradients form ONE matrix with one scale per row
   const float s_g = mg > 0.f ? mg : 1.f, s_u = mu > 0.f ? mu : 1.f;
   const float ig = 1.f / s_g, iu = 1.f / s_u;
@@ -1011,7 +1263,9 @@ template <typename DT>
 static void launch_swiglu_bwd_t(const DT* dh, const float* in_scale, const __half* g, const __half* u, size_t gp, int rows,
                                 int ff, __half* dg16, __half* du16, size_t op, int common, float* sg, float* su,
                                 cudaStream_t st) {
-  if ((ff & 7) == 0 && ff <= 2 * 8 * 256) pdl(swiglu_bwd_cached_kernel<2, DT>, rows, 256, 0, st)(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
+  // rows that fill three chunks of 128 threads exactly (3072) leave no thread idle that way
+  if ((ff & 7) == 0 && ff > 2 * 8 * 128 && ff <= 3 * 8 * 128) pdl(swiglu_bwd_cached_kernel<3, DT>, rows, 128, 0, st)(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
+  else if ((ff & 7) == 0 && ff <= 2 * 8 * 256) pdl(swiglu_bwd_cached_kernel<2, DT>, rows, 256, 0, st)(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
   else if ((ff & 7) == 0 && ff <= 3 * 8 * 512) pdl(swiglu_bwd_cached_kernel<3, DT>, rows, 512, 0, st)(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
   else swiglu_bwd_kernel<DT><<<rows, 256, 0, st>>>(dh, in_scale, g, u, gp, ff, dg16, du16, op, common, sg, su);
   RT_COUNT_LAUNCH(1);
