@@ -957,24 +957,43 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   }
 }
 
-// delta[h, m] = sum_d O * dO (the row sum of P * dP, src/attention.rs:282-287)
+// delta[h, m] = sum_d O * dO (the row sum of P * dP, src/attention.rs:282-287).  A pure stream:
+// HD / 8 lanes share a row with one 16-byte load of each operand per lane, four rows per lane
+// group in flight.
 template <int HD>
 __global__ void attn_delta_tc_kernel(const __half* __restrict__ o, const __half* __restrict__ dO, int M, int nh,
                                      float* __restrict__ delta) {
   pdl_entry();
-  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (w >= M * nh) return;
-  const int m = w / nh, h = w % nh;
-  const __half* a = o + ((size_t)m * nh + h) * HD;
-  const __half* b = dO + ((size_t)m * nh + h) * HD;
-  float s = 0.f;
-  for (int i = lane * 2; i < HD; i += 64) {
-    float2 x = __half22float2(*(const __half2*)(a + i)), y = __half22float2(*(const __half2*)(b + i));
-    s += x.x * y.x + x.y * y.y;
+  constexpr int LPR = HD / 8, RPW = 32 / LPR, UN = 4;
+  const int lane = threadIdx.x & 31, sub = lane % LPR, grp = lane / LPR;
+  const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long total = (long long)M * nh, row0 = wg * (UN * RPW) + grp;
+  uint4 av[UN], bv[UN];
+#pragma unroll
+  for (int u = 0; u < UN; ++u) {
+    const long long r = row0 + u * RPW;
+    if (r < total) {
+      av[u] = *(const uint4*)(o + r * HD + sub * 8);
+      bv[u] = *(const uint4*)(dO + r * HD + sub * 8);
+    } else {
+      av[u] = bv[u] = make_uint4(0u, 0u, 0u, 0u);
+    }
   }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) delta[(size_t)h * M + m] = s;
+  for (int u = 0; u < UN; ++u) {
+    const __half2* a2 = (const __half2*)&av[u];
+    const __half2* b2 = (const __half2*)&bv[u];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 x = __half22float2(a2[k]), y = __half22float2(b2[k]);
+      s += x.x * y.x + x.y * y.y;
+    }
+#pragma unroll
+    for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    const long long r = row0 + u * RPW;
+    if (sub == 0 && r < total) delta[(size_t)(r % nh) * M + (size_t)(r / nh)] = s;
+  }
 }
 
 template <int HD>
@@ -1000,8 +1019,9 @@ int bwd_tc_impl(rt_ctx* c, const __half* q, const __half* k, const __half* v, co
   if (tensor_map_f16_2d(c, &tv64, v, (uint64_t)M, (uint64_t)nkv * HD, 64, 64)) return 3;
   const float scale = 1.0f / sqrtf((float)HD);
   cudaStream_t st = c->stream;
-  const int warps = M * nh;
-  pdl(attn_delta_tc_kernel<HD>, (warps * 32 + 255) / 256, 256, 0, st)(o, dO, M, nh, delta);
+  // one warp takes 4 passes of 32 / (HD / 8) rows
+  const long long delta_warps = ((long long)M * nh + (4 * 32 / (HD / 8)) - 1) / (4 * 32 / (HD / 8));
+  pdl(attn_delta_tc_kernel<HD>, (unsigned)((delta_warps * 32 + 255) / 256), 256, 0, st)(o, dO, M, nh, delta);
   dim3 gkv((M + 127) / 128, nkv), gq((M + BM - 1) / BM, nh);
   pdl(attn_bwd_dkdv_tc_kernel<HD>, gkv, BWD_THREADS, LK::TOTAL, st)(tk128, tv128, tq64, tdo64, do_scale, row_scale, lse, delta, seq_start, gap,
                                                           M, nh, nkv, scale, dk, dv, c->status_dev);
